@@ -1,0 +1,82 @@
+"""ctypes binding of the C-ABI declared in include/nn_b200.h."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+class NnbError(RuntimeError):
+    """A C-ABI call returned a non-zero nnb_status."""
+
+
+def lib_path() -> str:
+    return os.path.join(_HERE, "libnn-b200.so")
+
+
+_lib = None
+
+_P = C.c_void_p
+_SZ = C.c_size_t
+_I = C.c_int
+
+# name -> (restype, argtypes); status-returning unless noted
+_SIGNATURES = {
+    "nnb_last_error": (C.c_char_p, []),
+    "nnb_engine_create": (_I, [_I, C.POINTER(_P)]),
+    "nnb_engine_destroy": (None, [_P]),
+    "nnb_engine_describe": (_I, [_P, C.c_char_p, _SZ]),
+    "nnb_engine_sync": (_I, [_P]),
+    "nnb_engine_set_stream": (_I, [_P, _P]),
+    "nnb_engine_stream": (_P, [_P]),
+    "nnb_engine_launch_count": (C.c_ulonglong, [_P]),
+    "nnb_alloc": (_I, [_P, _SZ, C.POINTER(_P)]),
+    "nnb_free": (_I, [_P, _P]),
+    "nnb_upload": (_I, [_P, _P, _P, _SZ]),
+    "nnb_download": (_I, [_P, _P, _P, _SZ]),
+    "nnb_zero": (_I, [_P, _P, _SZ]),
+    "nnb_absmean_tau": (_I, [_P, _P, _SZ, _SZ, _P]),
+    "nnb_trit_pack": (_I, [_P, _P, _P, _SZ, _SZ, _P]),
+    "nnb_col_absmax_scale": (_I, [_P, _P, _SZ, _SZ, _P]),
+    "nnb_quantize_i8": (_I, [_P, _P, _SZ, _SZ, _P, _I, _P]),
+    "nnb_unpack_i8": (_I, [_P, _P, _SZ, _SZ, _P]),
+    "nnb_matmul_q_i8": (_I, [_P, _P, _P, _P, _P, _SZ, _SZ, _SZ, _P, _P]),
+    "nnb_matmul_q": (_I, [_P, _P, _P, _P, _SZ, _SZ, _SZ, _P]),
+    "nnb_matmul_q_t": (_I, [_P, _P, _P, _P, _SZ, _SZ, _SZ, _P]),
+    "nnb_actq_bytes": (_SZ, [_SZ, _SZ]),
+    "nnb_act_quant_tm": (_I, [_P, _P, _I, _SZ, _SZ, _P, _P, _P]),
+    "nnb_actq_to_plain": (_I, [_P, _P, _SZ, _SZ, _P]),
+    "nnb_bitlinear_fwd_tm": (_I, [_P, _P, _P, _P, _P, _P, _P, _SZ, _SZ, _SZ, _P, _I, _P]),
+    "nnb_bitlinear_fwd_tm_stack": (_I, [_P, _P, _SZ, _P, _P, _P, _P, _P, _SZ, _SZ, _SZ, _SZ, _P, _SZ, _I]),
+    "nnb_bitlinear_fwd_host": (_I, [_P, _P, _P, _P, _P, _SZ, _SZ, _SZ, _P]),
+}
+
+
+def exported_symbols() -> list[str]:
+    return sorted(_SIGNATURES)
+
+
+def lib() -> C.CDLL:
+    """Load libnn-b200.so (once).  Raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        path = lib_path()
+        if not os.path.exists(path):
+            raise NnbError(
+                f"{path} is missing: build it with `python neuralnet.cpp_b200/build.py` "
+                "(nvcc, sm_100a). This engine has no CPU fallback."
+            )
+        handle = C.CDLL(path)
+        for name, (res, args) in _SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def check(status: int) -> None:
+    if status != 0:
+        msg = lib().nnb_last_error()
+        raise NnbError(f"nnb_status {status}: {msg.decode() if msg else '?'}")

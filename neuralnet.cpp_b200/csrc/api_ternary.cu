@@ -1,0 +1,122 @@
+// api_ternary.cu — C-ABI entry points of the ternary linear operators.
+#include "common.cuh"
+
+using namespace nnb;
+
+extern "C" {
+
+nnb_status nnb_absmean_tau(nnb_engine* e, const float* d_latent, size_t rows, size_t k, float* d_tau)
+{
+    NNB_REQUIRE(e, "engine is NULL");
+    return launch_absmean_tau(e, d_latent, rows, k, d_tau);
+}
+
+nnb_status nnb_trit_pack(nnb_engine* e, const float* d_latent, const float* d_tau, size_t rows,
+                         size_t k, uint32_t* d_packed)
+{
+    NNB_REQUIRE(e, "engine is NULL");
+    return launch_trit_pack(e, d_latent, d_tau, rows, k, d_packed);
+}
+
+nnb_status nnb_col_absmax_scale(nnb_engine* e, const float* d_x, size_t k, size_t n, float* d_s)
+{
+    NNB_REQUIRE(e, "engine is NULL");
+    return launch_col_absmax_scale(e, d_x, k, n, d_s);
+}
+
+nnb_status nnb_quantize_i8(nnb_engine* e, const float* d_x, size_t m, size_t n, const float* d_scale,
+                           int col_scale, uint32_t* d_out)
+{
+    NNB_REQUIRE(e, "engine is NULL");
+    return launch_quantize_i8(e, d_x, m, n, d_scale, col_scale, d_out);
+}
+
+nnb_status nnb_unpack_i8(nnb_engine* e, const uint32_t* d_packed, size_t m, size_t n, float* d_out)
+{
+    NNB_REQUIRE(e, "engine is NULL");
+    return launch_unpack_i8(e, d_packed, m, n, d_out);
+}
+
+nnb_status nnb_matmul_q_i8(nnb_engine* e, const uint32_t* d_wq, const float* d_tau,
+                           const uint32_t* d_xq, const float* d_s, size_t rows, size_t k, size_t n,
+                           float* d_y, int32_t* d_acc)
+{
+    NNB_REQUIRE(e, "engine is NULL");
+    return launch_matmul_q_i8_ref(e, d_wq, d_tau, d_xq, d_s, rows, k, n, d_y, d_acc);
+}
+
+nnb_status nnb_matmul_q(nnb_engine* e, const uint32_t* d_wq, const float* d_tau, const float* d_x,
+                        size_t rows, size_t k, size_t n, float* d_c)
+{
+    NNB_REQUIRE(e, "engine is NULL");
+    return launch_matmul_q_ref(e, d_wq, d_tau, d_x, rows, k, n, d_c);
+}
+
+nnb_status nnb_matmul_q_t(nnb_engine* e, const uint32_t* d_wq, const float* d_tau, const float* d_b,
+                          size_t rows, size_t mcols, size_t n, float* d_c)
+{
+    NNB_REQUIRE(e, "engine is NULL");
+    return launch_matmul_q_t_ref(e, d_wq, d_tau, d_b, rows, mcols, n, d_c);
+}
+
+size_t nnb_actq_bytes(size_t t, size_t k) { return t * k; }
+
+nnb_status nnb_act_quant_tm(nnb_engine* e, const void* d_x, nnb_dtype dtype, size_t t, size_t k,
+                            int8_t* d_q, float* d_s, int32_t* d_qsum)
+{
+    NNB_REQUIRE(e, "engine is NULL");
+    return launch_act_quant_tm(e, d_x, dtype, t, k, d_q, d_s, d_qsum);
+}
+
+nnb_status nnb_actq_to_plain(nnb_engine* e, const int8_t* d_q, size_t t, size_t k, int8_t* d_plain)
+{
+    NNB_REQUIRE(e, "engine is NULL");
+    return launch_actq_to_plain(e, d_q, t, k, d_plain);
+}
+
+nnb_status nnb_bitlinear_fwd_tm(nnb_engine* e, const uint32_t* d_wq, const float* d_tau,
+                                const float* d_bias, const int8_t* d_q, const float* d_s,
+                                const int32_t* d_qsum, size_t t, size_t k, size_t out, void* d_y,
+                                nnb_dtype dtype, int32_t* d_acc)
+{
+    NNB_REQUIRE(e, "engine is NULL");
+    return launch_bitlinear_fwd_tm(e, d_wq, 0, d_tau, d_bias, d_q, d_s, d_qsum, 1, t, k, out, d_y, 0,
+                                   dtype, d_acc);
+}
+
+nnb_status nnb_bitlinear_fwd_tm_stack(nnb_engine* e, const uint32_t* d_wq, size_t wq_stride_words,
+                                      const float* d_tau, const float* d_bias, const int8_t* d_q,
+                                      const float* d_s, const int32_t* d_qsum, size_t n_mats,
+                                      size_t t, size_t k, size_t out, void* d_y,
+                                      size_t y_stride_elems, nnb_dtype dtype)
+{
+    NNB_REQUIRE(e, "engine is NULL");
+    return launch_bitlinear_fwd_tm(e, d_wq, wq_stride_words, d_tau, d_bias, d_q, d_s, d_qsum, n_mats,
+                                   t, k, out, d_y, y_stride_elems, dtype, nullptr);
+}
+
+nnb_status nnb_bitlinear_fwd_host(nnb_engine* e, const uint32_t* d_wq, const float* d_tau,
+                                  const float* d_bias, const float* h_x, size_t t, size_t k,
+                                  size_t out, float* h_y)
+{
+    NNB_REQUIRE(e && h_x && h_y, "bitlinear_fwd_host: NULL argument");
+    NNB_REQUIRE(t > 0 && k > 0 && k % 64 == 0 && out > 0, "bitlinear_fwd_host: bad shape");
+    auto al = [](size_t v) { return (v + 255) & ~(size_t)255; };
+    const size_t x_b = al(t * k * 4), q_b = al(t * k), s_b = al(t * 4), y_b = al(t * out * 4);
+    NNB_TRY(e->ensure_scratch(x_b + q_b + 2 * s_b + y_b));
+    unsigned char* base = (unsigned char*)e->scratch;
+    float* d_x = (float*)base;
+    int8_t* d_q = (int8_t*)(base + x_b);
+    float* d_s = (float*)(base + x_b + q_b);
+    int32_t* d_qsum = (int32_t*)(base + x_b + q_b + s_b);
+    float* d_y = (float*)(base + x_b + q_b + 2 * s_b);
+    NNB_CUDA(cudaMemcpyAsync(d_x, h_x, t * k * 4, cudaMemcpyHostToDevice, e->stream));
+    NNB_TRY(launch_act_quant_tm(e, d_x, NNB_F32, t, k, d_q, d_s, d_qsum));
+    NNB_TRY(launch_bitlinear_fwd_tm(e, d_wq, 0, d_tau, d_bias, d_q, d_s, d_qsum, 1, t, k, out, d_y, 0,
+                                    NNB_F32, nullptr));
+    NNB_CUDA(cudaMemcpyAsync(h_y, d_y, t * out * 4, cudaMemcpyDeviceToHost, e->stream));
+    NNB_CUDA(cudaStreamSynchronize(e->stream));
+    return NNB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,100 @@
+// common.cuh — shared declarations of the engine's translation units.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include <string>
+
+#include "nn_b200.h"
+
+namespace nnb {
+
+// thread-local error text behind nnb_last_error()
+void set_error(const char* fmt, ...);
+const char* get_error();
+
+#define NNB_FAIL(code, ...)           \
+    do {                              \
+        ::nnb::set_error(__VA_ARGS__); \
+        return (code);                \
+    } while (0)
+
+#define NNB_CUDA(call)                                                                       \
+    do {                                                                                     \
+        cudaError_t err__ = (call);                                                          \
+        if (err__ != cudaSuccess)                                                            \
+            NNB_FAIL(NNB_ERR_CUDA, "%s failed: %s (%s:%d)", #call, cudaGetErrorString(err__), \
+                     __FILE__, __LINE__);                                                    \
+    } while (0)
+
+#define NNB_CHECK_LAUNCH(name)                                                              \
+    do {                                                                                    \
+        cudaError_t err__ = cudaGetLastError();                                             \
+        if (err__ != cudaSuccess)                                                           \
+            NNB_FAIL(NNB_ERR_CUDA, "launch of %s failed: %s", name, cudaGetErrorString(err__)); \
+    } while (0)
+
+#define NNB_REQUIRE(cond, ...)                         \
+    do {                                               \
+        if (!(cond)) NNB_FAIL(NNB_ERR_INVALID, __VA_ARGS__); \
+    } while (0)
+
+#define NNB_TRY(expr)                  \
+    do {                               \
+        nnb_status st__ = (expr);      \
+        if (st__ != NNB_OK) return st__; \
+    } while (0)
+
+inline size_t ceil_div(size_t a, size_t b) { return (a + b - 1) / b; }
+
+}  // namespace nnb
+
+// The engine object behind the opaque C handle.
+struct nnb_engine {
+    int device = 0;
+    int sm_count = 0;
+    cudaStream_t own_stream = nullptr;
+    cudaStream_t stream = nullptr;  // the stream in use (own_stream or the caller's)
+    // grow-only scratch arena for operators that need temporaries
+    void* scratch = nullptr;
+    size_t scratch_bytes = 0;
+    // pinned staging for the *_host entry points
+    void* pinned = nullptr;
+    size_t pinned_bytes = 0;
+    // counts kernel launches issued through this engine (reported by the benchmark)
+    unsigned long long launches = 0;
+    std::string describe_text;
+
+    nnb_status ensure_scratch(size_t bytes);
+    nnb_status ensure_pinned(size_t bytes);
+};
+
+namespace nnb {
+
+// ---- ternary.cu: launchers (all enqueue on e->stream)
+nnb_status launch_absmean_tau(nnb_engine* e, const float* latent, size_t rows, size_t k, float* tau);
+nnb_status launch_trit_pack(nnb_engine* e, const float* latent, const float* tau, size_t rows,
+                            size_t k, uint32_t* packed);
+nnb_status launch_col_absmax_scale(nnb_engine* e, const float* x, size_t k, size_t n, float* s);
+nnb_status launch_quantize_i8(nnb_engine* e, const float* x, size_t m, size_t n, const float* scale,
+                              int col_scale, uint32_t* out);
+nnb_status launch_unpack_i8(nnb_engine* e, const uint32_t* packed, size_t m, size_t n, float* out);
+nnb_status launch_matmul_q_i8_ref(nnb_engine* e, const uint32_t* wq, const float* tau,
+                                  const uint32_t* xq, const float* s, size_t rows, size_t k,
+                                  size_t n, float* y, int32_t* acc);
+nnb_status launch_matmul_q_ref(nnb_engine* e, const uint32_t* wq, const float* tau, const float* x,
+                               size_t rows, size_t k, size_t n, float* c);
+nnb_status launch_matmul_q_t_ref(nnb_engine* e, const uint32_t* wq, const float* tau,
+                                 const float* b, size_t rows, size_t mcols, size_t n, float* c);
+nnb_status launch_act_quant_tm(nnb_engine* e, const void* x, nnb_dtype dtype, size_t t, size_t k,
+                               int8_t* q, float* s, int32_t* qsum);
+nnb_status launch_actq_to_plain(nnb_engine* e, const int8_t* q, size_t t, size_t k, int8_t* plain);
+nnb_status launch_bitlinear_fwd_tm(nnb_engine* e, const uint32_t* wq, size_t wq_stride_words,
+                                   const float* tau, const float* bias, const int8_t* q,
+                                   const float* s, const int32_t* qsum, size_t n_mats, size_t t,
+                                   size_t k, size_t out, void* y, size_t y_stride_elems,
+                                   nnb_dtype dtype, int32_t* acc);
+
+}  // namespace nnb

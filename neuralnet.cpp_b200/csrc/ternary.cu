@@ -1,0 +1,700 @@
+// ternary.cu — ternary (BitNet b1.58) linear: codecs, activation quantisation and the
+// int8 x 2-bit GEMM with int32 accumulation.
+//
+// Arithmetic contract (reference: include/neuralnet.cpp/compute_layer_bitlinear.hpp:443-455,
+// 637-667; src/int8_act_test.cpp:210-236; src/ternary_gemm_test.cpp:69-99):
+//   code = trit + 2 in {1,2,3}, weight j of a row at bits (word >> 2j) & 3, tail = code 2
+//   q = round_half_away(clamp(x / s, -127, 127)), NaN -> 0, s == 0 -> 0
+//   acc = sum_k trit * q in int32;  y = (tau * s) * float(acc) [+ bias], no FMA contraction
+//
+// Fast path layouts (token-major):
+//   weights  : the reference container itself, (out, K/16) words
+//   q        : (T, K) int8 where every 64-byte block along K is permuted so that a
+//              2-bit weight word needs only shift+mask to become tensor-core operands:
+//              dest[16*(j%4) + 4*(j/16) + (j/4)%4] = src[j], j in 0..63
+//   qsum     : (T) int32 row sums of q.  The kernel multiplies unsigned codes (0..3)
+//              with q on the tensor cores (u8 x s8) and subtracts 2*qsum afterwards:
+//              sum (code-2)*q = sum code*q - 2*sum q, exact in int32.
+#include "common.cuh"
+
+namespace nnb {
+
+// ------------------------------------------------------------------ helpers
+__device__ __forceinline__ uint32_t trit_code_of(float w, float tau)
+{
+    const float hi = __fmul_rn(tau, 0.5f);
+    const float lo = __fmul_rn(tau, -0.5f);
+    return w > hi ? 3u : (w < lo ? 1u : 2u);
+}
+
+__device__ __forceinline__ int i8_quantize(float x, float s)
+{
+    if (s == 0.0f) return 0;
+    float v = __fdiv_rn(x, s);
+    if (v != v) return 0;
+    v = fminf(fmaxf(v, -127.0f), 127.0f);
+    return (int)roundf(v);
+}
+
+__device__ __forceinline__ float warp_max(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+__device__ __forceinline__ int warp_sum_i(int v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_sum_f(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// position of source byte j (0..63) inside a permuted 64-byte block
+__host__ __device__ __forceinline__ int qperm_pos(int j)
+{
+    return 16 * (j & 3) + 4 * (j >> 4) + ((j >> 2) & 3);
+}
+
+// ------------------------------------------------- reference-layout kernels
+// tau_r = sum_k |W[r,k]| * (1/K): one warp per row, lanes stride k, tree reduce.
+__global__ void absmean_tau_kernel(const float* __restrict__ latent, size_t rows, size_t k,
+                                   float* __restrict__ tau)
+{
+    const size_t row = (size_t)blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const float inv = 1.0f / (float)k;
+    const float* p = latent + row * k;
+    float s = 0.0f;
+    for (size_t c = lane; c < k; c += 32) s += __fmul_rn(fabsf(p[c]), inv);
+    s = warp_sum_f(s);
+    if (lane == 0) tau[row] = s;
+}
+
+// one thread per packed word
+__global__ void trit_pack_kernel(const float* __restrict__ latent, const float* __restrict__ tau,
+                                 size_t rows, size_t k, uint32_t* __restrict__ packed)
+{
+    const size_t wpr = (k + 15) / 16;
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= rows * wpr) return;
+    const size_t r = idx / wpr, wi = idx % wpr;
+    const float t = tau[r];
+    const float* p = latent + r * k + wi * 16;
+    const size_t left = k - wi * 16;
+    uint32_t word = 0;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const uint32_t code = ((size_t)j < left) ? trit_code_of(p[j], t) : 2u;
+        word |= code << (2 * j);
+    }
+    packed[idx] = word;
+}
+
+// s_n = max_k |x[k,n]| * (1/127); x is (k, n): one thread per column, coalesced over n
+__global__ void col_absmax_scale_kernel(const float* __restrict__ x, size_t k, size_t n,
+                                        float* __restrict__ s)
+{
+    const size_t c = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= n) return;
+    float mx = 0.0f;
+    for (size_t r = 0; r < k; ++r) {
+        const float a = fabsf(x[r * n + c]);
+        if (a > mx) mx = a;
+    }
+    s[c] = __fmul_rn(mx, 1.0f / 127.0f);
+}
+
+__global__ void quantize_i8_kernel(const float* __restrict__ x, size_t m, size_t n,
+                                   const float* __restrict__ scale, int col_scale,
+                                   uint32_t* __restrict__ out)
+{
+    const size_t wpr = (n + 3) / 4;
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= m * wpr) return;
+    const size_t r = idx / wpr, wi = idx % wpr;
+    uint32_t word = 0;
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        const size_t c = wi * 4 + b;
+        if (c < n) {
+            const float sc = col_scale ? scale[c] : scale[r];
+            word |= (uint32_t)(uint8_t)(int8_t)i8_quantize(x[r * n + c], sc) << (8 * b);
+        }
+    }
+    out[idx] = word;
+}
+
+__global__ void unpack_i8_kernel(const uint32_t* __restrict__ packed, size_t m, size_t n,
+                                 float* __restrict__ out)
+{
+    const size_t wpr = (n + 3) / 4;
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= m * n) return;
+    const size_t r = idx / n, c = idx % n;
+    out[idx] = (float)(int8_t)((packed[r * wpr + c / 4] >> (8 * (c % 4))) & 0xFFu);
+}
+
+// Any-shape matmul_q_i8 on the reference containers: one thread per output, k ascending.
+__global__ void matmul_q_i8_ref_kernel(const uint32_t* __restrict__ wq,
+                                       const float* __restrict__ tau,
+                                       const uint32_t* __restrict__ xq, const float* __restrict__ s,
+                                       size_t rows, size_t k, size_t n, float* __restrict__ y,
+                                       int32_t* __restrict__ acc_out)
+{
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= rows * n) return;
+    const size_t m = idx / n, j = idx % n;
+    const size_t wpr_w = (k + 15) / 16, wpr_q = (n + 3) / 4;
+    int acc = 0;
+    for (size_t kk = 0; kk < k; ++kk) {
+        const int trit = (int)((wq[m * wpr_w + kk / 16] >> (2 * (kk % 16))) & 3u) - 2;
+        const int q = (int)(int8_t)((xq[kk * wpr_q + j / 4] >> (8 * (j % 4))) & 0xFFu);
+        acc += trit * q;
+    }
+    if (y) y[idx] = __fmul_rn(__fmul_rn(tau[m], s[j]), (float)acc);
+    if (acc_out) acc_out[idx] = acc;
+}
+
+// Any-shape matmul_q: C[m,n] = sum_k (tau_m * trit) * X[k,n], f32 accumulate, k ascending.
+__global__ void matmul_q_ref_kernel(const uint32_t* __restrict__ wq, const float* __restrict__ tau,
+                                    const float* __restrict__ x, size_t rows, size_t k, size_t n,
+                                    float* __restrict__ c)
+{
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= rows * n) return;
+    const size_t m = idx / n, j = idx % n;
+    const size_t wpr = (k + 15) / 16;
+    const float t = tau[m];
+    float acc = 0.0f;
+    for (size_t kk = 0; kk < k; ++kk) {
+        const float trit = (float)((int)((wq[m * wpr + kk / 16] >> (2 * (kk % 16))) & 3u) - 2);
+        acc = fmaf(__fmul_rn(t, trit), x[kk * n + j], acc);
+    }
+    c[idx] = acc;
+}
+
+// Any-shape matmul_q_t: C[m,n] = sum_k (tau_k * trit[k,m]) * B[k,n]
+__global__ void matmul_q_t_ref_kernel(const uint32_t* __restrict__ wq,
+                                      const float* __restrict__ tau, const float* __restrict__ b,
+                                      size_t rows, size_t mcols, size_t n, float* __restrict__ c)
+{
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= mcols * n) return;
+    const size_t m = idx / n, j = idx % n;
+    const size_t wpr = (mcols + 15) / 16;
+    float acc = 0.0f;
+    for (size_t kk = 0; kk < rows; ++kk) {
+        const float trit = (float)((int)((wq[kk * wpr + m / 16] >> (2 * (m % 16))) & 3u) - 2);
+        acc = fmaf(__fmul_rn(tau[kk], trit), b[kk * n + j], acc);
+    }
+    c[idx] = acc;
+}
+
+// ------------------------------------------------ token-major activation quant
+// One CTA per token: stage the row in shared memory, block absmax, quantise, write the
+// permuted int8 row and the int32 row sum.
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+act_quant_tm_kernel(const T* __restrict__ x, int k, int8_t* __restrict__ q, float* __restrict__ s,
+                    int32_t* __restrict__ qsum)
+{
+    extern __shared__ float row[];
+    __shared__ float red_f[8];
+    __shared__ int red_i[8];
+    const size_t tok = blockIdx.x;
+    const T* xr = x + tok * (size_t)k;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    float mx = 0.0f;
+    for (int i = tid; i < k; i += 256) {
+        const float v = to_f32<T>(xr[i]);
+        row[i] = v;
+        const float a = fabsf(v);
+        if (a > mx) mx = a;
+    }
+    mx = warp_max(mx);
+    if (lane == 0) red_f[warp] = mx;
+    __syncthreads();
+    mx = red_f[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) mx = fmaxf(mx, red_f[w]);
+    const float sc = __fmul_rn(mx, 1.0f / 127.0f);
+    // each thread writes whole 32-bit words of the permuted row
+    uint32_t* qrow = reinterpret_cast<uint32_t*>(q + tok * (size_t)k);
+    int local = 0;
+    for (int w = tid; w < k / 4; w += 256) {
+        const int blk = w >> 4, wd = w & 15;  // word wd of 64-byte block blk
+        const int i = wd >> 2, t = wd & 3;    // dest word = 4*i + t holds src 16t + 4b + i
+        uint32_t word = 0;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const int qi = i8_quantize(row[blk * 64 + 16 * t + 4 * b + i], sc);
+            local += qi;
+            word |= (uint32_t)(uint8_t)(int8_t)qi << (8 * b);
+        }
+        qrow[w] = word;
+    }
+    local = warp_sum_i(local);
+    if (lane == 0) red_i[warp] = local;
+    __syncthreads();
+    if (tid == 0) {
+        int tot = 0;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) tot += red_i[w];
+        qsum[tok] = tot;
+        s[tok] = sc;
+    }
+}
+
+__global__ void actq_to_plain_kernel(const int8_t* __restrict__ q, size_t total,
+                                     int8_t* __restrict__ plain)
+{
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const size_t blk = idx >> 6;
+    const int j = (int)(idx & 63);
+    plain[idx] = q[(blk << 6) + qperm_pos(j)];
+}
+
+// ------------------------------------------------------- tensor-core GEMM
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid)
+{
+    const uint32_t sa = (uint32_t)__cvta_generic_to_shared(smem);
+    const int sz = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(sa), "l"(gmem), "r"(sz));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait()
+{
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem)
+{
+    const uint32_t sa = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(sa));
+}
+
+// D += A(u8 codes, 16x32) * B(s8, 32x8)
+__device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                         uint32_t a3, uint32_t b0, uint32_t b1)
+{
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};\n"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <typename OutT>
+__device__ __forceinline__ void store_out(OutT* p, float v);
+template <>
+__device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
+template <>
+__device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16* p, float v)
+{
+    *p = __float2bfloat16_rn(v);
+}
+
+// CTA tile: BM output rows x BN tokens, BK features per pipeline stage.
+// Warps: WM x WN over the tile, WK ways over the 64-feature blocks of a stage
+// (WK > 1 gives a small matrix enough warps; partial sums meet in shared memory).
+template <int BM, int BN, int BK, int STAGES, int WM, int WN, int WK, typename OutT>
+__global__ void __launch_bounds__(WM* WN* WK * 32)
+bitlinear_mma_kernel(const uint32_t* __restrict__ wq, size_t wq_stride_words,
+                     const float* __restrict__ tau, const float* __restrict__ bias,
+                     const int8_t* __restrict__ q, const float* __restrict__ s,
+                     const int32_t* __restrict__ qsum, int T, int K, int OUT, OutT* __restrict__ y,
+                     size_t y_stride_elems, int32_t* __restrict__ acc_out)
+{
+    constexpr int THREADS = WM * WN * WK * 32;
+    constexpr int A_ROW_BYTES = BK / 4;          // 2 bits per feature
+    constexpr int A_UNITS = BK / 64;             // 16-byte units per A row
+    constexpr int B_UNITS = BK / 16;             // 16-byte units per B row
+    constexpr int A_STAGE = BM * A_ROW_BYTES;
+    constexpr int B_STAGE = BN * BK;
+    constexpr int TM = BM / WM, TN = BN / WN;    // warp tile
+    constexpr int MT = TM / 16, NT = TN / 8;
+    constexpr int NBLK = BK / 64;
+    static_assert(BK % 128 == 0, "B swizzle needs 8 units per row");
+    static_assert(TM % 16 == 0 && TN % 8 == 0, "warp tile");
+    static_assert(NBLK % WK == 0, "k split");
+
+    extern __shared__ __align__(128) unsigned char smem[];
+    unsigned char* As = smem;
+    unsigned char* Bs = smem + STAGES * A_STAGE;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wk = warp % WK, wn = (warp / WK) % WN, wm = warp / (WK * WN);
+    const int g = lane >> 2, t4 = lane & 3;
+    const int row0 = blockIdx.x * BM, tok0 = blockIdx.y * BN;
+    const int mat = blockIdx.z;
+    wq += (size_t)mat * wq_stride_words;
+    tau += (size_t)mat * OUT;
+    if (bias) bias += (size_t)mat * OUT;
+    y += (size_t)mat * y_stride_elems;
+
+    const int words_per_row = K / 16;
+    const int ktiles = (K + BK - 1) / BK;
+
+    auto load_stage = [&](int slot, int kt) {
+        const int k0 = kt * BK;
+        unsigned char* as = As + slot * A_STAGE;
+        unsigned char* bs = Bs + slot * B_STAGE;
+        for (int i = tid; i < BM * A_UNITS; i += THREADS) {
+            const int r = i / A_UNITS, u = i % A_UNITS;
+            const int grow = row0 + r;
+            const bool ok = grow < OUT && (k0 + u * 64) < K;
+            const uint32_t* src =
+                wq + (size_t)(ok ? grow : 0) * words_per_row + (ok ? (k0 / 16 + u * 4) : 0);
+            int pu = u;
+            if (A_UNITS == 4) pu = u ^ ((r >> 1) & 3);
+            if (A_UNITS == 2) pu = u ^ ((r >> 2) & 1);
+            cp_async16(as + r * A_ROW_BYTES + pu * 16, src, ok);
+        }
+        for (int i = tid; i < BN * B_UNITS; i += THREADS) {
+            const int r = i / B_UNITS, u = i % B_UNITS;
+            const int gt = tok0 + r;
+            const bool ok = gt < T && (k0 + u * 16) < K;
+            const int8_t* src = q + (size_t)(ok ? gt : 0) * K + (ok ? (k0 + u * 16) : 0);
+            cp_async16(bs + r * BK + ((u ^ (r & 7)) * 16), src, ok);
+        }
+    };
+
+    int acc[MT][NT][4];
+#pragma unroll
+    for (int i = 0; i < MT; ++i)
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[i][j][c] = 0;
+
+#pragma unroll
+    for (int st = 0; st < STAGES - 1; ++st) {
+        if (st < ktiles) load_stage(st, st);
+        cp_async_commit();
+    }
+
+    for (int kt = 0; kt < ktiles; ++kt) {
+        cp_async_wait<STAGES - 2>();
+        __syncthreads();
+        {
+            const int nk = kt + STAGES - 1;
+            if (nk < ktiles) load_stage(nk % STAGES, nk);
+            cp_async_commit();
+        }
+        const unsigned char* as = As + (kt % STAGES) * A_STAGE;
+        const unsigned char* bs = Bs + (kt % STAGES) * B_STAGE;
+#pragma unroll
+        for (int bi = 0; bi < NBLK / WK; ++bi) {
+            const int blk = bi * WK + wk;
+            uint32_t bf[NT][4];
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const int r = wn * TN + nt * 8 + (lane & 7);
+                const int u = blk * 4 + (lane >> 3);
+                ldmatrix_x4(bf[nt], bs + r * BK + ((u ^ (r & 7)) * 16));
+            }
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                const int r_lo = wm * TM + mt * 16 + g, r_hi = r_lo + 8;
+                int pu_lo = blk, pu_hi = blk;
+                if (A_UNITS == 4) {
+                    pu_lo = blk ^ ((r_lo >> 1) & 3);
+                    pu_hi = blk ^ ((r_hi >> 1) & 3);
+                }
+                if (A_UNITS == 2) {
+                    pu_lo = blk ^ ((r_lo >> 2) & 1);
+                    pu_hi = blk ^ ((r_hi >> 2) & 1);
+                }
+                const uint32_t w_lo =
+                    *reinterpret_cast<const uint32_t*>(as + r_lo * A_ROW_BYTES + pu_lo * 16 + t4 * 4);
+                const uint32_t w_hi =
+                    *reinterpret_cast<const uint32_t*>(as + r_hi * A_ROW_BYTES + pu_hi * 16 + t4 * 4);
+                constexpr uint32_t MSK = 0x03030303u;
+                const uint32_t a0 = w_lo & MSK, a1 = w_hi & MSK;
+                const uint32_t a2 = (w_lo >> 2) & MSK, a3 = (w_hi >> 2) & MSK;
+                const uint32_t c0 = (w_lo >> 4) & MSK, c1 = (w_hi >> 4) & MSK;
+                const uint32_t c2 = (w_lo >> 6) & MSK, c3 = (w_hi >> 6) & MSK;
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    mma_u8s8(acc[mt][nt], a0, a1, a2, a3, bf[nt][0], bf[nt][1]);
+                    mma_u8s8(acc[mt][nt], c0, c1, c2, c3, bf[nt][2], bf[nt][3]);
+                }
+            }
+        }
+    }
+    cp_async_wait<0>();
+
+    if (WK > 1) {
+        // partial sums of the k-split warps meet in shared memory (pipeline buffers are free now)
+        __syncthreads();
+        int* red = reinterpret_cast<int*>(smem);
+        constexpr int PER_THREAD = MT * NT * 4;
+        const int group = warp / WK;  // (wm, wn) pair
+        if (wk > 0) {
+            int* dst = red + ((size_t)(group * (WK - 1) + (wk - 1)) * 32 + lane) * PER_THREAD;
+#pragma unroll
+            for (int i = 0; i < MT; ++i)
+#pragma unroll
+                for (int j = 0; j < NT; ++j)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) dst[(i * NT + j) * 4 + c] = acc[i][j][c];
+        }
+        __syncthreads();
+        if (wk > 0) return;
+#pragma unroll
+        for (int o = 1; o < WK; ++o) {
+            const int* src = red + ((size_t)(group * (WK - 1) + (o - 1)) * 32 + lane) * PER_THREAD;
+#pragma unroll
+            for (int i = 0; i < MT; ++i)
+#pragma unroll
+                for (int j = 0; j < NT; ++j)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) acc[i][j][c] += src[(i * NT + j) * 4 + c];
+        }
+    }
+
+    // epilogue: acc - 2*qsum, scale, bias, store token-major
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+            const int tok = tok0 + wn * TN + nt * 8 + t4 * 2 + cc;
+            if (tok >= T) continue;
+            const int qs2 = 2 * qsum[tok];
+            const float st = s[tok];
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int row = row0 + wm * TM + mt * 16 + g + h * 8;
+                    if (row >= OUT) continue;
+                    const int a = acc[mt][nt][h * 2 + cc] - qs2;
+                    float v = __fmul_rn(__fmul_rn(tau[row], st), (float)a);
+                    if (bias) v = __fadd_rn(v, bias[row]);
+                    store_out<OutT>(y + (size_t)tok * OUT + row, v);
+                    if (acc_out) acc_out[(size_t)tok * OUT + row] = a;
+                }
+            }
+        }
+    }
+}
+
+template <int BM, int BN, int BK, int STAGES, int WM, int WN, int WK, typename OutT>
+static nnb_status launch_cfg(nnb_engine* e, const uint32_t* wq, size_t wq_stride,
+                             const float* tau, const float* bias, const int8_t* q, const float* s,
+                             const int32_t* qsum, size_t n_mats, size_t t, size_t k, size_t out,
+                             OutT* y, size_t y_stride, int32_t* acc)
+{
+    constexpr int THREADS = WM * WN * WK * 32;
+    constexpr size_t pipe = (size_t)STAGES * (BM * (BK / 4) + BN * BK);
+    constexpr size_t red = WK > 1 ? (size_t)(WM * WN) * (WK - 1) * 32 * ((BM / WM / 16) * (BN / WN / 8) * 4) * 4 : 0;
+    constexpr size_t smem = pipe > red ? pipe : red;
+    auto kern = bitlinear_mma_kernel<BM, BN, BK, STAGES, WM, WN, WK, OutT>;
+    static bool configured = false;
+    if (!configured) {
+        NNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = true;
+    }
+    dim3 grid((unsigned)ceil_div(out, BM), (unsigned)ceil_div(t, BN), (unsigned)n_mats);
+    NNB_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "bitlinear_fwd: grid too large (t=%zu, n_mats=%zu)",
+                t, n_mats);
+    kern<<<grid, THREADS, smem, e->stream>>>(wq, wq_stride, tau, bias, q, s, qsum, (int)t, (int)k,
+                                             (int)out, y, y_stride, acc);
+    e->launches++;
+    NNB_CHECK_LAUNCH("bitlinear_mma_kernel");
+    return NNB_OK;
+}
+
+template <typename OutT>
+static nnb_status dispatch_fwd(nnb_engine* e, const uint32_t* wq, size_t wq_stride, const float* tau,
+                               const float* bias, const int8_t* q, const float* s,
+                               const int32_t* qsum, size_t n_mats, size_t t, size_t k, size_t out,
+                               OutT* y, size_t y_stride, int32_t* acc)
+{
+    if (t <= 8)
+        return launch_cfg<32, 8, 256, 4, 1, 1, 4, OutT>(e, wq, wq_stride, tau, bias, q, s, qsum,
+                                                         n_mats, t, k, out, y, y_stride, acc);
+    if (t <= 16)
+        return launch_cfg<32, 16, 256, 4, 1, 1, 4, OutT>(e, wq, wq_stride, tau, bias, q, s, qsum,
+                                                          n_mats, t, k, out, y, y_stride, acc);
+    if (t <= 32)
+        return launch_cfg<32, 32, 256, 4, 1, 1, 4, OutT>(e, wq, wq_stride, tau, bias, q, s, qsum,
+                                                          n_mats, t, k, out, y, y_stride, acc);
+    if (t <= 64)
+        return launch_cfg<64, 64, 128, 4, 2, 2, 1, OutT>(e, wq, wq_stride, tau, bias, q, s, qsum,
+                                                          n_mats, t, k, out, y, y_stride, acc);
+    return launch_cfg<128, 128, 128, 4, 2, 4, 1, OutT>(e, wq, wq_stride, tau, bias, q, s, qsum,
+                                                        n_mats, t, k, out, y, y_stride, acc);
+}
+
+// ------------------------------------------------------------------ launchers
+static inline unsigned blocks_for(size_t n, int threads) { return (unsigned)ceil_div(n, (size_t)threads); }
+
+nnb_status launch_absmean_tau(nnb_engine* e, const float* latent, size_t rows, size_t k, float* tau)
+{
+    NNB_REQUIRE(latent && tau && rows > 0 && k > 0, "absmean_tau: bad arguments");
+    absmean_tau_kernel<<<blocks_for(rows, 8), 256, 0, e->stream>>>(latent, rows, k, tau);
+    e->launches++;
+    NNB_CHECK_LAUNCH("absmean_tau_kernel");
+    return NNB_OK;
+}
+
+nnb_status launch_trit_pack(nnb_engine* e, const float* latent, const float* tau, size_t rows,
+                            size_t k, uint32_t* packed)
+{
+    NNB_REQUIRE(latent && tau && packed && rows > 0 && k > 0, "trit_pack: bad arguments");
+    const size_t words = rows * ceil_div(k, 16);
+    trit_pack_kernel<<<blocks_for(words, 256), 256, 0, e->stream>>>(latent, tau, rows, k, packed);
+    e->launches++;
+    NNB_CHECK_LAUNCH("trit_pack_kernel");
+    return NNB_OK;
+}
+
+nnb_status launch_col_absmax_scale(nnb_engine* e, const float* x, size_t k, size_t n, float* s)
+{
+    NNB_REQUIRE(x && s && k > 0 && n > 0, "col_absmax_scale: bad arguments");
+    col_absmax_scale_kernel<<<blocks_for(n, 128), 128, 0, e->stream>>>(x, k, n, s);
+    e->launches++;
+    NNB_CHECK_LAUNCH("col_absmax_scale_kernel");
+    return NNB_OK;
+}
+
+nnb_status launch_quantize_i8(nnb_engine* e, const float* x, size_t m, size_t n, const float* scale,
+                              int col_scale, uint32_t* out)
+{
+    NNB_REQUIRE(x && scale && out && m > 0 && n > 0, "quantize_i8: bad arguments");
+    const size_t words = m * ceil_div(n, 4);
+    quantize_i8_kernel<<<blocks_for(words, 256), 256, 0, e->stream>>>(x, m, n, scale, col_scale, out);
+    e->launches++;
+    NNB_CHECK_LAUNCH("quantize_i8_kernel");
+    return NNB_OK;
+}
+
+nnb_status launch_unpack_i8(nnb_engine* e, const uint32_t* packed, size_t m, size_t n, float* out)
+{
+    NNB_REQUIRE(packed && out && m > 0 && n > 0, "unpack_i8: bad arguments");
+    unpack_i8_kernel<<<blocks_for(m * n, 256), 256, 0, e->stream>>>(packed, m, n, out);
+    e->launches++;
+    NNB_CHECK_LAUNCH("unpack_i8_kernel");
+    return NNB_OK;
+}
+
+nnb_status launch_matmul_q_i8_ref(nnb_engine* e, const uint32_t* wq, const float* tau,
+                                  const uint32_t* xq, const float* s, size_t rows, size_t k,
+                                  size_t n, float* y, int32_t* acc)
+{
+    NNB_REQUIRE(wq && tau && xq && s && (y || acc) && rows > 0 && k > 0 && n > 0,
+                "matmul_q_i8: bad arguments");
+    matmul_q_i8_ref_kernel<<<blocks_for(rows * n, 128), 128, 0, e->stream>>>(wq, tau, xq, s, rows, k,
+                                                                             n, y, acc);
+    e->launches++;
+    NNB_CHECK_LAUNCH("matmul_q_i8_ref_kernel");
+    return NNB_OK;
+}
+
+nnb_status launch_matmul_q_ref(nnb_engine* e, const uint32_t* wq, const float* tau, const float* x,
+                               size_t rows, size_t k, size_t n, float* c)
+{
+    NNB_REQUIRE(wq && tau && x && c && rows > 0 && k > 0 && n > 0, "matmul_q: bad arguments");
+    matmul_q_ref_kernel<<<blocks_for(rows * n, 128), 128, 0, e->stream>>>(wq, tau, x, rows, k, n, c);
+    e->launches++;
+    NNB_CHECK_LAUNCH("matmul_q_ref_kernel");
+    return NNB_OK;
+}
+
+nnb_status launch_matmul_q_t_ref(nnb_engine* e, const uint32_t* wq, const float* tau,
+                                 const float* b, size_t rows, size_t mcols, size_t n, float* c)
+{
+    NNB_REQUIRE(wq && tau && b && c && rows > 0 && mcols > 0 && n > 0, "matmul_q_t: bad arguments");
+    matmul_q_t_ref_kernel<<<blocks_for(mcols * n, 128), 128, 0, e->stream>>>(wq, tau, b, rows, mcols,
+                                                                             n, c);
+    e->launches++;
+    NNB_CHECK_LAUNCH("matmul_q_t_ref_kernel");
+    return NNB_OK;
+}
+
+nnb_status launch_act_quant_tm(nnb_engine* e, const void* x, nnb_dtype dtype, size_t t, size_t k,
+                               int8_t* q, float* s, int32_t* qsum)
+{
+    NNB_REQUIRE(x && q && s && qsum && t > 0, "act_quant_tm: bad arguments");
+    NNB_REQUIRE(k > 0 && k % 64 == 0, "act_quant_tm: k=%zu must be a positive multiple of 64", k);
+    NNB_REQUIRE(k * 4 <= 96 * 1024, "act_quant_tm: k=%zu too large", k);
+    NNB_REQUIRE(((uintptr_t)q & 15) == 0, "act_quant_tm: q must be 16-byte aligned");
+    const size_t smem = k * sizeof(float);
+    if (dtype == NNB_F32) {
+        static bool cfg = false;
+        if (!cfg) {
+            NNB_CUDA(cudaFuncSetAttribute(act_quant_tm_kernel<float>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+            cfg = true;
+        }
+        act_quant_tm_kernel<float><<<(unsigned)t, 256, smem, e->stream>>>((const float*)x, (int)k, q, s, qsum);
+    } else if (dtype == NNB_BF16) {
+        static bool cfg = false;
+        if (!cfg) {
+            NNB_CUDA(cudaFuncSetAttribute(act_quant_tm_kernel<__nv_bfloat16>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+            cfg = true;
+        }
+        act_quant_tm_kernel<__nv_bfloat16>
+            <<<(unsigned)t, 256, smem, e->stream>>>((const __nv_bfloat16*)x, (int)k, q, s, qsum);
+    } else {
+        NNB_FAIL(NNB_ERR_INVALID, "act_quant_tm: unknown dtype %d", (int)dtype);
+    }
+    e->launches++;
+    NNB_CHECK_LAUNCH("act_quant_tm_kernel");
+    return NNB_OK;
+}
+
+nnb_status launch_actq_to_plain(nnb_engine* e, const int8_t* q, size_t t, size_t k, int8_t* plain)
+{
+    NNB_REQUIRE(q && plain && t > 0 && k > 0 && k % 64 == 0, "actq_to_plain: bad arguments");
+    actq_to_plain_kernel<<<blocks_for(t * k, 256), 256, 0, e->stream>>>(q, t * k, plain);
+    e->launches++;
+    NNB_CHECK_LAUNCH("actq_to_plain_kernel");
+    return NNB_OK;
+}
+
+nnb_status launch_bitlinear_fwd_tm(nnb_engine* e, const uint32_t* wq, size_t wq_stride_words,
+                                   const float* tau, const float* bias, const int8_t* q,
+                                   const float* s, const int32_t* qsum, size_t n_mats, size_t t,
+                                   size_t k, size_t out, void* y, size_t y_stride_elems,
+                                   nnb_dtype dtype, int32_t* acc)
+{
+    NNB_REQUIRE(wq && tau && q && s && qsum && y, "bitlinear_fwd: NULL argument");
+    NNB_REQUIRE(t > 0 && out > 0 && n_mats > 0, "bitlinear_fwd: empty shape");
+    NNB_REQUIRE(k > 0 && k % 64 == 0, "bitlinear_fwd: k=%zu must be a positive multiple of 64", k);
+    NNB_REQUIRE(((uintptr_t)wq & 15) == 0 && ((uintptr_t)q & 15) == 0 && (wq_stride_words % 4) == 0,
+                "bitlinear_fwd: weights and activations must be 16-byte aligned");
+    NNB_REQUIRE(t <= 0x7fffffff && out <= 0x7fffffff && k <= 0x7fffffff, "bitlinear_fwd: shape too large");
+    NNB_REQUIRE(acc == nullptr || n_mats == 1, "bitlinear_fwd: accumulator output needs n_mats == 1");
+    if (dtype == NNB_F32)
+        return dispatch_fwd<float>(e, wq, wq_stride_words, tau, bias, q, s, qsum, n_mats, t, k, out,
+                                   (float*)y, y_stride_elems, acc);
+    if (dtype == NNB_BF16)
+        return dispatch_fwd<__nv_bfloat16>(e, wq, wq_stride_words, tau, bias, q, s, qsum, n_mats, t,
+                                           k, out, (__nv_bfloat16*)y, y_stride_elems, acc);
+    NNB_FAIL(NNB_ERR_INVALID, "bitlinear_fwd: unknown dtype %d", (int)dtype);
+}
+
+}  // namespace nnb

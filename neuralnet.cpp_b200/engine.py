@@ -1,0 +1,178 @@
+"""Engine: the reference's ComputeEngine operator names over the C-ABI, on torch device tensors.
+
+torch is plumbing only (device memory, streams); every operator below is one call into
+libnn-b200.so.  Names, argument meaning and layouts follow the reference's call sites in
+include/neuralnet.cpp/compute_layer_bitlinear.hpp (trit_pack :650, quantize_i8 :447,
+matmul_q_i8 :454, matmul_q :464, matmul_q_t :494, unpack_i8 :516).
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from ._lib import NnbError, check, lib
+
+F32, BF16 = 0, 1
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise NnbError(f"unsupported activation dtype {t.dtype}")
+
+
+def _ptr(t):
+    if t is None:
+        return None
+    if not t.is_cuda or not t.is_contiguous():
+        raise NnbError("operands must be contiguous CUDA tensors")
+    return C.c_void_p(t.data_ptr())
+
+
+class Engine:
+    """One engine per device and per thread (the reference's threading contract,
+    docs/usage/07-thread-safety.md:11-17)."""
+
+    def __init__(self, device: int = 0, use_torch_stream: bool = True):
+        self._lib = lib()
+        if not torch.cuda.is_available():
+            raise NnbError("no CUDA device: the nn-b200 engine needs a B200 and has no CPU fallback")
+        h = C.c_void_p()
+        check(self._lib.nnb_engine_create(device, C.byref(h)))
+        self._h = h
+        self.device = torch.device("cuda", device)
+        if use_torch_stream:
+            # launch on torch's current stream so torch allocations, copies and events order with us
+            s = torch.cuda.current_stream(self.device)
+            check(self._lib.nnb_engine_set_stream(self._h, C.c_void_p(s.cuda_stream)))
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._lib.nnb_engine_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def handle(self):
+        return self._h
+
+    def describe(self) -> str:
+        buf = C.create_string_buffer(512)
+        check(self._lib.nnb_engine_describe(self._h, buf, 512))
+        return buf.value.decode()
+
+    def sync(self):
+        check(self._lib.nnb_engine_sync(self._h))
+
+    def set_stream(self, stream: "torch.cuda.Stream | None"):
+        check(self._lib.nnb_engine_set_stream(self._h, C.c_void_p(stream.cuda_stream) if stream else None))
+
+    def launch_count(self) -> int:
+        return int(self._lib.nnb_engine_launch_count(self._h))
+
+    # ------------------------------------------------------------ reference layout
+    def absmean_tau(self, latent: torch.Tensor) -> torch.Tensor:
+        rows, k = latent.shape
+        tau = torch.empty(rows, device=self.device, dtype=torch.float32)
+        check(self._lib.nnb_absmean_tau(self._h, _ptr(latent), rows, k, _ptr(tau)))
+        return tau
+
+    def trit_pack(self, latent: torch.Tensor, tau: torch.Tensor) -> torch.Tensor:
+        """(rows,K) f32 + (rows) -> (rows, ceil(K/16)) int32 words (bit pattern of the uint32 codes)."""
+        rows, k = latent.shape
+        packed = torch.empty((rows, (k + 15) // 16), device=self.device, dtype=torch.int32)
+        check(self._lib.nnb_trit_pack(self._h, _ptr(latent), _ptr(tau), rows, k, _ptr(packed)))
+        return packed
+
+    def col_absmax_scale(self, x: torch.Tensor) -> torch.Tensor:
+        k, n = x.shape
+        s = torch.empty(n, device=self.device, dtype=torch.float32)
+        check(self._lib.nnb_col_absmax_scale(self._h, _ptr(x), k, n, _ptr(s)))
+        return s
+
+    def quantize_i8(self, x: torch.Tensor, scale: torch.Tensor, col_scale: bool = True) -> torch.Tensor:
+        m, n = x.shape
+        out = torch.empty((m, (n + 3) // 4), device=self.device, dtype=torch.int32)
+        check(self._lib.nnb_quantize_i8(self._h, _ptr(x), m, n, _ptr(scale), int(col_scale), _ptr(out)))
+        return out
+
+    def unpack_i8(self, packed: torch.Tensor, cols: int) -> torch.Tensor:
+        m = packed.shape[0]
+        out = torch.empty((m, cols), device=self.device, dtype=torch.float32)
+        check(self._lib.nnb_unpack_i8(self._h, _ptr(packed), m, cols, _ptr(out)))
+        return out
+
+    def matmul_q_i8(self, wq, tau, xq, s, k: int, n: int, want_acc: bool = False):
+        rows = wq.shape[0]
+        y = torch.empty((rows, n), device=self.device, dtype=torch.float32)
+        acc = torch.empty((rows, n), device=self.device, dtype=torch.int32) if want_acc else None
+        check(self._lib.nnb_matmul_q_i8(self._h, _ptr(wq), _ptr(tau), _ptr(xq), _ptr(s), rows, k, n,
+                                        _ptr(y), _ptr(acc)))
+        return (y, acc) if want_acc else y
+
+    def matmul_q(self, wq, tau, x, k: int) -> torch.Tensor:
+        rows = wq.shape[0]
+        n = x.shape[1]
+        c = torch.empty((rows, n), device=self.device, dtype=torch.float32)
+        check(self._lib.nnb_matmul_q(self._h, _ptr(wq), _ptr(tau), _ptr(x), rows, k, n, _ptr(c)))
+        return c
+
+    def matmul_q_t(self, wq, tau, b, mcols: int) -> torch.Tensor:
+        rows = wq.shape[0]
+        n = b.shape[1]
+        c = torch.empty((mcols, n), device=self.device, dtype=torch.float32)
+        check(self._lib.nnb_matmul_q_t(self._h, _ptr(wq), _ptr(tau), _ptr(b), rows, mcols, n, _ptr(c)))
+        return c
+
+    # ------------------------------------------------------------------ token-major
+    def act_quant_tm(self, x: torch.Tensor):
+        """x (T,K) f32/bf16 -> (q private layout (T,K) int8, s (T) f32, qsum (T) int32)."""
+        t, k = x.shape
+        q = torch.empty((t, k), device=self.device, dtype=torch.int8)
+        s = torch.empty(t, device=self.device, dtype=torch.float32)
+        qsum = torch.empty(t, device=self.device, dtype=torch.int32)
+        check(self._lib.nnb_act_quant_tm(self._h, _ptr(x), _dt(x), t, k, _ptr(q), _ptr(s), _ptr(qsum)))
+        return q, s, qsum
+
+    def actq_to_plain(self, q: torch.Tensor) -> torch.Tensor:
+        t, k = q.shape
+        out = torch.empty_like(q)
+        check(self._lib.nnb_actq_to_plain(self._h, _ptr(q), t, k, _ptr(out)))
+        return out
+
+    def bitlinear_fwd_tm(self, wq, tau, bias, q, s, qsum, out_dtype=torch.float32, want_acc=False,
+                         y=None):
+        t, k = q.shape
+        out = wq.shape[0]
+        if y is None:
+            y = torch.empty((t, out), device=self.device, dtype=out_dtype)
+        acc = torch.empty((t, out), device=self.device, dtype=torch.int32) if want_acc else None
+        check(self._lib.nnb_bitlinear_fwd_tm(self._h, _ptr(wq), _ptr(tau), _ptr(bias), _ptr(q), _ptr(s),
+                                             _ptr(qsum), t, k, out, _ptr(y), _dt(y), _ptr(acc)))
+        return (y, acc) if want_acc else y
+
+    def bitlinear_fwd_tm_stack(self, wq, tau, bias, q, s, qsum, y):
+        """wq (n_mats, out, K/16), tau/bias (n_mats, out), y (n_mats, T, out)."""
+        n_mats, out, words = wq.shape
+        t, k = q.shape
+        check(self._lib.nnb_bitlinear_fwd_tm_stack(self._h, _ptr(wq), out * words, _ptr(tau), _ptr(bias),
+                                                   _ptr(q), _ptr(s), _ptr(qsum), n_mats, t, k, out,
+                                                   _ptr(y), t * out, _dt(y)))
+        return y
+
+    def bitlinear_fwd_host(self, wq, tau, bias, h_x: torch.Tensor, h_y: torch.Tensor):
+        """h_x (T,K) f32 and h_y (T,out) f32 are HOST tensors (pinned for async copies)."""
+        t, k = h_x.shape
+        out = wq.shape[0]
+        check(self._lib.nnb_bitlinear_fwd_host(self._h, _ptr(wq), _ptr(tau), _ptr(bias),
+                                               C.c_void_p(h_x.data_ptr()), t, k, out,
+                                               C.c_void_p(h_y.data_ptr())))
+        return h_y

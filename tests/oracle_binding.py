@@ -1,0 +1,178 @@
+"""ctypes binding of oracle/liboracle.so — the CPU checker.  Test infrastructure only."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+_SO = os.path.join(ROOT, "oracle", "liboracle.so")
+
+_f32p = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
+_u32p = np.ctypeslib.ndpointer(np.uint32, flags="C_CONTIGUOUS")
+_i32p = np.ctypeslib.ndpointer(np.int32, flags="C_CONTIGUOUS")
+_i8p = np.ctypeslib.ndpointer(np.int8, flags="C_CONTIGUOUS")
+_SZ = C.c_size_t
+
+
+def _ensure_built():
+    src = os.path.join(ROOT, "oracle", "oracle.c")
+    if not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(src):
+        subprocess.run(["make", "-s", "-C", os.path.join(ROOT, "oracle")], check=True)
+
+
+def _c(a, dt):
+    return np.ascontiguousarray(a, dtype=dt)
+
+
+class Oracle:
+    def __init__(self):
+        _ensure_built()
+        L = C.CDLL(_SO)
+        self.L = L
+        L.orc_trit_code_of.restype = C.c_uint32
+        L.orc_trit_code_of.argtypes = [C.c_float, C.c_float]
+        L.orc_trit_value_of.restype = C.c_float
+        L.orc_trit_value_of.argtypes = [C.c_uint32]
+        L.orc_trit_words_per_row.restype = _SZ
+        L.orc_trit_words_per_row.argtypes = [_SZ]
+        L.orc_trit_bytes_per_row.restype = _SZ
+        L.orc_trit_bytes_per_row.argtypes = [_SZ]
+        L.orc_trit_pack_row.argtypes = [_f32p, _SZ, C.c_float, _u32p]
+        L.orc_trit_at.restype = C.c_float
+        L.orc_trit_at.argtypes = [_u32p, _SZ]
+        L.orc_absmean_tau.argtypes = [_f32p, _SZ, _SZ, _f32p]
+        L.orc_trit_pack.argtypes = [_f32p, _f32p, _SZ, _SZ, _u32p]
+        L.orc_i8_quantize.restype = C.c_int8
+        L.orc_i8_quantize.argtypes = [C.c_float, C.c_float]
+        L.orc_i8_words_per_row.restype = _SZ
+        L.orc_i8_words_per_row.argtypes = [_SZ]
+        L.orc_i8_at.restype = C.c_int8
+        L.orc_i8_at.argtypes = [_u32p, _SZ]
+        L.orc_quantize_i8.argtypes = [_f32p, _SZ, _SZ, _f32p, C.c_int, _u32p]
+        L.orc_unpack_i8.argtypes = [_u32p, _SZ, _SZ, _f32p]
+        L.orc_col_absmax_scale.argtypes = [_f32p, _SZ, _SZ, _f32p]
+        L.orc_matmul_q.argtypes = [_u32p, _f32p, _f32p, _SZ, _SZ, _SZ, _f32p]
+        L.orc_matmul_q_t.argtypes = [_u32p, _f32p, _f32p, _SZ, _SZ, _SZ, _f32p]
+        L.orc_matmul_q_i8.argtypes = [_u32p, _f32p, _u32p, _f32p, _SZ, _SZ, _SZ, C.c_void_p, C.c_void_p]
+        L.orc_bitlinear_i8_tm.argtypes = [_u32p, _f32p, C.c_void_p, _i8p, _f32p, _SZ, _SZ, _SZ,
+                                          C.c_void_p, C.c_void_p]
+        L.orc_act_quant_tm.argtypes = [_f32p, _SZ, _SZ, _i8p, _f32p]
+
+    # ---- codecs
+    def trit_code_of(self, w, tau):
+        return int(self.L.orc_trit_code_of(w, tau))
+
+    def trit_value_of(self, code):
+        return float(self.L.orc_trit_value_of(code))
+
+    def trit_words_per_row(self, k):
+        return int(self.L.orc_trit_words_per_row(k))
+
+    def trit_bytes_per_row(self, k):
+        return int(self.L.orc_trit_bytes_per_row(k))
+
+    def trit_pack_row(self, w, tau):
+        w = _c(w, np.float32)
+        out = np.zeros(self.trit_words_per_row(len(w)), np.uint32)
+        self.L.orc_trit_pack_row(w, len(w), tau, out)
+        return out
+
+    def trit_at(self, words, i):
+        return float(self.L.orc_trit_at(_c(words, np.uint32), i))
+
+    def absmean_tau(self, latent):
+        latent = _c(latent, np.float32)
+        tau = np.empty(latent.shape[0], np.float32)
+        self.L.orc_absmean_tau(latent, latent.shape[0], latent.shape[1], tau)
+        return tau
+
+    def trit_pack(self, latent, tau):
+        latent = _c(latent, np.float32)
+        rows, k = latent.shape
+        out = np.empty((rows, self.trit_words_per_row(k)), np.uint32)
+        self.L.orc_trit_pack(latent, _c(tau, np.float32), rows, k, out)
+        return out
+
+    def trit_unpack(self, packed, k):
+        """decode to int8 trits (rows, k) with numpy"""
+        packed = _c(packed, np.uint32)
+        idx = np.arange(k)
+        codes = (packed[:, idx // 16] >> (2 * (idx % 16)).astype(np.uint32)) & 3
+        return codes.astype(np.int8) - 2
+
+    def i8_quantize(self, x, s):
+        return int(self.L.orc_i8_quantize(x, s))
+
+    def i8_at(self, words, i):
+        return int(self.L.orc_i8_at(_c(words, np.uint32), i))
+
+    def quantize_i8(self, x, scale, col_scale=True):
+        x = _c(x, np.float32)
+        m, n = x.shape
+        out = np.empty((m, (n + 3) // 4), np.uint32)
+        self.L.orc_quantize_i8(x, m, n, _c(scale, np.float32), int(col_scale), out)
+        return out
+
+    def unpack_i8(self, packed, n):
+        packed = _c(packed, np.uint32)
+        out = np.empty((packed.shape[0], n), np.float32)
+        self.L.orc_unpack_i8(packed, packed.shape[0], n, out)
+        return out
+
+    def col_absmax_scale(self, x):
+        x = _c(x, np.float32)
+        s = np.empty(x.shape[1], np.float32)
+        self.L.orc_col_absmax_scale(x, x.shape[0], x.shape[1], s)
+        return s
+
+    # ---- matmuls (reference layout)
+    def matmul_q(self, packed, tau, x, k):
+        packed = _c(packed, np.uint32)
+        x = _c(x, np.float32)
+        rows, n = packed.shape[0], x.shape[1]
+        c = np.empty((rows, n), np.float32)
+        self.L.orc_matmul_q(packed, _c(tau, np.float32), x, rows, k, n, c)
+        return c
+
+    def matmul_q_t(self, packed, tau, b, mcols):
+        packed = _c(packed, np.uint32)
+        b = _c(b, np.float32)
+        rows, n = packed.shape[0], b.shape[1]
+        c = np.empty((mcols, n), np.float32)
+        self.L.orc_matmul_q_t(packed, _c(tau, np.float32), b, rows, mcols, n, c)
+        return c
+
+    def matmul_q_i8(self, packed, tau, xq, s, k, n):
+        packed = _c(packed, np.uint32)
+        xq = _c(xq, np.uint32)
+        rows = packed.shape[0]
+        y = np.empty((rows, n), np.float32)
+        acc = np.empty((rows, n), np.int32)
+        self.L.orc_matmul_q_i8(packed, _c(tau, np.float32), xq, _c(s, np.float32), rows, k, n,
+                               y.ctypes.data, acc.ctypes.data)
+        return y, acc
+
+    # ---- token-major
+    def act_quant_tm(self, x):
+        x = _c(x, np.float32)
+        t, k = x.shape
+        q = np.empty((t, k), np.int8)
+        s = np.empty(t, np.float32)
+        self.L.orc_act_quant_tm(x, t, k, q, s)
+        return q, s
+
+    def bitlinear_i8_tm(self, packed, tau, bias, q, s, want_acc=True):
+        packed = _c(packed, np.uint32)
+        q = _c(q, np.int8)
+        t, k = q.shape
+        out = packed.shape[0]
+        y = np.empty((t, out), np.float32)
+        acc = np.empty((t, out), np.int32) if want_acc else None
+        b = _c(bias, np.float32) if bias is not None else None
+        self.L.orc_bitlinear_i8_tm(packed, _c(tau, np.float32), b.ctypes.data if b is not None else None,
+                                   q, _c(s, np.float32), t, k, out, y.ctypes.data,
+                                   acc.ctypes.data if acc is not None else None)
+        return (y, acc) if want_acc else y
