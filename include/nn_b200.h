@@ -54,7 +54,10 @@ const char* nnb_last_error(void);
 nnb_status nnb_engine_describe(nnb_engine* e, char* buf, size_t buf_len);
 /* end_batch()/flush_batch() equivalent: wait for everything enqueued so far */
 nnb_status nnb_engine_sync(nnb_engine* e);
-/* use a caller-owned cudaStream_t (as void*) for all later launches; NULL restores the engine's own */
+/* use a caller-owned cudaStream_t (as void*) for all later launches.  NULL is the legacy
+ * default stream (what torch uses unless told otherwise); NNB_STREAM_OWN restores the engine's
+ * own non-blocking stream. */
+#define NNB_STREAM_OWN ((void*)(intptr_t)-1)
 nnb_status nnb_engine_set_stream(nnb_engine* e, void* cuda_stream);
 void* nnb_engine_stream(nnb_engine* e);
 /* number of kernel launches issued through this engine so far (for benchmarks) */

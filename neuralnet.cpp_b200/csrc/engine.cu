@@ -124,7 +124,7 @@ nnb_status nnb_engine_set_stream(nnb_engine* e, void* cuda_stream)
 {
     NNB_REQUIRE(e, "engine is NULL");
     NNB_CUDA(cudaStreamSynchronize(e->stream));
-    e->stream = cuda_stream ? (cudaStream_t)cuda_stream : e->own_stream;
+    e->stream = (cuda_stream == NNB_STREAM_OWN) ? e->own_stream : (cudaStream_t)cuda_stream;
     return NNB_OK;
 }
 

@@ -73,7 +73,8 @@ class Engine:
         check(self._lib.nnb_engine_sync(self._h))
 
     def set_stream(self, stream: "torch.cuda.Stream | None"):
-        check(self._lib.nnb_engine_set_stream(self._h, C.c_void_p(stream.cuda_stream) if stream else None))
+        ptr = C.c_void_p(stream.cuda_stream) if stream is not None else C.c_void_p(-1)  # -1: the engine's own
+        check(self._lib.nnb_engine_set_stream(self._h, ptr))
 
     def launch_count(self) -> int:
         return int(self._lib.nnb_engine_launch_count(self._h))
