@@ -80,8 +80,8 @@ nnb_status nnb_bitlinear_fwd_tm(nnb_engine* e, const uint32_t* d_wq, const float
                                 nnb_dtype dtype, int32_t* d_acc)
 {
     NNB_REQUIRE(e, "engine is NULL");
-    return launch_bitlinear_fwd_tm(e, d_wq, 0, d_tau, d_bias, d_q, d_s, d_qsum, 1, t, k, out, d_y, 0,
-                                   dtype, d_acc);
+    return launch_bitlinear_fwd_tm(e, d_wq, 0, d_tau, d_bias, nullptr, d_q, d_s, d_qsum, 1, t, k, out,
+                                   d_y, 0, dtype, d_acc);
 }
 
 nnb_status nnb_bitlinear_fwd_tm_stack(nnb_engine* e, const uint32_t* d_wq, size_t wq_stride_words,
@@ -91,8 +91,8 @@ nnb_status nnb_bitlinear_fwd_tm_stack(nnb_engine* e, const uint32_t* d_wq, size_
                                       size_t y_stride_elems, nnb_dtype dtype)
 {
     NNB_REQUIRE(e, "engine is NULL");
-    return launch_bitlinear_fwd_tm(e, d_wq, wq_stride_words, d_tau, d_bias, d_q, d_s, d_qsum, n_mats,
-                                   t, k, out, d_y, y_stride_elems, dtype, nullptr);
+    return launch_bitlinear_fwd_tm(e, d_wq, wq_stride_words, d_tau, d_bias, nullptr, d_q, d_s, d_qsum,
+                                   n_mats, t, k, out, d_y, y_stride_elems, dtype, nullptr);
 }
 
 nnb_status nnb_bitlinear_fwd_host(nnb_engine* e, const uint32_t* d_wq, const float* d_tau,
@@ -112,8 +112,8 @@ nnb_status nnb_bitlinear_fwd_host(nnb_engine* e, const uint32_t* d_wq, const flo
     float* d_y = (float*)(base + x_b + q_b + 2 * s_b);
     NNB_CUDA(cudaMemcpyAsync(d_x, h_x, t * k * 4, cudaMemcpyHostToDevice, e->stream));
     NNB_TRY(launch_act_quant_tm(e, d_x, NNB_F32, t, k, d_q, d_s, d_qsum));
-    NNB_TRY(launch_bitlinear_fwd_tm(e, d_wq, 0, d_tau, d_bias, d_q, d_s, d_qsum, 1, t, k, out, d_y, 0,
-                                    NNB_F32, nullptr));
+    NNB_TRY(launch_bitlinear_fwd_tm(e, d_wq, 0, d_tau, d_bias, nullptr, d_q, d_s, d_qsum, 1, t, k, out,
+                                    d_y, 0, NNB_F32, nullptr));
     NNB_CUDA(cudaMemcpyAsync(h_y, d_y, t * out * 4, cudaMemcpyDeviceToHost, e->stream));
     NNB_CUDA(cudaStreamSynchronize(e->stream));
     return NNB_OK;

@@ -91,10 +91,11 @@ nnb_status launch_matmul_q_t_ref(nnb_engine* e, const uint32_t* wq, const float*
 nnb_status launch_act_quant_tm(nnb_engine* e, const void* x, nnb_dtype dtype, size_t t, size_t k,
                                int8_t* q, float* s, int32_t* qsum);
 nnb_status launch_actq_to_plain(nnb_engine* e, const int8_t* q, size_t t, size_t k, int8_t* plain);
+// y = [residual +] (tau*s)*acc [+ bias]; residual (t,out) f32 and acc (t,out) may be NULL
 nnb_status launch_bitlinear_fwd_tm(nnb_engine* e, const uint32_t* wq, size_t wq_stride_words,
-                                   const float* tau, const float* bias, const int8_t* q,
-                                   const float* s, const int32_t* qsum, size_t n_mats, size_t t,
-                                   size_t k, size_t out, void* y, size_t y_stride_elems,
-                                   nnb_dtype dtype, int32_t* acc);
+                                   const float* tau, const float* bias, const float* residual,
+                                   const int8_t* q, const float* s, const int32_t* qsum,
+                                   size_t n_mats, size_t t, size_t k, size_t out, void* y,
+                                   size_t y_stride_elems, nnb_dtype dtype, int32_t* acc);
 
 }  // namespace nnb

@@ -321,7 +321,7 @@ template <int BM, int BN, int BK, int STAGES, int WM, int WN, int WK, typename O
 __global__ void __launch_bounds__(WM* WN* WK * 32)
 bitlinear_mma_kernel(const uint32_t* __restrict__ wq, size_t wq_stride_words,
                      const float* __restrict__ tau, const float* __restrict__ bias,
-                     const int8_t* __restrict__ q, const float* __restrict__ s,
+                     const float* __restrict__ residual, const int8_t* __restrict__ q, const float* __restrict__ s,
                      const int32_t* __restrict__ qsum, int T, int K, int OUT, OutT* __restrict__ y,
                      size_t y_stride_elems, int32_t* __restrict__ acc_out)
 {
@@ -491,6 +491,7 @@ bitlinear_mma_kernel(const uint32_t* __restrict__ wq, size_t wq_stride_words,
                     const int a = acc[mt][nt][h * 2 + cc] - qs2;
                     float v = __fmul_rn(__fmul_rn(tau[row], st), (float)a);
                     if (bias) v = __fadd_rn(v, bias[row]);
+                    if (residual) v = __fadd_rn(residual[(size_t)tok * OUT + row], v);
                     store_out<OutT>(y + (size_t)tok * OUT + row, v);
                     if (acc_out) acc_out[(size_t)tok * OUT + row] = a;
                 }
@@ -499,9 +500,195 @@ bitlinear_mma_kernel(const uint32_t* __restrict__ wq, size_t wq_stride_words,
     }
 }
 
+// ----------------------------------------------------------- skinny (decode) kernel
+// Few tokens (<= 8*NT), many output rows: the packed weights are the only real traffic, so the
+// kernel is a persistent weight streamer.  The activations of all tokens stay resident in
+// shared memory for the CTA's lifetime; every group of WK warps owns one 16-row slab at a
+// time and splits K between its warps; weights go straight from global memory to the
+// tensor-core operand registers (two 32-bit loads per 64 features per lane, register
+// double-buffered), no shared-memory staging and no barrier inside the K loop.
+template <int NT, int WK, typename OutT>
+__global__ void __launch_bounds__(256)
+bitlinear_skinny_kernel(const uint32_t* __restrict__ wq, size_t wq_stride_words,
+                        const float* __restrict__ tau, const float* __restrict__ bias,
+                        const float* __restrict__ residual, const int8_t* __restrict__ q,
+                        const float* __restrict__ s, const int32_t* __restrict__ qsum, int T, int K,
+                        int OUT, int n_mats, OutT* __restrict__ y, size_t y_stride_elems,
+                        int32_t* __restrict__ acc_out)
+{
+    constexpr int GROUPS = 8 / WK;
+    constexpr int UNROLL = 4;  // 64-feature blocks per register buffer
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int row_stride = K + 16;  // +16 bytes: conflict-free ldmatrix across tokens
+    unsigned char* Bs = smem;
+    int* red = reinterpret_cast<int*>(smem + (size_t)NT * 8 * row_stride);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int group = warp / WK, wk = warp % WK;
+    const int g = lane >> 2, t4 = lane & 3;
+
+    // stage the activations once
+    {
+        const int units_per_row = K / 16;
+        const int total = NT * 8 * units_per_row;
+        for (int i = tid; i < total; i += 256) {
+            const int r = i / units_per_row, u = i - r * units_per_row;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (r < T) v = *reinterpret_cast<const uint4*>(q + (size_t)r * K + u * 16);
+            *reinterpret_cast<uint4*>(Bs + (size_t)r * row_stride + u * 16) = v;
+        }
+    }
+    __syncthreads();
+
+    const int words_per_row = K / 16;
+    const int nblk = K / 64;
+    const int mtiles = (OUT + 15) / 16;
+    const int n_items = mtiles * n_mats;
+    const int blk_lo = (int)(((long long)nblk * wk) / WK);
+    const int blk_hi = (int)(((long long)nblk * (wk + 1)) / WK);
+    // ldmatrix row address of this lane (token lane&7 of each n-tile, 16-byte unit lane>>3)
+    const unsigned char* b_lane = Bs + (size_t)(lane & 7) * row_stride + (lane >> 3) * 16;
+
+    for (int item = blockIdx.x * GROUPS + group; item < n_items; item += gridDim.x * GROUPS) {
+        const int mat = item / mtiles, mt = item - mat * mtiles;
+        const int r_lo = mt * 16 + g, r_hi = r_lo + 8;
+        const uint32_t* wm = wq + (size_t)mat * wq_stride_words;
+        const bool ok_lo = r_lo < OUT, ok_hi = r_hi < OUT;
+        const uint32_t* p_lo = wm + (size_t)(ok_lo ? r_lo : 0) * words_per_row + t4;
+        const uint32_t* p_hi = wm + (size_t)(ok_hi ? r_hi : 0) * words_per_row + t4;
+
+        int acc[NT][4];
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[j][c] = 0;
+
+        uint32_t cur_lo[UNROLL], cur_hi[UNROLL], nxt_lo[UNROLL], nxt_hi[UNROLL];
+        auto fetch = [&](int b0, uint32_t (&lo)[UNROLL], uint32_t (&hi)[UNROLL]) {
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                const int b = b0 + u;
+                const bool in = b < blk_hi;
+                lo[u] = (in && ok_lo) ? __ldg(p_lo + 4 * b) : 0u;
+                hi[u] = (in && ok_hi) ? __ldg(p_hi + 4 * b) : 0u;
+            }
+        };
+        fetch(blk_lo, cur_lo, cur_hi);
+        for (int b0 = blk_lo; b0 < blk_hi; b0 += UNROLL) {
+            fetch(b0 + UNROLL, nxt_lo, nxt_hi);
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                const int b = b0 + u;
+                if (b < blk_hi) {
+                    constexpr uint32_t MSK = 0x03030303u;
+                    const uint32_t w_lo = cur_lo[u], w_hi = cur_hi[u];
+                    const uint32_t a0 = w_lo & MSK, a1 = w_hi & MSK;
+                    const uint32_t a2 = (w_lo >> 2) & MSK, a3 = (w_hi >> 2) & MSK;
+                    const uint32_t c0 = (w_lo >> 4) & MSK, c1 = (w_hi >> 4) & MSK;
+                    const uint32_t c2 = (w_lo >> 6) & MSK, c3 = (w_hi >> 6) & MSK;
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+                        uint32_t bf[4];
+                        ldmatrix_x4(bf, b_lane + (size_t)nt * 8 * row_stride + b * 64);
+                        mma_u8s8(acc[nt], a0, a1, a2, a3, bf[0], bf[1]);
+                        mma_u8s8(acc[nt], c0, c1, c2, c3, bf[2], bf[3]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                cur_lo[u] = nxt_lo[u];
+                cur_hi[u] = nxt_hi[u];
+            }
+        }
+
+        if (WK > 1) {
+            // items are assigned per group, so the WK warps of a group always iterate together;
+            // they meet on a named barrier of their own (id group+1), never on the CTA barrier
+            int* slot = red + ((size_t)(group * WK + wk) * 32 + lane) * (NT * 4);
+            if (wk > 0) {
+#pragma unroll
+                for (int j = 0; j < NT; ++j)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) slot[j * 4 + c] = acc[j][c];
+            }
+            // named barrier per group: only the WK warps of this group take part
+            asm volatile("bar.sync %0, %1;\n" ::"r"(group + 1), "r"(WK * 32));
+            if (wk == 0) {
+#pragma unroll
+                for (int o = 1; o < WK; ++o) {
+                    const int* src = red + ((size_t)(group * WK + o) * 32 + lane) * (NT * 4);
+#pragma unroll
+                    for (int j = 0; j < NT; ++j)
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) acc[j][c] += src[j * 4 + c];
+                }
+            }
+            asm volatile("bar.sync %0, %1;\n" ::"r"(group + 1), "r"(WK * 32));
+        }
+        if (wk == 0) {
+            const float* tau_m = tau + (size_t)mat * OUT;
+            const float* bias_m = bias ? bias + (size_t)mat * OUT : nullptr;
+            OutT* y_m = y + (size_t)mat * y_stride_elems;
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+                for (int cc = 0; cc < 2; ++cc) {
+                    const int tok = nt * 8 + t4 * 2 + cc;
+                    if (tok >= T) continue;
+                    const int qs2 = 2 * qsum[tok];
+                    const float st = s[tok];
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int row = h ? r_hi : r_lo;
+                        if (row >= OUT) continue;
+                        const int a = acc[nt][h * 2 + cc] - qs2;
+                        float v = __fmul_rn(__fmul_rn(tau_m[row], st), (float)a);
+                        if (bias_m) v = __fadd_rn(v, bias_m[row]);
+                        if (residual) v = __fadd_rn(residual[(size_t)tok * OUT + row], v);
+                        store_out<OutT>(y_m + (size_t)tok * OUT + row, v);
+                        if (acc_out) acc_out[(size_t)tok * OUT + row] = a;
+                    }
+                }
+            }
+        }
+    }
+}
+
+template <int NT, int WK, typename OutT>
+static nnb_status launch_skinny(nnb_engine* e, const uint32_t* wq, size_t wq_stride,
+                                const float* tau, const float* bias, const float* residual,
+                                const int8_t* q, const float* s, const int32_t* qsum, size_t n_mats,
+                                size_t t, size_t k, size_t out, OutT* y, size_t y_stride,
+                                int32_t* acc)
+{
+    constexpr int GROUPS = 8 / WK;
+    const size_t smem = (size_t)NT * 8 * (k + 16) + (size_t)8 * 32 * NT * 4 * sizeof(int);
+    auto kern = bitlinear_skinny_kernel<NT, WK, OutT>;
+    static size_t configured = 0;
+    if (smem > configured) {
+        NNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = smem;
+    }
+    const size_t n_items = ceil_div(out, 16) * n_mats;
+    size_t ctas_per_sm = (200 * 1024) / (smem + 1024);
+    if (ctas_per_sm > 4) ctas_per_sm = 4;
+    if (ctas_per_sm < 1) ctas_per_sm = 1;
+    size_t grid = ceil_div(n_items, GROUPS);
+    const size_t cap = (size_t)e->sm_count * ctas_per_sm;
+    if (grid > cap) grid = cap;
+    kern<<<(unsigned)grid, 256, smem, e->stream>>>(wq, wq_stride, tau, bias, residual, q, s, qsum,
+                                                   (int)t, (int)k, (int)out, (int)n_mats, y, y_stride,
+                                                   acc);
+    e->launches++;
+    NNB_CHECK_LAUNCH("bitlinear_skinny_kernel");
+    return NNB_OK;
+}
+
 template <int BM, int BN, int BK, int STAGES, int WM, int WN, int WK, typename OutT>
 static nnb_status launch_cfg(nnb_engine* e, const uint32_t* wq, size_t wq_stride,
-                             const float* tau, const float* bias, const int8_t* q, const float* s,
+                             const float* tau, const float* bias, const float* residual,
+                             const int8_t* q, const float* s,
                              const int32_t* qsum, size_t n_mats, size_t t, size_t k, size_t out,
                              OutT* y, size_t y_stride, int32_t* acc)
 {
@@ -518,33 +705,59 @@ static nnb_status launch_cfg(nnb_engine* e, const uint32_t* wq, size_t wq_stride
     dim3 grid((unsigned)ceil_div(out, BM), (unsigned)ceil_div(t, BN), (unsigned)n_mats);
     NNB_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "bitlinear_fwd: grid too large (t=%zu, n_mats=%zu)",
                 t, n_mats);
-    kern<<<grid, THREADS, smem, e->stream>>>(wq, wq_stride, tau, bias, q, s, qsum, (int)t, (int)k,
-                                             (int)out, y, y_stride, acc);
+    kern<<<grid, THREADS, smem, e->stream>>>(wq, wq_stride, tau, bias, residual, q, s, qsum, (int)t,
+                                             (int)k, (int)out, y, y_stride, acc);
     e->launches++;
     NNB_CHECK_LAUNCH("bitlinear_mma_kernel");
     return NNB_OK;
 }
 
+template <int NT, typename OutT>
+static nnb_status dispatch_skinny(nnb_engine* e, const uint32_t* wq, size_t wq_stride,
+                                  const float* tau, const float* bias, const float* residual,
+                                  const int8_t* q, const float* s, const int32_t* qsum,
+                                  size_t n_mats, size_t t, size_t k, size_t out, OutT* y,
+                                  size_t y_stride, int32_t* acc)
+{
+    // pick the K split so that the 16-row slabs fill the machine's warp slots
+    const size_t smem = (size_t)NT * 8 * (k + 16) + 4096 * NT;
+    size_t ctas_per_sm = (200 * 1024) / (smem + 1024);
+    if (ctas_per_sm > 4) ctas_per_sm = 4;
+    if (ctas_per_sm < 1) ctas_per_sm = 1;
+    const size_t slots = (size_t)e->sm_count * ctas_per_sm * 8;
+    const size_t items = ceil_div(out, 16) * n_mats;
+    const size_t nblk = k / 64;
+#define NNB_SKINNY(WK_)                                                                          \
+    return launch_skinny<NT, WK_, OutT>(e, wq, wq_stride, tau, bias, residual, q, s, qsum, n_mats, \
+                                        t, k, out, y, y_stride, acc)
+    if (items >= slots || nblk < 2) NNB_SKINNY(1);
+    if (items * 2 >= slots || nblk < 4) NNB_SKINNY(2);
+    if (items * 4 >= slots || nblk < 8) NNB_SKINNY(4);
+    NNB_SKINNY(8);
+#undef NNB_SKINNY
+}
+
 template <typename OutT>
 static nnb_status dispatch_fwd(nnb_engine* e, const uint32_t* wq, size_t wq_stride, const float* tau,
-                               const float* bias, const int8_t* q, const float* s,
-                               const int32_t* qsum, size_t n_mats, size_t t, size_t k, size_t out,
-                               OutT* y, size_t y_stride, int32_t* acc)
+                               const float* bias, const float* residual, const int8_t* q,
+                               const float* s, const int32_t* qsum, size_t n_mats, size_t t,
+                               size_t k, size_t out, OutT* y, size_t y_stride, int32_t* acc)
 {
-    if (t <= 8)
-        return launch_cfg<32, 8, 256, 4, 1, 1, 4, OutT>(e, wq, wq_stride, tau, bias, q, s, qsum,
-                                                         n_mats, t, k, out, y, y_stride, acc);
-    if (t <= 16)
-        return launch_cfg<32, 16, 256, 4, 1, 1, 4, OutT>(e, wq, wq_stride, tau, bias, q, s, qsum,
-                                                          n_mats, t, k, out, y, y_stride, acc);
-    if (t <= 32)
-        return launch_cfg<32, 32, 256, 4, 1, 1, 4, OutT>(e, wq, wq_stride, tau, bias, q, s, qsum,
-                                                          n_mats, t, k, out, y, y_stride, acc);
+    const size_t skinny_limit = 200 * 1024;
+    if (t <= 8 && 8 * (k + 16) + 4096 <= skinny_limit)
+        return dispatch_skinny<1, OutT>(e, wq, wq_stride, tau, bias, residual, q, s, qsum, n_mats, t,
+                                        k, out, y, y_stride, acc);
+    if (t <= 16 && 16 * (k + 16) + 8192 <= skinny_limit)
+        return dispatch_skinny<2, OutT>(e, wq, wq_stride, tau, bias, residual, q, s, qsum, n_mats, t,
+                                        k, out, y, y_stride, acc);
+    if (t <= 32 && 32 * (k + 16) + 16384 <= skinny_limit)
+        return dispatch_skinny<4, OutT>(e, wq, wq_stride, tau, bias, residual, q, s, qsum, n_mats, t,
+                                        k, out, y, y_stride, acc);
     if (t <= 64)
-        return launch_cfg<64, 64, 128, 4, 2, 2, 1, OutT>(e, wq, wq_stride, tau, bias, q, s, qsum,
-                                                          n_mats, t, k, out, y, y_stride, acc);
-    return launch_cfg<128, 128, 128, 4, 2, 4, 1, OutT>(e, wq, wq_stride, tau, bias, q, s, qsum,
-                                                        n_mats, t, k, out, y, y_stride, acc);
+        return launch_cfg<64, 64, 128, 4, 2, 2, 1, OutT>(e, wq, wq_stride, tau, bias, residual, q, s,
+                                                          qsum, n_mats, t, k, out, y, y_stride, acc);
+    return launch_cfg<128, 128, 128, 4, 2, 4, 1, OutT>(e, wq, wq_stride, tau, bias, residual, q, s,
+                                                        qsum, n_mats, t, k, out, y, y_stride, acc);
 }
 
 // ------------------------------------------------------------------ launchers
@@ -676,10 +889,10 @@ nnb_status launch_actq_to_plain(nnb_engine* e, const int8_t* q, size_t t, size_t
 }
 
 nnb_status launch_bitlinear_fwd_tm(nnb_engine* e, const uint32_t* wq, size_t wq_stride_words,
-                                   const float* tau, const float* bias, const int8_t* q,
-                                   const float* s, const int32_t* qsum, size_t n_mats, size_t t,
-                                   size_t k, size_t out, void* y, size_t y_stride_elems,
-                                   nnb_dtype dtype, int32_t* acc)
+                                   const float* tau, const float* bias, const float* residual,
+                                   const int8_t* q, const float* s, const int32_t* qsum,
+                                   size_t n_mats, size_t t, size_t k, size_t out, void* y,
+                                   size_t y_stride_elems, nnb_dtype dtype, int32_t* acc)
 {
     NNB_REQUIRE(wq && tau && q && s && qsum && y, "bitlinear_fwd: NULL argument");
     NNB_REQUIRE(t > 0 && out > 0 && n_mats > 0, "bitlinear_fwd: empty shape");
@@ -688,12 +901,13 @@ nnb_status launch_bitlinear_fwd_tm(nnb_engine* e, const uint32_t* wq, size_t wq_
                 "bitlinear_fwd: weights and activations must be 16-byte aligned");
     NNB_REQUIRE(t <= 0x7fffffff && out <= 0x7fffffff && k <= 0x7fffffff, "bitlinear_fwd: shape too large");
     NNB_REQUIRE(acc == nullptr || n_mats == 1, "bitlinear_fwd: accumulator output needs n_mats == 1");
+    NNB_REQUIRE(residual == nullptr || n_mats == 1, "bitlinear_fwd: residual needs n_mats == 1");
     if (dtype == NNB_F32)
-        return dispatch_fwd<float>(e, wq, wq_stride_words, tau, bias, q, s, qsum, n_mats, t, k, out,
-                                   (float*)y, y_stride_elems, acc);
+        return dispatch_fwd<float>(e, wq, wq_stride_words, tau, bias, residual, q, s, qsum, n_mats, t,
+                                   k, out, (float*)y, y_stride_elems, acc);
     if (dtype == NNB_BF16)
-        return dispatch_fwd<__nv_bfloat16>(e, wq, wq_stride_words, tau, bias, q, s, qsum, n_mats, t,
-                                           k, out, (__nv_bfloat16*)y, y_stride_elems, acc);
+        return dispatch_fwd<__nv_bfloat16>(e, wq, wq_stride_words, tau, bias, residual, q, s, qsum,
+                                           n_mats, t, k, out, (__nv_bfloat16*)y, y_stride_elems, acc);
     NNB_FAIL(NNB_ERR_INVALID, "bitlinear_fwd: unknown dtype %d", (int)dtype);
 }
 
