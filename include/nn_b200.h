@@ -137,6 +137,54 @@ nnb_status nnb_bitlinear_fwd_host(nnb_engine* e, const uint32_t* d_wq, const flo
                                   const float* d_bias, const float* h_x, size_t t, size_t k,
                                   size_t out, float* h_y);
 
+/* ================= GPT policy with ternary linears ========================
+ * The model the reference builds with build_gpt_model(engine, GptConfig)
+ * (include/neuralnet.cpp/domain_gpt.hpp:59-77): token embedding, learned or rotary positions,
+ * pre-norm blocks (RMSNorm, causal MHA, QuickGELU or SwiGLU feed-forward), final RMSNorm and an
+ * untied BitLinear head; every linear is a BitLinear with bias and int8 activations. */
+typedef struct nnb_gpt_config {
+    int32_t n_layer, d_model, n_head, d_ff, vocab, ctx;
+    int32_t act;        /* 0 = QuickGELU (GeLU layer of the reference), 1 = SwiGLU */
+    int32_t pos;        /* 0 = learned additive positions, 1 = RoPE */
+    int32_t value_head; /* 1 adds a Linear(d_model -> 1) port on the final-norm output */
+    int32_t exact;      /* 1: f32 activations and KV cache, f64-accumulated reductions (the mode
+                           compared token by token with the CPU restatement); 0: bf16 KV cache */
+} nnb_gpt_config;
+
+typedef struct nnb_policy nnb_policy;
+
+nnb_status nnb_policy_create(nnb_engine* e, const nnb_gpt_config* cfg, nnb_policy** out);
+void nnb_policy_destroy(nnb_policy* p);
+/* the f32 master parameters live in one flat device buffer; tensors are described by name */
+size_t nnb_policy_param_count(const nnb_policy* p);
+float* nnb_policy_params(nnb_policy* p);
+size_t nnb_policy_tensor_count(const nnb_policy* p);
+nnb_status nnb_policy_tensor_info(const nnb_policy* p, size_t index, char* name, size_t name_len,
+                                  size_t* offset, size_t* rows, size_t* cols);
+/* Layer::import_param for every tensor at once: copy host parameters in and requantise */
+nnb_status nnb_policy_upload_params(nnb_policy* p, const float* h_params);
+/* BitLinear::quantize_weights_ for every linear (compute_layer_bitlinear.hpp:627-674):
+ * call after the master weights changed */
+nnb_status nnb_policy_requantize(nnb_policy* p);
+/* device pointers of one linear's container and scales; layer < 0 selects the head,
+ * which in 0..5 = q, k, v, o, fc1, fc2 */
+nnb_status nnb_policy_linear(nnb_policy* p, int layer, int which, uint32_t** d_packed, float** d_tau,
+                             size_t* in, size_t* out);
+
+/* Batched GPTModel::generate (include/neuralnet.cpp/compute_layer_gpt.hpp:740-852) with
+ * sample_next_token_ (compute_layer_base.hpp:1025-1163; temperature and top-k): n_seq prompts of
+ * prompt_len ids each, max_new sampled tokens.  temperature <= 0 is greedy.  The uniform draw of
+ * sequence b at generated step t is Philox4x32-10 keyed by seed with counter (seq0 + b, t).
+ * d_tokens (n_seq, prompt_len + max_new); d_logp (n_seq, max_new) log-prob of each sampled token
+ * under softmax(raw logits), may be NULL; d_logits (n_seq, max_new, vocab) may be NULL. */
+nnb_status nnb_rollout(nnb_policy* p, const int32_t* d_prompts, size_t n_seq, size_t prompt_len,
+                       size_t max_new, float temperature, int top_k, uint64_t seed, uint32_t seq0,
+                       int32_t* d_tokens, float* d_logp, float* d_logits);
+/* the same with host buffers: copies prompts in and tokens / log-probs out, and synchronises */
+nnb_status nnb_rollout_host(nnb_policy* p, const int32_t* h_prompts, size_t n_seq, size_t prompt_len,
+                            size_t max_new, float temperature, int top_k, uint64_t seed, uint32_t seq0,
+                            int32_t* h_tokens, float* h_logp);
+
 #ifdef __cplusplus
 }
 #endif

@@ -50,6 +50,17 @@ _SIGNATURES = {
     "nnb_bitlinear_fwd_tm": (_I, [_P, _P, _P, _P, _P, _P, _P, _SZ, _SZ, _SZ, _P, _I, _P]),
     "nnb_bitlinear_fwd_tm_stack": (_I, [_P, _P, _SZ, _P, _P, _P, _P, _P, _SZ, _SZ, _SZ, _SZ, _P, _SZ, _I]),
     "nnb_bitlinear_fwd_host": (_I, [_P, _P, _P, _P, _P, _SZ, _SZ, _SZ, _P]),
+    "nnb_policy_create": (_I, [_P, _P, C.POINTER(_P)]),
+    "nnb_policy_destroy": (None, [_P]),
+    "nnb_policy_param_count": (_SZ, [_P]),
+    "nnb_policy_params": (_P, [_P]),
+    "nnb_policy_tensor_count": (_SZ, [_P]),
+    "nnb_policy_tensor_info": (_I, [_P, _SZ, C.c_char_p, _SZ, C.POINTER(_SZ), C.POINTER(_SZ), C.POINTER(_SZ)]),
+    "nnb_policy_upload_params": (_I, [_P, _P]),
+    "nnb_policy_requantize": (_I, [_P]),
+    "nnb_policy_linear": (_I, [_P, _I, _I, C.POINTER(_P), C.POINTER(_P), C.POINTER(_SZ), C.POINTER(_SZ)]),
+    "nnb_rollout": (_I, [_P, _P, _SZ, _SZ, _SZ, C.c_float, _I, C.c_uint64, C.c_uint32, _P, _P, _P]),
+    "nnb_rollout_host": (_I, [_P, _P, _SZ, _SZ, _SZ, C.c_float, _I, C.c_uint64, C.c_uint32, _P, _P]),
 }
 
 

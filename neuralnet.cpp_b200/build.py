@@ -18,7 +18,7 @@ LIB = os.path.join(HERE, "libnn-b200.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
-    "-lineinfo", "-O3", "-std=c++17",
+    "-lineinfo", "-O3", "-std=c++17", "-fmad=false",
     "-Xcompiler", "-fPIC,-fvisibility=default,-Wall,-Wno-unused-function",
     "--expt-relaxed-constexpr",
     "-I", os.path.join(ROOT, "include"),

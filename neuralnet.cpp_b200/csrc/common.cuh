@@ -98,4 +98,22 @@ nnb_status launch_bitlinear_fwd_tm(nnb_engine* e, const uint32_t* wq, size_t wq_
                                    size_t n_mats, size_t t, size_t k, size_t out, void* y,
                                    size_t y_stride_elems, nnb_dtype dtype, int32_t* acc);
 
+// ---- decode.cu
+// mode 0 RMSNorm*gamma, 1 QuickGELU, 2 SwiGLU (row = gate|up, in_stride = 2k), 3 identity;
+// quantises the transformed row; f_out (t,k) optional copy of the transformed row
+nnb_status launch_row_quant(nnb_engine* e, int mode, bool exact, const float* in, const float* gamma,
+                            size_t t, size_t k, size_t in_stride, int8_t* q, float* s,
+                            int32_t* qsum, float* f_out);
+nnb_status launch_attn_decode(nnb_engine* e, bool exact, const float* qkv, void* kcache, void* vcache,
+                              const float* rope_cos, const float* rope_sin, const int* d_pos,
+                              size_t B, size_t H, size_t dk, size_t ctx_alloc, float* out);
+nnb_status launch_sample(nnb_engine* e, bool exact, const float* logits, size_t B, size_t V,
+                         float temperature, int top_k, unsigned long long seed, unsigned seq0,
+                         const int* d_pos, int prompt_len, int32_t* tokens, size_t tokens_stride,
+                         float* logp, size_t logp_stride, float* entropy);
+nnb_status launch_set_int(nnb_engine* e, int* p, int v);
+nnb_status launch_add_int(nnb_engine* e, int* p, int v);
+nnb_status launch_embed(nnb_engine* e, const float* tok_emb, const float* pos_emb, const int32_t* tokens,
+                        size_t tokens_stride, const int* d_pos, size_t B, size_t d, size_t vocab, float* x);
+
 }  // namespace nnb

@@ -1,0 +1,666 @@
+// decode.cu — kernels of one batched decode step of the ternary GPT policy:
+// embedding, RMSNorm fused with activation quantisation, RoPE + KV-cache append + attention,
+// FFN activation fused with quantisation, and the sampler.
+//
+// Reference semantics (per sequence; the batch dimension only runs sequences side by side):
+//   GPTModel::forward_step           include/neuralnet.cpp/compute_layer_gpt.hpp:693-725
+//   AttentionBase::forward_step      include/neuralnet.cpp/compute_layer_attention.hpp:1003-1092
+//   RMSNorm::forward                 include/neuralnet.cpp/compute_layer_mlp.hpp:686-707
+//   RotaryEmbedding::apply_step      include/neuralnet.cpp/compute_position_encoding.hpp:149-168
+//   GeLU / SwiGLU forward            include/neuralnet.cpp/compute_layer_mlp.hpp:243-252,317-330
+//   sample_next_token_               include/neuralnet.cpp/compute_layer_base.hpp:1025-1163
+//
+// Two numeric modes.  EXACT: f32 storage, every float reduction accumulated in f64 and rounded
+// once (independent of the reduction tree), exp as a fixed fmaf sequence; this is the mode
+// whose greedy rollouts are compared token by token with the CPU restatement.  Fast: bf16 KV
+// cache, f32 accumulation.
+#include "common.cuh"
+#include "device_math.cuh"
+
+namespace nnb {
+
+// ---------------------------------------------------------------- embedding
+// x[b,:] = tok_emb[token[b, pos],:] (+ pos_emb[pos,:])
+__global__ void embed_kernel(const float* __restrict__ tok_emb, const float* __restrict__ pos_emb,
+                             const int32_t* __restrict__ tokens, int tokens_stride,
+                             const int* __restrict__ d_pos, int d, int vocab, float* __restrict__ x)
+{
+    const int b = blockIdx.x;
+    const int pos = *d_pos;
+    int tok = tokens[(size_t)b * tokens_stride + pos];
+    tok = min(max(tok, 0), vocab - 1);
+    const float* e = tok_emb + (size_t)tok * d;
+    const float* p = pos_emb ? pos_emb + (size_t)pos * d : nullptr;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        float v = e[i];
+        if (p) v = __fadd_rn(v, p[i]);
+        x[(size_t)b * d + i] = v;
+    }
+}
+
+// -------------------------------------------- row transform + quantisation
+// One CTA per token.  MODE 0: RMSNorm(x)*gamma.  MODE 1: QuickGELU(h).  MODE 2: SwiGLU(h) with
+// h = (gate | up).  MODE 3: identity.  The transformed row is quantised to the engine's int8
+// layout (see ternary.cu) and optionally also written as f32 (`f_out`).
+template <int MODE, bool EXACT>
+__global__ void __launch_bounds__(256)
+row_quant_kernel(const float* __restrict__ in, const float* __restrict__ gamma, int k, int in_stride,
+                 int8_t* __restrict__ q, float* __restrict__ s, int32_t* __restrict__ qsum,
+                 float* __restrict__ f_out)
+{
+    extern __shared__ float row[];
+    __shared__ double red_d[8];
+    __shared__ float red_f[8];
+    __shared__ int red_i[8];
+    const size_t tok = blockIdx.x;
+    const float* xr = in + tok * (size_t)in_stride;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+    float sinv = 0.0f;
+    if (MODE == 0) {
+        float ssf;
+        if (EXACT) {
+            double ss = 0.0;
+            for (int i = tid; i < k; i += 256) {
+                const float v = xr[i];
+                ss += (double)__fmul_rn(v, v);
+            }
+            ss = warp_sum_d(ss);
+            if (lane == 0) red_d[warp] = ss;
+            __syncthreads();
+            ss = 0.0;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) ss += red_d[w];
+            ssf = (float)ss;
+        } else {
+            float ss = 0.0f;
+            for (int i = tid; i < k; i += 256) {
+                const float v = xr[i];
+                ss = fmaf(v, v, ss);
+            }
+            ss = warp_sum(ss);
+            if (lane == 0) red_f[warp] = ss;
+            __syncthreads();
+            ss = 0.0f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) ss += red_f[w];
+            ssf = ss;
+        }
+        const float v = __fadd_rn(__fmul_rn(ssf, __frcp_rn((float)k)), 1e-5f);
+        sinv = __frcp_rn(__fsqrt_rn(v));
+        __syncthreads();
+    }
+    float mx = 0.0f;
+    for (int i = tid; i < k; i += 256) {
+        float v;
+        if (MODE == 0) {
+            v = __fmul_rn(__fmul_rn(xr[i], sinv), gamma[i]);
+        } else if (MODE == 1) {
+            const float xv = xr[i];
+            v = __fdiv_rn(xv, __fadd_rn(1.0f, nnb_expf(-__fmul_rn(xv, 1.702f))));
+        } else if (MODE == 2) {
+            const float gv = xr[i], uv = xr[k + i];
+            const float sig = __fdiv_rn(1.0f, __fadd_rn(1.0f, nnb_expf(-gv)));
+            v = __fmul_rn(__fmul_rn(gv, sig), uv);
+        } else {
+            v = xr[i];
+        }
+        row[i] = v;
+        if (f_out) f_out[tok * (size_t)k + i] = v;
+        const float a = fabsf(v);
+        if (a > mx) mx = a;
+    }
+    mx = warp_max(mx);
+    if (lane == 0) red_f[warp] = mx;
+    __syncthreads();
+    mx = red_f[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) mx = fmaxf(mx, red_f[w]);
+    const float sc = __fmul_rn(mx, 1.0f / 127.0f);
+    uint32_t* qrow = reinterpret_cast<uint32_t*>(q + tok * (size_t)k);
+    int local = 0;
+    for (int w = tid; w < k / 4; w += 256) {
+        const int blk = w >> 4, wd = w & 15;
+        const int i = wd >> 2, t = wd & 3;
+        uint32_t word = 0;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const int qi = i8_quantize(row[blk * 64 + 16 * t + 4 * b + i], sc);
+            local += qi;
+            word |= (uint32_t)(uint8_t)(int8_t)qi << (8 * b);
+        }
+        qrow[w] = word;
+    }
+    local = warp_sum_i(local);
+    if (lane == 0) red_i[warp] = local;
+    __syncthreads();
+    if (tid == 0) {
+        int tot = 0;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) tot += red_i[w];
+        qsum[tok] = tot;
+        s[tok] = sc;
+    }
+}
+
+template <int MODE>
+static nnb_status launch_row_quant_mode(nnb_engine* e, bool exact, const float* in,
+                                        const float* gamma, size_t t, size_t k, size_t in_stride,
+                                        int8_t* q, float* s, int32_t* qsum, float* f_out)
+{
+    const size_t smem = k * sizeof(float);
+    static bool cfg = false;
+    if (!cfg) {
+        NNB_CUDA(cudaFuncSetAttribute(row_quant_kernel<MODE, true>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+        NNB_CUDA(cudaFuncSetAttribute(row_quant_kernel<MODE, false>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+        cfg = true;
+    }
+    if (exact)
+        row_quant_kernel<MODE, true><<<(unsigned)t, 256, smem, e->stream>>>(in, gamma, (int)k, (int)in_stride, q, s, qsum, f_out);
+    else
+        row_quant_kernel<MODE, false><<<(unsigned)t, 256, smem, e->stream>>>(in, gamma, (int)k, (int)in_stride, q, s, qsum, f_out);
+    e->launches++;
+    NNB_CHECK_LAUNCH("row_quant_kernel");
+    return NNB_OK;
+}
+
+nnb_status launch_row_quant(nnb_engine* e, int mode, bool exact, const float* in, const float* gamma,
+                            size_t t, size_t k, size_t in_stride, int8_t* q, float* s,
+                            int32_t* qsum, float* f_out)
+{
+    NNB_REQUIRE(in && q && s && qsum && t > 0, "row_quant: bad arguments");
+    NNB_REQUIRE(k > 0 && k % 64 == 0 && k * 4 <= 96 * 1024, "row_quant: k=%zu must be a multiple of 64 (<= 24576)", k);
+    switch (mode) {
+        case 0:
+            NNB_REQUIRE(gamma, "row_quant: RMSNorm needs gamma");
+            return launch_row_quant_mode<0>(e, exact, in, gamma, t, k, in_stride, q, s, qsum, f_out);
+        case 1: return launch_row_quant_mode<1>(e, exact, in, gamma, t, k, in_stride, q, s, qsum, f_out);
+        case 2: return launch_row_quant_mode<2>(e, exact, in, gamma, t, k, in_stride, q, s, qsum, f_out);
+        case 3: return launch_row_quant_mode<3>(e, exact, in, gamma, t, k, in_stride, q, s, qsum, f_out);
+    }
+    NNB_FAIL(NNB_ERR_INVALID, "row_quant: unknown mode %d", mode);
+}
+
+// ------------------------------------------------- decode attention (one new token)
+template <typename KV>
+__device__ __forceinline__ void load4(const KV* p, float (&v)[4]);
+template <>
+__device__ __forceinline__ void load4<float>(const float* p, float (&v)[4])
+{
+    const float4 t = *reinterpret_cast<const float4*>(p);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+template <>
+__device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[4])
+{
+    const uint2 t = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&t.x);
+    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&t.y);
+    v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
+}
+template <typename KV>
+__device__ __forceinline__ KV to_kv(float v);
+template <>
+__device__ __forceinline__ float to_kv<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 to_kv<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <typename KV>
+__device__ __forceinline__ float from_kv(KV v);
+template <>
+__device__ __forceinline__ float from_kv<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float from_kv<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+// grid = B*H, block = 128.  qkv is (3, B, d) f32 (the three projections of the new token).
+// Cache layout (B, H, ctx_alloc, dk) per layer for K (post-RoPE) and V.
+// 1. RoPE on q and k at position pos; k, v appended to the cache at row pos
+// 2. scores_j = (q . k_j) * scale for j <= pos; softmax; out = sum_j p_j v_j
+template <typename KV, bool EXACT>
+__global__ void __launch_bounds__(128)
+attn_decode_kernel(const float* __restrict__ qkv, KV* __restrict__ kcache, KV* __restrict__ vcache,
+                   const float* __restrict__ rope_cos, const float* __restrict__ rope_sin,
+                   const int* __restrict__ d_pos, int B, int H, int dk, int ctx_alloc, float scale,
+                   float* __restrict__ out)
+{
+    typedef typename AccT<EXACT>::type acc_t;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    float* qs = reinterpret_cast<float*>(smem_raw);        // dk (padded to 128)
+    float* sc = qs + 128;                                  // ctx_alloc
+    acc_t* red = reinterpret_cast<acc_t*>(sc + ((ctx_alloc + 3) & ~3));  // 8 * dk
+    __shared__ float bcast[4];
+    __shared__ acc_t bsum[4];
+
+    const int b = blockIdx.x / H, h = blockIdx.x % H;
+    const int d = H * dk;
+    const int pos = *d_pos;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const size_t head_off = ((size_t)b * H + h) * (size_t)ctx_alloc * dk;
+    KV* kc = kcache + head_off;
+    KV* vc = vcache + head_off;
+    const float* qn = qkv + (size_t)b * d + (size_t)h * dk;
+    const float* kn = qkv + (size_t)B * d + (size_t)b * d + (size_t)h * dk;
+    const float* vn = qkv + 2 * (size_t)B * d + (size_t)b * d + (size_t)h * dk;
+
+    // 1. RoPE + append
+    if (rope_cos) {
+        const int half = dk / 2;
+        for (int j = tid; j < half; j += 128) {
+            const float c = rope_cos[(size_t)pos * half + j], sn = rope_sin[(size_t)pos * half + j];
+            const float qa = qn[j], qb = qn[j + half];
+            const float ka = kn[j], kb = kn[j + half];
+            qs[j] = __fadd_rn(__fmul_rn(qa, c), __fmul_rn(-qb, sn));
+            qs[j + half] = __fadd_rn(__fmul_rn(qb, c), __fmul_rn(qa, sn));
+            kc[(size_t)pos * dk + j] = to_kv<KV>(__fadd_rn(__fmul_rn(ka, c), __fmul_rn(-kb, sn)));
+            kc[(size_t)pos * dk + j + half] = to_kv<KV>(__fadd_rn(__fmul_rn(kb, c), __fmul_rn(ka, sn)));
+        }
+    } else {
+        for (int j = tid; j < dk; j += 128) {
+            qs[j] = qn[j];
+            kc[(size_t)pos * dk + j] = to_kv<KV>(kn[j]);
+        }
+    }
+    for (int j = tid; j < dk; j += 128) vc[(size_t)pos * dk + j] = to_kv<KV>(vn[j]);
+    __syncthreads();
+
+    // lane mapping: LPK lanes per key, 4 contiguous features per lane
+    const int LPK = dk <= 64 ? 16 : 32;
+    const int KPW = 32 / LPK;  // keys per warp iteration
+    const int sub = lane / LPK, sl = lane % LPK;
+    const int e0 = sl * 4;
+    const bool act = e0 < dk;
+    float qv[4] = {0.f, 0.f, 0.f, 0.f};
+    if (act) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) qv[i] = qs[e0 + i];
+    }
+    const int n_keys = pos + 1;
+    const int key_stride = 4 * KPW;
+
+    // 2a. scores
+    for (int j0 = warp * KPW; j0 < n_keys; j0 += key_stride) {
+        const int j = j0 + sub;
+        acc_t part = 0;
+        if (act && j < n_keys) {
+            float kv[4];
+            load4<KV>(kc + (size_t)j * dk + e0, kv);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) part += (acc_t)qv[i] * (acc_t)kv[i];
+        }
+        for (int o = LPK / 2; o > 0; o >>= 1) part += shfl_xor_t(part, o);
+        if (sl == 0 && j < n_keys) sc[j] = __fmul_rn((float)part, scale);
+    }
+    __syncthreads();
+    // 2b. softmax over sc[0..n_keys)
+    float mx = -INFINITY;
+    for (int j = tid; j < n_keys; j += 128) mx = fmaxf(mx, sc[j]);
+    mx = warp_max(mx);
+    if (lane == 0) bcast[warp] = mx;
+    __syncthreads();
+    mx = fmaxf(fmaxf(bcast[0], bcast[1]), fmaxf(bcast[2], bcast[3]));
+    acc_t sum = 0;
+    for (int j = tid; j < n_keys; j += 128) {
+        const float ev = EXACT ? nnb_expf(__fsub_rn(sc[j], mx)) : __expf(sc[j] - mx);
+        sc[j] = ev;
+        sum += (acc_t)ev;
+    }
+    sum = warp_sum_t(sum);
+    if (lane == 0) bsum[warp] = sum;
+    __syncthreads();
+    const float sumf = (float)(bsum[0] + bsum[1] + bsum[2] + bsum[3]);
+    for (int j = tid; j < n_keys; j += 128) sc[j] = __fdiv_rn(sc[j], sumf);
+    __syncthreads();
+    // 2c. out = sum_j p_j v_j
+    acc_t o4[4] = {0, 0, 0, 0};
+    for (int j0 = warp * KPW; j0 < n_keys; j0 += key_stride) {
+        const int j = j0 + sub;
+        if (act && j < n_keys) {
+            float vv[4];
+            load4<KV>(vc + (size_t)j * dk + e0, vv);
+            const acc_t p = (acc_t)sc[j];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) o4[i] += p * (acc_t)vv[i];
+        }
+    }
+    const int grp = warp * KPW + sub;  // 0 .. 4*KPW-1
+    if (act) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) red[(size_t)grp * dk + e0 + i] = o4[i];
+    }
+    __syncthreads();
+    for (int i = tid; i < dk; i += 128) {
+        acc_t a = 0;
+        for (int gI = 0; gI < 4 * KPW; ++gI) a += red[(size_t)gI * dk + i];
+        out[(size_t)b * d + (size_t)h * dk + i] = (float)a;
+    }
+}
+
+nnb_status launch_attn_decode(nnb_engine* e, bool exact, const float* qkv, void* kcache, void* vcache,
+                              const float* rope_cos, const float* rope_sin, const int* d_pos,
+                              size_t B, size_t H, size_t dk, size_t ctx_alloc, float* out)
+{
+    NNB_REQUIRE(dk % 4 == 0 && dk <= 128 && dk >= 8, "attn_decode: head dim %zu unsupported (multiple of 4, <= 128)", dk);
+    const float scale = 1.0f / sqrtf((float)dk);
+    const size_t acc_sz = exact ? 8 : 4;
+    const size_t smem = 128 * 4 + ((ctx_alloc + 3) & ~(size_t)3) * 4 + 8 * dk * acc_sz + 16;
+    NNB_REQUIRE(smem <= 200 * 1024, "attn_decode: context %zu too long for one CTA", ctx_alloc);
+    const unsigned grid = (unsigned)(B * H);
+    if (exact) {
+        auto kern = attn_decode_kernel<float, true>;
+        static size_t cfg = 0;
+        if (smem > cfg) {
+            NNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            cfg = smem;
+        }
+        kern<<<grid, 128, smem, e->stream>>>(qkv, (float*)kcache, (float*)vcache, rope_cos, rope_sin, d_pos,
+                                             (int)B, (int)H, (int)dk, (int)ctx_alloc, scale, out);
+    } else {
+        auto kern = attn_decode_kernel<__nv_bfloat16, false>;
+        static size_t cfg = 0;
+        if (smem > cfg) {
+            NNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            cfg = smem;
+        }
+        kern<<<grid, 128, smem, e->stream>>>(qkv, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, rope_cos,
+                                             rope_sin, d_pos, (int)B, (int)H, (int)dk, (int)ctx_alloc, scale, out);
+    }
+    e->launches++;
+    NNB_CHECK_LAUNCH("attn_decode_kernel");
+    return NNB_OK;
+}
+
+// ------------------------------------------------------------------ sampler
+__device__ __forceinline__ uint32_t float_key(float v)
+{
+    // order-preserving map float -> uint32 (larger float -> larger key)
+    const uint32_t u = __float_as_uint(v);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+// One CTA (256 threads) per sequence.  logits (B, V) f32.  Writes the chosen token at
+// tokens[b, pos+1], and log softmax(raw logits)[token] into logp[b, gen_index] where
+// gen_index = pos + 1 - prompt_len.
+template <bool EXACT>
+__global__ void __launch_bounds__(256)
+sample_kernel(const float* __restrict__ logits, int V, float temperature, int top_k,
+              unsigned long long seed, unsigned seq0, const int* __restrict__ d_pos, int prompt_len,
+              int32_t* __restrict__ tokens, int tokens_stride, float* __restrict__ logp, int logp_stride,
+              float* __restrict__ entropy)
+{
+    typedef typename AccT<EXACT>::type acc_t;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    float* lg = reinterpret_cast<float*>(smem_raw);  // V scaled logits
+    int* cand = reinterpret_cast<int*>(lg + ((V + 3) & ~3));  // up to 1024 candidates
+    __shared__ int hist[256];
+    __shared__ int scan_a[256], scan_b[256];
+    __shared__ float red_f[8];
+    __shared__ int red_i[8];
+    __shared__ acc_t red_a[8];
+    __shared__ uint32_t sh_prefix;
+    __shared__ int sh_need, sh_tok;
+
+    const int b = blockIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int pos = *d_pos;
+    const int gen = pos + 1 - prompt_len;
+    const float* row = logits + (size_t)b * V;
+
+    // raw max and log-sum-exp (for the recorded log-prob)
+    float mx = -INFINITY;
+    for (int i = tid; i < V; i += 256) mx = fmaxf(mx, row[i]);
+    mx = warp_max(mx);
+    if (lane == 0) red_f[warp] = mx;
+    __syncthreads();
+    mx = red_f[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) mx = fmaxf(mx, red_f[w]);
+    acc_t se = 0, sxe = 0;
+    for (int i = tid; i < V; i += 256) {
+        const float dlt = row[i] - mx;
+        const float ev = expf(dlt);
+        se += (acc_t)ev;
+        sxe += (acc_t)ev * (acc_t)dlt;
+    }
+    se = warp_sum_t(se);
+    sxe = warp_sum_t(sxe);
+    __syncthreads();
+    if (lane == 0) red_a[warp] = se;
+    __syncthreads();
+    acc_t se_tot = 0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) se_tot += red_a[w];
+    __syncthreads();
+    if (lane == 0) red_a[warp] = sxe;
+    __syncthreads();
+    acc_t sxe_tot = 0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) sxe_tot += red_a[w];
+    const float lse = logf((float)se_tot);  // log sum exp(x - mx)
+    __syncthreads();
+
+    const bool scale_t = temperature > 0.0f && temperature != 1.0f;
+    for (int i = tid; i < V; i += 256) lg[i] = scale_t ? __fdiv_rn(row[i], temperature) : row[i];
+    __syncthreads();
+
+    if (!(temperature > 0.0f)) {
+        // greedy: largest value, ties to the smallest index
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int i = tid; i < V; i += 256) {
+            const float v = lg[i];
+            if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (lane == 0) { red_f[warp] = bv; red_i[warp] = bi; }
+        __syncthreads();
+        if (tid == 0) {
+            for (int w = 1; w < 8; ++w)
+                if (red_f[w] > bv || (red_f[w] == bv && red_i[w] < bi)) { bv = red_f[w]; bi = red_i[w]; }
+            sh_tok = bi;
+        }
+        __syncthreads();
+    } else {
+        const float r = philox_uniform(seed, seq0 + (unsigned)b, (unsigned)gen);
+        if (top_k > 0 && top_k < V) {
+            // radix select of the top_k-th largest key, 8 bits per pass
+            if (tid == 0) { sh_prefix = 0u; sh_need = top_k; }
+            __syncthreads();
+            for (int pass = 3; pass >= 0; --pass) {
+                hist[tid] = 0;
+                __syncthreads();
+                const uint32_t prefix = sh_prefix;
+                const uint32_t himask = pass == 3 ? 0u : (0xFFFFFFFFu << (8 * (pass + 1)));
+                for (int i = tid; i < V; i += 256) {
+                    const uint32_t key = float_key(lg[i]);
+                    if ((key & himask) == (prefix & himask)) atomicAdd(&hist[(key >> (8 * pass)) & 0xFF], 1);
+                }
+                __syncthreads();
+                if (tid == 0) {
+                    int need = sh_need;
+                    int bin = 255;
+                    for (; bin > 0; --bin) {
+                        if (hist[bin] >= need) break;
+                        need -= hist[bin];
+                    }
+                    sh_prefix = prefix | ((uint32_t)bin << (8 * pass));
+                    sh_need = need;
+                }
+                __syncthreads();
+            }
+            const uint32_t thr = sh_prefix;  // key of the top_k-th element
+            const int need_eq = sh_need;     // how many elements equal to thr are kept (smallest indices)
+            // ordered compaction: thread t owns the contiguous index range [t*chunk, (t+1)*chunk)
+            const int chunk = (V + 255) / 256;
+            const int lo = tid * chunk, hi = min(V, lo + chunk);
+            int n_gt = 0, n_eq = 0;
+            for (int i = lo; i < hi; ++i) {
+                const uint32_t key = float_key(lg[i]);
+                n_gt += key > thr;
+                n_eq += key == thr;
+            }
+            scan_a[tid] = n_gt;
+            scan_b[tid] = n_eq;
+            __syncthreads();
+            if (tid == 0) {
+                int a = 0, c = 0;
+                for (int t = 0; t < 256; ++t) {
+                    const int ta = scan_a[t], tb = scan_b[t];
+                    scan_a[t] = a;
+                    scan_b[t] = c;
+                    a += ta;
+                    c += tb;
+                }
+            }
+            __syncthreads();
+            {
+                int eq_before = scan_b[tid];
+                // selected count before this thread = gt before + min(eq before, need_eq)
+                int w = scan_a[tid] + min(eq_before, need_eq);
+                for (int i = lo; i < hi; ++i) {
+                    const uint32_t key = float_key(lg[i]);
+                    if (key > thr) cand[w++] = i;
+                    else if (key == thr) {
+                        if (eq_before < need_eq) cand[w++] = i;
+                        ++eq_before;
+                    }
+                }
+            }
+            __syncthreads();
+            if (tid == 0) {
+                // softmax over the candidates in ascending index order, f32, then inverse CDF
+                const int nc = top_k;
+                float m2 = lg[cand[0]];
+                for (int i = 1; i < nc; ++i) m2 = fmaxf(m2, lg[cand[i]]);
+                float sum = 0.0f;
+                for (int i = 0; i < nc; ++i) {
+                    const float ev = nnb_expf(__fsub_rn(lg[cand[i]], m2));
+                    lg[cand[i]] = ev;
+                    sum = __fadd_rn(sum, ev);
+                }
+                float cum = 0.0f;
+                int next = cand[nc - 1];
+                for (int i = 0; i < nc; ++i) {
+                    cum = __fadd_rn(cum, __fdiv_rn(lg[cand[i]], sum));
+                    if (r <= cum) { next = cand[i]; break; }
+                }
+                sh_tok = next;
+            }
+            __syncthreads();
+        } else {
+            // full vocabulary: p_i = exp(x_i - max)/sum with the sum and the CDF accumulated in
+            // f64 by contiguous chunks (the reference walks them in f32, ascending index)
+            float m2 = -INFINITY;
+            for (int i = tid; i < V; i += 256) m2 = fmaxf(m2, lg[i]);
+            m2 = warp_max(m2);
+            if (lane == 0) red_f[warp] = m2;
+            __syncthreads();
+            m2 = red_f[0];
+#pragma unroll
+            for (int w = 1; w < 8; ++w) m2 = fmaxf(m2, red_f[w]);
+            __shared__ double dsum[256];
+            const int chunk = (V + 255) / 256;
+            const int lo = tid * chunk, hi = min(V, lo + chunk);
+            double part = 0.0;
+            for (int i = lo; i < hi; ++i) {
+                const float ev = nnb_expf(__fsub_rn(lg[i], m2));
+                lg[i] = ev;
+                part += (double)ev;
+            }
+            dsum[tid] = part;
+            __syncthreads();
+            if (tid == 0) {
+                double tot = 0.0;
+                for (int t = 0; t < 256; ++t) tot += dsum[t];
+                const float sumf = (float)tot;
+                double cum = 0.0;
+                int next = V - 1;
+                bool found = false;
+                for (int t = 0; t < 256 && !found; ++t) {
+                    const int l2 = t * chunk, h2 = min(V, l2 + chunk);
+                    for (int i = l2; i < h2; ++i) {
+                        cum += (double)__fdiv_rn(lg[i], sumf);
+                        if ((double)r <= cum) { next = i; found = true; break; }
+                    }
+                }
+                sh_tok = next;
+            }
+            __syncthreads();
+        }
+    }
+    if (tid == 0) {
+        const int tok = sh_tok;
+        tokens[(size_t)b * tokens_stride + pos + 1] = tok;
+        if (logp) logp[(size_t)b * logp_stride + gen] = (row[tok] - mx) - lse;
+        if (entropy) entropy[(size_t)b * logp_stride + gen] = lse - (float)(sxe_tot / se_tot);
+    }
+}
+
+nnb_status launch_sample(nnb_engine* e, bool exact, const float* logits, size_t B, size_t V,
+                         float temperature, int top_k, unsigned long long seed, unsigned seq0,
+                         const int* d_pos, int prompt_len, int32_t* tokens, size_t tokens_stride,
+                         float* logp, size_t logp_stride, float* entropy)
+{
+    NNB_REQUIRE(logits && tokens && B > 0 && V > 0, "sample: bad arguments");
+    NNB_REQUIRE(top_k >= 0 && top_k <= 1024, "sample: top_k=%d out of range (0..1024)", top_k);
+    const size_t smem = ((V + 3) & ~(size_t)3) * 4 + 1024 * 4;
+    NNB_REQUIRE(smem <= 200 * 1024, "sample: vocabulary %zu too large for one CTA", V);
+    if (exact) {
+        auto kern = sample_kernel<true>;
+        static size_t cfg = 0;
+        if (smem > cfg) {
+            NNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            cfg = smem;
+        }
+        kern<<<(unsigned)B, 256, smem, e->stream>>>(logits, (int)V, temperature, top_k, seed, seq0, d_pos,
+                                                    prompt_len, tokens, (int)tokens_stride, logp,
+                                                    (int)logp_stride, entropy);
+    } else {
+        auto kern = sample_kernel<false>;
+        static size_t cfg = 0;
+        if (smem > cfg) {
+            NNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            cfg = smem;
+        }
+        kern<<<(unsigned)B, 256, smem, e->stream>>>(logits, (int)V, temperature, top_k, seed, seq0, d_pos,
+                                                    prompt_len, tokens, (int)tokens_stride, logp,
+                                                    (int)logp_stride, entropy);
+    }
+    e->launches++;
+    NNB_CHECK_LAUNCH("sample_kernel");
+    return NNB_OK;
+}
+
+__global__ void set_int_kernel(int* p, int v) { *p = v; }
+__global__ void add_int_kernel(int* p, int v) { *p += v; }
+
+nnb_status launch_set_int(nnb_engine* e, int* p, int v)
+{
+    set_int_kernel<<<1, 1, 0, e->stream>>>(p, v);
+    e->launches++;
+    NNB_CHECK_LAUNCH("set_int_kernel");
+    return NNB_OK;
+}
+nnb_status launch_add_int(nnb_engine* e, int* p, int v)
+{
+    add_int_kernel<<<1, 1, 0, e->stream>>>(p, v);
+    e->launches++;
+    NNB_CHECK_LAUNCH("add_int_kernel");
+    return NNB_OK;
+}
+
+nnb_status launch_embed(nnb_engine* e, const float* tok_emb, const float* pos_emb, const int32_t* tokens,
+                        size_t tokens_stride, const int* d_pos, size_t B, size_t d, size_t vocab, float* x)
+{
+    embed_kernel<<<(unsigned)B, 128, 0, e->stream>>>(tok_emb, pos_emb, tokens, (int)tokens_stride, d_pos,
+                                                     (int)d, (int)vocab, x);
+    e->launches++;
+    NNB_CHECK_LAUNCH("embed_kernel");
+    return NNB_OK;
+}
+
+}  // namespace nnb

@@ -1,0 +1,421 @@
+// policy.cu — the ternary GPT policy object: parameter storage, requantisation, and the
+// batched rollout (prefill + decode + sampling) that replaces per-sequence
+// GPTModel::generate (include/neuralnet.cpp/compute_layer_gpt.hpp:740-852).
+#include <math.h>
+#include <string.h>
+
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+#include "policy.cuh"
+
+namespace nnb {
+
+static void add_tensor(nnb_policy* p, const std::string& name, size_t off, size_t rows, size_t cols)
+{
+    p->tensors.push_back({name, off, rows, cols});
+}
+
+// Parameter order (one flat f32 buffer):
+//   tok_emb (V,d) | pos_emb (ctx,d) if learned |
+//   per layer: ln1_g | wq wk wv | bq bk bv | wo | bo | ln2_g | w1 | b1 | w2 | b2
+//   lnf_g | head_w (V,d) | head_b | value_w (1,d) | value_b if value head
+static void build_layout(nnb_policy* p)
+{
+    const nnb_gpt_config& c = p->cfg;
+    const size_t d = c.d_model, F = c.d_ff, V = c.vocab;
+    const size_t F1 = c.act == 1 ? 2 * F : F;
+    size_t o = 0, po = 0, to = 0;
+    auto lin = [&](LinW& l, const std::string& nm, size_t w_off, size_t b_off, size_t in, size_t out) {
+        l.w_off = w_off;
+        l.b_off = b_off;
+        l.in = in;
+        l.out = out;
+        l.packed_off = po;
+        l.tau_off = to;
+        po += out * (in / 16);
+        to += out;
+        add_tensor(p, nm + ".weight", w_off, out, in);
+        add_tensor(p, nm + ".bias", b_off, out, 1);
+    };
+    p->tok_emb = o;
+    add_tensor(p, "tok_emb", o, V, d);
+    o += V * d;
+    p->pos_emb = (size_t)-1;
+    if (c.pos == 0) {
+        p->pos_emb = o;
+        add_tensor(p, "pos_emb", o, c.ctx, d);
+        o += (size_t)c.ctx * d;
+    }
+    p->layers.resize(c.n_layer);
+    for (int l = 0; l < c.n_layer; ++l) {
+        LayerW& L = p->layers[l];
+        const std::string pre = "blocks." + std::to_string(l) + ".";
+        L.ln1_g = o;
+        add_tensor(p, pre + "ln1.gamma", o, d, 1);
+        o += d;
+        const size_t wq = o, wk = o + d * d, wv = o + 2 * d * d;
+        o += 3 * d * d;
+        const size_t bq = o, bk = o + d, bv = o + 2 * d;
+        o += 3 * d;
+        lin(L.q, pre + "attn.q", wq, bq, d, d);
+        lin(L.k, pre + "attn.k", wk, bk, d, d);
+        lin(L.v, pre + "attn.v", wv, bv, d, d);
+        const size_t wo = o;
+        o += d * d;
+        const size_t bo = o;
+        o += d;
+        lin(L.o, pre + "attn.o", wo, bo, d, d);
+        L.ln2_g = o;
+        add_tensor(p, pre + "ln2.gamma", o, d, 1);
+        o += d;
+        const size_t w1 = o;
+        o += F1 * d;
+        const size_t b1 = o;
+        o += F1;
+        lin(L.fc1, pre + "ffn.fc1", w1, b1, d, F1);
+        const size_t w2 = o;
+        o += d * F;
+        const size_t b2 = o;
+        o += d;
+        lin(L.fc2, pre + "ffn.fc2", w2, b2, F, d);
+    }
+    p->lnf_g = o;
+    add_tensor(p, "ln_f.gamma", o, d, 1);
+    o += d;
+    const size_t hw = o;
+    o += V * d;
+    const size_t hb = o;
+    o += V;
+    lin(p->head, "lm_head", hw, hb, d, V);
+    p->value_w = p->value_b = (size_t)-1;
+    if (c.value_head) {
+        p->value_w = o;
+        add_tensor(p, "value_head.weight", o, 1, d);
+        o += d;
+        p->value_b = o;
+        add_tensor(p, "value_head.bias", o, 1, 1);
+        o += 1;
+    }
+    p->n_params = o;
+    p->packed_words = po;
+    p->tau_count = to;
+}
+
+static nnb_status requantize_linear(nnb_policy* p, const LinW& l)
+{
+    float* tau = p->tau + l.tau_off;
+    NNB_TRY(launch_absmean_tau(p->e, p->params + l.w_off, l.out, l.in, tau));
+    return launch_trit_pack(p->e, p->params + l.w_off, tau, l.out, l.in, p->packed + l.packed_off);
+}
+
+nnb_status policy_requantize(nnb_policy* p)
+{
+    for (auto& L : p->layers) {
+        NNB_TRY(requantize_linear(p, L.q));
+        NNB_TRY(requantize_linear(p, L.k));
+        NNB_TRY(requantize_linear(p, L.v));
+        NNB_TRY(requantize_linear(p, L.o));
+        NNB_TRY(requantize_linear(p, L.fc1));
+        NNB_TRY(requantize_linear(p, L.fc2));
+    }
+    return requantize_linear(p, p->head);
+}
+
+void policy_free_train(nnb_policy*) {}
+
+static void free_decode(nnb_policy* p)
+{
+    DecodeWs& w = p->dec;
+    void* ptrs[] = {w.k, w.v, w.x, w.qkv, w.att, w.h1, w.logits, w.q8, w.s, w.qsum, w.d_pos, w.tokens, w.logp};
+    for (void* q : ptrs)
+        if (q) cudaFree(q);
+    w = DecodeWs();
+}
+
+static nnb_status ensure_decode(nnb_policy* p, size_t B, size_t ctx_alloc)
+{
+    DecodeWs& w = p->dec;
+    if (w.B == B && w.ctx_alloc == ctx_alloc) return NNB_OK;
+    NNB_CUDA(cudaStreamSynchronize(p->e->stream));
+    free_decode(p);
+    const nnb_gpt_config& c = p->cfg;
+    const size_t d = c.d_model, F = c.d_ff, V = c.vocab, F1 = c.act == 1 ? 2 * F : F;
+    const size_t kv_elem = c.exact ? 4 : 2;
+    const size_t kv_bytes = (size_t)c.n_layer * B * d * ctx_alloc * kv_elem;
+    size_t free_b = 0, total_b = 0;
+    NNB_CUDA(cudaMemGetInfo(&free_b, &total_b));
+    const size_t need = 2 * kv_bytes + B * (d * 4 * 5 + F1 * 4 + V * 4 + (F > d ? F : d)) + (64u << 20);
+    if (need > free_b)
+        NNB_FAIL(NNB_ERR_OOM, "rollout of %zu sequences x %zu positions needs %.1f GB (KV cache %.1f GB), %.1f GB free",
+                 B, ctx_alloc, need / 1e9, 2 * kv_bytes / 1e9, free_b / 1e9);
+#define NNB_ALLOC(ptr, bytes)                                                          \
+    do {                                                                               \
+        cudaError_t er__ = cudaMalloc((void**)&(ptr), (bytes));                        \
+        if (er__ != cudaSuccess) {                                                     \
+            cudaGetLastError();                                                        \
+            free_decode(p);                                                            \
+            NNB_FAIL(NNB_ERR_OOM, "cudaMalloc(%zu) failed: %s", (size_t)(bytes), cudaGetErrorString(er__)); \
+        }                                                                              \
+    } while (0)
+    NNB_ALLOC(w.k, kv_bytes);
+    NNB_ALLOC(w.v, kv_bytes);
+    NNB_ALLOC(w.x, B * d * 4);
+    NNB_ALLOC(w.qkv, 3 * B * d * 4);
+    NNB_ALLOC(w.att, B * d * 4);
+    NNB_ALLOC(w.h1, B * F1 * 4);
+    NNB_ALLOC(w.logits, B * V * 4);
+    NNB_ALLOC(w.q8, B * (F > d ? F : d));
+    NNB_ALLOC(w.s, B * 4);
+    NNB_ALLOC(w.qsum, B * 4);
+    NNB_ALLOC(w.d_pos, 16);
+    NNB_ALLOC(w.tokens, B * ctx_alloc * 4);
+    NNB_ALLOC(w.logp, B * ctx_alloc * 4);
+#undef NNB_ALLOC
+    w.B = B;
+    w.ctx_alloc = ctx_alloc;
+    return NNB_OK;
+}
+
+// one decode step at the position stored in d_pos: consumes tokens[:, pos], appends to the KV
+// cache and, when with_head, samples tokens[:, pos+1]
+static nnb_status decode_step(nnb_policy* p, bool with_head, float temperature, int top_k,
+                              unsigned long long seed, unsigned seq0, int prompt_len, bool want_logp)
+{
+    nnb_engine* e = p->e;
+    const nnb_gpt_config& c = p->cfg;
+    DecodeWs& w = p->dec;
+    const size_t B = w.B, d = c.d_model, F = c.d_ff, V = c.vocab, H = c.n_head, dk = d / H;
+    const size_t F1 = c.act == 1 ? 2 * F : F;
+    const bool exact = c.exact != 0;
+    const float* P = p->params;
+    const size_t kv_elem = exact ? 4 : 2;
+    const size_t layer_kv = B * d * w.ctx_alloc * kv_elem;
+
+    NNB_TRY(launch_embed(e, P + p->tok_emb, c.pos == 0 ? P + p->pos_emb : nullptr, w.tokens, w.ctx_alloc,
+                         w.d_pos, B, d, V, w.x));
+    for (int l = 0; l < c.n_layer; ++l) {
+        const LayerW& L = p->layers[l];
+        NNB_TRY(launch_row_quant(e, 0, exact, w.x, P + L.ln1_g, B, d, d, w.q8, w.s, w.qsum, nullptr));
+        // q, k, v projections: three equally shaped matrices stored back to back, one launch
+        NNB_TRY(launch_bitlinear_fwd_tm(e, p->packed + L.q.packed_off, d * (d / 16), p->tau + L.q.tau_off,
+                                        P + L.q.b_off, nullptr, w.q8, w.s, w.qsum, 3, B, d, d, w.qkv,
+                                        B * d, NNB_F32, nullptr));
+        NNB_TRY(launch_attn_decode(e, exact, w.qkv, (char*)w.k + (size_t)l * layer_kv,
+                                   (char*)w.v + (size_t)l * layer_kv, p->rope_cos, p->rope_sin, w.d_pos, B,
+                                   H, dk, w.ctx_alloc, w.att));
+        NNB_TRY(launch_row_quant(e, 3, exact, w.att, nullptr, B, d, d, w.q8, w.s, w.qsum, nullptr));
+        NNB_TRY(launch_bitlinear_fwd_tm(e, p->packed + L.o.packed_off, 0, p->tau + L.o.tau_off,
+                                        P + L.o.b_off, w.x, w.q8, w.s, w.qsum, 1, B, d, d, w.x, 0, NNB_F32,
+                                        nullptr));
+        NNB_TRY(launch_row_quant(e, 0, exact, w.x, P + L.ln2_g, B, d, d, w.q8, w.s, w.qsum, nullptr));
+        NNB_TRY(launch_bitlinear_fwd_tm(e, p->packed + L.fc1.packed_off, 0, p->tau + L.fc1.tau_off,
+                                        P + L.fc1.b_off, nullptr, w.q8, w.s, w.qsum, 1, B, d, F1, w.h1, 0,
+                                        NNB_F32, nullptr));
+        NNB_TRY(launch_row_quant(e, c.act == 1 ? 2 : 1, exact, w.h1, nullptr, B, F, F1, w.q8, w.s, w.qsum,
+                                 nullptr));
+        NNB_TRY(launch_bitlinear_fwd_tm(e, p->packed + L.fc2.packed_off, 0, p->tau + L.fc2.tau_off,
+                                        P + L.fc2.b_off, w.x, w.q8, w.s, w.qsum, 1, B, F, d, w.x, 0, NNB_F32,
+                                        nullptr));
+    }
+    if (with_head) {
+        NNB_TRY(launch_row_quant(e, 0, exact, w.x, P + p->lnf_g, B, d, d, w.q8, w.s, w.qsum, nullptr));
+        NNB_TRY(launch_bitlinear_fwd_tm(e, p->packed + p->head.packed_off, 0, p->tau + p->head.tau_off,
+                                        P + p->head.b_off, nullptr, w.q8, w.s, w.qsum, 1, B, d, V, w.logits,
+                                        0, NNB_F32, nullptr));
+        NNB_TRY(launch_sample(e, exact, w.logits, B, V, temperature, top_k, seed, seq0, w.d_pos, prompt_len,
+                              w.tokens, w.ctx_alloc, want_logp ? w.logp : nullptr, w.ctx_alloc, nullptr));
+    }
+    return NNB_OK;
+}
+
+nnb_status policy_rollout(nnb_policy* p, const int32_t* d_prompts, size_t B, size_t P, size_t max_new,
+                          float temperature, int top_k, unsigned long long seed, unsigned seq0,
+                          int32_t* d_tokens, float* d_logp, float* d_logits)
+{
+    NNB_REQUIRE(p && d_prompts && d_tokens, "rollout: NULL argument");
+    NNB_REQUIRE(B > 0 && P > 0 && max_new > 0, "rollout: empty shape");
+    NNB_REQUIRE(P + max_new <= (size_t)p->cfg.ctx, "rollout: prompt %zu + %zu new tokens exceeds the context %d",
+                P, max_new, p->cfg.ctx);
+    nnb_engine* e = p->e;
+    const size_t total = P + max_new;
+    NNB_TRY(ensure_decode(p, B, total));
+    DecodeWs& w = p->dec;
+    const size_t V = p->cfg.vocab;
+    NNB_CUDA(cudaMemcpy2DAsync(w.tokens, total * 4, d_prompts, P * 4, P * 4, B, cudaMemcpyDeviceToDevice,
+                               e->stream));
+    NNB_TRY(launch_set_int(e, w.d_pos, 0));
+    for (size_t t = 0; t + 1 < total; ++t) {
+        const bool with_head = t + 1 >= P;
+        NNB_TRY(decode_step(p, with_head, temperature, top_k, seed, seq0, (int)P, d_logp != nullptr));
+        if (with_head && d_logits) {
+            const size_t g = t + 1 - P;
+            NNB_CUDA(cudaMemcpy2DAsync(d_logits + g * V, max_new * V * 4, w.logits, V * 4, V * 4, B,
+                                       cudaMemcpyDeviceToDevice, e->stream));
+        }
+        NNB_TRY(launch_add_int(e, w.d_pos, 1));
+    }
+    NNB_CUDA(cudaMemcpyAsync(d_tokens, w.tokens, B * total * 4, cudaMemcpyDeviceToDevice, e->stream));
+    if (d_logp)
+        NNB_CUDA(cudaMemcpy2DAsync(d_logp, max_new * 4, w.logp, total * 4, max_new * 4, B,
+                                   cudaMemcpyDeviceToDevice, e->stream));
+    return NNB_OK;
+}
+
+}  // namespace nnb
+
+using namespace nnb;
+
+extern "C" {
+
+nnb_status nnb_policy_create(nnb_engine* e, const nnb_gpt_config* cfg, nnb_policy** out)
+{
+    NNB_REQUIRE(e && cfg && out, "policy_create: NULL argument");
+    *out = nullptr;
+    const nnb_gpt_config& c = *cfg;
+    NNB_REQUIRE(c.n_layer > 0 && c.d_model > 0 && c.n_head > 0 && c.d_ff > 0 && c.vocab > 0 && c.ctx > 0,
+                "policy_create: non-positive dimension");
+    NNB_REQUIRE(c.d_model % c.n_head == 0, "policy_create: d_model %d not divisible by n_head %d", c.d_model, c.n_head);
+    NNB_REQUIRE(c.d_model % 64 == 0 && c.d_ff % 64 == 0,
+                "policy_create: d_model and d_ff must be multiples of 64 (got %d, %d)", c.d_model, c.d_ff);
+    const int dk = c.d_model / c.n_head;
+    NNB_REQUIRE(dk % 4 == 0 && dk <= 128, "policy_create: head dim %d unsupported (multiple of 4, <= 128)", dk);
+    NNB_REQUIRE(c.act == 0 || c.act == 1, "policy_create: act must be 0 (QuickGELU) or 1 (SwiGLU)");
+    NNB_REQUIRE(c.pos == 0 || c.pos == 1, "policy_create: pos must be 0 (learned) or 1 (RoPE)");
+    NNB_REQUIRE(c.pos == 0 || dk % 2 == 0, "policy_create: RoPE needs an even head dim");
+    nnb_policy* p = new nnb_policy();
+    p->e = e;
+    p->cfg = c;
+    build_layout(p);
+    auto fail = [&](nnb_status st) {
+        nnb_policy_destroy(p);
+        return st;
+    };
+    if (cudaMalloc((void**)&p->params, p->n_params * 4) != cudaSuccess ||
+        cudaMalloc((void**)&p->packed, p->packed_words * 4) != cudaSuccess ||
+        cudaMalloc((void**)&p->tau, p->tau_count * 4) != cudaSuccess) {
+        cudaGetLastError();
+        nnb::set_error("policy_create: out of device memory for %zu parameters", p->n_params);
+        return fail(NNB_ERR_OOM);
+    }
+    cudaMemsetAsync(p->params, 0, p->n_params * 4, e->stream);
+    if (c.pos == 1) {
+        // RotaryEmbedding::fill_pos_column_ (compute_position_encoding.hpp:64-80): f32 host tables
+        const int half = dk / 2;
+        std::vector<float> cs((size_t)c.ctx * half), sn((size_t)c.ctx * half);
+        for (int pos = 0; pos < c.ctx; ++pos)
+            for (int j = 0; j < half; ++j) {
+                const float theta = (float)pos / powf(10000.0f, (float)(2 * j) / (float)dk);
+                cs[(size_t)pos * half + j] = cosf(theta);
+                sn[(size_t)pos * half + j] = sinf(theta);
+            }
+        if (cudaMalloc((void**)&p->rope_cos, cs.size() * 4) != cudaSuccess ||
+            cudaMalloc((void**)&p->rope_sin, sn.size() * 4) != cudaSuccess) {
+            cudaGetLastError();
+            nnb::set_error("policy_create: out of device memory for RoPE tables");
+            return fail(NNB_ERR_OOM);
+        }
+        cudaMemcpyAsync(p->rope_cos, cs.data(), cs.size() * 4, cudaMemcpyHostToDevice, e->stream);
+        cudaMemcpyAsync(p->rope_sin, sn.data(), sn.size() * 4, cudaMemcpyHostToDevice, e->stream);
+        cudaStreamSynchronize(e->stream);
+    }
+    *out = p;
+    return NNB_OK;
+}
+
+void nnb_policy_destroy(nnb_policy* p)
+{
+    if (!p) return;
+    cudaStreamSynchronize(p->e->stream);
+    free_decode(p);
+    policy_free_train(p);
+    void* ptrs[] = {p->params, p->grads, p->adam_m, p->adam_v, p->packed, p->tau, p->rope_cos, p->rope_sin};
+    for (void* q : ptrs)
+        if (q) cudaFree(q);
+    delete p;
+}
+
+size_t nnb_policy_param_count(const nnb_policy* p) { return p ? p->n_params : 0; }
+float* nnb_policy_params(nnb_policy* p) { return p ? p->params : nullptr; }
+size_t nnb_policy_tensor_count(const nnb_policy* p) { return p ? p->tensors.size() : 0; }
+
+nnb_status nnb_policy_tensor_info(const nnb_policy* p, size_t index, char* name, size_t name_len,
+                                  size_t* offset, size_t* rows, size_t* cols)
+{
+    NNB_REQUIRE(p && index < p->tensors.size(), "policy_tensor_info: index out of range");
+    const TensorInfo& t = p->tensors[index];
+    if (name && name_len) snprintf(name, name_len, "%s", t.name.c_str());
+    if (offset) *offset = t.offset;
+    if (rows) *rows = t.rows;
+    if (cols) *cols = t.cols;
+    return NNB_OK;
+}
+
+nnb_status nnb_policy_upload_params(nnb_policy* p, const float* h_params)
+{
+    NNB_REQUIRE(p && h_params, "policy_upload_params: NULL argument");
+    NNB_CUDA(cudaMemcpyAsync(p->params, h_params, p->n_params * 4, cudaMemcpyHostToDevice, p->e->stream));
+    NNB_TRY(policy_requantize(p));
+    NNB_CUDA(cudaStreamSynchronize(p->e->stream));
+    return NNB_OK;
+}
+
+nnb_status nnb_policy_requantize(nnb_policy* p)
+{
+    NNB_REQUIRE(p, "policy is NULL");
+    return policy_requantize(p);
+}
+
+nnb_status nnb_policy_linear(nnb_policy* p, int layer, int which, uint32_t** d_packed, float** d_tau,
+                             size_t* in, size_t* out)
+{
+    NNB_REQUIRE(p, "policy is NULL");
+    const LinW* l = nullptr;
+    if (layer < 0) l = &p->head;
+    else {
+        NNB_REQUIRE(layer < p->cfg.n_layer && which >= 0 && which < 6, "policy_linear: bad index");
+        LayerW& L = p->layers[layer];
+        const LinW* all[6] = {&L.q, &L.k, &L.v, &L.o, &L.fc1, &L.fc2};
+        l = all[which];
+    }
+    if (d_packed) *d_packed = p->packed + l->packed_off;
+    if (d_tau) *d_tau = p->tau + l->tau_off;
+    if (in) *in = l->in;
+    if (out) *out = l->out;
+    return NNB_OK;
+}
+
+nnb_status nnb_rollout(nnb_policy* p, const int32_t* d_prompts, size_t n_seq, size_t prompt_len,
+                       size_t max_new, float temperature, int top_k, uint64_t seed, uint32_t seq0,
+                       int32_t* d_tokens, float* d_logp, float* d_logits)
+{
+    return policy_rollout(p, d_prompts, n_seq, prompt_len, max_new, temperature, top_k, seed, seq0, d_tokens,
+                          d_logp, d_logits);
+}
+
+nnb_status nnb_rollout_host(nnb_policy* p, const int32_t* h_prompts, size_t n_seq, size_t prompt_len,
+                            size_t max_new, float temperature, int top_k, uint64_t seed, uint32_t seq0,
+                            int32_t* h_tokens, float* h_logp)
+{
+    NNB_REQUIRE(p && h_prompts && h_tokens, "rollout_host: NULL argument");
+    nnb_engine* e = p->e;
+    const size_t total = prompt_len + max_new;
+    auto al = [](size_t v) { return (v + 255) & ~(size_t)255; };
+    const size_t pb = al(n_seq * prompt_len * 4), tb = al(n_seq * total * 4), lb = al(n_seq * max_new * 4);
+    NNB_TRY(e->ensure_scratch(pb + tb + lb));
+    char* base = (char*)e->scratch;
+    int32_t* d_prompts = (int32_t*)base;
+    int32_t* d_tokens = (int32_t*)(base + pb);
+    float* d_logp = (float*)(base + pb + tb);
+    NNB_CUDA(cudaMemcpyAsync(d_prompts, h_prompts, n_seq * prompt_len * 4, cudaMemcpyHostToDevice, e->stream));
+    NNB_TRY(policy_rollout(p, d_prompts, n_seq, prompt_len, max_new, temperature, top_k, seed, seq0, d_tokens,
+                           h_logp ? d_logp : nullptr, nullptr));
+    NNB_CUDA(cudaMemcpyAsync(h_tokens, d_tokens, n_seq * total * 4, cudaMemcpyDeviceToHost, e->stream));
+    if (h_logp)
+        NNB_CUDA(cudaMemcpyAsync(h_logp, d_logp, n_seq * max_new * 4, cudaMemcpyDeviceToHost, e->stream));
+    NNB_CUDA(cudaStreamSynchronize(e->stream));
+    return NNB_OK;
+}
+
+}  // extern "C"

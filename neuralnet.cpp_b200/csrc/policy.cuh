@@ -1,0 +1,63 @@
+// policy.cuh — the policy object behind the opaque nnb_policy handle.
+#pragma once
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+
+namespace nnb {
+
+struct LinW {
+    size_t w_off = 0, b_off = 0;  // offsets (floats) of latent weight (out,in) and bias (out) in params
+    size_t in = 0, out = 0;
+    size_t packed_off = 0;        // offset (words) of the 2-bit container in `packed`
+    size_t tau_off = 0;           // offset of the per-row scales in `tau`
+};
+
+struct LayerW {
+    size_t ln1_g = 0, ln2_g = 0;
+    LinW q, k, v, o, fc1, fc2;
+};
+
+struct TensorInfo {
+    std::string name;
+    size_t offset, rows, cols;
+};
+
+struct DecodeWs {
+    size_t B = 0, ctx_alloc = 0;
+    void *k = nullptr, *v = nullptr;  // (L, B, H, ctx_alloc, dk), f32 in the exact mode else bf16
+    float *x = nullptr, *qkv = nullptr, *att = nullptr, *h1 = nullptr, *logits = nullptr;
+    int8_t* q8 = nullptr;
+    float* s = nullptr;
+    int32_t* qsum = nullptr;
+    int* d_pos = nullptr;
+    int32_t* tokens = nullptr;  // (B, ctx_alloc)
+    float* logp = nullptr;      // (B, ctx_alloc), generated index
+};
+
+}  // namespace nnb
+
+struct nnb_policy {
+    nnb_engine* e = nullptr;
+    nnb_gpt_config cfg{};
+    size_t n_params = 0, packed_words = 0, tau_count = 0;
+    float* params = nullptr;  // f32 master weights, flat
+    float* grads = nullptr;   // allocated on first training use
+    float* adam_m = nullptr;
+    float* adam_v = nullptr;
+    uint32_t* packed = nullptr;
+    float* tau = nullptr;
+    float *rope_cos = nullptr, *rope_sin = nullptr;  // (ctx, dk/2)
+    size_t tok_emb = 0, pos_emb = 0, lnf_g = 0, value_w = 0, value_b = 0;
+    std::vector<nnb::LayerW> layers;
+    nnb::LinW head;
+    std::vector<nnb::TensorInfo> tensors;
+    nnb::DecodeWs dec;
+    void* train = nullptr;  // training workspace (train.cu)
+};
+
+namespace nnb {
+nnb_status policy_requantize(nnb_policy* p);
+void policy_free_train(nnb_policy* p);
+}  // namespace nnb

@@ -16,46 +16,9 @@
 //              with q on the tensor cores (u8 x s8) and subtracts 2*qsum afterwards:
 //              sum (code-2)*q = sum code*q - 2*sum q, exact in int32.
 #include "common.cuh"
+#include "device_math.cuh"
 
 namespace nnb {
-
-// ------------------------------------------------------------------ helpers
-__device__ __forceinline__ uint32_t trit_code_of(float w, float tau)
-{
-    const float hi = __fmul_rn(tau, 0.5f);
-    const float lo = __fmul_rn(tau, -0.5f);
-    return w > hi ? 3u : (w < lo ? 1u : 2u);
-}
-
-__device__ __forceinline__ int i8_quantize(float x, float s)
-{
-    if (s == 0.0f) return 0;
-    float v = __fdiv_rn(x, s);
-    if (v != v) return 0;
-    v = fminf(fmaxf(v, -127.0f), 127.0f);
-    return (int)roundf(v);
-}
-
-__device__ __forceinline__ float warp_max(float v)
-{
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-    return v;
-}
-
-__device__ __forceinline__ int warp_sum_i(int v)
-{
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    return v;
-}
-
-__device__ __forceinline__ float warp_sum_f(float v)
-{
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    return v;
-}
 
 // position of source byte j (0..63) inside a permuted 64-byte block
 __host__ __device__ __forceinline__ int qperm_pos(int j)
@@ -64,7 +27,8 @@ __host__ __device__ __forceinline__ int qperm_pos(int j)
 }
 
 // ------------------------------------------------- reference-layout kernels
-// tau_r = sum_k |W[r,k]| * (1/K): one warp per row, lanes stride k, tree reduce.
+// tau_r = sum_k |W[r,k]| * (1/K): one warp per row.  Terms are f32 products; they are summed
+// in double and rounded once so the value does not depend on the reduction order.
 __global__ void absmean_tau_kernel(const float* __restrict__ latent, size_t rows, size_t k,
                                    float* __restrict__ tau)
 {
@@ -73,10 +37,11 @@ __global__ void absmean_tau_kernel(const float* __restrict__ latent, size_t rows
     const int lane = threadIdx.x & 31;
     const float inv = 1.0f / (float)k;
     const float* p = latent + row * k;
-    float s = 0.0f;
-    for (size_t c = lane; c < k; c += 32) s += __fmul_rn(fabsf(p[c]), inv);
-    s = warp_sum_f(s);
-    if (lane == 0) tau[row] = s;
+    double s = 0.0;
+    for (size_t c = lane; c < k; c += 32) s += (double)__fmul_rn(fabsf(p[c]), inv);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) tau[row] = (float)s;
 }
 
 // one thread per packed word

@@ -1,0 +1,183 @@
+"""Policy: host-side handle of the ternary GPT policy inside libnn-b200.so.
+
+Mirrors what a consumer of the reference does with build_gpt_model(engine, GptConfig)
+(include/neuralnet.cpp/domain_gpt.hpp:33-77) plus GPTModel::generate
+(include/neuralnet.cpp/compute_layer_gpt.hpp:740-852), batched over sequences.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from ._lib import NnbError, check, lib
+from .engine import Engine, _ptr
+
+GELU, SWIGLU = 0, 1
+LEARNED, ROPE = 0, 1
+
+
+class _CConfig(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in
+                ("n_layer", "d_model", "n_head", "d_ff", "vocab", "ctx", "act", "pos", "value_head", "exact")]
+
+
+@dataclass
+class GptConfig:
+    n_layer: int
+    d_model: int
+    n_head: int
+    d_ff: int
+    vocab: int
+    ctx: int
+    act: int = GELU
+    pos: int = LEARNED
+    value_head: bool = False
+    exact: bool = True
+
+    def to_c(self) -> _CConfig:
+        return _CConfig(self.n_layer, self.d_model, self.n_head, self.d_ff, self.vocab, self.ctx,
+                        self.act, self.pos, int(self.value_head), int(self.exact))
+
+    def param_layout(self):
+        """(name, offset, shape) of every tensor in the flat parameter buffer, in order."""
+        d, F, V = self.d_model, self.d_ff, self.vocab
+        F1 = 2 * F if self.act == SWIGLU else F
+        out, o = [], 0
+
+        def add(name, *shape):
+            nonlocal o
+            out.append((name, o, shape))
+            o += int(np.prod(shape))
+
+        add("tok_emb", V, d)
+        if self.pos == LEARNED:
+            add("pos_emb", self.ctx, d)
+        for l in range(self.n_layer):
+            p = f"blocks.{l}."
+            add(p + "ln1.gamma", d)
+            add(p + "attn.q.weight", d, d); add(p + "attn.k.weight", d, d); add(p + "attn.v.weight", d, d)
+            add(p + "attn.q.bias", d); add(p + "attn.k.bias", d); add(p + "attn.v.bias", d)
+            add(p + "attn.o.weight", d, d); add(p + "attn.o.bias", d)
+            add(p + "ln2.gamma", d)
+            add(p + "ffn.fc1.weight", F1, d); add(p + "ffn.fc1.bias", F1)
+            add(p + "ffn.fc2.weight", d, F); add(p + "ffn.fc2.bias", d)
+        add("ln_f.gamma", d)
+        add("lm_head.weight", V, d); add("lm_head.bias", V)
+        if self.value_head:
+            add("value_head.weight", 1, d); add("value_head.bias", 1)
+        return out, o
+
+    def init_params(self, seed: int, linear_std: float = 0.02, bias_std: float = 0.0) -> np.ndarray:
+        """Seeded synthetic initialisation: linears N(0, linear_std) (absmean-quantised by the engine),
+        embeddings N(0, 0.02), norm gains 1, biases N(0, bias_std) (0 = zeros, the reference default)."""
+        layout, n = self.param_layout()
+        rng = np.random.default_rng(seed)
+        flat = np.zeros(n, np.float32)
+        for name, off, shape in layout:
+            size = int(np.prod(shape))
+            if name.endswith("gamma"):
+                v = np.ones(size, np.float32)
+            elif name.endswith(".bias"):
+                v = rng.normal(0, bias_std, size).astype(np.float32) if bias_std > 0 else np.zeros(size, np.float32)
+            elif name in ("tok_emb", "pos_emb"):
+                v = rng.normal(0, 0.02, size).astype(np.float32)
+            else:
+                v = rng.normal(0, linear_std, size).astype(np.float32)
+            flat[off:off + size] = v
+        return flat
+
+
+class Policy:
+    def __init__(self, engine: Engine, cfg: GptConfig):
+        self._lib = lib()
+        self.engine = engine
+        self.cfg = cfg
+        h = C.c_void_p()
+        cc = cfg.to_c()
+        check(self._lib.nnb_policy_create(engine.handle, C.byref(cc), C.byref(h)))
+        self._h = h
+        self.n_params = int(self._lib.nnb_policy_param_count(self._h))
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._lib.nnb_policy_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def handle(self):
+        return self._h
+
+    def tensors(self):
+        out = []
+        n = int(self._lib.nnb_policy_tensor_count(self._h))
+        for i in range(n):
+            name = C.create_string_buffer(128)
+            off, rows, cols = C.c_size_t(), C.c_size_t(), C.c_size_t()
+            check(self._lib.nnb_policy_tensor_info(self._h, i, name, 128, C.byref(off), C.byref(rows), C.byref(cols)))
+            out.append((name.value.decode(), off.value, rows.value, cols.value))
+        return out
+
+    def params_view(self) -> torch.Tensor:
+        """The flat f32 master parameters as a torch tensor aliasing the engine's buffer."""
+        ptr = self._lib.nnb_policy_params(self._h)
+        return _alias(ptr, self.n_params, torch.float32, self.engine.device)
+
+    def upload_params(self, flat: np.ndarray):
+        flat = np.ascontiguousarray(flat, np.float32)
+        if flat.size != self.n_params:
+            raise NnbError(f"expected {self.n_params} parameters, got {flat.size}")
+        check(self._lib.nnb_policy_upload_params(self._h, flat.ctypes.data_as(C.c_void_p)))
+
+    def requantize(self):
+        check(self._lib.nnb_policy_requantize(self._h))
+
+    def linear(self, layer: int, which: int):
+        pk, tau = C.c_void_p(), C.c_void_p()
+        i, o = C.c_size_t(), C.c_size_t()
+        check(self._lib.nnb_policy_linear(self._h, layer, which, C.byref(pk), C.byref(tau), C.byref(i), C.byref(o)))
+        packed = _alias(pk.value, o.value * (i.value // 16), torch.int32, self.engine.device).view(o.value, i.value // 16)
+        return packed, _alias(tau.value, o.value, torch.float32, self.engine.device)
+
+    def rollout(self, prompts: torch.Tensor, max_new: int, temperature: float = 1.0, top_k: int = 0,
+                seed: int = 0, seq0: int = 0, want_logp: bool = True, want_logits: bool = False):
+        """prompts (B, P) int32 on the device -> tokens (B, P+max_new) int32, logp (B, max_new), [logits]."""
+        B, P = prompts.shape
+        dev = self.engine.device
+        tokens = torch.empty((B, P + max_new), device=dev, dtype=torch.int32)
+        logp = torch.empty((B, max_new), device=dev, dtype=torch.float32) if want_logp else None
+        logits = torch.empty((B, max_new, self.cfg.vocab), device=dev, dtype=torch.float32) if want_logits else None
+        check(self._lib.nnb_rollout(self._h, _ptr(prompts), B, P, max_new, float(temperature), int(top_k),
+                                    C.c_uint64(seed), C.c_uint32(seq0), _ptr(tokens), _ptr(logp), _ptr(logits)))
+        return tokens, logp, logits
+
+    def rollout_host(self, h_prompts: torch.Tensor, max_new: int, temperature: float, top_k: int, seed: int,
+                     seq0: int, h_tokens: torch.Tensor, h_logp: torch.Tensor | None):
+        B, P = h_prompts.shape
+        check(self._lib.nnb_rollout_host(self._h, C.c_void_p(h_prompts.data_ptr()), B, P, max_new,
+                                         float(temperature), int(top_k), C.c_uint64(seed), C.c_uint32(seq0),
+                                         C.c_void_p(h_tokens.data_ptr()),
+                                         C.c_void_p(h_logp.data_ptr()) if h_logp is not None else None))
+        return h_tokens, h_logp
+
+
+def _alias(ptr: int, numel: int, dtype, device) -> torch.Tensor:
+    """A torch tensor over engine-owned device memory (no copy, no ownership)."""
+    itemsize = torch.empty((), dtype=dtype).element_size()
+
+    class _Iface:
+        pass
+
+    holder = _Iface()
+    typestr = {torch.float32: "<f4", torch.int32: "<i4", torch.int8: "|i1"}[dtype]
+    holder.__cuda_array_interface__ = {"shape": (numel,), "typestr": typestr, "data": (int(ptr), False),
+                                       "version": 2, "strides": (itemsize,)}
+    return torch.as_tensor(holder, device=device)

@@ -62,17 +62,17 @@ ORC_API float orc_trit_at(const uint32_t* words, size_t i)
     return orc_trit_value_of((words[i / 16] >> (2 * (i % 16))) & 3u);
 }
 
-/* tau_o = sum_k |W[o,k]| * (1/K) in f32, k ascending
- * (compute_layer_bitlinear.hpp:637-640; the order of the f32 row sum is
- * engine-defined in the reference, so tau is tolerance-level: 1e-6 in
- * src/t1_58_test.cpp:291). */
+/* tau_o = sum_k |W[o,k]| * (1/K)  (compute_layer_bitlinear.hpp:637-640).  The terms are
+ * f32 products as in the reference; the order of the reference's f32 row sum is
+ * engine-defined (tau is tolerance-level there: 1e-6 in src/t1_58_test.cpp:291), so the
+ * sum is taken in double and rounded once, which makes it independent of the order. */
 ORC_API void orc_absmean_tau(const float* latent, size_t rows, size_t k, float* tau)
 {
     const float inv = 1.0f / (float)k;
     for (size_t r = 0; r < rows; ++r) {
-        float s = 0.0f;
-        for (size_t c = 0; c < k; ++c) s += fabsf(latent[r * k + c]) * inv;
-        tau[r] = s;
+        double s = 0.0;
+        for (size_t c = 0; c < k; ++c) s += (double)(fabsf(latent[r * k + c]) * inv);
+        tau[r] = (float)s;
     }
 }
 

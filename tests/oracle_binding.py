@@ -18,8 +18,8 @@ _SZ = C.c_size_t
 
 
 def _ensure_built():
-    src = os.path.join(ROOT, "oracle", "oracle.c")
-    if not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(src):
+    srcs = [os.path.join(ROOT, "oracle", f) for f in ("oracle.c", "oracle_model.c")]
+    if not os.path.exists(_SO) or os.path.getmtime(_SO) < max(os.path.getmtime(f) for f in srcs):
         subprocess.run(["make", "-s", "-C", os.path.join(ROOT, "oracle")], check=True)
 
 
@@ -176,3 +176,126 @@ class Oracle:
                                    q, _c(s, np.float32), t, k, out, y.ctypes.data,
                                    acc.ctypes.data if acc is not None else None)
         return (y, acc) if want_acc else y
+
+
+# ------------------------------------------------------------------ GPT model (oracle_model.c)
+class _OrcCfg(C.Structure):
+    _fields_ = [(n, C.c_int) for n in
+                ("n_layer", "d_model", "n_head", "d_ff", "vocab", "ctx", "act", "pos", "value_head")]
+
+
+class OracleGpt:
+    """CPU restatement of the GPT decode path on a flat parameter buffer (same order as the engine's)."""
+
+    def __init__(self, cfg, flat_params: np.ndarray):
+        _ensure_built()
+        L = C.CDLL(_SO)
+        self.L = L
+        self.cfg = cfg
+        self._c = _OrcCfg(cfg.n_layer, cfg.d_model, cfg.n_head, cfg.d_ff, cfg.vocab, cfg.ctx, cfg.act, cfg.pos,
+                          int(cfg.value_head))
+        L.orc_gpt_param_count.restype = _SZ
+        L.orc_gpt_param_count.argtypes = [C.POINTER(_OrcCfg)]
+        L.orc_gpt_create.restype = C.c_void_p
+        L.orc_gpt_create.argtypes = [C.POINTER(_OrcCfg), _f32p]
+        L.orc_gpt_destroy.argtypes = [C.c_void_p]
+        L.orc_gpt_get_linear.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+        L.orc_gpt_rollout.restype = C.c_int
+        L.orc_gpt_rollout.argtypes = [C.c_void_p, _i32p, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int,
+                                      C.c_uint64, C.c_uint32, _i32p, C.c_void_p, C.c_void_p]
+        L.orc_gpt_step_logits.restype = C.c_int
+        L.orc_gpt_step_logits.argtypes = [C.c_void_p, _i32p, C.c_int, _f32p]
+        self.params = np.ascontiguousarray(flat_params, np.float32)  # keep alive: the model points into it
+        assert self.params.size == L.orc_gpt_param_count(C.byref(self._c))
+        self.h = L.orc_gpt_create(C.byref(self._c), self.params)
+
+    def __del__(self):
+        try:
+            if self.h:
+                self.L.orc_gpt_destroy(self.h)
+                self.h = None
+        except Exception:
+            pass
+
+    def param_count(self):
+        return int(self.L.orc_gpt_param_count(C.byref(self._c)))
+
+    def linear(self, layer, which, rows, cols):
+        tau = np.empty(rows, np.float32)
+        trit = np.empty((rows, cols), np.int8)
+        self.L.orc_gpt_get_linear(self.h, layer, which, tau.ctypes.data, trit.ctypes.data)
+        return tau, trit
+
+    def rollout(self, prompts, max_new, temperature, top_k, seed, seq0=0, want_logits=False):
+        prompts = np.ascontiguousarray(prompts, np.int32)
+        B, P = prompts.shape
+        tokens = np.empty((B, P + max_new), np.int32)
+        logp = np.empty((B, max_new), np.float32)
+        logits = np.empty((B, max_new, self.cfg.vocab), np.float32) if want_logits else None
+        rc = self.L.orc_gpt_rollout(self.h, prompts, B, P, max_new, temperature, top_k, seed, seq0, tokens,
+                                    logp.ctypes.data, logits.ctypes.data if logits is not None else None)
+        assert rc == 0
+        return tokens, logp, logits
+
+    def step_logits(self, tokens):
+        tokens = np.ascontiguousarray(tokens, np.int32)
+        out = np.empty((len(tokens), self.cfg.vocab), np.float32)
+        assert self.L.orc_gpt_step_logits(self.h, tokens, len(tokens), out) == 0
+        return out
+
+
+def _bind_extra(L):
+    L.orc_expf.restype = C.c_float
+    L.orc_expf.argtypes = [C.c_float]
+    L.orc_philox_uniform.restype = C.c_float
+    L.orc_philox_uniform.argtypes = [C.c_uint64, C.c_uint32, C.c_uint32]
+    L.orc_sample_token.restype = C.c_int
+    L.orc_sample_token.argtypes = [_f32p, C.c_int, C.c_float, C.c_int, C.c_float]
+    L.orc_rmsnorm.argtypes = [_f32p, _f32p, C.c_int, C.c_float, _f32p]
+    L.orc_logprob_entropy.argtypes = [_f32p, C.c_int, C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_float)]
+
+
+def _oracle_extra(self):
+    _bind_extra(self.L)
+
+
+def _expf(self, x):
+    return float(self.L.orc_expf(x))
+
+
+def _philox(self, seed, seq, step):
+    return float(self.L.orc_philox_uniform(seed, seq, step))
+
+
+def _sample(self, logits, temperature, top_k, r):
+    work = np.ascontiguousarray(logits, np.float32).copy()
+    return int(self.L.orc_sample_token(work, len(work), temperature, top_k, r))
+
+
+def _rmsnorm(self, x, gamma, eps=1e-5):
+    x = _c(x, np.float32)
+    out = np.empty_like(x)
+    self.L.orc_rmsnorm(x, _c(gamma, np.float32), len(x), eps, out)
+    return out
+
+
+def _logprob_entropy(self, logits, token):
+    lp, h = C.c_float(), C.c_float()
+    self.L.orc_logprob_entropy(_c(logits, np.float32), len(logits), token, C.byref(lp), C.byref(h))
+    return lp.value, h.value
+
+
+_orig_init = Oracle.__init__
+
+
+def _init(self):
+    _orig_init(self)
+    _bind_extra(self.L)
+
+
+Oracle.__init__ = _init
+Oracle.expf = _expf
+Oracle.philox_uniform = _philox
+Oracle.sample_token = _sample
+Oracle.rmsnorm = _rmsnorm
+Oracle.logprob_entropy = _logprob_entropy
