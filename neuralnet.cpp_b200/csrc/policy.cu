@@ -4,6 +4,7 @@
 #include <math.h>
 #include <string.h>
 
+#include <algorithm>
 #include <string>
 #include <vector>
 
@@ -98,6 +99,8 @@ static void build_layout(nnb_policy* p)
         add_tensor(p, "value_head.bias", o, 1, 1);
         o += 1;
     }
+    std::sort(p->tensors.begin(), p->tensors.end(),
+              [](const TensorInfo& a, const TensorInfo& b) { return a.offset < b.offset; });
     p->n_params = o;
     p->packed_words = po;
     p->tau_count = to;
