@@ -185,6 +185,54 @@ nnb_status nnb_rollout_host(nnb_policy* p, const int32_t* h_prompts, size_t n_se
                             size_t max_new, float temperature, int top_k, uint64_t seed, uint32_t seq0,
                             int32_t* h_tokens, float* h_logp);
 
+/* ================= advantages, objectives, optimizer ======================
+ * Per-decision vectors are plain f32 arrays of length n (the reference's (1,T) tensors);
+ * logits are token-major (t, vocab).  Nothing here synchronises with the host. */
+
+/* GaeAdvantage::apply (include/neuralnet.cpp/rl_experience.hpp:273-380).  rewards, values,
+ * done, mask, outputs are (steps, batch) with row = time; done, mask, bootstrap (batch) may be NULL. */
+nnb_status nnb_gae(nnb_engine* e, const float* d_rewards, const float* d_values, const float* d_done,
+                   const float* d_mask, const float* d_bootstrap, size_t steps, size_t batch, float gamma,
+                   float lambda, float* d_advantage, float* d_returns);
+/* GroupAdvantage::apply (rl_experience.hpp:516-545): spans (first_row, row_count) given on the
+ * host must be contiguous and cover all n rows, else NNB_ERR_INVALID. */
+nnb_status nnb_group_advantage(nnb_engine* e, const float* d_returns, size_t n, const int32_t* h_first,
+                               const int32_t* h_count, size_t n_spans, float eps, float* d_out);
+/* MaskedNormalizer::apply (rl_experience.hpp:456-498); mask may be NULL (all ones) */
+nnb_status nnb_masked_normalize(nnb_engine* e, const float* d_values, const float* d_mask, size_t n, float eps,
+                                float* d_out);
+/* CategoricalDistribution::log_prob / entropy (include/neuralnet.cpp/rl_policy.hpp:92-143) */
+nnb_status nnb_categorical_logp_entropy(nnb_engine* e, const float* d_logits, const int32_t* d_actions, size_t t,
+                                        size_t v, float* d_logp, float* d_entropy);
+/* log_prob_with_gradient + entropy_with_gradient (rl_policy.hpp:145-187):
+ * dlogits = (onehot - p)*up_logp + (-p*(log p + H))*up_entropy; either upstream may be NULL */
+nnb_status nnb_categorical_backward(nnb_engine* e, const float* d_logits, const int32_t* d_actions,
+                                    const float* d_up_logp, const float* d_up_entropy, size_t t, size_t v,
+                                    float* d_dlogits);
+/* ClippedPolicyObjective + SampledKlObjective + EntropyBonusObjective in one pass
+ * (rl_policy.hpp:564-661, 503-530, 460-481; the PPO / GRPO presets :799-953 sum them).
+ * units <= 0 means sum(mask); pass the global count when the batch is sharded.
+ * d_old_logp/d_advantage (clipped term), d_ref_logp (KL term) and d_entropy may be NULL.
+ * Outputs: d_up_logp = d loss/d logp, d_up_entropy = d loss/d entropy (may be NULL),
+ * d_report[8] = policy_loss, ratio_mean, approx_kl, clip_fraction, kl_loss, entropy_loss,
+ * mean entropy, units (may be NULL). */
+nnb_status nnb_token_objective(nnb_engine* e, const float* d_logp, const float* d_entropy, const float* d_old_logp,
+                               const float* d_ref_logp, const float* d_advantage, const float* d_mask, size_t n,
+                               float units, float clip_eps, float kl_coef, float entropy_coef, float* d_up_logp,
+                               float* d_up_entropy, float* d_report);
+/* ClippedValueObjective (rl_policy.hpp:670-773); d_report[2] = value_loss, clip_fraction */
+nnb_status nnb_clipped_value(nnb_engine* e, const float* d_value, const float* d_returns, const float* d_old_value,
+                             const float* d_mask, size_t n, float units, float clip_eps, float coef, float* d_grad,
+                             float* d_report);
+/* Optimizer::clip_grad_norm (include/neuralnet.cpp/compute_optimizer.hpp:134-187); the norm
+ * before clipping is written to d_norm_out (may be NULL) */
+nnb_status nnb_clip_grad_norm(nnb_engine* e, float* d_grads, size_t n, float max_norm, float* d_norm_out);
+/* ComputeEngine::scale_inplace */
+nnb_status nnb_scale_inplace(nnb_engine* e, float* d_x, size_t n, float scale);
+/* AdamW::step (compute_optimizer.hpp:384-436,563-597) at 1-based step t */
+nnb_status nnb_adamw_step(nnb_engine* e, float* d_params, const float* d_grads, float* d_m, float* d_v, size_t n,
+                          float lr, float beta1, float beta2, float eps, float weight_decay, int t);
+
 #ifdef __cplusplus
 }
 #endif

@@ -116,4 +116,27 @@ nnb_status launch_add_int(nnb_engine* e, int* p, int v);
 nnb_status launch_embed(nnb_engine* e, const float* tok_emb, const float* pos_emb, const int32_t* tokens,
                         size_t tokens_stride, const int* d_pos, size_t B, size_t d, size_t vocab, float* x);
 
+// ---- rl.cu
+nnb_status launch_gae(nnb_engine* e, const float* rewards, const float* values, const float* done,
+                      const float* mask, const float* bootstrap, size_t steps, size_t batch, float gamma,
+                      float lambda, float* adv, float* ret);
+nnb_status launch_group_advantage(nnb_engine* e, const float* returns, const int32_t* first, const int32_t* count,
+                                  size_t n_spans, float eps, float* out);
+nnb_status launch_masked_normalize(nnb_engine* e, const float* x, const float* mask, size_t n, float eps, float* out);
+nnb_status launch_categorical_fwd(nnb_engine* e, const float* logits, const int32_t* actions, size_t t, size_t v,
+                                  float* logp, float* entropy);
+nnb_status launch_categorical_bwd(nnb_engine* e, const float* logits, const int32_t* actions, const float* up_lp,
+                                  const float* up_ent, size_t t, size_t v, float* dlogits);
+nnb_status launch_token_objective(nnb_engine* e, const float* logp, const float* entropy, const float* old_logp,
+                                  const float* ref_logp, const float* adv, const float* mask, size_t n,
+                                  float units_override, float clip_eps, float kl_coef, float ent_coef,
+                                  float* up_lp, float* up_ent, float* report);
+nnb_status launch_clipped_value(nnb_engine* e, const float* value, const float* returns, const float* old_value,
+                                const float* mask, size_t n, float units_override, float clip_eps, float coef,
+                                float* grad, float* report);
+nnb_status launch_clip_grad_norm(nnb_engine* e, float* g, size_t n, float max_norm, float* norm_out);
+nnb_status launch_scale(nnb_engine* e, float* x, size_t n, float sc);
+nnb_status launch_adamw(nnb_engine* e, float* p, const float* g, float* m, float* v, size_t n, float lr,
+                        float beta1, float beta2, float eps, float wd, int t);
+
 }  // namespace nnb

@@ -177,3 +177,90 @@ class Engine:
                                                C.c_void_p(h_x.data_ptr()), t, k, out,
                                                C.c_void_p(h_y.data_ptr())))
         return h_y
+
+
+# ------------------------------------------------------------------ RL operators
+def _f32(self, *shape):
+    return torch.empty(shape, device=self.device, dtype=torch.float32)
+
+
+def gae(self, rewards, values, done=None, mask=None, bootstrap=None, gamma=0.99, lam=0.95):
+    """GaeAdvantage::apply — (steps, batch) tensors, row = time.  Returns (advantage, returns)."""
+    steps, batch = rewards.shape
+    adv, ret = _f32(self, steps, batch), _f32(self, steps, batch)
+    check(self._lib.nnb_gae(self._h, _ptr(rewards), _ptr(values), _ptr(done), _ptr(mask), _ptr(bootstrap),
+                            steps, batch, gamma, lam, _ptr(adv), _ptr(ret)))
+    return adv, ret
+
+
+def group_advantage(self, returns, spans, eps=1e-8):
+    """GroupAdvantage::apply — returns (N,), spans = [(first_row, row_count), ...]."""
+    import numpy as np
+
+    first = np.ascontiguousarray([s[0] for s in spans], np.int32)
+    count = np.ascontiguousarray([s[1] for s in spans], np.int32)
+    out = _f32(self, returns.numel())
+    check(self._lib.nnb_group_advantage(self._h, _ptr(returns), returns.numel(), first.ctypes.data_as(C.c_void_p),
+                                        count.ctypes.data_as(C.c_void_p), len(spans), eps, _ptr(out)))
+    return out
+
+
+def masked_normalize(self, values, mask=None, eps=1e-8):
+    out = torch.empty_like(values)
+    check(self._lib.nnb_masked_normalize(self._h, _ptr(values), _ptr(mask), values.numel(), eps, _ptr(out)))
+    return out
+
+
+def categorical_logp_entropy(self, logits, actions):
+    t, v = logits.shape
+    logp, ent = _f32(self, t), _f32(self, t)
+    check(self._lib.nnb_categorical_logp_entropy(self._h, _ptr(logits), _ptr(actions), t, v, _ptr(logp), _ptr(ent)))
+    return logp, ent
+
+
+def categorical_backward(self, logits, actions, up_logp=None, up_entropy=None):
+    t, v = logits.shape
+    out = torch.empty_like(logits)
+    check(self._lib.nnb_categorical_backward(self._h, _ptr(logits), _ptr(actions), _ptr(up_logp), _ptr(up_entropy),
+                                             t, v, _ptr(out)))
+    return out
+
+
+def token_objective(self, logp, mask, old_logp=None, advantage=None, ref_logp=None, entropy=None, units=0.0,
+                    clip_eps=0.2, kl_coef=0.0, entropy_coef=0.0):
+    """Clipped policy + sampled KL + entropy bonus.  Returns (up_logp, up_entropy, report[8])."""
+    n = logp.numel()
+    up_lp, up_ent, report = _f32(self, n), _f32(self, n), _f32(self, 8)
+    check(self._lib.nnb_token_objective(self._h, _ptr(logp), _ptr(entropy), _ptr(old_logp), _ptr(ref_logp),
+                                        _ptr(advantage), _ptr(mask), n, units, clip_eps, kl_coef, entropy_coef,
+                                        _ptr(up_lp), _ptr(up_ent), _ptr(report)))
+    return up_lp, up_ent, report
+
+
+def clipped_value(self, value, returns, old_value, mask, units=0.0, clip_eps=0.2, coef=1.0):
+    n = value.numel()
+    grad, report = _f32(self, n), _f32(self, 2)
+    check(self._lib.nnb_clipped_value(self._h, _ptr(value), _ptr(returns), _ptr(old_value), _ptr(mask), n, units,
+                                      clip_eps, coef, _ptr(grad), _ptr(report)))
+    return grad, report
+
+
+def clip_grad_norm(self, grads, max_norm):
+    norm = _f32(self, 1)
+    check(self._lib.nnb_clip_grad_norm(self._h, _ptr(grads), grads.numel(), max_norm, _ptr(norm)))
+    return norm
+
+
+def scale_inplace(self, x, scale):
+    check(self._lib.nnb_scale_inplace(self._h, _ptr(x), x.numel(), scale))
+    return x
+
+
+def adamw_step(self, params, grads, m, v, lr, t, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01):
+    check(self._lib.nnb_adamw_step(self._h, _ptr(params), _ptr(grads), _ptr(m), _ptr(v), params.numel(), lr, beta1,
+                                   beta2, eps, weight_decay, t))
+
+
+for _f in (gae, group_advantage, masked_normalize, categorical_logp_entropy, categorical_backward,
+           token_objective, clipped_value, clip_grad_norm, scale_inplace, adamw_step):
+    setattr(Engine, _f.__name__, _f)

@@ -18,7 +18,7 @@ _SZ = C.c_size_t
 
 
 def _ensure_built():
-    srcs = [os.path.join(ROOT, "oracle", f) for f in ("oracle.c", "oracle_model.c")]
+    srcs = [os.path.join(ROOT, "oracle", f) for f in ("oracle.c", "oracle_model.c", "oracle_rl.c")]
     if not os.path.exists(_SO) or os.path.getmtime(_SO) < max(os.path.getmtime(f) for f in srcs):
         subprocess.run(["make", "-s", "-C", os.path.join(ROOT, "oracle")], check=True)
 
@@ -299,3 +299,119 @@ Oracle.philox_uniform = _philox
 Oracle.sample_token = _sample
 Oracle.rmsnorm = _rmsnorm
 Oracle.logprob_entropy = _logprob_entropy
+
+
+# ------------------------------------------------------------------ RL (oracle_rl.c)
+class _PolicyMetrics(C.Structure):
+    _fields_ = [("loss", C.c_float), ("ratio_mean", C.c_float), ("approx_kl", C.c_float),
+                ("clip_fraction", C.c_float)]
+
+
+def _opt(a):
+    return None if a is None else _c(a, np.float32).ctypes.data_as(C.c_void_p)
+
+
+class OracleRL:
+    def __init__(self):
+        _ensure_built()
+        L = C.CDLL(_SO)
+        self.L = L
+        vp = C.c_void_p
+        L.orc_gae.argtypes = [_f32p, _f32p, vp, vp, vp, _SZ, _SZ, C.c_float, C.c_float, _f32p, _f32p]
+        L.orc_masked_normalize.argtypes = [_f32p, vp, _SZ, C.c_float, _f32p]
+        L.orc_group_advantage.restype = C.c_int
+        L.orc_group_advantage.argtypes = [_f32p, _SZ, _i32p, _i32p, _SZ, C.c_float, _f32p]
+        L.orc_categorical_logp_entropy.argtypes = [_f32p, _i32p, _SZ, _SZ, _f32p, _f32p]
+        L.orc_categorical_backward.argtypes = [_f32p, _i32p, vp, vp, _SZ, _SZ, _f32p]
+        L.orc_clipped_policy.argtypes = [_f32p, _f32p, _f32p, _f32p, _SZ, C.c_float, _f32p, C.POINTER(_PolicyMetrics)]
+        L.orc_entropy_bonus.restype = C.c_float
+        L.orc_entropy_bonus.argtypes = [_f32p, _f32p, _SZ, C.c_float, _f32p]
+        L.orc_sampled_kl.restype = C.c_float
+        L.orc_sampled_kl.argtypes = [_f32p, _f32p, _f32p, _SZ, C.c_float, _f32p]
+        L.orc_clipped_value.restype = C.c_float
+        L.orc_clipped_value.argtypes = [_f32p, _f32p, _f32p, _f32p, _SZ, C.c_float, C.c_float, _f32p,
+                                        C.POINTER(C.c_float)]
+        L.orc_clip_grad_norm.restype = C.c_float
+        L.orc_clip_grad_norm.argtypes = [_f32p, _SZ, C.c_float]
+        L.orc_adamw.argtypes = [_f32p, _f32p, _f32p, _f32p, _SZ, C.c_float, C.c_float, C.c_float, C.c_float,
+                                C.c_float, C.c_int]
+
+    def gae(self, rewards, values, done=None, mask=None, bootstrap=None, gamma=0.99, lam=0.95):
+        r = _c(rewards, np.float32)
+        steps, batch = r.shape
+        adv, ret = np.empty_like(r), np.empty_like(r)
+        keep = [_c(x, np.float32) if x is not None else None for x in (done, mask, bootstrap)]
+        ptr = [k.ctypes.data_as(C.c_void_p) if k is not None else None for k in keep]
+        self.L.orc_gae(r, _c(values, np.float32), ptr[0], ptr[1], ptr[2], steps, batch, gamma, lam, adv, ret)
+        return adv, ret
+
+    def masked_normalize(self, values, mask=None, eps=1e-8):
+        v = _c(values, np.float32)
+        out = np.empty_like(v)
+        m = _c(mask, np.float32) if mask is not None else None
+        self.L.orc_masked_normalize(v.ravel(), m.ctypes.data_as(C.c_void_p) if m is not None else None, v.size, eps,
+                                    out.ravel())
+        return out
+
+    def group_advantage(self, returns, spans, eps=1e-8):
+        r = _c(returns, np.float32)
+        out = np.empty_like(r)
+        first = np.ascontiguousarray([s[0] for s in spans], np.int32)
+        count = np.ascontiguousarray([s[1] for s in spans], np.int32)
+        rc = self.L.orc_group_advantage(r, r.size, first, count, len(spans), eps, out)
+        return out if rc == 0 else None
+
+    def categorical_logp_entropy(self, logits, actions):
+        lg = _c(logits, np.float32)
+        t, v = lg.shape
+        logp, ent = np.empty(t, np.float32), np.empty(t, np.float32)
+        self.L.orc_categorical_logp_entropy(lg, _c(actions, np.int32), t, v, logp, ent)
+        return logp, ent
+
+    def categorical_backward(self, logits, actions, up_lp=None, up_ent=None):
+        lg = _c(logits, np.float32)
+        t, v = lg.shape
+        out = np.empty_like(lg)
+        a = _c(up_lp, np.float32) if up_lp is not None else None
+        b = _c(up_ent, np.float32) if up_ent is not None else None
+        self.L.orc_categorical_backward(lg, _c(actions, np.int32), a.ctypes.data_as(C.c_void_p) if a is not None else None,
+                                        b.ctypes.data_as(C.c_void_p) if b is not None else None, t, v, out)
+        return out
+
+    def clipped_policy(self, logp, old_logp, adv, mask, clip_eps=0.2):
+        n = len(logp)
+        up = np.empty(n, np.float32)
+        m = _PolicyMetrics()
+        self.L.orc_clipped_policy(_c(logp, np.float32), _c(old_logp, np.float32), _c(adv, np.float32),
+                                  _c(mask, np.float32), n, clip_eps, up, C.byref(m))
+        return up, dict(loss=m.loss, ratio_mean=m.ratio_mean, approx_kl=m.approx_kl, clip_fraction=m.clip_fraction)
+
+    def entropy_bonus(self, entropy, mask, coef):
+        n = len(entropy)
+        up = np.empty(n, np.float32)
+        loss = self.L.orc_entropy_bonus(_c(entropy, np.float32), _c(mask, np.float32), n, coef, up)
+        return float(loss), up
+
+    def sampled_kl(self, logp, ref, mask, coef):
+        n = len(logp)
+        up = np.empty(n, np.float32)
+        loss = self.L.orc_sampled_kl(_c(logp, np.float32), _c(ref, np.float32), _c(mask, np.float32), n, coef, up)
+        return float(loss), up
+
+    def clipped_value(self, value, returns, old_value, mask, clip_eps=0.2, coef=1.0):
+        n = len(value)
+        grad = np.empty(n, np.float32)
+        cf = C.c_float()
+        loss = self.L.orc_clipped_value(_c(value, np.float32), _c(returns, np.float32), _c(old_value, np.float32),
+                                        _c(mask, np.float32), n, clip_eps, coef, grad, C.byref(cf))
+        return float(loss), grad, cf.value
+
+    def clip_grad_norm(self, g, max_norm):
+        g = np.ascontiguousarray(g, np.float32).copy()
+        norm = self.L.orc_clip_grad_norm(g, g.size, max_norm)
+        return g, float(norm)
+
+    def adamw(self, p, g, m, v, lr, t, beta1=0.9, beta2=0.999, eps=1e-8, wd=0.01):
+        p, m, v = (np.ascontiguousarray(x, np.float32).copy() for x in (p, m, v))
+        self.L.orc_adamw(p, _c(g, np.float32), m, v, p.size, lr, beta1, beta2, eps, wd, t)
+        return p, m, v
