@@ -142,4 +142,4 @@ def test_clip_grad_norm(rl):
     g, norm = rl.clip_grad_norm([3.0, 4.0], 1.0)
     assert abs(norm - 5.0) < 1e-6 and near(g, [0.6, 0.8], 1e-6)
     g, norm = rl.clip_grad_norm([0.3, 0.4], 1.0)
-    assert near(g, [0.3, 0.4], 0)
+    assert np.array_equal(g, np.array([0.3, 0.4], np.float32))  # below the limit: untouched
