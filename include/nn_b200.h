@@ -185,6 +185,50 @@ nnb_status nnb_rollout_host(nnb_policy* p, const int32_t* h_prompts, size_t n_se
                             size_t max_new, float temperature, int top_k, uint64_t seed, uint32_t seq0,
                             int32_t* h_tokens, float* h_logp);
 
+/* ---- training of the policy on micro-batches of whole sequences.
+ * A sequence of seq_len tokens whose first prompt_len are the prompt has G = seq_len - prompt_len
+ * decisions; decision g is taken at position prompt_len-1+g and its action is token prompt_len+g.
+ * Per-decision vectors are (n_seq, G) f32 on the device. */
+
+/* teacher-forced GPTModel::forward (include/neuralnet.cpp/compute_layer_gpt.hpp:460-543) followed by
+ * CategoricalDistribution::log_prob / entropy; d_entropy and d_value may be NULL.  No gradients:
+ * this is how a frozen reference policy (TrainingGroupSession readonly role,
+ * include/neuralnet.cpp/training_group_session.hpp:102-110) is evaluated. */
+nnb_status nnb_policy_logprobs(nnb_policy* p, const int32_t* d_tokens, size_t n_seq, size_t seq_len, size_t prompt_len,
+                               float* d_logp, float* d_entropy, float* d_value);
+
+/* the objective of one training micro-batch: PpoObjective / GrpoObjective with explicit advantages
+ * (include/neuralnet.cpp/rl_policy.hpp:799-953) plus a sampled-KL term against a reference policy */
+typedef struct nnb_objective {
+    const float* d_mask;       /* action mask, required */
+    const float* d_old_logp;   /* with d_advantage: clipped policy term; both NULL to skip */
+    const float* d_advantage;
+    const float* d_ref_logp;   /* KL term (kl_coef != 0) */
+    const float* d_returns;    /* value term (value_coef != 0): returns and old values */
+    const float* d_old_value;
+    float units;               /* normalisation count; <= 0 = sum of this micro-batch's mask.  Pass the
+                                  count of the whole (global) batch when it is split into micro-batches
+                                  or across GPUs (normalization_units, training_session.hpp:102-109) */
+    float clip_eps, kl_coef, entropy_coef, value_coef, value_clip_eps;
+} nnb_objective;
+
+/* forward + objective + GPTModel::backward (compute_layer_gpt.hpp:545-636): gradients are ADDED to the
+ * policy's gradient buffer.  d_report[10] (may be NULL) = policy_loss, ratio_mean, approx_kl,
+ * clip_fraction, kl_loss, entropy_loss, mean entropy, units, value_loss, value clip_fraction. */
+nnb_status nnb_policy_train_step(nnb_policy* p, const int32_t* d_tokens, size_t n_seq, size_t seq_len,
+                                 size_t prompt_len, const nnb_objective* obj, float* d_report);
+/* flat f32 gradient buffer, same layout as the parameters (allocated and zeroed on first use) */
+float* nnb_policy_grads(nnb_policy* p);
+nnb_status nnb_policy_zero_grad(nnb_policy* p);
+/* TrainingSession::finish_update_ (include/neuralnet.cpp/training_session.hpp:599-638): global-norm clip
+ * (max_grad_norm <= 0 disables), AdamW step, zero_grad, and requantisation of every BitLinear.  The
+ * gradient norm before clipping goes to d_norm_out (may be NULL).  With several GPUs, all-reduce
+ * nnb_policy_grads before calling this. */
+nnb_status nnb_policy_optimizer_step(nnb_policy* p, float lr, float beta1, float beta2, float eps, float weight_decay,
+                                     float max_grad_norm, float* d_norm_out);
+/* frees the rollout (KV cache) and training workspaces; they are re-created on demand */
+nnb_status nnb_policy_release_workspaces(nnb_policy* p);
+
 /* ================= advantages, objectives, optimizer ======================
  * Per-decision vectors are plain f32 arrays of length n (the reference's (1,T) tensors);
  * logits are token-major (t, vocab).  Nothing here synchronises with the host. */

@@ -60,6 +60,12 @@ _SIGNATURES = {
     "nnb_policy_requantize": (_I, [_P]),
     "nnb_policy_linear": (_I, [_P, _I, _I, C.POINTER(_P), C.POINTER(_P), C.POINTER(_SZ), C.POINTER(_SZ)]),
     "nnb_rollout": (_I, [_P, _P, _SZ, _SZ, _SZ, C.c_float, _I, C.c_uint64, C.c_uint32, _P, _P, _P]),
+    "nnb_policy_logprobs": (_I, [_P, _P, _SZ, _SZ, _SZ, _P, _P, _P]),
+    "nnb_policy_train_step": (_I, [_P, _P, _SZ, _SZ, _SZ, _P, _P]),
+    "nnb_policy_grads": (_P, [_P]),
+    "nnb_policy_zero_grad": (_I, [_P]),
+    "nnb_policy_optimizer_step": (_I, [_P, C.c_float, C.c_float, C.c_float, C.c_float, C.c_float, C.c_float, _P]),
+    "nnb_policy_release_workspaces": (_I, [_P]),
     "nnb_gae": (_I, [_P, _P, _P, _P, _P, _P, _SZ, _SZ, C.c_float, C.c_float, _P, _P]),
     "nnb_group_advantage": (_I, [_P, _P, _SZ, _P, _P, _SZ, C.c_float, _P]),
     "nnb_masked_normalize": (_I, [_P, _P, _P, _SZ, C.c_float, _P]),

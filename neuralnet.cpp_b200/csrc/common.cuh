@@ -139,4 +139,38 @@ nnb_status launch_scale(nnb_engine* e, float* x, size_t n, float sc);
 nnb_status launch_adamw(nnb_engine* e, float* p, const float* g, float* m, float* v, size_t n, float lr,
                         float beta1, float beta2, float eps, float wd, int t);
 
+// ---- gemm_float.cu
+// dx (t,k) (+)= (dy (t,out) * tau) . trit (out,k)
+nnb_status launch_bitlinear_dx(nnb_engine* e, bool exact, const float* dy, const uint32_t* wq, const float* tau,
+                               size_t t, size_t k, size_t out, float* dx, bool accumulate);
+// dw (out,k) += tau * ((dy * s)^T . q)
+nnb_status launch_bitlinear_dw(nnb_engine* e, bool exact, const float* dy, const int8_t* q, const float* s,
+                               const float* tau, size_t t, size_t k, size_t out, float* dw);
+nnb_status launch_colsum_add(nnb_engine* e, const float* dy, size_t t, size_t out, float* db);
+
+// ---- train.cu
+nnb_status launch_embed_fwd(nnb_engine* e, const float* tok_emb, const float* pos_emb, const int32_t* tokens,
+                            size_t n_rows, size_t S, size_t d, size_t vocab, float* x);
+nnb_status launch_embed_bwd(nnb_engine* e, const float* g, const int32_t* tokens, size_t n_rows, size_t S, size_t d,
+                            size_t vocab, float* g_tok, float* g_pos);
+nnb_status launch_rope(nnb_engine* e, float* x, const float* rope_cos, const float* rope_sin, size_t n_rows,
+                       size_t S, size_t H, size_t dk, bool backward);
+nnb_status launch_attn_fwd(nnb_engine* e, const float* q, const float* k, const float* v, size_t n_seq, size_t S,
+                           size_t H, size_t dk, float* out, float* lse);
+nnb_status launch_attn_bwd(nnb_engine* e, const float* q, const float* k, const float* v, const float* out,
+                           const float* dout, const float* lse, float* delta, size_t n_seq, size_t S, size_t H,
+                           size_t dk, float* dq, float* dkk, float* dvv);
+nnb_status launch_rmsnorm_bwd(nnb_engine* e, const float* x, const float* gamma, const float* dy,
+                              const float* residual, size_t T, size_t F, float* dx, float* dgamma);
+nnb_status launch_act_bwd(nnb_engine* e, int mode, const float* h, const float* da, size_t T, size_t F, float* dh);
+nnb_status launch_gather_decisions(nnb_engine* e, const float* src, size_t n_seq, size_t S, size_t P, size_t G,
+                                   size_t d, float* dst);
+nnb_status launch_scatter_decisions(nnb_engine* e, const float* src, size_t n_seq, size_t S, size_t P, size_t G,
+                                    size_t d, float* dst);
+nnb_status launch_value_fwd(nnb_engine* e, const float* x, const float* w, const float* b, size_t n, size_t d,
+                            float* value);
+nnb_status launch_value_bwd(nnb_engine* e, const float* x, const float* w, const float* dv, size_t n, size_t d,
+                            float* dx, float* dw, float* db);
+nnb_status launch_add(nnb_engine* e, float* dst, const float* src, size_t n);
+
 }  // namespace nnb

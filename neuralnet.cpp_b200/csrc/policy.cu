@@ -126,8 +126,6 @@ nnb_status policy_requantize(nnb_policy* p)
     return requantize_linear(p, p->head);
 }
 
-void policy_free_train(nnb_policy*) {}
-
 static void free_decode(nnb_policy* p)
 {
     DecodeWs& w = p->dec;
@@ -136,6 +134,8 @@ static void free_decode(nnb_policy* p)
         if (q) cudaFree(q);
     w = DecodeWs();
 }
+
+void policy_free_decode(nnb_policy* p) { free_decode(p); }
 
 static nnb_status ensure_decode(nnb_policy* p, size_t B, size_t ctx_alloc)
 {

@@ -46,6 +46,7 @@ struct nnb_policy {
     float* grads = nullptr;   // allocated on first training use
     float* adam_m = nullptr;
     float* adam_v = nullptr;
+    int adam_t = 0;  // optimizer steps taken
     uint32_t* packed = nullptr;
     float* tau = nullptr;
     float *rope_cos = nullptr, *rope_sin = nullptr;  // (ctx, dk/2)
@@ -60,4 +61,5 @@ struct nnb_policy {
 namespace nnb {
 nnb_status policy_requantize(nnb_policy* p);
 void policy_free_train(nnb_policy* p);
+void policy_free_decode(nnb_policy* p);
 }  // namespace nnb

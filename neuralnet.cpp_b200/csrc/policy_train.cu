@@ -1,0 +1,373 @@
+// policy_train.cu — teacher-forced forward, objective and backward of the ternary GPT policy,
+// and the optimizer step.  Replaces the reference's
+//   GPTModel::forward / backward            include/neuralnet.cpp/compute_layer_gpt.hpp:460-636
+//   PpoObjective / GrpoObjective::evaluate  include/neuralnet.cpp/rl_policy.hpp:799-953
+//   TrainingSession::train_named_step, finish_update_  include/neuralnet.cpp/training_session.hpp:322-467,599-638
+// for one micro-batch of whole sequences.  Gradients accumulate (+=) into the policy's flat
+// gradient buffer, as the reference's layers accumulate into their grad tensors; the caller
+// runs as many micro-batches as it likes before nnb_policy_optimizer_step.
+//
+// Decisions: sequence b of length S with a prompt of P tokens has G = S - P decisions; decision g
+// is taken at position P-1+g and its action is token P+g.  All per-decision vectors are (n_seq, G).
+#include <vector>
+
+#include "common.cuh"
+#include "policy.cuh"
+
+namespace nnb {
+
+struct LayerSave {
+    float *x_in = nullptr, *qkv = nullptr, *att = nullptr, *lse = nullptr, *x_mid = nullptr, *h1 = nullptr;
+    int8_t *q1 = nullptr, *q2 = nullptr, *q3 = nullptr, *q4 = nullptr;
+    float *s1 = nullptr, *s2 = nullptr, *s3 = nullptr, *s4 = nullptr;
+};
+
+struct TrainWs {
+    size_t n_seq = 0, S = 0, P = 0;
+    bool saved_layers = false;
+    char* arena = nullptr;
+    size_t arena_bytes = 0;
+    std::vector<LayerSave> L;
+    float* x_last = nullptr;  // output of the last block (T,d)
+    int32_t* qsum = nullptr;
+    // head
+    int32_t* actions = nullptr;
+    float *xd = nullptr, *hn = nullptr, *sh = nullptr, *logits = nullptr, *logp = nullptr, *ent = nullptr,
+          *value = nullptr, *up_lp = nullptr, *up_ent = nullptr, *dvalue = nullptr, *dhn = nullptr, *report = nullptr,
+          *vreport = nullptr;
+    int8_t* qh = nullptr;
+    // backward temporaries
+    float *g = nullptr, *g2 = nullptr, *dn = nullptr, *datt = nullptr, *dqkv = nullptr, *da = nullptr, *dh1 = nullptr,
+          *delta = nullptr;
+};
+
+void policy_free_train(nnb_policy* p)
+{
+    TrainWs* w = (TrainWs*)p->train;
+    if (!w) return;
+    if (w->arena) cudaFree(w->arena);
+    delete w;
+    p->train = nullptr;
+}
+
+static nnb_status ensure_train(nnb_policy* p, size_t n_seq, size_t S, size_t P, bool save_layers)
+{
+    TrainWs* w = (TrainWs*)p->train;
+    if (w && w->n_seq == n_seq && w->S == S && w->P == P && (w->saved_layers || !save_layers)) return NNB_OK;
+    NNB_CUDA(cudaStreamSynchronize(p->e->stream));
+    policy_free_train(p);
+    w = new TrainWs();
+    p->train = w;
+    const nnb_gpt_config& c = p->cfg;
+    const size_t d = c.d_model, F = c.d_ff, F1 = c.act == 1 ? 2 * F : F, V = c.vocab, H = c.n_head;
+    const size_t T = n_seq * S, G = S - P, Td = n_seq * G;
+    const size_t n_save = save_layers ? (size_t)c.n_layer : 1;
+    // carve one arena: first pass measures, second assigns
+    for (int pass = 0; pass < 2; ++pass) {
+        size_t off = 0;
+        auto take = [&](size_t bytes) -> char* {
+            char* ptr = w->arena ? w->arena + off : nullptr;
+            off += (bytes + 255) & ~(size_t)255;
+            return ptr;
+        };
+        w->L.assign(c.n_layer, LayerSave());
+        for (size_t l = 0; l < n_save; ++l) {
+            LayerSave s;
+            s.x_in = (float*)take(T * d * 4);
+            s.qkv = (float*)take(3 * T * d * 4);
+            s.att = (float*)take(T * d * 4);
+            s.lse = (float*)take(n_seq * H * S * 4);
+            s.x_mid = (float*)take(T * d * 4);
+            s.h1 = (float*)take(T * F1 * 4);
+            s.q1 = (int8_t*)take(T * d);
+            s.q2 = (int8_t*)take(T * d);
+            s.q3 = (int8_t*)take(T * d);
+            s.q4 = (int8_t*)take(T * F);
+            s.s1 = (float*)take(T * 4);
+            s.s2 = (float*)take(T * 4);
+            s.s3 = (float*)take(T * 4);
+            s.s4 = (float*)take(T * 4);
+            w->L[l] = s;
+        }
+        if (!save_layers)
+            for (int l = 1; l < c.n_layer; ++l) w->L[l] = w->L[0];
+        w->x_last = (float*)take(T * d * 4);
+        w->qsum = (int32_t*)take(T * 4);
+        w->actions = (int32_t*)take(Td * 4);
+        w->xd = (float*)take(Td * d * 4);
+        w->hn = (float*)take(Td * d * 4);
+        w->qh = (int8_t*)take(Td * d);
+        w->sh = (float*)take(Td * 4);
+        w->logits = (float*)take(Td * V * 4);
+        w->logp = (float*)take(Td * 4);
+        w->ent = (float*)take(Td * 4);
+        w->value = (float*)take(Td * 4);
+        w->up_lp = (float*)take(Td * 4);
+        w->up_ent = (float*)take(Td * 4);
+        w->dvalue = (float*)take(Td * 4);
+        w->report = (float*)take(64);
+        w->vreport = (float*)take(64);
+        if (save_layers) {
+            w->dhn = (float*)take(Td * d * 4);
+            w->g = (float*)take(T * d * 4);
+            w->g2 = (float*)take(T * d * 4);
+            w->dn = (float*)take(T * d * 4);
+            w->datt = (float*)take(T * d * 4);
+            w->dqkv = (float*)take(3 * T * d * 4);
+            w->da = (float*)take(T * F * 4);
+            w->dh1 = (float*)take(T * F1 * 4);
+            w->delta = (float*)take(n_seq * H * S * 4);
+        }
+        if (pass == 0) {
+            size_t free_b = 0, total_b = 0;
+            NNB_CUDA(cudaMemGetInfo(&free_b, &total_b));
+            if (off + (256u << 20) > free_b) {
+                policy_free_train(p);
+                NNB_FAIL(NNB_ERR_OOM, "training workspace for %zu sequences x %zu needs %.1f GB, %.1f GB free: use smaller micro-batches",
+                         n_seq, S, off / 1e9, free_b / 1e9);
+            }
+            cudaError_t er = cudaMalloc((void**)&w->arena, off);
+            if (er != cudaSuccess) {
+                cudaGetLastError();
+                policy_free_train(p);
+                NNB_FAIL(NNB_ERR_OOM, "cudaMalloc(%zu) for the training workspace failed: %s", off, cudaGetErrorString(er));
+            }
+            w->arena_bytes = off;
+        }
+    }
+    w->n_seq = n_seq;
+    w->S = S;
+    w->P = P;
+    w->saved_layers = save_layers;
+    return NNB_OK;
+}
+
+__global__ void gather_actions_kernel(const int32_t* __restrict__ tokens, int S, int P, int G, size_t n,
+                                      int32_t* __restrict__ actions)
+{
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const size_t b = i / G, g = i % G;
+    actions[i] = tokens[b * S + P + g];
+}
+
+static nnb_status lin_fwd(nnb_policy* p, const LinW& l, size_t n_mats, const int8_t* q, const float* s,
+                          const int32_t* qsum, size_t T, const float* residual, float* y, size_t y_stride)
+{
+    return launch_bitlinear_fwd_tm(p->e, p->packed + l.packed_off, n_mats > 1 ? l.out * (l.in / 16) : 0,
+                                   p->tau + l.tau_off, p->params + l.b_off, residual, q, s, qsum, n_mats, T, l.in, l.out,
+                                   y, y_stride, NNB_F32, nullptr);
+}
+
+// teacher-forced forward of n_seq sequences; fills w->logp / w->ent / w->value for the decisions
+static nnb_status forward(nnb_policy* p, const int32_t* tokens, size_t n_seq, size_t S, size_t P, bool want_entropy)
+{
+    nnb_engine* e = p->e;
+    const nnb_gpt_config& c = p->cfg;
+    TrainWs* w = (TrainWs*)p->train;
+    const size_t d = c.d_model, F = c.d_ff, F1 = c.act == 1 ? 2 * F : F, V = c.vocab, H = c.n_head, dk = d / H;
+    const size_t T = n_seq * S, G = S - P, Td = n_seq * G;
+    const bool exact = c.exact != 0;
+    const float* PP = p->params;
+    NNB_TRY(launch_embed_fwd(e, PP + p->tok_emb, c.pos == 0 ? PP + p->pos_emb : nullptr, tokens, T, S, d, V, w->L[0].x_in));
+    for (int l = 0; l < c.n_layer; ++l) {
+        const LayerW& LW = p->layers[l];
+        LayerSave& s = w->L[l];
+        float* x_out = (l + 1 < c.n_layer) ? w->L[l + 1].x_in : w->x_last;
+        if (!w->saved_layers) x_out = (l % 2 == 0) ? w->x_last : w->L[0].x_in;  // ping-pong when nothing is kept
+        const float* x_in = (!w->saved_layers) ? ((l % 2 == 0) ? w->L[0].x_in : w->x_last) : s.x_in;
+        NNB_TRY(launch_row_quant(e, 0, exact, x_in, PP + LW.ln1_g, T, d, d, s.q1, s.s1, w->qsum, nullptr));
+        NNB_TRY(lin_fwd(p, LW.q, 3, s.q1, s.s1, w->qsum, T, nullptr, s.qkv, T * d));
+        if (c.pos == 1) {
+            NNB_TRY(launch_rope(e, s.qkv, p->rope_cos, p->rope_sin, T, S, H, dk, false));
+            NNB_TRY(launch_rope(e, s.qkv + T * d, p->rope_cos, p->rope_sin, T, S, H, dk, false));
+        }
+        NNB_TRY(launch_attn_fwd(e, s.qkv, s.qkv + T * d, s.qkv + 2 * T * d, n_seq, S, H, dk, s.att, s.lse));
+        NNB_TRY(launch_row_quant(e, 3, exact, s.att, nullptr, T, d, d, s.q2, s.s2, w->qsum, nullptr));
+        NNB_TRY(lin_fwd(p, LW.o, 1, s.q2, s.s2, w->qsum, T, x_in, s.x_mid, 0));
+        NNB_TRY(launch_row_quant(e, 0, exact, s.x_mid, PP + LW.ln2_g, T, d, d, s.q3, s.s3, w->qsum, nullptr));
+        NNB_TRY(lin_fwd(p, LW.fc1, 1, s.q3, s.s3, w->qsum, T, nullptr, s.h1, 0));
+        NNB_TRY(launch_row_quant(e, c.act == 1 ? 2 : 1, exact, s.h1, nullptr, T, F, F1, s.q4, s.s4, w->qsum, nullptr));
+        NNB_TRY(lin_fwd(p, LW.fc2, 1, s.q4, s.s4, w->qsum, T, s.x_mid, x_out, 0));
+    }
+    const float* x_final = w->x_last;
+    if (!w->saved_layers) x_final = (c.n_layer % 2 == 1) ? w->x_last : w->L[0].x_in;
+    NNB_TRY(launch_gather_decisions(e, x_final, n_seq, S, P, G, d, w->xd));
+    gather_actions_kernel<<<(unsigned)ceil_div(Td, 256), 256, 0, e->stream>>>(tokens, (int)S, (int)P, (int)G, Td, w->actions);
+    e->launches++;
+    NNB_TRY(launch_row_quant(e, 0, exact, w->xd, PP + p->lnf_g, Td, d, d, w->qh, w->sh, w->qsum, w->hn));
+    NNB_TRY(lin_fwd(p, p->head, 1, w->qh, w->sh, w->qsum, Td, nullptr, w->logits, 0));
+    NNB_TRY(launch_categorical_fwd(e, w->logits, w->actions, Td, V, w->logp, want_entropy ? w->ent : nullptr));
+    if (c.value_head) NNB_TRY(launch_value_fwd(e, w->hn, PP + p->value_w, PP + p->value_b, Td, d, w->value));
+    return NNB_OK;
+}
+
+static nnb_status lin_bwd(nnb_policy* p, const LinW& l, const float* dy, const int8_t* q, const float* s, size_t T,
+                          float* dx, bool accumulate_dx)
+{
+    nnb_engine* e = p->e;
+    const bool exact = p->cfg.exact != 0;
+    if (dx) NNB_TRY(launch_bitlinear_dx(e, exact, dy, p->packed + l.packed_off, p->tau + l.tau_off, T, l.in, l.out, dx, accumulate_dx));
+    NNB_TRY(launch_bitlinear_dw(e, exact, dy, q, s, p->tau + l.tau_off, T, l.in, l.out, p->grads + l.w_off));
+    return launch_colsum_add(e, dy, T, l.out, p->grads + l.b_off);
+}
+
+static nnb_status backward(nnb_policy* p, const int32_t* tokens, size_t n_seq, size_t S, size_t P)
+{
+    nnb_engine* e = p->e;
+    const nnb_gpt_config& c = p->cfg;
+    TrainWs* w = (TrainWs*)p->train;
+    const size_t d = c.d_model, F = c.d_ff, V = c.vocab, H = c.n_head, dk = d / H;
+    const size_t T = n_seq * S, G = S - P, Td = n_seq * G;
+    const float* PP = p->params;
+    float* GG = p->grads;
+    // head: logits buffer now holds dlogits
+    NNB_TRY(lin_bwd(p, p->head, w->logits, w->qh, w->sh, Td, w->dhn, false));
+    if (c.value_head)
+        NNB_TRY(launch_value_bwd(e, w->hn, PP + p->value_w, w->dvalue, Td, d, w->dhn, GG + p->value_w, GG + p->value_b));
+    NNB_TRY(launch_rmsnorm_bwd(e, w->xd, PP + p->lnf_g, w->dhn, nullptr, Td, d, w->xd, GG + p->lnf_g));
+    NNB_TRY(launch_scatter_decisions(e, w->xd, n_seq, S, P, G, d, w->g));
+    for (int l = c.n_layer - 1; l >= 0; --l) {
+        const LayerW& LW = p->layers[l];
+        LayerSave& s = w->L[l];
+        // feed-forward branch
+        NNB_TRY(lin_bwd(p, LW.fc2, w->g, s.q4, s.s4, T, w->da, false));
+        NNB_TRY(launch_act_bwd(e, c.act == 1 ? 2 : 1, s.h1, w->da, T, F, w->dh1));
+        NNB_TRY(lin_bwd(p, LW.fc1, w->dh1, s.q3, s.s3, T, w->dn, false));
+        NNB_TRY(launch_rmsnorm_bwd(e, s.x_mid, PP + LW.ln2_g, w->dn, w->g, T, d, w->g2, GG + LW.ln2_g));
+        // attention branch
+        NNB_TRY(lin_bwd(p, LW.o, w->g2, s.q2, s.s2, T, w->datt, false));
+        NNB_TRY(launch_attn_bwd(e, s.qkv, s.qkv + T * d, s.qkv + 2 * T * d, s.att, w->datt, s.lse, w->delta, n_seq, S, H,
+                                dk, w->dqkv, w->dqkv + T * d, w->dqkv + 2 * T * d));
+        if (c.pos == 1) {
+            NNB_TRY(launch_rope(e, w->dqkv, p->rope_cos, p->rope_sin, T, S, H, dk, true));
+            NNB_TRY(launch_rope(e, w->dqkv + T * d, p->rope_cos, p->rope_sin, T, S, H, dk, true));
+        }
+        NNB_TRY(lin_bwd(p, LW.q, w->dqkv, s.q1, s.s1, T, w->dn, false));
+        NNB_TRY(lin_bwd(p, LW.k, w->dqkv + T * d, s.q1, s.s1, T, w->dn, true));
+        NNB_TRY(lin_bwd(p, LW.v, w->dqkv + 2 * T * d, s.q1, s.s1, T, w->dn, true));
+        NNB_TRY(launch_rmsnorm_bwd(e, s.x_in, PP + LW.ln1_g, w->dn, w->g2, T, d, w->g, GG + LW.ln1_g));
+    }
+    return launch_embed_bwd(e, w->g, tokens, T, S, d, V, GG + p->tok_emb, c.pos == 0 ? GG + p->pos_emb : nullptr);
+}
+
+static nnb_status check_shape(nnb_policy* p, const int32_t* tokens, size_t n_seq, size_t S, size_t P)
+{
+    NNB_REQUIRE(p && tokens, "policy or tokens is NULL");
+    NNB_REQUIRE(n_seq > 0 && S >= 2 && P >= 1 && P < S, "bad sequence shape (n_seq=%zu, seq_len=%zu, prompt_len=%zu)", n_seq, S, P);
+    NNB_REQUIRE(S <= (size_t)p->cfg.ctx, "sequence length %zu exceeds the context %d", S, p->cfg.ctx);
+    return NNB_OK;
+}
+
+}  // namespace nnb
+
+using namespace nnb;
+
+extern "C" {
+
+nnb_status nnb_policy_logprobs(nnb_policy* p, const int32_t* d_tokens, size_t n_seq, size_t seq_len, size_t prompt_len,
+                               float* d_logp, float* d_entropy, float* d_value)
+{
+    NNB_TRY(check_shape(p, d_tokens, n_seq, seq_len, prompt_len));
+    NNB_REQUIRE(d_value == nullptr || p->cfg.value_head, "policy has no value head");
+    NNB_TRY(ensure_train(p, n_seq, seq_len, prompt_len, false));
+    NNB_TRY(forward(p, d_tokens, n_seq, seq_len, prompt_len, d_entropy != nullptr));
+    TrainWs* w = (TrainWs*)p->train;
+    const size_t Td = n_seq * (seq_len - prompt_len);
+    cudaStream_t st = p->e->stream;
+    if (d_logp) NNB_CUDA(cudaMemcpyAsync(d_logp, w->logp, Td * 4, cudaMemcpyDeviceToDevice, st));
+    if (d_entropy) NNB_CUDA(cudaMemcpyAsync(d_entropy, w->ent, Td * 4, cudaMemcpyDeviceToDevice, st));
+    if (d_value) NNB_CUDA(cudaMemcpyAsync(d_value, w->value, Td * 4, cudaMemcpyDeviceToDevice, st));
+    return NNB_OK;
+}
+
+float* nnb_policy_grads(nnb_policy* p)
+{
+    if (!p) return nullptr;
+    if (!p->grads) {
+        if (cudaMalloc((void**)&p->grads, p->n_params * 4) != cudaSuccess) {
+            cudaGetLastError();
+            return nullptr;
+        }
+        cudaMemsetAsync(p->grads, 0, p->n_params * 4, p->e->stream);
+    }
+    return p->grads;
+}
+
+nnb_status nnb_policy_zero_grad(nnb_policy* p)
+{
+    NNB_REQUIRE(p, "policy is NULL");
+    NNB_REQUIRE(nnb_policy_grads(p), "out of device memory for the gradient buffer");
+    NNB_CUDA(cudaMemsetAsync(p->grads, 0, p->n_params * 4, p->e->stream));
+    return NNB_OK;
+}
+
+nnb_status nnb_policy_train_step(nnb_policy* p, const int32_t* d_tokens, size_t n_seq, size_t seq_len,
+                                 size_t prompt_len, const nnb_objective* obj, float* d_report)
+{
+    NNB_TRY(check_shape(p, d_tokens, n_seq, seq_len, prompt_len));
+    NNB_REQUIRE(obj && obj->d_mask, "train_step: objective or mask is NULL");
+    NNB_REQUIRE(nnb_policy_grads(p), "out of device memory for the gradient buffer");
+    const bool use_value = obj->value_coef != 0.0f;
+    NNB_REQUIRE(!use_value || (p->cfg.value_head && obj->d_returns && obj->d_old_value),
+                "train_step: the value term needs a value head, returns and old values");
+    NNB_TRY(ensure_train(p, n_seq, seq_len, prompt_len, true));
+    nnb_engine* e = p->e;
+    TrainWs* w = (TrainWs*)p->train;
+    const size_t Td = n_seq * (seq_len - prompt_len), V = p->cfg.vocab;
+    const bool use_ent = obj->entropy_coef != 0.0f;
+    NNB_TRY(forward(p, d_tokens, n_seq, seq_len, prompt_len, true));
+    NNB_TRY(launch_token_objective(e, w->logp, w->ent, obj->d_old_logp, obj->d_ref_logp, obj->d_advantage, obj->d_mask,
+                                   Td, obj->units, obj->clip_eps, obj->kl_coef, obj->entropy_coef, w->up_lp, w->up_ent,
+                                   w->report));
+    if (use_value) {
+        NNB_TRY(launch_clipped_value(e, w->value, obj->d_returns, obj->d_old_value, obj->d_mask, Td, obj->units,
+                                     obj->value_clip_eps, obj->value_coef, w->dvalue, w->vreport));
+    } else if (p->cfg.value_head) {
+        NNB_CUDA(cudaMemsetAsync(w->dvalue, 0, Td * 4, e->stream));
+        NNB_CUDA(cudaMemsetAsync(w->vreport, 0, 8, e->stream));
+    }
+    NNB_TRY(launch_categorical_bwd(e, w->logits, w->actions, w->up_lp, use_ent ? w->up_ent : nullptr, Td, V, w->logits));
+    NNB_TRY(backward(p, d_tokens, n_seq, seq_len, prompt_len));
+    if (d_report) {
+        NNB_CUDA(cudaMemcpyAsync(d_report, w->report, 8 * 4, cudaMemcpyDeviceToDevice, e->stream));
+        if (p->cfg.value_head)
+            NNB_CUDA(cudaMemcpyAsync(d_report + 8, w->vreport, 2 * 4, cudaMemcpyDeviceToDevice, e->stream));
+        else
+            NNB_CUDA(cudaMemsetAsync(d_report + 8, 0, 8, e->stream));
+    }
+    return NNB_OK;
+}
+
+nnb_status nnb_policy_optimizer_step(nnb_policy* p, float lr, float beta1, float beta2, float eps, float weight_decay,
+                                     float max_grad_norm, float* d_norm_out)
+{
+    NNB_REQUIRE(p && p->grads, "optimizer_step: no gradients have been computed");
+    nnb_engine* e = p->e;
+    if (!p->adam_m) {
+        if (cudaMalloc((void**)&p->adam_m, p->n_params * 4) != cudaSuccess ||
+            cudaMalloc((void**)&p->adam_v, p->n_params * 4) != cudaSuccess) {
+            cudaGetLastError();
+            NNB_FAIL(NNB_ERR_OOM, "out of device memory for the AdamW moments");
+        }
+        NNB_CUDA(cudaMemsetAsync(p->adam_m, 0, p->n_params * 4, e->stream));
+        NNB_CUDA(cudaMemsetAsync(p->adam_v, 0, p->n_params * 4, e->stream));
+    }
+    if (max_grad_norm > 0.0f || d_norm_out) NNB_TRY(launch_clip_grad_norm(e, p->grads, p->n_params, max_grad_norm, d_norm_out));
+    p->adam_t += 1;
+    NNB_TRY(launch_adamw(e, p->params, p->grads, p->adam_m, p->adam_v, p->n_params, lr, beta1, beta2, eps, weight_decay,
+                         p->adam_t));
+    NNB_CUDA(cudaMemsetAsync(p->grads, 0, p->n_params * 4, e->stream));
+    return policy_requantize(p);
+}
+
+nnb_status nnb_policy_release_workspaces(nnb_policy* p)
+{
+    NNB_REQUIRE(p, "policy is NULL");
+    NNB_CUDA(cudaStreamSynchronize(p->e->stream));
+    policy_free_train(p);
+    policy_free_decode(p);
+    return NNB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,610 @@
+// train.cu — kernels of the teacher-forced forward and the backward pass of the ternary GPT
+// policy (token-major, T = sequences x positions):
+//   embedding gather / scatter-add          compute_layer_gpt.hpp:475-489, 620-636
+//   RoPE over whole sequences and its inverse   compute_position_encoding.hpp:126-145
+//   causal attention, online softmax forward    compute_layer_attention.hpp:698-828
+//   attention backward (recompute P from lse)   compute_layer_attention.hpp:830-988
+//   RMSNorm backward                            compute_layer_mlp.hpp:716-746
+//   QuickGELU / SwiGLU backward                 compute_layer_mlp.hpp:254-270, 332-369
+// (paths are under include/neuralnet.cpp/ of the reference).
+#include "common.cuh"
+#include "device_math.cuh"
+
+namespace nnb {
+
+// ------------------------------------------------------------- embedding
+__global__ void embed_fwd_kernel(const float* __restrict__ tok_emb, const float* __restrict__ pos_emb,
+                                 const int32_t* __restrict__ tokens, int S, int d, int vocab, float* __restrict__ x)
+{
+    const size_t row = blockIdx.x;  // b*S + t
+    const int t = (int)(row % S);
+    int tok = tokens[row];
+    tok = min(max(tok, 0), vocab - 1);
+    const float* e = tok_emb + (size_t)tok * d;
+    const float* p = pos_emb ? pos_emb + (size_t)t * d : nullptr;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        float v = e[i];
+        if (p) v = __fadd_rn(v, p[i]);
+        x[row * d + i] = v;
+    }
+}
+
+__global__ void embed_bwd_kernel(const float* __restrict__ g, const int32_t* __restrict__ tokens, int S, int d,
+                                 int vocab, float* __restrict__ g_tok, float* __restrict__ g_pos)
+{
+    const size_t row = blockIdx.x;
+    const int t = (int)(row % S);
+    int tok = tokens[row];
+    tok = min(max(tok, 0), vocab - 1);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float v = g[row * d + i];
+        atomicAdd(g_tok + (size_t)tok * d + i, v);
+        if (g_pos) atomicAdd(g_pos + (size_t)t * d + i, v);
+    }
+}
+
+// ------------------------------------------------------------------ RoPE
+// In place on x (rows, d) viewed as heads of dk; position of a row = row % S.
+// sign = +1 forward, -1 backward (the rotation is orthogonal: inverse = opposite angle).
+__global__ void rope_kernel(float* __restrict__ x, const float* __restrict__ rope_cos,
+                            const float* __restrict__ rope_sin, int S, int H, int dk, float sign)
+{
+    const size_t row = blockIdx.x;
+    const int pos = (int)(row % S);
+    const int half = dk / 2;
+    float* xr = x + row * (size_t)(H * dk);
+    for (int i = threadIdx.x; i < H * half; i += blockDim.x) {
+        const int h = i / half, j = i % half;
+        const float c = rope_cos[(size_t)pos * half + j], sn = __fmul_rn(sign, rope_sin[(size_t)pos * half + j]);
+        float* v = xr + (size_t)h * dk;
+        const float a = v[j], b = v[j + half];
+        v[j] = __fadd_rn(__fmul_rn(a, c), __fmul_rn(-b, sn));
+        v[j + half] = __fadd_rn(__fmul_rn(b, c), __fmul_rn(a, sn));
+    }
+}
+
+// ---------------------------------------------------- causal attention, forward
+// q, k, v: (n*S, d) token-major (the three slabs of the qkv buffer), post-RoPE.
+// One warp per query.  Keys are processed in tiles of 32 held in shared memory: lane j scores
+// key j, then the lanes switch to owning output features for the P.V update (online softmax).
+constexpr int ATT_WARPS = 8;
+__global__ void __launch_bounds__(ATT_WARPS * 32)
+attn_fwd_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, int S,
+                int H, int dk, float scale, float* __restrict__ out, float* __restrict__ lse)
+{
+    extern __shared__ float sm[];
+    const int dkp = dk + 1;
+    float* Ks = sm;                       // 32 x dkp
+    float* Vs = Ks + 32 * dkp;            // 32 x dkp
+    float* Qs = Vs + 32 * dkp;            // ATT_WARPS x dk (scaled)
+    const int bh = blockIdx.x, b = bh / H, h = bh % H;
+    const int d = H * dk;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int q0 = blockIdx.y * ATT_WARPS;
+    const int qi = q0 + warp;             // query position of this warp
+    const bool qvalid = qi < S;
+    const size_t base = (size_t)b * S;
+    float* qs = Qs + warp * dk;
+    if (qvalid)
+        for (int i = lane; i < dk; i += 32) qs[i] = __fmul_rn(q[(base + qi) * d + (size_t)h * dk + i], scale);
+    float o[4] = {0.f, 0.f, 0.f, 0.f};
+    float m = -INFINITY, l = 0.0f;
+    const int last_q = min(S - 1, q0 + ATT_WARPS - 1);
+    for (int j0 = 0; j0 <= last_q; j0 += 32) {
+        __syncthreads();
+        for (int i = threadIdx.x; i < 32 * dk; i += ATT_WARPS * 32) {
+            const int r = i / dk, c = i % dk;
+            const int j = j0 + r;
+            float kv = 0.0f, vv = 0.0f;
+            if (j < S) {
+                kv = k[(base + j) * d + (size_t)h * dk + c];
+                vv = v[(base + j) * d + (size_t)h * dk + c];
+            }
+            Ks[r * dkp + c] = kv;
+            Vs[r * dkp + c] = vv;
+        }
+        __syncthreads();
+        if (!qvalid || j0 > qi) continue;
+        const int j = j0 + lane;
+        float sc = -INFINITY;
+        if (j <= qi) {
+            float a = 0.0f;
+            const float* kr = Ks + lane * dkp;
+            for (int c = 0; c < dk; ++c) a = fmaf(qs[c], kr[c], a);
+            sc = a;
+        }
+        const float tmax = warp_max(sc);
+        const float m_new = fmaxf(m, tmax);
+        const float p = (j <= qi) ? __expf(sc - m_new) : 0.0f;
+        const float corr = __expf(m - m_new);
+        l = l * corr + warp_sum(p);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[i] *= corr;
+        for (int jj = 0; jj < 32; ++jj) {
+            const float pj = __shfl_sync(0xffffffffu, p, jj);
+            if (pj != 0.0f) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int c = lane + 32 * i;
+                    if (c < dk) o[i] = fmaf(pj, Vs[jj * dkp + c], o[i]);
+                }
+            }
+        }
+        m = m_new;
+    }
+    if (qvalid) {
+        const float inv = 1.0f / l;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int c = lane + 32 * i;
+            if (c < dk) out[(base + qi) * d + (size_t)h * dk + c] = o[i] * inv;
+        }
+        if (lane == 0) lse[((size_t)b * H + h) * S + qi] = m + logf(l);
+    }
+}
+
+// D[b,h,i] = sum_c dO[i,c] * O[i,c]
+__global__ void attn_bwd_delta_kernel(const float* __restrict__ dout, const float* __restrict__ out, int S, int H,
+                                      int dk, size_t n_rows, float* __restrict__ delta)
+{
+    const size_t w = (size_t)blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;  // (row, h)
+    if (w >= n_rows * H) return;
+    const size_t row = w / H;
+    const int h = (int)(w % H), lane = threadIdx.x & 31;
+    const int d = H * dk;
+    float a = 0.0f;
+    for (int c = lane; c < dk; c += 32) a = fmaf(dout[row * d + (size_t)h * dk + c], out[row * d + (size_t)h * dk + c], a);
+    a = warp_sum(a);
+    const size_t b = row / S, i = row % S;
+    if (lane == 0) delta[(b * H + h) * S + i] = a;
+}
+
+// dQ: one warp per query, key tiles in shared memory.  dq = scale * sum_j ds_ij k_j,
+// ds_ij = p_ij (dO_i . v_j - D_i), p_ij = exp(s_ij - lse_i)
+__global__ void __launch_bounds__(ATT_WARPS * 32)
+attn_bwd_dq_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
+                   const float* __restrict__ dout, const float* __restrict__ lse, const float* __restrict__ delta,
+                   int S, int H, int dk, float scale, float* __restrict__ dq)
+{
+    extern __shared__ float sm[];
+    const int dkp = dk + 1;
+    float* Ks = sm;
+    float* Vs = Ks + 32 * dkp;
+    float* Qs = Vs + 32 * dkp;              // ATT_WARPS x dk scaled q
+    float* Gs = Qs + ATT_WARPS * dk;        // ATT_WARPS x dk dO
+    const int bh = blockIdx.x, b = bh / H, h = bh % H;
+    const int d = H * dk;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int q0 = blockIdx.y * ATT_WARPS;
+    const int qi = q0 + warp;
+    const bool qvalid = qi < S;
+    const size_t base = (size_t)b * S;
+    float* qs = Qs + warp * dk;
+    float* gs = Gs + warp * dk;
+    float li = 0.0f, di = 0.0f;
+    if (qvalid) {
+        for (int i = lane; i < dk; i += 32) {
+            qs[i] = __fmul_rn(q[(base + qi) * d + (size_t)h * dk + i], scale);
+            gs[i] = dout[(base + qi) * d + (size_t)h * dk + i];
+        }
+        li = lse[((size_t)b * H + h) * S + qi];
+        di = delta[((size_t)b * H + h) * S + qi];
+    }
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    const int last_q = min(S - 1, q0 + ATT_WARPS - 1);
+    for (int j0 = 0; j0 <= last_q; j0 += 32) {
+        __syncthreads();
+        for (int i = threadIdx.x; i < 32 * dk; i += ATT_WARPS * 32) {
+            const int r = i / dk, c = i % dk;
+            const int j = j0 + r;
+            float kv = 0.0f, vv = 0.0f;
+            if (j < S) {
+                kv = k[(base + j) * d + (size_t)h * dk + c];
+                vv = v[(base + j) * d + (size_t)h * dk + c];
+            }
+            Ks[r * dkp + c] = kv;
+            Vs[r * dkp + c] = vv;
+        }
+        __syncthreads();
+        if (!qvalid || j0 > qi) continue;
+        const int j = j0 + lane;
+        float ds = 0.0f;
+        if (j <= qi) {
+            float sc = 0.0f, dp = 0.0f;
+            const float* kr = Ks + lane * dkp;
+            const float* vr = Vs + lane * dkp;
+            for (int c = 0; c < dk; ++c) {
+                sc = fmaf(qs[c], kr[c], sc);
+                dp = fmaf(gs[c], vr[c], dp);
+            }
+            const float p = __expf(sc - li);
+            ds = p * (dp - di);
+        }
+        for (int jj = 0; jj < 32; ++jj) {
+            const float dsj = __shfl_sync(0xffffffffu, ds, jj);
+            if (dsj != 0.0f) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int c = lane + 32 * i;
+                    if (c < dk) acc[i] = fmaf(dsj, Ks[jj * dkp + c], acc[i]);
+                }
+            }
+        }
+    }
+    if (qvalid) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int c = lane + 32 * i;
+            if (c < dk) dq[(base + qi) * d + (size_t)h * dk + c] = acc[i] * scale;
+        }
+    }
+}
+
+// dK, dV: one warp per key, query tiles (scaled q, dO, lse, D) in shared memory.
+// dv_j = sum_i p_ij dO_i ; dk_j = sum_i ds_ij (scale q_i)
+__global__ void __launch_bounds__(ATT_WARPS * 32)
+attn_bwd_dkv_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
+                    const float* __restrict__ dout, const float* __restrict__ lse, const float* __restrict__ delta,
+                    int S, int H, int dk, float scale, float* __restrict__ dkk, float* __restrict__ dvv)
+{
+    extern __shared__ float sm[];
+    const int dkp = dk + 1;
+    float* Qs = sm;                         // 32 x dkp scaled q
+    float* Gs = Qs + 32 * dkp;              // 32 x dkp dO
+    float* Ks = Gs + 32 * dkp;              // ATT_WARPS x dk
+    float* Vs = Ks + ATT_WARPS * dk;        // ATT_WARPS x dk
+    float* Ls = Vs + ATT_WARPS * dk;        // 32 lse
+    float* Ds = Ls + 32;                    // 32 delta
+    const int bh = blockIdx.x, b = bh / H, h = bh % H;
+    const int d = H * dk;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int k0 = blockIdx.y * ATT_WARPS;
+    const int kj = k0 + warp;
+    const bool kvalid = kj < S;
+    const size_t base = (size_t)b * S;
+    float* ks = Ks + warp * dk;
+    float* vs = Vs + warp * dk;
+    if (kvalid)
+        for (int i = lane; i < dk; i += 32) {
+            ks[i] = k[(base + kj) * d + (size_t)h * dk + i];
+            vs[i] = v[(base + kj) * d + (size_t)h * dk + i];
+        }
+    float ak[4] = {0.f, 0.f, 0.f, 0.f}, av[4] = {0.f, 0.f, 0.f, 0.f};
+    const int first_tile = (k0 / 32) * 32;
+    for (int i0 = first_tile; i0 < S; i0 += 32) {
+        __syncthreads();
+        for (int i = threadIdx.x; i < 32 * dk; i += ATT_WARPS * 32) {
+            const int r = i / dk, c = i % dk;
+            const int qi = i0 + r;
+            float qv = 0.0f, gv = 0.0f;
+            if (qi < S) {
+                qv = __fmul_rn(q[(base + qi) * d + (size_t)h * dk + c], scale);
+                gv = dout[(base + qi) * d + (size_t)h * dk + c];
+            }
+            Qs[r * dkp + c] = qv;
+            Gs[r * dkp + c] = gv;
+        }
+        if (threadIdx.x < 32) {
+            const int qi = i0 + threadIdx.x;
+            Ls[threadIdx.x] = qi < S ? lse[((size_t)b * H + h) * S + qi] : 0.0f;
+            Ds[threadIdx.x] = qi < S ? delta[((size_t)b * H + h) * S + qi] : 0.0f;
+        }
+        __syncthreads();
+        if (!kvalid || i0 + 31 < kj) continue;
+        const int qi = i0 + lane;
+        float p = 0.0f, ds = 0.0f;
+        if (qi < S && qi >= kj) {
+            float sc = 0.0f, dp = 0.0f;
+            const float* qr = Qs + lane * dkp;
+            const float* gr = Gs + lane * dkp;
+            for (int c = 0; c < dk; ++c) {
+                sc = fmaf(qr[c], ks[c], sc);
+                dp = fmaf(gr[c], vs[c], dp);
+            }
+            p = __expf(sc - Ls[lane]);
+            ds = p * (dp - Ds[lane]);
+        }
+        for (int ii = 0; ii < 32; ++ii) {
+            const float pi = __shfl_sync(0xffffffffu, p, ii);
+            const float dsi = __shfl_sync(0xffffffffu, ds, ii);
+            if (pi != 0.0f || dsi != 0.0f) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int c = lane + 32 * i;
+                    if (c < dk) {
+                        av[i] = fmaf(pi, Gs[ii * dkp + c], av[i]);
+                        ak[i] = fmaf(dsi, Qs[ii * dkp + c], ak[i]);
+                    }
+                }
+            }
+        }
+    }
+    if (kvalid) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int c = lane + 32 * i;
+            if (c < dk) {
+                dkk[(base + kj) * d + (size_t)h * dk + c] = ak[i];
+                dvv[(base + kj) * d + (size_t)h * dk + c] = av[i];
+            }
+        }
+    }
+}
+
+// ----------------------------------------------------------- RMSNorm backward
+// gy = dy*gamma; normed = x*sinv; m = sum(gy*normed)/F; dx = (gy - m*normed)*sinv (+ residual)
+// dgamma[f] += sum_t dy[t,f]*normed[t,f].  One warp per token, TOK tokens per CTA; gamma
+// gradients are reduced in shared memory and flushed with one atomic per feature per CTA.
+constexpr int RN_TOK = 16;
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_kernel(const float* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ dy,
+                   const float* __restrict__ residual, size_t T, int F, float* __restrict__ dx,
+                   float* __restrict__ dgamma)
+{
+    extern __shared__ float dg[];  // F
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int i = threadIdx.x; i < F; i += 256) dg[i] = 0.0f;
+    __syncthreads();
+    const float inv_f = __frcp_rn((float)F);
+    for (int tt = warp; tt < RN_TOK; tt += 8) {
+        const size_t t = (size_t)blockIdx.x * RN_TOK + tt;
+        if (t >= T) break;
+        const float* xr = x + t * F;
+        const float* gr = dy + t * F;
+        float ss = 0.0f;
+        for (int i = lane; i < F; i += 32) ss = fmaf(xr[i], xr[i], ss);
+        ss = warp_sum(ss);
+        const float sinv = __frcp_rn(__fsqrt_rn(__fadd_rn(__fmul_rn(ss, inv_f), 1e-5f)));
+        float dot = 0.0f;
+        for (int i = lane; i < F; i += 32) dot = fmaf(gr[i] * gamma[i], xr[i] * sinv, dot);
+        dot = warp_sum(dot) * inv_f;
+        for (int i = lane; i < F; i += 32) {
+            const float normed = xr[i] * sinv;
+            const float gy = gr[i] * gamma[i];
+            float v = (gy - dot * normed) * sinv;
+            if (residual) v += residual[t * F + i];
+            dx[t * F + i] = v;
+            atomicAdd(dg + i, gr[i] * normed);
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < F; i += 256)
+        if (dg[i] != 0.0f) atomicAdd(dgamma + i, dg[i]);
+}
+
+// ------------------------------------------------------- activation backward
+// MODE 1 QuickGELU: dh = da * s*(1 + bx*(1-s)), s = sigmoid(bx), bx = 1.702 h
+// MODE 2 SwiGLU: h = (gate|up): dgate = da*up*s*(1+gate*(1-s)), dup = da*gate*s
+template <int MODE>
+__global__ void act_bwd_kernel(const float* __restrict__ h, const float* __restrict__ da, size_t T, int F,
+                               float* __restrict__ dh)
+{
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= T * F) return;
+    const size_t t = idx / F;
+    const int f = (int)(idx % F);
+    if (MODE == 1) {
+        const float xv = h[idx];
+        const float bx = xv * 1.702f;
+        const float sg = 1.0f / (1.0f + nnb_expf(-bx));
+        dh[idx] = da[idx] * (sg * (1.0f + bx * (1.0f - sg)));
+    } else {
+        const float gv = h[t * 2 * F + f], uv = h[t * 2 * F + F + f];
+        const float sg = 1.0f / (1.0f + nnb_expf(-gv));
+        const float go = da[idx];
+        dh[t * 2 * F + f] = go * uv * (sg * (1.0f + gv * (1.0f - sg)));
+        dh[t * 2 * F + F + f] = go * gv * sg;
+    }
+}
+
+// --------------------------------------------------- row gather / scatter / add
+// dst[i,:] = src[index(i),:] where decision i = (b, g) maps to row b*S + P-1+g
+__global__ void gather_decisions_kernel(const float* __restrict__ src, int S, int P, int G, int d,
+                                        float* __restrict__ dst)
+{
+    const size_t i = blockIdx.x;
+    const size_t b = i / G, g = i % G;
+    const size_t row = b * S + P - 1 + g;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) dst[i * d + c] = src[row * d + c];
+}
+
+// dst (n*S, d) = 0 everywhere except decision rows, which get src
+__global__ void scatter_decisions_kernel(const float* __restrict__ src, int S, int P, int G, int d,
+                                         float* __restrict__ dst)
+{
+    const size_t row = blockIdx.x;
+    const size_t b = row / S;
+    const int t = (int)(row % S);
+    const int g = t - (P - 1);
+    const bool hit = g >= 0 && g < G;
+    for (int c = threadIdx.x; c < d; c += blockDim.x)
+        dst[row * d + c] = hit ? src[(b * G + g) * d + c] : 0.0f;
+}
+
+// value head: value[i] = w . x[i,:] + b   (Linear(d -> 1) on the final-norm output)
+__global__ void value_fwd_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b,
+                                 size_t n, int d, float* __restrict__ value)
+{
+    const size_t i = (size_t)blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
+    if (i >= n) return;
+    const int lane = threadIdx.x & 31;
+    float a = 0.0f;
+    for (int c = lane; c < d; c += 32) a = fmaf(x[i * d + c], w[c], a);
+    a = warp_sum(a);
+    if (lane == 0) value[i] = a + b[0];
+}
+
+// dx[i,:] += dv[i]*w ; dw += sum_i dv[i]*x[i,:] ; db += sum_i dv[i]
+__global__ void value_bwd_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ dv,
+                                 size_t n, int d, float* __restrict__ dx, float* __restrict__ dw, float* __restrict__ db)
+{
+    // one CTA per feature chunk of 256; loops over decisions
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    float aw = 0.0f, ab = 0.0f;
+    const float wc = c < d ? w[c] : 0.0f;
+    for (size_t i = 0; i < n; ++i) {
+        const float g = dv[i];
+        if (c < d) {
+            dx[i * d + c] += g * wc;
+            aw = fmaf(g, x[i * d + c], aw);
+        }
+        if (c == 0) ab += g;
+    }
+    if (c < d) atomicAdd(dw + c, aw);
+    if (c == 0) atomicAdd(db, ab);
+}
+
+__global__ void add_kernel(float* __restrict__ dst, const float* __restrict__ src, size_t n)
+{
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) dst[i] += src[i];
+}
+
+// ------------------------------------------------------------------ launchers
+nnb_status launch_embed_fwd(nnb_engine* e, const float* tok_emb, const float* pos_emb, const int32_t* tokens,
+                            size_t n_rows, size_t S, size_t d, size_t vocab, float* x)
+{
+    embed_fwd_kernel<<<(unsigned)n_rows, 128, 0, e->stream>>>(tok_emb, pos_emb, tokens, (int)S, (int)d, (int)vocab, x);
+    e->launches++;
+    NNB_CHECK_LAUNCH("embed_fwd_kernel");
+    return NNB_OK;
+}
+
+nnb_status launch_embed_bwd(nnb_engine* e, const float* g, const int32_t* tokens, size_t n_rows, size_t S, size_t d,
+                            size_t vocab, float* g_tok, float* g_pos)
+{
+    embed_bwd_kernel<<<(unsigned)n_rows, 128, 0, e->stream>>>(g, tokens, (int)S, (int)d, (int)vocab, g_tok, g_pos);
+    e->launches++;
+    NNB_CHECK_LAUNCH("embed_bwd_kernel");
+    return NNB_OK;
+}
+
+nnb_status launch_rope(nnb_engine* e, float* x, const float* rope_cos, const float* rope_sin, size_t n_rows,
+                       size_t S, size_t H, size_t dk, bool backward)
+{
+    rope_kernel<<<(unsigned)n_rows, 128, 0, e->stream>>>(x, rope_cos, rope_sin, (int)S, (int)H, (int)dk,
+                                                         backward ? -1.0f : 1.0f);
+    e->launches++;
+    NNB_CHECK_LAUNCH("rope_kernel");
+    return NNB_OK;
+}
+
+nnb_status launch_attn_fwd(nnb_engine* e, const float* q, const float* k, const float* v, size_t n_seq, size_t S,
+                           size_t H, size_t dk, float* out, float* lse)
+{
+    NNB_REQUIRE(dk <= 128, "attention: head dim %zu > 128", dk);
+    const size_t smem = (2 * 32 * (dk + 1) + ATT_WARPS * dk) * sizeof(float);
+    static size_t cfg = 0;
+    if (smem > cfg) {
+        NNB_CUDA(cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        cfg = smem;
+    }
+    dim3 grid((unsigned)(n_seq * H), (unsigned)ceil_div(S, ATT_WARPS));
+    attn_fwd_kernel<<<grid, ATT_WARPS * 32, smem, e->stream>>>(q, k, v, (int)S, (int)H, (int)dk,
+                                                              1.0f / sqrtf((float)dk), out, lse);
+    e->launches++;
+    NNB_CHECK_LAUNCH("attn_fwd_kernel");
+    return NNB_OK;
+}
+
+nnb_status launch_attn_bwd(nnb_engine* e, const float* q, const float* k, const float* v, const float* out,
+                           const float* dout, const float* lse, float* delta, size_t n_seq, size_t S, size_t H,
+                           size_t dk, float* dq, float* dkk, float* dvv)
+{
+    NNB_REQUIRE(dk <= 128, "attention: head dim %zu > 128", dk);
+    const float scale = 1.0f / sqrtf((float)dk);
+    const size_t rows = n_seq * S;
+    attn_bwd_delta_kernel<<<(unsigned)ceil_div(rows * H, 8), 256, 0, e->stream>>>(dout, out, (int)S, (int)H, (int)dk,
+                                                                                 rows, delta);
+    const size_t smem_q = (2 * 32 * (dk + 1) + 2 * ATT_WARPS * dk) * sizeof(float);
+    const size_t smem_kv = (2 * 32 * (dk + 1) + 2 * ATT_WARPS * dk + 64) * sizeof(float);
+    static size_t cfg_q = 0, cfg_kv = 0;
+    if (smem_q > cfg_q) {
+        NNB_CUDA(cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_q));
+        cfg_q = smem_q;
+    }
+    if (smem_kv > cfg_kv) {
+        NNB_CUDA(cudaFuncSetAttribute(attn_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_kv));
+        cfg_kv = smem_kv;
+    }
+    dim3 grid((unsigned)(n_seq * H), (unsigned)ceil_div(S, ATT_WARPS));
+    attn_bwd_dq_kernel<<<grid, ATT_WARPS * 32, smem_q, e->stream>>>(q, k, v, dout, lse, delta, (int)S, (int)H, (int)dk,
+                                                                   scale, dq);
+    attn_bwd_dkv_kernel<<<grid, ATT_WARPS * 32, smem_kv, e->stream>>>(q, k, v, dout, lse, delta, (int)S, (int)H,
+                                                                     (int)dk, scale, dkk, dvv);
+    e->launches += 3;
+    NNB_CHECK_LAUNCH("attention backward kernels");
+    return NNB_OK;
+}
+
+nnb_status launch_rmsnorm_bwd(nnb_engine* e, const float* x, const float* gamma, const float* dy,
+                              const float* residual, size_t T, size_t F, float* dx, float* dgamma)
+{
+    const size_t smem = F * sizeof(float);
+    static size_t cfg = 0;
+    if (smem > cfg && smem > 48 * 1024) {
+        NNB_CUDA(cudaFuncSetAttribute(rmsnorm_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        cfg = smem;
+    }
+    rmsnorm_bwd_kernel<<<(unsigned)ceil_div(T, RN_TOK), 256, smem, e->stream>>>(x, gamma, dy, residual, T, (int)F, dx,
+                                                                               dgamma);
+    e->launches++;
+    NNB_CHECK_LAUNCH("rmsnorm_bwd_kernel");
+    return NNB_OK;
+}
+
+nnb_status launch_act_bwd(nnb_engine* e, int mode, const float* h, const float* da, size_t T, size_t F, float* dh)
+{
+    const unsigned grid = (unsigned)ceil_div(T * F, 256);
+    if (mode == 1) act_bwd_kernel<1><<<grid, 256, 0, e->stream>>>(h, da, T, (int)F, dh);
+    else act_bwd_kernel<2><<<grid, 256, 0, e->stream>>>(h, da, T, (int)F, dh);
+    e->launches++;
+    NNB_CHECK_LAUNCH("act_bwd_kernel");
+    return NNB_OK;
+}
+
+nnb_status launch_gather_decisions(nnb_engine* e, const float* src, size_t n_seq, size_t S, size_t P, size_t G,
+                                   size_t d, float* dst)
+{
+    gather_decisions_kernel<<<(unsigned)(n_seq * G), 128, 0, e->stream>>>(src, (int)S, (int)P, (int)G, (int)d, dst);
+    e->launches++;
+    NNB_CHECK_LAUNCH("gather_decisions_kernel");
+    return NNB_OK;
+}
+
+nnb_status launch_scatter_decisions(nnb_engine* e, const float* src, size_t n_seq, size_t S, size_t P, size_t G,
+                                    size_t d, float* dst)
+{
+    scatter_decisions_kernel<<<(unsigned)(n_seq * S), 128, 0, e->stream>>>(src, (int)S, (int)P, (int)G, (int)d, dst);
+    e->launches++;
+    NNB_CHECK_LAUNCH("scatter_decisions_kernel");
+    return NNB_OK;
+}
+
+nnb_status launch_value_fwd(nnb_engine* e, const float* x, const float* w, const float* b, size_t n, size_t d,
+                            float* value)
+{
+    value_fwd_kernel<<<(unsigned)ceil_div(n, 8), 256, 0, e->stream>>>(x, w, b, n, (int)d, value);
+    e->launches++;
+    NNB_CHECK_LAUNCH("value_fwd_kernel");
+    return NNB_OK;
+}
+
+nnb_status launch_value_bwd(nnb_engine* e, const float* x, const float* w, const float* dv, size_t n, size_t d,
+                            float* dx, float* dw, float* db)
+{
+    value_bwd_kernel<<<(unsigned)ceil_div(d, 256), 256, 0, e->stream>>>(x, w, dv, n, (int)d, dx, dw, db);
+    e->launches++;
+    NNB_CHECK_LAUNCH("value_bwd_kernel");
+    return NNB_OK;
+}
+
+nnb_status launch_add(nnb_engine* e, float* dst, const float* src, size_t n)
+{
+    add_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, e->stream>>>(dst, src, n);
+    e->launches++;
+    NNB_CHECK_LAUNCH("add_kernel");
+    return NNB_OK;
+}
+
+}  // namespace nnb

@@ -181,3 +181,63 @@ def _alias(ptr: int, numel: int, dtype, device) -> torch.Tensor:
     holder.__cuda_array_interface__ = {"shape": (numel,), "typestr": typestr, "data": (int(ptr), False),
                                        "version": 2, "strides": (itemsize,)}
     return torch.as_tensor(holder, device=device)
+
+
+class _CObjective(C.Structure):
+    _fields_ = [("d_mask", C.c_void_p), ("d_old_logp", C.c_void_p), ("d_advantage", C.c_void_p),
+                ("d_ref_logp", C.c_void_p), ("d_returns", C.c_void_p), ("d_old_value", C.c_void_p),
+                ("units", C.c_float), ("clip_eps", C.c_float), ("kl_coef", C.c_float), ("entropy_coef", C.c_float),
+                ("value_coef", C.c_float), ("value_clip_eps", C.c_float)]
+
+
+def _dp(t):
+    return None if t is None else t.data_ptr()
+
+
+def logprobs(self, tokens: torch.Tensor, prompt_len: int, want_entropy=False, want_value=False):
+    """Teacher-forced log-probs (and entropy / values) of the decisions of tokens (n, S) int32."""
+    n, S = tokens.shape
+    G = S - prompt_len
+    dev = self.engine.device
+    logp = torch.empty((n, G), device=dev, dtype=torch.float32)
+    ent = torch.empty((n, G), device=dev, dtype=torch.float32) if want_entropy else None
+    val = torch.empty((n, G), device=dev, dtype=torch.float32) if want_value else None
+    check(self._lib.nnb_policy_logprobs(self._h, _ptr(tokens), n, S, prompt_len, _ptr(logp), _ptr(ent), _ptr(val)))
+    return logp, ent, val
+
+
+def grads_view(self) -> torch.Tensor:
+    ptr = self._lib.nnb_policy_grads(self._h)
+    if not ptr:
+        raise NnbError("out of device memory for the gradient buffer")
+    return _alias(ptr, self.n_params, torch.float32, self.engine.device)
+
+
+def zero_grad(self):
+    check(self._lib.nnb_policy_zero_grad(self._h))
+
+
+def train_step(self, tokens: torch.Tensor, prompt_len: int, mask, old_logp=None, advantage=None, ref_logp=None,
+               returns=None, old_value=None, units=0.0, clip_eps=0.2, kl_coef=0.0, entropy_coef=0.0,
+               value_coef=0.0, value_clip_eps=0.2):
+    """One micro-batch: forward, objective, backward; gradients accumulate.  Returns report[10] (device)."""
+    n, S = tokens.shape
+    obj = _CObjective(_dp(mask), _dp(old_logp), _dp(advantage), _dp(ref_logp), _dp(returns), _dp(old_value),
+                      units, clip_eps, kl_coef, entropy_coef, value_coef, value_clip_eps)
+    report = torch.empty(10, device=self.engine.device, dtype=torch.float32)
+    check(self._lib.nnb_policy_train_step(self._h, _ptr(tokens), n, S, prompt_len, C.byref(obj), _ptr(report)))
+    return report
+
+
+def optimizer_step(self, lr, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01, max_grad_norm=0.0):
+    norm = torch.empty(1, device=self.engine.device, dtype=torch.float32)
+    check(self._lib.nnb_policy_optimizer_step(self._h, lr, beta1, beta2, eps, weight_decay, max_grad_norm, _ptr(norm)))
+    return norm
+
+
+def release_workspaces(self):
+    check(self._lib.nnb_policy_release_workspaces(self._h))
+
+
+for _f in (logprobs, grads_view, zero_grad, train_step, optimizer_step, release_workspaces):
+    setattr(Policy, _f.__name__, _f)

@@ -1,0 +1,199 @@
+"""Teacher-forced log-probs, objective reports and gradients of the CUDA training path against the
+numpy restatement (oracle/oracle_train.py): 1e-3 relative in f32, as the parity gate states."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, os.path.join(ROOT, "oracle"))
+import oracle_train as ot  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+REL = 1e-3
+
+
+def dev(a, eng, dt=np.float32):
+    return torch.from_numpy(np.ascontiguousarray(a, dt)).to(eng.device)
+
+
+def rel_err(got, ref):
+    ref = np.asarray(ref, np.float64)
+    got = np.asarray(got, np.float64)
+    return np.abs(got - ref).max() / max(np.abs(ref).max(), 1e-12)
+
+
+def _case(pkg, eng, act, pos, value_head, seed=1, n=3, S=12, P=4, d=64, heads=2, vocab=97, layers=2):
+    cfg = pkg.GptConfig(n_layer=layers, d_model=d, n_head=heads, d_ff=2 * d, vocab=vocab, ctx=S + 4, act=act, pos=pos,
+                        value_head=value_head)
+    flat = cfg.init_params(seed, bias_std=0.01)
+    if value_head:
+        layout, _ = cfg.param_layout()
+        for name, off, shape in layout:
+            if name == "value_head.weight":
+                flat[off:off + d] = np.random.default_rng(9).normal(0, 0.1, d)
+    pol = pkg.Policy(eng, cfg)
+    pol.upload_params(flat)
+    tr = ot.OracleTrainer(cfg, flat)
+    tokens = np.random.default_rng(seed + 1).integers(0, vocab, (n, S)).astype(np.int32)
+    return cfg, pol, tr, tokens, P
+
+
+@pytest.mark.parametrize("act,pos", [(0, 0), (1, 1)])
+def test_teacher_forced_logprobs(pkg, eng, act, pos):
+    cfg, pol, tr, tokens, P = _case(pkg, eng, act, pos, True)
+    lp_ref, ent_ref, val_ref = tr.forward(tokens, P)
+    lp, ent, val = pol.logprobs(dev(tokens, eng, np.int32), P, want_entropy=True, want_value=True)
+    assert rel_err(lp.cpu().numpy(), lp_ref) <= REL
+    assert rel_err(ent.cpu().numpy(), ent_ref) <= REL
+    assert rel_err(val.cpu().numpy(), val_ref) <= REL
+
+
+def test_logprobs_agree_with_rollout_logprobs(pkg, eng):
+    """old log-probs recorded by the rollout equal the teacher-forced ones (ratio = 1 at the first epoch)"""
+    cfg = pkg.GptConfig(n_layer=2, d_model=64, n_head=2, d_ff=128, vocab=300, ctx=40, act=1, pos=1)
+    pol = pkg.Policy(eng, cfg)
+    pol.upload_params(cfg.init_params(2, bias_std=0.01))
+    prompts = torch.from_numpy(np.random.default_rng(3).integers(0, 300, (6, 5)).astype(np.int32)).to(eng.device)
+    tokens, old_lp, _ = pol.rollout(prompts, 10, temperature=1.0, top_k=20, seed=1)
+    lp, _, _ = pol.logprobs(tokens, 5)
+    assert rel_err(lp.cpu().numpy(), old_lp.cpu().numpy()) <= REL
+
+
+def _grad_check(pol, tr, cfg, got_flat, ref_flat):
+    layout, _ = cfg.param_layout()
+    worst = 0.0
+    for name, off, shape in layout:
+        size = int(np.prod(shape))
+        g, r = got_flat[off:off + size], ref_flat[off:off + size]
+        scale = np.abs(r).max()
+        if scale < 1e-12:
+            assert np.abs(g).max() < 1e-9, name
+            continue
+        err = np.abs(g - r).max() / scale
+        worst = max(worst, err)
+        assert err <= REL, f"{name}: rel err {err:.2e}"
+    return worst
+
+
+@pytest.mark.parametrize("act,pos,value_head", [(0, 0, False), (1, 1, False), (1, 1, True), (0, 1, True)])
+def test_train_step_gradients(pkg, eng, act, pos, value_head):
+    cfg, pol, tr, tokens, P = _case(pkg, eng, act, pos, value_head)
+    n, S = tokens.shape
+    G = S - P
+    rng = np.random.default_rng(5)
+    lp_ref, ent_ref, val_ref = tr.forward(tokens, P)
+    old = lp_ref + rng.normal(0, 0.3, (n, G))
+    ref = lp_ref + rng.normal(0, 0.1, (n, G))
+    adv = rng.normal(0, 1, (n, G))
+    mask = (rng.uniform(size=(n, G)) < 0.8).astype(np.float64)
+    kw = dict(clip_eps=0.2, kl_coef=0.04, entropy_coef=0.01)
+    ret = oldv = None
+    if value_head:
+        ret = val_ref + rng.normal(0, 0.5, (n, G))
+        oldv = val_ref + rng.normal(0, 0.3, (n, G))
+        kw.update(value_coef=0.5, value_clip_eps=0.2)
+    rep_ref, up_lp, up_ent, dv = tr.objective(lp_ref, ent_ref, mask, old, adv, ref, val_ref, ret, oldv, **kw)
+    g_ref = tr.backward(up_lp, up_ent, dv)
+
+    pol.zero_grad()
+    rep = pol.train_step(dev(tokens, eng, np.int32), P, dev(mask, eng), old_logp=dev(old, eng), advantage=dev(adv, eng),
+                         ref_logp=dev(ref, eng), returns=None if ret is None else dev(ret, eng),
+                         old_value=None if oldv is None else dev(oldv, eng), **kw).cpu().numpy()
+    g = pol.grads_view().cpu().numpy().astype(np.float64)
+    names = ["policy_loss", "ratio_mean", "approx_kl", "clip_fraction", "kl_loss", "entropy_loss"]
+    for i, nm in enumerate(names):
+        assert abs(rep[i] - rep_ref[nm]) <= REL * max(abs(rep_ref[nm]), 1e-2), nm
+    assert rep[7] == mask.sum()
+    if value_head:
+        assert abs(rep[8] - rep_ref["value_loss"]) <= REL * max(abs(rep_ref["value_loss"]), 1e-2)
+    _grad_check(pol, tr, cfg, g, g_ref)
+    # a second micro-batch accumulates
+    pol.train_step(dev(tokens, eng, np.int32), P, dev(mask, eng), old_logp=dev(old, eng), advantage=dev(adv, eng),
+                   ref_logp=dev(ref, eng), returns=None if ret is None else dev(ret, eng),
+                   old_value=None if oldv is None else dev(oldv, eng), **kw)
+    g2 = pol.grads_view().cpu().numpy().astype(np.float64)
+    assert rel_err(g2, 2 * g) <= 1e-5
+
+
+def test_micro_batches_with_global_units_equal_one_batch(pkg, eng):
+    cfg, pol, tr, tokens, P = _case(pkg, eng, 1, 1, False, n=4)
+    n, S = tokens.shape
+    G = S - P
+    rng = np.random.default_rng(6)
+    lp_ref, _, _ = tr.forward(tokens, P)
+    old = lp_ref + rng.normal(0, 0.2, (n, G))
+    adv = rng.normal(0, 1, (n, G))
+    mask = (rng.uniform(size=(n, G)) < 0.7).astype(np.float32)
+    t = dev(tokens, eng, np.int32)
+    pol.zero_grad()
+    pol.train_step(t, P, dev(mask, eng), old_logp=dev(old, eng), advantage=dev(adv, eng))
+    whole = pol.grads_view().clone()
+    pol.zero_grad()
+    units = float(mask.sum())
+    for sl in (slice(0, 2), slice(2, 4)):
+        pol.train_step(t[sl].contiguous(), P, dev(mask[sl], eng), old_logp=dev(old[sl], eng), advantage=dev(adv[sl], eng),
+                       units=units)
+    parts = pol.grads_view()
+    assert rel_err(parts.cpu().numpy(), whole.cpu().numpy()) <= 1e-5
+
+
+def test_optimizer_step_updates_and_requantises(pkg, eng, orc):
+    cfg, pol, tr, tokens, P = _case(pkg, eng, 0, 0, False)
+    n, S = tokens.shape
+    G = S - P
+    rng = np.random.default_rng(7)
+    lp_ref, ent_ref, _ = tr.forward(tokens, P)
+    old = lp_ref + rng.normal(0, 0.2, (n, G))
+    adv = rng.normal(0, 1, (n, G))
+    mask = np.ones((n, G), np.float32)
+    pol.zero_grad()
+    pol.train_step(dev(tokens, eng, np.int32), P, dev(mask, eng), old_logp=dev(old, eng), advantage=dev(adv, eng))
+    g = pol.grads_view().cpu().numpy()
+    p0 = pol.params_view().cpu().numpy()
+    from oracle_binding import OracleRL
+
+    rl = OracleRL()
+    g_clip, norm_ref = rl.clip_grad_norm(g, 1.0)
+    p_ref, _, _ = rl.adamw(p0, g_clip, np.zeros_like(p0), np.zeros_like(p0), lr=1e-3, t=1, wd=0.01)
+    norm = pol.optimizer_step(lr=1e-3, weight_decay=0.01, max_grad_norm=1.0)
+    assert abs(norm.item() - norm_ref) <= 1e-5 * norm_ref
+    p1 = pol.params_view().cpu().numpy()
+    assert rel_err(p1, p_ref) <= 1e-6
+    assert torch.all(pol.grads_view() == 0)
+    # the packed weights follow the new master weights
+    layout = {nm: (off, shape) for nm, off, shape in cfg.param_layout()[0]}
+    off, shape = layout["blocks.0.ffn.fc1.weight"]
+    W = p1[off:off + shape[0] * shape[1]].reshape(shape)
+    packed, tau = pol.linear(0, 4)
+    tau_ref = orc.absmean_tau(W)
+    assert np.array_equal(tau.cpu().numpy(), tau_ref)
+    assert np.array_equal(packed.cpu().numpy().view(np.uint32), orc.trit_pack(W, tau_ref))
+
+
+def test_tiny_grpo_configuration_step(pkg, eng):
+    """The CPU-runnable configuration at reduced batch: 4 layers, d 256, 4 heads, GELU 1024, vocab 10000;
+    log-probs, loss and gradients within 1e-3 of the restatement."""
+    cfg = pkg.GptConfig(n_layer=4, d_model=256, n_head=4, d_ff=1024, vocab=10000, ctx=256, act=0, pos=0)
+    flat = cfg.init_params(1)
+    pol = pkg.Policy(eng, cfg)
+    pol.upload_params(flat)
+    tr = ot.OracleTrainer(cfg, flat)
+    rng = np.random.default_rng(2)
+    prompts = np.repeat(rng.integers(0, 10000, (2, 32)), 4, axis=0).astype(np.int32)  # 2 groups of 4
+    tokens, old_lp, _ = pol.rollout(dev(prompts, eng, np.int32), 24, temperature=1.0, seed=3)
+    tok_np = tokens.cpu().numpy()
+    reward = (tok_np[:, 32:] < 5000).mean(1).astype(np.float32)
+    adv_seq = eng.group_advantage(dev(reward, eng), [(0, 4), (4, 4)]).cpu().numpy()
+    adv = np.repeat(adv_seq[:, None], 24, 1)
+    mask = np.ones((8, 24), np.float32)
+    lp_ref, ent_ref, _ = tr.forward(tok_np, 32)
+    assert rel_err(old_lp.cpu().numpy(), lp_ref) <= REL
+    rep_ref, up_lp, up_ent, _ = tr.objective(lp_ref, ent_ref, mask, old_lp.cpu().numpy(), adv, clip_eps=0.2)
+    g_ref = tr.backward(up_lp)
+    pol.zero_grad()
+    rep = pol.train_step(tokens, 32, dev(mask, eng), old_logp=old_lp, advantage=dev(adv, eng), clip_eps=0.2).cpu().numpy()
+    assert abs(rep[0] - rep_ref["policy_loss"]) <= REL * max(abs(rep_ref["policy_loss"]), 1e-2)
+    _grad_check(pol, tr, cfg, pol.grads_view().cpu().numpy().astype(np.float64), g_ref)
