@@ -146,6 +146,11 @@ nnb_status launch_bitlinear_dx(nnb_engine* e, bool exact, const float* dy, const
 // dw (out,k) += tau * ((dy * s)^T . q)
 nnb_status launch_bitlinear_dw(nnb_engine* e, bool exact, const float* dy, const int8_t* q, const float* s,
                                const float* tau, size_t t, size_t k, size_t out, float* dw);
+// ---- gemm_bf16.cu (bf16 tensor-core versions of the two above)
+nnb_status launch_bitlinear_dx_bf16(nnb_engine* e, const float* dy, const uint32_t* wq, const float* tau, size_t t,
+                                    size_t k, size_t out, float* dx, bool accumulate);
+nnb_status launch_bitlinear_dw_bf16(nnb_engine* e, const float* dy, const int8_t* q, const float* s, const float* tau,
+                                    size_t t, size_t k, size_t out, float* dw);
 nnb_status launch_colsum_add(nnb_engine* e, const float* dy, size_t t, size_t out, float* db);
 
 // ---- train.cu
@@ -155,8 +160,8 @@ nnb_status launch_embed_bwd(nnb_engine* e, const float* g, const int32_t* tokens
                             size_t vocab, float* g_tok, float* g_pos);
 nnb_status launch_rope(nnb_engine* e, float* x, const float* rope_cos, const float* rope_sin, size_t n_rows,
                        size_t S, size_t H, size_t dk, bool backward);
-nnb_status launch_attn_fwd(nnb_engine* e, const float* q, const float* k, const float* v, size_t n_seq, size_t S,
-                           size_t H, size_t dk, float* out, float* lse);
+nnb_status launch_attn_fwd(nnb_engine* e, bool exact, const float* q, const float* k, const float* v, size_t n_seq,
+                           size_t S, size_t H, size_t dk, float* out, float* lse);
 nnb_status launch_attn_bwd(nnb_engine* e, const float* q, const float* k, const float* v, const float* out,
                            const float* dout, const float* lse, float* delta, size_t n_seq, size_t S, size_t H,
                            size_t dk, float* dq, float* dkk, float* dvv);

@@ -127,7 +127,7 @@ nnb_status launch_bitlinear_dx(nnb_engine* e, bool exact, const float* dy, const
 {
     NNB_REQUIRE(dy && wq && tau && dx && t > 0 && out > 0, "bitlinear_dx: bad arguments");
     NNB_REQUIRE(k > 0 && k % 64 == 0, "bitlinear_dx: k=%zu must be a multiple of 64", k);
-    (void)exact;
+    if (!exact) return launch_bitlinear_dx_bf16(e, dy, wq, tau, t, k, out, dx, accumulate);
     dim3 grid((unsigned)ceil_div(k, BN), (unsigned)ceil_div(t, BM));
     NNB_REQUIRE(grid.y <= 65535, "bitlinear_dx: too many tokens (%zu)", t);
     gemm_f32_kernel<0><<<grid, THREADS, 0, e->stream>>>(dy, tau, nullptr, wq, nullptr, (int)t, (int)out, (int)k, dx,
@@ -142,7 +142,7 @@ nnb_status launch_bitlinear_dw(nnb_engine* e, bool exact, const float* dy, const
 {
     NNB_REQUIRE(dy && q && s && tau && dw && t > 0 && out > 0, "bitlinear_dw: bad arguments");
     NNB_REQUIRE(k > 0 && k % 64 == 0, "bitlinear_dw: k=%zu must be a multiple of 64", k);
-    (void)exact;
+    if (!exact) return launch_bitlinear_dw_bf16(e, dy, q, s, tau, t, k, out, dw);
     dim3 grid((unsigned)ceil_div(k, BN), (unsigned)ceil_div(out, BM));
     NNB_REQUIRE(grid.y <= 65535, "bitlinear_dw: too many rows (%zu)", out);
     gemm_f32_kernel<1><<<grid, THREADS, 0, e->stream>>>(dy, tau, s, nullptr, q, (int)t, (int)out, (int)k, dw, 1);

@@ -182,7 +182,7 @@ static nnb_status forward(nnb_policy* p, const int32_t* tokens, size_t n_seq, si
             NNB_TRY(launch_rope(e, s.qkv, p->rope_cos, p->rope_sin, T, S, H, dk, false));
             NNB_TRY(launch_rope(e, s.qkv + T * d, p->rope_cos, p->rope_sin, T, S, H, dk, false));
         }
-        NNB_TRY(launch_attn_fwd(e, s.qkv, s.qkv + T * d, s.qkv + 2 * T * d, n_seq, S, H, dk, s.att, s.lse));
+        NNB_TRY(launch_attn_fwd(e, exact, s.qkv, s.qkv + T * d, s.qkv + 2 * T * d, n_seq, S, H, dk, s.att, s.lse));
         NNB_TRY(launch_row_quant(e, 3, exact, s.att, nullptr, T, d, d, s.q2, s.s2, w->qsum, nullptr));
         NNB_TRY(lin_fwd(p, LW.o, 1, s.q2, s.s2, w->qsum, T, x_in, s.x_mid, 0));
         NNB_TRY(launch_row_quant(e, 0, exact, s.x_mid, PP + LW.ln2_g, T, d, d, s.q3, s.s3, w->qsum, nullptr));

@@ -68,10 +68,15 @@ __global__ void rope_kernel(float* __restrict__ x, const float* __restrict__ rop
 // One warp per query.  Keys are processed in tiles of 32 held in shared memory: lane j scores
 // key j, then the lanes switch to owning output features for the P.V update (online softmax).
 constexpr int ATT_WARPS = 8;
+// EXACT: scores, softmax sums and the P.V accumulation in f64 (the value then rounds once to
+// f32, independent of the tile order), so that the int8 quantisation that follows sees the same
+// activations as the high-precision restatement.
+template <bool EXACT>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
 attn_fwd_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, int S,
                 int H, int dk, float scale, float* __restrict__ out, float* __restrict__ lse)
 {
+    typedef typename AccT<EXACT>::type acc_t;
     extern __shared__ float sm[];
     const int dkp = dk + 1;
     float* Ks = sm;                       // 32 x dkp
@@ -87,8 +92,8 @@ attn_fwd_kernel(const float* __restrict__ q, const float* __restrict__ k, const 
     float* qs = Qs + warp * dk;
     if (qvalid)
         for (int i = lane; i < dk; i += 32) qs[i] = __fmul_rn(q[(base + qi) * d + (size_t)h * dk + i], scale);
-    float o[4] = {0.f, 0.f, 0.f, 0.f};
-    float m = -INFINITY, l = 0.0f;
+    acc_t o[4] = {0, 0, 0, 0};
+    acc_t m = -INFINITY, l = 0;
     const int last_q = min(S - 1, q0 + ATT_WARPS - 1);
     for (int j0 = 0; j0 <= last_q; j0 += 32) {
         __syncthreads();
@@ -106,40 +111,49 @@ attn_fwd_kernel(const float* __restrict__ q, const float* __restrict__ k, const 
         __syncthreads();
         if (!qvalid || j0 > qi) continue;
         const int j = j0 + lane;
-        float sc = -INFINITY;
+        acc_t sc = -INFINITY;
         if (j <= qi) {
-            float a = 0.0f;
+            acc_t a = 0;
             const float* kr = Ks + lane * dkp;
-            for (int c = 0; c < dk; ++c) a = fmaf(qs[c], kr[c], a);
+            for (int c = 0; c < dk; ++c) a += (acc_t)qs[c] * (acc_t)kr[c];
             sc = a;
         }
-        const float tmax = warp_max(sc);
-        const float m_new = fmaxf(m, tmax);
-        const float p = (j <= qi) ? __expf(sc - m_new) : 0.0f;
-        const float corr = __expf(m - m_new);
-        l = l * corr + warp_sum(p);
+        acc_t tmax = sc;
+        for (int off = 16; off > 0; off >>= 1) {
+            const acc_t other = shfl_xor_t(tmax, off);
+            tmax = other > tmax ? other : tmax;
+        }
+        const acc_t m_new = m > tmax ? m : tmax;
+        acc_t p, corr;
+        if (EXACT) {
+            p = (j <= qi) ? (acc_t)exp((double)(sc - m_new)) : (acc_t)0;
+            corr = (acc_t)exp((double)(m - m_new));
+        } else {
+            p = (j <= qi) ? (acc_t)__expf((float)(sc - m_new)) : (acc_t)0;
+            corr = (acc_t)__expf((float)(m - m_new));
+        }
+        l = l * corr + warp_sum_t(p);
 #pragma unroll
         for (int i = 0; i < 4; ++i) o[i] *= corr;
         for (int jj = 0; jj < 32; ++jj) {
-            const float pj = __shfl_sync(0xffffffffu, p, jj);
-            if (pj != 0.0f) {
+            const acc_t pj = __shfl_sync(0xffffffffu, p, jj);
+            if (pj != (acc_t)0) {
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const int c = lane + 32 * i;
-                    if (c < dk) o[i] = fmaf(pj, Vs[jj * dkp + c], o[i]);
+                    if (c < dk) o[i] += pj * (acc_t)Vs[jj * dkp + c];
                 }
             }
         }
         m = m_new;
     }
     if (qvalid) {
-        const float inv = 1.0f / l;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int c = lane + 32 * i;
-            if (c < dk) out[(base + qi) * d + (size_t)h * dk + c] = o[i] * inv;
+            if (c < dk) out[(base + qi) * d + (size_t)h * dk + c] = (float)(o[i] / l);
         }
-        if (lane == 0) lse[((size_t)b * H + h) * S + qi] = m + logf(l);
+        if (lane == 0) lse[((size_t)b * H + h) * S + qi] = (float)(m + (acc_t)log((double)l));
     }
 }
 
@@ -489,19 +503,23 @@ nnb_status launch_rope(nnb_engine* e, float* x, const float* rope_cos, const flo
     return NNB_OK;
 }
 
-nnb_status launch_attn_fwd(nnb_engine* e, const float* q, const float* k, const float* v, size_t n_seq, size_t S,
-                           size_t H, size_t dk, float* out, float* lse)
+nnb_status launch_attn_fwd(nnb_engine* e, bool exact, const float* q, const float* k, const float* v, size_t n_seq,
+                           size_t S, size_t H, size_t dk, float* out, float* lse)
 {
     NNB_REQUIRE(dk <= 128, "attention: head dim %zu > 128", dk);
     const size_t smem = (2 * 32 * (dk + 1) + ATT_WARPS * dk) * sizeof(float);
     static size_t cfg = 0;
     if (smem > cfg) {
-        NNB_CUDA(cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        NNB_CUDA(cudaFuncSetAttribute(attn_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        NNB_CUDA(cudaFuncSetAttribute(attn_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         cfg = smem;
     }
     dim3 grid((unsigned)(n_seq * H), (unsigned)ceil_div(S, ATT_WARPS));
-    attn_fwd_kernel<<<grid, ATT_WARPS * 32, smem, e->stream>>>(q, k, v, (int)S, (int)H, (int)dk,
-                                                              1.0f / sqrtf((float)dk), out, lse);
+    const float scale = 1.0f / sqrtf((float)dk);
+    if (exact)
+        attn_fwd_kernel<true><<<grid, ATT_WARPS * 32, smem, e->stream>>>(q, k, v, (int)S, (int)H, (int)dk, scale, out, lse);
+    else
+        attn_fwd_kernel<false><<<grid, ATT_WARPS * 32, smem, e->stream>>>(q, k, v, (int)S, (int)H, (int)dk, scale, out, lse);
     e->launches++;
     NNB_CHECK_LAUNCH("attn_fwd_kernel");
     return NNB_OK;

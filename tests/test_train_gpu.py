@@ -190,10 +190,41 @@ def test_tiny_grpo_configuration_step(pkg, eng):
     adv = np.repeat(adv_seq[:, None], 24, 1)
     mask = np.ones((8, 24), np.float32)
     lp_ref, ent_ref, _ = tr.forward(tok_np, 32)
-    assert rel_err(old_lp.cpu().numpy(), lp_ref) <= REL
+    lp_tf, _, _ = pol.logprobs(tokens, 32)
+    assert rel_err(lp_tf.cpu().numpy(), lp_ref) <= REL
+    # the rollout's step path rounds attention in a different order than the full forward, which can
+    # flip an int8 activation here and there (the reference's own decode-vs-forward check allows 5e-2
+    # on logits, src/attn_consistency_test.cpp:262-264)
+    assert rel_err(old_lp.cpu().numpy(), lp_ref) <= 5e-3
     rep_ref, up_lp, up_ent, _ = tr.objective(lp_ref, ent_ref, mask, old_lp.cpu().numpy(), adv, clip_eps=0.2)
     g_ref = tr.backward(up_lp)
     pol.zero_grad()
     rep = pol.train_step(tokens, 32, dev(mask, eng), old_logp=old_lp, advantage=dev(adv, eng), clip_eps=0.2).cpu().numpy()
     assert abs(rep[0] - rep_ref["policy_loss"]) <= REL * max(abs(rep_ref["policy_loss"]), 1e-2)
     _grad_check(pol, tr, cfg, pol.grads_view().cpu().numpy().astype(np.float64), g_ref)
+
+
+def test_fast_mode_gradients_are_close(pkg, eng):
+    """bf16 tensor-core backward GEMMs and bf16 KV cache against the exact mode."""
+    kw = dict(n_layer=2, d_model=128, n_head=2, d_ff=256, vocab=531, ctx=40, act=1, pos=1)
+    cfg_e, cfg_f = pkg.GptConfig(exact=True, **kw), pkg.GptConfig(exact=False, **kw)
+    flat = cfg_e.init_params(4, bias_std=0.01)
+    pe, pf = pkg.Policy(eng, cfg_e), pkg.Policy(eng, cfg_f)
+    pe.upload_params(flat)
+    pf.upload_params(flat)
+    rng = np.random.default_rng(8)
+    tokens = dev(rng.integers(0, 531, (5, 33)), eng, np.int32)
+    P, G = 9, 24
+    lp, _, _ = pe.logprobs(tokens, P)
+    old = lp + dev(rng.normal(0, 0.2, (5, G)), eng)
+    adv = dev(rng.normal(0, 1, (5, G)), eng)
+    mask = dev(np.ones((5, G)), eng)
+    for pol in (pe, pf):
+        pol.zero_grad()
+        pol.train_step(tokens, P, mask, old_logp=old, advantage=adv)
+    ge, gf = pe.grads_view().cpu().numpy(), pf.grads_view().cpu().numpy()
+    layout, _ = cfg_e.param_layout()
+    for name, off, shape in layout:
+        size = int(np.prod(shape))
+        a, b = ge[off:off + size], gf[off:off + size]
+        assert np.abs(a - b).max() <= 3e-2 * max(np.abs(a).max(), 1e-12), name
