@@ -536,3 +536,20 @@ ORC_API int orc_gpt_step_logits(const orc_gpt* m, const int32_t* tokens, int n_t
     state_free(st);
     return 0;
 }
+
+/* helpers for the numpy training restatement: the same exp and RoPE tables as the step path */
+ORC_API void orc_expf_array(const float* x, size_t n, float* out)
+{
+    for (size_t i = 0; i < n; ++i) out[i] = orc_expf(x[i]);
+}
+
+ORC_API void orc_rope_tables(int dk, int ctx, float* cos_out, float* sin_out)
+{
+    const int half = dk / 2;
+    for (int p = 0; p < ctx; ++p)
+        for (int j = 0; j < half; ++j) {
+            const float theta = (float)p / powf(10000.0f, (float)(2 * j) / (float)dk);
+            cos_out[(size_t)p * half + j] = cosf(theta);
+            sin_out[(size_t)p * half + j] = sinf(theta);
+        }
+}

@@ -18,9 +18,32 @@ engine-defined: parity unpinned bitwise, tolerance-gated.
 """
 from __future__ import annotations
 
+import ctypes as C
+import os
+
 import numpy as np
 
 F32 = np.float32
+_LIB = None
+
+
+def _lib():
+    """liboracle.so supplies the bit-reproducible exp and the RoPE tables of the step path."""
+    global _LIB
+    if _LIB is None:
+        L = C.CDLL(os.path.join(os.path.dirname(os.path.abspath(__file__)), "liboracle.so"))
+        fp = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
+        L.orc_expf_array.argtypes = [fp, C.c_size_t, fp]
+        L.orc_rope_tables.argtypes = [C.c_int, C.c_int, fp, fp]
+        _LIB = L
+    return _LIB
+
+
+def expf32(x):
+    x = np.ascontiguousarray(x, F32)
+    out = np.empty_like(x)
+    _lib().orc_expf_array(x.reshape(-1), x.size, out.reshape(-1))
+    return out
 
 
 def unflatten(cfg, flat):
@@ -79,10 +102,16 @@ class Linear:
 
 
 def rmsnorm_fwd(x, g):
+    """Output in the engine's f32 rounding order (it feeds a quantiser); cache in float64."""
+    x = x.astype(F32)
+    f = x.shape[-1]
+    ss = (x * x).astype(np.float64).sum(-1, keepdims=True).astype(F32)
+    v = (ss * (F32(1.0) / F32(f)) + F32(1e-5)).astype(F32)
+    sinv32 = (F32(1.0) / np.sqrt(v).astype(F32)).astype(F32)
+    out = ((x * sinv32).astype(F32) * g.astype(F32)).astype(F32)
     x64 = x.astype(np.float64)
     sinv = 1.0 / np.sqrt((x64 * x64).mean(-1, keepdims=True) + 1e-5)
-    normed = x64 * sinv
-    return (normed * g).astype(F32), (normed, sinv)
+    return out, (x64 * sinv, sinv)
 
 
 def rmsnorm_bwd(dy, g, cache):
@@ -101,18 +130,19 @@ def sigmoid(x):
 def rope_tables(cfg, S):
     dk = cfg.d_model // cfg.n_head
     half = dk // 2
-    pos = np.arange(S, dtype=F32)[:, None]
-    j = np.arange(half, dtype=F32)[None, :]
-    theta = (pos / np.power(F32(10000.0), (F32(2.0) * j) / F32(dk)).astype(F32)).astype(F32)
-    return np.cos(theta).astype(np.float64), np.sin(theta).astype(np.float64)
+    cos, sin = np.empty((S, half), F32), np.empty((S, half), F32)
+    _lib().orc_rope_tables(dk, S, cos, sin)
+    return cos, sin
 
 
 def rope_apply(x, cos, sin, sign=1.0):
-    """x (n,S,H,dk); out = x*cos + rotate_half(x)*sin (sign=-1: the inverse rotation)."""
+    """x (n,S,H,dk); out = x*cos + rotate_half(x)*sin (sign=-1: the inverse rotation).
+    f32 inputs are rotated with the engine's f32 roundings, float64 inputs in float64."""
     half = x.shape[-1] // 2
     a, b = x[..., :half], x[..., half:]
-    c, s = cos[None, :, None, :], sign * sin[None, :, None, :]
-    return np.concatenate([a * c - b * s, b * c + a * s], -1)
+    dt = x.dtype
+    c, s = cos[None, :, None, :].astype(dt), (sign * sin[None, :, None, :]).astype(dt)
+    return np.concatenate([(a * c).astype(dt) + ((-b) * s).astype(dt), (b * c).astype(dt) + (a * s).astype(dt)], -1).astype(dt)
 
 
 class OracleTrainer:
@@ -151,12 +181,14 @@ class OracleTrainer:
             c["x_in"] = x
             n1, c["n1"] = rmsnorm_fwd(x, p[pre + "ln1.gamma"])
             flat1 = n1.reshape(n * S, d)
-            q = self.lin[pre + "attn.q"].forward(flat1).astype(np.float64).reshape(n, S, H, dk)
-            k = self.lin[pre + "attn.k"].forward(flat1).astype(np.float64).reshape(n, S, H, dk)
+            q = self.lin[pre + "attn.q"].forward(flat1).reshape(n, S, H, dk)
+            k = self.lin[pre + "attn.k"].forward(flat1).reshape(n, S, H, dk)
             v = self.lin[pre + "attn.v"].forward(flat1).astype(np.float64).reshape(n, S, H, dk)
             if cfg.pos == 1:
                 q, k = rope_apply(q, cos, sin), rope_apply(k, cos, sin)
-            qs = q * scale  # the reference folds the scale into Q after RoPE
+            # the reference folds the scale into Q after RoPE (one f32 multiply)
+            qs = (q * F32(1.0 / np.sqrt(F32(dk)))).astype(F32).astype(np.float64)
+            k = k.astype(np.float64)
             sc = np.einsum("bihd,bjhd->bhij", qs, k)
             sc = np.where(causal[None, None], sc, -np.inf)
             sc = sc - sc.max(-1, keepdims=True)
@@ -171,12 +203,12 @@ class OracleTrainer:
             n2, c["n2"] = rmsnorm_fwd(x_mid, p[pre + "ln2.gamma"])
             h1 = self.lin[pre + "ffn.fc1"].forward(n2.reshape(n * S, d))
             c["h1"] = h1
-            h64 = h1.astype(np.float64)
             if cfg.act == 0:
-                act = h64 / (1.0 + np.exp(-(h64 * 1.702)))
+                act = (h1 / (F32(1.0) + expf32(-(h1 * F32(1.702)).astype(F32))).astype(F32)).astype(F32)
             else:
-                g, u = h64[:, :F], h64[:, F:]
-                act = g * sigmoid(g) * u
+                g, u = h1[:, :F], h1[:, F:]
+                sg = (F32(1.0) / (F32(1.0) + expf32(-g)).astype(F32)).astype(F32)
+                act = ((g * sg).astype(F32) * u).astype(F32)
             f2 = self.lin[pre + "ffn.fc2"].forward(act.astype(F32))
             x = (x_mid + f2.reshape(n, S, d)).astype(F32)
             self.cache.append(c)
