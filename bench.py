@@ -1,10 +1,14 @@
-"""bench.py — hot-path benchmark of the nn-b200 engine.
+"""bench.py — hot-path benchmark of the nn-b200 engine: one GRPO step of the ~1B ternary policy.
 
-python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload grpo1b|tiny]
 
-Prints ONE JSON line on rank 0.  A "step" is one pass of the workload over one batch of seeded
-synthetic input.  `value` is timed with inputs resident in HBM; `e2e` goes through the host-buffer
-C-ABI entry point with host<->device copies inside the timed region.
+Workload (default grpo1b): GRPO on a 24-layer, d 2048, 16-head, RoPE, SwiGLU 5632, vocab 32000 ternary
+policy; 64 prompt groups x 16 samples, prompt 128 uniform-random ids, 512 generated tokens, top-k 50,
+temperature 0.8; reward = seeded hash of the generated tokens -> {0,1} with p 0.3; clip 0.2, KL 0.04
+against a frozen copy of the initial weights; AdamW.  Prompt groups are sharded over the ranks
+(whole groups per rank, strong scaling); the policy gradient is all-reduced with NCCL.
+A "step" = rollout + rewards/advantages + reference log-probs + forward/backward + optimizer.
+Synthetic data, random-init weights.  Prints ONE JSON line on rank 0.
 """
 from __future__ import annotations
 
@@ -21,8 +25,18 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+WORKLOADS = {
+    # the configuration the metric is quoted on
+    "grpo1b": dict(model=dict(n_layer=24, d_model=2048, n_head=16, d_ff=5632, vocab=32000, ctx=640, act=1, pos=1),
+                   groups=64, group_size=16, prompt_len=128, max_new=512, temperature=0.8, top_k=50,
+                   micro_batch=16, rollout_chunk=512),
+    # the CPU-runnable configuration (parity-test shape; selectable for quick checks)
+    "tiny": dict(model=dict(n_layer=4, d_model=256, n_head=4, d_ff=1024, vocab=10000, ctx=256, act=0, pos=0),
+                 groups=8, group_size=8, prompt_len=32, max_new=64, temperature=1.0, top_k=0,
+                 micro_batch=64, rollout_chunk=64),
+}
 
-# ----------------------------------------------------------------------------- helpers
+
 def _peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -40,15 +54,12 @@ class ClockSampler:
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
-        self.index = index
-        self.rows = []
-        self.proc = None
-        self.thread = None
+        self.index, self.rows, self.proc = index, [], None
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
                  "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except Exception:
             self.proc = None
@@ -58,90 +69,116 @@ class ClockSampler:
             for line in self.proc.stdout:
                 self.rows.append((time.time(), line.strip()))
 
-        self.thread = threading.Thread(target=pump, daemon=True)
-        self.thread.start()
+        threading.Thread(target=pump, daemon=True).start()
 
     def stop(self, t0: float, t1: float):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+        time.sleep(0.25)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=2)
         except Exception:
             self.proc.kill()
-        sm, smax, reasons = [], None, set()
+        sm, smax, reasons, power = [], None, set(), []
         for ts, line in self.rows:
             f = [x.strip() for x in line.split(",")]
-            if len(f) < 9:
+            if len(f) < 9 or not (t0 <= ts <= t1 + 0.2):
                 continue
             try:
-                clk = float(f[1])
+                sm.append(float(f[1]))
                 smax = float(f[2])
+                power.append(float(f[3]))
             except ValueError:
                 continue
-            if t0 - 0.05 <= ts <= t1 + 0.05:
-                sm.append(clk)
-                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
-                    if val.lower().startswith("active"):
-                        reasons.add(name)
-        if not sm:  # region shorter than the sampling period: use every sample we have
-            for ts, line in self.rows:
-                f = [x.strip() for x in line.split(",")]
-                try:
-                    sm.append(float(f[1]))
-                    smax = float(f[2])
-                except (ValueError, IndexError):
-                    pass
-        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": smax,
-                "reasons": sorted(reasons), "samples": len(sm)}
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons),
+                "samples": len(sm), "power_w_max": max(power) if power else None}
 
 
 def _dist_env():
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    return rank, world, local
+    return int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
 
 
-# ------------------------------------------------------------------- workload: ternary stream
-# Operator sweep configuration: activations M x K f32 N(0,1), per-token absmax int8; weights
-# iid ternary p=1/3 each, 2-bit packed, per-tensor scale U[0.01,0.1].  To keep the packed-weight
-# stream out of L2 (126 MB) the step walks a stack of independent (K=2048 -> N=5632) matrices.
-K_DIM, N_DIM, M_TOK = 2048, 5632, 16
-STACK = 128  # 128 x 2.88 MB = 369 MB of packed weights per step (> L2)
-
-
-def _make_stack(seed: int, n_mats: int):
-    """numpy version (small n_mats; used by the CPU baseline)"""
-    rng = np.random.default_rng(seed)
-    codes = rng.integers(1, 4, size=(n_mats, N_DIM, K_DIM // 16, 16), dtype=np.uint8).astype(np.uint32)
-    words = np.zeros((n_mats, N_DIM, K_DIM // 16), np.uint32)
-    for j in range(16):
-        words |= codes[..., j] << np.uint32(2 * j)
-    tau = np.repeat(rng.uniform(0.01, 0.1, (n_mats, 1)).astype(np.float32), N_DIM, axis=1)
-    return words, tau
-
-
-def _make_stack_device(seed: int, n_mats: int, dev):
-    """same distribution generated on the device (iid codes 1..3, per-tensor scale)"""
+def _init_policy_device(pkg, eng, cfg, seed):
+    """Random-init weights on the device: linears and embeddings N(0, 0.02), gains 1, biases 0."""
     import torch
 
-    g = torch.Generator(device=dev)
+    pol = pkg.Policy(eng, cfg)
+    g = torch.Generator(device=eng.device)
     g.manual_seed(seed)
-    words = torch.zeros((n_mats, N_DIM, K_DIM // 16), device=dev, dtype=torch.int64)
-    for j in range(16):
-        c = torch.randint(1, 4, (n_mats, N_DIM, K_DIM // 16), device=dev, dtype=torch.int64, generator=g)
-        words |= c << (2 * j)
-    words = (words & 0xFFFFFFFF)
-    words = torch.where(words >= 2**31, words - 2**32, words).to(torch.int32).contiguous()
-    tau = torch.empty((n_mats, 1), device=dev).uniform_(0.01, 0.1, generator=g).expand(n_mats, N_DIM).contiguous()
-    return words, tau
+    pv = pol.params_view()
+    pv.normal_(0, 0.02, generator=g)
+    layout, _ = cfg.param_layout()
+    for name, off, shape in layout:
+        size = int(np.prod(shape))
+        if name.endswith("gamma"):
+            pv[off:off + size] = 1.0
+        elif name.endswith(".bias"):
+            pv[off:off + size] = 0.0
+    pol.requantize()
+    return pol
 
 
-def _algorithmic_bytes(m, k, n):
-    # packed weights + tau + int8 activations + scales + f32 output
-    return k * n / 4 + 4 * n + m * k + 4 * m + 4 * m * n
+def _time_loop(torch, fn, reps, warm=3):
+    for _ in range(warm):
+        fn()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    a.record()
+    for _ in range(reps):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / reps
+
+
+def _kernel_rooflines(torch, pkg, eng, pol, wl, peaks):
+    """Times the dominant kernels alone (CUDA events on the launching stream, inputs larger than L2)."""
+    m = wl["model"]
+    d, F = m["d_model"], m["d_ff"]
+    dev = eng.device
+    out = {}
+    # (1) backward dX GEMM of fc1 at one micro-batch: the largest share of the step's GEMM time
+    T = wl["micro_batch"] * (wl["prompt_len"] + wl["max_new"])
+    packed, tau = pol.linear(0, 4)  # fc1: (2F, d)
+    O = packed.shape[0]
+    dy = torch.randn((T, O), device=dev)
+    dx = torch.empty((T, d), device=dev)
+    ms = _time_loop(torch, lambda: eng.bitlinear_dx_tm(dy, packed, tau, d, dx=dx, exact=False), 10)
+    flops = 2.0 * T * d * O
+    ach = flops / (ms * 1e-3) / 1e12
+    out["roofline"] = {"bound": "tensor", "achieved": ach, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                       "frac": ach / peaks["bf16_tflops_sustained"], "traffic": None, "peak_source": peaks["src"] + " (sustained)",
+                       "kernel": "gemm_bf16_kernel<dX>", "kernel_ms": ms, "shape": f"T={T} K={d} O={O}"}
+    # (2) ternary forward GEMM at one micro-batch (int8 x 2-bit -> int32)
+    x = torch.randn((T, d), device=dev)
+    q, s, qsum = eng.act_quant_tm(x)
+    y = torch.empty((T, O), device=dev)
+    ms = _time_loop(torch, lambda: eng.bitlinear_fwd_tm(packed, tau, None, q, s, qsum, y=y), 10)
+    out["roofline_int8_gemm"] = {"bound": "tensor", "achieved": 2.0 * T * d * O / (ms * 1e-3) / 1e12, "unit": "TOP/s (int8)",
+                                 "peak": None, "kernel": "bitlinear_mma_kernel", "kernel_ms": ms, "shape": f"T={T} K={d} O={O}"}
+    # (3) decode-sized ternary GEMV: packed-weight stream of a stack of fc1-shaped matrices (> L2)
+    n_mats = 64
+    wst = torch.randint(-2**31, 2**31 - 1, (n_mats, O, d // 16), device=dev, dtype=torch.int64)
+    lo, hi = wst & 0x55555555, (wst >> 1) & 0x55555555
+    wst = wst | ((~(lo | hi)) & 0x55555555) << 1
+    wst = (wst & 0xFFFFFFFF)
+    wst = torch.where(wst >= 2**31, wst - 2**32, wst).to(torch.int32).contiguous()
+    taus = torch.rand((n_mats, O), device=dev) * 0.09 + 0.01
+    for mtok in (1, 16):
+        xq = torch.randn((mtok, d), device=dev)
+        q1, s1, qs1 = eng.act_quant_tm(xq)
+        ys = torch.empty((n_mats, mtok, O), device=dev)
+        ms = _time_loop(torch, lambda: eng.bitlinear_fwd_tm_stack(wst, taus, None, q1, s1, qs1, ys), 20)
+        alg = n_mats * (d * O / 4 + 4 * O + mtok * d + 4 * mtok + 4 * mtok * O)
+        ach = alg / (ms * 1e-3) / 1e9
+        out[f"roofline_gemv_m{mtok}"] = {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                          "frac": ach / peaks["hbm_gbs"], "kernel": "bitlinear_skinny_kernel",
+                                          "kernel_ms": ms, "shape": f"M={mtok} K={d} N={O} x{n_mats}"}
+    return out
 
 
 def run_ours(args):
@@ -149,146 +186,220 @@ def run_ours(args):
     from __graft_entry__ import load_package
 
     rank, world, local = _dist_env()
+    torch.cuda.set_device(local)
     if world > 1:
         import torch.distributed as dist
-        torch.cuda.set_device(local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     pkg = load_package()
     eng = pkg.Engine(local)
     dev = eng.device
     peaks = _peaks()
+    wl = WORKLOADS[args.workload]
+    cfg = pkg.GptConfig(exact=False, **wl["model"])
+    assert wl["groups"] % world == 0, "prompt groups must divide over the ranks"
+    groups_local = wl["groups"] // world
+    pol = _init_policy_device(pkg, eng, cfg, seed=1)
+    ref = _init_policy_device(pkg, eng, cfg, seed=1)  # frozen copy of the initial weights
+    gcfg = pkg.GrpoConfig(group_size=wl["group_size"], prompt_len=wl["prompt_len"], max_new=wl["max_new"],
+                          temperature=wl["temperature"], top_k=wl["top_k"], clip_eps=0.2, kl_coef=0.04, lr=1e-4,
+                          micro_batch=wl["micro_batch"], rollout_chunk=wl["rollout_chunk"])
+    trainer = pkg.GrpoTrainer(pol, ref, gcfg)
+    P, G = gcfg.prompt_len, gcfg.max_new
+    rng = np.random.default_rng(2)
+    all_prompts = rng.integers(0, cfg.vocab, (wl["groups"], P)).astype(np.int32)
+    h_prompts = torch.from_numpy(all_prompts[rank * groups_local:(rank + 1) * groups_local].copy()).pin_memory()
+    d_prompts = h_prompts.to(dev)
 
-    d_w, d_tau = _make_stack_device(4 + rank, STACK, dev)
-    rng = np.random.default_rng(3 + rank)
-    x = rng.normal(0, 1, (M_TOK, K_DIM)).astype(np.float32)
-    d_x = torch.from_numpy(x).to(dev)
-    y = torch.empty((STACK, M_TOK, N_DIM), device=dev, dtype=torch.float32)
+    def reward_dev(tokens):
+        return pkg.hash_reward(tokens[:, P:], 7)
 
-    def step():
-        q, s, qsum = eng.act_quant_tm(d_x)
-        eng.bitlinear_fwd_tm_stack(d_w, d_tau, None, q, s, qsum, y)
+    class Phases:
+        def __init__(self):
+            self.ev = []
+
+        def mark(self, name):
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            self.ev.append((name, e))
 
     def barrier():
         if world > 1:
             torch.distributed.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
-        step()
+    step_no = [0]
+
+    def step(prompts, reward_fn, phases=None):
+        step_no[0] += 1
+        return trainer.step(prompts, reward_fn, seed=step_no[0], timers=phases)
+
+    W = max(args.warmup, 3)
+    for _ in range(W):
+        step(d_prompts, reward_dev)
     barrier()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-        time.sleep(0.3)
+        time.sleep(0.4)
     l0 = eng.launch_count()
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    phases = Phases()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     t0 = time.time()
-    ev[0].record()
-    for i in range(args.steps):
-        step()
-        ev[i + 1].record()
+    ev0.record()
+    last = None
+    for _ in range(args.steps):
+        last = step(d_prompts, reward_dev, phases)
+    ev1.record()
     barrier()
     t1 = time.time()
     launches = eng.launch_count() - l0
-    total_ms = ev[0].elapsed_time(ev[-1])
-    # the dominant kernel alone (second launch of each step): time it separately with events
-    q, s, qsum = eng.act_quant_tm(d_x)
-    kev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-    reps = max(args.steps, 10)
-    torch.cuda.synchronize()
-    kev[0].record()
-    for _ in range(reps):
-        eng.bitlinear_fwd_tm_stack(d_w, d_tau, None, q, s, qsum, y)
-    kev[1].record()
-    torch.cuda.synchronize()
-    kern_ms = kev[0].elapsed_time(kev[1]) / reps
-
+    total_ms = ev0.elapsed_time(ev1)
+    # phase breakdown (this rank)
+    ph = {}
+    for i in range(1, len(phases.ev)):
+        nm = phases.ev[i][0]
+        if nm != "start":
+            ph[nm] = ph.get(nm, 0.0) + phases.ev[i - 1][1].elapsed_time(phases.ev[i][1]) / args.steps
     if world > 1:
-        tt = torch.tensor([total_ms], device=dev)
+        tt = torch.tensor([total_ms, ph.get("rollout", 0.0)], device=dev)
         torch.distributed.all_reduce(tt, op=torch.distributed.ReduceOp.MAX)
-        total_ms = float(tt.item())
+        total_ms, ph["rollout"] = float(tt[0]), float(tt[1])
+    clocks = sampler.stop(t0, t1) if rank == 0 else None
     ms_per_step = total_ms / args.steps
-    tokens_per_step = M_TOK * STACK * world  # token x linear applications
-    value = tokens_per_step / (ms_per_step * 1e-3)
+    value = 1000.0 / ms_per_step
+    gen_tokens = wl["groups"] * wl["group_size"] * G
+    rollout_tok_s = gen_tokens / (ph["rollout"] * 1e-3)
 
-    # e2e: host buffers through the C-ABI host entry point, one linear at a time
-    h_x = torch.from_numpy(x).pin_memory()
-    h_y = torch.empty((M_TOK, N_DIM), dtype=torch.float32).pin_memory()
-    n_e2e = 16
-    for i in range(3):
-        eng.bitlinear_fwd_host(d_w[i], d_tau[i], None, h_x, h_y)
+    # e2e: prompts start in pinned host memory, generated tokens go back to the host where the reward is
+    # computed, rewards come back up, and the step's report is read on the host
+    def reward_host(tokens):
+        tk = tokens[:, P:].cpu().numpy().astype(np.int64)
+        pos = (np.arange(1, G + 1, dtype=np.int64) * 2654435761) % 2147483647
+        h = ((tk + 1) * pos).sum(1) + 7 * 97003
+        h = (h * 1103515245 + 12345) % 2147483648
+        h = ((h ^ (h >> 13)) * 1274126177) % 2147483648
+        r = ((h % 1000003).astype(np.float32) / np.float32(1000003.0) < 0.3).astype(np.float32)
+        return torch.from_numpy(r).pin_memory().to(dev, non_blocking=True)
+
+    n_e2e = max(1, args.steps // 2)
     barrier()
     te0 = time.perf_counter()
-    for i in range(n_e2e):
-        eng.bitlinear_fwd_host(d_w[i % STACK], d_tau[i % STACK], None, h_x, h_y)
+    for _ in range(n_e2e):
+        out = step(h_prompts.to(dev, non_blocking=True), reward_host)
+        host_report = out["report"].cpu()
     barrier()
     te = time.perf_counter() - te0
-    e2e_value = M_TOK * n_e2e * world / te
+    if world > 1:
+        tt = torch.tensor([te], device=dev)
+        torch.distributed.all_reduce(tt, op=torch.distributed.ReduceOp.MAX)
+        te = float(tt[0])
+    e2e_value = n_e2e / te
+    N_local = groups_local * wl["group_size"]
+    h2d = groups_local * P * 4 + N_local * 4
+    d2h = N_local * G * 4 + 10 * 4
 
-    clocks = sampler.stop(t0, t1) if rank == 0 else None
-    alg = _algorithmic_bytes(M_TOK, K_DIM, N_DIM) * STACK
-    achieved = alg / (kern_ms * 1e-3) / 1e9
-    out = {
-        "metric": "ternary_linear_tok_per_s", "value": value, "unit": "tok/s (token x linear)",
-        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "int8xint2->int32", "data": "synthetic",
-        "config": {"workload": f"ternary GEMV operator sweep point M={M_TOK} K={K_DIM} N={N_DIM}, "
-                               f"stack of {STACK} matrices per step", "l2": "inputs larger than L2 (369 MB packed weights per step)"},
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["src"],
-                     "kernel": "bitlinear_mma_kernel", "kernel_ms": kern_ms},
-        "e2e": {"value": e2e_value, "unit": "tok/s (token x linear)",
-                "h2d_bytes_per_step": M_TOK * K_DIM * 4, "d2h_bytes_per_step": M_TOK * N_DIM * 4},
+    res = {
+        "metric": "grpo_steps_per_s", "value": value, "unit": "GRPO steps/s", "n_gpus": world, "steps": args.steps,
+        "warmup": W, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "int8 x 2-bit -> int32 forward, bf16 backward, f32 master weights", "data": "synthetic",
+        "config": {"workload": "GRPO step, ~1B ternary Llama-style policy (24 layers, d 2048, 16 heads, RoPE, SwiGLU 5632, "
+                               "vocab 32000), 64 prompts x group 16, prompt 128, 512 generated, top-k 50, T 0.8, clip 0.2, "
+                               "KL 0.04 vs frozen initial policy" if args.workload == "grpo1b" else "tiny GRPO configuration",
+                   "global_batch": wl["groups"] * wl["group_size"], "seq_len": P + G, "parallelism": f"dp{world} by prompt group",
+                   "l2": "working set per step (weights 0.34 GB packed + 11 GB f32, KV cache, activations) far larger than L2"},
+        "rollout_tok_per_s": rollout_tok_s,
+        "phase_ms": {k: round(v, 2) for k, v in ph.items()},
+        "e2e": {"value": e2e_value, "unit": "GRPO steps/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+                "steps": n_e2e},
         "gpu_launches": int(launches),
         "clocks": clocks,
+        "last_report": {k: float(v) for k, v in zip(
+            ["policy_loss", "ratio_mean", "approx_kl", "clip_fraction", "kl_loss", "entropy_loss", "entropy", "units"],
+            last["report"].cpu().tolist())},
     }
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        out["cpu_baseline"] = cpu_baseline(n_mats=4)
+    del host_report
+    if rank == 0 and world == 1:
+        pol.release_workspaces()
+        ref.release_workspaces()
+        res.update(_kernel_rooflines(torch, pkg, eng, pol, wl, peaks))
+        if not args.no_cpu_baseline:
+            res["cpu_baseline"] = cpu_baseline(args.workload)
     if rank == 0:
-        print(json.dumps(out))
+        print(json.dumps(res))
     if world > 1:
         torch.distributed.destroy_process_group()
 
 
-def cpu_baseline(n_mats: int):
-    """The oracle's token-major ternary linear on the host cores, on a bounded sample."""
+# ----------------------------------------------------------------------------- CPU arm
+def cpu_baseline(workload: str, budget_s: float = 25.0):
+    """The CPU restatement (oracle/) on the host cores, on a bounded sample of the same workload:
+    a rollout of a few sequences and tokens through the C step path (OpenMP over sequences) and one
+    teacher-forced forward/backward of one short sequence through the numpy restatement; the per-token
+    costs are extrapolated to the full step."""
     sys.path.insert(0, os.path.join(ROOT, "tests"))
-    from oracle_binding import Oracle
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    from __graft_entry__ import load_package
+    from oracle_binding import OracleGpt
+    import oracle_train as ot
 
-    orc = Oracle()
-    words, tau = _make_stack(4, n_mats)
-    rng = np.random.default_rng(3)
-    x = rng.normal(0, 1, (M_TOK, K_DIM)).astype(np.float32)
-    q, s = orc.act_quant_tm(x)
-    orc.bitlinear_i8_tm(words[0], tau[0], None, q, s, want_acc=False)
+    pkg = load_package()
+    wl = WORKLOADS[workload]
+    cfg = pkg.GptConfig(exact=True, **wl["model"])
+    cores = os.cpu_count() or 1
+    layout, n = cfg.param_layout()
+    rng = np.random.default_rng(1)
+    flat = (rng.standard_normal(n, dtype=np.float32) * np.float32(0.02))
+    for name, off, shape in layout:
+        size = int(np.prod(shape))
+        if name.endswith("gamma"):
+            flat[off:off + size] = 1.0
+        elif name.endswith(".bias"):
+            flat[off:off + size] = 0.0
+    P_s, G_s, n_seq = 8, 8, min(cores, 16)
+    m = OracleGpt(cfg, flat)
+    prompts = rng.integers(0, cfg.vocab, (n_seq, P_s)).astype(np.int32)
     t0 = time.perf_counter()
-    reps = 0
-    while time.perf_counter() - t0 < 10.0:
-        for i in range(n_mats):
-            qq, ss = orc.act_quant_tm(x)
-            orc.bitlinear_i8_tm(words[i], tau[i], None, qq, ss, want_acc=False)
-        reps += 1
-    dt = time.perf_counter() - t0
-    return {"value": M_TOK * n_mats * reps / dt, "unit": "tok/s (token x linear)",
-            "cores": os.cpu_count(), "kind": "port",
-            "sample": f"{n_mats} matrices of the stack repeated for ~10 s"}
+    tokens, _, _ = m.rollout(prompts, G_s, wl["temperature"], wl["top_k"], seed=1)
+    t_roll = time.perf_counter() - t0
+    per_tok_decode = t_roll / (n_seq * (P_s + G_s - 1))
+    del m
+    tr = ot.OracleTrainer(cfg, flat)
+    S_t = 32
+    toks = rng.integers(0, cfg.vocab, (1, S_t)).astype(np.int32)
+    t0 = time.perf_counter()
+    lp, ent, _ = tr.forward(toks, 8)
+    t_fwd = time.perf_counter() - t0
+    rep, up_lp, up_ent, _ = tr.objective(lp, ent, np.ones_like(lp), lp, np.ones_like(lp), lp, kl_coef=0.04)
+    t0 = time.perf_counter()
+    tr.backward(up_lp)
+    t_bwd = time.perf_counter() - t0
+    N = wl["groups"] * wl["group_size"]
+    S = wl["prompt_len"] + wl["max_new"]
+    # full step: decode N*(S-1) token-steps, reference forward over N*S tokens, policy forward+backward over N*S
+    est = per_tok_decode * N * (S - 1) + (t_fwd / S_t) * N * S * 2 + (t_bwd / S_t) * N * S
+    return {"value": 1.0 / est, "unit": "GRPO steps/s", "cores": cores, "kind": "port",
+            "sample": f"C step-path rollout of {n_seq} seqs x {P_s + G_s} tokens ({t_roll:.1f} s), numpy forward+backward of 1 x {S_t} "
+                      f"tokens ({t_fwd:.1f}+{t_bwd:.1f} s), extrapolated per token to the full step (attention cost at the sample's short context)",
+            "estimated_step_s": est}
 
 
 def run_reference(args):
     rank, world, _ = _dist_env()
     if rank != 0:
         return
-    cb = cpu_baseline(n_mats=4)
+    cb = cpu_baseline(args.workload)
+    wl = WORKLOADS[args.workload]
     out = {
-        "impl": "reference", "metric": "ternary_linear_tok_per_s", "value": cb["value"],
-        "unit": cb["unit"], "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": None, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "int8xint2->int32", "data": "synthetic",
-        "config": {"workload": f"ternary GEMV operator sweep point M={M_TOK} K={K_DIM} N={N_DIM}"},
+        "impl": "reference", "metric": "grpo_steps_per_s", "value": cb["value"], "unit": "GRPO steps/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": cb["estimated_step_s"] * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "int8 x 2-bit -> int32 forward, f64 backward (numpy restatement)",
+        "data": "synthetic",
+        "config": {"workload": "GRPO step, ~1B ternary Llama-style policy; CPU restatement of the reference CpuEngine semantics "
+                               "(the reference's own engine source is an un-vendored submodule and cannot be built)",
+                   "global_batch": wl["groups"] * wl["group_size"], "seq_len": wl["prompt_len"] + wl["max_new"]},
         "cpu_baseline": cb,
-        "e2e": {"value": cb["value"], "unit": cb["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "e2e": {"value": cb["value"], "unit": "GRPO steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(out))
 
@@ -296,9 +407,10 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=2)
+    ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="grpo1b", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":

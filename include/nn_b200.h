@@ -131,6 +131,15 @@ nnb_status nnb_bitlinear_fwd_tm_stack(nnb_engine* e, const uint32_t* d_wq, size_
                                       size_t t, size_t k, size_t out, void* d_y,
                                       size_t y_stride_elems, nnb_dtype dtype);
 
+/* BitLinear::backward, token-major (compute_layer_bitlinear.hpp:475-544).
+ * dX (matmul_q_t, :494): d_dx (t,k) (+)= (d_dy (t,out) * tau) . trit (out,k).
+ * dW (:514-534): d_dw (out,k) += tau * ((d_dy * s)^T . q) with q, s from nnb_act_quant_tm.
+ * exact = 1: f32 operands on CUDA cores; 0: bf16 operands on tensor cores, f32 accumulation. */
+nnb_status nnb_bitlinear_dx_tm(nnb_engine* e, const float* d_dy, const uint32_t* d_wq, const float* d_tau, size_t t,
+                               size_t k, size_t out, float* d_dx, int accumulate, int exact);
+nnb_status nnb_bitlinear_dw_tm(nnb_engine* e, const float* d_dy, const int8_t* d_q, const float* d_s,
+                               const float* d_tau, size_t t, size_t k, size_t out, float* d_dw, int exact);
+
 /* Host-buffer convenience: quantise h_x (t,k) f32, run the linear, return h_y (t,out) f32.
  * Copies host->device and device->host inside the call and synchronises. */
 nnb_status nnb_bitlinear_fwd_host(nnb_engine* e, const uint32_t* d_wq, const float* d_tau,

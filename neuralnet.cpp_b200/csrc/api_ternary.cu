@@ -95,6 +95,20 @@ nnb_status nnb_bitlinear_fwd_tm_stack(nnb_engine* e, const uint32_t* d_wq, size_
                                    n_mats, t, k, out, d_y, y_stride_elems, dtype, nullptr);
 }
 
+nnb_status nnb_bitlinear_dx_tm(nnb_engine* e, const float* d_dy, const uint32_t* d_wq, const float* d_tau, size_t t,
+                               size_t k, size_t out, float* d_dx, int accumulate, int exact)
+{
+    NNB_REQUIRE(e, "engine is NULL");
+    return launch_bitlinear_dx(e, exact != 0, d_dy, d_wq, d_tau, t, k, out, d_dx, accumulate != 0);
+}
+
+nnb_status nnb_bitlinear_dw_tm(nnb_engine* e, const float* d_dy, const int8_t* d_q, const float* d_s,
+                               const float* d_tau, size_t t, size_t k, size_t out, float* d_dw, int exact)
+{
+    NNB_REQUIRE(e, "engine is NULL");
+    return launch_bitlinear_dw(e, exact != 0, d_dy, d_q, d_s, d_tau, t, k, out, d_dw);
+}
+
 nnb_status nnb_bitlinear_fwd_host(nnb_engine* e, const uint32_t* d_wq, const float* d_tau,
                                   const float* d_bias, const float* h_x, size_t t, size_t k,
                                   size_t out, float* h_y)

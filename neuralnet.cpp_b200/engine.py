@@ -264,3 +264,25 @@ def adamw_step(self, params, grads, m, v, lr, t, beta1=0.9, beta2=0.999, eps=1e-
 for _f in (gae, group_advantage, masked_normalize, categorical_logp_entropy, categorical_backward,
            token_objective, clipped_value, clip_grad_norm, scale_inplace, adamw_step):
     setattr(Engine, _f.__name__, _f)
+
+
+def bitlinear_dx_tm(self, dy, wq, tau, k, dx=None, accumulate=False, exact=True):
+    """dX (t,k) (+)= (dY (t,out) * tau) . trit (out,k) — matmul_q_t, token-major."""
+    t, out = dy.shape
+    if dx is None:
+        dx = torch.empty((t, k), device=self.device, dtype=torch.float32)
+    check(self._lib.nnb_bitlinear_dx_tm(self._h, _ptr(dy), _ptr(wq), _ptr(tau), t, k, out, _ptr(dx), int(accumulate),
+                                        int(exact)))
+    return dx
+
+
+def bitlinear_dw_tm(self, dy, q, s, tau, dw, exact=True):
+    """dW (out,k) += tau * ((dY * s)^T . q) — the STE weight gradient of the int8-activation path."""
+    t, out = dy.shape
+    k = q.shape[1]
+    check(self._lib.nnb_bitlinear_dw_tm(self._h, _ptr(dy), _ptr(q), _ptr(s), _ptr(tau), t, k, out, _ptr(dw), int(exact)))
+    return dw
+
+
+Engine.bitlinear_dx_tm = bitlinear_dx_tm
+Engine.bitlinear_dw_tm = bitlinear_dw_tm

@@ -211,3 +211,25 @@ def test_bad_arguments_are_rejected(eng, pkg):
     x = torch.zeros((2, 100), device=eng.device)
     with pytest.raises(pkg.NnbError):
         eng.act_quant_tm(x)  # k not a multiple of 64
+
+
+@pytest.mark.parametrize("t,k,out", [(5, 64, 33), (130, 192, 100), (300, 256, 257)])
+def test_bitlinear_backward_gemms(eng, orc, t, k, out):
+    """dX = matmul_q_t and dW = ((dY*s) Q^T)*tau against the reference formulas
+    (src/t1_58_test.cpp:345-403, src/int8_act_test.cpp:327-359)."""
+    W, tau, X, _ = _case_tm(orc, t, k, out, seed=t + k)
+    packed = orc.trit_pack(W, tau)
+    trit = orc.trit_unpack(packed, k).astype(np.float64)
+    q_ref, s_ref = orc.act_quant_tm(X)
+    dY = np.random.default_rng(1).normal(0, 1, (t, out)).astype(np.float32)
+    dx_ref = (dY.astype(np.float64) * tau[None, :]) @ trit
+    dw_ref = ((dY.astype(np.float64) * s_ref[:, None]).T @ q_ref.astype(np.float64)) * tau[:, None]
+    q, s, _ = eng.act_quant_tm(_dev(X, eng))
+    for exact, tol in ((True, 1e-5), (False, 2e-2)):
+        dx = eng.bitlinear_dx_tm(_dev(dY, eng), _dev(packed.view(np.int32), eng), _dev(tau, eng), k, exact=exact)
+        assert np.abs(dx.cpu().numpy() - dx_ref).max() <= tol * np.abs(dx_ref).max()
+        dw = torch.zeros((out, k), device=eng.device)
+        eng.bitlinear_dw_tm(_dev(dY, eng), q, s, _dev(tau, eng), dw, exact=exact)
+        assert np.abs(dw.cpu().numpy() - dw_ref).max() <= tol * np.abs(dw_ref).max()
+        eng.bitlinear_dw_tm(_dev(dY, eng), q, s, _dev(tau, eng), dw, exact=exact)  # accumulates
+        assert np.abs(dw.cpu().numpy() - 2 * dw_ref).max() <= tol * 2 * np.abs(dw_ref).max()
