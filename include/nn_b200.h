@@ -140,6 +140,22 @@ nnb_status nnb_bitlinear_dx_tm(nnb_engine* e, const float* d_dy, const uint32_t*
 nnb_status nnb_bitlinear_dw_tm(nnb_engine* e, const float* d_dy, const int8_t* d_q, const float* d_s,
                                const float* d_tau, size_t t, size_t k, size_t out, float* d_dw, int exact);
 
+/* ---- the tcgen05 (tensor memory) versions for large token counts.  The ternary container is
+ * expanded once per requantisation: d_w8 (rows,k) int8 trits with k permuted like the engine's
+ * activation layout, d_wb (rows,k) bf16 trits; either may be NULL. */
+nnb_status nnb_expand_weights(nnb_engine* e, const uint32_t* d_wq, size_t rows, size_t k, int8_t* d_w8, void* d_wb);
+/* same result as nnb_bitlinear_fwd_tm (bit-exact), f32 output, optional bias and residual (t,out) */
+nnb_status nnb_bitlinear_fwd_tc(nnb_engine* e, const int8_t* d_w8, const float* d_tau, const float* d_bias,
+                                const float* d_residual, const int8_t* d_q, const float* d_s, size_t t, size_t k,
+                                size_t out, float* d_y);
+/* BitLinear::backward on bf16 tensor cores: d_dyb (t,out) and d_xs (t,k) are bf16 scratch buffers the
+ * call fills (dy*tau and s*q); d_dx (t,k) and/or d_dw (out,k) may be NULL to skip that half. */
+nnb_status nnb_bitlinear_bwd_tc(nnb_engine* e, const float* d_dy, const float* d_tau, const void* d_wb,
+                                const int8_t* d_q, const float* d_s, size_t t, size_t k, size_t out, void* d_dyb,
+                                void* d_xs, float* d_dx, int accumulate_dx, float* d_dw);
+/* synchronises and reports NNB_ERR_TIMEOUT if a kernel gave up on a bounded device-side wait */
+nnb_status nnb_engine_check(nnb_engine* e);
+
 /* Host-buffer convenience: quantise h_x (t,k) f32, run the linear, return h_y (t,out) f32.
  * Copies host->device and device->host inside the call and synchronises. */
 nnb_status nnb_bitlinear_fwd_host(nnb_engine* e, const uint32_t* d_wq, const float* d_tau,

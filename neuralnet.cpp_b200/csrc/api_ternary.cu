@@ -109,6 +109,47 @@ nnb_status nnb_bitlinear_dw_tm(nnb_engine* e, const float* d_dy, const int8_t* d
     return launch_bitlinear_dw(e, exact != 0, d_dy, d_q, d_s, d_tau, t, k, out, d_dw);
 }
 
+nnb_status nnb_expand_weights(nnb_engine* e, const uint32_t* d_wq, size_t rows, size_t k, int8_t* d_w8, void* d_wb)
+{
+    NNB_REQUIRE(e && d_wq && (d_w8 || d_wb), "expand_weights: NULL argument");
+    NNB_REQUIRE(k > 0 && k % 64 == 0, "expand_weights: k=%zu must be a multiple of 64", k);
+    return launch_expand_weights(e, d_wq, rows, k, d_w8, (__nv_bfloat16*)d_wb);
+}
+
+nnb_status nnb_bitlinear_fwd_tc(nnb_engine* e, const int8_t* d_w8, const float* d_tau, const float* d_bias,
+                                const float* d_residual, const int8_t* d_q, const float* d_s, size_t t, size_t k,
+                                size_t out, float* d_y)
+{
+    NNB_REQUIRE(e && d_w8 && d_tau && d_q && d_s && d_y, "bitlinear_fwd_tc: NULL argument");
+    NNB_REQUIRE(k > 0 && k % 64 == 0, "bitlinear_fwd_tc: k=%zu must be a multiple of 64", k);
+    return launch_tc_forward(e, d_q, d_w8, d_tau, d_s, d_bias, d_residual, t, k, out, d_y);
+}
+
+nnb_status nnb_bitlinear_bwd_tc(nnb_engine* e, const float* d_dy, const float* d_tau, const void* d_wb,
+                                const int8_t* d_q, const float* d_s, size_t t, size_t k, size_t out, void* d_dyb,
+                                void* d_xs, float* d_dx, int accumulate_dx, float* d_dw)
+{
+    NNB_REQUIRE(e && d_dy && d_tau && d_dyb, "bitlinear_bwd_tc: NULL argument");
+    NNB_REQUIRE(k % 64 == 0 && out % 8 == 0, "bitlinear_bwd_tc: needs k %% 64 == 0 and out %% 8 == 0 (k=%zu, out=%zu)", k, out);
+    NNB_TRY(launch_scale_to_bf16(e, d_dy, d_tau, t, out, (__nv_bfloat16*)d_dyb));
+    if (d_dx) {
+        NNB_REQUIRE(d_wb, "bitlinear_bwd_tc: dX needs the bf16 weights");
+        NNB_TRY(launch_tc_dx(e, (const __nv_bfloat16*)d_dyb, (const __nv_bfloat16*)d_wb, t, k, out, d_dx, accumulate_dx != 0));
+    }
+    if (d_dw) {
+        NNB_REQUIRE(d_q && d_s && d_xs, "bitlinear_bwd_tc: dW needs the activation cache and scratch");
+        NNB_TRY(launch_dequant_to_bf16(e, d_q, d_s, t, k, (__nv_bfloat16*)d_xs));
+        NNB_TRY(launch_tc_dw(e, (const __nv_bfloat16*)d_dyb, (const __nv_bfloat16*)d_xs, t, k, out, d_dw));
+    }
+    return NNB_OK;
+}
+
+nnb_status nnb_engine_check(nnb_engine* e)
+{
+    NNB_REQUIRE(e, "engine is NULL");
+    return tc_check_errors(e);
+}
+
 nnb_status nnb_bitlinear_fwd_host(nnb_engine* e, const uint32_t* d_wq, const float* d_tau,
                                   const float* d_bias, const float* h_x, size_t t, size_t k,
                                   size_t out, float* h_y)

@@ -65,6 +65,7 @@ struct nnb_engine {
     size_t pinned_bytes = 0;
     // counts kernel launches issued through this engine (reported by the benchmark)
     unsigned long long launches = 0;
+    bool tc_flag_cleared = false;  // the tensor-core GEMM error flag in the scratch page has been zeroed
     std::string describe_text;
 
     nnb_status ensure_scratch(size_t bytes);
@@ -177,5 +178,17 @@ nnb_status launch_value_fwd(nnb_engine* e, const float* x, const float* w, const
 nnb_status launch_value_bwd(nnb_engine* e, const float* x, const float* w, const float* dv, size_t n, size_t d,
                             float* dx, float* dw, float* db);
 nnb_status launch_add(nnb_engine* e, float* dst, const float* src, size_t n);
+
+// ---- gemm_tc.cu (tcgen05 / TMEM / TMA GEMMs)
+nnb_status launch_tc_forward(nnb_engine* e, const int8_t* q, const int8_t* w8, const float* tau, const float* s,
+                             const float* bias, const float* residual, size_t t, size_t k, size_t out, float* y);
+nnb_status launch_tc_dx(nnb_engine* e, const __nv_bfloat16* dyb, const __nv_bfloat16* wb, size_t t, size_t k, size_t out,
+                        float* dx, bool accumulate);
+nnb_status launch_tc_dw(nnb_engine* e, const __nv_bfloat16* dyb, const __nv_bfloat16* xs, size_t t, size_t k, size_t out,
+                        float* dw);
+nnb_status tc_check_errors(nnb_engine* e);
+nnb_status launch_expand_weights(nnb_engine* e, const uint32_t* wq, size_t rows, size_t k, int8_t* w8, __nv_bfloat16* wb);
+nnb_status launch_scale_to_bf16(nnb_engine* e, const float* dy, const float* tau, size_t t, size_t out, __nv_bfloat16* dyb);
+nnb_status launch_dequant_to_bf16(nnb_engine* e, const int8_t* q, const float* s, size_t t, size_t k, __nv_bfloat16* xs);
 
 }  // namespace nnb

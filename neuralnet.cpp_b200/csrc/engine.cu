@@ -36,6 +36,8 @@ nnb_status nnb_engine::ensure_scratch(size_t bytes)
                  cudaGetErrorString(err));
     }
     scratch_bytes = want;
+    tc_flag_cleared = false;
+    NNB_CUDA(cudaMemsetAsync(scratch, 0, 4096, stream));
     return NNB_OK;
 }
 

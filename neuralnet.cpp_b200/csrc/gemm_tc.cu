@@ -1,0 +1,510 @@
+// gemm_tc.cu — the Blackwell tensor-core GEMM of the engine: TMA-fed tcgen05.mma with the
+// accumulator in tensor memory, persistent over output tiles.
+//
+// One kernel template serves the three large GEMMs of a ternary linear
+// (include/neuralnet.cpp/compute_layer_bitlinear.hpp:454, 494, 514-534):
+//   forward  y[t,o]  = (tau_o*s_t) * sum_k q[t,k]*trit[o,k] (+bias, +residual)   kind::i8, int32 accum
+//   dX       dx[t,k] (+)= sum_o dyb[t,o] * trit[o,k]                              kind::f16 (bf16), f32 accum
+//   dW       dw[o,k] += sum_t dyb[t,o] * xs[t,k]                                  kind::f16 (bf16), f32 accum
+// with dyb = bf16(dy*tau) and xs = bf16(s*q) prepared by small elementwise kernels, and the ternary
+// weights expanded once per requantisation to int8 (K permuted like q) and to bf16.
+//
+// Roles inside a CTA (192 threads): warp 0 issues TMA loads into a 4-stage shared-memory ring,
+// warp 1 issues tcgen05.mma (one thread) and owns the TMEM allocation, warps 2-5 drain the
+// accumulator (tcgen05.ld) through the epilogue.  Two 256-column accumulators let the epilogue of one
+// tile overlap the main loop of the next.  Every mbarrier wait is bounded: on expiry the kernel raises
+// an error flag and all roles leave their loops, TMEM is released, and the host reports NNB_ERR_TIMEOUT.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "device_math.cuh"
+
+namespace nnb {
+namespace tc {
+
+constexpr int BM = 128, BN = 256, STAGES = 4;
+constexpr int STAGE_A = BM * 128, STAGE_B = BN * 128;  // bytes: 128 B of K (or 64 k-rows x 128 B) per row
+constexpr int STAGE_BYTES = STAGE_A + STAGE_B;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int THREADS = 192;
+constexpr uint32_t SPIN_LIMIT = 1u << 24;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+// bounded wait: false when the limit was reached (the caller then raises the error flag and leaves)
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag)
+{
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t it = 0; it < SPIN_LIMIT; ++it) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}\n"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+        if ((it & 1023) == 1023 && *abort_flag) return false;
+    }
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* tm, uint64_t* bar, int c0, int c1)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(tm)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+        : "memory");
+}
+
+// shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor version 1
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+template <int KIND>
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
+{
+    if (KIND == 0) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}\n"
+            ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}\n"
+            ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+    }
+}
+
+__device__ __forceinline__ void umma_commit(uint64_t* bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+
+struct Epi {
+    // forward: y = (tau[n]*s[m])*acc (+bias[n]) (+residual[m,n]);  dX: c (+)= acc;  dW: c += acc
+    float* out;
+    const float* tau;
+    const float* s;
+    const float* bias;
+    const float* residual;
+    int accumulate;
+};
+
+// KIND 0: int8 (A, B K-major, 128 k per stage).  KIND 1: bf16 (64 k per stage), A/B K- or MN-major.
+// EPI 0: forward, 1: plain store/accumulate.
+template <int KIND, bool A_MN, bool B_MN, int EPI>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Epi ep, int M, int N,
+               int KC, int* __restrict__ err)
+{
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+    uint64_t* full = bars;                 // [STAGES] TMA -> MMA
+    uint64_t* empty = bars + STAGES;       // [STAGES] MMA -> TMA
+    uint64_t* acc_full = bars + 2 * STAGES;      // [2] MMA -> epilogue
+    uint64_t* acc_empty = bars + 2 * STAGES + 2; // [2] epilogue -> MMA
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    volatile int* abort_flag = err;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int KE = KIND == 0 ? 128 : 64;  // contraction elements per stage
+    const int ktiles = (KC + KE - 1) / KE;
+    const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+    const int n_tiles = tiles_m * tiles_n;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < STAGES; ++i) {
+            mbar_init(&full[i], 1);
+            mbar_init(&empty[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&acc_full[i], 1);
+            mbar_init(&acc_empty[i], 4);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+                const int tm = tile / tiles_n, tn = tile % tiles_n;
+                for (int kt = 0; kt < ktiles && ok; ++kt, ++it) {
+                    const int st = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (it >= STAGES && !mbar_wait(&empty[st], ph ^ 1, abort_flag)) { ok = false; break; }
+                    unsigned char* sa = smem + st * STAGE_BYTES;
+                    unsigned char* sb = sa + STAGE_A;
+                    mbar_expect_tx(&full[st], STAGE_BYTES);
+                    if (!A_MN) {
+                        tma_load_2d(sa, &tmA, &full[st], kt * KE, tm * BM);
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < BM / 64; ++c) tma_load_2d(sa + c * 8192, &tmA, &full[st], tm * BM + c * 64, kt * KE);
+                    }
+                    if (!B_MN) {
+                        tma_load_2d(sb, &tmB, &full[st], kt * KE, tn * BN);
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < BN / 64; ++c) tma_load_2d(sb + c * 8192, &tmB, &full[st], tn * BN + c * 64, kt * KE);
+                    }
+                }
+            }
+            if (!ok) atomicExch(err, 1);
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = (KIND == 0 ? (2u << 4) | (1u << 7) | (1u << 10) : (1u << 4) | (1u << 7) | (1u << 10)) |
+                                       ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) |
+                                       ((uint32_t)(BM >> 4) << 24);
+            uint32_t it = 0, tcount = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++tcount) {
+                const int acc = tcount & 1;
+                if (tcount >= 2 && !mbar_wait(&acc_empty[acc], ((tcount >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kt = 0; kt < ktiles; ++kt, ++it) {
+                    const int st = it % STAGES;
+                    if (!mbar_wait(&full[st], (it / STAGES) & 1, abort_flag)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                    const uint32_t sa = smem_u32(smem + st * STAGE_BYTES), sb = sa + STAGE_A;
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks) {
+                        // K-major: 32 bytes of K per instruction inside the 128-byte swizzle row;
+                        // MN-major: 16 k-rows of 128 bytes per instruction
+                        const uint64_t ad = A_MN ? make_desc(sa + ks * 2048, 8192, 1024) : make_desc(sa + ks * 32, 16, 1024);
+                        const uint64_t bd = B_MN ? make_desc(sb + ks * 2048, 8192, 1024) : make_desc(sb + ks * 32, 16, 1024);
+                        umma<KIND>(d_tmem, ad, bd, idesc, (kt > 0 || ks > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&empty[st]);
+                }
+                if (ok) umma_commit(&acc_full[acc]);
+            }
+            if (!ok) atomicExch(err, 1);
+        }
+    } else {
+        // ---------------- epilogue: warps 2..5, TMEM lane quarter = warp % 4
+        const int quarter = warp & 3;
+        uint32_t tcount = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++tcount) {
+            const int tm = tile / tiles_n, tn = tile % tiles_n;
+            const int acc = tcount & 1;
+            if (!mbar_wait(&acc_full[acc], (tcount >> 1) & 1, abort_flag)) { ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const int row = tm * BM + quarter * 32 + lane;
+            const float srow = (EPI == 0 && row < M) ? ep.s[row] : 0.0f;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + c0, r);
+                const int col0 = tn * BN + c0;
+                if (row < M && col0 < N) {
+                    float* dst = ep.out + (size_t)row * N + col0;
+                    const bool vec = (col0 + 32 <= N) && ((N & 3) == 0);
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int col = col0 + j;
+                        if (EPI == 0) {
+                            float x = 0.0f;
+                            if (col < N) {
+                                x = __fmul_rn(__fmul_rn(ep.tau[col], srow), (float)(int)r[j]);
+                                if (ep.bias) x = __fadd_rn(x, ep.bias[col]);
+                                if (ep.residual) x = __fadd_rn(ep.residual[(size_t)row * N + col], x);
+                            }
+                            v[j] = x;
+                        } else {
+                            v[j] = __uint_as_float(r[j]);
+                        }
+                    }
+                    if (vec) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                            if (EPI == 1 && ep.accumulate) {
+                                const float4 old = *reinterpret_cast<const float4*>(dst + j);
+                                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                            }
+                            *reinterpret_cast<float4*>(dst + j) = o;
+                        }
+                    } else {
+                        for (int j = 0; j < 32; ++j)
+                            if (col0 + j < N) dst[j] = (EPI == 1 && ep.accumulate) ? dst[j] + v[j] : v[j];
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[acc]);
+        }
+        if (!ok && lane == 0) atomicExch(err, 1);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// 2-D row-major matrix (rows, cols) of `esize`-byte elements; box = (box_cols, box_rows), 128-byte swizzle
+static nnb_status make_map(CUtensorMap* tm, const void* base, CUtensorMapDataType dt, size_t esize, size_t rows, size_t cols,
+                           uint32_t box_cols, uint32_t box_rows)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) NNB_FAIL(NNB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    NNB_REQUIRE(((uintptr_t)base & 15) == 0 && (cols * esize) % 16 == 0,
+                "tensor-core GEMM operand must be 16-byte aligned with a row pitch that is a multiple of 16 bytes");
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {cols * esize};
+    cuuint32_t box[2] = {box_cols, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(tm, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) NNB_FAIL(NNB_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return NNB_OK;
+}
+
+static nnb_status err_flag(nnb_engine* e, int** flag)
+{
+    // the flag lives at the end of the first scratch page (the accumulator block of rl.cu uses its start)
+    NNB_TRY(e->ensure_scratch(4096));
+    *flag = reinterpret_cast<int*>((char*)e->scratch + 4000);
+    return NNB_OK;
+}
+
+template <int KIND, bool A_MN, bool B_MN, int EPI>
+static nnb_status launch(nnb_engine* e, const CUtensorMap& ta, const CUtensorMap& tb, const Epi& ep, size_t M, size_t N, size_t KC)
+{
+    auto kern = gemm_tc_kernel<KIND, A_MN, B_MN, EPI>;
+    static bool cfg = false;
+    if (!cfg) {
+        NNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        cfg = true;
+    }
+    int* flag;
+    NNB_TRY(err_flag(e, &flag));
+    if (!e->tc_flag_cleared) {
+        NNB_CUDA(cudaMemsetAsync(flag, 0, sizeof(int), e->stream));
+        e->tc_flag_cleared = true;
+    }
+    const size_t tiles = ceil_div(M, BM) * ceil_div(N, BN);
+    const unsigned grid = (unsigned)(tiles < (size_t)e->sm_count ? tiles : (size_t)e->sm_count);
+    kern<<<grid, THREADS, SMEM_BYTES, e->stream>>>(ta, tb, ep, (int)M, (int)N, (int)KC, flag);
+    e->launches++;
+    NNB_CHECK_LAUNCH("gemm_tc_kernel");
+    return NNB_OK;
+}
+
+}  // namespace tc
+
+// forward: q (T,K) permuted int8, w8 (OUT,K) int8 trits in the same K permutation
+nnb_status launch_tc_forward(nnb_engine* e, const int8_t* q, const int8_t* w8, const float* tau, const float* s,
+                             const float* bias, const float* residual, size_t t, size_t k, size_t out, float* y)
+{
+    using namespace tc;
+    CUtensorMap ta, tb;
+    NNB_TRY(make_map(&ta, q, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, t, k, 128, BM));
+    NNB_TRY(make_map(&tb, w8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, out, k, 128, BN));
+    Epi ep{y, tau, s, bias, residual, 0};
+    return launch<0, false, false, 0>(e, ta, tb, ep, t, out, k);
+}
+
+// dX: dyb (T,OUT) bf16, wb (OUT,K) bf16 trits; dx (T,K) f32
+nnb_status launch_tc_dx(nnb_engine* e, const __nv_bfloat16* dyb, const __nv_bfloat16* wb, size_t t, size_t k, size_t out,
+                        float* dx, bool accumulate)
+{
+    using namespace tc;
+    CUtensorMap ta, tb;
+    NNB_TRY(make_map(&ta, dyb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, t, out, 64, BM));
+    NNB_TRY(make_map(&tb, wb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, out, k, 64, 64));
+    Epi ep{dx, nullptr, nullptr, nullptr, nullptr, accumulate ? 1 : 0};
+    return launch<1, false, true, 1>(e, ta, tb, ep, t, k, out);
+}
+
+// dW: dyb (T,OUT) bf16, xs (T,K) bf16; dw (OUT,K) f32 +=
+nnb_status launch_tc_dw(nnb_engine* e, const __nv_bfloat16* dyb, const __nv_bfloat16* xs, size_t t, size_t k, size_t out,
+                        float* dw)
+{
+    using namespace tc;
+    CUtensorMap ta, tb;
+    NNB_TRY(make_map(&ta, dyb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, t, out, 64, 64));
+    NNB_TRY(make_map(&tb, xs, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, t, k, 64, 64));
+    Epi ep{dw, nullptr, nullptr, nullptr, nullptr, 1};
+    return launch<1, true, true, 1>(e, ta, tb, ep, out, k, t);
+}
+
+// reads (and clears) the device error flag of the tensor-core GEMMs; synchronises the stream
+nnb_status tc_check_errors(nnb_engine* e)
+{
+    if (!e->scratch) return NNB_OK;
+    int h = 0;
+    int* flag = reinterpret_cast<int*>((char*)e->scratch + 4000);
+    NNB_CUDA(cudaMemcpyAsync(&h, flag, sizeof(int), cudaMemcpyDeviceToHost, e->stream));
+    NNB_CUDA(cudaStreamSynchronize(e->stream));
+    if (h) {
+        NNB_CUDA(cudaMemsetAsync(flag, 0, sizeof(int), e->stream));
+        NNB_FAIL(NNB_ERR_TIMEOUT, "a tensor-core GEMM gave up on a bounded barrier wait");
+    }
+    return NNB_OK;
+}
+
+// ------------------------------------------------------------- operand preparation
+// ternary container -> int8 trits with K permuted per 64-block like q, and bf16 trits in natural order
+__global__ void expand_weights_kernel(const uint32_t* __restrict__ wq, size_t n_words, int8_t* __restrict__ w8,
+                                      __nv_bfloat16* __restrict__ wb)
+{
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n_words) return;
+    const uint32_t w = wq[idx];
+    if (w8) {
+        // word t of its 64-block: masked register i = trits {i, 4+i, 8+i, 12+i} -> bytes [16i + 4t, +4)
+        const size_t blk = idx >> 2;
+        const int t = (int)(idx & 3);
+        uint32_t* dst = reinterpret_cast<uint32_t*>(w8 + blk * 64);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t codes = (w >> (2 * i)) & 0x03030303u;
+            dst[4 * i + t] = __vsub4(codes, 0x02020202u);
+        }
+    }
+    if (wb) {
+        uint32_t o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t c0 = (w >> (4 * i)) & 3u, c1 = (w >> (4 * i + 2)) & 3u;
+            const uint32_t lo = c0 == 3u ? 0x3F80u : (c0 == 1u ? 0xBF80u : 0u);
+            const uint32_t hi = c1 == 3u ? 0x3F80u : (c1 == 1u ? 0xBF80u : 0u);
+            o[i] = lo | (hi << 16);
+        }
+        uint4* d = reinterpret_cast<uint4*>(wb + idx * 16);
+        d[0] = make_uint4(o[0], o[1], o[2], o[3]);
+        d[1] = make_uint4(o[4], o[5], o[6], o[7]);
+    }
+}
+
+nnb_status launch_expand_weights(nnb_engine* e, const uint32_t* wq, size_t rows, size_t k, int8_t* w8, __nv_bfloat16* wb)
+{
+    const size_t n_words = rows * (k / 16);
+    expand_weights_kernel<<<(unsigned)ceil_div(n_words, 256), 256, 0, e->stream>>>(wq, n_words, w8, wb);
+    e->launches++;
+    NNB_CHECK_LAUNCH("expand_weights_kernel");
+    return NNB_OK;
+}
+
+// dyb[t,o] = bf16(dy[t,o] * tau[o])
+__global__ void scale_to_bf16_kernel(const float* __restrict__ dy, const float* __restrict__ tau, size_t n, int O,
+                                     __nv_bfloat16* __restrict__ out)
+{
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 2;
+    if (i >= n) return;
+    const int o = (int)(i % O);
+    const float a = dy[i] * tau[o];
+    const float b = (i + 1 < n) ? dy[i + 1] * tau[(o + 1) % O] : 0.0f;
+    *reinterpret_cast<__nv_bfloat162*>(out + i) = __floats2bfloat162_rn(a, b);
+}
+
+// xs[t,k] = bf16(s[t] * q[t, perm(k)]) in natural feature order
+__global__ void dequant_to_bf16_kernel(const int8_t* __restrict__ q, const float* __restrict__ s, size_t T, int K,
+                                       __nv_bfloat16* __restrict__ out)
+{
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // one 32-bit word of q
+    if (idx >= T * (size_t)(K / 4)) return;
+    const size_t t = idx / (K / 4);
+    const int w = (int)(idx % (K / 4));
+    const int blk = w >> 4, wd = w & 15, i = wd >> 2, tt = wd & 3;  // dest word 4i+tt holds src 16tt + 4b + i
+    const uint32_t word = reinterpret_cast<const uint32_t*>(q + t * K)[w];
+    const float sc = s[t];
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        const float v = (float)(int8_t)((word >> (8 * b)) & 0xFFu) * sc;
+        out[t * K + blk * 64 + 16 * tt + 4 * b + i] = __float2bfloat16_rn(v);
+    }
+}
+
+nnb_status launch_scale_to_bf16(nnb_engine* e, const float* dy, const float* tau, size_t t, size_t out, __nv_bfloat16* dyb)
+{
+    NNB_REQUIRE(out % 2 == 0, "scale_to_bf16: out=%zu must be even", out);
+    const size_t n = t * out;
+    scale_to_bf16_kernel<<<(unsigned)ceil_div(n / 2, 256), 256, 0, e->stream>>>(dy, tau, n, (int)out, dyb);
+    e->launches++;
+    NNB_CHECK_LAUNCH("scale_to_bf16_kernel");
+    return NNB_OK;
+}
+
+nnb_status launch_dequant_to_bf16(nnb_engine* e, const int8_t* q, const float* s, size_t t, size_t k, __nv_bfloat16* xs)
+{
+    dequant_to_bf16_kernel<<<(unsigned)ceil_div(t * (k / 4), 256), 256, 0, e->stream>>>(q, s, t, (int)k, xs);
+    e->launches++;
+    NNB_CHECK_LAUNCH("dequant_to_bf16_kernel");
+    return NNB_OK;
+}
+
+}  // namespace nnb

@@ -113,8 +113,49 @@ static nnb_status requantize_linear(nnb_policy* p, const LinW& l)
     return launch_trit_pack(p->e, p->params + l.w_off, tau, l.out, l.in, p->packed + l.packed_off);
 }
 
+static nnb_status expand_all(nnb_policy* p, bool want_w8, bool want_wb)
+{
+    // one launch over the whole container arena: every matrix starts on a 64-feature block boundary
+    return launch_expand_weights(p->e, p->packed, 1, p->packed_words * 16, want_w8 ? p->w8 : nullptr,
+                                 want_wb ? p->wb : nullptr);
+}
+
+nnb_status policy_ensure_wb(nnb_policy* p)
+{
+    if (p->cfg.exact) return NNB_OK;
+    if (!p->wb) {
+        cudaError_t er = cudaMalloc((void**)&p->wb, p->packed_words * 16 * sizeof(__nv_bfloat16));
+        if (er != cudaSuccess) {
+            cudaGetLastError();
+            NNB_FAIL(NNB_ERR_OOM, "out of device memory for the bf16 weight copy");
+        }
+        p->wb_valid = false;
+    }
+    if (!p->wb_valid) {
+        NNB_TRY(expand_all(p, false, true));
+        p->wb_valid = true;
+    }
+    return NNB_OK;
+}
+
+nnb_status policy_linear_fwd(nnb_policy* p, const LinW& l, size_t n_mats, const int8_t* q, const float* s,
+                             const int32_t* qsum, size_t T, const float* residual, float* y, size_t y_stride)
+{
+    if (!p->cfg.exact && p->w8 && T >= 64) {
+        for (size_t m = 0; m < n_mats; ++m)
+            NNB_TRY(launch_tc_forward(p->e, q, p->w8 + (l.packed_off + m * l.out * (l.in / 16)) * 16,
+                                      p->tau + l.tau_off + m * l.out, s, p->params + l.b_off + m * l.out, residual, T,
+                                      l.in, l.out, y + m * y_stride));
+        return NNB_OK;
+    }
+    return launch_bitlinear_fwd_tm(p->e, p->packed + l.packed_off, n_mats > 1 ? l.out * (l.in / 16) : 0, p->tau + l.tau_off,
+                                   p->params + l.b_off, residual, q, s, qsum, n_mats, T, l.in, l.out, y, y_stride, NNB_F32,
+                                   nullptr);
+}
+
 nnb_status policy_requantize(nnb_policy* p)
 {
+    p->wb_valid = false;
     for (auto& L : p->layers) {
         NNB_TRY(requantize_linear(p, L.q));
         NNB_TRY(requantize_linear(p, L.k));
@@ -123,7 +164,19 @@ nnb_status policy_requantize(nnb_policy* p)
         NNB_TRY(requantize_linear(p, L.fc1));
         NNB_TRY(requantize_linear(p, L.fc2));
     }
-    return requantize_linear(p, p->head);
+    NNB_TRY(requantize_linear(p, p->head));
+    if (!p->cfg.exact) {
+        if (!p->w8) {
+            cudaError_t er = cudaMalloc((void**)&p->w8, p->packed_words * 16);
+            if (er != cudaSuccess) {
+                cudaGetLastError();
+                NNB_FAIL(NNB_ERR_OOM, "out of device memory for the int8 weight copy");
+            }
+        }
+        NNB_TRY(expand_all(p, true, p->wb != nullptr));
+        p->wb_valid = p->wb != nullptr;
+    }
+    return NNB_OK;
 }
 
 static void free_decode(nnb_policy* p)
@@ -202,31 +255,21 @@ static nnb_status decode_step(nnb_policy* p, bool with_head, float temperature, 
         const LayerW& L = p->layers[l];
         NNB_TRY(launch_row_quant(e, 0, exact, w.x, P + L.ln1_g, B, d, d, w.q8, w.s, w.qsum, nullptr));
         // q, k, v projections: three equally shaped matrices stored back to back, one launch
-        NNB_TRY(launch_bitlinear_fwd_tm(e, p->packed + L.q.packed_off, d * (d / 16), p->tau + L.q.tau_off,
-                                        P + L.q.b_off, nullptr, w.q8, w.s, w.qsum, 3, B, d, d, w.qkv,
-                                        B * d, NNB_F32, nullptr));
+        NNB_TRY(policy_linear_fwd(p, L.q, 3, w.q8, w.s, w.qsum, B, nullptr, w.qkv, B * d));
         NNB_TRY(launch_attn_decode(e, exact, w.qkv, (char*)w.k + (size_t)l * layer_kv,
                                    (char*)w.v + (size_t)l * layer_kv, p->rope_cos, p->rope_sin, w.d_pos, B,
                                    H, dk, w.ctx_alloc, w.att));
         NNB_TRY(launch_row_quant(e, 3, exact, w.att, nullptr, B, d, d, w.q8, w.s, w.qsum, nullptr));
-        NNB_TRY(launch_bitlinear_fwd_tm(e, p->packed + L.o.packed_off, 0, p->tau + L.o.tau_off,
-                                        P + L.o.b_off, w.x, w.q8, w.s, w.qsum, 1, B, d, d, w.x, 0, NNB_F32,
-                                        nullptr));
+        NNB_TRY(policy_linear_fwd(p, L.o, 1, w.q8, w.s, w.qsum, B, w.x, w.x, 0));
         NNB_TRY(launch_row_quant(e, 0, exact, w.x, P + L.ln2_g, B, d, d, w.q8, w.s, w.qsum, nullptr));
-        NNB_TRY(launch_bitlinear_fwd_tm(e, p->packed + L.fc1.packed_off, 0, p->tau + L.fc1.tau_off,
-                                        P + L.fc1.b_off, nullptr, w.q8, w.s, w.qsum, 1, B, d, F1, w.h1, 0,
-                                        NNB_F32, nullptr));
+        NNB_TRY(policy_linear_fwd(p, L.fc1, 1, w.q8, w.s, w.qsum, B, nullptr, w.h1, 0));
         NNB_TRY(launch_row_quant(e, c.act == 1 ? 2 : 1, exact, w.h1, nullptr, B, F, F1, w.q8, w.s, w.qsum,
                                  nullptr));
-        NNB_TRY(launch_bitlinear_fwd_tm(e, p->packed + L.fc2.packed_off, 0, p->tau + L.fc2.tau_off,
-                                        P + L.fc2.b_off, w.x, w.q8, w.s, w.qsum, 1, B, F, d, w.x, 0, NNB_F32,
-                                        nullptr));
+        NNB_TRY(policy_linear_fwd(p, L.fc2, 1, w.q8, w.s, w.qsum, B, w.x, w.x, 0));
     }
     if (with_head) {
         NNB_TRY(launch_row_quant(e, 0, exact, w.x, P + p->lnf_g, B, d, d, w.q8, w.s, w.qsum, nullptr));
-        NNB_TRY(launch_bitlinear_fwd_tm(e, p->packed + p->head.packed_off, 0, p->tau + p->head.tau_off,
-                                        P + p->head.b_off, nullptr, w.q8, w.s, w.qsum, 1, B, d, V, w.logits,
-                                        0, NNB_F32, nullptr));
+        NNB_TRY(policy_linear_fwd(p, p->head, 1, w.q8, w.s, w.qsum, B, nullptr, w.logits, 0));
         NNB_TRY(launch_sample(e, exact, w.logits, B, V, temperature, top_k, seed, seq0, w.d_pos, prompt_len,
                               w.tokens, w.ctx_alloc, want_logp ? w.logp : nullptr, w.ctx_alloc, nullptr));
     }
@@ -333,7 +376,7 @@ void nnb_policy_destroy(nnb_policy* p)
     cudaStreamSynchronize(p->e->stream);
     free_decode(p);
     policy_free_train(p);
-    void* ptrs[] = {p->params, p->grads, p->adam_m, p->adam_v, p->packed, p->tau, p->rope_cos, p->rope_sin};
+    void* ptrs[] = {p->params, p->grads, p->adam_m, p->adam_v, p->packed, p->tau, p->rope_cos, p->rope_sin, p->w8, p->wb};
     for (void* q : ptrs)
         if (q) cudaFree(q);
     delete p;

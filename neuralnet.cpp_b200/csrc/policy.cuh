@@ -48,6 +48,9 @@ struct nnb_policy {
     float* adam_v = nullptr;
     int adam_t = 0;  // optimizer steps taken
     uint32_t* packed = nullptr;
+    int8_t* w8 = nullptr;           // fast mode: int8 trits, K permuted like the activations (tcgen05 forward)
+    __nv_bfloat16* wb = nullptr;    // fast mode, trainable policies: bf16 trits (tcgen05 dX)
+    bool wb_valid = false;
     float* tau = nullptr;
     float *rope_cos = nullptr, *rope_sin = nullptr;  // (ctx, dk/2)
     size_t tok_emb = 0, pos_emb = 0, lnf_g = 0, value_w = 0, value_b = 0;
@@ -62,4 +65,8 @@ namespace nnb {
 nnb_status policy_requantize(nnb_policy* p);
 void policy_free_train(nnb_policy* p);
 void policy_free_decode(nnb_policy* p);
+nnb_status policy_ensure_wb(nnb_policy* p);
+// y = [residual +] linear(q) through the fastest kernel for this mode and token count
+nnb_status policy_linear_fwd(nnb_policy* p, const LinW& l, size_t n_mats, const int8_t* q, const float* s,
+                             const int32_t* qsum, size_t T, const float* residual, float* y, size_t y_stride);
 }  // namespace nnb

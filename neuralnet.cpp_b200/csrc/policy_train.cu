@@ -39,6 +39,7 @@ struct TrainWs {
     // backward temporaries
     float *g = nullptr, *g2 = nullptr, *dn = nullptr, *datt = nullptr, *dqkv = nullptr, *da = nullptr, *dh1 = nullptr,
           *delta = nullptr;
+    __nv_bfloat16 *dyb = nullptr, *xs = nullptr;  // bf16 operand scratch of the tcgen05 backward GEMMs
 };
 
 void policy_free_train(nnb_policy* p)
@@ -117,6 +118,11 @@ static nnb_status ensure_train(nnb_policy* p, size_t n_seq, size_t S, size_t P, 
             w->da = (float*)take(T * F * 4);
             w->dh1 = (float*)take(T * F1 * 4);
             w->delta = (float*)take(n_seq * H * S * 4);
+            if (!c.exact) {
+                const size_t dyb_elems = T * F1 > Td * V ? T * F1 : Td * V;
+                w->dyb = (__nv_bfloat16*)take(dyb_elems * 2);
+                w->xs = (__nv_bfloat16*)take(T * (F > d ? F : d) * 2);
+            }
         }
         if (pass == 0) {
             size_t free_b = 0, total_b = 0;
@@ -154,9 +160,7 @@ __global__ void gather_actions_kernel(const int32_t* __restrict__ tokens, int S,
 static nnb_status lin_fwd(nnb_policy* p, const LinW& l, size_t n_mats, const int8_t* q, const float* s,
                           const int32_t* qsum, size_t T, const float* residual, float* y, size_t y_stride)
 {
-    return launch_bitlinear_fwd_tm(p->e, p->packed + l.packed_off, n_mats > 1 ? l.out * (l.in / 16) : 0,
-                                   p->tau + l.tau_off, p->params + l.b_off, residual, q, s, qsum, n_mats, T, l.in, l.out,
-                                   y, y_stride, NNB_F32, nullptr);
+    return policy_linear_fwd(p, l, n_mats, q, s, qsum, T, residual, y, y_stride);
 }
 
 // teacher-forced forward of n_seq sequences; fills w->logp / w->ent / w->value for the decisions
@@ -207,6 +211,15 @@ static nnb_status lin_bwd(nnb_policy* p, const LinW& l, const float* dy, const i
 {
     nnb_engine* e = p->e;
     const bool exact = p->cfg.exact != 0;
+    TrainWs* w = (TrainWs*)p->train;
+    if (!exact && p->wb && p->wb_valid && l.out % 8 == 0 && T >= 64) {
+        // tcgen05 path: dyb = bf16(dy*tau) serves both GEMMs, xs = bf16(s*q) in natural feature order
+        NNB_TRY(launch_scale_to_bf16(e, dy, p->tau + l.tau_off, T, l.out, w->dyb));
+        if (dx) NNB_TRY(launch_tc_dx(e, w->dyb, p->wb + l.packed_off * 16, T, l.in, l.out, dx, accumulate_dx));
+        NNB_TRY(launch_dequant_to_bf16(e, q, s, T, l.in, w->xs));
+        NNB_TRY(launch_tc_dw(e, w->dyb, w->xs, T, l.in, l.out, p->grads + l.w_off));
+        return launch_colsum_add(e, dy, T, l.out, p->grads + l.b_off);
+    }
     if (dx) NNB_TRY(launch_bitlinear_dx(e, exact, dy, p->packed + l.packed_off, p->tau + l.tau_off, T, l.in, l.out, dx, accumulate_dx));
     NNB_TRY(launch_bitlinear_dw(e, exact, dy, q, s, p->tau + l.tau_off, T, l.in, l.out, p->grads + l.w_off));
     return launch_colsum_add(e, dy, T, l.out, p->grads + l.b_off);
@@ -312,6 +325,7 @@ nnb_status nnb_policy_train_step(nnb_policy* p, const int32_t* d_tokens, size_t 
     NNB_REQUIRE(!use_value || (p->cfg.value_head && obj->d_returns && obj->d_old_value),
                 "train_step: the value term needs a value head, returns and old values");
     NNB_TRY(ensure_train(p, n_seq, seq_len, prompt_len, true));
+    NNB_TRY(policy_ensure_wb(p));
     nnb_engine* e = p->e;
     TrainWs* w = (TrainWs*)p->train;
     const size_t Td = n_seq * (seq_len - prompt_len), V = p->cfg.vocab;
@@ -358,7 +372,8 @@ nnb_status nnb_policy_optimizer_step(nnb_policy* p, float lr, float beta1, float
     NNB_TRY(launch_adamw(e, p->params, p->grads, p->adam_m, p->adam_v, p->n_params, lr, beta1, beta2, eps, weight_decay,
                          p->adam_t));
     NNB_CUDA(cudaMemsetAsync(p->grads, 0, p->n_params * 4, e->stream));
-    return policy_requantize(p);
+    NNB_TRY(policy_requantize(p));
+    return p->cfg.exact ? NNB_OK : tc_check_errors(e);
 }
 
 nnb_status nnb_policy_release_workspaces(nnb_policy* p)

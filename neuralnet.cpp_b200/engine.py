@@ -286,3 +286,43 @@ def bitlinear_dw_tm(self, dy, q, s, tau, dw, exact=True):
 
 Engine.bitlinear_dx_tm = bitlinear_dx_tm
 Engine.bitlinear_dw_tm = bitlinear_dw_tm
+
+
+def expand_weights(self, wq, k, want_bf16=True):
+    """2-bit container (rows, k/16) -> (int8 trits in the engine's K permutation, bf16 trits)."""
+    rows = wq.shape[0]
+    w8 = torch.empty((rows, k), device=self.device, dtype=torch.int8)
+    wb = torch.empty((rows, k), device=self.device, dtype=torch.bfloat16) if want_bf16 else None
+    check(self._lib.nnb_expand_weights(self._h, _ptr(wq), rows, k, _ptr(w8), _ptr(wb)))
+    return w8, wb
+
+
+def bitlinear_fwd_tc(self, w8, tau, bias, q, s, residual=None, y=None):
+    t, k = q.shape
+    out = w8.shape[0]
+    if y is None:
+        y = torch.empty((t, out), device=self.device, dtype=torch.float32)
+    check(self._lib.nnb_bitlinear_fwd_tc(self._h, _ptr(w8), _ptr(tau), _ptr(bias), _ptr(residual), _ptr(q), _ptr(s), t, k,
+                                         out, _ptr(y)))
+    return y
+
+
+def bitlinear_bwd_tc(self, dy, tau, wb, q, s, k, want_dx=True, dw=None, dx=None, accumulate_dx=False):
+    t, out = dy.shape
+    dyb = torch.empty((t, out), device=self.device, dtype=torch.bfloat16)
+    xs = torch.empty((t, k), device=self.device, dtype=torch.bfloat16) if dw is not None else None
+    if want_dx and dx is None:
+        dx = torch.empty((t, k), device=self.device, dtype=torch.float32)
+    check(self._lib.nnb_bitlinear_bwd_tc(self._h, _ptr(dy), _ptr(tau), _ptr(wb), _ptr(q), _ptr(s), t, k, out, _ptr(dyb),
+                                         _ptr(xs), _ptr(dx) if want_dx else None, int(accumulate_dx), _ptr(dw)))
+    return dx, dw
+
+
+def check_device_errors(self):
+    check(self._lib.nnb_engine_check(self._h))
+
+
+Engine.expand_weights = expand_weights
+Engine.bitlinear_fwd_tc = bitlinear_fwd_tc
+Engine.bitlinear_bwd_tc = bitlinear_bwd_tc
+Engine.check_device_errors = check_device_errors

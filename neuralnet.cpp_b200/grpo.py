@@ -104,10 +104,12 @@ class GrpoTrainer:
                                      ref_logp=None if ref_lp is None else ref_lp[sl].contiguous(),
                                      units=units_global, clip_eps=c.clip_eps, kl_coef=c.kl_coef,
                                      entropy_coef=c.entropy_coef)
+        report[7] = units_global  # every micro-batch reports the global count: it is not a sum
         ev("train")
         if self.world > 1:
             self._allreduce(pol.grads_view())
             self._allreduce(report)
+            report[7] = units_global
         ev("allreduce")
         norm = pol.optimizer_step(c.lr, weight_decay=c.weight_decay, max_grad_norm=c.max_grad_norm)
         ev("optimizer")

@@ -1,0 +1,69 @@
+"""The tcgen05 / TMEM / TMA GEMMs against the CPU oracle and the mma.sync path: the int8 forward
+is bit-exact; the bf16 backward GEMMs are within bf16 rounding of the f64 reference."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev(a, eng):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(eng.device)
+
+
+def _case(orc, t, k, out, seed):
+    rng = np.random.default_rng(seed)
+    W = rng.normal(0, 0.02, (out, k)).astype(np.float32)
+    tau = orc.absmean_tau(W)
+    X = rng.normal(0, 1, (t, k)).astype(np.float32)
+    bias = rng.normal(0, 0.05, out).astype(np.float32)
+    return W, tau, X, bias
+
+
+def test_expand_weights(eng, orc):
+    W, tau, _, _ = _case(orc, 1, 256, 70, 1)
+    packed = orc.trit_pack(W, tau)
+    trit = orc.trit_unpack(packed, 256)
+    w8, wb = eng.expand_weights(_dev(packed.view(np.int32), eng), 256)
+    assert np.array_equal(eng.actq_to_plain(w8).cpu().numpy(), trit)  # same K permutation as the activations
+    assert np.array_equal(wb.float().cpu().numpy(), trit.astype(np.float32))
+
+
+@pytest.mark.parametrize("t,k,out", [(128, 128, 256), (64, 64, 40), (130, 192, 300), (300, 2048, 384), (1000, 320, 1000),
+                                     (2048, 2048, 5632)])
+def test_forward_tc_bit_exact(eng, orc, t, k, out):
+    W, tau, X, bias = _case(orc, t, k, out, t + k + out)
+    packed = orc.trit_pack(W, tau)
+    q_ref, s_ref = orc.act_quant_tm(X)
+    y_ref = orc.bitlinear_i8_tm(packed, tau, bias, q_ref, s_ref, want_acc=False)
+    q, s, qsum = eng.act_quant_tm(_dev(X, eng))
+    w8, _ = eng.expand_weights(_dev(packed.view(np.int32), eng), k, want_bf16=False)
+    y = eng.bitlinear_fwd_tc(w8, _dev(tau, eng), _dev(bias, eng), q, s)
+    eng.check_device_errors()
+    assert np.array_equal(y.cpu().numpy().view(np.uint32), y_ref.view(np.uint32))
+    res = torch.randn((t, out), device=eng.device)
+    y2 = eng.bitlinear_fwd_tc(w8, _dev(tau, eng), _dev(bias, eng), q, s, residual=res)
+    y_mma = eng.bitlinear_fwd_tm(_dev(packed.view(np.int32), eng), _dev(tau, eng), _dev(bias, eng), q, s, qsum)
+    assert torch.equal(y2, res + y_mma)
+
+
+@pytest.mark.parametrize("t,k,out", [(128, 256, 256), (64, 64, 64), (130, 192, 328), (300, 2048, 384), (1000, 320, 1000)])
+def test_backward_tc(eng, orc, t, k, out):
+    W, tau, X, _ = _case(orc, t, k, out, t + 3 * k + out)
+    packed = orc.trit_pack(W, tau)
+    trit = orc.trit_unpack(packed, k).astype(np.float64)
+    q_ref, s_ref = orc.act_quant_tm(X)
+    dY = np.random.default_rng(2).normal(0, 1, (t, out)).astype(np.float32)
+    dx_ref = (dY.astype(np.float64) * tau[None, :]) @ trit
+    dw_ref = ((dY.astype(np.float64) * s_ref[:, None]).T @ q_ref.astype(np.float64)) * tau[:, None]
+    q, s, _ = eng.act_quant_tm(_dev(X, eng))
+    _, wb = eng.expand_weights(_dev(packed.view(np.int32), eng), k)
+    dw = torch.zeros((out, k), device=eng.device)
+    dx, dw = eng.bitlinear_bwd_tc(_dev(dY, eng), _dev(tau, eng), wb, q, s, k, dw=dw)
+    eng.check_device_errors()
+    assert np.abs(dx.cpu().numpy() - dx_ref).max() <= 2e-2 * np.abs(dx_ref).max()
+    assert np.abs(dw.cpu().numpy() - dw_ref).max() <= 2e-2 * np.abs(dw_ref).max()
+    # accumulation
+    dx2, dw2 = eng.bitlinear_bwd_tc(_dev(dY, eng), _dev(tau, eng), wb, q, s, k, dw=dw, dx=dx, accumulate_dx=True)
+    assert np.abs(dx2.cpu().numpy() - 2 * dx_ref).max() <= 2e-2 * 2 * np.abs(dx_ref).max()
+    assert np.abs(dw2.cpu().numpy() - 2 * dw_ref).max() <= 2e-2 * 2 * np.abs(dw_ref).max()
