@@ -250,7 +250,7 @@ static nnb_status backward(nnb_policy* p, const int32_t* tokens, size_t n_seq, s
         NNB_TRY(launch_rmsnorm_bwd(e, s.x_mid, PP + LW.ln2_g, w->dn, w->g, T, d, w->g2, GG + LW.ln2_g));
         // attention branch
         NNB_TRY(lin_bwd(p, LW.o, w->g2, s.q2, s.s2, T, w->datt, false));
-        NNB_TRY(launch_attn_bwd(e, s.qkv, s.qkv + T * d, s.qkv + 2 * T * d, s.att, w->datt, s.lse, w->delta, n_seq, S, H,
+        NNB_TRY(launch_attn_bwd(e, c.exact != 0, s.qkv, s.qkv + T * d, s.qkv + 2 * T * d, s.att, w->datt, s.lse, w->delta, n_seq, S, H,
                                 dk, w->dqkv, w->dqkv + T * d, w->dqkv + 2 * T * d));
         if (c.pos == 1) {
             NNB_TRY(launch_rope(e, w->dqkv, p->rope_cos, p->rope_sin, T, S, H, dk, true));

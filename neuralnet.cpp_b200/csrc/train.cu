@@ -507,6 +507,7 @@ nnb_status launch_attn_fwd(nnb_engine* e, bool exact, const float* q, const floa
                            size_t S, size_t H, size_t dk, float* out, float* lse)
 {
     NNB_REQUIRE(dk <= 128, "attention: head dim %zu > 128", dk);
+    if (!exact && attn_tc_supported(dk, H * dk)) return launch_attn_fwd_tc(e, q, k, v, n_seq, S, H, dk, out, lse);
     const size_t smem = (2 * 32 * (dk + 1) + ATT_WARPS * dk) * sizeof(float);
     static size_t cfg = 0;
     if (smem > cfg) {
@@ -525,7 +526,7 @@ nnb_status launch_attn_fwd(nnb_engine* e, bool exact, const float* q, const floa
     return NNB_OK;
 }
 
-nnb_status launch_attn_bwd(nnb_engine* e, const float* q, const float* k, const float* v, const float* out,
+nnb_status launch_attn_bwd(nnb_engine* e, bool exact, const float* q, const float* k, const float* v, const float* out,
                            const float* dout, const float* lse, float* delta, size_t n_seq, size_t S, size_t H,
                            size_t dk, float* dq, float* dkk, float* dvv)
 {
@@ -534,6 +535,11 @@ nnb_status launch_attn_bwd(nnb_engine* e, const float* q, const float* k, const 
     const size_t rows = n_seq * S;
     attn_bwd_delta_kernel<<<(unsigned)ceil_div(rows * H, 8), 256, 0, e->stream>>>(dout, out, (int)S, (int)H, (int)dk,
                                                                                  rows, delta);
+    if (!exact && attn_tc_supported(dk, H * dk)) {
+        e->launches++;
+        NNB_CHECK_LAUNCH("attn_bwd_delta_kernel");
+        return launch_attn_bwd_tc(e, q, k, v, dout, lse, delta, n_seq, S, H, dk, dq, dkk, dvv);
+    }
     const size_t smem_q = (2 * 32 * (dk + 1) + 2 * ATT_WARPS * dk) * sizeof(float);
     const size_t smem_kv = (2 * 32 * (dk + 1) + 2 * ATT_WARPS * dk + 64) * sizeof(float);
     static size_t cfg_q = 0, cfg_kv = 0;

@@ -204,27 +204,31 @@ def test_tiny_grpo_configuration_step(pkg, eng):
     _grad_check(pol, tr, cfg, pol.grads_view().cpu().numpy().astype(np.float64), g_ref)
 
 
-def test_fast_mode_gradients_are_close(pkg, eng):
-    """bf16 tensor-core backward GEMMs and bf16 KV cache against the exact mode."""
-    kw = dict(n_layer=2, d_model=128, n_head=2, d_ff=256, vocab=531, ctx=40, act=1, pos=1)
+@pytest.mark.parametrize("d,heads,S", [(128, 2, 33), (256, 2, 150), (128, 2, 97)])
+def test_fast_mode_gradients_are_close(pkg, eng, d, heads, S):
+    """bf16 tensor-core attention and backward GEMMs (tcgen05) against the exact mode."""
+    kw = dict(n_layer=2, d_model=d, n_head=heads, d_ff=2 * d, vocab=536, ctx=S + 7, act=1, pos=1)
     cfg_e, cfg_f = pkg.GptConfig(exact=True, **kw), pkg.GptConfig(exact=False, **kw)
     flat = cfg_e.init_params(4, bias_std=0.01)
     pe, pf = pkg.Policy(eng, cfg_e), pkg.Policy(eng, cfg_f)
     pe.upload_params(flat)
     pf.upload_params(flat)
     rng = np.random.default_rng(8)
-    tokens = dev(rng.integers(0, 531, (5, 33)), eng, np.int32)
-    P, G = 9, 24
+    tokens = dev(rng.integers(0, 536, (5, S)), eng, np.int32)
+    P, G = 9, S - 9
     lp, _, _ = pe.logprobs(tokens, P)
     old = lp + dev(rng.normal(0, 0.2, (5, G)), eng)
     adv = dev(rng.normal(0, 1, (5, G)), eng)
     mask = dev(np.ones((5, G)), eng)
+    lp_f, _, _ = pf.logprobs(tokens, P)
+    assert (lp - lp_f).abs().max().item() <= 3e-2 * lp.abs().max().item()
     for pol in (pe, pf):
         pol.zero_grad()
         pol.train_step(tokens, P, mask, old_logp=old, advantage=adv)
+    eng.check_device_errors()
     ge, gf = pe.grads_view().cpu().numpy(), pf.grads_view().cpu().numpy()
     layout, _ = cfg_e.param_layout()
     for name, off, shape in layout:
         size = int(np.prod(shape))
         a, b = ge[off:off + size], gf[off:off + size]
-        assert np.abs(a - b).max() <= 3e-2 * max(np.abs(a).max(), 1e-12), name
+        assert np.abs(a - b).max() <= 5e-2 * max(np.abs(a).max(), 1e-12), name
