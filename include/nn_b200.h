@@ -153,6 +153,16 @@ nnb_status nnb_bitlinear_fwd_tc(nnb_engine* e, const int8_t* d_w8, const float* 
 nnb_status nnb_bitlinear_bwd_tc(nnb_engine* e, const float* d_dy, const float* d_tau, const void* d_wb,
                                 const int8_t* d_q, const float* d_s, size_t t, size_t k, size_t out, void* d_dyb,
                                 void* d_xs, float* d_dx, int accumulate_dx, float* d_dw);
+/* Causal multi-head self-attention over whole sequences, token-major: q, k, v, out, dout and the
+ * gradients are (n_seq*seq_len, n_head*dk) f32 (q, k already rotated), lse and delta (n_seq, n_head, seq_len).
+ * AttentionBase::forward core (include/neuralnet.cpp/compute_layer_attention.hpp:752-828: scale folded into
+ * Q, online-softmax fold) and backward core (:873-960).  exact = 1: f64/f32 CUDA-core path; 0: bf16
+ * tensor cores (head dims 64 and 128, else the CUDA-core path). */
+nnb_status nnb_attention_fwd(nnb_engine* e, const float* d_q, const float* d_k, const float* d_v, size_t n_seq,
+                             size_t seq_len, size_t n_head, size_t dk, int exact, float* d_out, float* d_lse);
+nnb_status nnb_attention_bwd(nnb_engine* e, const float* d_q, const float* d_k, const float* d_v, const float* d_out,
+                             const float* d_dout, const float* d_lse, size_t n_seq, size_t seq_len, size_t n_head,
+                             size_t dk, int exact, float* d_delta, float* d_dq, float* d_dk, float* d_dv);
 /* synchronises and reports NNB_ERR_TIMEOUT if a kernel gave up on a bounded device-side wait */
 nnb_status nnb_engine_check(nnb_engine* e);
 

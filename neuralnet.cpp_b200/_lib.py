@@ -55,6 +55,8 @@ _SIGNATURES = {
     "nnb_bitlinear_fwd_tc": (_I, [_P, _P, _P, _P, _P, _P, _P, _SZ, _SZ, _SZ, _P]),
     "nnb_bitlinear_bwd_tc": (_I, [_P, _P, _P, _P, _P, _P, _SZ, _SZ, _SZ, _P, _P, _P, _I, _P]),
     "nnb_engine_check": (_I, [_P]),
+    "nnb_attention_fwd": (_I, [_P, _P, _P, _P, _SZ, _SZ, _SZ, _SZ, _I, _P, _P]),
+    "nnb_attention_bwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _SZ, _SZ, _SZ, _SZ, _I, _P, _P, _P, _P]),
     "nnb_bitlinear_fwd_host": (_I, [_P, _P, _P, _P, _P, _SZ, _SZ, _SZ, _P]),
     "nnb_policy_create": (_I, [_P, _P, C.POINTER(_P)]),
     "nnb_policy_destroy": (None, [_P]),

@@ -144,6 +144,25 @@ nnb_status nnb_bitlinear_bwd_tc(nnb_engine* e, const float* d_dy, const float* d
     return NNB_OK;
 }
 
+nnb_status nnb_attention_fwd(nnb_engine* e, const float* d_q, const float* d_k, const float* d_v, size_t n_seq,
+                             size_t seq_len, size_t n_head, size_t dk, int exact, float* d_out, float* d_lse)
+{
+    NNB_REQUIRE(e && d_q && d_k && d_v && d_out && d_lse, "attention_fwd: NULL argument");
+    NNB_REQUIRE(n_seq > 0 && seq_len > 0 && n_head > 0 && dk > 0 && dk % 4 == 0, "attention_fwd: bad shape");
+    return launch_attn_fwd(e, exact != 0, d_q, d_k, d_v, n_seq, seq_len, n_head, dk, d_out, d_lse);
+}
+
+nnb_status nnb_attention_bwd(nnb_engine* e, const float* d_q, const float* d_k, const float* d_v, const float* d_out,
+                             const float* d_dout, const float* d_lse, size_t n_seq, size_t seq_len, size_t n_head,
+                             size_t dk, int exact, float* d_delta, float* d_dq, float* d_dk, float* d_dv)
+{
+    NNB_REQUIRE(e && d_q && d_k && d_v && d_out && d_dout && d_lse && d_delta && d_dq && d_dk && d_dv,
+                "attention_bwd: NULL argument");
+    NNB_REQUIRE(n_seq > 0 && seq_len > 0 && n_head > 0 && dk > 0 && dk % 4 == 0, "attention_bwd: bad shape");
+    return launch_attn_bwd(e, exact != 0, d_q, d_k, d_v, d_out, d_dout, d_lse, d_delta, n_seq, seq_len, n_head, dk, d_dq,
+                           d_dk, d_dv);
+}
+
 nnb_status nnb_engine_check(nnb_engine* e)
 {
     NNB_REQUIRE(e, "engine is NULL");

@@ -65,7 +65,7 @@ struct nnb_engine {
     size_t pinned_bytes = 0;
     // counts kernel launches issued through this engine (reported by the benchmark)
     unsigned long long launches = 0;
-    bool tc_flag_cleared = false;  // the tensor-core GEMM error flag in the scratch page has been zeroed
+    int* dev_flags = nullptr;  // small device block: [0] error flag raised by bounded device-side waits
     std::string describe_text;
 
     nnb_status ensure_scratch(size_t bytes);

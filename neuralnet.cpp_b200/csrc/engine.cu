@@ -36,8 +36,6 @@ nnb_status nnb_engine::ensure_scratch(size_t bytes)
                  cudaGetErrorString(err));
     }
     scratch_bytes = want;
-    tc_flag_cleared = false;
-    NNB_CUDA(cudaMemsetAsync(scratch, 0, 4096, stream));
     return NNB_OK;
 }
 
@@ -86,6 +84,12 @@ nnb_status nnb_engine_create(int device, nnb_engine** out)
         NNB_FAIL(NNB_ERR_CUDA, "cudaStreamCreate failed: %s", cudaGetErrorString(err));
     }
     e->stream = e->own_stream;
+    if (cudaMalloc((void**)&e->dev_flags, 256) != cudaSuccess || cudaMemset(e->dev_flags, 0, 256) != cudaSuccess) {
+        cudaGetLastError();
+        cudaStreamDestroy(e->own_stream);
+        delete e;
+        NNB_FAIL(NNB_ERR_OOM, "out of device memory for the engine's flag block");
+    }
     char buf[512];
     snprintf(buf, sizeof(buf),
              "nn-b200 engine on %s (sm_%d%d, %d SMs, %.1f GB): ternary_gemm=true int8_dot=true "
@@ -103,6 +107,7 @@ void nnb_engine_destroy(nnb_engine* e)
     cudaSetDevice(e->device);
     cudaStreamSynchronize(e->stream);
     if (e->scratch) cudaFree(e->scratch);
+    if (e->dev_flags) cudaFree(e->dev_flags);
     if (e->pinned) cudaFreeHost(e->pinned);
     if (e->own_stream) cudaStreamDestroy(e->own_stream);
     delete e;

@@ -332,14 +332,6 @@ static nnb_status make_map(CUtensorMap* tm, const void* base, CUtensorMapDataTyp
     return NNB_OK;
 }
 
-static nnb_status err_flag(nnb_engine* e, int** flag)
-{
-    // the flag lives at the end of the first scratch page (the accumulator block of rl.cu uses its start)
-    NNB_TRY(e->ensure_scratch(4096));
-    *flag = reinterpret_cast<int*>((char*)e->scratch + 4000);
-    return NNB_OK;
-}
-
 template <int KIND, bool A_MN, bool B_MN, int EPI>
 static nnb_status launch(nnb_engine* e, const CUtensorMap& ta, const CUtensorMap& tb, const Epi& ep, size_t M, size_t N, size_t KC)
 {
@@ -349,12 +341,7 @@ static nnb_status launch(nnb_engine* e, const CUtensorMap& ta, const CUtensorMap
         NNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         cfg = true;
     }
-    int* flag;
-    NNB_TRY(err_flag(e, &flag));
-    if (!e->tc_flag_cleared) {
-        NNB_CUDA(cudaMemsetAsync(flag, 0, sizeof(int), e->stream));
-        e->tc_flag_cleared = true;
-    }
+    int* flag = e->dev_flags;
     const size_t tiles = ceil_div(M, BM) * ceil_div(N, BN);
     const unsigned grid = (unsigned)(tiles < (size_t)e->sm_count ? tiles : (size_t)e->sm_count);
     kern<<<grid, THREADS, SMEM_BYTES, e->stream>>>(ta, tb, ep, (int)M, (int)N, (int)KC, flag);
@@ -404,9 +391,8 @@ nnb_status launch_tc_dw(nnb_engine* e, const __nv_bfloat16* dyb, const __nv_bflo
 // reads (and clears) the device error flag of the tensor-core GEMMs; synchronises the stream
 nnb_status tc_check_errors(nnb_engine* e)
 {
-    if (!e->scratch) return NNB_OK;
     int h = 0;
-    int* flag = reinterpret_cast<int*>((char*)e->scratch + 4000);
+    int* flag = e->dev_flags;
     NNB_CUDA(cudaMemcpyAsync(&h, flag, sizeof(int), cudaMemcpyDeviceToHost, e->stream));
     NNB_CUDA(cudaStreamSynchronize(e->stream));
     if (h) {

@@ -326,3 +326,25 @@ Engine.expand_weights = expand_weights
 Engine.bitlinear_fwd_tc = bitlinear_fwd_tc
 Engine.bitlinear_bwd_tc = bitlinear_bwd_tc
 Engine.check_device_errors = check_device_errors
+
+
+def attention_fwd(self, q, k, v, n_seq, seq_len, n_head, exact=True):
+    d = q.shape[1]
+    out = torch.empty_like(q)
+    lse = torch.empty((n_seq, n_head, seq_len), device=self.device, dtype=torch.float32)
+    check(self._lib.nnb_attention_fwd(self._h, _ptr(q), _ptr(k), _ptr(v), n_seq, seq_len, n_head, d // n_head,
+                                      int(exact), _ptr(out), _ptr(lse)))
+    return out, lse
+
+
+def attention_bwd(self, q, k, v, out, dout, lse, n_seq, seq_len, n_head, exact=True):
+    d = q.shape[1]
+    delta = torch.empty_like(lse)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
+    check(self._lib.nnb_attention_bwd(self._h, _ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(dout), _ptr(lse), n_seq, seq_len,
+                                      n_head, d // n_head, int(exact), _ptr(delta), _ptr(dq), _ptr(dk), _ptr(dv)))
+    return dq, dk, dv
+
+
+Engine.attention_fwd = attention_fwd
+Engine.attention_bwd = attention_bwd
