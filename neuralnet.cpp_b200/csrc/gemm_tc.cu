@@ -16,6 +16,9 @@
 // an error flag and all roles leave their loops, TMEM is released, and the host reports NNB_ERR_TIMEOUT.
 #include <cuda.h>
 
+#include <map>
+#include <tuple>
+
 #include "common.cuh"
 #include "device_math.cuh"
 
@@ -314,10 +317,21 @@ static EncodeTiledFn encode_fn()
     return fn;
 }
 
-// 2-D row-major matrix (rows, cols) of `esize`-byte elements; box = (box_cols, box_rows), 128-byte swizzle
+// 2-D row-major matrix (rows, cols) of `esize`-byte elements; box = (box_cols, box_rows), 128-byte swizzle.
+// Encoding a map costs several microseconds of host time, and the same buffers recur step after step,
+// so encoded maps are memoised per thread.
 static nnb_status make_map(CUtensorMap* tm, const void* base, CUtensorMapDataType dt, size_t esize, size_t rows, size_t cols,
                            uint32_t box_cols, uint32_t box_rows)
 {
+    typedef std::tuple<const void*, int, size_t, size_t, uint32_t, uint32_t> Key;
+    static thread_local std::map<Key, CUtensorMap> cache;
+    const Key key(base, (int)dt, rows, cols, box_cols, box_rows);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+        *tm = it->second;
+        return NNB_OK;
+    }
+    if (cache.size() > 8192) cache.clear();
     EncodeTiledFn fn = encode_fn();
     if (!fn) NNB_FAIL(NNB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     NNB_REQUIRE(((uintptr_t)base & 15) == 0 && (cols * esize) % 16 == 0,
@@ -329,6 +343,7 @@ static nnb_status make_map(CUtensorMap* tm, const void* base, CUtensorMapDataTyp
     CUresult r = fn(tm, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) NNB_FAIL(NNB_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    cache[key] = *tm;
     return NNB_OK;
 }
 

@@ -141,7 +141,9 @@ nnb_status policy_ensure_wb(nnb_policy* p)
 nnb_status policy_linear_fwd(nnb_policy* p, const LinW& l, size_t n_mats, const int8_t* q, const float* s,
                              const int32_t* qsum, size_t T, const float* residual, float* y, size_t y_stride)
 {
-    if (!p->cfg.exact && p->w8 && T >= 64) {
+    // below a couple of thousand tokens the 128x256 tcgen05 tiles leave most SMs idle: the mma.sync
+    // kernel with its smaller tiles (and one launch for stacked matrices) is faster there
+    if (!p->cfg.exact && p->w8 && T >= 2048) {
         for (size_t m = 0; m < n_mats; ++m)
             NNB_TRY(launch_tc_forward(p->e, q, p->w8 + (l.packed_off + m * l.out * (l.in / 16)) * 16,
                                       p->tau + l.tau_off + m * l.out, s, p->params + l.b_off + m * l.out, residual, T,
@@ -273,8 +275,17 @@ static nnb_status decode_step(nnb_policy* p, bool with_head, float temperature, 
         NNB_TRY(launch_sample(e, exact, w.logits, B, V, temperature, top_k, seed, seq0, w.d_pos, prompt_len,
                               w.tokens, w.ctx_alloc, want_logp ? w.logp : nullptr, w.ctx_alloc, nullptr));
     }
-    return NNB_OK;
+    return launch_add_int(e, w.d_pos, 1);  // the position lives on the device so a captured step can be replayed
 }
+
+// One decode step is ~10 launches per layer; at decode sizes the host cannot issue them as fast as the
+// GPU retires them.  The first step of each kind (with / without the head) runs eagerly, the second is
+// captured into a CUDA graph, and every later step replays that graph.
+struct StepGraph {
+    cudaGraphExec_t exec = nullptr;
+    unsigned long long launches = 0;
+    int seen = 0;
+};
 
 nnb_status policy_rollout(nnb_policy* p, const int32_t* d_prompts, size_t B, size_t P, size_t max_new,
                           float temperature, int top_k, unsigned long long seed, unsigned seq0,
@@ -289,23 +300,80 @@ nnb_status policy_rollout(nnb_policy* p, const int32_t* d_prompts, size_t B, siz
     NNB_TRY(ensure_decode(p, B, total));
     DecodeWs& w = p->dec;
     const size_t V = p->cfg.vocab;
-    NNB_CUDA(cudaMemcpy2DAsync(w.tokens, total * 4, d_prompts, P * 4, P * 4, B, cudaMemcpyDeviceToDevice,
-                               e->stream));
-    NNB_TRY(launch_set_int(e, w.d_pos, 0));
-    for (size_t t = 0; t + 1 < total; ++t) {
-        const bool with_head = t + 1 >= P;
-        NNB_TRY(decode_step(p, with_head, temperature, top_k, seed, seq0, (int)P, d_logp != nullptr));
-        if (with_head && d_logits) {
-            const size_t g = t + 1 - P;
-            NNB_CUDA(cudaMemcpy2DAsync(d_logits + g * V, max_new * V * 4, w.logits, V * 4, V * 4, B,
-                                       cudaMemcpyDeviceToDevice, e->stream));
+    // the steps run on the engine's own stream (graph capture is not possible on the legacy default
+    // stream); it is ordered after and before the caller's stream with events
+    cudaStream_t user = e->stream;
+    const bool swap = user != e->own_stream;
+    cudaEvent_t ev = nullptr;
+    if (swap) {
+        NNB_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+        NNB_CUDA(cudaEventRecord(ev, user));
+        NNB_CUDA(cudaStreamWaitEvent(e->own_stream, ev, 0));
+        e->stream = e->own_stream;
+    }
+    StepGraph graphs[2];
+    nnb_status st = NNB_OK;
+    auto run = [&]() -> nnb_status {
+        NNB_CUDA(cudaMemcpy2DAsync(w.tokens, total * 4, d_prompts, P * 4, P * 4, B, cudaMemcpyDeviceToDevice, e->stream));
+        NNB_TRY(launch_set_int(e, w.d_pos, 0));
+        for (size_t t = 0; t + 1 < total; ++t) {
+            const bool with_head = t + 1 >= P;
+            StepGraph& g = graphs[with_head ? 1 : 0];
+            if (g.exec) {
+                NNB_CUDA(cudaGraphLaunch(g.exec, e->stream));
+                e->launches += g.launches;
+            } else if (g.seen == 0 || total < 8) {
+                NNB_TRY(decode_step(p, with_head, temperature, top_k, seed, seq0, (int)P, d_logp != nullptr));
+                g.seen = 1;
+            } else {
+                NNB_CUDA(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
+                const unsigned long long l0 = e->launches;
+                const nnb_status cs = decode_step(p, with_head, temperature, top_k, seed, seq0, (int)P, d_logp != nullptr);
+                cudaGraph_t graph = nullptr;
+                const cudaError_t ce = cudaStreamEndCapture(e->stream, &graph);
+                if (cs != NNB_OK) {
+                    if (graph) cudaGraphDestroy(graph);
+                    return cs;
+                }
+                if (ce != cudaSuccess) NNB_FAIL(NNB_ERR_CUDA, "stream capture of a decode step failed: %s", cudaGetErrorString(ce));
+                g.launches = e->launches - l0;
+                const cudaError_t ie = cudaGraphInstantiate(&g.exec, graph, 0);
+                cudaGraphDestroy(graph);
+                if (ie != cudaSuccess) NNB_FAIL(NNB_ERR_CUDA, "cudaGraphInstantiate failed: %s", cudaGetErrorString(ie));
+                NNB_CUDA(cudaGraphLaunch(g.exec, e->stream));
+            }
+            if (with_head && d_logits) {
+                const size_t gi = t + 1 - P;
+                NNB_CUDA(cudaMemcpy2DAsync(d_logits + gi * V, max_new * V * 4, w.logits, V * 4, V * 4, B,
+                                           cudaMemcpyDeviceToDevice, e->stream));
+            }
         }
-        NNB_TRY(launch_add_int(e, w.d_pos, 1));
+        return NNB_OK;
+    };
+    st = run();
+    for (auto& g : graphs)
+        if (g.exec) {
+            cudaStreamSynchronize(e->stream);
+            cudaGraphExecDestroy(g.exec);
+        }
+    if (st != NNB_OK) {
+        if (swap) {
+            cudaStreamSynchronize(e->own_stream);
+            e->stream = user;
+            cudaEventDestroy(ev);
+        }
+        return st;
     }
     NNB_CUDA(cudaMemcpyAsync(d_tokens, w.tokens, B * total * 4, cudaMemcpyDeviceToDevice, e->stream));
     if (d_logp)
         NNB_CUDA(cudaMemcpy2DAsync(d_logp, max_new * 4, w.logp, total * 4, max_new * 4, B,
                                    cudaMemcpyDeviceToDevice, e->stream));
+    if (swap) {
+        NNB_CUDA(cudaEventRecord(ev, e->own_stream));
+        NNB_CUDA(cudaStreamWaitEvent(user, ev, 0));
+        e->stream = user;
+        NNB_CUDA(cudaEventDestroy(ev));
+    }
     return NNB_OK;
 }
 

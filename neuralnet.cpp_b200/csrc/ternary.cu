@@ -721,6 +721,9 @@ static nnb_status dispatch_fwd(nnb_engine* e, const uint32_t* wq, size_t wq_stri
     if (t <= 64)
         return launch_cfg<64, 64, 128, 4, 2, 2, 1, OutT>(e, wq, wq_stride, tau, bias, residual, q, s,
                                                           qsum, n_mats, t, k, out, y, y_stride, acc);
+    if (t <= 1024)  // few token tiles: narrower token tiles give the machine more CTAs
+        return launch_cfg<128, 64, 128, 4, 4, 2, 1, OutT>(e, wq, wq_stride, tau, bias, residual, q, s,
+                                                           qsum, n_mats, t, k, out, y, y_stride, acc);
     return launch_cfg<128, 128, 128, 4, 2, 4, 1, OutT>(e, wq, wq_stride, tau, bias, residual, q, s,
                                                         qsum, n_mats, t, k, out, y, y_stride, acc);
 }
