@@ -215,6 +215,13 @@ nnb_status nnb_policy_linear(nnb_policy* p, int layer, int which, uint32_t** d_p
 nnb_status nnb_rollout(nnb_policy* p, const int32_t* d_prompts, size_t n_seq, size_t prompt_len,
                        size_t max_new, float temperature, int top_k, uint64_t seed, uint32_t seq0,
                        int32_t* d_tokens, float* d_logp, float* d_logits);
+/* The same when every `group_size` consecutive sequences were given the same prompt (the GRPO sampling
+ * pattern): the shared prompt prefix is decoded once per group into a prefix KV cache that all members
+ * read, so prompt positions cost 1/group_size of the work and of the cache traffic.  Per-sequence
+ * results are identical to nnb_rollout.  n_seq must be a multiple of group_size. */
+nnb_status nnb_rollout_grouped(nnb_policy* p, const int32_t* d_prompts, size_t n_seq, size_t prompt_len, size_t max_new,
+                               size_t group_size, float temperature, int top_k, uint64_t seed, uint32_t seq0,
+                               int32_t* d_tokens, float* d_logp, float* d_logits);
 /* the same with host buffers: copies prompts in and tokens / log-probs out, and synchronises */
 nnb_status nnb_rollout_host(nnb_policy* p, const int32_t* h_prompts, size_t n_seq, size_t prompt_len,
                             size_t max_new, float temperature, int top_k, uint64_t seed, uint32_t seq0,

@@ -106,8 +106,9 @@ nnb_status launch_row_quant(nnb_engine* e, int mode, bool exact, const float* in
                             size_t t, size_t k, size_t in_stride, int8_t* q, float* s,
                             int32_t* qsum, float* f_out);
 nnb_status launch_attn_decode(nnb_engine* e, bool exact, const float* qkv, void* kcache, void* vcache,
-                              const float* rope_cos, const float* rope_sin, const int* d_pos,
-                              size_t B, size_t H, size_t dk, size_t ctx_alloc, float* out);
+                              size_t own_alloc, const void* kpre, const void* vpre, size_t pre_len, size_t pre_alloc,
+                              size_t group, const float* rope_cos, const float* rope_sin, const int* d_pos, size_t B,
+                              size_t H, size_t dk, float* out);
 nnb_status launch_sample(nnb_engine* e, bool exact, const float* logits, size_t B, size_t V,
                          float temperature, int top_k, unsigned long long seed, unsigned seq0,
                          const int* d_pos, int prompt_len, int32_t* tokens, size_t tokens_stride,

@@ -214,21 +214,25 @@ template <>
 __device__ __forceinline__ float from_kv<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 
 // grid = B*H, block = 128.  qkv is (3, B, d) f32 (the three projections of the new token).
-// Cache layout (B, H, ctx_alloc, dk) per layer for K (post-RoPE) and V.
-// 1. RoPE on q and k at position pos; k, v appended to the cache at row pos
+// Two caches per layer, both (sequence, head, position, dk): a prefix cache shared by the `group`
+// consecutive sequences that were given the same prompt (positions [0, pre_len), one row block per
+// group) and the sequence's own cache (positions pre_len + i).  With group == 1 / pre_len == 0 only the
+// own cache is used.
+// 1. RoPE on q and k at position pos; k, v appended to the own cache at row pos - pre_len
 // 2. scores_j = (q . k_j) * scale for j <= pos; softmax; out = sum_j p_j v_j
 template <typename KV, bool EXACT>
 __global__ void __launch_bounds__(128)
-attn_decode_kernel(const float* __restrict__ qkv, KV* __restrict__ kcache, KV* __restrict__ vcache,
+attn_decode_kernel(const float* __restrict__ qkv, KV* __restrict__ kcache, KV* __restrict__ vcache, int own_alloc,
+                   const KV* __restrict__ kpre, const KV* __restrict__ vpre, int pre_len, int pre_alloc, int group,
                    const float* __restrict__ rope_cos, const float* __restrict__ rope_sin,
-                   const int* __restrict__ d_pos, int B, int H, int dk, int ctx_alloc, float scale,
+                   const int* __restrict__ d_pos, int B, int H, int dk, int ctx_total, float scale,
                    float* __restrict__ out)
 {
     typedef typename AccT<EXACT>::type acc_t;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     float* qs = reinterpret_cast<float*>(smem_raw);        // dk (padded to 128)
-    float* sc = qs + 128;                                  // ctx_alloc
-    acc_t* red = reinterpret_cast<acc_t*>(sc + ((ctx_alloc + 3) & ~3));  // 8 * dk
+    float* sc = qs + 128;                                  // ctx_total
+    acc_t* red = reinterpret_cast<acc_t*>(sc + ((ctx_total + 3) & ~3));  // 8 * dk
     __shared__ float bcast[4];
     __shared__ acc_t bsum[4];
 
@@ -236,9 +240,12 @@ attn_decode_kernel(const float* __restrict__ qkv, KV* __restrict__ kcache, KV* _
     const int d = H * dk;
     const int pos = *d_pos;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const size_t head_off = ((size_t)b * H + h) * (size_t)ctx_alloc * dk;
-    KV* kc = kcache + head_off;
-    KV* vc = vcache + head_off;
+    const size_t head_off = ((size_t)b * H + h) * (size_t)own_alloc * dk;
+    KV* kc = kcache + head_off - (size_t)pre_len * dk;   // indexed by absolute position >= pre_len
+    KV* vc = vcache + head_off - (size_t)pre_len * dk;
+    const size_t pre_off = ((size_t)(b / group) * H + h) * (size_t)pre_alloc * dk;
+    const KV* kp = kpre ? kpre + pre_off : nullptr;
+    const KV* vp = vpre ? vpre + pre_off : nullptr;
     const float* qn = qkv + (size_t)b * d + (size_t)h * dk;
     const float* kn = qkv + (size_t)B * d + (size_t)b * d + (size_t)h * dk;
     const float* vn = qkv + 2 * (size_t)B * d + (size_t)b * d + (size_t)h * dk;
@@ -284,7 +291,7 @@ attn_decode_kernel(const float* __restrict__ qkv, KV* __restrict__ kcache, KV* _
         acc_t part = 0;
         if (act && j < n_keys) {
             float kv[4];
-            load4<KV>(kc + (size_t)j * dk + e0, kv);
+            load4<KV>((j < pre_len ? kp : kc) + (size_t)j * dk + e0, kv);
 #pragma unroll
             for (int i = 0; i < 4; ++i) part += (acc_t)qv[i] * (acc_t)kv[i];
         }
@@ -317,7 +324,7 @@ attn_decode_kernel(const float* __restrict__ qkv, KV* __restrict__ kcache, KV* _
         const int j = j0 + sub;
         if (act && j < n_keys) {
             float vv[4];
-            load4<KV>(vc + (size_t)j * dk + e0, vv);
+            load4<KV>((j < pre_len ? vp : vc) + (size_t)j * dk + e0, vv);
             const acc_t p = (acc_t)sc[j];
 #pragma unroll
             for (int i = 0; i < 4; ++i) o4[i] += p * (acc_t)vv[i];
@@ -337,14 +344,17 @@ attn_decode_kernel(const float* __restrict__ qkv, KV* __restrict__ kcache, KV* _
 }
 
 nnb_status launch_attn_decode(nnb_engine* e, bool exact, const float* qkv, void* kcache, void* vcache,
-                              const float* rope_cos, const float* rope_sin, const int* d_pos,
-                              size_t B, size_t H, size_t dk, size_t ctx_alloc, float* out)
+                              size_t own_alloc, const void* kpre, const void* vpre, size_t pre_len, size_t pre_alloc,
+                              size_t group, const float* rope_cos, const float* rope_sin, const int* d_pos, size_t B,
+                              size_t H, size_t dk, float* out)
 {
     NNB_REQUIRE(dk % 4 == 0 && dk <= 128 && dk >= 8, "attn_decode: head dim %zu unsupported (multiple of 4, <= 128)", dk);
+    NNB_REQUIRE(group >= 1 && (pre_len == 0 || (kpre && vpre)), "attn_decode: bad prefix arguments");
     const float scale = 1.0f / sqrtf((float)dk);
     const size_t acc_sz = exact ? 8 : 4;
-    const size_t smem = 128 * 4 + ((ctx_alloc + 3) & ~(size_t)3) * 4 + 8 * dk * acc_sz + 16;
-    NNB_REQUIRE(smem <= 200 * 1024, "attn_decode: context %zu too long for one CTA", ctx_alloc);
+    const size_t ctx_total = pre_len + own_alloc;
+    const size_t smem = 128 * 4 + ((ctx_total + 3) & ~(size_t)3) * 4 + 8 * dk * acc_sz + 16;
+    NNB_REQUIRE(smem <= 200 * 1024, "attn_decode: context %zu too long for one CTA", ctx_total);
     const unsigned grid = (unsigned)(B * H);
     if (exact) {
         auto kern = attn_decode_kernel<float, true>;
@@ -353,8 +363,9 @@ nnb_status launch_attn_decode(nnb_engine* e, bool exact, const float* qkv, void*
             NNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             cfg = smem;
         }
-        kern<<<grid, 128, smem, e->stream>>>(qkv, (float*)kcache, (float*)vcache, rope_cos, rope_sin, d_pos,
-                                             (int)B, (int)H, (int)dk, (int)ctx_alloc, scale, out);
+        kern<<<grid, 128, smem, e->stream>>>(qkv, (float*)kcache, (float*)vcache, (int)own_alloc, (const float*)kpre,
+                                             (const float*)vpre, (int)pre_len, (int)pre_alloc, (int)group, rope_cos, rope_sin,
+                                             d_pos, (int)B, (int)H, (int)dk, (int)ctx_total, scale, out);
     } else {
         auto kern = attn_decode_kernel<__nv_bfloat16, false>;
         static size_t cfg = 0;
@@ -362,8 +373,10 @@ nnb_status launch_attn_decode(nnb_engine* e, bool exact, const float* qkv, void*
             NNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             cfg = smem;
         }
-        kern<<<grid, 128, smem, e->stream>>>(qkv, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, rope_cos,
-                                             rope_sin, d_pos, (int)B, (int)H, (int)dk, (int)ctx_alloc, scale, out);
+        kern<<<grid, 128, smem, e->stream>>>(qkv, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, (int)own_alloc,
+                                             (const __nv_bfloat16*)kpre, (const __nv_bfloat16*)vpre, (int)pre_len,
+                                             (int)pre_alloc, (int)group, rope_cos, rope_sin, d_pos, (int)B, (int)H, (int)dk,
+                                             (int)ctx_total, scale, out);
     }
     e->launches++;
     NNB_CHECK_LAUNCH("attn_decode_kernel");

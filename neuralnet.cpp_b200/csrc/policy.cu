@@ -184,7 +184,8 @@ nnb_status policy_requantize(nnb_policy* p)
 static void free_decode(nnb_policy* p)
 {
     DecodeWs& w = p->dec;
-    void* ptrs[] = {w.k, w.v, w.x, w.qkv, w.att, w.h1, w.logits, w.q8, w.s, w.qsum, w.d_pos, w.tokens, w.logp};
+    void* ptrs[] = {w.k, w.v, w.k_pre, w.v_pre, w.tokens_pre, w.x, w.qkv, w.att, w.h1, w.logits, w.q8, w.s, w.qsum, w.d_pos,
+                    w.tokens, w.logp};
     for (void* q : ptrs)
         if (q) cudaFree(q);
     w = DecodeWs();
@@ -192,22 +193,25 @@ static void free_decode(nnb_policy* p)
 
 void policy_free_decode(nnb_policy* p) { free_decode(p); }
 
-static nnb_status ensure_decode(nnb_policy* p, size_t B, size_t ctx_alloc)
+// total positions = pre_len (shared prefix, one copy per group) + ctx_alloc (per sequence)
+static nnb_status ensure_decode(nnb_policy* p, size_t B, size_t ctx_alloc, size_t group, size_t pre_len)
 {
     DecodeWs& w = p->dec;
-    if (w.B == B && w.ctx_alloc == ctx_alloc) return NNB_OK;
+    if (w.B == B && w.ctx_alloc == ctx_alloc && w.group == group && w.pre_len == pre_len) return NNB_OK;
     NNB_CUDA(cudaStreamSynchronize(p->e->stream));
     free_decode(p);
     const nnb_gpt_config& c = p->cfg;
     const size_t d = c.d_model, F = c.d_ff, V = c.vocab, F1 = c.act == 1 ? 2 * F : F;
     const size_t kv_elem = c.exact ? 4 : 2;
     const size_t kv_bytes = (size_t)c.n_layer * B * d * ctx_alloc * kv_elem;
+    const size_t pre_bytes = (size_t)c.n_layer * (B / group) * d * pre_len * kv_elem;
+    const size_t total = pre_len + ctx_alloc;
     size_t free_b = 0, total_b = 0;
     NNB_CUDA(cudaMemGetInfo(&free_b, &total_b));
-    const size_t need = 2 * kv_bytes + B * (d * 4 * 5 + F1 * 4 + V * 4 + (F > d ? F : d)) + (64u << 20);
+    const size_t need = 2 * (kv_bytes + pre_bytes) + B * (d * 4 * 5 + F1 * 4 + V * 4 + (F > d ? F : d) + total * 8) + (64u << 20);
     if (need > free_b)
         NNB_FAIL(NNB_ERR_OOM, "rollout of %zu sequences x %zu positions needs %.1f GB (KV cache %.1f GB), %.1f GB free",
-                 B, ctx_alloc, need / 1e9, 2 * kv_bytes / 1e9, free_b / 1e9);
+                 B, total, need / 1e9, 2 * (kv_bytes + pre_bytes) / 1e9, free_b / 1e9);
 #define NNB_ALLOC(ptr, bytes)                                                          \
     do {                                                                               \
         cudaError_t er__ = cudaMalloc((void**)&(ptr), (bytes));                        \
@@ -219,6 +223,11 @@ static nnb_status ensure_decode(nnb_policy* p, size_t B, size_t ctx_alloc)
     } while (0)
     NNB_ALLOC(w.k, kv_bytes);
     NNB_ALLOC(w.v, kv_bytes);
+    if (pre_len > 0) {
+        NNB_ALLOC(w.k_pre, pre_bytes);
+        NNB_ALLOC(w.v_pre, pre_bytes);
+        NNB_ALLOC(w.tokens_pre, (B / group) * pre_len * 4);
+    }
     NNB_ALLOC(w.x, B * d * 4);
     NNB_ALLOC(w.qkv, 3 * B * d * 4);
     NNB_ALLOC(w.att, B * d * 4);
@@ -228,78 +237,136 @@ static nnb_status ensure_decode(nnb_policy* p, size_t B, size_t ctx_alloc)
     NNB_ALLOC(w.s, B * 4);
     NNB_ALLOC(w.qsum, B * 4);
     NNB_ALLOC(w.d_pos, 16);
-    NNB_ALLOC(w.tokens, B * ctx_alloc * 4);
-    NNB_ALLOC(w.logp, B * ctx_alloc * 4);
+    NNB_ALLOC(w.tokens, B * total * 4);
+    NNB_ALLOC(w.logp, B * total * 4);
 #undef NNB_ALLOC
     w.B = B;
     w.ctx_alloc = ctx_alloc;
+    w.group = group;
+    w.pre_len = pre_len;
     return NNB_OK;
 }
 
+// What one decode step runs on: either all sequences (own caches + shared prefix) or, while the shared
+// prompt prefix is being filled, one representative per group writing the prefix cache.
+struct StepView {
+    size_t B;
+    const int32_t* tokens;
+    size_t tok_stride;
+    void *k, *v;          // cache written by this step, per layer stride = layer_bytes
+    size_t own_alloc, layer_bytes;
+    const void *k_pre, *v_pre;
+    size_t pre_len, pre_alloc, pre_layer_bytes, group;
+};
+
 // one decode step at the position stored in d_pos: consumes tokens[:, pos], appends to the KV
 // cache and, when with_head, samples tokens[:, pos+1]
-static nnb_status decode_step(nnb_policy* p, bool with_head, float temperature, int top_k,
+static nnb_status decode_step(nnb_policy* p, const StepView& sv, bool with_head, float temperature, int top_k,
                               unsigned long long seed, unsigned seq0, int prompt_len, bool want_logp)
 {
     nnb_engine* e = p->e;
     const nnb_gpt_config& c = p->cfg;
     DecodeWs& w = p->dec;
-    const size_t B = w.B, d = c.d_model, F = c.d_ff, V = c.vocab, H = c.n_head, dk = d / H;
+    const size_t B = sv.B, d = c.d_model, F = c.d_ff, V = c.vocab, H = c.n_head, dk = d / H;
     const size_t F1 = c.act == 1 ? 2 * F : F;
     const bool exact = c.exact != 0;
     const float* P = p->params;
-    const size_t kv_elem = exact ? 4 : 2;
-    const size_t layer_kv = B * d * w.ctx_alloc * kv_elem;
 
-    NNB_TRY(launch_embed(e, P + p->tok_emb, c.pos == 0 ? P + p->pos_emb : nullptr, w.tokens, w.ctx_alloc,
-                         w.d_pos, B, d, V, w.x));
+    NNB_TRY(launch_embed(e, P + p->tok_emb, c.pos == 0 ? P + p->pos_emb : nullptr, sv.tokens, sv.tok_stride, w.d_pos, B, d,
+                         V, w.x));
     for (int l = 0; l < c.n_layer; ++l) {
         const LayerW& L = p->layers[l];
         NNB_TRY(launch_row_quant(e, 0, exact, w.x, P + L.ln1_g, B, d, d, w.q8, w.s, w.qsum, nullptr));
         // q, k, v projections: three equally shaped matrices stored back to back, one launch
         NNB_TRY(policy_linear_fwd(p, L.q, 3, w.q8, w.s, w.qsum, B, nullptr, w.qkv, B * d));
-        NNB_TRY(launch_attn_decode(e, exact, w.qkv, (char*)w.k + (size_t)l * layer_kv,
-                                   (char*)w.v + (size_t)l * layer_kv, p->rope_cos, p->rope_sin, w.d_pos, B,
-                                   H, dk, w.ctx_alloc, w.att));
+        NNB_TRY(launch_attn_decode(e, exact, w.qkv, (char*)sv.k + (size_t)l * sv.layer_bytes,
+                                   (char*)sv.v + (size_t)l * sv.layer_bytes, sv.own_alloc,
+                                   sv.k_pre ? (const char*)sv.k_pre + (size_t)l * sv.pre_layer_bytes : nullptr,
+                                   sv.v_pre ? (const char*)sv.v_pre + (size_t)l * sv.pre_layer_bytes : nullptr, sv.pre_len,
+                                   sv.pre_alloc, sv.group, p->rope_cos, p->rope_sin, w.d_pos, B, H, dk, w.att));
         NNB_TRY(launch_row_quant(e, 3, exact, w.att, nullptr, B, d, d, w.q8, w.s, w.qsum, nullptr));
         NNB_TRY(policy_linear_fwd(p, L.o, 1, w.q8, w.s, w.qsum, B, w.x, w.x, 0));
         NNB_TRY(launch_row_quant(e, 0, exact, w.x, P + L.ln2_g, B, d, d, w.q8, w.s, w.qsum, nullptr));
         NNB_TRY(policy_linear_fwd(p, L.fc1, 1, w.q8, w.s, w.qsum, B, nullptr, w.h1, 0));
-        NNB_TRY(launch_row_quant(e, c.act == 1 ? 2 : 1, exact, w.h1, nullptr, B, F, F1, w.q8, w.s, w.qsum,
-                                 nullptr));
+        NNB_TRY(launch_row_quant(e, c.act == 1 ? 2 : 1, exact, w.h1, nullptr, B, F, F1, w.q8, w.s, w.qsum, nullptr));
         NNB_TRY(policy_linear_fwd(p, L.fc2, 1, w.q8, w.s, w.qsum, B, w.x, w.x, 0));
     }
     if (with_head) {
+        const size_t total = w.pre_len + w.ctx_alloc;
         NNB_TRY(launch_row_quant(e, 0, exact, w.x, P + p->lnf_g, B, d, d, w.q8, w.s, w.qsum, nullptr));
         NNB_TRY(policy_linear_fwd(p, p->head, 1, w.q8, w.s, w.qsum, B, nullptr, w.logits, 0));
-        NNB_TRY(launch_sample(e, exact, w.logits, B, V, temperature, top_k, seed, seq0, w.d_pos, prompt_len,
-                              w.tokens, w.ctx_alloc, want_logp ? w.logp : nullptr, w.ctx_alloc, nullptr));
+        NNB_TRY(launch_sample(e, exact, w.logits, B, V, temperature, top_k, seed, seq0, w.d_pos, prompt_len, w.tokens, total,
+                              want_logp ? w.logp : nullptr, total, nullptr));
     }
     return launch_add_int(e, w.d_pos, 1);  // the position lives on the device so a captured step can be replayed
 }
 
 // One decode step is ~10 launches per layer; at decode sizes the host cannot issue them as fast as the
-// GPU retires them.  The first step of each kind (with / without the head) runs eagerly, the second is
-// captured into a CUDA graph, and every later step replays that graph.
+// GPU retires them.  The first step of each kind runs eagerly, the second is captured into a CUDA
+// graph, and every later step of that kind replays the graph.
 struct StepGraph {
     cudaGraphExec_t exec = nullptr;
     unsigned long long launches = 0;
     int seen = 0;
 };
 
-nnb_status policy_rollout(nnb_policy* p, const int32_t* d_prompts, size_t B, size_t P, size_t max_new,
+static nnb_status run_step(nnb_policy* p, StepGraph& g, bool allow_graph, const StepView& sv, bool with_head, float temperature,
+                           int top_k, unsigned long long seed, unsigned seq0, int prompt_len, bool want_logp)
+{
+    nnb_engine* e = p->e;
+    if (g.exec) {
+        NNB_CUDA(cudaGraphLaunch(g.exec, e->stream));
+        e->launches += g.launches;
+        return NNB_OK;
+    }
+    if (g.seen == 0 || !allow_graph) {
+        g.seen = 1;
+        return decode_step(p, sv, with_head, temperature, top_k, seed, seq0, prompt_len, want_logp);
+    }
+    NNB_CUDA(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
+    const unsigned long long l0 = e->launches;
+    const nnb_status cs = decode_step(p, sv, with_head, temperature, top_k, seed, seq0, prompt_len, want_logp);
+    cudaGraph_t graph = nullptr;
+    const cudaError_t ce = cudaStreamEndCapture(e->stream, &graph);
+    if (cs != NNB_OK) {
+        if (graph) cudaGraphDestroy(graph);
+        return cs;
+    }
+    if (ce != cudaSuccess) NNB_FAIL(NNB_ERR_CUDA, "stream capture of a decode step failed: %s", cudaGetErrorString(ce));
+    g.launches = e->launches - l0;
+    const cudaError_t ie = cudaGraphInstantiate(&g.exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (ie != cudaSuccess) NNB_FAIL(NNB_ERR_CUDA, "cudaGraphInstantiate failed: %s", cudaGetErrorString(ie));
+    NNB_CUDA(cudaGraphLaunch(g.exec, e->stream));
+    return NNB_OK;
+}
+
+// group > 1: sequences [g*group, (g+1)*group) were given the same prompt.  Their first P-1 prompt
+// positions are computed once per group (batch B/group) into a prefix cache that all members read;
+// from position P-1 on every sequence runs on its own.  The arithmetic per sequence is unchanged.
+nnb_status policy_rollout(nnb_policy* p, const int32_t* d_prompts, size_t B, size_t P, size_t max_new, size_t group,
                           float temperature, int top_k, unsigned long long seed, unsigned seq0,
                           int32_t* d_tokens, float* d_logp, float* d_logits)
 {
     NNB_REQUIRE(p && d_prompts && d_tokens, "rollout: NULL argument");
     NNB_REQUIRE(B > 0 && P > 0 && max_new > 0, "rollout: empty shape");
+    NNB_REQUIRE(group >= 1 && B % group == 0, "rollout: %zu sequences do not divide into groups of %zu", B, group);
     NNB_REQUIRE(P + max_new <= (size_t)p->cfg.ctx, "rollout: prompt %zu + %zu new tokens exceeds the context %d",
                 P, max_new, p->cfg.ctx);
     nnb_engine* e = p->e;
+    const nnb_gpt_config& c = p->cfg;
     const size_t total = P + max_new;
-    NNB_TRY(ensure_decode(p, B, total));
+    const size_t pre_len = (group > 1 && P > 1) ? P - 1 : 0;
+    const size_t own = total - pre_len;
+    NNB_TRY(ensure_decode(p, B, own, group, pre_len));
     DecodeWs& w = p->dec;
-    const size_t V = p->cfg.vocab;
+    const size_t V = c.vocab, d = c.d_model;
+    const size_t kv_elem = c.exact ? 4 : 2;
+    const size_t Bg = B / group;
+    StepView main_view{B, w.tokens, total, w.k, w.v, own, B * d * own * kv_elem, w.k_pre, w.v_pre, pre_len, pre_len,
+                       Bg * d * pre_len * kv_elem, group};
+    StepView pre_view{Bg, w.tokens_pre, pre_len, w.k_pre, w.v_pre, pre_len, Bg * d * pre_len * kv_elem, nullptr, nullptr, 0, 0, 0, 1};
+
     // the steps run on the engine's own stream (graph capture is not possible on the legacy default
     // stream); it is ordered after and before the caller's stream with events
     cudaStream_t user = e->stream;
@@ -311,37 +378,22 @@ nnb_status policy_rollout(nnb_policy* p, const int32_t* d_prompts, size_t B, siz
         NNB_CUDA(cudaStreamWaitEvent(e->own_stream, ev, 0));
         e->stream = e->own_stream;
     }
-    StepGraph graphs[2];
-    nnb_status st = NNB_OK;
+    StepGraph graphs[3];  // prefix fill, own steps without head, own steps with head
     auto run = [&]() -> nnb_status {
         NNB_CUDA(cudaMemcpy2DAsync(w.tokens, total * 4, d_prompts, P * 4, P * 4, B, cudaMemcpyDeviceToDevice, e->stream));
+        if (pre_len > 0)  // prompt of the first member of every group, without its last token
+            NNB_CUDA(cudaMemcpy2DAsync(w.tokens_pre, pre_len * 4, d_prompts, group * P * 4, pre_len * 4, Bg,
+                                       cudaMemcpyDeviceToDevice, e->stream));
         NNB_TRY(launch_set_int(e, w.d_pos, 0));
+        const bool allow_graph = total >= 8;
         for (size_t t = 0; t + 1 < total; ++t) {
-            const bool with_head = t + 1 >= P;
-            StepGraph& g = graphs[with_head ? 1 : 0];
-            if (g.exec) {
-                NNB_CUDA(cudaGraphLaunch(g.exec, e->stream));
-                e->launches += g.launches;
-            } else if (g.seen == 0 || total < 8) {
-                NNB_TRY(decode_step(p, with_head, temperature, top_k, seed, seq0, (int)P, d_logp != nullptr));
-                g.seen = 1;
-            } else {
-                NNB_CUDA(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
-                const unsigned long long l0 = e->launches;
-                const nnb_status cs = decode_step(p, with_head, temperature, top_k, seed, seq0, (int)P, d_logp != nullptr);
-                cudaGraph_t graph = nullptr;
-                const cudaError_t ce = cudaStreamEndCapture(e->stream, &graph);
-                if (cs != NNB_OK) {
-                    if (graph) cudaGraphDestroy(graph);
-                    return cs;
-                }
-                if (ce != cudaSuccess) NNB_FAIL(NNB_ERR_CUDA, "stream capture of a decode step failed: %s", cudaGetErrorString(ce));
-                g.launches = e->launches - l0;
-                const cudaError_t ie = cudaGraphInstantiate(&g.exec, graph, 0);
-                cudaGraphDestroy(graph);
-                if (ie != cudaSuccess) NNB_FAIL(NNB_ERR_CUDA, "cudaGraphInstantiate failed: %s", cudaGetErrorString(ie));
-                NNB_CUDA(cudaGraphLaunch(g.exec, e->stream));
+            if (t < pre_len) {
+                NNB_TRY(run_step(p, graphs[0], allow_graph, pre_view, false, temperature, top_k, seed, seq0, (int)P, false));
+                continue;
             }
+            const bool with_head = t + 1 >= P;
+            NNB_TRY(run_step(p, graphs[with_head ? 2 : 1], allow_graph, main_view, with_head, temperature, top_k, seed, seq0,
+                             (int)P, d_logp != nullptr));
             if (with_head && d_logits) {
                 const size_t gi = t + 1 - P;
                 NNB_CUDA(cudaMemcpy2DAsync(d_logits + gi * V, max_new * V * 4, w.logits, V * 4, V * 4, B,
@@ -350,7 +402,7 @@ nnb_status policy_rollout(nnb_policy* p, const int32_t* d_prompts, size_t B, siz
         }
         return NNB_OK;
     };
-    st = run();
+    const nnb_status st = run();
     for (auto& g : graphs)
         if (g.exec) {
             cudaStreamSynchronize(e->stream);
@@ -504,7 +556,15 @@ nnb_status nnb_rollout(nnb_policy* p, const int32_t* d_prompts, size_t n_seq, si
                        size_t max_new, float temperature, int top_k, uint64_t seed, uint32_t seq0,
                        int32_t* d_tokens, float* d_logp, float* d_logits)
 {
-    return policy_rollout(p, d_prompts, n_seq, prompt_len, max_new, temperature, top_k, seed, seq0, d_tokens,
+    return policy_rollout(p, d_prompts, n_seq, prompt_len, max_new, 1, temperature, top_k, seed, seq0, d_tokens,
+                          d_logp, d_logits);
+}
+
+nnb_status nnb_rollout_grouped(nnb_policy* p, const int32_t* d_prompts, size_t n_seq, size_t prompt_len, size_t max_new,
+                               size_t group_size, float temperature, int top_k, uint64_t seed, uint32_t seq0,
+                               int32_t* d_tokens, float* d_logp, float* d_logits)
+{
+    return policy_rollout(p, d_prompts, n_seq, prompt_len, max_new, group_size, temperature, top_k, seed, seq0, d_tokens,
                           d_logp, d_logits);
 }
 
@@ -523,7 +583,7 @@ nnb_status nnb_rollout_host(nnb_policy* p, const int32_t* h_prompts, size_t n_se
     int32_t* d_tokens = (int32_t*)(base + pb);
     float* d_logp = (float*)(base + pb + tb);
     NNB_CUDA(cudaMemcpyAsync(d_prompts, h_prompts, n_seq * prompt_len * 4, cudaMemcpyHostToDevice, e->stream));
-    NNB_TRY(policy_rollout(p, d_prompts, n_seq, prompt_len, max_new, temperature, top_k, seed, seq0, d_tokens,
+    NNB_TRY(policy_rollout(p, d_prompts, n_seq, prompt_len, max_new, 1, temperature, top_k, seed, seq0, d_tokens,
                            h_logp ? d_logp : nullptr, nullptr));
     NNB_CUDA(cudaMemcpyAsync(h_tokens, d_tokens, n_seq * total * 4, cudaMemcpyDeviceToHost, e->stream));
     if (h_logp)

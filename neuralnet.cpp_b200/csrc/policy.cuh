@@ -25,8 +25,11 @@ struct TensorInfo {
 };
 
 struct DecodeWs {
-    size_t B = 0, ctx_alloc = 0;
+    size_t B = 0, ctx_alloc = 0;     // sequences; positions held by the per-sequence cache
+    size_t group = 1, pre_len = 0;   // sequences per shared prompt; positions held by the shared prefix cache
     void *k = nullptr, *v = nullptr;  // (L, B, H, ctx_alloc, dk), f32 in the exact mode else bf16
+    void *k_pre = nullptr, *v_pre = nullptr;  // (L, B/group, H, pre_len, dk): prompt prefix, one per group
+    int32_t* tokens_pre = nullptr;            // (B/group, pre_len) prompt tokens of the group representatives
     float *x = nullptr, *qkv = nullptr, *att = nullptr, *h1 = nullptr, *logits = nullptr;
     int8_t* q8 = nullptr;
     float* s = nullptr;

@@ -66,7 +66,7 @@ class GrpoTrainer:
         toks, lps = [], []
         for a in range(0, n, chunk):
             t, lp, _ = self.policy.rollout(rep[a:a + chunk].contiguous(), c.max_new, temperature=c.temperature,
-                                           top_k=c.top_k, seed=seed, seq0=seq0 + a)
+                                           top_k=c.top_k, seed=seed, seq0=seq0 + a, group_size=c.group_size)
             toks.append(t)
             lps.append(lp)
         return torch.cat(toks), torch.cat(lps)

@@ -148,15 +148,19 @@ class Policy:
         return packed, _alias(tau.value, o.value, torch.float32, self.engine.device)
 
     def rollout(self, prompts: torch.Tensor, max_new: int, temperature: float = 1.0, top_k: int = 0,
-                seed: int = 0, seq0: int = 0, want_logp: bool = True, want_logits: bool = False):
-        """prompts (B, P) int32 on the device -> tokens (B, P+max_new) int32, logp (B, max_new), [logits]."""
+                seed: int = 0, seq0: int = 0, want_logp: bool = True, want_logits: bool = False,
+                group_size: int = 1):
+        """prompts (B, P) int32 on the device -> tokens (B, P+max_new) int32, logp (B, max_new), [logits].
+        group_size > 1: every group_size consecutive rows of `prompts` are the same prompt; the shared
+        prefix is decoded once per group."""
         B, P = prompts.shape
         dev = self.engine.device
         tokens = torch.empty((B, P + max_new), device=dev, dtype=torch.int32)
         logp = torch.empty((B, max_new), device=dev, dtype=torch.float32) if want_logp else None
         logits = torch.empty((B, max_new, self.cfg.vocab), device=dev, dtype=torch.float32) if want_logits else None
-        check(self._lib.nnb_rollout(self._h, _ptr(prompts), B, P, max_new, float(temperature), int(top_k),
-                                    C.c_uint64(seed), C.c_uint32(seq0), _ptr(tokens), _ptr(logp), _ptr(logits)))
+        check(self._lib.nnb_rollout_grouped(self._h, _ptr(prompts), B, P, max_new, int(group_size), float(temperature),
+                                            int(top_k), C.c_uint64(seed), C.c_uint32(seq0), _ptr(tokens), _ptr(logp),
+                                            _ptr(logits)))
         return tokens, logp, logits
 
     def rollout_host(self, h_prompts: torch.Tensor, max_new: int, temperature: float, top_k: int, seed: int,

@@ -33,7 +33,7 @@ class StubPolicy:
         self.calls = []
         self.stepped = 0
 
-    def rollout(self, prompts, max_new, temperature, top_k, seed, seq0):
+    def rollout(self, prompts, max_new, temperature, top_k, seed, seq0, group_size=1):
         self.calls.append(("rollout", prompts.shape[0], seq0))
         n, p = prompts.shape
         gen = (torch.arange(n)[:, None] + seq0 + torch.arange(max_new)[None, :]).to(torch.int32) % 7
