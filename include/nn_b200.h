@@ -284,6 +284,17 @@ nnb_status nnb_gae(nnb_engine* e, const float* d_rewards, const float* d_values,
  * host must be contiguous and cover all n rows, else NNB_ERR_INVALID. */
 nnb_status nnb_group_advantage(nnb_engine* e, const float* d_returns, size_t n, const int32_t* h_first,
                                const int32_t* h_count, size_t n_spans, float eps, float* d_out);
+/* nnb_group_advantage for callers that cannot allocate device memory (a host whose own pool owns the
+ * whole GPU, a step running where the CUDA allocator must not be entered, a fixed start-up budget).
+ * It has no counterpart in the reference.  Same arguments and result as nnb_group_advantage; the
+ * device copy of the span table lives in a fixed 128 KiB array inside the library (held by every GPU
+ * that loads it, until exit), so the call does no cudaMalloc / cudaFree.  Limit: n_spans <= 16384,
+ * larger requests are rejected with NNB_ERR_INVALID.  The first call on a device looks up the array's
+ * device address (cudaGetSymbolAddress); make that first call before any stream capture begins.  All
+ * calls share the one array: calls whose GPU work can overlap (different streams or engines on the
+ * same device) race on it and must be serialised by the caller. */
+nnb_status nnb_group_advantage_noalloc(nnb_engine* e, const float* d_returns, size_t n, const int32_t* h_first,
+                                       const int32_t* h_count, size_t n_spans, float eps, float* d_out);
 /* MaskedNormalizer::apply (rl_experience.hpp:456-498); mask may be NULL (all ones) */
 nnb_status nnb_masked_normalize(nnb_engine* e, const float* d_values, const float* d_mask, size_t n, float eps,
                                 float* d_out);

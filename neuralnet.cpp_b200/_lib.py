@@ -76,6 +76,7 @@ _SIGNATURES = {
     "nnb_policy_release_workspaces": (_I, [_P]),
     "nnb_gae": (_I, [_P, _P, _P, _P, _P, _P, _SZ, _SZ, C.c_float, C.c_float, _P, _P]),
     "nnb_group_advantage": (_I, [_P, _P, _SZ, _P, _P, _SZ, C.c_float, _P]),
+    "nnb_group_advantage_noalloc": (_I, [_P, _P, _SZ, _P, _P, _SZ, C.c_float, _P]),
     "nnb_masked_normalize": (_I, [_P, _P, _P, _SZ, C.c_float, _P]),
     "nnb_categorical_logp_entropy": (_I, [_P, _P, _P, _SZ, _SZ, _P, _P]),
     "nnb_categorical_backward": (_I, [_P, _P, _P, _P, _P, _SZ, _SZ, _P]),
