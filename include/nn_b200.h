@@ -148,6 +148,9 @@ nnb_status nnb_expand_weights(nnb_engine* e, const uint32_t* d_wq, size_t rows, 
 nnb_status nnb_bitlinear_fwd_tc(nnb_engine* e, const int8_t* d_w8, const float* d_tau, const float* d_bias,
                                 const float* d_residual, const int8_t* d_q, const float* d_s, size_t t, size_t k,
                                 size_t out, float* d_y);
+/* Tuning knob, process-wide: width of the 128 x bn output tile of nnb_bitlinear_fwd_tc (64, 128, 192 or
+ * 256); 0 restores the automatic choice from the problem shape.  Results do not depend on it. */
+nnb_status nnb_tc_set_forward_tile(int bn);
 /* BitLinear::backward on bf16 tensor cores: d_dyb (t,out) and d_xs (t,k) are bf16 scratch buffers the
  * call fills (dy*tau and s*q); d_dx (t,k) and/or d_dw (out,k) may be NULL to skip that half. */
 nnb_status nnb_bitlinear_bwd_tc(nnb_engine* e, const float* d_dy, const float* d_tau, const void* d_wb,

@@ -52,6 +52,7 @@ _SIGNATURES = {
     "nnb_bitlinear_dx_tm": (_I, [_P, _P, _P, _P, _SZ, _SZ, _SZ, _P, _I, _I]),
     "nnb_bitlinear_dw_tm": (_I, [_P, _P, _P, _P, _P, _SZ, _SZ, _SZ, _P, _I]),
     "nnb_expand_weights": (_I, [_P, _P, _SZ, _SZ, _P, _P]),
+    "nnb_tc_set_forward_tile": (_I, [_I]),
     "nnb_bitlinear_fwd_tc": (_I, [_P, _P, _P, _P, _P, _P, _P, _SZ, _SZ, _SZ, _P]),
     "nnb_bitlinear_bwd_tc": (_I, [_P, _P, _P, _P, _P, _P, _SZ, _SZ, _SZ, _P, _P, _P, _I, _P]),
     "nnb_engine_check": (_I, [_P]),

@@ -125,6 +125,8 @@ nnb_status nnb_bitlinear_fwd_tc(nnb_engine* e, const int8_t* d_w8, const float* 
     return launch_tc_forward(e, d_q, d_w8, d_tau, d_s, d_bias, d_residual, t, k, out, d_y);
 }
 
+nnb_status nnb_tc_set_forward_tile(int bn) { return tc_set_forward_tile(bn); }
+
 nnb_status nnb_bitlinear_bwd_tc(nnb_engine* e, const float* d_dy, const float* d_tau, const void* d_wb,
                                 const int8_t* d_q, const float* d_s, size_t t, size_t k, size_t out, void* d_dyb,
                                 void* d_xs, float* d_dx, int accumulate_dx, float* d_dw)

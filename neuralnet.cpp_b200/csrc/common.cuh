@@ -182,12 +182,14 @@ nnb_status launch_add(nnb_engine* e, float* dst, const float* src, size_t n);
 
 // ---- gemm_tc.cu (tcgen05 / TMEM / TMA GEMMs)
 nnb_status launch_tc_forward(nnb_engine* e, const int8_t* q, const int8_t* w8, const float* tau, const float* s,
-                             const float* bias, const float* residual, size_t t, size_t k, size_t out, float* y);
+                             const float* bias, const float* residual, size_t t, size_t k, size_t out, float* y,
+                             size_t n_mats = 1, size_t y_stride = 0);
 nnb_status launch_tc_dx(nnb_engine* e, const __nv_bfloat16* dyb, const __nv_bfloat16* wb, size_t t, size_t k, size_t out,
                         float* dx, bool accumulate);
 nnb_status launch_tc_dw(nnb_engine* e, const __nv_bfloat16* dyb, const __nv_bfloat16* xs, size_t t, size_t k, size_t out,
                         float* dw);
 nnb_status tc_check_errors(nnb_engine* e);
+nnb_status tc_set_forward_tile(int bn);
 nnb_status launch_expand_weights(nnb_engine* e, const uint32_t* wq, size_t rows, size_t k, int8_t* w8, __nv_bfloat16* wb);
 nnb_status launch_scale_to_bf16(nnb_engine* e, const float* dy, const float* tau, size_t t, size_t out, __nv_bfloat16* dyb);
 nnb_status launch_dequant_to_bf16(nnb_engine* e, const int8_t* q, const float* s, size_t t, size_t k, __nv_bfloat16* xs);

@@ -343,6 +343,177 @@ attn_decode_kernel(const float* __restrict__ qkv, KV* __restrict__ kcache, KV* _
     }
 }
 
+// Fast-mode variant of attn_decode_kernel for a bf16 cache and head dims 64 / 128: same arguments and
+// the same two passes, but every lane reads 16 bytes (8 features) of a key, DK/8 lanes share a key, and
+// each lane group keeps U keys in flight, so one CTA has 4*U*512 bytes of cache reads outstanding.
+__device__ __forceinline__ void bf16x8_to_float(const uint4& t, float (&v)[8])
+{
+    v[0] = __uint_as_float(t.x << 16); v[1] = __uint_as_float(t.x & 0xffff0000u);
+    v[2] = __uint_as_float(t.y << 16); v[3] = __uint_as_float(t.y & 0xffff0000u);
+    v[4] = __uint_as_float(t.z << 16); v[5] = __uint_as_float(t.z & 0xffff0000u);
+    v[6] = __uint_as_float(t.w << 16); v[7] = __uint_as_float(t.w & 0xffff0000u);
+}
+
+template <int DK>
+__global__ void __launch_bounds__(128)
+attn_decode_bf16_kernel(const float* __restrict__ qkv, __nv_bfloat16* __restrict__ kcache, __nv_bfloat16* __restrict__ vcache,
+                        int own_alloc, const __nv_bfloat16* __restrict__ kpre, const __nv_bfloat16* __restrict__ vpre,
+                        int pre_len, int pre_alloc, int group, const float* __restrict__ rope_cos,
+                        const float* __restrict__ rope_sin, const int* __restrict__ d_pos, int B, int H, int ctx_total,
+                        float scale, float* __restrict__ out)
+{
+    constexpr int LPK = DK / 8;    // lanes per key
+    constexpr int KPW = 32 / LPK;  // keys per warp-wide load
+    constexpr int G = 4 * KPW;     // lane groups per CTA
+    constexpr int U = 4;           // keys in flight per lane group
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    float* qs = reinterpret_cast<float*>(smem_raw);  // DK
+    float* red = qs + DK;                            // G * DK
+    float* sc = red + G * DK;                        // ctx_total
+    __shared__ float bcast[4];
+    __shared__ float bsum[4];
+
+    const int b = blockIdx.x / H, h = blockIdx.x % H;
+    const int d = H * DK;
+    const int pos = *d_pos;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const size_t head_off = ((size_t)b * H + h) * (size_t)own_alloc * DK;
+    __nv_bfloat16* kc = kcache + head_off - (size_t)pre_len * DK;  // indexed by absolute position >= pre_len
+    __nv_bfloat16* vc = vcache + head_off - (size_t)pre_len * DK;
+    const size_t pre_off = ((size_t)(b / group) * H + h) * (size_t)pre_alloc * DK;
+    const __nv_bfloat16* kp = kpre ? kpre + pre_off : nullptr;
+    const __nv_bfloat16* vp = vpre ? vpre + pre_off : nullptr;
+    const float* qn = qkv + (size_t)b * d + (size_t)h * DK;
+    const float* kn = qkv + (size_t)B * d + (size_t)b * d + (size_t)h * DK;
+    const float* vn = qkv + 2 * (size_t)B * d + (size_t)b * d + (size_t)h * DK;
+
+    if (rope_cos) {
+        constexpr int half = DK / 2;
+        for (int j = tid; j < half; j += 128) {
+            const float c = rope_cos[(size_t)pos * half + j], sn = rope_sin[(size_t)pos * half + j];
+            const float qa = qn[j], qb = qn[j + half];
+            const float ka = kn[j], kb = kn[j + half];
+            qs[j] = __fadd_rn(__fmul_rn(qa, c), __fmul_rn(-qb, sn));
+            qs[j + half] = __fadd_rn(__fmul_rn(qb, c), __fmul_rn(qa, sn));
+            kc[(size_t)pos * DK + j] = __float2bfloat16_rn(__fadd_rn(__fmul_rn(ka, c), __fmul_rn(-kb, sn)));
+            kc[(size_t)pos * DK + j + half] = __float2bfloat16_rn(__fadd_rn(__fmul_rn(kb, c), __fmul_rn(ka, sn)));
+        }
+    } else {
+        for (int j = tid; j < DK; j += 128) {
+            qs[j] = qn[j];
+            kc[(size_t)pos * DK + j] = __float2bfloat16_rn(kn[j]);
+        }
+    }
+    for (int j = tid; j < DK; j += 128) vc[(size_t)pos * DK + j] = __float2bfloat16_rn(vn[j]);
+    __syncthreads();
+
+    const int sub = lane / LPK, sl = lane % LPK;
+    const int g = warp * KPW + sub;
+    const int e0 = sl * 8;
+    float qv[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) qv[i] = qs[e0 + i];
+    const int n_keys = pos + 1;
+
+    // scores
+    for (int base = 0; base < n_keys; base += G * U) {
+        uint4 raw[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int j = base + u * G + g;
+            raw[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (j < n_keys) raw[u] = *reinterpret_cast<const uint4*>((j < pre_len ? kp : kc) + (size_t)j * DK + e0);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int j = base + u * G + g;
+            float kv[8];
+            bf16x8_to_float(raw[u], kv);
+            float part = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) part = fmaf(qv[i], kv[i], part);
+#pragma unroll
+            for (int o = LPK / 2; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+            if (sl == 0 && j < n_keys) sc[j] = part * scale;
+        }
+    }
+    __syncthreads();
+    float mx = -INFINITY;
+    for (int j = tid; j < n_keys; j += 128) mx = fmaxf(mx, sc[j]);
+    mx = warp_max(mx);
+    if (lane == 0) bcast[warp] = mx;
+    __syncthreads();
+    mx = fmaxf(fmaxf(bcast[0], bcast[1]), fmaxf(bcast[2], bcast[3]));
+    float sum = 0.0f;
+    for (int j = tid; j < n_keys; j += 128) {
+        const float ev = __expf(sc[j] - mx);
+        sc[j] = ev;
+        sum += ev;
+    }
+    sum = warp_sum(sum);
+    if (lane == 0) bsum[warp] = sum;
+    __syncthreads();
+    const float inv = 1.0f / (bsum[0] + bsum[1] + bsum[2] + bsum[3]);
+
+    // out = sum_j p_j v_j
+    float o8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int base = 0; base < n_keys; base += G * U) {
+        uint4 raw[U];
+        float p[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int j = base + u * G + g;
+            raw[u] = make_uint4(0u, 0u, 0u, 0u);
+            p[u] = 0.0f;
+            if (j < n_keys) {
+                raw[u] = *reinterpret_cast<const uint4*>((j < pre_len ? vp : vc) + (size_t)j * DK + e0);
+                p[u] = sc[j];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            float vv[8];
+            bf16x8_to_float(raw[u], vv);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o8[i] = fmaf(p[u], vv[i], o8[i]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) red[g * DK + e0 + i] = o8[i];
+    __syncthreads();
+    for (int i = tid; i < DK; i += 128) {
+        float a = 0.0f;
+#pragma unroll
+        for (int gi = 0; gi < G; ++gi) a += red[gi * DK + i];
+        out[(size_t)b * d + (size_t)h * DK + i] = a * inv;
+    }
+}
+
+template <int DK>
+static nnb_status launch_attn_decode_bf16(nnb_engine* e, const float* qkv, void* kcache, void* vcache, size_t own_alloc,
+                                          const void* kpre, const void* vpre, size_t pre_len, size_t pre_alloc, size_t group,
+                                          const float* rope_cos, const float* rope_sin, const int* d_pos, size_t B, size_t H,
+                                          float* out)
+{
+    const size_t ctx_total = pre_len + own_alloc;
+    constexpr size_t G = 4 * (32 / (DK / 8));
+    const size_t smem = (DK + G * DK + ((ctx_total + 3) & ~(size_t)3)) * sizeof(float);
+    NNB_REQUIRE(smem <= 200 * 1024, "attn_decode: context %zu too long for one CTA", ctx_total);
+    auto kern = attn_decode_bf16_kernel<DK>;
+    static size_t cfg = 0;
+    if (smem > cfg) {
+        NNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        cfg = smem;
+    }
+    kern<<<(unsigned)(B * H), 128, smem, e->stream>>>(qkv, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, (int)own_alloc,
+                                                      (const __nv_bfloat16*)kpre, (const __nv_bfloat16*)vpre, (int)pre_len,
+                                                      (int)pre_alloc, (int)group, rope_cos, rope_sin, d_pos, (int)B, (int)H,
+                                                      (int)ctx_total, 1.0f / sqrtf((float)DK), out);
+    e->launches++;
+    NNB_CHECK_LAUNCH("attn_decode_bf16_kernel");
+    return NNB_OK;
+}
+
 nnb_status launch_attn_decode(nnb_engine* e, bool exact, const float* qkv, void* kcache, void* vcache,
                               size_t own_alloc, const void* kpre, const void* vpre, size_t pre_len, size_t pre_alloc,
                               size_t group, const float* rope_cos, const float* rope_sin, const int* d_pos, size_t B,
@@ -350,6 +521,12 @@ nnb_status launch_attn_decode(nnb_engine* e, bool exact, const float* qkv, void*
 {
     NNB_REQUIRE(dk % 4 == 0 && dk <= 128 && dk >= 8, "attn_decode: head dim %zu unsupported (multiple of 4, <= 128)", dk);
     NNB_REQUIRE(group >= 1 && (pre_len == 0 || (kpre && vpre)), "attn_decode: bad prefix arguments");
+    if (!exact && dk == 128)
+        return launch_attn_decode_bf16<128>(e, qkv, kcache, vcache, own_alloc, kpre, vpre, pre_len, pre_alloc, group, rope_cos,
+                                            rope_sin, d_pos, B, H, out);
+    if (!exact && dk == 64)
+        return launch_attn_decode_bf16<64>(e, qkv, kcache, vcache, own_alloc, kpre, vpre, pre_len, pre_alloc, group, rope_cos,
+                                           rope_sin, d_pos, B, H, out);
     const float scale = 1.0f / sqrtf((float)dk);
     const size_t acc_sz = exact ? 8 : 4;
     const size_t ctx_total = pre_len + own_alloc;

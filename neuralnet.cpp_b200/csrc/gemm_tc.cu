@@ -9,10 +9,12 @@
 // with dyb = bf16(dy*tau) and xs = bf16(s*q) prepared by small elementwise kernels, and the ternary
 // weights expanded once per requantisation to int8 (K permuted like q) and to bf16.
 //
-// Roles inside a CTA (192 threads): warp 0 issues TMA loads into a 4-stage shared-memory ring,
-// warp 1 issues tcgen05.mma (one thread) and owns the TMEM allocation, warps 2-5 drain the
-// accumulator (tcgen05.ld) through the epilogue.  Two 256-column accumulators let the epilogue of one
-// tile overlap the main loop of the next.  Every mbarrier wait is bounded: on expiry the kernel raises
+// Roles inside a CTA (320 threads): warp 0 issues TMA loads into a shared-memory ring (4 to 8 stages,
+// as many as fit), warp 1 issues tcgen05.mma (one thread) and owns the TMEM allocation, warps 2-9 drain
+// the accumulator (tcgen05.ld) through the epilogue, two warps per TMEM lane quarter, each taking half of
+// the tile's columns.  Two accumulators of BN columns let the epilogue of one tile overlap the main loop
+// of the next.  The output tile is 128 x BN with BN in {64, 128, 192, 256}: the large training GEMMs use
+// 256, the forward at a few hundred tokens picks the width that fills the SMs best.  Every mbarrier wait is bounded: on expiry the kernel raises
 // an error flag and all roles leave their loops, TMEM is released, and the host reports NNB_ERR_TIMEOUT.
 #include <cuda.h>
 
@@ -25,11 +27,20 @@
 namespace nnb {
 namespace tc {
 
-constexpr int BM = 128, BN = 256, STAGES = 4;
-constexpr int STAGE_A = BM * 128, STAGE_B = BN * 128;  // bytes: 128 B of K (or 64 k-rows x 128 B) per row
-constexpr int STAGE_BYTES = STAGE_A + STAGE_B;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
-constexpr int THREADS = 192;
+constexpr int BM = 128;
+constexpr int STAGE_A = BM * 128;  // bytes: 128 B of K (or 64 k-rows x 128 B) per row
+constexpr int MAX_STAGES = 8;
+constexpr int THREADS = 320;
+constexpr int EPI_WARPS = 8;
+template <int BN>
+struct Tile {
+    static constexpr int STAGE_B = BN * 128;
+    static constexpr int STAGE_BYTES = STAGE_A + STAGE_B;
+    static constexpr int FIT = (200 * 1024) / STAGE_BYTES;
+    static constexpr int STAGES = FIT > MAX_STAGES ? MAX_STAGES : FIT;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr uint32_t TMEM_COLS = 2 * BN <= 128 ? 128u : (2 * BN <= 256 ? 256u : 512u);
+};
 constexpr uint32_t SPIN_LIMIT = 1u << 24;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -126,15 +137,21 @@ struct Epi {
     const float* bias;
     const float* residual;
     int accumulate;
+    // stacked matrices: column c belongs to matrix c / n_mat and lands at out + (c / n_mat) * mat_stride +
+    // row * n_mat + c % n_mat (n_mat = N and mat_stride = 0 for a single matrix)
+    int n_mat;
+    size_t mat_stride;
 };
 
 // KIND 0: int8 (A, B K-major, 128 k per stage).  KIND 1: bf16 (64 k per stage), A/B K- or MN-major.
 // EPI 0: forward, 1: plain store/accumulate.
-template <int KIND, bool A_MN, bool B_MN, int EPI>
+template <int KIND, bool A_MN, bool B_MN, int EPI, int BN>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Epi ep, int M, int N,
                int KC, int* __restrict__ err)
 {
+    constexpr int STAGES = Tile<BN>::STAGES, STAGE_BYTES = Tile<BN>::STAGE_BYTES;
+    constexpr uint32_t TMEM_COLS = Tile<BN>::TMEM_COLS;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
@@ -150,6 +167,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int ktiles = (KC + KE - 1) / KE;
     const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
     const int n_tiles = tiles_m * tiles_n;
+    // with few row tiles, CTAs that run side by side take the row tiles of one column tile, so a tile of B
+    // (the weights, in the forward) comes from DRAM once and from L2 for the others
+    const bool m_fast = tiles_m <= 8;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < STAGES; ++i) {
@@ -158,13 +178,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&acc_full[i], 1);
-            mbar_init(&acc_empty[i], 4);
+            mbar_init(&acc_empty[i], EPI_WARPS);
         }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -178,7 +198,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             uint32_t it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-                const int tm = tile / tiles_n, tn = tile % tiles_n;
+                const int tm = m_fast ? tile % tiles_m : tile / tiles_n, tn = m_fast ? tile / tiles_m : tile % tiles_n;
                 for (int kt = 0; kt < ktiles && ok; ++kt, ++it) {
                     const int st = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
@@ -235,25 +255,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             if (!ok) atomicExch(err, 1);
         }
     } else {
-        // ---------------- epilogue: warps 2..5, TMEM lane quarter = warp % 4
+        // ---------------- epilogue: warps 2..9, TMEM lane quarter = warp % 4, column half = (warp - 2) / 4
         const int quarter = warp & 3;
+        const int chalf = (warp - 2) >> 2;
         uint32_t tcount = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++tcount) {
-            const int tm = tile / tiles_n, tn = tile % tiles_n;
+            const int tm = m_fast ? tile % tiles_m : tile / tiles_n, tn = m_fast ? tile / tiles_m : tile % tiles_n;
             const int acc = tcount & 1;
             if (!mbar_wait(&acc_full[acc], (tcount >> 1) & 1, abort_flag)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const int row = tm * BM + quarter * 32 + lane;
             const float srow = (EPI == 0 && row < M) ? ep.s[row] : 0.0f;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
+            for (int c0 = chalf * (BN / 2); c0 < (chalf + 1) * (BN / 2); c0 += 32) {
                 uint32_t r[32];
                 tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + c0, r);
                 const int col0 = tn * BN + c0;
                 if (row < M && col0 < N) {
-                    float* dst = ep.out + (size_t)row * N + col0;
-                    const bool vec = (col0 + 32 <= N) && ((N & 3) == 0);
+                    const int mat = col0 / ep.n_mat;
+                    const size_t off = (size_t)mat * ep.mat_stride + (size_t)row * ep.n_mat + (col0 - mat * ep.n_mat);
+                    float* dst = ep.out + off;
+                    const bool vec = (col0 + 32 <= N) && ((ep.n_mat & 3) == 0);
                     float v[32];
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
@@ -263,7 +286,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                             if (col < N) {
                                 x = __fmul_rn(__fmul_rn(ep.tau[col], srow), (float)(int)r[j]);
                                 if (ep.bias) x = __fadd_rn(x, ep.bias[col]);
-                                if (ep.residual) x = __fadd_rn(ep.residual[(size_t)row * N + col], x);
+                                if (ep.residual) x = __fadd_rn(ep.residual[off + j], x);
                             }
                             v[j] = x;
                         } else {
@@ -296,7 +319,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512u) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
 }
 
@@ -347,10 +370,11 @@ static nnb_status make_map(CUtensorMap* tm, const void* base, CUtensorMapDataTyp
     return NNB_OK;
 }
 
-template <int KIND, bool A_MN, bool B_MN, int EPI>
+template <int KIND, bool A_MN, bool B_MN, int EPI, int BN>
 static nnb_status launch(nnb_engine* e, const CUtensorMap& ta, const CUtensorMap& tb, const Epi& ep, size_t M, size_t N, size_t KC)
 {
-    auto kern = gemm_tc_kernel<KIND, A_MN, B_MN, EPI>;
+    auto kern = gemm_tc_kernel<KIND, A_MN, B_MN, EPI, BN>;
+    constexpr int SMEM_BYTES = Tile<BN>::SMEM_BYTES;
     static bool cfg = false;
     if (!cfg) {
         NNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
@@ -367,16 +391,66 @@ static nnb_status launch(nnb_engine* e, const CUtensorMap& ta, const CUtensorMap
 
 }  // namespace tc
 
-// forward: q (T,K) permuted int8, w8 (OUT,K) int8 trits in the same K permutation
-nnb_status launch_tc_forward(nnb_engine* e, const int8_t* q, const int8_t* w8, const float* tau, const float* s,
-                             const float* bias, const float* residual, size_t t, size_t k, size_t out, float* y)
+// Width of the forward output tile.  The int8 tensor pipe is the bound (a 128 x 256 x 32 kind::i8 instruction
+// occupies it for 512 clocks, and narrower instructions in proportion), so a launch takes about
+// ceil(tiles / SMs) * BN: the choice only trades rounding of the last round of tiles; ties go to the wider
+// tile, which pulls fewer bytes through L2.
+static int g_forward_bn_override = 0;
+static int choose_forward_bn(size_t t, size_t out, int sm_count)
+{
+    if (g_forward_bn_override) return g_forward_bn_override;
+    const int cand[4] = {256, 192, 128, 64};
+    int best = 256;
+    size_t best_cost = (size_t)-1;
+    for (int bn : cand) {
+        const size_t tiles = ceil_div(t, (size_t)tc::BM) * ceil_div(out, (size_t)bn);
+        const size_t cost = ceil_div(tiles, (size_t)sm_count) * (size_t)bn;
+        if (cost < best_cost) {
+            best_cost = cost;
+            best = bn;
+        }
+    }
+    return best;
+}
+
+template <int BN>
+static nnb_status tc_forward_bn(nnb_engine* e, const int8_t* q, const int8_t* w8, const tc::Epi& ep, size_t t, size_t k, size_t out)
 {
     using namespace tc;
     CUtensorMap ta, tb;
     NNB_TRY(make_map(&ta, q, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, t, k, 128, BM));
     NNB_TRY(make_map(&tb, w8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, out, k, 128, BN));
-    Epi ep{y, tau, s, bias, residual, 0};
-    return launch<0, false, false, 0>(e, ta, tb, ep, t, out, k);
+    return launch<0, false, false, 0, BN>(e, ta, tb, ep, t, out, k);
+}
+
+// forward: q (T,K) permuted int8, w8 (OUT,K) int8 trits in the same K permutation
+// n_mats > 1: w8 / tau / bias hold n_mats matrices of `out` rows one after the other and matrix m writes the
+// (t, out) block at y + m * y_stride; one launch covers them all when out is a multiple of 32
+nnb_status launch_tc_forward(nnb_engine* e, const int8_t* q, const int8_t* w8, const float* tau, const float* s,
+                             const float* bias, const float* residual, size_t t, size_t k, size_t out, float* y,
+                             size_t n_mats, size_t y_stride)
+{
+    if (n_mats > 1 && out % 32 != 0) {
+        for (size_t m = 0; m < n_mats; ++m)
+            NNB_TRY(launch_tc_forward(e, q, w8 + m * out * k, tau + m * out, s, bias ? bias + m * out : nullptr,
+                                      residual ? residual + m * y_stride : nullptr, t, k, out, y + m * y_stride, 1, 0));
+        return NNB_OK;
+    }
+    tc::Epi ep{y, tau, s, bias, residual, 0, (int)out, n_mats > 1 ? y_stride : 0};
+    out *= n_mats;
+    switch (choose_forward_bn(t, out, e->sm_count)) {
+        case 64: return tc_forward_bn<64>(e, q, w8, ep, t, k, out);
+        case 128: return tc_forward_bn<128>(e, q, w8, ep, t, k, out);
+        case 192: return tc_forward_bn<192>(e, q, w8, ep, t, k, out);
+        default: return tc_forward_bn<256>(e, q, w8, ep, t, k, out);
+    }
+}
+
+nnb_status tc_set_forward_tile(int bn)
+{
+    NNB_REQUIRE(bn == 0 || bn == 64 || bn == 128 || bn == 192 || bn == 256, "forward tile width %d: 0 (automatic), 64, 128, 192 or 256", bn);
+    g_forward_bn_override = bn;
+    return NNB_OK;
 }
 
 // dX: dyb (T,OUT) bf16, wb (OUT,K) bf16 trits; dx (T,K) f32
@@ -387,8 +461,8 @@ nnb_status launch_tc_dx(nnb_engine* e, const __nv_bfloat16* dyb, const __nv_bflo
     CUtensorMap ta, tb;
     NNB_TRY(make_map(&ta, dyb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, t, out, 64, BM));
     NNB_TRY(make_map(&tb, wb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, out, k, 64, 64));
-    Epi ep{dx, nullptr, nullptr, nullptr, nullptr, accumulate ? 1 : 0};
-    return launch<1, false, true, 1>(e, ta, tb, ep, t, k, out);
+    Epi ep{dx, nullptr, nullptr, nullptr, nullptr, accumulate ? 1 : 0, (int)k, 0};
+    return launch<1, false, true, 1, 256>(e, ta, tb, ep, t, k, out);
 }
 
 // dW: dyb (T,OUT) bf16, xs (T,K) bf16; dw (OUT,K) f32 +=
@@ -399,8 +473,8 @@ nnb_status launch_tc_dw(nnb_engine* e, const __nv_bfloat16* dyb, const __nv_bflo
     CUtensorMap ta, tb;
     NNB_TRY(make_map(&ta, dyb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, t, out, 64, 64));
     NNB_TRY(make_map(&tb, xs, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, t, k, 64, 64));
-    Epi ep{dw, nullptr, nullptr, nullptr, nullptr, 1};
-    return launch<1, true, true, 1>(e, ta, tb, ep, out, k, t);
+    Epi ep{dw, nullptr, nullptr, nullptr, nullptr, 1, (int)k, 0};
+    return launch<1, true, true, 1, 256>(e, ta, tb, ep, out, k, t);
 }
 
 // reads (and clears) the device error flag of the tensor-core GEMMs; synchronises the stream

@@ -141,15 +141,11 @@ nnb_status policy_ensure_wb(nnb_policy* p)
 nnb_status policy_linear_fwd(nnb_policy* p, const LinW& l, size_t n_mats, const int8_t* q, const float* s,
                              const int32_t* qsum, size_t T, const float* residual, float* y, size_t y_stride)
 {
-    // below a couple of thousand tokens the 128x256 tcgen05 tiles leave most SMs idle: the mma.sync
-    // kernel with its smaller tiles (and one launch for stacked matrices) is faster there
-    if (!p->cfg.exact && p->w8 && T >= 2048) {
-        for (size_t m = 0; m < n_mats; ++m)
-            NNB_TRY(launch_tc_forward(p->e, q, p->w8 + (l.packed_off + m * l.out * (l.in / 16)) * 16,
-                                      p->tau + l.tau_off + m * l.out, s, p->params + l.b_off + m * l.out, residual, T,
-                                      l.in, l.out, y + m * y_stride));
-        return NNB_OK;
-    }
+    // from a few hundred tokens up the tcgen05 kernel wins (its tile width follows the shape); below that the
+    // persistent mma.sync kernels stream the 2-bit container, a quarter of the int8 copy's bytes
+    if (!p->cfg.exact && p->w8 && T >= 256)
+        return launch_tc_forward(p->e, q, p->w8 + l.packed_off * 16, p->tau + l.tau_off, s, p->params + l.b_off, residual, T,
+                                 l.in, l.out, y, n_mats, y_stride);
     return launch_bitlinear_fwd_tm(p->e, p->packed + l.packed_off, n_mats > 1 ? l.out * (l.in / 16) : 0, p->tau + l.tau_off,
                                    p->params + l.b_off, residual, q, s, qsum, n_mats, T, l.in, l.out, y, y_stride, NNB_F32,
                                    nullptr);

@@ -307,6 +307,11 @@ def bitlinear_fwd_tc(self, w8, tau, bias, q, s, residual=None, y=None):
     return y
 
 
+def set_tc_forward_tile(self, bn: int = 0):
+    """Process-wide width of the tensor-core forward's output tile (64/128/192/256; 0 = automatic)."""
+    check(self._lib.nnb_tc_set_forward_tile(int(bn)))
+
+
 def bitlinear_bwd_tc(self, dy, tau, wb, q, s, k, want_dx=True, dw=None, dx=None, accumulate_dx=False):
     t, out = dy.shape
     dyb = torch.empty((t, out), device=self.device, dtype=torch.bfloat16)
@@ -323,6 +328,7 @@ def check_device_errors(self):
 
 
 Engine.expand_weights = expand_weights
+Engine.set_tc_forward_tile = set_tc_forward_tile
 Engine.bitlinear_fwd_tc = bitlinear_fwd_tc
 Engine.bitlinear_bwd_tc = bitlinear_bwd_tc
 Engine.check_device_errors = check_device_errors

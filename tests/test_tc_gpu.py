@@ -47,6 +47,30 @@ def test_forward_tc_bit_exact(eng, orc, t, k, out):
     assert torch.equal(y2, res + y_mma)
 
 
+@pytest.mark.parametrize("bn", [64, 128, 192, 256])
+@pytest.mark.parametrize("t,k,out", [(130, 192, 300), (512, 2048, 2048), (300, 5632, 1000)])
+def test_forward_tc_every_tile_width(eng, orc, bn, t, k, out):
+    """The result of the forward does not depend on the width of its output tile."""
+    W, tau, X, bias = _case(orc, t, k, out, t + k + out + bn)
+    packed = orc.trit_pack(W, tau)
+    q_ref, s_ref = orc.act_quant_tm(X)
+    y_ref = orc.bitlinear_i8_tm(packed, tau, bias, q_ref, s_ref, want_acc=False)
+    q, s, _ = eng.act_quant_tm(_dev(X, eng))
+    w8, _ = eng.expand_weights(_dev(packed.view(np.int32), eng), k, want_bf16=False)
+    eng.set_tc_forward_tile(bn)
+    try:
+        y = eng.bitlinear_fwd_tc(w8, _dev(tau, eng), _dev(bias, eng), q, s)
+        eng.check_device_errors()
+    finally:
+        eng.set_tc_forward_tile(0)
+    assert np.array_equal(y.cpu().numpy().view(np.uint32), y_ref.view(np.uint32))
+
+
+def test_forward_tile_width_rejected(eng):
+    with pytest.raises(Exception):
+        eng.set_tc_forward_tile(100)
+
+
 @pytest.mark.parametrize("t,k,out", [(128, 256, 256), (64, 64, 64), (130, 192, 328), (300, 2048, 384), (1000, 320, 1000)])
 def test_backward_tc(eng, orc, t, k, out):
     W, tau, X, _ = _case(orc, t, k, out, t + 3 * k + out)
