@@ -166,6 +166,17 @@ nnb_status nnb_attention_fwd(nnb_engine* e, const float* d_q, const float* d_k, 
 nnb_status nnb_attention_bwd(nnb_engine* e, const float* d_q, const float* d_k, const float* d_v, const float* d_out,
                              const float* d_dout, const float* d_lse, size_t n_seq, size_t seq_len, size_t n_head,
                              size_t dk, int exact, float* d_delta, float* d_dq, float* d_dk, float* d_dv);
+/* The same operators with the rotary embedding inside (AttentionBase with rope,
+ * include/neuralnet.cpp/compute_layer_attention.hpp:698-750 applies it to q and k before the core): q and k
+ * are un-rotated, d_rope_cos / d_rope_sin are (seq_len, dk/2) tables indexed by the position in the
+ * sequence, and d_dq / d_dk are gradients with respect to the un-rotated q and k. */
+nnb_status nnb_attention_rope_fwd(nnb_engine* e, const float* d_q, const float* d_k, const float* d_v,
+                                  const float* d_rope_cos, const float* d_rope_sin, size_t n_seq, size_t seq_len,
+                                  size_t n_head, size_t dk, int exact, float* d_out, float* d_lse);
+nnb_status nnb_attention_rope_bwd(nnb_engine* e, const float* d_q, const float* d_k, const float* d_v,
+                                  const float* d_rope_cos, const float* d_rope_sin, const float* d_out, const float* d_dout,
+                                  const float* d_lse, size_t n_seq, size_t seq_len, size_t n_head, size_t dk, int exact,
+                                  float* d_delta, float* d_dq, float* d_dk, float* d_dv);
 /* synchronises and reports NNB_ERR_TIMEOUT if a kernel gave up on a bounded device-side wait */
 nnb_status nnb_engine_check(nnb_engine* e);
 

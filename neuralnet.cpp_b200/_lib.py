@@ -58,6 +58,8 @@ _SIGNATURES = {
     "nnb_engine_check": (_I, [_P]),
     "nnb_attention_fwd": (_I, [_P, _P, _P, _P, _SZ, _SZ, _SZ, _SZ, _I, _P, _P]),
     "nnb_attention_bwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _SZ, _SZ, _SZ, _SZ, _I, _P, _P, _P, _P]),
+    "nnb_attention_rope_fwd": (_I, [_P, _P, _P, _P, _P, _P, _SZ, _SZ, _SZ, _SZ, _I, _P, _P]),
+    "nnb_attention_rope_bwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _SZ, _SZ, _SZ, _SZ, _I, _P, _P, _P, _P]),
     "nnb_bitlinear_fwd_host": (_I, [_P, _P, _P, _P, _P, _SZ, _SZ, _SZ, _P]),
     "nnb_policy_create": (_I, [_P, _P, C.POINTER(_P)]),
     "nnb_policy_destroy": (None, [_P]),

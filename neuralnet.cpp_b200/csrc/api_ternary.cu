@@ -165,6 +165,73 @@ nnb_status nnb_attention_bwd(nnb_engine* e, const float* d_q, const float* d_k, 
                            d_dk, d_dv);
 }
 
+// Attention with the rotary embedding inside the operator: q and k come un-rotated, the gradients are with
+// respect to the un-rotated q and k.  The exact mode composes the rotation kernel with the attention
+// kernels on scratch copies; the fast mode uses the fused bf16 path.
+nnb_status nnb_attention_rope_fwd(nnb_engine* e, const float* d_q, const float* d_k, const float* d_v,
+                                  const float* d_rope_cos, const float* d_rope_sin, size_t n_seq, size_t seq_len,
+                                  size_t n_head, size_t dk, int exact, float* d_out, float* d_lse)
+{
+    NNB_REQUIRE(e && d_q && d_k && d_v && d_rope_cos && d_rope_sin && d_out && d_lse, "attention_rope_fwd: NULL argument");
+    NNB_REQUIRE(n_seq > 0 && seq_len > 0 && n_head > 0 && dk > 0 && dk % 4 == 0, "attention_rope_fwd: bad shape");
+    const size_t T = n_seq * seq_len, td = T * n_head * dk;
+    if (!exact && attn_b16_supported(dk, n_head * dk)) {
+        __nv_bfloat16* tmp = nullptr;
+        NNB_CUDA(cudaMallocAsync((void**)&tmp, 3 * td * sizeof(__nv_bfloat16), e->stream));
+        nnb_status st = launch_rope_pack_b16(e, d_q, d_k, d_v, d_rope_cos, d_rope_sin, T, seq_len, n_head, dk, tmp);
+        if (st == NNB_OK) st = launch_attn_fwd_b16(e, tmp, tmp + td, tmp + 2 * td, n_seq, seq_len, n_head, dk, d_out, d_lse);
+        cudaFreeAsync(tmp, e->stream);
+        return st;
+    }
+    float* tmp = nullptr;
+    NNB_CUDA(cudaMallocAsync((void**)&tmp, 2 * td * sizeof(float), e->stream));
+    nnb_status st = NNB_OK;
+    if (cudaMemcpyAsync(tmp, d_q, td * 4, cudaMemcpyDeviceToDevice, e->stream) != cudaSuccess ||
+        cudaMemcpyAsync(tmp + td, d_k, td * 4, cudaMemcpyDeviceToDevice, e->stream) != cudaSuccess)
+        st = NNB_ERR_CUDA;
+    if (st == NNB_OK) st = launch_rope(e, tmp, d_rope_cos, d_rope_sin, T, seq_len, n_head, dk, false);
+    if (st == NNB_OK) st = launch_rope(e, tmp + td, d_rope_cos, d_rope_sin, T, seq_len, n_head, dk, false);
+    if (st == NNB_OK) st = launch_attn_fwd(e, exact != 0, tmp, tmp + td, d_v, n_seq, seq_len, n_head, dk, d_out, d_lse);
+    cudaFreeAsync(tmp, e->stream);
+    return st;
+}
+
+nnb_status nnb_attention_rope_bwd(nnb_engine* e, const float* d_q, const float* d_k, const float* d_v,
+                                  const float* d_rope_cos, const float* d_rope_sin, const float* d_out, const float* d_dout,
+                                  const float* d_lse, size_t n_seq, size_t seq_len, size_t n_head, size_t dk, int exact,
+                                  float* d_delta, float* d_dq, float* d_dk, float* d_dv)
+{
+    NNB_REQUIRE(e && d_q && d_k && d_v && d_rope_cos && d_rope_sin && d_out && d_dout && d_lse && d_delta && d_dq && d_dk && d_dv,
+                "attention_rope_bwd: NULL argument");
+    NNB_REQUIRE(n_seq > 0 && seq_len > 0 && n_head > 0 && dk > 0 && dk % 4 == 0, "attention_rope_bwd: bad shape");
+    const size_t T = n_seq * seq_len, td = T * n_head * dk;
+    if (!exact && attn_b16_supported(dk, n_head * dk)) {
+        __nv_bfloat16* tmp = nullptr;
+        NNB_CUDA(cudaMallocAsync((void**)&tmp, 4 * td * sizeof(__nv_bfloat16), e->stream));
+        nnb_status st = launch_rope_pack_b16(e, d_q, d_k, d_v, d_rope_cos, d_rope_sin, T, seq_len, n_head, dk, tmp);
+        if (st == NNB_OK)
+            st = launch_attn_bwd_b16(e, tmp, tmp + td, tmp + 2 * td, d_out, d_dout, d_lse, d_delta, tmp + 3 * td, d_rope_cos,
+                                     d_rope_sin, n_seq, seq_len, n_head, dk, d_dq, d_dk, d_dv);
+        cudaFreeAsync(tmp, e->stream);
+        return st;
+    }
+    float* tmp = nullptr;
+    NNB_CUDA(cudaMallocAsync((void**)&tmp, 2 * td * sizeof(float), e->stream));
+    nnb_status st = NNB_OK;
+    if (cudaMemcpyAsync(tmp, d_q, td * 4, cudaMemcpyDeviceToDevice, e->stream) != cudaSuccess ||
+        cudaMemcpyAsync(tmp + td, d_k, td * 4, cudaMemcpyDeviceToDevice, e->stream) != cudaSuccess)
+        st = NNB_ERR_CUDA;
+    if (st == NNB_OK) st = launch_rope(e, tmp, d_rope_cos, d_rope_sin, T, seq_len, n_head, dk, false);
+    if (st == NNB_OK) st = launch_rope(e, tmp + td, d_rope_cos, d_rope_sin, T, seq_len, n_head, dk, false);
+    if (st == NNB_OK)
+        st = launch_attn_bwd(e, exact != 0, tmp, tmp + td, d_v, d_out, d_dout, d_lse, d_delta, n_seq, seq_len, n_head, dk, d_dq,
+                             d_dk, d_dv);
+    if (st == NNB_OK) st = launch_rope(e, d_dq, d_rope_cos, d_rope_sin, T, seq_len, n_head, dk, true);
+    if (st == NNB_OK) st = launch_rope(e, d_dk, d_rope_cos, d_rope_sin, T, seq_len, n_head, dk, true);
+    cudaFreeAsync(tmp, e->stream);
+    return st;
+}
+
 nnb_status nnb_engine_check(nnb_engine* e)
 {
     NNB_REQUIRE(e, "engine is NULL");

@@ -192,14 +192,19 @@ nnb_status tc_check_errors(nnb_engine* e);
 nnb_status tc_set_forward_tile(int bn);
 nnb_status launch_expand_weights(nnb_engine* e, const uint32_t* wq, size_t rows, size_t k, int8_t* w8, __nv_bfloat16* wb);
 nnb_status launch_scale_to_bf16(nnb_engine* e, const float* dy, const float* tau, size_t t, size_t out, __nv_bfloat16* dyb);
+nnb_status launch_scale_colsum(nnb_engine* e, const float* dy, const float* tau, size_t t, size_t out, __nv_bfloat16* dyb,
+                               float* db);
 nnb_status launch_dequant_to_bf16(nnb_engine* e, const int8_t* q, const float* s, size_t t, size_t k, __nv_bfloat16* xs);
 
-// ---- attn_tc.cu (bf16 tensor-core attention of the teacher-forced pass, head dims 64 and 128)
-bool attn_tc_supported(size_t dk, size_t d);
-nnb_status launch_attn_fwd_tc(nnb_engine* e, const float* q, const float* k, const float* v, size_t n_seq, size_t S,
-                              size_t H, size_t dk, float* out, float* lse);
-nnb_status launch_attn_bwd_tc(nnb_engine* e, const float* q, const float* k, const float* v, const float* dout,
-                              const float* lse, const float* delta, size_t n_seq, size_t S, size_t H, size_t dk,
-                              float* dq, float* dkk, float* dvv);
+// ---- attn_b16.cu (bf16 tensor-core attention of the teacher-forced pass, head dims 64 and 128)
+bool attn_b16_supported(size_t dk, size_t d);
+nnb_status launch_rope_pack_b16(nnb_engine* e, const float* q, const float* k, const float* v, const float* rope_cos,
+                                const float* rope_sin, size_t T, size_t S, size_t H, size_t dk, __nv_bfloat16* out);
+nnb_status launch_attn_fwd_b16(nnb_engine* e, const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v,
+                               size_t n_seq, size_t S, size_t H, size_t dk, float* out, float* lse);
+nnb_status launch_attn_bwd_b16(nnb_engine* e, const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v,
+                               const float* out, const float* dout, const float* lse, float* delta, __nv_bfloat16* dob,
+                               const float* rope_cos, const float* rope_sin, size_t n_seq, size_t S, size_t H, size_t dk,
+                               float* dq, float* dkk, float* dvv);
 
 }  // namespace nnb

@@ -143,6 +143,99 @@ row_quant_kernel(const float* __restrict__ in, const float* __restrict__ gamma, 
     }
 }
 
+// Fast-mode variant of row_quant_kernel: same layout and outputs, 16-byte loads and stores, hardware
+// exp / divide approximations and f32 sums (the exact mode keeps the kernel above, whose every rounding
+// step follows the reference).
+template <int MODE>
+__global__ void __launch_bounds__(256)
+row_quant_fast_kernel(const float* __restrict__ in, const float* __restrict__ gamma, int k, int in_stride,
+                      int8_t* __restrict__ q, float* __restrict__ s, int32_t* __restrict__ qsum, float* __restrict__ f_out)
+{
+    extern __shared__ __align__(16) float row[];
+    __shared__ float red_f[8];
+    __shared__ int red_i[8];
+    const size_t tok = blockIdx.x;
+    const float4* x4 = reinterpret_cast<const float4*>(in + tok * (size_t)in_stride);
+    float4* row4 = reinterpret_cast<float4*>(row);
+    float4* f4 = f_out ? reinterpret_cast<float4*>(f_out + tok * (size_t)k) : nullptr;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nv = k >> 2;
+
+    float sinv = 0.0f;
+    if (MODE == 0) {
+        float ss = 0.0f;
+        for (int c = tid; c < nv; c += 256) {
+            const float4 v = x4[c];
+            row4[c] = v;
+            ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+        }
+        ss = warp_sum(ss);
+        if (lane == 0) red_f[warp] = ss;
+        __syncthreads();
+        ss = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) ss += red_f[w];
+        sinv = rsqrtf(ss / (float)k + 1e-5f);
+        __syncthreads();
+    }
+    float mx = 0.0f;
+    for (int c = tid; c < nv; c += 256) {
+        float4 v;
+        if (MODE == 0) {
+            const float4 x = row4[c];
+            const float4 g = reinterpret_cast<const float4*>(gamma)[c];
+            v = make_float4(x.x * sinv * g.x, x.y * sinv * g.y, x.z * sinv * g.z, x.w * sinv * g.w);
+        } else if (MODE == 1) {
+            const float4 x = x4[c];
+            v = make_float4(__fdividef(x.x, 1.0f + __expf(-1.702f * x.x)), __fdividef(x.y, 1.0f + __expf(-1.702f * x.y)),
+                            __fdividef(x.z, 1.0f + __expf(-1.702f * x.z)), __fdividef(x.w, 1.0f + __expf(-1.702f * x.w)));
+        } else if (MODE == 2) {
+            const float4 g = x4[c], u = x4[nv + c];
+            v = make_float4(__fdividef(g.x, 1.0f + __expf(-g.x)) * u.x, __fdividef(g.y, 1.0f + __expf(-g.y)) * u.y,
+                            __fdividef(g.z, 1.0f + __expf(-g.z)) * u.z, __fdividef(g.w, 1.0f + __expf(-g.w)) * u.w);
+        } else {
+            v = x4[c];
+        }
+        row4[c] = v;
+        if (f4) f4[c] = v;
+        mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+    }
+    mx = warp_max(mx);
+    if (lane == 0) red_f[warp] = mx;
+    __syncthreads();
+    mx = red_f[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) mx = fmaxf(mx, red_f[w]);
+    const float sc = __fmul_rn(mx, 1.0f / 127.0f);
+    const float inv = sc > 0.0f ? 1.0f / sc : 0.0f;
+    uint32_t* qrow = reinterpret_cast<uint32_t*>(q + tok * (size_t)k);
+    int local = 0;
+    for (int w = tid; w < nv; w += 256) {
+        const int blk = w >> 4, wd = w & 15;
+        const int i = wd >> 2, t = wd & 3;
+        uint32_t word = 0;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            float v = row[blk * 64 + 16 * t + 4 * b + i] * inv;
+            v = (v != v) ? 0.0f : fminf(fmaxf(v, -127.0f), 127.0f);
+            const int qi = (int)roundf(v);
+            local += qi;
+            word |= (uint32_t)(uint8_t)(int8_t)qi << (8 * b);
+        }
+        qrow[w] = word;
+    }
+    local = warp_sum_i(local);
+    if (lane == 0) red_i[warp] = local;
+    __syncthreads();
+    if (tid == 0) {
+        int tot = 0;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) tot += red_i[w];
+        qsum[tok] = tot;
+        s[tok] = sc;
+    }
+}
+
 template <int MODE>
 static nnb_status launch_row_quant_mode(nnb_engine* e, bool exact, const float* in,
                                         const float* gamma, size_t t, size_t k, size_t in_stride,
@@ -155,10 +248,15 @@ static nnb_status launch_row_quant_mode(nnb_engine* e, bool exact, const float* 
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
         NNB_CUDA(cudaFuncSetAttribute(row_quant_kernel<MODE, false>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+        NNB_CUDA(cudaFuncSetAttribute(row_quant_fast_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
         cfg = true;
     }
+    const bool aligned = in_stride % 4 == 0 && ((uintptr_t)in & 15) == 0 && (!f_out || ((uintptr_t)f_out & 15) == 0) &&
+                         (MODE != 0 || ((uintptr_t)gamma & 15) == 0);
     if (exact)
         row_quant_kernel<MODE, true><<<(unsigned)t, 256, smem, e->stream>>>(in, gamma, (int)k, (int)in_stride, q, s, qsum, f_out);
+    else if (aligned)
+        row_quant_fast_kernel<MODE><<<(unsigned)t, 256, smem, e->stream>>>(in, gamma, (int)k, (int)in_stride, q, s, qsum, f_out);
     else
         row_quant_kernel<MODE, false><<<(unsigned)t, 256, smem, e->stream>>>(in, gamma, (int)k, (int)in_stride, q, s, qsum, f_out);
     e->launches++;

@@ -546,6 +546,39 @@ __global__ void scale_to_bf16_kernel(const float* __restrict__ dy, const float* 
     *reinterpret_cast<__nv_bfloat162*>(out + i) = __floats2bfloat162_rn(a, b);
 }
 
+// The two uses of dy in one pass: dyb[t,o] = bf16(dy[t,o] * tau[o]) and db[o] += sum_t dy[t,o].
+// grid (ceil(O/256), ceil(T/chunk)), 128 threads, two adjacent columns per thread.
+__global__ void __launch_bounds__(128)
+scale_colsum_kernel(const float* __restrict__ dy, const float* __restrict__ tau, int T, int O, int chunk,
+                    __nv_bfloat16* __restrict__ out, float* __restrict__ db)
+{
+    const int o = (blockIdx.x * 128 + threadIdx.x) * 2;
+    if (o >= O) return;
+    const int t0 = blockIdx.y * chunk, t1 = min(T, t0 + chunk);
+    const float2 tv = *reinterpret_cast<const float2*>(tau + o);
+    float sa = 0.0f, sb = 0.0f;
+    int t = t0;
+    for (; t + 4 <= t1; t += 4) {
+        float2 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) v[u] = *reinterpret_cast<const float2*>(dy + (size_t)(t + u) * O + o);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            sa += v[u].x;
+            sb += v[u].y;
+            *reinterpret_cast<__nv_bfloat162*>(out + (size_t)(t + u) * O + o) = __floats2bfloat162_rn(v[u].x * tv.x, v[u].y * tv.y);
+        }
+    }
+    for (; t < t1; ++t) {
+        const float2 v = *reinterpret_cast<const float2*>(dy + (size_t)t * O + o);
+        sa += v.x;
+        sb += v.y;
+        *reinterpret_cast<__nv_bfloat162*>(out + (size_t)t * O + o) = __floats2bfloat162_rn(v.x * tv.x, v.y * tv.y);
+    }
+    atomicAdd(db + o, sa);
+    atomicAdd(db + o + 1, sb);
+}
+
 // xs[t,k] = bf16(s[t] * q[t, perm(k)]) in natural feature order
 __global__ void dequant_to_bf16_kernel(const int8_t* __restrict__ q, const float* __restrict__ s, size_t T, int K,
                                        __nv_bfloat16* __restrict__ out)
@@ -571,6 +604,19 @@ nnb_status launch_scale_to_bf16(nnb_engine* e, const float* dy, const float* tau
     scale_to_bf16_kernel<<<(unsigned)ceil_div(n / 2, 256), 256, 0, e->stream>>>(dy, tau, n, (int)out, dyb);
     e->launches++;
     NNB_CHECK_LAUNCH("scale_to_bf16_kernel");
+    return NNB_OK;
+}
+
+nnb_status launch_scale_colsum(nnb_engine* e, const float* dy, const float* tau, size_t t, size_t out, __nv_bfloat16* dyb,
+                               float* db)
+{
+    NNB_REQUIRE(out % 2 == 0, "scale_colsum: out=%zu must be even", out);
+    const int chunk = 128;
+    dim3 grid((unsigned)ceil_div(out, 256), (unsigned)ceil_div(t, chunk));
+    NNB_REQUIRE(grid.y <= 65535, "scale_colsum: too many tokens (%zu)", t);
+    scale_colsum_kernel<<<grid, 128, 0, e->stream>>>(dy, tau, (int)t, (int)out, chunk, dyb, db);
+    e->launches++;
+    NNB_CHECK_LAUNCH("scale_colsum_kernel");
     return NNB_OK;
 }
 

@@ -20,6 +20,7 @@ struct LayerSave {
     float *x_in = nullptr, *qkv = nullptr, *att = nullptr, *lse = nullptr, *x_mid = nullptr, *h1 = nullptr;
     int8_t *q1 = nullptr, *q2 = nullptr, *q3 = nullptr, *q4 = nullptr;
     float *s1 = nullptr, *s2 = nullptr, *s3 = nullptr, *s4 = nullptr;
+    __nv_bfloat16* qkvb = nullptr;  // fast mode: rotated q, k and v as bf16 (3, T, d), the attention operands
 };
 
 struct TrainWs {
@@ -40,6 +41,8 @@ struct TrainWs {
     float *g = nullptr, *g2 = nullptr, *dn = nullptr, *datt = nullptr, *dqkv = nullptr, *da = nullptr, *dh1 = nullptr,
           *delta = nullptr;
     __nv_bfloat16 *dyb = nullptr, *xs = nullptr;  // bf16 operand scratch of the tcgen05 backward GEMMs
+    __nv_bfloat16* dob = nullptr;                 // bf16 copy of the attention output gradient
+    bool b16_attn = false;
 };
 
 void policy_free_train(nnb_policy* p)
@@ -63,6 +66,9 @@ static nnb_status ensure_train(nnb_policy* p, size_t n_seq, size_t S, size_t P, 
     const size_t d = c.d_model, F = c.d_ff, F1 = c.act == 1 ? 2 * F : F, V = c.vocab, H = c.n_head;
     const size_t T = n_seq * S, G = S - P, Td = n_seq * G;
     const size_t n_save = save_layers ? (size_t)c.n_layer : 1;
+    // fast mode: attention runs on bf16 copies of q, k, v; those are what a layer keeps for its backward,
+    // and the f32 projections become one buffer shared by all layers
+    w->b16_attn = !c.exact && attn_b16_supported(d / H, d);
     // carve one arena: first pass measures, second assigns
     for (int pass = 0; pass < 2; ++pass) {
         size_t off = 0;
@@ -75,7 +81,12 @@ static nnb_status ensure_train(nnb_policy* p, size_t n_seq, size_t S, size_t P, 
         for (size_t l = 0; l < n_save; ++l) {
             LayerSave s;
             s.x_in = (float*)take(T * d * 4);
-            s.qkv = (float*)take(3 * T * d * 4);
+            if (w->b16_attn) {
+                s.qkv = l == 0 ? (float*)take(3 * T * d * 4) : w->L[0].qkv;
+                s.qkvb = (__nv_bfloat16*)take(3 * T * d * 2);
+            } else {
+                s.qkv = (float*)take(3 * T * d * 4);
+            }
             s.att = (float*)take(T * d * 4);
             s.lse = (float*)take(n_seq * H * S * 4);
             s.x_mid = (float*)take(T * d * 4);
@@ -122,6 +133,7 @@ static nnb_status ensure_train(nnb_policy* p, size_t n_seq, size_t S, size_t P, 
                 const size_t dyb_elems = T * F1 > Td * V ? T * F1 : Td * V;
                 w->dyb = (__nv_bfloat16*)take(dyb_elems * 2);
                 w->xs = (__nv_bfloat16*)take(T * (F > d ? F : d) * 2);
+                if (w->b16_attn) w->dob = (__nv_bfloat16*)take(T * d * 2);
             }
         }
         if (pass == 0) {
@@ -182,11 +194,17 @@ static nnb_status forward(nnb_policy* p, const int32_t* tokens, size_t n_seq, si
         const float* x_in = (!w->saved_layers) ? ((l % 2 == 0) ? w->L[0].x_in : w->x_last) : s.x_in;
         NNB_TRY(launch_row_quant(e, 0, exact, x_in, PP + LW.ln1_g, T, d, d, s.q1, s.s1, w->qsum, nullptr));
         NNB_TRY(lin_fwd(p, LW.q, 3, s.q1, s.s1, w->qsum, T, nullptr, s.qkv, T * d));
-        if (c.pos == 1) {
-            NNB_TRY(launch_rope(e, s.qkv, p->rope_cos, p->rope_sin, T, S, H, dk, false));
-            NNB_TRY(launch_rope(e, s.qkv + T * d, p->rope_cos, p->rope_sin, T, S, H, dk, false));
+        if (w->b16_attn) {
+            NNB_TRY(launch_rope_pack_b16(e, s.qkv, s.qkv + T * d, s.qkv + 2 * T * d, c.pos == 1 ? p->rope_cos : nullptr,
+                                         c.pos == 1 ? p->rope_sin : nullptr, T, S, H, dk, s.qkvb));
+            NNB_TRY(launch_attn_fwd_b16(e, s.qkvb, s.qkvb + T * d, s.qkvb + 2 * T * d, n_seq, S, H, dk, s.att, s.lse));
+        } else {
+            if (c.pos == 1) {
+                NNB_TRY(launch_rope(e, s.qkv, p->rope_cos, p->rope_sin, T, S, H, dk, false));
+                NNB_TRY(launch_rope(e, s.qkv + T * d, p->rope_cos, p->rope_sin, T, S, H, dk, false));
+            }
+            NNB_TRY(launch_attn_fwd(e, exact, s.qkv, s.qkv + T * d, s.qkv + 2 * T * d, n_seq, S, H, dk, s.att, s.lse));
         }
-        NNB_TRY(launch_attn_fwd(e, exact, s.qkv, s.qkv + T * d, s.qkv + 2 * T * d, n_seq, S, H, dk, s.att, s.lse));
         NNB_TRY(launch_row_quant(e, 3, exact, s.att, nullptr, T, d, d, s.q2, s.s2, w->qsum, nullptr));
         NNB_TRY(lin_fwd(p, LW.o, 1, s.q2, s.s2, w->qsum, T, x_in, s.x_mid, 0));
         NNB_TRY(launch_row_quant(e, 0, exact, s.x_mid, PP + LW.ln2_g, T, d, d, s.q3, s.s3, w->qsum, nullptr));
@@ -214,11 +232,10 @@ static nnb_status lin_bwd(nnb_policy* p, const LinW& l, const float* dy, const i
     TrainWs* w = (TrainWs*)p->train;
     if (!exact && p->wb && p->wb_valid && l.out % 8 == 0 && T >= 64) {
         // tcgen05 path: dyb = bf16(dy*tau) serves both GEMMs, xs = bf16(s*q) in natural feature order
-        NNB_TRY(launch_scale_to_bf16(e, dy, p->tau + l.tau_off, T, l.out, w->dyb));
+        NNB_TRY(launch_scale_colsum(e, dy, p->tau + l.tau_off, T, l.out, w->dyb, p->grads + l.b_off));
         if (dx) NNB_TRY(launch_tc_dx(e, w->dyb, p->wb + l.packed_off * 16, T, l.in, l.out, dx, accumulate_dx));
         NNB_TRY(launch_dequant_to_bf16(e, q, s, T, l.in, w->xs));
-        NNB_TRY(launch_tc_dw(e, w->dyb, w->xs, T, l.in, l.out, p->grads + l.w_off));
-        return launch_colsum_add(e, dy, T, l.out, p->grads + l.b_off);
+        return launch_tc_dw(e, w->dyb, w->xs, T, l.in, l.out, p->grads + l.w_off);
     }
     if (dx) NNB_TRY(launch_bitlinear_dx(e, exact, dy, p->packed + l.packed_off, p->tau + l.tau_off, T, l.in, l.out, dx, accumulate_dx));
     NNB_TRY(launch_bitlinear_dw(e, exact, dy, q, s, p->tau + l.tau_off, T, l.in, l.out, p->grads + l.w_off));
@@ -250,11 +267,18 @@ static nnb_status backward(nnb_policy* p, const int32_t* tokens, size_t n_seq, s
         NNB_TRY(launch_rmsnorm_bwd(e, s.x_mid, PP + LW.ln2_g, w->dn, w->g, T, d, w->g2, GG + LW.ln2_g));
         // attention branch
         NNB_TRY(lin_bwd(p, LW.o, w->g2, s.q2, s.s2, T, w->datt, false));
-        NNB_TRY(launch_attn_bwd(e, c.exact != 0, s.qkv, s.qkv + T * d, s.qkv + 2 * T * d, s.att, w->datt, s.lse, w->delta, n_seq, S, H,
-                                dk, w->dqkv, w->dqkv + T * d, w->dqkv + 2 * T * d));
-        if (c.pos == 1) {
-            NNB_TRY(launch_rope(e, w->dqkv, p->rope_cos, p->rope_sin, T, S, H, dk, true));
-            NNB_TRY(launch_rope(e, w->dqkv + T * d, p->rope_cos, p->rope_sin, T, S, H, dk, true));
+        if (w->b16_attn) {
+            // the inverse rotation of dq and dk is part of the kernels' epilogues
+            NNB_TRY(launch_attn_bwd_b16(e, s.qkvb, s.qkvb + T * d, s.qkvb + 2 * T * d, s.att, w->datt, s.lse, w->delta, w->dob,
+                                        c.pos == 1 ? p->rope_cos : nullptr, c.pos == 1 ? p->rope_sin : nullptr, n_seq, S, H, dk,
+                                        w->dqkv, w->dqkv + T * d, w->dqkv + 2 * T * d));
+        } else {
+            NNB_TRY(launch_attn_bwd(e, c.exact != 0, s.qkv, s.qkv + T * d, s.qkv + 2 * T * d, s.att, w->datt, s.lse, w->delta, n_seq,
+                                    S, H, dk, w->dqkv, w->dqkv + T * d, w->dqkv + 2 * T * d));
+            if (c.pos == 1) {
+                NNB_TRY(launch_rope(e, w->dqkv, p->rope_cos, p->rope_sin, T, S, H, dk, true));
+                NNB_TRY(launch_rope(e, w->dqkv + T * d, p->rope_cos, p->rope_sin, T, S, H, dk, true));
+            }
         }
         NNB_TRY(lin_bwd(p, LW.q, w->dqkv, s.q1, s.s1, T, w->dn, false));
         NNB_TRY(lin_bwd(p, LW.k, w->dqkv + T * d, s.q1, s.s1, T, w->dn, true));

@@ -7,6 +7,8 @@
 //   RMSNorm backward                            compute_layer_mlp.hpp:716-746
 //   QuickGELU / SwiGLU backward                 compute_layer_mlp.hpp:254-270, 332-369
 // (paths are under include/neuralnet.cpp/ of the reference).
+#include <algorithm>
+
 #include "common.cuh"
 #include "device_math.cuh"
 
@@ -386,6 +388,71 @@ rmsnorm_bwd_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
         if (dg[i] != 0.0f) atomicAdd(dgamma + i, dg[i]);
 }
 
+// Same operator for F = 128*NV: a warp keeps a token's x and dy*gamma in registers (NV float4 each per
+// lane, all loads of a pass in flight together) and its share of the gamma gradient too; warps walk the
+// tokens with a grid-wide stride, so there is one shared-memory reduction and one flush per CTA.
+template <int NV>
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_vec_kernel(const float* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ dy,
+                       const float* __restrict__ residual, size_t T, float* __restrict__ dx, float* __restrict__ dgamma)
+{
+    constexpr int F = 128 * NV;
+    __shared__ float dg[F];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int i = threadIdx.x; i < F; i += 256) dg[i] = 0.0f;
+    __syncthreads();
+    const float inv_f = __frcp_rn((float)F);
+    float4 dgr[NV];
+#pragma unroll
+    for (int j = 0; j < NV; ++j) dgr[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (size_t t = (size_t)blockIdx.x * 8 + warp; t < T; t += (size_t)gridDim.x * 8) {
+        const float4* xr = reinterpret_cast<const float4*>(x + t * F);
+        const float4* gr = reinterpret_cast<const float4*>(dy + t * F);
+        float4 xv[NV], gv[NV];
+#pragma unroll
+        for (int j = 0; j < NV; ++j) xv[j] = xr[j * 32 + lane];
+#pragma unroll
+        for (int j = 0; j < NV; ++j) gv[j] = gr[j * 32 + lane];
+        float ss = 0.0f;
+#pragma unroll
+        for (int j = 0; j < NV; ++j) ss = fmaf(xv[j].x, xv[j].x, fmaf(xv[j].y, xv[j].y, fmaf(xv[j].z, xv[j].z, fmaf(xv[j].w, xv[j].w, ss))));
+        ss = warp_sum(ss);
+        const float sinv = __frcp_rn(__fsqrt_rn(__fadd_rn(__fmul_rn(ss, inv_f), 1e-5f)));
+        float dot = 0.0f;
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            xv[j].x *= sinv; xv[j].y *= sinv; xv[j].z *= sinv; xv[j].w *= sinv;  // normed
+            dgr[j].x = fmaf(gv[j].x, xv[j].x, dgr[j].x); dgr[j].y = fmaf(gv[j].y, xv[j].y, dgr[j].y);
+            dgr[j].z = fmaf(gv[j].z, xv[j].z, dgr[j].z); dgr[j].w = fmaf(gv[j].w, xv[j].w, dgr[j].w);
+            const float4 gm = __ldg(reinterpret_cast<const float4*>(gamma) + j * 32 + lane);
+            gv[j].x *= gm.x; gv[j].y *= gm.y; gv[j].z *= gm.z; gv[j].w *= gm.w;  // gy
+            dot = fmaf(gv[j].x, xv[j].x, fmaf(gv[j].y, xv[j].y, fmaf(gv[j].z, xv[j].z, fmaf(gv[j].w, xv[j].w, dot))));
+        }
+        dot = warp_sum(dot) * inv_f;
+        float4* dxr = reinterpret_cast<float4*>(dx + t * F);
+        const float4* rr = residual ? reinterpret_cast<const float4*>(residual + t * F) : nullptr;
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            float4 o = make_float4((gv[j].x - dot * xv[j].x) * sinv, (gv[j].y - dot * xv[j].y) * sinv,
+                                   (gv[j].z - dot * xv[j].z) * sinv, (gv[j].w - dot * xv[j].w) * sinv);
+            if (rr) {
+                const float4 r = rr[j * 32 + lane];
+                o.x += r.x; o.y += r.y; o.z += r.z; o.w += r.w;
+            }
+            dxr[j * 32 + lane] = o;
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        const int c = (j * 32 + lane) * 4;
+        atomicAdd(dg + c, dgr[j].x); atomicAdd(dg + c + 1, dgr[j].y);
+        atomicAdd(dg + c + 2, dgr[j].z); atomicAdd(dg + c + 3, dgr[j].w);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < F; i += 256)
+        if (dg[i] != 0.0f) atomicAdd(dgamma + i, dg[i]);
+}
+
 // ------------------------------------------------------- activation backward
 // MODE 1 QuickGELU: dh = da * s*(1 + bx*(1-s)), s = sigmoid(bx), bx = 1.702 h
 // MODE 2 SwiGLU: h = (gate|up): dgate = da*up*s*(1+gate*(1-s)), dup = da*gate*s
@@ -408,6 +475,45 @@ __global__ void act_bwd_kernel(const float* __restrict__ h, const float* __restr
         const float go = da[idx];
         dh[t * 2 * F + f] = go * uv * (sg * (1.0f + gv * (1.0f - sg)));
         dh[t * 2 * F + F + f] = go * gv * sg;
+    }
+}
+
+// four features per thread (F a multiple of 4), same arithmetic
+template <int MODE>
+__global__ void __launch_bounds__(256)
+act_bwd_vec_kernel(const float* __restrict__ h, const float* __restrict__ da, size_t T, int F, float* __restrict__ dh)
+{
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // float4 index into da
+    const int F4 = F >> 2;
+    if (idx >= T * F4) return;
+    const size_t t = idx / F4;
+    const int f = (int)(idx % F4);
+    const float4 go = reinterpret_cast<const float4*>(da)[idx];
+    const float g4[4] = {go.x, go.y, go.z, go.w};
+    if (MODE == 1) {
+        const float4 xv = reinterpret_cast<const float4*>(h)[idx];
+        const float x4[4] = {xv.x, xv.y, xv.z, xv.w};
+        float o[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float bx = x4[i] * 1.702f;
+            const float sg = 1.0f / (1.0f + nnb_expf(-bx));
+            o[i] = g4[i] * (sg * (1.0f + bx * (1.0f - sg)));
+        }
+        reinterpret_cast<float4*>(dh)[idx] = make_float4(o[0], o[1], o[2], o[3]);
+    } else {
+        const float4 gv = reinterpret_cast<const float4*>(h + t * 2 * F)[f];
+        const float4 uv = reinterpret_cast<const float4*>(h + t * 2 * F + F)[f];
+        const float ga[4] = {gv.x, gv.y, gv.z, gv.w}, ua[4] = {uv.x, uv.y, uv.z, uv.w};
+        float og[4], ou[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float sg = 1.0f / (1.0f + nnb_expf(-ga[i]));
+            og[i] = g4[i] * ua[i] * (sg * (1.0f + ga[i] * (1.0f - sg)));
+            ou[i] = g4[i] * ga[i] * sg;
+        }
+        reinterpret_cast<float4*>(dh + t * 2 * F)[f] = make_float4(og[0], og[1], og[2], og[3]);
+        reinterpret_cast<float4*>(dh + t * 2 * F + F)[f] = make_float4(ou[0], ou[1], ou[2], ou[3]);
     }
 }
 
@@ -507,7 +613,16 @@ nnb_status launch_attn_fwd(nnb_engine* e, bool exact, const float* q, const floa
                            size_t S, size_t H, size_t dk, float* out, float* lse)
 {
     NNB_REQUIRE(dk <= 128, "attention: head dim %zu > 128", dk);
-    if (!exact && attn_tc_supported(dk, H * dk)) return launch_attn_fwd_tc(e, q, k, v, n_seq, S, H, dk, out, lse);
+    if (!exact && attn_b16_supported(dk, H * dk)) {
+        // standalone operator on f32 operands: bf16 copies live in stream-ordered scratch
+        const size_t td = n_seq * S * H * dk;
+        __nv_bfloat16* tmp = nullptr;
+        NNB_CUDA(cudaMallocAsync((void**)&tmp, 3 * td * sizeof(__nv_bfloat16), e->stream));
+        nnb_status st = launch_rope_pack_b16(e, q, k, v, nullptr, nullptr, n_seq * S, S, H, dk, tmp);
+        if (st == NNB_OK) st = launch_attn_fwd_b16(e, tmp, tmp + td, tmp + 2 * td, n_seq, S, H, dk, out, lse);
+        cudaFreeAsync(tmp, e->stream);
+        return st;
+    }
     const size_t smem = (2 * 32 * (dk + 1) + ATT_WARPS * dk) * sizeof(float);
     static size_t cfg = 0;
     if (smem > cfg) {
@@ -533,13 +648,19 @@ nnb_status launch_attn_bwd(nnb_engine* e, bool exact, const float* q, const floa
     NNB_REQUIRE(dk <= 128, "attention: head dim %zu > 128", dk);
     const float scale = 1.0f / sqrtf((float)dk);
     const size_t rows = n_seq * S;
+    if (!exact && attn_b16_supported(dk, H * dk)) {
+        const size_t td = rows * H * dk;
+        __nv_bfloat16* tmp = nullptr;
+        NNB_CUDA(cudaMallocAsync((void**)&tmp, 4 * td * sizeof(__nv_bfloat16), e->stream));
+        nnb_status st = launch_rope_pack_b16(e, q, k, v, nullptr, nullptr, rows, S, H, dk, tmp);
+        if (st == NNB_OK)
+            st = launch_attn_bwd_b16(e, tmp, tmp + td, tmp + 2 * td, out, dout, lse, delta, tmp + 3 * td, nullptr, nullptr, n_seq, S,
+                                     H, dk, dq, dkk, dvv);
+        cudaFreeAsync(tmp, e->stream);
+        return st;
+    }
     attn_bwd_delta_kernel<<<(unsigned)ceil_div(rows * H, 8), 256, 0, e->stream>>>(dout, out, (int)S, (int)H, (int)dk,
                                                                                  rows, delta);
-    if (!exact && attn_tc_supported(dk, H * dk)) {
-        e->launches++;
-        NNB_CHECK_LAUNCH("attn_bwd_delta_kernel");
-        return launch_attn_bwd_tc(e, q, k, v, dout, lse, delta, n_seq, S, H, dk, dq, dkk, dvv);
-    }
     const size_t smem_q = (2 * 32 * (dk + 1) + 2 * ATT_WARPS * dk) * sizeof(float);
     const size_t smem_kv = (2 * 32 * (dk + 1) + 2 * ATT_WARPS * dk + 64) * sizeof(float);
     static size_t cfg_q = 0, cfg_kv = 0;
@@ -564,6 +685,16 @@ nnb_status launch_attn_bwd(nnb_engine* e, bool exact, const float* q, const floa
 nnb_status launch_rmsnorm_bwd(nnb_engine* e, const float* x, const float* gamma, const float* dy,
                               const float* residual, size_t T, size_t F, float* dx, float* dgamma)
 {
+    const bool al = (((uintptr_t)x | (uintptr_t)gamma | (uintptr_t)dy | (uintptr_t)residual | (uintptr_t)dx) & 15) == 0;
+    if (al && (F == 2048 || F == 1024 || F == 512)) {
+        const unsigned grid = (unsigned)std::min<size_t>(ceil_div(T, 8), (size_t)e->sm_count);
+        if (F == 2048) rmsnorm_bwd_vec_kernel<16><<<grid, 256, 0, e->stream>>>(x, gamma, dy, residual, T, dx, dgamma);
+        else if (F == 1024) rmsnorm_bwd_vec_kernel<8><<<grid, 256, 0, e->stream>>>(x, gamma, dy, residual, T, dx, dgamma);
+        else rmsnorm_bwd_vec_kernel<4><<<grid, 256, 0, e->stream>>>(x, gamma, dy, residual, T, dx, dgamma);
+        e->launches++;
+        NNB_CHECK_LAUNCH("rmsnorm_bwd_vec_kernel");
+        return NNB_OK;
+    }
     const size_t smem = F * sizeof(float);
     static size_t cfg = 0;
     if (smem > cfg && smem > 48 * 1024) {
@@ -579,6 +710,14 @@ nnb_status launch_rmsnorm_bwd(nnb_engine* e, const float* x, const float* gamma,
 
 nnb_status launch_act_bwd(nnb_engine* e, int mode, const float* h, const float* da, size_t T, size_t F, float* dh)
 {
+    if (F % 4 == 0 && (((uintptr_t)h | (uintptr_t)da | (uintptr_t)dh) & 15) == 0) {
+        const unsigned g4 = (unsigned)ceil_div(T * (F / 4), 256);
+        if (mode == 1) act_bwd_vec_kernel<1><<<g4, 256, 0, e->stream>>>(h, da, T, (int)F, dh);
+        else act_bwd_vec_kernel<2><<<g4, 256, 0, e->stream>>>(h, da, T, (int)F, dh);
+        e->launches++;
+        NNB_CHECK_LAUNCH("act_bwd_vec_kernel");
+        return NNB_OK;
+    }
     const unsigned grid = (unsigned)ceil_div(T * F, 256);
     if (mode == 1) act_bwd_kernel<1><<<grid, 256, 0, e->stream>>>(h, da, T, (int)F, dh);
     else act_bwd_kernel<2><<<grid, 256, 0, e->stream>>>(h, da, T, (int)F, dh);

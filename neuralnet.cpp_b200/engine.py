@@ -352,5 +352,27 @@ def attention_bwd(self, q, k, v, out, dout, lse, n_seq, seq_len, n_head, exact=T
     return dq, dk, dv
 
 
+def attention_rope_fwd(self, q, k, v, rope_cos, rope_sin, n_seq, seq_len, n_head, exact=True):
+    """Attention with RoPE inside: q, k un-rotated, tables (seq_len, dk/2)."""
+    d = q.shape[1]
+    out = torch.empty_like(q)
+    lse = torch.empty((n_seq, n_head, seq_len), device=self.device, dtype=torch.float32)
+    check(self._lib.nnb_attention_rope_fwd(self._h, _ptr(q), _ptr(k), _ptr(v), _ptr(rope_cos), _ptr(rope_sin), n_seq, seq_len,
+                                           n_head, d // n_head, int(exact), _ptr(out), _ptr(lse)))
+    return out, lse
+
+
+def attention_rope_bwd(self, q, k, v, rope_cos, rope_sin, out, dout, lse, n_seq, seq_len, n_head, exact=True):
+    d = q.shape[1]
+    delta = torch.empty_like(lse)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
+    check(self._lib.nnb_attention_rope_bwd(self._h, _ptr(q), _ptr(k), _ptr(v), _ptr(rope_cos), _ptr(rope_sin), _ptr(out),
+                                           _ptr(dout), _ptr(lse), n_seq, seq_len, n_head, d // n_head, int(exact), _ptr(delta),
+                                           _ptr(dq), _ptr(dk), _ptr(dv)))
+    return dq, dk, dv
+
+
 Engine.attention_fwd = attention_fwd
 Engine.attention_bwd = attention_bwd
+Engine.attention_rope_fwd = attention_rope_fwd
+Engine.attention_rope_bwd = attention_rope_bwd

@@ -49,3 +49,35 @@ def test_attention_paths(eng, n, S, H, dk):
         assert np.abs(lse.cpu().numpy() - lse_ref).max() <= tol * max(1.0, np.abs(lse_ref).max())
         dq, dkk, dv = eng.attention_bwd(tq, tk, tv, out, tg, lse, n, S, H, exact=exact)
         assert _err(dq, dq_ref) <= tol and _err(dkk, dk_ref) <= tol and _err(dv, dv_ref) <= tol
+
+
+def _rope(x, n, S, H, cos, sin, sign=1.0):
+    """Rotate pairs (j, j + dk/2) of every head by the row's position; sign=-1 is the inverse."""
+    d = x.shape[1]
+    dk = d // H
+    half = dk // 2
+    x4 = x.astype(np.float64).reshape(n, S, H, dk)
+    a, b = x4[..., :half], x4[..., half:]
+    c, s = cos[None, :, None, :], sign * sin[None, :, None, :]
+    return np.concatenate([a * c - b * s, b * c + a * s], -1).reshape(n * S, d)
+
+
+@pytest.mark.parametrize("n,S,H,dk", [(2, 33, 2, 64), (2, 150, 2, 128), (1, 257, 3, 128), (2, 40, 2, 100)])
+def test_attention_with_rope_inside(eng, n, S, H, dk):
+    """q and k un-rotated, gradients with respect to the un-rotated q and k, both numeric modes."""
+    rng = np.random.default_rng(S + dk)
+    d = H * dk
+    half = dk // 2
+    q, k, v, g = (rng.normal(0, 1, (n * S, d)).astype(np.float32) for _ in range(4))
+    ang = np.arange(S)[:, None] * (10000.0 ** (-np.arange(half) / half))[None, :]
+    cos, sin = np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
+    qr, kr = _rope(q, n, S, H, cos, sin), _rope(k, n, S, H, cos, sin)
+    out_ref, lse_ref, dqr, dkr, dv_ref = _ref(qr, kr, v, g, n, S, H)
+    dq_ref, dk_ref = _rope(dqr, n, S, H, cos, sin, -1.0), _rope(dkr, n, S, H, cos, sin, -1.0)
+    tq, tk, tv, tg, tc, ts = (torch.from_numpy(a).to(eng.device) for a in (q, k, v, g, cos, sin))
+    for exact, tol in ((True, 1e-4), (False, 2e-2)):
+        out, lse = eng.attention_rope_fwd(tq, tk, tv, tc, ts, n, S, H, exact=exact)
+        assert _err(out, out_ref) <= tol
+        assert np.abs(lse.cpu().numpy() - lse_ref).max() <= tol * max(1.0, np.abs(lse_ref).max())
+        dq, dkk, dv = eng.attention_rope_bwd(tq, tk, tv, tc, ts, out, tg, lse, n, S, H, exact=exact)
+        assert _err(dq, dq_ref) <= tol and _err(dkk, dk_ref) <= tol and _err(dv, dv_ref) <= tol
