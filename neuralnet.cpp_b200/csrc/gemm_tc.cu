@@ -36,9 +36,10 @@ template <int BN>
 struct Tile {
     static constexpr int STAGE_B = BN * 128;
     static constexpr int STAGE_BYTES = STAGE_A + STAGE_B;
-    static constexpr int FIT = (200 * 1024) / STAGE_BYTES;
+    static constexpr int EPI_STAGING = EPI_WARPS * 32 * 32 * 4;  // one 32 x 32 f32 transposition tile per epilogue warp
+    static constexpr int FIT = (227 * 1024 - 1024 - 256 - EPI_STAGING) / STAGE_BYTES;
     static constexpr int STAGES = FIT > MAX_STAGES ? MAX_STAGES : FIT;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + EPI_STAGING;
     static constexpr uint32_t TMEM_COLS = 2 * BN <= 128 ? 128u : (2 * BN <= 256 ? 256u : 512u);
 };
 constexpr uint32_t SPIN_LIMIT = 1u << 24;
@@ -255,57 +256,119 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             if (!ok) atomicExch(err, 1);
         }
     } else {
-        // ---------------- epilogue: warps 2..9, TMEM lane quarter = warp % 4, column half = (warp - 2) / 4
+        // ---------------- epilogue: warps 2..9, TMEM lane quarter = warp % 4, column half = (warp - 2) / 4.
+        // tcgen05.ld hands a thread 32 columns of ONE row; storing that directly would scatter every store
+        // instruction over 32 rows.  Each warp therefore transposes its 32 x 32 block through a swizzled
+        // 4 KB staging tile: afterwards 8 lanes cover the 32 columns of a row with 16-byte accesses, a store
+        // (and the residual / accumulate load) instruction covers 4 full 128-byte rows, and tau / bias are
+        // one 16-byte load per chunk.
         const int quarter = warp & 3;
         const int chalf = (warp - 2) >> 2;
+        float* stg = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES + 256) + (warp - 2) * 1024;
+        const int lc = (lane & 7) * 4, lr = lane >> 3;
+        const bool aligned = (((uintptr_t)ep.out | (uintptr_t)ep.tau | (uintptr_t)ep.bias | (uintptr_t)ep.residual) & 15) == 0 &&
+                             (ep.n_mat & 3) == 0 && (ep.mat_stride & 3) == 0;
         uint32_t tcount = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++tcount) {
             const int tm = m_fast ? tile % tiles_m : tile / tiles_n, tn = m_fast ? tile / tiles_m : tile % tiles_n;
             const int acc = tcount & 1;
+            const int row0 = tm * BM + quarter * 32;
+            const int row = row0 + lane;
+            constexpr int NCHUNK = BN / 64;  // 32-column chunks per warp
+            // what a chunk needs from global memory (tau, bias, and the residual or the values to accumulate
+            // into) is fetched one chunk ahead, the first chunk's before the accumulator is even ready, so
+            // that DRAM latency stays off the path between tcgen05.ld and the stores
+            const float* pre_src = EPI == 0 ? ep.residual : (ep.accumulate ? ep.out : nullptr);
+            float4 pre[2][8], tau4[2], bias4[2];
+            auto fetch = [&](int ci, int slot) {
+                const int col0 = tn * BN + chalf * (BN / 2) + ci * 32;
+                tau4[slot] = bias4[slot] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) pre[slot][i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (!(aligned && col0 + 32 <= N)) return;
+                if (EPI == 0) {
+                    tau4[slot] = *reinterpret_cast<const float4*>(ep.tau + col0 + lc);
+                    if (ep.bias) bias4[slot] = *reinterpret_cast<const float4*>(ep.bias + col0 + lc);
+                }
+                if (!pre_src) return;
+                const int mat = col0 / ep.n_mat;
+                const size_t off0 = (size_t)mat * ep.mat_stride + (size_t)(col0 - mat * ep.n_mat);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int rr = i * 4 + lr;
+                    if (row0 + rr < M) pre[slot][i] = *reinterpret_cast<const float4*>(pre_src + off0 + (size_t)(row0 + rr) * ep.n_mat + lc);
+                }
+            };
+            const float srow = (EPI == 0 && row < M) ? ep.s[row] : 0.0f;
+            fetch(0, 0);
             if (!mbar_wait(&acc_full[acc], (tcount >> 1) & 1, abort_flag)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            const int row = tm * BM + quarter * 32 + lane;
-            const float srow = (EPI == 0 && row < M) ? ep.s[row] : 0.0f;
-#pragma unroll 1
-            for (int c0 = chalf * (BN / 2); c0 < (chalf + 1) * (BN / 2); c0 += 32) {
+#pragma unroll
+            for (int ci = 0; ci < NCHUNK; ++ci) {
+                const int slot = ci & 1;
+                const int c0 = chalf * (BN / 2) + ci * 32;
+                if (ci + 1 < NCHUNK) fetch(ci + 1, slot ^ 1);
                 uint32_t r[32];
                 tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + c0, r);
                 const int col0 = tn * BN + c0;
-                if (row < M && col0 < N) {
-                    const int mat = col0 / ep.n_mat;
-                    const size_t off = (size_t)mat * ep.mat_stride + (size_t)row * ep.n_mat + (col0 - mat * ep.n_mat);
-                    float* dst = ep.out + off;
-                    const bool vec = (col0 + 32 <= N) && ((ep.n_mat & 3) == 0);
-                    float v[32];
+                if (col0 >= N) continue;  // warp-uniform
+                const int mat = col0 / ep.n_mat;
+                const size_t off0 = (size_t)mat * ep.mat_stride + (size_t)(col0 - mat * ep.n_mat);
+                if (aligned && col0 + 32 <= N) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int col = col0 + j;
-                        if (EPI == 0) {
-                            float x = 0.0f;
-                            if (col < N) {
-                                x = __fmul_rn(__fmul_rn(ep.tau[col], srow), (float)(int)r[j]);
-                                if (ep.bias) x = __fadd_rn(x, ep.bias[col]);
-                                if (ep.residual) x = __fadd_rn(ep.residual[off + j], x);
+                    for (int c4 = 0; c4 < 8; ++c4)
+                        *reinterpret_cast<uint4*>(stg + lane * 32 + ((c4 ^ (lane & 7)) << 2)) =
+                            make_uint4(r[4 * c4], r[4 * c4 + 1], r[4 * c4 + 2], r[4 * c4 + 3]);
+                    __syncwarp();
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int rr = i * 4 + lr;
+                        const float sr = __shfl_sync(0xffffffffu, srow, rr);
+                        const uint4 a = *reinterpret_cast<const uint4*>(stg + rr * 32 + (((lane & 7) ^ (rr & 7)) << 2));
+                        if (row0 + rr < M) {
+                            const size_t off = off0 + (size_t)(row0 + rr) * ep.n_mat + lc;
+                            const float4 t4 = tau4[slot], b4 = bias4[slot], p4 = pre[slot][i];
+                            float4 o;
+                            if (EPI == 0) {
+                                o.x = __fmul_rn(__fmul_rn(t4.x, sr), (float)(int)a.x);
+                                o.y = __fmul_rn(__fmul_rn(t4.y, sr), (float)(int)a.y);
+                                o.z = __fmul_rn(__fmul_rn(t4.z, sr), (float)(int)a.z);
+                                o.w = __fmul_rn(__fmul_rn(t4.w, sr), (float)(int)a.w);
+                                if (ep.bias) {
+                                    o.x = __fadd_rn(o.x, b4.x); o.y = __fadd_rn(o.y, b4.y);
+                                    o.z = __fadd_rn(o.z, b4.z); o.w = __fadd_rn(o.w, b4.w);
+                                }
+                                if (ep.residual) {
+                                    o.x = __fadd_rn(p4.x, o.x); o.y = __fadd_rn(p4.y, o.y);
+                                    o.z = __fadd_rn(p4.z, o.z); o.w = __fadd_rn(p4.w, o.w);
+                                }
+                            } else {
+                                o = make_float4(__uint_as_float(a.x), __uint_as_float(a.y), __uint_as_float(a.z), __uint_as_float(a.w));
+                                if (ep.accumulate) {
+                                    o.x += p4.x; o.y += p4.y; o.z += p4.z; o.w += p4.w;
+                                }
                             }
-                            v[j] = x;
-                        } else {
-                            v[j] = __uint_as_float(r[j]);
+                            *reinterpret_cast<float4*>(ep.out + off) = o;
                         }
                     }
-                    if (vec) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4) {
-                            float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                            if (EPI == 1 && ep.accumulate) {
-                                const float4 old = *reinterpret_cast<const float4*>(dst + j);
-                                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-                            }
-                            *reinterpret_cast<float4*>(dst + j) = o;
+                    __syncwarp();
+                } else if (row < M) {
+                    // ragged right edge or unaligned operands: the row owner writes its own columns
+                    const size_t off = off0 + (size_t)row * ep.n_mat;
+                    for (int j = 0; j < 32; ++j) {
+                        const int col = col0 + j;
+                        if (col >= N) break;
+                        float x;
+                        if (EPI == 0) {
+                            x = __fmul_rn(__fmul_rn(ep.tau[col], srow), (float)(int)r[j]);
+                            if (ep.bias) x = __fadd_rn(x, ep.bias[col]);
+                            if (ep.residual) x = __fadd_rn(ep.residual[off + j], x);
+                        } else {
+                            x = __uint_as_float(r[j]);
+                            if (ep.accumulate) x += ep.out[off + j];
                         }
-                    } else {
-                        for (int j = 0; j < 32; ++j)
-                            if (col0 + j < N) dst[j] = (EPI == 1 && ep.accumulate) ? dst[j] + v[j] : v[j];
+                        ep.out[off + j] = x;
                     }
                 }
             }
