@@ -141,25 +141,33 @@ def _kernel_rooflines(torch, pkg, eng, pol, wl, peaks):
     d, F = m["d_model"], m["d_ff"]
     dev = eng.device
     out = {}
-    # (1) backward dX GEMM of fc1 at one micro-batch: the largest share of the step's GEMM time
+    # (1) backward dX GEMM of fc1 at one micro-batch (tcgen05, bf16 operands, f32 accumulation in TMEM): the
+    # backward GEMMs are the largest single share of the step.  Operands are prepared once; the timed loop
+    # launches the GEMM kernel only.
     T = wl["micro_batch"] * (wl["prompt_len"] + wl["max_new"])
     packed, tau = pol.linear(0, 4)  # fc1: (2F, d)
     O = packed.shape[0]
+    w8, wb = eng.expand_weights(packed, d)
     dy = torch.randn((T, O), device=dev)
     dx = torch.empty((T, d), device=dev)
-    ms = _time_loop(torch, lambda: eng.bitlinear_dx_tm(dy, packed, tau, d, dx=dx, exact=False), 10)
+    x = torch.randn((T, d), device=dev)
+    q, s, qsum = eng.act_quant_tm(x)
+    dyb = torch.empty((T, O), device=dev, dtype=torch.bfloat16)
+    eng.bitlinear_bwd_tc(dy, tau, wb, q, s, d, dx=dx, scratch=(dyb, None))
+    ms = _time_loop(torch, lambda: eng.bitlinear_bwd_tc(dy, tau, wb, q, s, d, dx=dx, scratch=(dyb, None), prepared=True), 10)
     flops = 2.0 * T * d * O
     ach = flops / (ms * 1e-3) / 1e12
     out["roofline"] = {"bound": "tensor", "achieved": ach, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
                        "frac": ach / peaks["bf16_tflops_sustained"], "traffic": None, "peak_source": peaks["src"] + " (sustained)",
-                       "kernel": "gemm_bf16_kernel<dX>", "kernel_ms": ms, "shape": f"T={T} K={d} O={O}"}
-    # (2) ternary forward GEMM at one micro-batch (int8 x 2-bit -> int32)
-    x = torch.randn((T, d), device=dev)
-    q, s, qsum = eng.act_quant_tm(x)
+                       "kernel": "gemm_tc_kernel<bf16 dX>", "kernel_ms": ms, "shape": f"T={T} K={O} N={d}"}
+    # (2) ternary forward GEMM at one micro-batch (tcgen05 kind::i8, int32 accumulation in TMEM)
     y = torch.empty((T, O), device=dev)
-    ms = _time_loop(torch, lambda: eng.bitlinear_fwd_tm(packed, tau, None, q, s, qsum, y=y), 10)
+    ms = _time_loop(torch, lambda: eng.bitlinear_fwd_tc(w8, tau, None, q, s, y=y), 10)
     out["roofline_int8_gemm"] = {"bound": "tensor", "achieved": 2.0 * T * d * O / (ms * 1e-3) / 1e12, "unit": "TOP/s (int8)",
-                                 "peak": None, "kernel": "bitlinear_mma_kernel", "kernel_ms": ms, "shape": f"T={T} K={d} O={O}"}
+                                 "peak": None, "kernel": "gemm_tc_kernel<int8 forward>", "kernel_ms": ms,
+                                 "shape": f"T={T} K={d} O={O}"}
+    eng.check_device_errors()
+    del w8, wb, dy, dx, dyb, y
     # (3) decode-sized ternary GEMV: packed-weight stream of a stack of fc1-shaped matrices (> L2)
     n_mats = 64
     wst = torch.randint(-2**31, 2**31 - 1, (n_mats, O, d // 16), device=dev, dtype=torch.int64)

@@ -152,7 +152,8 @@ nnb_status nnb_bitlinear_fwd_tc(nnb_engine* e, const int8_t* d_w8, const float* 
  * 256); 0 restores the automatic choice from the problem shape.  Results do not depend on it. */
 nnb_status nnb_tc_set_forward_tile(int bn);
 /* BitLinear::backward on bf16 tensor cores: d_dyb (t,out) and d_xs (t,k) are bf16 scratch buffers the
- * call fills (dy*tau and s*q); d_dx (t,k) and/or d_dw (out,k) may be NULL to skip that half. */
+ * call fills (dy*tau and s*q); d_dx (t,k) and/or d_dw (out,k) may be NULL to skip that half.  With
+ * d_dy == NULL the scratch buffers are taken as already filled by an earlier call and only the GEMMs run. */
 nnb_status nnb_bitlinear_bwd_tc(nnb_engine* e, const float* d_dy, const float* d_tau, const void* d_wb,
                                 const int8_t* d_q, const float* d_s, size_t t, size_t k, size_t out, void* d_dyb,
                                 void* d_xs, float* d_dx, int accumulate_dx, float* d_dw);

@@ -131,16 +131,18 @@ nnb_status nnb_bitlinear_bwd_tc(nnb_engine* e, const float* d_dy, const float* d
                                 const int8_t* d_q, const float* d_s, size_t t, size_t k, size_t out, void* d_dyb,
                                 void* d_xs, float* d_dx, int accumulate_dx, float* d_dw)
 {
-    NNB_REQUIRE(e && d_dy && d_tau && d_dyb, "bitlinear_bwd_tc: NULL argument");
+    NNB_REQUIRE(e && d_dyb && (d_dy == nullptr || d_tau), "bitlinear_bwd_tc: NULL argument");
     NNB_REQUIRE(k % 64 == 0 && out % 8 == 0, "bitlinear_bwd_tc: needs k %% 64 == 0 and out %% 8 == 0 (k=%zu, out=%zu)", k, out);
-    NNB_TRY(launch_scale_to_bf16(e, d_dy, d_tau, t, out, (__nv_bfloat16*)d_dyb));
+    // d_dy == NULL: d_dyb (and d_xs) already hold the operands an earlier call prepared; only the GEMMs run
+    const bool prepared = d_dy == nullptr;
+    if (!prepared) NNB_TRY(launch_scale_to_bf16(e, d_dy, d_tau, t, out, (__nv_bfloat16*)d_dyb));
     if (d_dx) {
         NNB_REQUIRE(d_wb, "bitlinear_bwd_tc: dX needs the bf16 weights");
         NNB_TRY(launch_tc_dx(e, (const __nv_bfloat16*)d_dyb, (const __nv_bfloat16*)d_wb, t, k, out, d_dx, accumulate_dx != 0));
     }
     if (d_dw) {
-        NNB_REQUIRE(d_q && d_s && d_xs, "bitlinear_bwd_tc: dW needs the activation cache and scratch");
-        NNB_TRY(launch_dequant_to_bf16(e, d_q, d_s, t, k, (__nv_bfloat16*)d_xs));
+        NNB_REQUIRE(d_xs && (prepared || (d_q && d_s)), "bitlinear_bwd_tc: dW needs the activation cache and scratch");
+        if (!prepared) NNB_TRY(launch_dequant_to_bf16(e, d_q, d_s, t, k, (__nv_bfloat16*)d_xs));
         NNB_TRY(launch_tc_dw(e, (const __nv_bfloat16*)d_dyb, (const __nv_bfloat16*)d_xs, t, k, out, d_dw));
     }
     return NNB_OK;

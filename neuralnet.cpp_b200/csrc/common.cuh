@@ -193,7 +193,9 @@ nnb_status tc_set_forward_tile(int bn);
 nnb_status launch_expand_weights(nnb_engine* e, const uint32_t* wq, size_t rows, size_t k, int8_t* w8, __nv_bfloat16* wb);
 nnb_status launch_scale_to_bf16(nnb_engine* e, const float* dy, const float* tau, size_t t, size_t out, __nv_bfloat16* dyb);
 nnb_status launch_scale_colsum(nnb_engine* e, const float* dy, const float* tau, size_t t, size_t out, __nv_bfloat16* dyb,
-                               float* db);
+                               float* db, size_t dyb_ld = 0);
+nnb_status launch_act_bwd_scale_colsum(nnb_engine* e, int mode, const float* h, const float* da, const float* tau, size_t t,
+                                       size_t F, __nv_bfloat16* dyb, float* db);
 nnb_status launch_dequant_to_bf16(nnb_engine* e, const int8_t* q, const float* s, size_t t, size_t k, __nv_bfloat16* xs);
 
 // ---- attn_b16.cu (bf16 tensor-core attention of the teacher-forced pass, head dims 64 and 128)

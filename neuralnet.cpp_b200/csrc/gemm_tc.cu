@@ -613,7 +613,7 @@ __global__ void scale_to_bf16_kernel(const float* __restrict__ dy, const float* 
 // grid (ceil(O/256), ceil(T/chunk)), 128 threads, two adjacent columns per thread.
 __global__ void __launch_bounds__(128)
 scale_colsum_kernel(const float* __restrict__ dy, const float* __restrict__ tau, int T, int O, int chunk,
-                    __nv_bfloat16* __restrict__ out, float* __restrict__ db)
+                    __nv_bfloat16* __restrict__ out, size_t ld, float* __restrict__ db)
 {
     const int o = (blockIdx.x * 128 + threadIdx.x) * 2;
     if (o >= O) return;
@@ -629,17 +629,74 @@ scale_colsum_kernel(const float* __restrict__ dy, const float* __restrict__ tau,
         for (int u = 0; u < 4; ++u) {
             sa += v[u].x;
             sb += v[u].y;
-            *reinterpret_cast<__nv_bfloat162*>(out + (size_t)(t + u) * O + o) = __floats2bfloat162_rn(v[u].x * tv.x, v[u].y * tv.y);
+            *reinterpret_cast<__nv_bfloat162*>(out + (size_t)(t + u) * ld + o) = __floats2bfloat162_rn(v[u].x * tv.x, v[u].y * tv.y);
         }
     }
     for (; t < t1; ++t) {
         const float2 v = *reinterpret_cast<const float2*>(dy + (size_t)t * O + o);
         sa += v.x;
         sb += v.y;
-        *reinterpret_cast<__nv_bfloat162*>(out + (size_t)t * O + o) = __floats2bfloat162_rn(v.x * tv.x, v.y * tv.y);
+        *reinterpret_cast<__nv_bfloat162*>(out + (size_t)t * ld + o) = __floats2bfloat162_rn(v.x * tv.x, v.y * tv.y);
     }
     atomicAdd(db + o, sa);
     atomicAdd(db + o + 1, sb);
+}
+
+// Activation backward fused with the preparation of the next GEMM's operand: with h (T, F1) the
+// pre-activation (F1 = 2F for SwiGLU, gate | up; F for QuickGELU) and da (T, F) the gradient of the
+// activation's output, dh = act'(h) o da never reaches memory as f32: dyb[t,c] = bf16(dh[t,c] * tau[c]) and
+// db[c] += sum_t dh[t,c].  Same grid as scale_colsum_kernel over the F output features.
+template <int MODE>
+__global__ void __launch_bounds__(128)
+act_bwd_scale_colsum_kernel(const float* __restrict__ h, const float* __restrict__ da, const float* __restrict__ tau, int T,
+                            int F, int chunk, __nv_bfloat16* __restrict__ out, float* __restrict__ db)
+{
+    const int f = (blockIdx.x * 128 + threadIdx.x) * 2;
+    if (f >= F) return;
+    const int F1 = MODE == 2 ? 2 * F : F;
+    const int t0 = blockIdx.y * chunk, t1 = min(T, t0 + chunk);
+    const float2 tg = *reinterpret_cast<const float2*>(tau + f);
+    const float2 tu = MODE == 2 ? *reinterpret_cast<const float2*>(tau + F + f) : make_float2(0.f, 0.f);
+    float sg0 = 0.f, sg1 = 0.f, su0 = 0.f, su1 = 0.f;
+    for (int t = t0; t < t1; t += 2) {
+        float2 gv[2], uv[2], go[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int tt = min(t + u, t1 - 1);
+            gv[u] = *reinterpret_cast<const float2*>(h + (size_t)tt * F1 + f);
+            uv[u] = MODE == 2 ? *reinterpret_cast<const float2*>(h + (size_t)tt * F1 + F + f) : make_float2(0.f, 0.f);
+            go[u] = *reinterpret_cast<const float2*>(da + (size_t)tt * F + f);
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            if (t + u >= t1) break;
+            float dgx, dgy, dux = 0.f, duy = 0.f;
+            if (MODE == 2) {
+                const float s0 = __fdividef(1.0f, 1.0f + __expf(-gv[u].x)), s1 = __fdividef(1.0f, 1.0f + __expf(-gv[u].y));
+                dgx = go[u].x * uv[u].x * (s0 * (1.0f + gv[u].x * (1.0f - s0)));
+                dgy = go[u].y * uv[u].y * (s1 * (1.0f + gv[u].y * (1.0f - s1)));
+                dux = go[u].x * gv[u].x * s0;
+                duy = go[u].y * gv[u].y * s1;
+            } else {
+                const float b0 = gv[u].x * 1.702f, b1 = gv[u].y * 1.702f;
+                const float s0 = __fdividef(1.0f, 1.0f + __expf(-b0)), s1 = __fdividef(1.0f, 1.0f + __expf(-b1));
+                dgx = go[u].x * (s0 * (1.0f + b0 * (1.0f - s0)));
+                dgy = go[u].y * (s1 * (1.0f + b1 * (1.0f - s1)));
+            }
+            sg0 += dgx; sg1 += dgy;
+            *reinterpret_cast<__nv_bfloat162*>(out + (size_t)(t + u) * F1 + f) = __floats2bfloat162_rn(dgx * tg.x, dgy * tg.y);
+            if (MODE == 2) {
+                su0 += dux; su1 += duy;
+                *reinterpret_cast<__nv_bfloat162*>(out + (size_t)(t + u) * F1 + F + f) = __floats2bfloat162_rn(dux * tu.x, duy * tu.y);
+            }
+        }
+    }
+    atomicAdd(db + f, sg0);
+    atomicAdd(db + f + 1, sg1);
+    if (MODE == 2) {
+        atomicAdd(db + F + f, su0);
+        atomicAdd(db + F + f + 1, su1);
+    }
 }
 
 // xs[t,k] = bf16(s[t] * q[t, perm(k)]) in natural feature order
@@ -670,14 +727,30 @@ nnb_status launch_scale_to_bf16(nnb_engine* e, const float* dy, const float* tau
     return NNB_OK;
 }
 
-nnb_status launch_scale_colsum(nnb_engine* e, const float* dy, const float* tau, size_t t, size_t out, __nv_bfloat16* dyb,
-                               float* db)
+// mode 1 QuickGELU, 2 SwiGLU; F even
+nnb_status launch_act_bwd_scale_colsum(nnb_engine* e, int mode, const float* h, const float* da, const float* tau, size_t t,
+                                       size_t F, __nv_bfloat16* dyb, float* db)
 {
-    NNB_REQUIRE(out % 2 == 0, "scale_colsum: out=%zu must be even", out);
+    NNB_REQUIRE(F % 2 == 0 && (mode == 1 || mode == 2), "act_bwd_scale_colsum: bad arguments");
+    const int chunk = 128;
+    dim3 grid((unsigned)ceil_div(F, 256), (unsigned)ceil_div(t, chunk));
+    NNB_REQUIRE(grid.y <= 65535, "act_bwd_scale_colsum: too many tokens (%zu)", t);
+    if (mode == 2) act_bwd_scale_colsum_kernel<2><<<grid, 128, 0, e->stream>>>(h, da, tau, (int)t, (int)F, chunk, dyb, db);
+    else act_bwd_scale_colsum_kernel<1><<<grid, 128, 0, e->stream>>>(h, da, tau, (int)t, (int)F, chunk, dyb, db);
+    e->launches++;
+    NNB_CHECK_LAUNCH("act_bwd_scale_colsum_kernel");
+    return NNB_OK;
+}
+
+// dyb_ld: row pitch of dyb in elements (0 = out), so that several matrices' gradients can sit side by side
+nnb_status launch_scale_colsum(nnb_engine* e, const float* dy, const float* tau, size_t t, size_t out, __nv_bfloat16* dyb,
+                               float* db, size_t dyb_ld)
+{
+    NNB_REQUIRE(out % 2 == 0 && dyb_ld % 2 == 0, "scale_colsum: out=%zu must be even", out);
     const int chunk = 128;
     dim3 grid((unsigned)ceil_div(out, 256), (unsigned)ceil_div(t, chunk));
     NNB_REQUIRE(grid.y <= 65535, "scale_colsum: too many tokens (%zu)", t);
-    scale_colsum_kernel<<<grid, 128, 0, e->stream>>>(dy, tau, (int)t, (int)out, chunk, dyb, db);
+    scale_colsum_kernel<<<grid, 128, 0, e->stream>>>(dy, tau, (int)t, (int)out, chunk, dyb, dyb_ld ? dyb_ld : out, db);
     e->launches++;
     NNB_CHECK_LAUNCH("scale_colsum_kernel");
     return NNB_OK;

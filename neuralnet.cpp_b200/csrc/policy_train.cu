@@ -224,18 +224,35 @@ static nnb_status forward(nnb_policy* p, const int32_t* tokens, size_t n_seq, si
     return NNB_OK;
 }
 
+// whether the tcgen05 backward serves a linear of `out` outputs at T tokens
+static bool tc_bwd_ok(const nnb_policy* p, size_t out, size_t T)
+{
+    return !p->cfg.exact && p->wb && p->wb_valid && out % 8 == 0 && T >= 64;
+}
+
+// the two GEMMs of a linear's backward on operands already prepared in the workspace: w->dyb (T, out) =
+// bf16(dy*tau).  `out` may span several matrices stored one after the other (their weights, and so their
+// weight gradients, are contiguous): one dX over the concatenated contraction, one dW for all rows.
+static nnb_status lin_bwd_gemms(nnb_policy* p, const LinW& l, size_t out, const int8_t* q, const float* s, size_t T, float* dx,
+                                bool accumulate_dx)
+{
+    nnb_engine* e = p->e;
+    TrainWs* w = (TrainWs*)p->train;
+    if (dx) NNB_TRY(launch_tc_dx(e, w->dyb, p->wb + l.packed_off * 16, T, l.in, out, dx, accumulate_dx));
+    NNB_TRY(launch_dequant_to_bf16(e, q, s, T, l.in, w->xs));
+    return launch_tc_dw(e, w->dyb, w->xs, T, l.in, out, p->grads + l.w_off);
+}
+
 static nnb_status lin_bwd(nnb_policy* p, const LinW& l, const float* dy, const int8_t* q, const float* s, size_t T,
                           float* dx, bool accumulate_dx)
 {
     nnb_engine* e = p->e;
     const bool exact = p->cfg.exact != 0;
     TrainWs* w = (TrainWs*)p->train;
-    if (!exact && p->wb && p->wb_valid && l.out % 8 == 0 && T >= 64) {
+    if (tc_bwd_ok(p, l.out, T)) {
         // tcgen05 path: dyb = bf16(dy*tau) serves both GEMMs, xs = bf16(s*q) in natural feature order
         NNB_TRY(launch_scale_colsum(e, dy, p->tau + l.tau_off, T, l.out, w->dyb, p->grads + l.b_off));
-        if (dx) NNB_TRY(launch_tc_dx(e, w->dyb, p->wb + l.packed_off * 16, T, l.in, l.out, dx, accumulate_dx));
-        NNB_TRY(launch_dequant_to_bf16(e, q, s, T, l.in, w->xs));
-        return launch_tc_dw(e, w->dyb, w->xs, T, l.in, l.out, p->grads + l.w_off);
+        return lin_bwd_gemms(p, l, l.out, q, s, T, dx, accumulate_dx);
     }
     if (dx) NNB_TRY(launch_bitlinear_dx(e, exact, dy, p->packed + l.packed_off, p->tau + l.tau_off, T, l.in, l.out, dx, accumulate_dx));
     NNB_TRY(launch_bitlinear_dw(e, exact, dy, q, s, p->tau + l.tau_off, T, l.in, l.out, p->grads + l.w_off));
@@ -262,8 +279,15 @@ static nnb_status backward(nnb_policy* p, const int32_t* tokens, size_t n_seq, s
         LayerSave& s = w->L[l];
         // feed-forward branch
         NNB_TRY(lin_bwd(p, LW.fc2, w->g, s.q4, s.s4, T, w->da, false));
-        NNB_TRY(launch_act_bwd(e, c.act == 1 ? 2 : 1, s.h1, w->da, T, F, w->dh1));
-        NNB_TRY(lin_bwd(p, LW.fc1, w->dh1, s.q3, s.s3, T, w->dn, false));
+        if (tc_bwd_ok(p, LW.fc1.out, T) && F % 2 == 0) {
+            // the activation's backward writes the GEMM operand directly (no f32 round trip of dh1)
+            NNB_TRY(launch_act_bwd_scale_colsum(e, c.act == 1 ? 2 : 1, s.h1, w->da, p->tau + LW.fc1.tau_off, T, F, w->dyb,
+                                                GG + LW.fc1.b_off));
+            NNB_TRY(lin_bwd_gemms(p, LW.fc1, LW.fc1.out, s.q3, s.s3, T, w->dn, false));
+        } else {
+            NNB_TRY(launch_act_bwd(e, c.act == 1 ? 2 : 1, s.h1, w->da, T, F, w->dh1));
+            NNB_TRY(lin_bwd(p, LW.fc1, w->dh1, s.q3, s.s3, T, w->dn, false));
+        }
         NNB_TRY(launch_rmsnorm_bwd(e, s.x_mid, PP + LW.ln2_g, w->dn, w->g, T, d, w->g2, GG + LW.ln2_g));
         // attention branch
         NNB_TRY(lin_bwd(p, LW.o, w->g2, s.q2, s.s2, T, w->datt, false));
@@ -280,9 +304,18 @@ static nnb_status backward(nnb_policy* p, const int32_t* tokens, size_t n_seq, s
                 NNB_TRY(launch_rope(e, w->dqkv + T * d, p->rope_cos, p->rope_sin, T, S, H, dk, true));
             }
         }
-        NNB_TRY(lin_bwd(p, LW.q, w->dqkv, s.q1, s.s1, T, w->dn, false));
-        NNB_TRY(lin_bwd(p, LW.k, w->dqkv + T * d, s.q1, s.s1, T, w->dn, true));
-        NNB_TRY(lin_bwd(p, LW.v, w->dqkv + 2 * T * d, s.q1, s.s1, T, w->dn, true));
+        if (tc_bwd_ok(p, 3 * d, T)) {
+            // q, k, v share their input: their gradients go side by side into one (T, 3d) operand, so the
+            // backward is one dX GEMM over the concatenated contraction and one dW GEMM for all three
+            for (int m = 0; m < 3; ++m)
+                NNB_TRY(launch_scale_colsum(e, w->dqkv + m * T * d, p->tau + LW.q.tau_off + m * d, T, d, w->dyb + m * d,
+                                            GG + LW.q.b_off + m * d, 3 * d));
+            NNB_TRY(lin_bwd_gemms(p, LW.q, 3 * d, s.q1, s.s1, T, w->dn, false));
+        } else {
+            NNB_TRY(lin_bwd(p, LW.q, w->dqkv, s.q1, s.s1, T, w->dn, false));
+            NNB_TRY(lin_bwd(p, LW.k, w->dqkv + T * d, s.q1, s.s1, T, w->dn, true));
+            NNB_TRY(lin_bwd(p, LW.v, w->dqkv + 2 * T * d, s.q1, s.s1, T, w->dn, true));
+        }
         NNB_TRY(launch_rmsnorm_bwd(e, s.x_in, PP + LW.ln1_g, w->dn, w->g2, T, d, w->g, GG + LW.ln1_g));
     }
     return launch_embed_bwd(e, w->g, tokens, T, S, d, V, GG + p->tok_emb, c.pos == 0 ? GG + p->pos_emb : nullptr);

@@ -312,10 +312,17 @@ def set_tc_forward_tile(self, bn: int = 0):
     check(self._lib.nnb_tc_set_forward_tile(int(bn)))
 
 
-def bitlinear_bwd_tc(self, dy, tau, wb, q, s, k, want_dx=True, dw=None, dx=None, accumulate_dx=False):
+def bitlinear_bwd_tc(self, dy, tau, wb, q, s, k, want_dx=True, dw=None, dx=None, accumulate_dx=False, scratch=None,
+                     prepared=False):
+    """scratch = (dyb, xs) bf16 buffers to reuse; prepared=True runs only the GEMMs on scratch filled by an earlier call."""
     t, out = dy.shape
-    dyb = torch.empty((t, out), device=self.device, dtype=torch.bfloat16)
-    xs = torch.empty((t, k), device=self.device, dtype=torch.bfloat16) if dw is not None else None
+    if scratch is not None:
+        dyb, xs = scratch
+    else:
+        dyb = torch.empty((t, out), device=self.device, dtype=torch.bfloat16)
+        xs = torch.empty((t, k), device=self.device, dtype=torch.bfloat16) if dw is not None else None
+    if prepared:
+        dy = None
     if want_dx and dx is None:
         dx = torch.empty((t, k), device=self.device, dtype=torch.float32)
     check(self._lib.nnb_bitlinear_bwd_tc(self._h, _ptr(dy), _ptr(tau), _ptr(wb), _ptr(q), _ptr(s), t, k, out, _ptr(dyb),
