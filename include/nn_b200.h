@@ -178,6 +178,20 @@ nnb_status nnb_attention_rope_bwd(nnb_engine* e, const float* d_q, const float* 
                                   const float* d_rope_cos, const float* d_rope_sin, const float* d_out, const float* d_dout,
                                   const float* d_lse, size_t n_seq, size_t seq_len, size_t n_head, size_t dk, int exact,
                                   float* d_delta, float* d_dq, float* d_dk, float* d_dv);
+/* Attention of one new token per sequence against the KV cache: the attention part of
+ * GPTModel::forward_step (include/neuralnet.cpp/compute_layer_gpt.hpp:520-560 drives
+ * AttentionBase::forward_step, compute_layer_attention.hpp:990-1080).  d_qkv (3, n_seq, d) f32 holds the
+ * new token's un-rotated projections; the position *d_pos lives on the device.  The call rotates q and k
+ * (tables (ctx, dk/2), or NULL for none), appends k and v at row *d_pos - pre_len of the per-sequence
+ * caches (n_seq, n_head, ctx_alloc, dk) — f32 when exact = 1, bf16 when 0 — and attends over positions
+ * 0..*d_pos, the first pre_len of them read from the prefix caches (n_seq / group, n_head, pre_alloc, dk)
+ * shared by `group` consecutive sequences (pre_len = 0, group = 1: none).  Outputs: d_out (n_seq, d) f32,
+ * and/or, in the fast mode, the int8 quantisation of that row in the engine's activation layout (d_q8,
+ * d_s, d_qsum as nnb_act_quant_tm would give), produced by the same launch. */
+nnb_status nnb_attention_decode(nnb_engine* e, const float* d_qkv, void* d_kcache, void* d_vcache, size_t ctx_alloc,
+                                const void* d_kpre, const void* d_vpre, size_t pre_len, size_t pre_alloc, size_t group,
+                                const float* d_rope_cos, const float* d_rope_sin, const int* d_pos, size_t n_seq,
+                                size_t n_head, size_t dk, int exact, float* d_out, int8_t* d_q8, float* d_s, int32_t* d_qsum);
 /* synchronises and reports NNB_ERR_TIMEOUT if a kernel gave up on a bounded device-side wait */
 nnb_status nnb_engine_check(nnb_engine* e);
 

@@ -58,6 +58,7 @@ _SIGNATURES = {
     "nnb_engine_check": (_I, [_P]),
     "nnb_attention_fwd": (_I, [_P, _P, _P, _P, _SZ, _SZ, _SZ, _SZ, _I, _P, _P]),
     "nnb_attention_bwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _SZ, _SZ, _SZ, _SZ, _I, _P, _P, _P, _P]),
+    "nnb_attention_decode": (_I, [_P, _P, _P, _P, _SZ, _P, _P, _SZ, _SZ, _SZ, _P, _P, _P, _SZ, _SZ, _SZ, _I, _P, _P, _P, _P]),
     "nnb_attention_rope_fwd": (_I, [_P, _P, _P, _P, _P, _P, _SZ, _SZ, _SZ, _SZ, _I, _P, _P]),
     "nnb_attention_rope_bwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _SZ, _SZ, _SZ, _SZ, _I, _P, _P, _P, _P]),
     "nnb_bitlinear_fwd_host": (_I, [_P, _P, _P, _P, _P, _SZ, _SZ, _SZ, _P]),

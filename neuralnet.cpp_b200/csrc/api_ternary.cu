@@ -234,6 +234,25 @@ nnb_status nnb_attention_rope_bwd(nnb_engine* e, const float* d_q, const float* 
     return st;
 }
 
+nnb_status nnb_attention_decode(nnb_engine* e, const float* d_qkv, void* d_kcache, void* d_vcache, size_t ctx_alloc,
+                                const void* d_kpre, const void* d_vpre, size_t pre_len, size_t pre_alloc, size_t group,
+                                const float* d_rope_cos, const float* d_rope_sin, const int* d_pos, size_t n_seq,
+                                size_t n_head, size_t dk, int exact, float* d_out, int8_t* d_q8, float* d_s, int32_t* d_qsum)
+{
+    NNB_REQUIRE(e && d_qkv && d_kcache && d_vcache && d_pos, "attention_decode: NULL argument");
+    NNB_REQUIRE(n_seq > 0 && n_head > 0 && dk > 0 && ctx_alloc > 0, "attention_decode: bad shape");
+    NNB_REQUIRE((d_rope_cos == nullptr) == (d_rope_sin == nullptr), "attention_decode: rope tables go together");
+    if (d_q8) {
+        NNB_REQUIRE(!exact && d_s && d_qsum && attn_decode_fused_supported(n_head, dk) && (n_head * dk) % 64 == 0,
+                    "attention_decode: the fused int8 output needs the fast mode, head dim 64 or 128, at most 32 heads");
+        return launch_attn_decode_fused(e, d_qkv, d_kcache, d_vcache, ctx_alloc, d_kpre, d_vpre, pre_len, pre_alloc, group,
+                                        d_rope_cos, d_rope_sin, d_pos, n_seq, n_head, dk, d_out, d_q8, d_s, d_qsum);
+    }
+    NNB_REQUIRE(d_out, "attention_decode: no output requested");
+    return launch_attn_decode(e, exact != 0, d_qkv, d_kcache, d_vcache, ctx_alloc, d_kpre, d_vpre, pre_len, pre_alloc, group,
+                              d_rope_cos, d_rope_sin, d_pos, n_seq, n_head, dk, d_out);
+}
+
 nnb_status nnb_engine_check(nnb_engine* e)
 {
     NNB_REQUIRE(e, "engine is NULL");

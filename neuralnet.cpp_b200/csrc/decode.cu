@@ -452,6 +452,12 @@ __device__ __forceinline__ void bf16x8_to_float(const uint4& t, float (&v)[8])
     v[6] = __uint_as_float(t.w << 16); v[7] = __uint_as_float(t.w & 0xffff0000u);
 }
 
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi)
+{
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
 template <int DK>
 __global__ void __launch_bounds__(128)
 attn_decode_bf16_kernel(const float* __restrict__ qkv, __nv_bfloat16* __restrict__ kcache, __nv_bfloat16* __restrict__ vcache,
@@ -609,6 +615,243 @@ static nnb_status launch_attn_decode_bf16(nnb_engine* e, const float* qkv, void*
                                                       (int)ctx_total, 1.0f / sqrtf((float)DK), out);
     e->launches++;
     NNB_CHECK_LAUNCH("attn_decode_bf16_kernel");
+    return NNB_OK;
+}
+
+// Decode attention of ALL heads of a sequence in one CTA, one warp per head, followed by the int8
+// quantisation of the token's attention output (the input of the output projection): what
+// attn_decode_bf16_kernel + row_quant_fast_kernel<3> compute, in one launch and without block-wide
+// barriers inside the attention part.  grid = B, block = 32*H (H <= 32).  A warp streams its head's keys
+// and values with 16-byte loads, U keys in flight per lane group; with ~55 resident warps per SM that
+// keeps > 100 KB of cache reads outstanding per SM.  att (B, d) f32 is optional.
+template <int DK>
+__global__ void __launch_bounds__(1024)
+attn_decode_fused_kernel(const float* __restrict__ qkv, __nv_bfloat16* __restrict__ kcache, __nv_bfloat16* __restrict__ vcache,
+                         int own_alloc, const __nv_bfloat16* __restrict__ kpre, const __nv_bfloat16* __restrict__ vpre,
+                         int pre_len, int pre_alloc, int group, const float* __restrict__ rope_cos,
+                         const float* __restrict__ rope_sin, const int* __restrict__ d_pos, int B, int H, int ctx_pad,
+                         float scale, float* __restrict__ att, int8_t* __restrict__ q8, float* __restrict__ s_out,
+                         int32_t* __restrict__ qsum_out)
+{
+    constexpr int LPK = DK / 8;    // lanes per key
+    constexpr int KPW = 32 / LPK;  // keys per warp-wide load
+    constexpr int U = 4;           // keys in flight per lane group
+    constexpr int half = DK / 2;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    float* orow = reinterpret_cast<float*>(smem_raw);  // d
+    float* sc_all = orow + H * DK;                     // H * ctx_pad
+    __shared__ float red_f[32];
+    __shared__ int red_i[32];
+
+    const int b = blockIdx.x, h = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int d = H * DK;
+    const int pos = *d_pos;
+    float* sc = sc_all + (size_t)h * ctx_pad;
+    const size_t head_off = ((size_t)b * H + h) * (size_t)own_alloc * DK;
+    __nv_bfloat16* kc = kcache + head_off - (size_t)pre_len * DK;  // indexed by absolute position >= pre_len
+    __nv_bfloat16* vc = vcache + head_off - (size_t)pre_len * DK;
+    const size_t pre_off = ((size_t)(b / group) * H + h) * (size_t)pre_alloc * DK;
+    const __nv_bfloat16* kp = kpre ? kpre + pre_off : nullptr;
+    const __nv_bfloat16* vp = vpre ? vpre + pre_off : nullptr;
+    const float* qn = qkv + (size_t)b * d + (size_t)h * DK;
+    const float* kn = qkv + (size_t)B * d + (size_t)b * d + (size_t)h * DK;
+    const float* vn = qkv + 2 * (size_t)B * d + (size_t)b * d + (size_t)h * DK;
+
+    const int sub = lane / LPK, sl = lane % LPK;
+    const int e0 = sl * 8;
+    // this lane's 8 features of q and of the new key, rotated; the partner half comes from global memory too
+    float qv[8], kv_new[8];
+    {
+        const int ep = e0 < half ? e0 + half : e0 - half;
+        float qa[8], qb[8], ka[8], kb[8];
+        *reinterpret_cast<float4*>(qa) = *reinterpret_cast<const float4*>(qn + e0);
+        *reinterpret_cast<float4*>(qa + 4) = *reinterpret_cast<const float4*>(qn + e0 + 4);
+        *reinterpret_cast<float4*>(ka) = *reinterpret_cast<const float4*>(kn + e0);
+        *reinterpret_cast<float4*>(ka + 4) = *reinterpret_cast<const float4*>(kn + e0 + 4);
+        if (rope_cos) {
+            *reinterpret_cast<float4*>(qb) = *reinterpret_cast<const float4*>(qn + ep);
+            *reinterpret_cast<float4*>(qb + 4) = *reinterpret_cast<const float4*>(qn + ep + 4);
+            *reinterpret_cast<float4*>(kb) = *reinterpret_cast<const float4*>(kn + ep);
+            *reinterpret_cast<float4*>(kb + 4) = *reinterpret_cast<const float4*>(kn + ep + 4);
+            const float sgn = e0 < half ? -1.0f : 1.0f;  // first half: a*c - b*s, second half: b*c + a*s
+            const int j0 = e0 % half;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float c = rope_cos[(size_t)pos * half + j0 + i], sn = sgn * rope_sin[(size_t)pos * half + j0 + i];
+                qv[i] = qa[i] * c + qb[i] * sn;
+                kv_new[i] = ka[i] * c + kb[i] * sn;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { qv[i] = qa[i]; kv_new[i] = ka[i]; }
+        }
+    }
+    if (sub == 0) {
+        float vv[8];
+        *reinterpret_cast<float4*>(vv) = *reinterpret_cast<const float4*>(vn + e0);
+        *reinterpret_cast<float4*>(vv + 4) = *reinterpret_cast<const float4*>(vn + e0 + 4);
+        uint4 pk, pv;
+        pk.x = pack_bf16x2(kv_new[0], kv_new[1]); pk.y = pack_bf16x2(kv_new[2], kv_new[3]);
+        pk.z = pack_bf16x2(kv_new[4], kv_new[5]); pk.w = pack_bf16x2(kv_new[6], kv_new[7]);
+        pv.x = pack_bf16x2(vv[0], vv[1]); pv.y = pack_bf16x2(vv[2], vv[3]);
+        pv.z = pack_bf16x2(vv[4], vv[5]); pv.w = pack_bf16x2(vv[6], vv[7]);
+        *reinterpret_cast<uint4*>(kc + (size_t)pos * DK + e0) = pk;
+        *reinterpret_cast<uint4*>(vc + (size_t)pos * DK + e0) = pv;
+    }
+    __syncwarp();
+    const int n_keys = pos + 1;
+
+    // scores
+    float mx = -INFINITY;
+    for (int base = 0; base < n_keys; base += KPW * U) {
+        uint4 raw[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int j = base + u * KPW + sub;
+            raw[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (j < n_keys) raw[u] = *reinterpret_cast<const uint4*>((j < pre_len ? kp : kc) + (size_t)j * DK + e0);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int j = base + u * KPW + sub;
+            float kf[8];
+            bf16x8_to_float(raw[u], kf);
+            float part = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) part = fmaf(qv[i], kf[i], part);
+#pragma unroll
+            for (int o = LPK / 2; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+            part *= scale;
+            if (j < n_keys) {
+                mx = fmaxf(mx, part);
+                if (sl == 0) sc[j] = part;
+            }
+        }
+    }
+    mx = warp_max(mx);
+    __syncwarp();
+    float sum = 0.0f;
+    for (int j = lane; j < n_keys; j += 32) {
+        const float ev = __expf(sc[j] - mx);
+        sc[j] = ev;
+        sum += ev;
+    }
+    sum = warp_sum(sum);
+    const float inv = 1.0f / sum;
+    __syncwarp();
+
+    // out = sum_j p_j v_j
+    float o8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int base = 0; base < n_keys; base += KPW * U) {
+        uint4 raw[U];
+        float pj[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int j = base + u * KPW + sub;
+            raw[u] = make_uint4(0u, 0u, 0u, 0u);
+            pj[u] = 0.0f;
+            if (j < n_keys) {
+                raw[u] = *reinterpret_cast<const uint4*>((j < pre_len ? vp : vc) + (size_t)j * DK + e0);
+                pj[u] = sc[j];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            float vf[8];
+            bf16x8_to_float(raw[u], vf);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o8[i] = fmaf(pj[u], vf[i], o8[i]);
+        }
+    }
+#pragma unroll
+    for (int o = LPK; o < 32; o <<= 1)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o8[i] += __shfl_xor_sync(0xffffffffu, o8[i], o);
+    if (sub == 0) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o8[i] *= inv;
+        float* dst = orow + h * DK + e0;
+        *reinterpret_cast<float4*>(dst) = make_float4(o8[0], o8[1], o8[2], o8[3]);
+        *reinterpret_cast<float4*>(dst + 4) = make_float4(o8[4], o8[5], o8[6], o8[7]);
+        if (att) {
+            float* ga = att + (size_t)b * d + (size_t)h * DK + e0;
+            *reinterpret_cast<float4*>(ga) = make_float4(o8[0], o8[1], o8[2], o8[3]);
+            *reinterpret_cast<float4*>(ga + 4) = make_float4(o8[4], o8[5], o8[6], o8[7]);
+        }
+    }
+    __syncthreads();
+    if (!q8) return;
+
+    // int8 quantisation of the token's row (same rule and layout as row_quant_fast_kernel)
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    float amx = 0.0f;
+    for (int i = tid; i < d; i += nthr) amx = fmaxf(amx, fabsf(orow[i]));
+    amx = warp_max(amx);
+    if (lane == 0) red_f[h] = amx;
+    __syncthreads();
+    amx = red_f[0];
+    for (int w = 1; w < H; ++w) amx = fmaxf(amx, red_f[w]);
+    const float scq = __fmul_rn(amx, 1.0f / 127.0f);
+    const float invq = scq > 0.0f ? 1.0f / scq : 0.0f;
+    uint32_t* qrow = reinterpret_cast<uint32_t*>(q8 + (size_t)b * d);
+    int local = 0;
+    for (int w = tid; w < d / 4; w += nthr) {
+        const int blk = w >> 4, wd = w & 15;
+        const int i = wd >> 2, t = wd & 3;
+        uint32_t word = 0;
+#pragma unroll
+        for (int bb = 0; bb < 4; ++bb) {
+            float v = orow[blk * 64 + 16 * t + 4 * bb + i] * invq;
+            v = (v != v) ? 0.0f : fminf(fmaxf(v, -127.0f), 127.0f);
+            const int qi = (int)roundf(v);
+            local += qi;
+            word |= (uint32_t)(uint8_t)(int8_t)qi << (8 * bb);
+        }
+        qrow[w] = word;
+    }
+    local = warp_sum_i(local);
+    if (lane == 0) red_i[h] = local;
+    __syncthreads();
+    if (tid == 0) {
+        int tot = 0;
+        for (int w = 0; w < H; ++w) tot += red_i[w];
+        qsum_out[b] = tot;
+        s_out[b] = scq;
+    }
+}
+
+bool attn_decode_fused_supported(size_t H, size_t dk) { return (dk == 64 || dk == 128) && H >= 1 && H <= 32; }
+
+// fast mode only (bf16 caches).  att may be NULL; q8 / s / qsum may be NULL together (attention only).
+nnb_status launch_attn_decode_fused(nnb_engine* e, const float* qkv, void* kcache, void* vcache, size_t own_alloc,
+                                    const void* kpre, const void* vpre, size_t pre_len, size_t pre_alloc, size_t group,
+                                    const float* rope_cos, const float* rope_sin, const int* d_pos, size_t B, size_t H,
+                                    size_t dk, float* att, int8_t* q8, float* s, int32_t* qsum)
+{
+    NNB_REQUIRE(attn_decode_fused_supported(H, dk), "attn_decode_fused: %zu heads of %zu features unsupported", H, dk);
+    NNB_REQUIRE(group >= 1 && (pre_len == 0 || (kpre && vpre)), "attn_decode_fused: bad prefix arguments");
+    NNB_REQUIRE((q8 == nullptr) == (s == nullptr) && (q8 == nullptr) == (qsum == nullptr), "attn_decode_fused: q8, s, qsum go together");
+    const size_t ctx_pad = (pre_len + own_alloc + 3) & ~(size_t)3;
+    const size_t smem = (H * dk + H * ctx_pad) * sizeof(float);
+    NNB_REQUIRE(smem <= 200 * 1024, "attn_decode_fused: context %zu too long for one CTA", pre_len + own_alloc);
+    const float scale = 1.0f / sqrtf((float)dk);
+#define NNB_FUSED(DKV)                                                                                                    \
+    {                                                                                                                     \
+        auto kern = attn_decode_fused_kernel<DKV>;                                                                        \
+        static size_t cfg = 0;                                                                                            \
+        if (smem > cfg) {                                                                                                 \
+            NNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                 \
+            cfg = smem;                                                                                                   \
+        }                                                                                                                 \
+        kern<<<(unsigned)B, (unsigned)(32 * H), smem, e->stream>>>(                                                       \
+            qkv, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, (int)own_alloc, (const __nv_bfloat16*)kpre,              \
+            (const __nv_bfloat16*)vpre, (int)pre_len, (int)pre_alloc, (int)group, rope_cos, rope_sin, d_pos, (int)B, (int)H, \
+            (int)ctx_pad, scale, att, q8, s, qsum);                                                                       \
+    }
+    if (dk == 128) NNB_FUSED(128) else NNB_FUSED(64)
+#undef NNB_FUSED
+    e->launches++;
+    NNB_CHECK_LAUNCH("attn_decode_fused_kernel");
     return NNB_OK;
 }
 

@@ -275,12 +275,20 @@ static nnb_status decode_step(nnb_policy* p, const StepView& sv, bool with_head,
         NNB_TRY(launch_row_quant(e, 0, exact, w.x, P + L.ln1_g, B, d, d, w.q8, w.s, w.qsum, nullptr));
         // q, k, v projections: three equally shaped matrices stored back to back, one launch
         NNB_TRY(policy_linear_fwd(p, L.q, 3, w.q8, w.s, w.qsum, B, nullptr, w.qkv, B * d));
-        NNB_TRY(launch_attn_decode(e, exact, w.qkv, (char*)sv.k + (size_t)l * sv.layer_bytes,
-                                   (char*)sv.v + (size_t)l * sv.layer_bytes, sv.own_alloc,
-                                   sv.k_pre ? (const char*)sv.k_pre + (size_t)l * sv.pre_layer_bytes : nullptr,
-                                   sv.v_pre ? (const char*)sv.v_pre + (size_t)l * sv.pre_layer_bytes : nullptr, sv.pre_len,
-                                   sv.pre_alloc, sv.group, p->rope_cos, p->rope_sin, w.d_pos, B, H, dk, w.att));
-        NNB_TRY(launch_row_quant(e, 3, exact, w.att, nullptr, B, d, d, w.q8, w.s, w.qsum, nullptr));
+        void* kl = (char*)sv.k + (size_t)l * sv.layer_bytes;
+        void* vl = (char*)sv.v + (size_t)l * sv.layer_bytes;
+        const void* kpl = sv.k_pre ? (const char*)sv.k_pre + (size_t)l * sv.pre_layer_bytes : nullptr;
+        const void* vpl = sv.v_pre ? (const char*)sv.v_pre + (size_t)l * sv.pre_layer_bytes : nullptr;
+        if (!exact && attn_decode_fused_supported(H, dk) && d % 64 == 0) {
+            // all heads of a sequence in one CTA, attention output quantised in the same launch
+            NNB_TRY(launch_attn_decode_fused(e, w.qkv, kl, vl, sv.own_alloc, kpl, vpl, sv.pre_len, sv.pre_alloc, sv.group,
+                                             c.pos == 1 ? p->rope_cos : nullptr, c.pos == 1 ? p->rope_sin : nullptr, w.d_pos, B, H,
+                                             dk, nullptr, w.q8, w.s, w.qsum));
+        } else {
+            NNB_TRY(launch_attn_decode(e, exact, w.qkv, kl, vl, sv.own_alloc, kpl, vpl, sv.pre_len, sv.pre_alloc, sv.group,
+                                       p->rope_cos, p->rope_sin, w.d_pos, B, H, dk, w.att));
+            NNB_TRY(launch_row_quant(e, 3, exact, w.att, nullptr, B, d, d, w.q8, w.s, w.qsum, nullptr));
+        }
         NNB_TRY(policy_linear_fwd(p, L.o, 1, w.q8, w.s, w.qsum, B, w.x, w.x, 0));
         NNB_TRY(launch_row_quant(e, 0, exact, w.x, P + L.ln2_g, B, d, d, w.q8, w.s, w.qsum, nullptr));
         NNB_TRY(policy_linear_fwd(p, L.fc1, 1, w.q8, w.s, w.qsum, B, nullptr, w.h1, 0));

@@ -379,6 +379,27 @@ def attention_rope_bwd(self, q, k, v, rope_cos, rope_sin, out, dout, lse, n_seq,
     return dq, dk, dv
 
 
+def attention_decode(self, qkv, kcache, vcache, pos, n_head, rope=None, prefix=None, group=1, exact=True, want_out=True,
+                     want_q8=False):
+    """One new token per sequence against the KV cache.  qkv (3, n_seq, d); caches (n_seq, H, ctx_alloc, dk) f32 (exact)
+    or bf16; pos: int32 device tensor of one element; rope = (cos, sin); prefix = (kpre, vpre, pre_len)."""
+    _, n_seq, d = qkv.shape
+    dk = d // n_head
+    ctx_alloc = kcache.shape[2]
+    kpre, vpre, pre_len = prefix if prefix is not None else (None, None, 0)
+    pre_alloc = kpre.shape[2] if kpre is not None else 0
+    cos, sin = rope if rope is not None else (None, None)
+    out = torch.empty((n_seq, d), device=self.device, dtype=torch.float32) if want_out else None
+    q8 = torch.empty((n_seq, d), device=self.device, dtype=torch.int8) if want_q8 else None
+    s = torch.empty((n_seq,), device=self.device, dtype=torch.float32) if want_q8 else None
+    qsum = torch.empty((n_seq,), device=self.device, dtype=torch.int32) if want_q8 else None
+    check(self._lib.nnb_attention_decode(self._h, _ptr(qkv), _ptr(kcache), _ptr(vcache), ctx_alloc, _ptr(kpre), _ptr(vpre),
+                                         pre_len, pre_alloc, group, _ptr(cos), _ptr(sin), _ptr(pos), n_seq, n_head, dk,
+                                         int(exact), _ptr(out), _ptr(q8), _ptr(s), _ptr(qsum)))
+    return out, q8, s, qsum
+
+
+Engine.attention_decode = attention_decode
 Engine.attention_fwd = attention_fwd
 Engine.attention_bwd = attention_bwd
 Engine.attention_rope_fwd = attention_rope_fwd

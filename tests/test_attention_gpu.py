@@ -81,3 +81,66 @@ def test_attention_with_rope_inside(eng, n, S, H, dk):
         assert np.abs(lse.cpu().numpy() - lse_ref).max() <= tol * max(1.0, np.abs(lse_ref).max())
         dq, dkk, dv = eng.attention_rope_bwd(tq, tk, tv, tc, ts, out, tg, lse, n, S, H, exact=exact)
         assert _err(dq, dq_ref) <= tol and _err(dkk, dk_ref) <= tol and _err(dv, dv_ref) <= tol
+
+
+def _bf16_round(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(torch.bfloat16).float().numpy()
+
+
+@pytest.mark.parametrize("n,H,dk,pos,pre_len,group", [(4, 4, 64, 17, 0, 1), (3, 16, 128, 40, 0, 1), (4, 2, 128, 21, 8, 2),
+                                                      (6, 3, 64, 9, 9, 3), (2, 2, 32, 5, 0, 1)])
+def test_attention_decode_step(eng, n, H, dk, pos, pre_len, group):
+    """One new token against the cache: rotation, append, attention over prefix + own positions; the exact path
+    against float64, the bf16 paths (per-head kernel and all-heads kernel with the fused int8 output) within
+    bf16 rounding, and the fused quantisation against the quantisation of its own f32 output."""
+    rng = np.random.default_rng(n * 1000 + pos)
+    d, half, ctx_alloc, pre_alloc = H * dk, dk // 2, 48, max(pre_len, 1) + 3
+    qkv = rng.normal(0, 1, (3, n, d)).astype(np.float32)
+    kown = rng.normal(0, 1, (n, H, ctx_alloc, dk)).astype(np.float32)
+    vown = rng.normal(0, 1, (n, H, ctx_alloc, dk)).astype(np.float32)
+    kpre = rng.normal(0, 1, (n // group, H, pre_alloc, dk)).astype(np.float32)
+    vpre = rng.normal(0, 1, (n // group, H, pre_alloc, dk)).astype(np.float32)
+    ang = np.arange(64)[:, None] * (10000.0 ** (-np.arange(half) / half))[None, :]
+    cos, sin = np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
+
+    def reference(rnd):
+        q4, k4, v4 = (qkv[i].astype(np.float64).reshape(n, H, dk) for i in range(3))
+        c, s = cos[pos].astype(np.float64), sin[pos].astype(np.float64)
+        rot = lambda x: np.concatenate([x[..., :half] * c - x[..., half:] * s, x[..., half:] * c + x[..., :half] * s], -1)
+        qr, kr = rot(q4), rnd(rot(k4))
+        out = np.zeros((n, H, dk))
+        for b in range(n):
+            keys = np.concatenate([rnd(kpre[b // group][:, :pre_len]), rnd(kown[b][:, :pos - pre_len]), kr[b][:, None]], 1)
+            vals = np.concatenate([rnd(vpre[b // group][:, :pre_len]), rnd(vown[b][:, :pos - pre_len]), rnd(v4[b])[:, None]], 1)
+            sc = np.einsum("hd,hjd->hj", qr[b], keys.astype(np.float64)) / np.sqrt(dk)
+            w = np.exp(sc - sc.max(-1, keepdims=True))
+            w /= w.sum(-1, keepdims=True)
+            out[b] = np.einsum("hj,hjd->hd", w, vals.astype(np.float64))
+        return out.reshape(n, d), kr
+
+    dev = eng.device
+    tq = torch.from_numpy(qkv).to(dev)
+    tpos = torch.tensor([pos], device=dev, dtype=torch.int32)
+    rope = (torch.from_numpy(cos).to(dev), torch.from_numpy(sin).to(dev))
+    for exact in (True, False):
+        dt = torch.float32 if exact else torch.bfloat16
+        rnd = (lambda a: a) if exact else _bf16_round
+        ref, kr = reference(rnd)
+        for fused in ((False,) if exact else (False, True)):
+            if fused and dk not in (64, 128):
+                continue
+            kc, vc = torch.from_numpy(kown).to(dev).to(dt), torch.from_numpy(vown).to(dev).to(dt)
+            prefix = (torch.from_numpy(kpre).to(dev).to(dt), torch.from_numpy(vpre).to(dev).to(dt), pre_len) if pre_len else None
+            out, q8, s, qsum = eng.attention_decode(tq, kc, vc, tpos, H, rope=rope, prefix=prefix, group=group, exact=exact,
+                                                    want_q8=fused)
+            tol = 1e-5 if exact else 2e-2
+            assert _err(out, ref) <= tol
+            # the new key and value were appended at row pos - pre_len
+            assert np.abs(kc[:, :, pos - pre_len].float().cpu().numpy() - kr).max() <= (1e-5 if exact else 2e-2)
+            assert np.abs(vc[:, :, pos - pre_len].float().cpu().numpy() - qkv[2].reshape(n, H, dk)).max() <= (1e-6 if exact else 2e-2)
+            if fused:
+                q_ref, s_ref, qs_ref = eng.act_quant_tm(out)
+                assert torch.allclose(s, s_ref, rtol=1e-6, atol=0)
+                dq = (q8.int() - q_ref.int()).abs()
+                assert int(dq.max()) <= 1 and float((dq > 0).float().mean()) < 1e-3  # x/s against x*(1/s) at a rounding tie
+                assert torch.equal(qsum, eng.actq_to_plain(q8).int().sum(1).int())
