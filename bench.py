@@ -29,7 +29,7 @@ WORKLOADS = {
     # the configuration the metric is quoted on
     "grpo1b": dict(model=dict(n_layer=24, d_model=2048, n_head=16, d_ff=5632, vocab=32000, ctx=640, act=1, pos=1),
                    groups=64, group_size=16, prompt_len=128, max_new=512, temperature=0.8, top_k=50,
-                   micro_batch=16, rollout_chunk=512),
+                   micro_batch=16, rollout_chunk=1024),
     # the CPU-runnable configuration (parity-test shape; selectable for quick checks)
     "tiny": dict(model=dict(n_layer=4, d_model=256, n_head=4, d_ff=1024, vocab=10000, ctx=256, act=0, pos=0),
                  groups=8, group_size=8, prompt_len=32, max_new=64, temperature=1.0, top_k=0,

@@ -120,4 +120,6 @@ def lib() -> C.CDLL:
 def check(status: int) -> None:
     if status != 0:
         msg = lib().nnb_last_error()
-        raise NnbError(f"nnb_status {status}: {msg.decode() if msg else '?'}")
+        err = NnbError(f"nnb_status {status}: {msg.decode() if msg else '?'}")
+        err.status = status
+        raise err

@@ -12,6 +12,7 @@ from dataclasses import dataclass
 
 import torch
 
+from ._lib import NnbError
 from .policy import Policy
 
 
@@ -51,6 +52,7 @@ class GrpoTrainer:
         self.rank = self.dist.get_rank() if self.dist else 0
         self.world = self.dist.get_world_size() if self.dist else 1
         self.timings = {}
+        self._chunk = cfg.rollout_chunk  # shrinks if a KV cache of that many sequences does not fit
 
     def _allreduce(self, t):
         if self.dist and self.world > 1:
@@ -62,14 +64,24 @@ class GrpoTrainer:
         c = self.cfg
         rep = prompts.repeat_interleave(c.group_size, dim=0).contiguous()
         n = rep.shape[0]
-        chunk = max(c.group_size, (min(c.rollout_chunk, n) // c.group_size) * c.group_size)
-        toks, lps = [], []
-        for a in range(0, n, chunk):
-            t, lp, _ = self.policy.rollout(rep[a:a + chunk].contiguous(), c.max_new, temperature=c.temperature,
-                                           top_k=c.top_k, seed=seed, seq0=seq0 + a, group_size=c.group_size)
-            toks.append(t)
-            lps.append(lp)
-        return torch.cat(toks), torch.cat(lps)
+        chunk = max(c.group_size, (min(self._chunk, n) // c.group_size) * c.group_size)
+        while True:
+            toks, lps = [], []
+            try:
+                for a in range(0, n, chunk):
+                    t, lp, _ = self.policy.rollout(rep[a:a + chunk].contiguous(), c.max_new, temperature=c.temperature,
+                                                   top_k=c.top_k, seed=seed, seq0=seq0 + a, group_size=c.group_size)
+                    toks.append(t)
+                    lps.append(lp)
+                return torch.cat(toks), torch.cat(lps)
+            except NnbError as ex:
+                # the engine refuses a KV cache that does not fit (status -4) before allocating it: decode
+                # fewer sequences together.  The samples do not depend on the chunking (Philox counters are
+                # per sequence), so the retry reproduces the same rollout.
+                if getattr(ex, "status", 0) != -4 or chunk <= c.group_size:
+                    raise
+                chunk = max(c.group_size, (chunk // 2 // c.group_size) * c.group_size)
+                self._chunk = chunk
 
     def step(self, prompts: torch.Tensor, reward_fn, seed: int, timers=None):
         """One GRPO step on this rank's prompt groups.  reward_fn(tokens (N,S)) -> (N,) f32 on the device."""
