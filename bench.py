@@ -158,7 +158,11 @@ def _kernel_rooflines(torch, pkg, eng, pol, wl, peaks):
     flops = 2.0 * T * d * O
     ach = flops / (ms * 1e-3) / 1e12
     out["roofline"] = {"bound": "tensor", "achieved": ach, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
-                       "frac": ach / peaks["bf16_tflops_sustained"], "traffic": None, "peak_source": peaks["src"] + " (sustained)",
+                       "frac": ach / peaks["bf16_tflops_sustained"],
+                       # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this shape
+                       # (profiles/gemm_tc_kernel_bf16_dx_10240x11264x2048.md); algorithmic bytes 361 MB
+                       "traffic": 557.7e6 if (T, O, d) == (10240, 11264, 2048) else None,
+                       "peak_source": peaks["src"] + " (sustained)",
                        "kernel": "gemm_tc_kernel<bf16 dX>", "kernel_ms": ms, "shape": f"T={T} K={O} N={d}"}
     # (2) ternary forward GEMM at one micro-batch (tcgen05 kind::i8, int32 accumulation in TMEM)
     y = torch.empty((T, O), device=dev)
@@ -168,6 +172,20 @@ def _kernel_rooflines(torch, pkg, eng, pol, wl, peaks):
                                  "shape": f"T={T} K={d} O={O}"}
     eng.check_device_errors()
     del w8, wb, dy, dx, dyb, y
+    # (2b) decode attention of one step at a mid-rollout context: the HBM-bound kernel of the rollout
+    H = m["n_head"]
+    dk = d // H
+    Bd, ctx, pos = 512, 512, 400
+    kc = torch.randn((Bd, H, ctx, dk), device=dev).to(torch.bfloat16)
+    vc = torch.randn((Bd, H, ctx, dk), device=dev).to(torch.bfloat16)
+    qkv = torch.randn((3, Bd, d), device=dev)
+    tpos = torch.tensor([pos], device=dev, dtype=torch.int32)
+    ms = _time_loop(torch, lambda: eng.attention_decode(qkv, kc, vc, tpos, H, exact=False, want_out=False, want_q8=True), 10)
+    alg = Bd * H * (pos + 1) * dk * 2 * 2 + 3 * Bd * d * 4 + Bd * d
+    out["roofline_attn_decode"] = {"bound": "hbm", "achieved": alg / (ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                   "frac": alg / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "kernel": "attn_decode_fused_kernel",
+                                   "kernel_ms": ms, "shape": f"B={Bd} H={H} dk={dk} pos={pos}"}
+    del kc, vc, qkv
     # (3) decode-sized ternary GEMV: packed-weight stream of a stack of fc1-shaped matrices (> L2)
     n_mats = 64
     wst = torch.randint(-2**31, 2**31 - 1, (n_mats, O, d // 16), device=dev, dtype=torch.int64)

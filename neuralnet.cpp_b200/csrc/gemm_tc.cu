@@ -454,12 +454,13 @@ static nnb_status launch(nnb_engine* e, const CUtensorMap& ta, const CUtensorMap
 
 }  // namespace tc
 
-// Width of the forward output tile.  The int8 tensor pipe is the bound (a 128 x 256 x 32 kind::i8 instruction
-// occupies it for 512 clocks, and narrower instructions in proportion), so a launch takes about
-// ceil(tiles / SMs) * BN: the choice only trades rounding of the last round of tiles; ties go to the wider
-// tile, which pulls fewer bytes through L2.
+// Width of the forward output tile.  A launch runs ceil(tiles / SMs) rounds of tiles; a round costs a fixed
+// part (pipeline fill, epilogue of the last tile, barrier turnarounds: about what 230 columns of a K = 2048
+// main loop cost) plus a main loop proportional to BN * K.  Measured on 10240 x 2048 x 6144: 5.1 / 6.2 /
+// 6.7 / 8.5 us per round for BN = 64 / 128 / 192 / 256.  Wide tiles win whenever they fill the SMs; narrow
+// ones only pay off for a few hundred tokens, where they turn a half-empty round into a full one.
 static int g_forward_bn_override = 0;
-static int choose_forward_bn(size_t t, size_t out, int sm_count)
+static int choose_forward_bn(size_t t, size_t k, size_t out, int sm_count)
 {
     if (g_forward_bn_override) return g_forward_bn_override;
     const int cand[4] = {256, 192, 128, 64};
@@ -467,7 +468,7 @@ static int choose_forward_bn(size_t t, size_t out, int sm_count)
     size_t best_cost = (size_t)-1;
     for (int bn : cand) {
         const size_t tiles = ceil_div(t, (size_t)tc::BM) * ceil_div(out, (size_t)bn);
-        const size_t cost = ceil_div(tiles, (size_t)sm_count) * (size_t)bn;
+        const size_t cost = ceil_div(tiles, (size_t)sm_count) * (230 * 2048 + (size_t)bn * k);
         if (cost < best_cost) {
             best_cost = cost;
             best = bn;
@@ -501,7 +502,7 @@ nnb_status launch_tc_forward(nnb_engine* e, const int8_t* q, const int8_t* w8, c
     }
     tc::Epi ep{y, tau, s, bias, residual, 0, (int)out, n_mats > 1 ? y_stride : 0};
     out *= n_mats;
-    switch (choose_forward_bn(t, out, e->sm_count)) {
+    switch (choose_forward_bn(t, k, out, e->sm_count)) {
         case 64: return tc_forward_bn<64>(e, q, w8, ep, t, k, out);
         case 128: return tc_forward_bn<128>(e, q, w8, ep, t, k, out);
         case 192: return tc_forward_bn<192>(e, q, w8, ep, t, k, out);

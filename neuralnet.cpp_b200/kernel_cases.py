@@ -1,0 +1,127 @@
+"""Runs one kernel (or one phase) of the RL-step path a few times on its benchmark shape.
+
+    python neuralnet.cpp_b200/kernel_cases.py <case> [args]
+
+Used for Nsight Compute captures and quick timing; every case prints its CUDA-event time.  Cases:
+  fwd          int8 ternary forward GEMM (tcgen05), T=10240 K=2048 O=11264
+  dx | dw      bf16 backward GEMMs (tcgen05) of the same linear
+  gemv         2-bit packed weight stream, 16 tokens, stack of 64 matrices (2048 x 11264)
+  attn_decode  decode attention of 512 sequences x 16 heads x 128 at position 400, fused int8 output
+  train [n]    reference log-probs + one training micro-batch of n (16) sequences x 640 on the 1B policy
+  rollout [B P new]   batched rollout on the 1B policy (default 512 16 24)
+"""
+import os
+import sys
+
+import numpy as np
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from __graft_entry__ import load_package  # noqa: E402
+
+MODEL_1B = dict(n_layer=24, d_model=2048, n_head=16, d_ff=5632, vocab=32000, ctx=640, act=1, pos=1)
+
+
+def _rand_packed(dev, *shape):
+    """Random 2-bit containers without the unused code 0 (trit + 2 in {1, 2, 3})."""
+    w = torch.randint(-2**31, 2**31 - 1, shape, device=dev, dtype=torch.int64) & 0xFFFFFFFF
+    lo, hi = w & 0x55555555, (w >> 1) & 0x55555555
+    w = w | (((~(lo | hi)) & 0x55555555) << 1)
+    return torch.where(w >= 2**31, w - 2**32, w).to(torch.int32).contiguous()
+
+
+def _timed(name, fn, reps=4):
+    fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    print(f"{name}: {a.elapsed_time(b) / reps * 1e3:.1f} us per call")
+
+
+def _policy(pkg, eng):
+    cfg = pkg.GptConfig(exact=False, **MODEL_1B)
+    pol = pkg.Policy(eng, cfg)
+    g = torch.Generator(device=eng.device)
+    g.manual_seed(1)
+    pv = pol.params_view()
+    pv.normal_(0, 0.02, generator=g)
+    for name, off, shape in cfg.param_layout()[0]:
+        size = int(np.prod(shape))
+        if name.endswith("gamma"):
+            pv[off:off + size] = 1.0
+        elif name.endswith(".bias"):
+            pv[off:off + size] = 0.0
+    pol.requantize()
+    return cfg, pol, g
+
+
+def main(argv):
+    case = argv[1] if len(argv) > 1 else "fwd"
+    pkg = load_package()
+    eng = pkg.Engine(0)
+    dev = eng.device
+    if case in ("fwd", "dx", "dw"):
+        T, k, out = 10240, 2048, 11264
+        w8, wb = eng.expand_weights(_rand_packed(dev, out, k // 16), k)
+        tau = torch.rand(out, device=dev) * 0.05 + 0.01
+        q, s, _ = eng.act_quant_tm(torch.randn(T, k, device=dev))
+        if case == "fwd":
+            y = torch.empty(T, out, device=dev)
+            _timed("int8 forward GEMM", lambda: eng.bitlinear_fwd_tc(w8, tau, None, q, s, y=y))
+        else:
+            dy = torch.randn(T, out, device=dev)
+            dx = torch.empty(T, k, device=dev)
+            dw = torch.zeros(out, k, device=dev)
+            scratch = (torch.empty(T, out, device=dev, dtype=torch.bfloat16), torch.empty(T, k, device=dev, dtype=torch.bfloat16))
+            eng.bitlinear_bwd_tc(dy, tau, wb, q, s, k, dx=dx, dw=dw, scratch=scratch)  # fills the bf16 operands
+            if case == "dx":
+                _timed("bf16 dX GEMM", lambda: eng.bitlinear_bwd_tc(dy, tau, wb, q, s, k, dx=dx, scratch=scratch, prepared=True))
+            else:
+                _timed("bf16 dW GEMM", lambda: eng.bitlinear_bwd_tc(dy, tau, wb, q, s, k, want_dx=False, dw=dw, scratch=scratch,
+                                                                    prepared=True))
+    elif case == "gemv":
+        k, out, n = 2048, 11264, 64
+        wst = _rand_packed(dev, n, out, k // 16)
+        taus = torch.rand(n, out, device=dev) * 0.05 + 0.01
+        q, s, qs = eng.act_quant_tm(torch.randn(16, k, device=dev))
+        ys = torch.empty(n, 16, out, device=dev)
+        _timed("packed GEMV stack", lambda: eng.bitlinear_fwd_tm_stack(wst, taus, None, q, s, qs, ys))
+    elif case == "attn_decode":
+        B, H, dk, ctx, pos = 512, 16, 128, 512, 400
+        kc = torch.randn(B, H, ctx, dk, device=dev).to(torch.bfloat16)
+        vc = torch.randn(B, H, ctx, dk, device=dev).to(torch.bfloat16)
+        qkv = torch.randn(3, B, H * dk, device=dev)
+        tpos = torch.tensor([pos], device=dev, dtype=torch.int32)
+        half = dk // 2
+        ang = torch.arange(ctx, device=dev)[:, None] * (10000.0 ** (-torch.arange(half, device=dev) / half))[None, :]
+        rope = (torch.cos(ang).contiguous(), torch.sin(ang).contiguous())
+        _timed("decode attention (fused int8 output)",
+               lambda: eng.attention_decode(qkv, kc, vc, tpos, H, rope=rope, exact=False, want_out=False, want_q8=True))
+    elif case == "train":
+        n = int(argv[2]) if len(argv) > 2 else 16
+        cfg, pol, g = _policy(pkg, eng)
+        tokens = torch.randint(0, cfg.vocab, (n, 640), device=dev, dtype=torch.int32, generator=g)
+        mask = torch.ones((n, 512), device=dev)
+        adv = torch.randn((n, 512), device=dev, generator=g)
+        lp, _, _ = pol.logprobs(tokens, 128)
+        pol.zero_grad()
+        pol.train_step(tokens, 128, mask, old_logp=lp, advantage=adv, ref_logp=lp, kl_coef=0.04)
+        _timed("reference log-probs", lambda: pol.logprobs(tokens, 128), reps=2)
+        _timed("training micro-batch", lambda: pol.train_step(tokens, 128, mask, old_logp=lp, advantage=adv, ref_logp=lp,
+                                                              kl_coef=0.04), reps=2)
+    elif case == "rollout":
+        B, P, new = (int(a) for a in argv[2:5]) if len(argv) > 4 else (512, 16, 24)
+        cfg, pol, g = _policy(pkg, eng)
+        prompts = torch.randint(0, cfg.vocab, (B, P), device=dev, dtype=torch.int32, generator=g)
+        _timed(f"rollout {B} x ({P}+{new})", lambda: pol.rollout(prompts, new, temperature=0.8, top_k=50, seed=1), reps=1)
+    else:
+        raise SystemExit(__doc__)
+    eng.check_device_errors()
+
+
+if __name__ == "__main__":
+    main(sys.argv)
