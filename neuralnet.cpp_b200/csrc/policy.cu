@@ -141,9 +141,10 @@ nnb_status policy_ensure_wb(nnb_policy* p)
 nnb_status policy_linear_fwd(nnb_policy* p, const LinW& l, size_t n_mats, const int8_t* q, const float* s,
                              const int32_t* qsum, size_t T, const float* residual, float* y, size_t y_stride)
 {
-    // from a few hundred tokens up the tcgen05 kernel wins (its tile width follows the shape); below that the
-    // persistent mma.sync kernels stream the 2-bit container, a quarter of the int8 copy's bytes
-    if (!p->cfg.exact && p->w8 && T >= 256)
+    // from 64 tokens up the tcgen05 kernel wins (its tile width follows the shape; measured 1.7-1.9x over the
+    // mma.sync kernel at 128 tokens); below that the persistent mma.sync kernels stream the 2-bit container,
+    // a quarter of the int8 copy's bytes
+    if (!p->cfg.exact && p->w8 && T >= 64)
         return launch_tc_forward(p->e, q, p->w8 + l.packed_off * 16, p->tau + l.tau_off, s, p->params + l.b_off, residual, T,
                                  l.in, l.out, y, n_mats, y_stride);
     return launch_bitlinear_fwd_tm(p->e, p->packed + l.packed_off, n_mats > 1 ? l.out * (l.in / 16) : 0, p->tau + l.tau_off,
