@@ -288,6 +288,17 @@ typedef struct nnb_objective {
  * clip_fraction, kl_loss, entropy_loss, mean entropy, units, value_loss, value clip_fraction. */
 nnb_status nnb_policy_train_step(nnb_policy* p, const int32_t* d_tokens, size_t n_seq, size_t seq_len,
                                  size_t prompt_len, const nnb_objective* obj, float* d_report);
+/* The same two calls for a batch whose sequences come in groups of `group` consecutive rows that share
+ * their first prompt_len tokens (the completions of one prompt, as nnb_rollout_grouped produces them; the
+ * caller vouches for it).  Results per sequence are those of the plain calls; the prompt's rows are
+ * stored and computed once per group instead of once per sequence, and their gradient contributions are
+ * summed before the weight-gradient GEMMs.  Applies in the fast mode when prompt_len is a multiple of 64;
+ * otherwise the calls fall back to one copy per sequence.  No counterpart in the reference, which runs
+ * every sequence in full. */
+nnb_status nnb_policy_logprobs_grouped(nnb_policy* p, const int32_t* d_tokens, size_t n_seq, size_t seq_len, size_t prompt_len,
+                                       size_t group, float* d_logp, float* d_entropy, float* d_value);
+nnb_status nnb_policy_train_step_grouped(nnb_policy* p, const int32_t* d_tokens, size_t n_seq, size_t seq_len,
+                                         size_t prompt_len, size_t group, const nnb_objective* obj, float* d_report);
 /* flat f32 gradient buffer, same layout as the parameters (allocated and zeroed on first use) */
 float* nnb_policy_grads(nnb_policy* p);
 nnb_status nnb_policy_zero_grad(nnb_policy* p);

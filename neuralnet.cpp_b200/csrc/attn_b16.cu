@@ -61,29 +61,46 @@ __device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_grou
 template <int N>
 __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
 
-// stage ROWS rows x DK features of a (n*S, d) bf16 matrix; rows at or beyond S are zero
+// Where the rows of one sequence live (see SeqMap): positions [0, P) at pre_base + r, positions >= P at
+// own_base + (r - P).  For the plain layout both pieces are contiguous.
+struct RowAddr {
+    size_t pre_base, own_base;
+    int P;
+    __device__ __forceinline__ size_t at(int r) const { return r < P ? pre_base + r : own_base + (r - P); }
+};
+__device__ __forceinline__ RowAddr row_addr(const SeqMap& m, int b)
+{
+    RowAddr ra;
+    ra.P = m.P;
+    ra.pre_base = map_row(m, b, 0);
+    ra.own_base = map_row(m, b, m.P);
+    return ra;
+}
+
+// stage ROWS rows x DK features of a bf16 matrix with d features per row; rows at or beyond S are zero
 template <int DK, int LD, int ROWS, int THREADS>
-__device__ __forceinline__ void stage(const bf16* __restrict__ src, size_t base_row, int row0, int S, int d, int col0, bf16* dst)
+__device__ __forceinline__ void stage(const bf16* __restrict__ src, const RowAddr& ra, int row0, int S, int d, int col0, bf16* dst)
 {
     constexpr int CH = DK / 8;  // 16-byte chunks per row
     for (int i = threadIdx.x; i < ROWS * CH; i += THREADS) {
         const int r = i / CH, c = (i % CH) * 8;
         const bool ok = row0 + r < S;
         const int rr = ok ? row0 + r : S - 1;
-        cp16(dst + r * LD + c, src + (base_row + rr) * d + col0 + c, ok);
+        cp16(dst + r * LD + c, src + ra.at(rr) * d + col0 + c, ok);
     }
 }
 
 // ------------------------------------------------------------------ RoPE + bf16 pack
 // q, k, v: (T, d) f32.  out: three (T, d) bf16 planes T*d apart: q and k
-// rotated by the row's position (row % S) when tables are given, v converted.  One CTA per row.
+// rotated by the row's position (row_pos[row], or row % S without that table) when rope tables are given,
+// v converted.  One CTA per row.
 __global__ void __launch_bounds__(256)
 rope_pack_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
-                 const float* __restrict__ rope_cos, const float* __restrict__ rope_sin, int S, int H, int dk, size_t T,
-                 bf16* __restrict__ out)
+                 const float* __restrict__ rope_cos, const float* __restrict__ rope_sin, const int* __restrict__ row_pos, int S,
+                 int H, int dk, size_t T, bf16* __restrict__ out)
 {
     const size_t row = blockIdx.x;
-    const int pos = (int)(row % S);
+    const int pos = row_pos ? row_pos[row] : (int)(row % S);
     const int d = H * dk, half = dk / 2;
     // q, k: groups of four consecutive pair indices j (half % 4 == 0)
     const int groups = H * (half / 4);
@@ -124,9 +141,10 @@ rope_pack_kernel(const float* __restrict__ q, const float* __restrict__ k, const
 // scheduled first.
 template <int DK>
 __global__ void __launch_bounds__(128)
-attn_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v, int S, int H,
-                float scale, float* __restrict__ out, float* __restrict__ lse)
+attn_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v, const SeqMap map,
+                size_t rows, int H, float scale, float* __restrict__ out, float* __restrict__ lse)
 {
+    const int S = map.S;
     constexpr int LD = DK + 8;
     extern __shared__ __align__(16) unsigned char smraw[];
     bf16* Qs = reinterpret_cast<bf16*>(smraw);
@@ -135,8 +153,11 @@ attn_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf
     const int bh = blockIdx.x, b = bh / H, h = bh % H;
     const int d = H * DK;
     const int q0 = (gridDim.y - 1 - blockIdx.y) * 128;
+    // in a grouped batch the shared prefix rows are computed by the group's first member only
+    const int first_row = (map.group > 1 && b % map.group != 0) ? map.P : 0;
+    if (q0 + 128 <= first_row) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
-    const size_t base = (size_t)b * S;
+    const RowAddr base = row_addr(map, b);
     const int col0 = h * DK;
     const float sl2 = scale * 1.4426950408889634f;
 
@@ -269,16 +290,17 @@ attn_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf
 #pragma unroll
     for (int mt = 0; mt < 2; ++mt) {
         const int row_a = wrow0 + mt * 16 + g, row_b = row_a + 8;
+        const bool ok_a = row_a < S && row_a >= first_row, ok_b = row_b < S && row_b >= first_row;
         const float inv_a = 1.0f / l[mt * 2], inv_b = 1.0f / l[mt * 2 + 1];
 #pragma unroll
         for (int i = 0; i < DK / 8; ++i) {
             const int c = col0 + i * 8 + 2 * t4;
-            if (row_a < S) *reinterpret_cast<float2*>(out + (base + row_a) * d + c) = make_float2(o[mt][i][0] * inv_a, o[mt][i][1] * inv_a);
-            if (row_b < S) *reinterpret_cast<float2*>(out + (base + row_b) * d + c) = make_float2(o[mt][i][2] * inv_b, o[mt][i][3] * inv_b);
+            if (ok_a) *reinterpret_cast<float2*>(out + base.at(row_a) * d + c) = make_float2(o[mt][i][0] * inv_a, o[mt][i][1] * inv_a);
+            if (ok_b) *reinterpret_cast<float2*>(out + base.at(row_b) * d + c) = make_float2(o[mt][i][2] * inv_b, o[mt][i][3] * inv_b);
         }
         if (t4 == 0) {
-            if (row_a < S) lse[((size_t)b * H + h) * S + row_a] = m[mt * 2] * scale + logf(l[mt * 2]);
-            if (row_b < S) lse[((size_t)b * H + h) * S + row_b] = m[mt * 2 + 1] * scale + logf(l[mt * 2 + 1]);
+            if (ok_a) lse[map_vec(map, b, h, row_a, H, rows)] = m[mt * 2] * scale + logf(l[mt * 2]);
+            if (ok_b) lse[map_vec(map, b, h, row_b, H, rows)] = m[mt * 2 + 1] * scale + logf(l[mt * 2 + 1]);
         }
     }
 }
@@ -287,7 +309,7 @@ attn_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf
 // delta[b,h,i] = sum_c dO[row,h,c] * O[row,h,c], and dO as bf16.  One warp per (row, head), 4 features per lane.
 __global__ void __launch_bounds__(256)
 delta_pack_kernel(const float* __restrict__ dout, const float* __restrict__ out, int S, int H, int dk, size_t n_rows,
-                  float* __restrict__ delta, bf16* __restrict__ dob)
+                  int grouped, float* __restrict__ delta, bf16* __restrict__ dob)
 {
     const size_t w = (size_t)blockIdx.x * 8 + threadIdx.x / 32;  // (row, h)
     if (w >= n_rows * H) return;
@@ -306,7 +328,7 @@ delta_pack_kernel(const float* __restrict__ dout, const float* __restrict__ out,
     }
     a = warp_sum(a);
     const size_t b = row / S, i = row % S;
-    if (lane == 0) delta[(b * H + h) * S + i] = a;
+    if (lane == 0) delta[grouped ? (size_t)h * n_rows + row : (b * H + h) * S + i] = a;
 }
 
 // S = Q K^T and dP = dO V^T for a 64 x 64 (query, key) block, then P and dS as bf16 into shared memory.
@@ -378,14 +400,16 @@ __device__ __forceinline__ int chunk_base(int wc, int np)
 // c >= 2), feature chunk_base(wc, np) + e*8 + 2*t4 + (c & 1)
 template <int DK>
 __device__ __forceinline__ void store_rows(float (&acc)[DK / 16][4], float mul, const float* rope_cos, const float* rope_sin,
-                                           int row_a, int S, size_t base, int d, int col0, int wc, float* dst)
+                                           int row_a, int first_row, int S, const RowAddr& base, int d, int col0, int wc,
+                                           float* dst)
 {
     constexpr int NCH = DK / 32, half = DK / 2;
     const int lane = threadIdx.x & 31, t4 = lane & 3;
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
         const int row = row_a + 8 * hh;
-        if (row >= S) continue;
+        if (row >= S || row < first_row) continue;
+        float* drow = dst + base.at(row) * d + col0;
 #pragma unroll
         for (int np = 0; np < NCH / 2; ++np) {
 #pragma unroll
@@ -400,8 +424,8 @@ __device__ __forceinline__ void store_rows(float (&acc)[DK / 16][4], float mul, 
                     lo[0] = a0 * c.x + b0 * sn.x; lo[1] = a1 * c.y + b1 * sn.y;
                     hi[0] = b0 * c.x - a0 * sn.x; hi[1] = b1 * c.y - a1 * sn.y;
                 }
-                *reinterpret_cast<float2*>(dst + (base + row) * d + col0 + j) = make_float2(lo[0], lo[1]);
-                *reinterpret_cast<float2*>(dst + (base + row) * d + col0 + j + half) = make_float2(hi[0], hi[1]);
+                *reinterpret_cast<float2*>(drow + j) = make_float2(lo[0], lo[1]);
+                *reinterpret_cast<float2*>(drow + j + half) = make_float2(hi[0], hi[1]);
             }
         }
     }
@@ -413,9 +437,10 @@ template <int DK>
 __global__ void __launch_bounds__(256)
 attn_bwd_dkv_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v,
                     const bf16* __restrict__ dob, const float* __restrict__ lse, const float* __restrict__ delta,
-                    const float* __restrict__ rope_cos, const float* __restrict__ rope_sin, int S, int H, float scale,
-                    float* __restrict__ dk, float* __restrict__ dv)
+                    const float* __restrict__ rope_cos, const float* __restrict__ rope_sin, const SeqMap map, size_t rows, int H,
+                    float scale, float* __restrict__ dk, float* __restrict__ dv, float* __restrict__ part)
 {
+    const int S = map.S;
     constexpr int LD = DK + 8, LP = 64 + 8, NCH = DK / 32;
     extern __shared__ __align__(16) unsigned char smraw[];
     bf16* Ks = reinterpret_cast<bf16*>(smraw);
@@ -431,22 +456,26 @@ attn_bwd_dkv_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, cons
     const int k0 = blockIdx.y * 64;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2;
     const int wr = warp & 3, wc = warp >> 2;
-    const size_t base = (size_t)b * S;
+    const RowAddr base = row_addr(map, b);
     const int col0 = h * DK;
-    const size_t vec0 = ((size_t)b * H + h) * S;
+    // Grouped batch, key tile inside the shared prefix (P is a multiple of 64 then): every member adds the
+    // share of its own queries (the first member also that of the prefix queries) into its slice of `part`
+    // ((2, n_seq, P, d): dK then dV), which prefix_sum_kernel adds up afterwards.
+    const bool prefix_tile = map.group > 1 && k0 < map.P;
+    const int q_start = (prefix_tile && b % map.group != 0) ? map.P : k0;
 
     auto load_q = [&](int i0, int buf) {
         stage<DK, LD, 64, 256>(q, base, i0, S, d, col0, Qs + buf * 64 * LD);
         stage<DK, LD, 64, 256>(dob, base, i0, S, d, col0, Gs + buf * 64 * LD);
         if (threadIdx.x < 64) {
             const int qi = i0 + threadIdx.x;
-            Ls[buf * 64 + threadIdx.x] = qi < S ? lse[vec0 + qi] : 0.0f;
-            Dl[buf * 64 + threadIdx.x] = qi < S ? delta[vec0 + qi] : 0.0f;
+            Ls[buf * 64 + threadIdx.x] = qi < S ? lse[map_vec(map, b, h, qi, H, rows)] : 0.0f;
+            Dl[buf * 64 + threadIdx.x] = qi < S ? delta[map_vec(map, b, h, qi, H, rows)] : 0.0f;
         }
     };
     stage<DK, LD, 64, 256>(k, base, k0, S, d, col0, Ks);
     stage<DK, LD, 64, 256>(v, base, k0, S, d, col0, Vs);
-    load_q(k0, 0);
+    load_q(q_start, 0);
     cp_commit();
 
     float adk[DK / 16][4], adv[DK / 16][4];
@@ -455,9 +484,9 @@ attn_bwd_dkv_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, cons
 #pragma unroll
         for (int j = 0; j < 4; ++j) adk[i][j] = adv[i][j] = 0.0f;
 
-    const int n_it = (S - k0 + 63) / 64;
+    const int n_it = (S - q_start + 63) / 64;
     for (int it = 0; it < n_it; ++it) {
-        const int i0 = k0 + it * 64, buf = it & 1;
+        const int i0 = q_start + it * 64, buf = it & 1;
         if (it + 1 < n_it) {
             load_q(i0 + 64, buf ^ 1);
             cp_commit();
@@ -492,8 +521,33 @@ attn_bwd_dkv_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, cons
         __syncthreads();
     }
     const int row_a = k0 + wr * 16 + g;
-    store_rows<DK>(adk, scale, rope_cos, rope_sin, row_a, S, base, d, col0, wc, dk);
-    store_rows<DK>(adv, 1.0f, nullptr, nullptr, row_a, S, base, d, col0, wc, dv);
+    if (prefix_tile) {
+        RowAddr pa;
+        pa.P = map.P;
+        pa.pre_base = (size_t)b * map.P;
+        pa.own_base = 0;
+        const size_t plane = (size_t)gridDim.x / H * map.P * d;  // n_seq * P * d
+        store_rows<DK>(adk, scale, rope_cos, rope_sin, row_a, 0, S, pa, d, col0, wc, part);
+        store_rows<DK>(adv, 1.0f, nullptr, nullptr, row_a, 0, S, pa, d, col0, wc, part + plane);
+    } else {
+        store_rows<DK>(adk, scale, rope_cos, rope_sin, row_a, 0, S, base, d, col0, wc, dk);
+        store_rows<DK>(adv, 1.0f, nullptr, nullptr, row_a, 0, S, base, d, col0, wc, dv);
+    }
+}
+
+// prefix rows of a grouped batch: dst[row of (group, r)] = sum over the group's members of part[member][r]
+__global__ void prefix_sum_kernel(const float* __restrict__ part, const SeqMap map, int d, float* __restrict__ dst)
+{
+    const int grp = blockIdx.x / map.P, r = blockIdx.x % map.P;
+    const size_t drow = map_row(map, grp * map.group, r);
+    for (int c = threadIdx.x * 4; c < d; c += blockDim.x * 4) {
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int mm = 0; mm < map.group; ++mm) {
+            const float4 v = *reinterpret_cast<const float4*>(part + ((size_t)(grp * map.group + mm) * map.P + r) * d + c);
+            a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+        }
+        *reinterpret_cast<float4*>(dst + drow * d + c) = a;
+    }
 }
 
 // dQ: grid (n*H, ceil(S/64)) over query tiles (late tiles first), 256 threads.  Q and dO of the tile stay
@@ -502,9 +556,10 @@ template <int DK>
 __global__ void __launch_bounds__(256)
 attn_bwd_dq_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v,
                    const bf16* __restrict__ dob, const float* __restrict__ lse, const float* __restrict__ delta,
-                   const float* __restrict__ rope_cos, const float* __restrict__ rope_sin, int S, int H, float scale,
-                   float* __restrict__ dq)
+                   const float* __restrict__ rope_cos, const float* __restrict__ rope_sin, const SeqMap map, size_t rows, int H,
+                   float scale, float* __restrict__ dq)
 {
+    const int S = map.S;
     constexpr int LD = DK + 8, LP = 64 + 8, NCH = DK / 32;
     extern __shared__ __align__(16) unsigned char smraw[];
     bf16* Qs = reinterpret_cast<bf16*>(smraw);
@@ -517,11 +572,12 @@ attn_bwd_dq_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const
     const int bh = blockIdx.x, b = bh / H, h = bh % H;
     const int d = H * DK;
     const int i0 = (gridDim.y - 1 - blockIdx.y) * 64;
+    const int first_row = (map.group > 1 && b % map.group != 0) ? map.P : 0;  // prefix rows belong to the first member
+    if (i0 + 64 <= first_row) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2;
     const int wr = warp & 3, wc = warp >> 2;
-    const size_t base = (size_t)b * S;
+    const RowAddr base = row_addr(map, b);
     const int col0 = h * DK;
-    const size_t vec0 = ((size_t)b * H + h) * S;
 
     stage<DK, LD, 64, 256>(q, base, i0, S, d, col0, Qs);
     stage<DK, LD, 64, 256>(dob, base, i0, S, d, col0, Gs);
@@ -530,8 +586,8 @@ attn_bwd_dq_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const
     cp_commit();
     if (threadIdx.x < 64) {
         const int qi = i0 + threadIdx.x;
-        Ls[threadIdx.x] = qi < S ? lse[vec0 + qi] : 0.0f;
-        Dl[threadIdx.x] = qi < S ? delta[vec0 + qi] : 0.0f;
+        Ls[threadIdx.x] = qi < S ? lse[map_vec(map, b, h, qi, H, rows)] : 0.0f;
+        Dl[threadIdx.x] = qi < S ? delta[map_vec(map, b, h, qi, H, rows)] : 0.0f;
     }
     float acc[DK / 16][4];
 #pragma unroll
@@ -572,7 +628,7 @@ attn_bwd_dq_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const
         }
         __syncthreads();
     }
-    store_rows<DK>(acc, scale, rope_cos, rope_sin, i0 + wr * 16 + g, S, base, d, col0, wc, dq);
+    store_rows<DK>(acc, scale, rope_cos, rope_sin, i0 + wr * 16 + g, first_row, S, base, d, col0, wc, dq);
 }
 
 template <typename K>
@@ -587,20 +643,38 @@ static nnb_status set_smem(K kern, size_t smem)
 bool attn_b16_supported(size_t dk, size_t d) { return (dk == 64 || dk == 128) && d % 8 == 0; }
 
 nnb_status launch_rope_pack_b16(nnb_engine* e, const float* q, const float* k, const float* v, const float* rope_cos,
-                                const float* rope_sin, size_t T, size_t S, size_t H, size_t dk, __nv_bfloat16* out)
+                                const float* rope_sin, size_t T, size_t S, size_t H, size_t dk, __nv_bfloat16* out,
+                                const int* row_pos)
 {
     NNB_REQUIRE(dk % 8 == 0, "rope_pack: head dim %zu must be a multiple of 8", dk);
     NNB_REQUIRE((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15) == 0, "rope_pack: operands must be 16-byte aligned");
-    ab::rope_pack_kernel<<<(unsigned)T, 256, 0, e->stream>>>(q, k, v, rope_cos, rope_sin, (int)S, (int)H, (int)dk, T, out);
+    ab::rope_pack_kernel<<<(unsigned)T, 256, 0, e->stream>>>(q, k, v, rope_cos, rope_sin, row_pos, (int)S, (int)H, (int)dk, T, out);
     e->launches++;
     NNB_CHECK_LAUNCH("rope_pack_kernel");
     return NNB_OK;
 }
 
+static nnb_status check_map(const SeqMap* map, size_t n_seq, size_t S, SeqMap* out)
+{
+    if (!map) {
+        *out = SeqMap{(int)S, 0, (int)S, 1};
+        return NNB_OK;
+    }
+    *out = *map;
+    NNB_REQUIRE((size_t)map->S == S && map->P + map->G == map->S && map->group >= 1, "attention: inconsistent sequence map");
+    if (map->group > 1)
+        NNB_REQUIRE(map->P % 64 == 0 && n_seq % map->group == 0,
+                    "attention: a grouped batch needs a prompt length that is a multiple of 64 and whole groups");
+    return NNB_OK;
+}
+
 nnb_status launch_attn_fwd_b16(nnb_engine* e, const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v,
-                               size_t n_seq, size_t S, size_t H, size_t dk, float* out, float* lse)
+                               size_t n_seq, size_t S, size_t H, size_t dk, float* out, float* lse, const SeqMap* map)
 {
     using namespace ab;
+    SeqMap m;
+    NNB_TRY(check_map(map, n_seq, S, &m));
+    const size_t rows = map_rows_total(m, n_seq);
     const float scale = 1.0f / sqrtf((float)dk);
     dim3 grid((unsigned)(n_seq * H), (unsigned)ceil_div(S, 128));
     const size_t smem = (128 + 4 * 64) * (dk + 8) * 2;
@@ -610,24 +684,29 @@ nnb_status launch_attn_fwd_b16(nnb_engine* e, const __nv_bfloat16* q, const __nv
         NNB_TRY(set_smem(attn_fwd_kernel<64>, (128 + 4 * 64) * 72 * 2));
         cfg = true;
     }
-    if (dk == 128) attn_fwd_kernel<128><<<grid, 128, smem, e->stream>>>(q, k, v, (int)S, (int)H, scale, out, lse);
-    else attn_fwd_kernel<64><<<grid, 128, smem, e->stream>>>(q, k, v, (int)S, (int)H, scale, out, lse);
+    if (dk == 128) attn_fwd_kernel<128><<<grid, 128, smem, e->stream>>>(q, k, v, m, rows, (int)H, scale, out, lse);
+    else attn_fwd_kernel<64><<<grid, 128, smem, e->stream>>>(q, k, v, m, rows, (int)H, scale, out, lse);
     e->launches++;
     NNB_CHECK_LAUNCH("attn_fwd_kernel (bf16)");
     return NNB_OK;
 }
 
-// dob: bf16 scratch (n_seq*S, H*dk); delta: f32 scratch (n_seq, H, S).  With rope tables the gradients of q
-// and k are returned with respect to the un-rotated projections.
+// dob: bf16 scratch (rows, H*dk); delta: f32 scratch, one value per (row, head).  With rope tables the
+// gradients of q and k are returned with respect to the un-rotated projections.
 nnb_status launch_attn_bwd_b16(nnb_engine* e, const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v,
                                const float* out, const float* dout, const float* lse, float* delta, __nv_bfloat16* dob,
                                const float* rope_cos, const float* rope_sin, size_t n_seq, size_t S, size_t H, size_t dk,
-                               float* dq, float* dkk, float* dvv)
+                               float* dq, float* dkk, float* dvv, const SeqMap* map, float* part)
 {
     using namespace ab;
+    SeqMap m;
+    NNB_TRY(check_map(map, n_seq, S, &m));
+    const bool grouped = m.group > 1;
+    NNB_REQUIRE(!grouped || part, "attention backward: a grouped batch needs the prefix scratch");
+    const size_t rows = map_rows_total(m, n_seq);
     const float scale = 1.0f / sqrtf((float)dk);
-    const size_t rows = n_seq * S;
-    delta_pack_kernel<<<(unsigned)ceil_div(rows * H, 8), 256, 0, e->stream>>>(dout, out, (int)S, (int)H, (int)dk, rows, delta, dob);
+    delta_pack_kernel<<<(unsigned)ceil_div(rows * H, 8), 256, 0, e->stream>>>(dout, out, (int)S, (int)H, (int)dk, rows,
+                                                                             grouped ? 1 : 0, delta, dob);
     dim3 grid((unsigned)(n_seq * H), (unsigned)ceil_div(S, 64));
     const size_t smem_kv = 6 * 64 * (dk + 8) * 2 + 2 * 64 * 72 * 2 + 256 * 4;
     const size_t smem_q = 6 * 64 * (dk + 8) * 2 + 64 * 72 * 2 + 128 * 4;
@@ -640,17 +719,24 @@ nnb_status launch_attn_bwd_b16(nnb_engine* e, const __nv_bfloat16* q, const __nv
         cfg = true;
     }
     if (dk == 128) {
-        attn_bwd_dkv_kernel<128><<<grid, 256, smem_kv, e->stream>>>(q, k, v, dob, lse, delta, rope_cos, rope_sin, (int)S, (int)H,
-                                                                    scale, dkk, dvv);
-        attn_bwd_dq_kernel<128><<<grid, 256, smem_q, e->stream>>>(q, k, v, dob, lse, delta, rope_cos, rope_sin, (int)S, (int)H,
+        attn_bwd_dkv_kernel<128><<<grid, 256, smem_kv, e->stream>>>(q, k, v, dob, lse, delta, rope_cos, rope_sin, m, rows, (int)H,
+                                                                    scale, dkk, dvv, part);
+        attn_bwd_dq_kernel<128><<<grid, 256, smem_q, e->stream>>>(q, k, v, dob, lse, delta, rope_cos, rope_sin, m, rows, (int)H,
                                                                   scale, dq);
     } else {
-        attn_bwd_dkv_kernel<64><<<grid, 256, smem_kv, e->stream>>>(q, k, v, dob, lse, delta, rope_cos, rope_sin, (int)S, (int)H,
-                                                                   scale, dkk, dvv);
-        attn_bwd_dq_kernel<64><<<grid, 256, smem_q, e->stream>>>(q, k, v, dob, lse, delta, rope_cos, rope_sin, (int)S, (int)H,
+        attn_bwd_dkv_kernel<64><<<grid, 256, smem_kv, e->stream>>>(q, k, v, dob, lse, delta, rope_cos, rope_sin, m, rows, (int)H,
+                                                                   scale, dkk, dvv, part);
+        attn_bwd_dq_kernel<64><<<grid, 256, smem_q, e->stream>>>(q, k, v, dob, lse, delta, rope_cos, rope_sin, m, rows, (int)H,
                                                                  scale, dq);
     }
     e->launches += 3;
+    if (grouped) {
+        const size_t d = H * dk, plane = n_seq * (size_t)m.P * d;
+        const unsigned blocks = (unsigned)((n_seq / m.group) * m.P);
+        prefix_sum_kernel<<<blocks, 256, 0, e->stream>>>(part, m, (int)d, dkk);
+        prefix_sum_kernel<<<blocks, 256, 0, e->stream>>>(part + plane, m, (int)d, dvv);
+        e->launches += 2;
+    }
     NNB_CHECK_LAUNCH("attention backward kernels (bf16)");
     return NNB_OK;
 }

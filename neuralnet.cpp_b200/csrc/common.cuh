@@ -175,6 +175,38 @@ nnb_status launch_attn_bwd(nnb_engine* e, bool exact, const float* q, const floa
 nnb_status launch_rmsnorm_bwd(nnb_engine* e, const float* x, const float* gamma, const float* dy,
                               const float* residual, size_t T, size_t F, float* dx, float* dgamma);
 nnb_status launch_act_bwd(nnb_engine* e, int mode, const float* h, const float* da, size_t T, size_t F, float* dh);
+// Row layout of a micro-batch of n_seq sequences of S = P + G tokens.  group == 1: sequence b owns rows
+// [b*S, (b+1)*S).  group > 1: the `group` consecutive sequences of a prompt group share their first P
+// tokens, which are stored (and computed) once: a group owns P + group*G rows, its prefix first, then the
+// G generated rows of each member.  Position r of sequence b lives in row map_row(m, b, r).
+struct SeqMap {
+    int S, P, G, group;
+};
+__host__ __device__ inline size_t map_row(const SeqMap& m, int b, int r)
+{
+    if (m.group <= 1) return (size_t)b * m.S + r;
+    const int grp = b / m.group, mm = b % m.group;
+    const size_t base = (size_t)grp * ((size_t)m.P + (size_t)m.group * m.G);
+    return r < m.P ? base + r : base + m.P + (size_t)mm * m.G + (r - m.P);
+}
+inline size_t map_rows_total(const SeqMap& m, size_t n_seq)
+{
+    return m.group <= 1 ? n_seq * m.S : (n_seq / m.group) * ((size_t)m.P + (size_t)m.group * m.G);
+}
+// per-(sequence, head, position) vectors (lse, delta): (n_seq, H, S) when group == 1, (H, rows) by row otherwise
+__host__ __device__ inline size_t map_vec(const SeqMap& m, int b, int h, int r, int H, size_t rows)
+{
+    return m.group <= 1 ? ((size_t)b * H + h) * m.S + r : (size_t)h * rows + map_row(m, b, r);
+}
+
+nnb_status launch_build_rows(nnb_engine* e, const int32_t* tokens, const SeqMap& map, size_t n_seq, int32_t* row_tok,
+                             int32_t* row_pos);
+nnb_status launch_embed_rows_fwd(nnb_engine* e, const float* tok_emb, const float* pos_emb, const int32_t* row_tok,
+                                 const int32_t* row_pos, size_t n_rows, size_t d, size_t vocab, float* x);
+nnb_status launch_embed_rows_bwd(nnb_engine* e, const float* g, const int32_t* row_tok, const int32_t* row_pos, size_t n_rows,
+                                 size_t d, size_t vocab, float* g_tok, float* g_pos);
+nnb_status launch_gather_decisions_map(nnb_engine* e, const float* src, const SeqMap& map, size_t n_seq, size_t d, float* dst);
+nnb_status launch_scatter_decisions_map(nnb_engine* e, const float* src, const SeqMap& map, size_t n_seq, size_t d, float* dst);
 nnb_status launch_gather_decisions(nnb_engine* e, const float* src, size_t n_seq, size_t S, size_t P, size_t G,
                                    size_t d, float* dst);
 nnb_status launch_scatter_decisions(nnb_engine* e, const float* src, size_t n_seq, size_t S, size_t P, size_t G,
@@ -206,12 +238,15 @@ nnb_status launch_dequant_to_bf16(nnb_engine* e, const int8_t* q, const float* s
 // ---- attn_b16.cu (bf16 tensor-core attention of the teacher-forced pass, head dims 64 and 128)
 bool attn_b16_supported(size_t dk, size_t d);
 nnb_status launch_rope_pack_b16(nnb_engine* e, const float* q, const float* k, const float* v, const float* rope_cos,
-                                const float* rope_sin, size_t T, size_t S, size_t H, size_t dk, __nv_bfloat16* out);
+                                const float* rope_sin, size_t T, size_t S, size_t H, size_t dk, __nv_bfloat16* out,
+                                const int* row_pos = nullptr);
 nnb_status launch_attn_fwd_b16(nnb_engine* e, const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v,
-                               size_t n_seq, size_t S, size_t H, size_t dk, float* out, float* lse);
+                               size_t n_seq, size_t S, size_t H, size_t dk, float* out, float* lse, const SeqMap* map = nullptr);
+// with a grouped map, part (2 * n_seq * P * H*dk floats) receives every member's share of the prefix rows'
+// dK and dV before they are summed
 nnb_status launch_attn_bwd_b16(nnb_engine* e, const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v,
                                const float* out, const float* dout, const float* lse, float* delta, __nv_bfloat16* dob,
                                const float* rope_cos, const float* rope_sin, size_t n_seq, size_t S, size_t H, size_t dk,
-                               float* dq, float* dkk, float* dvv);
+                               float* dq, float* dkk, float* dvv, const SeqMap* map = nullptr, float* part = nullptr);
 
 }  // namespace nnb

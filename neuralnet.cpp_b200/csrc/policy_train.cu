@@ -25,6 +25,11 @@ struct LayerSave {
 
 struct TrainWs {
     size_t n_seq = 0, S = 0, P = 0;
+    // row layout of the micro-batch: with group > 1 the prompt rows of a group are stored and computed once
+    SeqMap map{0, 0, 0, 1};
+    size_t rows = 0;
+    int32_t *row_tok = nullptr, *row_pos = nullptr;  // token and position of every row
+    float* part = nullptr;                           // per-member share of the prefix rows' dK, dV (grouped backward)
     bool saved_layers = false;
     char* arena = nullptr;
     size_t arena_bytes = 0;
@@ -54,17 +59,29 @@ void policy_free_train(nnb_policy* p)
     p->train = nullptr;
 }
 
-static nnb_status ensure_train(nnb_policy* p, size_t n_seq, size_t S, size_t P, bool save_layers)
+static nnb_status ensure_train(nnb_policy* p, size_t n_seq, size_t S, size_t P, bool save_layers, size_t group)
 {
     TrainWs* w = (TrainWs*)p->train;
-    if (w && w->n_seq == n_seq && w->S == S && w->P == P && (w->saved_layers || !save_layers)) return NNB_OK;
+    {
+        // sharing the prompt rows needs the bf16 attention kernels (they take the row map) and whole 64-row
+        // key tiles inside the prompt; otherwise every sequence keeps its own copy, which is always valid
+        const nnb_gpt_config& c0 = p->cfg;
+        const bool can = !c0.exact && attn_b16_supported(c0.d_model / c0.n_head, c0.d_model) && P % 64 == 0 && group > 1 &&
+                         n_seq % group == 0;
+        if (!can) group = 1;
+    }
+    if (w && w->n_seq == n_seq && w->S == S && w->P == P && (size_t)w->map.group == group && (w->saved_layers || !save_layers))
+        return NNB_OK;
     NNB_CUDA(cudaStreamSynchronize(p->e->stream));
     policy_free_train(p);
     w = new TrainWs();
     p->train = w;
     const nnb_gpt_config& c = p->cfg;
     const size_t d = c.d_model, F = c.d_ff, F1 = c.act == 1 ? 2 * F : F, V = c.vocab, H = c.n_head;
-    const size_t T = n_seq * S, G = S - P, Td = n_seq * G;
+    const size_t G = S - P, Td = n_seq * G;
+    w->map = SeqMap{(int)S, (int)P, (int)G, (int)group};
+    w->rows = map_rows_total(w->map, n_seq);
+    const size_t T = w->rows;
     const size_t n_save = save_layers ? (size_t)c.n_layer : 1;
     // fast mode: attention runs on bf16 copies of q, k, v; those are what a layer keeps for its backward,
     // and the f32 projections become one buffer shared by all layers
@@ -105,6 +122,8 @@ static nnb_status ensure_train(nnb_policy* p, size_t n_seq, size_t S, size_t P, 
             for (int l = 1; l < c.n_layer; ++l) w->L[l] = w->L[0];
         w->x_last = (float*)take(T * d * 4);
         w->qsum = (int32_t*)take(T * 4);
+        w->row_tok = (int32_t*)take(T * 4);
+        w->row_pos = (int32_t*)take(T * 4);
         w->actions = (int32_t*)take(Td * 4);
         w->xd = (float*)take(Td * d * 4);
         w->hn = (float*)take(Td * d * 4);
@@ -134,6 +153,7 @@ static nnb_status ensure_train(nnb_policy* p, size_t n_seq, size_t S, size_t P, 
                 w->dyb = (__nv_bfloat16*)take(dyb_elems * 2);
                 w->xs = (__nv_bfloat16*)take(T * (F > d ? F : d) * 2);
                 if (w->b16_attn) w->dob = (__nv_bfloat16*)take(T * d * 2);
+                if (group > 1) w->part = (float*)take(2 * n_seq * P * d * 4);
             }
         }
         if (pass == 0) {
@@ -182,10 +202,13 @@ static nnb_status forward(nnb_policy* p, const int32_t* tokens, size_t n_seq, si
     const nnb_gpt_config& c = p->cfg;
     TrainWs* w = (TrainWs*)p->train;
     const size_t d = c.d_model, F = c.d_ff, F1 = c.act == 1 ? 2 * F : F, V = c.vocab, H = c.n_head, dk = d / H;
-    const size_t T = n_seq * S, G = S - P, Td = n_seq * G;
+    const size_t T = w->rows, G = S - P, Td = n_seq * G;
     const bool exact = c.exact != 0;
+    const bool grouped = w->map.group > 1;
     const float* PP = p->params;
-    NNB_TRY(launch_embed_fwd(e, PP + p->tok_emb, c.pos == 0 ? PP + p->pos_emb : nullptr, tokens, T, S, d, V, w->L[0].x_in));
+    NNB_TRY(launch_build_rows(e, tokens, w->map, n_seq, w->row_tok, w->row_pos));
+    NNB_TRY(launch_embed_rows_fwd(e, PP + p->tok_emb, c.pos == 0 ? PP + p->pos_emb : nullptr, w->row_tok, w->row_pos, T, d, V,
+                                  w->L[0].x_in));
     for (int l = 0; l < c.n_layer; ++l) {
         const LayerW& LW = p->layers[l];
         LayerSave& s = w->L[l];
@@ -196,8 +219,8 @@ static nnb_status forward(nnb_policy* p, const int32_t* tokens, size_t n_seq, si
         NNB_TRY(lin_fwd(p, LW.q, 3, s.q1, s.s1, w->qsum, T, nullptr, s.qkv, T * d));
         if (w->b16_attn) {
             NNB_TRY(launch_rope_pack_b16(e, s.qkv, s.qkv + T * d, s.qkv + 2 * T * d, c.pos == 1 ? p->rope_cos : nullptr,
-                                         c.pos == 1 ? p->rope_sin : nullptr, T, S, H, dk, s.qkvb));
-            NNB_TRY(launch_attn_fwd_b16(e, s.qkvb, s.qkvb + T * d, s.qkvb + 2 * T * d, n_seq, S, H, dk, s.att, s.lse));
+                                         c.pos == 1 ? p->rope_sin : nullptr, T, S, H, dk, s.qkvb, w->row_pos));
+            NNB_TRY(launch_attn_fwd_b16(e, s.qkvb, s.qkvb + T * d, s.qkvb + 2 * T * d, n_seq, S, H, dk, s.att, s.lse, &w->map));
         } else {
             if (c.pos == 1) {
                 NNB_TRY(launch_rope(e, s.qkv, p->rope_cos, p->rope_sin, T, S, H, dk, false));
@@ -214,7 +237,8 @@ static nnb_status forward(nnb_policy* p, const int32_t* tokens, size_t n_seq, si
     }
     const float* x_final = w->x_last;
     if (!w->saved_layers) x_final = (c.n_layer % 2 == 1) ? w->x_last : w->L[0].x_in;
-    NNB_TRY(launch_gather_decisions(e, x_final, n_seq, S, P, G, d, w->xd));
+    if (grouped) NNB_TRY(launch_gather_decisions_map(e, x_final, w->map, n_seq, d, w->xd));
+    else NNB_TRY(launch_gather_decisions(e, x_final, n_seq, S, P, G, d, w->xd));
     gather_actions_kernel<<<(unsigned)ceil_div(Td, 256), 256, 0, e->stream>>>(tokens, (int)S, (int)P, (int)G, Td, w->actions);
     e->launches++;
     NNB_TRY(launch_row_quant(e, 0, exact, w->xd, PP + p->lnf_g, Td, d, d, w->qh, w->sh, w->qsum, w->hn));
@@ -265,7 +289,8 @@ static nnb_status backward(nnb_policy* p, const int32_t* tokens, size_t n_seq, s
     const nnb_gpt_config& c = p->cfg;
     TrainWs* w = (TrainWs*)p->train;
     const size_t d = c.d_model, F = c.d_ff, V = c.vocab, H = c.n_head, dk = d / H;
-    const size_t T = n_seq * S, G = S - P, Td = n_seq * G;
+    const size_t T = w->rows, G = S - P, Td = n_seq * G;
+    const bool grouped = w->map.group > 1;
     const float* PP = p->params;
     float* GG = p->grads;
     // head: logits buffer now holds dlogits
@@ -273,7 +298,8 @@ static nnb_status backward(nnb_policy* p, const int32_t* tokens, size_t n_seq, s
     if (c.value_head)
         NNB_TRY(launch_value_bwd(e, w->hn, PP + p->value_w, w->dvalue, Td, d, w->dhn, GG + p->value_w, GG + p->value_b));
     NNB_TRY(launch_rmsnorm_bwd(e, w->xd, PP + p->lnf_g, w->dhn, nullptr, Td, d, w->xd, GG + p->lnf_g));
-    NNB_TRY(launch_scatter_decisions(e, w->xd, n_seq, S, P, G, d, w->g));
+    if (grouped) NNB_TRY(launch_scatter_decisions_map(e, w->xd, w->map, n_seq, d, w->g));
+    else NNB_TRY(launch_scatter_decisions(e, w->xd, n_seq, S, P, G, d, w->g));
     for (int l = c.n_layer - 1; l >= 0; --l) {
         const LayerW& LW = p->layers[l];
         LayerSave& s = w->L[l];
@@ -295,7 +321,7 @@ static nnb_status backward(nnb_policy* p, const int32_t* tokens, size_t n_seq, s
             // the inverse rotation of dq and dk is part of the kernels' epilogues
             NNB_TRY(launch_attn_bwd_b16(e, s.qkvb, s.qkvb + T * d, s.qkvb + 2 * T * d, s.att, w->datt, s.lse, w->delta, w->dob,
                                         c.pos == 1 ? p->rope_cos : nullptr, c.pos == 1 ? p->rope_sin : nullptr, n_seq, S, H, dk,
-                                        w->dqkv, w->dqkv + T * d, w->dqkv + 2 * T * d));
+                                        w->dqkv, w->dqkv + T * d, w->dqkv + 2 * T * d, &w->map, w->part));
         } else {
             NNB_TRY(launch_attn_bwd(e, c.exact != 0, s.qkv, s.qkv + T * d, s.qkv + 2 * T * d, s.att, w->datt, s.lse, w->delta, n_seq,
                                     S, H, dk, w->dqkv, w->dqkv + T * d, w->dqkv + 2 * T * d));
@@ -318,7 +344,7 @@ static nnb_status backward(nnb_policy* p, const int32_t* tokens, size_t n_seq, s
         }
         NNB_TRY(launch_rmsnorm_bwd(e, s.x_in, PP + LW.ln1_g, w->dn, w->g2, T, d, w->g, GG + LW.ln1_g));
     }
-    return launch_embed_bwd(e, w->g, tokens, T, S, d, V, GG + p->tok_emb, c.pos == 0 ? GG + p->pos_emb : nullptr);
+    return launch_embed_rows_bwd(e, w->g, w->row_tok, w->row_pos, T, d, V, GG + p->tok_emb, c.pos == 0 ? GG + p->pos_emb : nullptr);
 }
 
 static nnb_status check_shape(nnb_policy* p, const int32_t* tokens, size_t n_seq, size_t S, size_t P)
@@ -338,9 +364,16 @@ extern "C" {
 nnb_status nnb_policy_logprobs(nnb_policy* p, const int32_t* d_tokens, size_t n_seq, size_t seq_len, size_t prompt_len,
                                float* d_logp, float* d_entropy, float* d_value)
 {
+    return nnb_policy_logprobs_grouped(p, d_tokens, n_seq, seq_len, prompt_len, 1, d_logp, d_entropy, d_value);
+}
+
+nnb_status nnb_policy_logprobs_grouped(nnb_policy* p, const int32_t* d_tokens, size_t n_seq, size_t seq_len, size_t prompt_len,
+                                       size_t group, float* d_logp, float* d_entropy, float* d_value)
+{
     NNB_TRY(check_shape(p, d_tokens, n_seq, seq_len, prompt_len));
     NNB_REQUIRE(d_value == nullptr || p->cfg.value_head, "policy has no value head");
-    NNB_TRY(ensure_train(p, n_seq, seq_len, prompt_len, false));
+    NNB_REQUIRE(group >= 1 && n_seq % group == 0, "logprobs: %zu sequences are not whole groups of %zu", n_seq, group);
+    NNB_TRY(ensure_train(p, n_seq, seq_len, prompt_len, false, group));
     NNB_TRY(forward(p, d_tokens, n_seq, seq_len, prompt_len, d_entropy != nullptr));
     TrainWs* w = (TrainWs*)p->train;
     const size_t Td = n_seq * (seq_len - prompt_len);
@@ -375,13 +408,20 @@ nnb_status nnb_policy_zero_grad(nnb_policy* p)
 nnb_status nnb_policy_train_step(nnb_policy* p, const int32_t* d_tokens, size_t n_seq, size_t seq_len,
                                  size_t prompt_len, const nnb_objective* obj, float* d_report)
 {
+    return nnb_policy_train_step_grouped(p, d_tokens, n_seq, seq_len, prompt_len, 1, obj, d_report);
+}
+
+nnb_status nnb_policy_train_step_grouped(nnb_policy* p, const int32_t* d_tokens, size_t n_seq, size_t seq_len,
+                                         size_t prompt_len, size_t group, const nnb_objective* obj, float* d_report)
+{
     NNB_TRY(check_shape(p, d_tokens, n_seq, seq_len, prompt_len));
+    NNB_REQUIRE(group >= 1 && n_seq % group == 0, "train_step: %zu sequences are not whole groups of %zu", n_seq, group);
     NNB_REQUIRE(obj && obj->d_mask, "train_step: objective or mask is NULL");
     NNB_REQUIRE(nnb_policy_grads(p), "out of device memory for the gradient buffer");
     const bool use_value = obj->value_coef != 0.0f;
     NNB_REQUIRE(!use_value || (p->cfg.value_head && obj->d_returns && obj->d_old_value),
                 "train_step: the value term needs a value head, returns and old values");
-    NNB_TRY(ensure_train(p, n_seq, seq_len, prompt_len, true));
+    NNB_TRY(ensure_train(p, n_seq, seq_len, prompt_len, true, group));
     NNB_TRY(policy_ensure_wb(p));
     nnb_engine* e = p->e;
     TrainWs* w = (TrainWs*)p->train;

@@ -45,6 +45,49 @@ __global__ void embed_bwd_kernel(const float* __restrict__ g, const int32_t* __r
     }
 }
 
+// The same two kernels for an explicit row table (token and position of every row), which is how the
+// teacher-forced pass lays out its micro-batch (see SeqMap): one thread per (sequence, position) fills the table.
+__global__ void build_rows_kernel(const int32_t* __restrict__ tokens, const SeqMap map, size_t n, int32_t* __restrict__ row_tok,
+                                  int32_t* __restrict__ row_pos)
+{
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n) return;
+    const int b = (int)(idx / map.S), r = (int)(idx % map.S);
+    if (map.group > 1 && r < map.P && b % map.group != 0) return;  // the prompt rows belong to the first member
+    const size_t row = map_row(map, b, r);
+    row_tok[row] = tokens[idx];
+    row_pos[row] = r;
+}
+
+__global__ void embed_rows_fwd_kernel(const float* __restrict__ tok_emb, const float* __restrict__ pos_emb,
+                                      const int32_t* __restrict__ row_tok, const int32_t* __restrict__ row_pos, int d, int vocab,
+                                      float* __restrict__ x)
+{
+    const size_t row = blockIdx.x;
+    const int tok = min(max(row_tok[row], 0), vocab - 1);
+    const float* e = tok_emb + (size_t)tok * d;
+    const float* p = pos_emb ? pos_emb + (size_t)row_pos[row] * d : nullptr;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        float v = e[i];
+        if (p) v = __fadd_rn(v, p[i]);
+        x[row * d + i] = v;
+    }
+}
+
+__global__ void embed_rows_bwd_kernel(const float* __restrict__ g, const int32_t* __restrict__ row_tok,
+                                      const int32_t* __restrict__ row_pos, int d, int vocab, float* __restrict__ g_tok,
+                                      float* __restrict__ g_pos)
+{
+    const size_t row = blockIdx.x;
+    const int tok = min(max(row_tok[row], 0), vocab - 1);
+    const int t = row_pos[row];
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float v = g[row * d + i];
+        atomicAdd(g_tok + (size_t)tok * d + i, v);
+        if (g_pos) atomicAdd(g_pos + (size_t)t * d + i, v);
+    }
+}
+
 // ------------------------------------------------------------------ RoPE
 // In place on x (rows, d) viewed as heads of dk; position of a row = row % S.
 // sign = +1 forward, -1 backward (the rotation is orthogonal: inverse = opposite angle).
@@ -541,6 +584,37 @@ __global__ void scatter_decisions_kernel(const float* __restrict__ src, int S, i
         dst[row * d + c] = hit ? src[(b * G + g) * d + c] : 0.0f;
 }
 
+// grouped layout: decision (b, g) reads the row of position P-1+g of sequence b (g = 0: the shared last
+// prompt row of b's group)
+__global__ void gather_decisions_map_kernel(const float* __restrict__ src, const SeqMap map, int d, float* __restrict__ dst)
+{
+    const size_t i = blockIdx.x;
+    const int b = (int)(i / map.G), g = (int)(i % map.G);
+    const size_t row = map_row(map, b, map.P - 1 + g);
+    for (int c = threadIdx.x; c < d; c += blockDim.x) dst[i * d + c] = src[row * d + c];
+}
+
+// grouped layout, one CTA per destination row: own rows take their decision's gradient, the last prompt row of
+// a group takes the sum of its members' first decisions (in member order), every other row is zero
+__global__ void scatter_decisions_map_kernel(const float* __restrict__ src, const SeqMap map, int d, float* __restrict__ dst)
+{
+    const size_t row = blockIdx.x;
+    const size_t rpg = (size_t)map.P + (size_t)map.group * map.G;
+    const int grp = (int)(row / rpg);
+    const int o = (int)(row % rpg);
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+        float v = 0.0f;
+        if (o < map.P) {
+            if (o == map.P - 1)
+                for (int mm = 0; mm < map.group; ++mm) v += src[((size_t)(grp * map.group + mm) * map.G) * d + c];
+        } else {
+            const int mm = (o - map.P) / map.G, g = (o - map.P) % map.G + 1;
+            if (g < map.G) v = src[((size_t)(grp * map.group + mm) * map.G + g) * d + c];
+        }
+        dst[row * d + c] = v;
+    }
+}
+
 // value head: value[i] = w . x[i,:] + b   (Linear(d -> 1) on the final-norm output)
 __global__ void value_fwd_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b,
                                  size_t n, int d, float* __restrict__ value)
@@ -596,6 +670,50 @@ nnb_status launch_embed_bwd(nnb_engine* e, const float* g, const int32_t* tokens
     embed_bwd_kernel<<<(unsigned)n_rows, 128, 0, e->stream>>>(g, tokens, (int)S, (int)d, (int)vocab, g_tok, g_pos);
     e->launches++;
     NNB_CHECK_LAUNCH("embed_bwd_kernel");
+    return NNB_OK;
+}
+
+nnb_status launch_build_rows(nnb_engine* e, const int32_t* tokens, const SeqMap& map, size_t n_seq, int32_t* row_tok,
+                             int32_t* row_pos)
+{
+    const size_t n = n_seq * map.S;
+    build_rows_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, e->stream>>>(tokens, map, n, row_tok, row_pos);
+    e->launches++;
+    NNB_CHECK_LAUNCH("build_rows_kernel");
+    return NNB_OK;
+}
+
+nnb_status launch_embed_rows_fwd(nnb_engine* e, const float* tok_emb, const float* pos_emb, const int32_t* row_tok,
+                                 const int32_t* row_pos, size_t n_rows, size_t d, size_t vocab, float* x)
+{
+    embed_rows_fwd_kernel<<<(unsigned)n_rows, 128, 0, e->stream>>>(tok_emb, pos_emb, row_tok, row_pos, (int)d, (int)vocab, x);
+    e->launches++;
+    NNB_CHECK_LAUNCH("embed_rows_fwd_kernel");
+    return NNB_OK;
+}
+
+nnb_status launch_embed_rows_bwd(nnb_engine* e, const float* g, const int32_t* row_tok, const int32_t* row_pos, size_t n_rows,
+                                 size_t d, size_t vocab, float* g_tok, float* g_pos)
+{
+    embed_rows_bwd_kernel<<<(unsigned)n_rows, 128, 0, e->stream>>>(g, row_tok, row_pos, (int)d, (int)vocab, g_tok, g_pos);
+    e->launches++;
+    NNB_CHECK_LAUNCH("embed_rows_bwd_kernel");
+    return NNB_OK;
+}
+
+nnb_status launch_gather_decisions_map(nnb_engine* e, const float* src, const SeqMap& map, size_t n_seq, size_t d, float* dst)
+{
+    gather_decisions_map_kernel<<<(unsigned)(n_seq * map.G), 128, 0, e->stream>>>(src, map, (int)d, dst);
+    e->launches++;
+    NNB_CHECK_LAUNCH("gather_decisions_map_kernel");
+    return NNB_OK;
+}
+
+nnb_status launch_scatter_decisions_map(nnb_engine* e, const float* src, const SeqMap& map, size_t n_seq, size_t d, float* dst)
+{
+    scatter_decisions_map_kernel<<<(unsigned)map_rows_total(map, n_seq), 128, 0, e->stream>>>(src, map, (int)d, dst);
+    e->launches++;
+    NNB_CHECK_LAUNCH("scatter_decisions_map_kernel");
     return NNB_OK;
 }
 

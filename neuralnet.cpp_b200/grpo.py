@@ -102,9 +102,11 @@ class GrpoTrainer:
         units_global = float(self._allreduce(units).item()) if self.world > 1 else float(N * c.max_new)
         ev("advantage")
         mb = c.micro_batch
+        # micro-batches made of whole groups let the engine compute a group's shared prompt once
+        gs = c.group_size if mb % c.group_size == 0 else 1
         ref_lp = None
         if self.ref is not None and c.kl_coef != 0.0:
-            parts = [self.ref.logprobs(tokens[a:a + mb].contiguous(), c.prompt_len)[0] for a in range(0, N, mb)]
+            parts = [self.ref.logprobs(tokens[a:a + mb].contiguous(), c.prompt_len, group_size=gs)[0] for a in range(0, N, mb)]
             ref_lp = torch.cat(parts)
         ev("reference")
         pol.zero_grad()
@@ -115,7 +117,7 @@ class GrpoTrainer:
                                      old_logp=old_lp[sl].contiguous(), advantage=adv[sl].contiguous(),
                                      ref_logp=None if ref_lp is None else ref_lp[sl].contiguous(),
                                      units=units_global, clip_eps=c.clip_eps, kl_coef=c.kl_coef,
-                                     entropy_coef=c.entropy_coef)
+                                     entropy_coef=c.entropy_coef, group_size=gs)
         report[7] = units_global  # every micro-batch reports the global count: it is not a sum
         ev("train")
         if self.world > 1:

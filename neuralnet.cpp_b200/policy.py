@@ -198,15 +198,17 @@ def _dp(t):
     return None if t is None else t.data_ptr()
 
 
-def logprobs(self, tokens: torch.Tensor, prompt_len: int, want_entropy=False, want_value=False):
-    """Teacher-forced log-probs (and entropy / values) of the decisions of tokens (n, S) int32."""
+def logprobs(self, tokens: torch.Tensor, prompt_len: int, want_entropy=False, want_value=False, group_size=1):
+    """Teacher-forced log-probs (and entropy / values) of the decisions of tokens (n, S) int32.  group_size > 1:
+    every group_size consecutive sequences share their prompt, which is then computed once per group."""
     n, S = tokens.shape
     G = S - prompt_len
     dev = self.engine.device
     logp = torch.empty((n, G), device=dev, dtype=torch.float32)
     ent = torch.empty((n, G), device=dev, dtype=torch.float32) if want_entropy else None
     val = torch.empty((n, G), device=dev, dtype=torch.float32) if want_value else None
-    check(self._lib.nnb_policy_logprobs(self._h, _ptr(tokens), n, S, prompt_len, _ptr(logp), _ptr(ent), _ptr(val)))
+    check(self._lib.nnb_policy_logprobs_grouped(self._h, _ptr(tokens), n, S, prompt_len, group_size, _ptr(logp), _ptr(ent),
+                                                _ptr(val)))
     return logp, ent, val
 
 
@@ -223,13 +225,15 @@ def zero_grad(self):
 
 def train_step(self, tokens: torch.Tensor, prompt_len: int, mask, old_logp=None, advantage=None, ref_logp=None,
                returns=None, old_value=None, units=0.0, clip_eps=0.2, kl_coef=0.0, entropy_coef=0.0,
-               value_coef=0.0, value_clip_eps=0.2):
-    """One micro-batch: forward, objective, backward; gradients accumulate.  Returns report[10] (device)."""
+               value_coef=0.0, value_clip_eps=0.2, group_size=1):
+    """One micro-batch: forward, objective, backward; gradients accumulate.  Returns report[10] (device).
+    group_size > 1: every group_size consecutive sequences share their prompt (computed once per group)."""
     n, S = tokens.shape
     obj = _CObjective(_dp(mask), _dp(old_logp), _dp(advantage), _dp(ref_logp), _dp(returns), _dp(old_value),
                       units, clip_eps, kl_coef, entropy_coef, value_coef, value_clip_eps)
     report = torch.empty(10, device=self.engine.device, dtype=torch.float32)
-    check(self._lib.nnb_policy_train_step(self._h, _ptr(tokens), n, S, prompt_len, C.byref(obj), _ptr(report)))
+    check(self._lib.nnb_policy_train_step_grouped(self._h, _ptr(tokens), n, S, prompt_len, group_size, C.byref(obj),
+                                                  _ptr(report)))
     return report
 
 

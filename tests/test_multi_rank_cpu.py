@@ -39,7 +39,7 @@ class StubPolicy:
         gen = (torch.arange(n)[:, None] + seq0 + torch.arange(max_new)[None, :]).to(torch.int32) % 7
         return torch.cat([prompts, gen], 1), torch.full((n, max_new), -1.0), None
 
-    def logprobs(self, tokens, prompt_len):
+    def logprobs(self, tokens, prompt_len, group_size=1):
         return torch.full((tokens.shape[0], tokens.shape[1] - prompt_len), -1.1), None, None
 
     def zero_grad(self):

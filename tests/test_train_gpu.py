@@ -236,3 +236,46 @@ def test_fast_mode_gradients_are_close(pkg, eng, d, heads, S):
         a, b = ge[off:off + size].astype(np.float64), gf[off:off + size].astype(np.float64)
         rms = np.sqrt(((a - b) ** 2).mean()) / max(np.sqrt((a ** 2).mean()), 1e-12)
         assert rms <= 0.2, f"{name}: rms relative difference {rms:.3f}"
+
+
+@pytest.mark.parametrize("d,heads,P,G,group,n_grp", [(128, 2, 64, 40, 4, 2), (256, 2, 128, 70, 3, 1), (128, 1, 64, 64, 2, 3)])
+def test_grouped_batch_matches_one_copy_per_sequence(pkg, eng, d, heads, P, G, group, n_grp):
+    """Sequences of a group share their prompt: computing the prompt rows once per group gives the log-probs of
+    the plain call bit for bit (every row sees the same keys in the same order) and the same gradients up to the
+    order of summation (the prompt rows' contributions are added before the weight-gradient GEMMs instead of
+    inside them)."""
+    S = P + G
+    kw = dict(n_layer=2, d_model=d, n_head=heads, d_ff=2 * d, vocab=536, ctx=S, act=1, pos=1)
+    cfg = pkg.GptConfig(exact=False, **kw)
+    flat = cfg.init_params(5, bias_std=0.01)
+    pa, pb = pkg.Policy(eng, cfg), pkg.Policy(eng, cfg)
+    pa.upload_params(flat)
+    pb.upload_params(flat)
+    rng = np.random.default_rng(P + G + group)
+    n = n_grp * group
+    prompts = np.repeat(rng.integers(0, 536, (n_grp, P)), group, axis=0)
+    tokens = dev(np.concatenate([prompts, rng.integers(0, 536, (n, G))], 1), eng, np.int32)
+    lp_a, ent_a, _ = pa.logprobs(tokens, P, want_entropy=True)
+    lp_b, ent_b, _ = pb.logprobs(tokens, P, want_entropy=True, group_size=group)
+    assert torch.equal(lp_a, lp_b) and torch.equal(ent_a, ent_b)
+    old = lp_a + dev(rng.normal(0, 0.2, (n, G)), eng)
+    adv = dev(rng.normal(0, 1, (n, G)), eng)
+    mask = dev((rng.random((n, G)) < 0.9).astype(np.float32), eng)
+    pa.zero_grad()
+    pb.zero_grad()
+    ra = pa.train_step(tokens, P, mask, old_logp=old, advantage=adv, ref_logp=lp_a, kl_coef=0.05)
+    rb = pb.train_step(tokens, P, mask, old_logp=old, advantage=adv, ref_logp=lp_a, kl_coef=0.05, group_size=group)
+    eng.check_device_errors()
+    assert torch.allclose(ra, rb, rtol=1e-5, atol=1e-7)
+    ga, gb = pa.grads_view().cpu().numpy().astype(np.float64), pb.grads_view().cpu().numpy().astype(np.float64)
+    layout, _ = cfg.param_layout()
+    for name, off, shape in layout:
+        size = int(np.prod(shape))
+        a, b = ga[off:off + size], gb[off:off + size]
+        # bf16 operands: the grouped pass rounds the sum of a prompt row's gradients once, the plain pass rounds
+        # each copy's
+        assert np.abs(a - b).max() <= 2e-2 * max(np.abs(a).max(), 1e-9), f"{name}: {np.abs(a - b).max()} vs {np.abs(a).max()}"
+    # a prompt length that is not a multiple of 64 falls back to one copy per sequence: same results as the plain call
+    if P == 64:
+        t2 = tokens[:, 3:].contiguous()
+        assert torch.equal(pa.logprobs(t2, P - 3)[0], pb.logprobs(t2, P - 3, group_size=group)[0])
