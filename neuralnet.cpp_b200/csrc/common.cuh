@@ -66,6 +66,10 @@ struct nnb_engine {
     // counts kernel launches issued through this engine (reported by the benchmark)
     unsigned long long launches = 0;
     int* dev_flags = nullptr;  // small device block: [0] error flag raised by bounded device-side waits
+    // While set, launch_ex marks its launches for programmatic dependent launch: the next kernel may become
+    // resident and run its prologue while this one drains.  Only kernels that call pdl_wait() before their
+    // first global-memory access go through launch_ex.
+    bool pdl = false;
     std::string describe_text;
 
     nnb_status ensure_scratch(size_t bytes);
@@ -73,6 +77,26 @@ struct nnb_engine {
 };
 
 namespace nnb {
+
+// Launch on the engine's stream; with e->pdl the launch carries the programmatic-stream-serialization
+// attribute (it is recorded as a programmatic edge when the stream is being captured into a graph).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_ex(nnb_engine* e, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, Args&&... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = e->stream;
+    cudaLaunchAttribute attr[1];
+    if (e->pdl) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
 
 // ---- ternary.cu: launchers (all enqueue on e->stream)
 nnb_status launch_absmean_tau(nnb_engine* e, const float* latent, size_t rows, size_t k, float* tau);

@@ -26,6 +26,8 @@ __global__ void embed_kernel(const float* __restrict__ tok_emb, const float* __r
                              const int* __restrict__ d_pos, int d, int vocab, float* __restrict__ x)
 {
     const int b = blockIdx.x;
+    pdl_launch();
+    pdl_wait();
     const int pos = *d_pos;
     int tok = tokens[(size_t)b * tokens_stride + pos];
     tok = min(max(tok, 0), vocab - 1);
@@ -160,6 +162,8 @@ row_quant_fast_kernel(const float* __restrict__ in, const float* __restrict__ ga
     float4* f4 = f_out ? reinterpret_cast<float4*>(f_out + tok * (size_t)k) : nullptr;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int nv = k >> 2;
+    pdl_launch();
+    pdl_wait();
 
     float sinv = 0.0f;
     if (MODE == 0) {
@@ -256,7 +260,8 @@ static nnb_status launch_row_quant_mode(nnb_engine* e, bool exact, const float* 
     if (exact)
         row_quant_kernel<MODE, true><<<(unsigned)t, 256, smem, e->stream>>>(in, gamma, (int)k, (int)in_stride, q, s, qsum, f_out);
     else if (aligned)
-        row_quant_fast_kernel<MODE><<<(unsigned)t, 256, smem, e->stream>>>(in, gamma, (int)k, (int)in_stride, q, s, qsum, f_out);
+        launch_ex(e, row_quant_fast_kernel<MODE>, dim3((unsigned)t), dim3(256), smem, in, gamma, (int)k, (int)in_stride, q, s, qsum,
+                  f_out);
     else
         row_quant_kernel<MODE, false><<<(unsigned)t, 256, smem, e->stream>>>(in, gamma, (int)k, (int)in_stride, q, s, qsum, f_out);
     e->launches++;
@@ -645,6 +650,8 @@ attn_decode_fused_kernel(const float* __restrict__ qkv, __nv_bfloat16* __restric
 
     const int b = blockIdx.x, h = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int d = H * DK;
+    pdl_launch();
+    pdl_wait();
     const int pos = *d_pos;
     float* sc = sc_all + (size_t)h * ctx_pad;
     const size_t head_off = ((size_t)b * H + h) * (size_t)own_alloc * DK;
@@ -843,10 +850,9 @@ nnb_status launch_attn_decode_fused(nnb_engine* e, const float* qkv, void* kcach
             NNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                 \
             cfg = smem;                                                                                                   \
         }                                                                                                                 \
-        kern<<<(unsigned)B, (unsigned)(32 * H), smem, e->stream>>>(                                                       \
-            qkv, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, (int)own_alloc, (const __nv_bfloat16*)kpre,              \
-            (const __nv_bfloat16*)vpre, (int)pre_len, (int)pre_alloc, (int)group, rope_cos, rope_sin, d_pos, (int)B, (int)H, \
-            (int)ctx_pad, scale, att, q8, s, qsum);                                                                       \
+        launch_ex(e, kern, dim3((unsigned)B), dim3((unsigned)(32 * H)), smem, qkv, (__nv_bfloat16*)kcache,                \
+                  (__nv_bfloat16*)vcache, (int)own_alloc, (const __nv_bfloat16*)kpre, (const __nv_bfloat16*)vpre, (int)pre_len, \
+                  (int)pre_alloc, (int)group, rope_cos, rope_sin, d_pos, (int)B, (int)H, (int)ctx_pad, scale, att, q8, s, qsum); \
     }
     if (dk == 128) NNB_FUSED(128) else NNB_FUSED(64)
 #undef NNB_FUSED
@@ -909,49 +915,95 @@ __device__ __forceinline__ uint32_t float_key(float v)
     return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
-// One CTA (256 threads) per sequence.  logits (B, V) f32.  Writes the chosen token at
+// One CTA (1024 threads) per sequence.  logits (B, V) f32.  Writes the chosen token at
 // tokens[b, pos+1], and log softmax(raw logits)[token] into logp[b, gen_index] where
 // gen_index = pos + 1 - prompt_len.
+// The row is read from global memory once and kept in shared memory.  Top-k: radix select of the k-th largest
+// key (8 bits per pass, one histogram per warp so that only lanes of a warp contend), an ordered compaction by
+// a block-wide scan, then the candidates' softmax: exponentials and quotients in parallel, the two running
+// sums in ascending index order by one thread, which is the order the reference's sampler adds them in.
+constexpr int SAMPLE_NT = 1024, SAMPLE_NW = SAMPLE_NT / 32;
+
+__device__ __forceinline__ void block_scan2(int& a, int& b, int* wa, int* wb, int& tot_a, int& tot_b)
+{
+    // exclusive scan of (a, b) over the block's threads; wa/wb: SAMPLE_NW ints each
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int ia = a, ib = b;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int ta = __shfl_up_sync(0xffffffffu, ia, o), tb = __shfl_up_sync(0xffffffffu, ib, o);
+        if (lane >= o) { ia += ta; ib += tb; }
+    }
+    if (lane == 31) { wa[warp] = ia; wb[warp] = ib; }
+    __syncthreads();
+    if (warp == 0) {
+        int va = wa[lane], vb = wb[lane];
+        int sa = va, sb = vb;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int ta = __shfl_up_sync(0xffffffffu, sa, o), tb = __shfl_up_sync(0xffffffffu, sb, o);
+            if (lane >= o) { sa += ta; sb += tb; }
+        }
+        wa[lane] = sa - va;  // exclusive prefix of the warp totals
+        wb[lane] = sb - vb;
+        if (lane == 31) { wa[SAMPLE_NW] = sa; wb[SAMPLE_NW] = sb; }
+    }
+    __syncthreads();
+    tot_a = wa[SAMPLE_NW];
+    tot_b = wb[SAMPLE_NW];
+    a = wa[warp] + ia - a;
+    b = wb[warp] + ib - b;
+}
+
 template <bool EXACT>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(SAMPLE_NT)
 sample_kernel(const float* __restrict__ logits, int V, float temperature, int top_k,
               unsigned long long seed, unsigned seq0, const int* __restrict__ d_pos, int prompt_len,
               int32_t* __restrict__ tokens, int tokens_stride, float* __restrict__ logp, int logp_stride,
               float* __restrict__ entropy)
 {
     typedef typename AccT<EXACT>::type acc_t;
+    constexpr int NT = SAMPLE_NT, NW = SAMPLE_NW;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    float* lg = reinterpret_cast<float*>(smem_raw);  // V scaled logits
-    int* cand = reinterpret_cast<int*>(lg + ((V + 3) & ~3));  // up to 1024 candidates
+    float* lg = reinterpret_cast<float*>(smem_raw);            // V (raw, then scaled) logits
+    int* cand = reinterpret_cast<int*>(lg + ((V + 3) & ~3));   // up to 1024 candidates
+    float* cval = reinterpret_cast<float*>(cand + 1024);       // their exponentials, then probabilities
+    int* whist = reinterpret_cast<int*>(cval + 1024);          // NW x 256 per-warp histograms
     __shared__ int hist[256];
-    __shared__ int scan_a[256], scan_b[256];
-    __shared__ float red_f[8];
-    __shared__ int red_i[8];
-    __shared__ acc_t red_a[8];
+    __shared__ int scan_a[NW + 1], scan_b[NW + 1];
+    __shared__ float red_f[NW];
+    __shared__ int red_i[NW];
+    __shared__ acc_t red_a[NW];
     __shared__ uint32_t sh_prefix;
     __shared__ int sh_need, sh_tok;
 
     const int b = blockIdx.x;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    pdl_launch();
+    pdl_wait();
     const int pos = *d_pos;
     const int gen = pos + 1 - prompt_len;
     const float* row = logits + (size_t)b * V;
 
     // raw max and log-sum-exp (for the recorded log-prob)
     float mx = -INFINITY;
-    for (int i = tid; i < V; i += 256) mx = fmaxf(mx, row[i]);
+    for (int i = tid; i < V; i += NT) {
+        const float v = row[i];
+        lg[i] = v;
+        mx = fmaxf(mx, v);
+    }
     mx = warp_max(mx);
     if (lane == 0) red_f[warp] = mx;
     __syncthreads();
     mx = red_f[0];
 #pragma unroll
-    for (int w = 1; w < 8; ++w) mx = fmaxf(mx, red_f[w]);
+    for (int w = 1; w < NW; ++w) mx = fmaxf(mx, red_f[w]);
     acc_t se = 0, sxe = 0;
-    for (int i = tid; i < V; i += 256) {
-        const float dlt = row[i] - mx;
-        const float ev = expf(dlt);
+    for (int i = tid; i < V; i += NT) {
+        const float dlt = lg[i] - mx;
+        const float ev = EXACT ? expf(dlt) : __expf(dlt);
         se += (acc_t)ev;
-        sxe += (acc_t)ev * (acc_t)dlt;
+        if (entropy) sxe += (acc_t)ev * (acc_t)dlt;
     }
     se = warp_sum_t(se);
     sxe = warp_sum_t(sxe);
@@ -960,25 +1012,26 @@ sample_kernel(const float* __restrict__ logits, int V, float temperature, int to
     __syncthreads();
     acc_t se_tot = 0;
 #pragma unroll
-    for (int w = 0; w < 8; ++w) se_tot += red_a[w];
+    for (int w = 0; w < NW; ++w) se_tot += red_a[w];
     __syncthreads();
     if (lane == 0) red_a[warp] = sxe;
     __syncthreads();
     acc_t sxe_tot = 0;
 #pragma unroll
-    for (int w = 0; w < 8; ++w) sxe_tot += red_a[w];
+    for (int w = 0; w < NW; ++w) sxe_tot += red_a[w];
     const float lse = logf((float)se_tot);  // log sum exp(x - mx)
     __syncthreads();
 
     const bool scale_t = temperature > 0.0f && temperature != 1.0f;
-    for (int i = tid; i < V; i += 256) lg[i] = scale_t ? __fdiv_rn(row[i], temperature) : row[i];
+    if (scale_t)
+        for (int i = tid; i < V; i += NT) lg[i] = __fdiv_rn(lg[i], temperature);
     __syncthreads();
 
     if (!(temperature > 0.0f)) {
         // greedy: largest value, ties to the smallest index
         float bv = -INFINITY;
         int bi = 0x7fffffff;
-        for (int i = tid; i < V; i += 256) {
+        for (int i = tid; i < V; i += NT) {
             const float v = lg[i];
             if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
         }
@@ -990,7 +1043,7 @@ sample_kernel(const float* __restrict__ logits, int V, float temperature, int to
         if (lane == 0) { red_f[warp] = bv; red_i[warp] = bi; }
         __syncthreads();
         if (tid == 0) {
-            for (int w = 1; w < 8; ++w)
+            for (int w = 1; w < NW; ++w)
                 if (red_f[w] > bv || (red_f[w] == bv && red_i[w] < bi)) { bv = red_f[w]; bi = red_i[w]; }
             sh_tok = bi;
         }
@@ -1000,15 +1053,29 @@ sample_kernel(const float* __restrict__ logits, int V, float temperature, int to
         if (top_k > 0 && top_k < V) {
             // radix select of the top_k-th largest key, 8 bits per pass
             if (tid == 0) { sh_prefix = 0u; sh_need = top_k; }
-            __syncthreads();
+            int* myhist = whist + warp * 256;
             for (int pass = 3; pass >= 0; --pass) {
-                hist[tid] = 0;
+                for (int i = lane; i < 256; i += 32) myhist[i] = 0;
                 __syncthreads();
                 const uint32_t prefix = sh_prefix;
                 const uint32_t himask = pass == 3 ? 0u : (0xFFFFFFFFu << (8 * (pass + 1)));
-                for (int i = tid; i < V; i += 256) {
-                    const uint32_t key = float_key(lg[i]);
-                    if ((key & himask) == (prefix & himask)) atomicAdd(&hist[(key >> (8 * pass)) & 0xFF], 1);
+                for (int i0 = 0; i0 < V; i0 += NT) {
+                    // lanes of a warp that fall into the same bin add once (in the first pass nearly all of them do)
+                    const int i = i0 + tid;
+                    int bin = -1;
+                    if (i < V) {
+                        const uint32_t key = float_key(lg[i]);
+                        if ((key & himask) == (prefix & himask)) bin = (int)((key >> (8 * pass)) & 0xFF);
+                    }
+                    const unsigned peers = __match_any_sync(0xffffffffu, bin);
+                    if (bin >= 0 && lane == __ffs(peers) - 1) atomicAdd(&myhist[bin], __popc(peers));
+                }
+                __syncthreads();
+                if (tid < 256) {
+                    int t = 0;
+#pragma unroll 8
+                    for (int w = 0; w < NW; ++w) t += whist[w * 256 + tid];
+                    hist[tid] = t;
                 }
                 __syncthreads();
                 if (tid == 0) {
@@ -1026,32 +1093,21 @@ sample_kernel(const float* __restrict__ logits, int V, float temperature, int to
             const uint32_t thr = sh_prefix;  // key of the top_k-th element
             const int need_eq = sh_need;     // how many elements equal to thr are kept (smallest indices)
             // ordered compaction: thread t owns the contiguous index range [t*chunk, (t+1)*chunk)
-            const int chunk = (V + 255) / 256;
-            const int lo = tid * chunk, hi = min(V, lo + chunk);
+            // (an odd chunk length keeps the lanes of a warp on different shared-memory banks)
+            const int chunk = ((V + NT - 1) / NT) | 1;
+            const int lo = min(V, tid * chunk), hi = min(V, lo + chunk);
             int n_gt = 0, n_eq = 0;
             for (int i = lo; i < hi; ++i) {
                 const uint32_t key = float_key(lg[i]);
                 n_gt += key > thr;
                 n_eq += key == thr;
             }
-            scan_a[tid] = n_gt;
-            scan_b[tid] = n_eq;
-            __syncthreads();
-            if (tid == 0) {
-                int a = 0, c = 0;
-                for (int t = 0; t < 256; ++t) {
-                    const int ta = scan_a[t], tb = scan_b[t];
-                    scan_a[t] = a;
-                    scan_b[t] = c;
-                    a += ta;
-                    c += tb;
-                }
-            }
-            __syncthreads();
+            int tot_gt, tot_eq;
+            block_scan2(n_gt, n_eq, scan_a, scan_b, tot_gt, tot_eq);  // now exclusive prefixes
             {
-                int eq_before = scan_b[tid];
+                int eq_before = n_eq;
                 // selected count before this thread = gt before + min(eq before, need_eq)
-                int w = scan_a[tid] + min(eq_before, need_eq);
+                int w = n_gt + min(eq_before, need_eq);
                 for (int i = lo; i < hi; ++i) {
                     const uint32_t key = float_key(lg[i]);
                     if (key > thr) cand[w++] = i;
@@ -1062,21 +1118,32 @@ sample_kernel(const float* __restrict__ logits, int V, float temperature, int to
                 }
             }
             __syncthreads();
+            // softmax over the candidates in ascending index order, f32, then inverse CDF
+            const int nc = top_k;
+            float m2 = -INFINITY;
+            for (int i = tid; i < nc; i += NT) m2 = fmaxf(m2, lg[cand[i]]);
+            m2 = warp_max(m2);
+            if (lane == 0) red_f[warp] = m2;
+            __syncthreads();
+            m2 = red_f[0];
+#pragma unroll
+            for (int w = 1; w < NW; ++w) m2 = fmaxf(m2, red_f[w]);
+            for (int i = tid; i < nc; i += NT) cval[i] = nnb_expf(__fsub_rn(lg[cand[i]], m2));
+            __syncthreads();
             if (tid == 0) {
-                // softmax over the candidates in ascending index order, f32, then inverse CDF
-                const int nc = top_k;
-                float m2 = lg[cand[0]];
-                for (int i = 1; i < nc; ++i) m2 = fmaxf(m2, lg[cand[i]]);
                 float sum = 0.0f;
-                for (int i = 0; i < nc; ++i) {
-                    const float ev = nnb_expf(__fsub_rn(lg[cand[i]], m2));
-                    lg[cand[i]] = ev;
-                    sum = __fadd_rn(sum, ev);
-                }
+                for (int i = 0; i < nc; ++i) sum = __fadd_rn(sum, cval[i]);
+                red_f[0] = sum;
+            }
+            __syncthreads();
+            const float sum = red_f[0];
+            for (int i = tid; i < nc; i += NT) cval[i] = __fdiv_rn(cval[i], sum);
+            __syncthreads();
+            if (tid == 0) {
                 float cum = 0.0f;
                 int next = cand[nc - 1];
                 for (int i = 0; i < nc; ++i) {
-                    cum = __fadd_rn(cum, __fdiv_rn(lg[cand[i]], sum));
+                    cum = __fadd_rn(cum, cval[i]);
                     if (r <= cum) { next = cand[i]; break; }
                 }
                 sh_tok = next;
@@ -1084,25 +1151,27 @@ sample_kernel(const float* __restrict__ logits, int V, float temperature, int to
             __syncthreads();
         } else {
             // full vocabulary: p_i = exp(x_i - max)/sum with the sum and the CDF accumulated in
-            // f64 by contiguous chunks (the reference walks them in f32, ascending index)
+            // f64 by 256 contiguous chunks (the reference walks them in f32, ascending index)
             float m2 = -INFINITY;
-            for (int i = tid; i < V; i += 256) m2 = fmaxf(m2, lg[i]);
+            for (int i = tid; i < V; i += NT) m2 = fmaxf(m2, lg[i]);
             m2 = warp_max(m2);
             if (lane == 0) red_f[warp] = m2;
             __syncthreads();
             m2 = red_f[0];
 #pragma unroll
-            for (int w = 1; w < 8; ++w) m2 = fmaxf(m2, red_f[w]);
+            for (int w = 1; w < NW; ++w) m2 = fmaxf(m2, red_f[w]);
             __shared__ double dsum[256];
             const int chunk = (V + 255) / 256;
-            const int lo = tid * chunk, hi = min(V, lo + chunk);
-            double part = 0.0;
-            for (int i = lo; i < hi; ++i) {
-                const float ev = nnb_expf(__fsub_rn(lg[i], m2));
-                lg[i] = ev;
-                part += (double)ev;
+            if (tid < 256) {
+                const int lo = min(V, tid * chunk), hi = min(V, lo + chunk);
+                double part = 0.0;
+                for (int i = lo; i < hi; ++i) {
+                    const float ev = nnb_expf(__fsub_rn(lg[i], m2));
+                    lg[i] = ev;
+                    part += (double)ev;
+                }
+                dsum[tid] = part;
             }
-            dsum[tid] = part;
             __syncthreads();
             if (tid == 0) {
                 double tot = 0.0;
@@ -1112,7 +1181,7 @@ sample_kernel(const float* __restrict__ logits, int V, float temperature, int to
                 int next = V - 1;
                 bool found = false;
                 for (int t = 0; t < 256 && !found; ++t) {
-                    const int l2 = t * chunk, h2 = min(V, l2 + chunk);
+                    const int l2 = min(V, t * chunk), h2 = min(V, l2 + chunk);
                     for (int i = l2; i < h2; ++i) {
                         cum += (double)__fdiv_rn(lg[i], sumf);
                         if ((double)r <= cum) { next = i; found = true; break; }
@@ -1138,8 +1207,8 @@ nnb_status launch_sample(nnb_engine* e, bool exact, const float* logits, size_t 
 {
     NNB_REQUIRE(logits && tokens && B > 0 && V > 0, "sample: bad arguments");
     NNB_REQUIRE(top_k >= 0 && top_k <= 1024, "sample: top_k=%d out of range (0..1024)", top_k);
-    const size_t smem = ((V + 3) & ~(size_t)3) * 4 + 1024 * 4;
-    NNB_REQUIRE(smem <= 200 * 1024, "sample: vocabulary %zu too large for one CTA", V);
+    const size_t smem = ((V + 3) & ~(size_t)3) * 4 + 2 * 1024 * 4 + SAMPLE_NW * 256 * 4;
+    NNB_REQUIRE(smem <= 220 * 1024, "sample: vocabulary %zu too large for one CTA", V);
     if (exact) {
         auto kern = sample_kernel<true>;
         static size_t cfg = 0;
@@ -1147,9 +1216,8 @@ nnb_status launch_sample(nnb_engine* e, bool exact, const float* logits, size_t 
             NNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             cfg = smem;
         }
-        kern<<<(unsigned)B, 256, smem, e->stream>>>(logits, (int)V, temperature, top_k, seed, seq0, d_pos,
-                                                    prompt_len, tokens, (int)tokens_stride, logp,
-                                                    (int)logp_stride, entropy);
+        launch_ex(e, kern, dim3((unsigned)B), dim3(SAMPLE_NT), smem, logits, (int)V, temperature, top_k, seed, seq0, d_pos, prompt_len,
+                  tokens, (int)tokens_stride, logp, (int)logp_stride, entropy);
     } else {
         auto kern = sample_kernel<false>;
         static size_t cfg = 0;
@@ -1157,9 +1225,8 @@ nnb_status launch_sample(nnb_engine* e, bool exact, const float* logits, size_t 
             NNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             cfg = smem;
         }
-        kern<<<(unsigned)B, 256, smem, e->stream>>>(logits, (int)V, temperature, top_k, seed, seq0, d_pos,
-                                                    prompt_len, tokens, (int)tokens_stride, logp,
-                                                    (int)logp_stride, entropy);
+        launch_ex(e, kern, dim3((unsigned)B), dim3(SAMPLE_NT), smem, logits, (int)V, temperature, top_k, seed, seq0, d_pos, prompt_len,
+                  tokens, (int)tokens_stride, logp, (int)logp_stride, entropy);
     }
     e->launches++;
     NNB_CHECK_LAUNCH("sample_kernel");
@@ -1167,7 +1234,11 @@ nnb_status launch_sample(nnb_engine* e, bool exact, const float* logits, size_t 
 }
 
 __global__ void set_int_kernel(int* p, int v) { *p = v; }
-__global__ void add_int_kernel(int* p, int v) { *p += v; }
+__global__ void add_int_kernel(int* p, int v)
+{
+    pdl_wait();
+    *p += v;
+}
 
 nnb_status launch_set_int(nnb_engine* e, int* p, int v)
 {
@@ -1178,7 +1249,7 @@ nnb_status launch_set_int(nnb_engine* e, int* p, int v)
 }
 nnb_status launch_add_int(nnb_engine* e, int* p, int v)
 {
-    add_int_kernel<<<1, 1, 0, e->stream>>>(p, v);
+    launch_ex(e, add_int_kernel, dim3(1), dim3(1), 0, p, v);
     e->launches++;
     NNB_CHECK_LAUNCH("add_int_kernel");
     return NNB_OK;
@@ -1187,8 +1258,8 @@ nnb_status launch_add_int(nnb_engine* e, int* p, int v)
 nnb_status launch_embed(nnb_engine* e, const float* tok_emb, const float* pos_emb, const int32_t* tokens,
                         size_t tokens_stride, const int* d_pos, size_t B, size_t d, size_t vocab, float* x)
 {
-    embed_kernel<<<(unsigned)B, 128, 0, e->stream>>>(tok_emb, pos_emb, tokens, (int)tokens_stride, d_pos,
-                                                     (int)d, (int)vocab, x);
+    launch_ex(e, embed_kernel, dim3((unsigned)B), dim3(128), 0, tok_emb, pos_emb, tokens, (int)tokens_stride, d_pos, (int)d,
+              (int)vocab, x);
     e->launches++;
     NNB_CHECK_LAUNCH("embed_kernel");
     return NNB_OK;

@@ -6,6 +6,12 @@
 
 namespace nnb {
 
+// Programmatic dependent launch (no-ops for a kernel launched without the attribute):
+// pdl_launch lets the next kernel in the stream become resident; pdl_wait returns once every kernel this one
+// depends on has completed and its writes are visible.  Nothing in global memory may be touched before it.
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+
 // code = trit + 2; strict compares so |w| == 0.5*tau -> 0
 // (include/neuralnet.cpp/compute_layer_bitlinear.hpp:657-667)
 __device__ __forceinline__ uint32_t trit_code_of(float w, float tau)

@@ -164,6 +164,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     volatile int* abort_flag = err;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_launch();  // the next kernel of the stream may take the SM as soon as this CTA leaves it
     constexpr int KE = KIND == 0 ? 128 : 64;  // contraction elements per stage
     const int ktiles = (KC + KE - 1) / KE;
     const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
@@ -192,6 +193,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
+    // barriers and TMEM are set up; operands written by the previous kernel of the stream are touched from here on
+    pdl_wait();
 
     if (warp == 0) {
         // ---------------- TMA producer
@@ -446,7 +449,7 @@ static nnb_status launch(nnb_engine* e, const CUtensorMap& ta, const CUtensorMap
     int* flag = e->dev_flags;
     const size_t tiles = ceil_div(M, BM) * ceil_div(N, BN);
     const unsigned grid = (unsigned)(tiles < (size_t)e->sm_count ? tiles : (size_t)e->sm_count);
-    kern<<<grid, THREADS, SMEM_BYTES, e->stream>>>(ta, tb, ep, (int)M, (int)N, (int)KC, flag);
+    launch_ex(e, kern, dim3(grid), dim3(THREADS), (size_t)SMEM_BYTES, ta, tb, ep, (int)M, (int)N, (int)KC, flag);
     e->launches++;
     NNB_CHECK_LAUNCH("gemm_tc_kernel");
     return NNB_OK;

@@ -8,6 +8,8 @@
 #include <string>
 #include <vector>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "policy.cuh"
 
@@ -256,6 +258,17 @@ struct StepView {
     size_t pre_len, pre_alloc, pre_layer_bytes, group;
 };
 
+// NNB_PDL=0 in the environment turns the programmatic launches of the decode step off (for A/B timing)
+static bool pdl_enabled()
+{
+    static int v = -1;
+    if (v < 0) {
+        const char* s = getenv("NNB_PDL");
+        v = (s && s[0] == '0') ? 0 : 1;
+    }
+    return v != 0;
+}
+
 // one decode step at the position stored in d_pos: consumes tokens[:, pos], appends to the KV
 // cache and, when with_head, samples tokens[:, pos+1]
 static nnb_status decode_step(nnb_policy* p, const StepView& sv, bool with_head, float temperature, int top_k,
@@ -268,6 +281,14 @@ static nnb_status decode_step(nnb_policy* p, const StepView& sv, bool with_head,
     const size_t F1 = c.act == 1 ? 2 * F : F;
     const bool exact = c.exact != 0;
     const float* P = p->params;
+    // The fast mode's step is ~200 short kernels, each of which waits for the one before it (pdl_wait) before
+    // touching memory: let each become resident while its predecessor drains.
+    struct PdlScope {
+        nnb_engine* e;
+        bool prev;
+        PdlScope(nnb_engine* en, bool on) : e(en), prev(en->pdl) { e->pdl = on; }
+        ~PdlScope() { e->pdl = prev; }
+    } pdl_scope(e, !exact && pdl_enabled());
 
     NNB_TRY(launch_embed(e, P + p->tok_emb, c.pos == 0 ? P + p->pos_emb : nullptr, sv.tokens, sv.tok_stride, w.d_pos, B, d,
                          V, w.x));
@@ -280,6 +301,11 @@ static nnb_status decode_step(nnb_policy* p, const StepView& sv, bool with_head,
         void* vl = (char*)sv.v + (size_t)l * sv.layer_bytes;
         const void* kpl = sv.k_pre ? (const char*)sv.k_pre + (size_t)l * sv.pre_layer_bytes : nullptr;
         const void* vpl = sv.v_pre ? (const char*)sv.v_pre + (size_t)l * sv.pre_layer_bytes : nullptr;
+        // The attention kernel lives on memory-level parallelism through L1; overlapped with a kernel that claims
+        // the whole shared-memory carve-out (the GEMMs) it loses a third of its bandwidth (measured).  So it and the
+        // projection after it are launched the plain way: each starts on a drained GPU.
+        const bool pdl_saved = e->pdl;
+        e->pdl = false;
         if (!exact && attn_decode_fused_supported(H, dk) && d % 64 == 0) {
             // all heads of a sequence in one CTA, attention output quantised in the same launch
             NNB_TRY(launch_attn_decode_fused(e, w.qkv, kl, vl, sv.own_alloc, kpl, vpl, sv.pre_len, sv.pre_alloc, sv.group,
@@ -290,7 +316,11 @@ static nnb_status decode_step(nnb_policy* p, const StepView& sv, bool with_head,
                                        p->rope_cos, p->rope_sin, w.d_pos, B, H, dk, w.att));
             NNB_TRY(launch_row_quant(e, 3, exact, w.att, nullptr, B, d, d, w.q8, w.s, w.qsum, nullptr));
         }
-        NNB_TRY(policy_linear_fwd(p, L.o, 1, w.q8, w.s, w.qsum, B, w.x, w.x, 0));
+        {
+            const nnb_status so = policy_linear_fwd(p, L.o, 1, w.q8, w.s, w.qsum, B, w.x, w.x, 0);
+            e->pdl = pdl_saved;
+            NNB_TRY(so);
+        }
         NNB_TRY(launch_row_quant(e, 0, exact, w.x, P + L.ln2_g, B, d, d, w.q8, w.s, w.qsum, nullptr));
         NNB_TRY(policy_linear_fwd(p, L.fc1, 1, w.q8, w.s, w.qsum, B, nullptr, w.h1, 0));
         NNB_TRY(launch_row_quant(e, c.act == 1 ? 2 : 1, exact, w.h1, nullptr, B, F, F1, w.q8, w.s, w.qsum, nullptr));

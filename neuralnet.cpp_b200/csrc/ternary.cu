@@ -468,11 +468,13 @@ bitlinear_mma_kernel(const uint32_t* __restrict__ wq, size_t wq_stride_words,
 // ----------------------------------------------------------- skinny (decode) kernel
 // Few tokens (<= 8*NT), many output rows: the packed weights are the only real traffic, so the
 // kernel is a persistent weight streamer.  The activations of all tokens stay resident in
-// shared memory for the CTA's lifetime; every group of WK warps owns one 16-row slab at a
+// shared memory for the CTA's lifetime; every group of WK warps owns MS 16-row slabs at a
 // time and splits K between its warps; weights go straight from global memory to the
-// tensor-core operand registers (two 32-bit loads per 64 features per lane, register
-// double-buffered), no shared-memory staging and no barrier inside the K loop.
-template <int NT, int WK, typename OutT>
+// tensor-core operand registers (two 32-bit loads per slab per 64 features per lane, register
+// double-buffered), no shared-memory staging and no barrier inside the K loop.  An activation
+// fragment read from shared memory serves all MS slabs: with one slab per warp the shared-memory
+// pipe, not HBM, bounds the kernel (2 to 4 bytes of activations per byte of weights).
+template <int NT, int WK, int MS, typename OutT>
 __global__ void __launch_bounds__(256)
 bitlinear_skinny_kernel(const uint32_t* __restrict__ wq, size_t wq_stride_words,
                         const float* __restrict__ tau, const float* __restrict__ bias,
@@ -482,7 +484,7 @@ bitlinear_skinny_kernel(const uint32_t* __restrict__ wq, size_t wq_stride_words,
                         int32_t* __restrict__ acc_out)
 {
     constexpr int GROUPS = 8 / WK;
-    constexpr int UNROLL = 4;  // 64-feature blocks per register buffer
+    constexpr int UNROLL = MS == 1 ? 4 : 2;  // 64-feature blocks per register buffer
     extern __shared__ __align__(128) unsigned char smem[];
     const int row_stride = K + 16;  // +16 bytes: conflict-free ldmatrix across tokens
     unsigned char* Bs = smem;
@@ -507,7 +509,7 @@ bitlinear_skinny_kernel(const uint32_t* __restrict__ wq, size_t wq_stride_words,
 
     const int words_per_row = K / 16;
     const int nblk = K / 64;
-    const int mtiles = (OUT + 15) / 16;
+    const int mtiles = (OUT + 16 * MS - 1) / (16 * MS);
     const int n_items = mtiles * n_mats;
     const int blk_lo = (int)(((long long)nblk * wk) / WK);
     const int blk_hi = (int)(((long long)nblk * (wk + 1)) / WK);
@@ -516,27 +518,39 @@ bitlinear_skinny_kernel(const uint32_t* __restrict__ wq, size_t wq_stride_words,
 
     for (int item = blockIdx.x * GROUPS + group; item < n_items; item += gridDim.x * GROUPS) {
         const int mat = item / mtiles, mt = item - mat * mtiles;
-        const int r_lo = mt * 16 + g, r_hi = r_lo + 8;
         const uint32_t* wm = wq + (size_t)mat * wq_stride_words;
-        const bool ok_lo = r_lo < OUT, ok_hi = r_hi < OUT;
-        const uint32_t* p_lo = wm + (size_t)(ok_lo ? r_lo : 0) * words_per_row + t4;
-        const uint32_t* p_hi = wm + (size_t)(ok_hi ? r_hi : 0) * words_per_row + t4;
+        int r_lo[MS], r_hi[MS];
+        bool ok_lo[MS], ok_hi[MS];
+        const uint32_t *p_lo[MS], *p_hi[MS];
+#pragma unroll
+        for (int ms = 0; ms < MS; ++ms) {
+            r_lo[ms] = (mt * MS + ms) * 16 + g;
+            r_hi[ms] = r_lo[ms] + 8;
+            ok_lo[ms] = r_lo[ms] < OUT;
+            ok_hi[ms] = r_hi[ms] < OUT;
+            p_lo[ms] = wm + (size_t)(ok_lo[ms] ? r_lo[ms] : 0) * words_per_row + t4;
+            p_hi[ms] = wm + (size_t)(ok_hi[ms] ? r_hi[ms] : 0) * words_per_row + t4;
+        }
 
-        int acc[NT][4];
+        int acc[MS][NT][4];
 #pragma unroll
-        for (int j = 0; j < NT; ++j)
+        for (int ms = 0; ms < MS; ++ms)
 #pragma unroll
-            for (int c = 0; c < 4; ++c) acc[j][c] = 0;
+            for (int j = 0; j < NT; ++j)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) acc[ms][j][c] = 0;
 
-        uint32_t cur_lo[UNROLL], cur_hi[UNROLL], nxt_lo[UNROLL], nxt_hi[UNROLL];
-        auto fetch = [&](int b0, uint32_t (&lo)[UNROLL], uint32_t (&hi)[UNROLL]) {
+        uint32_t cur_lo[MS][UNROLL], cur_hi[MS][UNROLL], nxt_lo[MS][UNROLL], nxt_hi[MS][UNROLL];
+        auto fetch = [&](int b0, uint32_t (&lo)[MS][UNROLL], uint32_t (&hi)[MS][UNROLL]) {
 #pragma unroll
-            for (int u = 0; u < UNROLL; ++u) {
-                const int b = b0 + u;
-                const bool in = b < blk_hi;
-                lo[u] = (in && ok_lo) ? __ldg(p_lo + 4 * b) : 0u;
-                hi[u] = (in && ok_hi) ? __ldg(p_hi + 4 * b) : 0u;
-            }
+            for (int ms = 0; ms < MS; ++ms)
+#pragma unroll
+                for (int u = 0; u < UNROLL; ++u) {
+                    const int b = b0 + u;
+                    const bool in = b < blk_hi;
+                    lo[ms][u] = (in && ok_lo[ms]) ? __ldg(p_lo[ms] + 4 * b) : 0u;
+                    hi[ms][u] = (in && ok_hi[ms]) ? __ldg(p_hi[ms] + 4 * b) : 0u;
+                }
         };
         fetch(blk_lo, cur_lo, cur_hi);
         for (int b0 = blk_lo; b0 < blk_hi; b0 += UNROLL) {
@@ -546,47 +560,53 @@ bitlinear_skinny_kernel(const uint32_t* __restrict__ wq, size_t wq_stride_words,
                 const int b = b0 + u;
                 if (b < blk_hi) {
                     constexpr uint32_t MSK = 0x03030303u;
-                    const uint32_t w_lo = cur_lo[u], w_hi = cur_hi[u];
-                    const uint32_t a0 = w_lo & MSK, a1 = w_hi & MSK;
-                    const uint32_t a2 = (w_lo >> 2) & MSK, a3 = (w_hi >> 2) & MSK;
-                    const uint32_t c0 = (w_lo >> 4) & MSK, c1 = (w_hi >> 4) & MSK;
-                    const uint32_t c2 = (w_lo >> 6) & MSK, c3 = (w_hi >> 6) & MSK;
 #pragma unroll
                     for (int nt = 0; nt < NT; ++nt) {
                         uint32_t bf[4];
                         ldmatrix_x4(bf, b_lane + (size_t)nt * 8 * row_stride + b * 64);
-                        mma_u8s8(acc[nt], a0, a1, a2, a3, bf[0], bf[1]);
-                        mma_u8s8(acc[nt], c0, c1, c2, c3, bf[2], bf[3]);
+#pragma unroll
+                        for (int ms = 0; ms < MS; ++ms) {
+                            const uint32_t w_lo = cur_lo[ms][u], w_hi = cur_hi[ms][u];
+                            mma_u8s8(acc[ms][nt], w_lo & MSK, w_hi & MSK, (w_lo >> 2) & MSK, (w_hi >> 2) & MSK, bf[0], bf[1]);
+                            mma_u8s8(acc[ms][nt], (w_lo >> 4) & MSK, (w_hi >> 4) & MSK, (w_lo >> 6) & MSK, (w_hi >> 6) & MSK, bf[2],
+                                     bf[3]);
+                        }
                     }
                 }
             }
 #pragma unroll
-            for (int u = 0; u < UNROLL; ++u) {
-                cur_lo[u] = nxt_lo[u];
-                cur_hi[u] = nxt_hi[u];
-            }
+            for (int ms = 0; ms < MS; ++ms)
+#pragma unroll
+                for (int u = 0; u < UNROLL; ++u) {
+                    cur_lo[ms][u] = nxt_lo[ms][u];
+                    cur_hi[ms][u] = nxt_hi[ms][u];
+                }
         }
 
         if (WK > 1) {
             // items are assigned per group, so the WK warps of a group always iterate together;
             // they meet on a named barrier of their own (id group+1), never on the CTA barrier
-            int* slot = red + ((size_t)(group * WK + wk) * 32 + lane) * (NT * 4);
+            int* slot = red + ((size_t)(group * WK + wk) * 32 + lane) * (MS * NT * 4);
             if (wk > 0) {
 #pragma unroll
-                for (int j = 0; j < NT; ++j)
+                for (int ms = 0; ms < MS; ++ms)
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) slot[j * 4 + c] = acc[j][c];
+                    for (int j = 0; j < NT; ++j)
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) slot[(ms * NT + j) * 4 + c] = acc[ms][j][c];
             }
             // named barrier per group: only the WK warps of this group take part
             asm volatile("bar.sync %0, %1;\n" ::"r"(group + 1), "r"(WK * 32));
             if (wk == 0) {
 #pragma unroll
                 for (int o = 1; o < WK; ++o) {
-                    const int* src = red + ((size_t)(group * WK + o) * 32 + lane) * (NT * 4);
+                    const int* src = red + ((size_t)(group * WK + o) * 32 + lane) * (MS * NT * 4);
 #pragma unroll
-                    for (int j = 0; j < NT; ++j)
+                    for (int ms = 0; ms < MS; ++ms)
 #pragma unroll
-                        for (int c = 0; c < 4; ++c) acc[j][c] += src[j * 4 + c];
+                        for (int j = 0; j < NT; ++j)
+#pragma unroll
+                            for (int c = 0; c < 4; ++c) acc[ms][j][c] += src[(ms * NT + j) * 4 + c];
                 }
             }
             asm volatile("bar.sync %0, %1;\n" ::"r"(group + 1), "r"(WK * 32));
@@ -604,15 +624,18 @@ bitlinear_skinny_kernel(const uint32_t* __restrict__ wq, size_t wq_stride_words,
                     const int qs2 = 2 * qsum[tok];
                     const float st = s[tok];
 #pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        const int row = h ? r_hi : r_lo;
-                        if (row >= OUT) continue;
-                        const int a = acc[nt][h * 2 + cc] - qs2;
-                        float v = __fmul_rn(__fmul_rn(tau_m[row], st), (float)a);
-                        if (bias_m) v = __fadd_rn(v, bias_m[row]);
-                        if (residual) v = __fadd_rn(residual[(size_t)tok * OUT + row], v);
-                        store_out<OutT>(y_m + (size_t)tok * OUT + row, v);
-                        if (acc_out) acc_out[(size_t)tok * OUT + row] = a;
+                    for (int ms = 0; ms < MS; ++ms) {
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const int row = h ? r_hi[ms] : r_lo[ms];
+                            if (row >= OUT) continue;
+                            const int a = acc[ms][nt][h * 2 + cc] - qs2;
+                            float v = __fmul_rn(__fmul_rn(tau_m[row], st), (float)a);
+                            if (bias_m) v = __fadd_rn(v, bias_m[row]);
+                            if (residual) v = __fadd_rn(residual[(size_t)tok * OUT + row], v);
+                            store_out<OutT>(y_m + (size_t)tok * OUT + row, v);
+                            if (acc_out) acc_out[(size_t)tok * OUT + row] = a;
+                        }
                     }
                 }
             }
@@ -620,7 +643,7 @@ bitlinear_skinny_kernel(const uint32_t* __restrict__ wq, size_t wq_stride_words,
     }
 }
 
-template <int NT, int WK, typename OutT>
+template <int NT, int WK, int MS, typename OutT>
 static nnb_status launch_skinny(nnb_engine* e, const uint32_t* wq, size_t wq_stride,
                                 const float* tau, const float* bias, const float* residual,
                                 const int8_t* q, const float* s, const int32_t* qsum, size_t n_mats,
@@ -628,14 +651,14 @@ static nnb_status launch_skinny(nnb_engine* e, const uint32_t* wq, size_t wq_str
                                 int32_t* acc)
 {
     constexpr int GROUPS = 8 / WK;
-    const size_t smem = (size_t)NT * 8 * (k + 16) + (size_t)8 * 32 * NT * 4 * sizeof(int);
-    auto kern = bitlinear_skinny_kernel<NT, WK, OutT>;
+    const size_t smem = (size_t)NT * 8 * (k + 16) + (size_t)8 * 32 * MS * NT * 4 * sizeof(int);
+    auto kern = bitlinear_skinny_kernel<NT, WK, MS, OutT>;
     static size_t configured = 0;
     if (smem > configured) {
         NNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured = smem;
     }
-    const size_t n_items = ceil_div(out, 16) * n_mats;
+    const size_t n_items = ceil_div(out, 16 * MS) * n_mats;
     size_t ctas_per_sm = (200 * 1024) / (smem + 1024);
     if (ctas_per_sm > 4) ctas_per_sm = 4;
     if (ctas_per_sm < 1) ctas_per_sm = 1;
@@ -684,21 +707,30 @@ static nnb_status dispatch_skinny(nnb_engine* e, const uint32_t* wq, size_t wq_s
                                   size_t n_mats, size_t t, size_t k, size_t out, OutT* y,
                                   size_t y_stride, int32_t* acc)
 {
-    // pick the K split so that the 16-row slabs fill the machine's warp slots
-    const size_t smem = (size_t)NT * 8 * (k + 16) + 4096 * NT;
+    // pick the rows per warp and the K split so that the slabs fill the machine's warp slots: two 16-row slabs
+    // per warp (half the shared-memory reads per weight byte) whenever that still leaves enough items
+    const size_t smem = (size_t)NT * 8 * (k + 16) + 8192 * NT;
     size_t ctas_per_sm = (200 * 1024) / (smem + 1024);
     if (ctas_per_sm > 4) ctas_per_sm = 4;
     if (ctas_per_sm < 1) ctas_per_sm = 1;
     const size_t slots = (size_t)e->sm_count * ctas_per_sm * 8;
-    const size_t items = ceil_div(out, 16) * n_mats;
     const size_t nblk = k / 64;
-#define NNB_SKINNY(WK_)                                                                          \
-    return launch_skinny<NT, WK_, OutT>(e, wq, wq_stride, tau, bias, residual, q, s, qsum, n_mats, \
-                                        t, k, out, y, y_stride, acc)
-    if (items >= slots || nblk < 2) NNB_SKINNY(1);
-    if (items * 2 >= slots || nblk < 4) NNB_SKINNY(2);
-    if (items * 4 >= slots || nblk < 8) NNB_SKINNY(4);
-    NNB_SKINNY(8);
+#define NNB_SKINNY(WK_, MS_)                                                                            \
+    return launch_skinny<NT, WK_, MS_, OutT>(e, wq, wq_stride, tau, bias, residual, q, s, qsum, n_mats, \
+                                             t, k, out, y, y_stride, acc)
+    const size_t items2 = ceil_div(out, 32) * n_mats;
+    // (measured on 2048 x 11264 stacks: 0.51-0.53 of the copy bandwidth at 1-8 tokens against 0.49-0.50 with
+    // one slab, 0.35 against 0.30 at 32 tokens; at 9-16 tokens the extra registers cost more occupancy than the
+    // shared-memory reads they save: 0.39 against 0.43)
+    if (NT != 2 && items2 * 2 >= slots) {
+        if (items2 >= slots || nblk < 2) NNB_SKINNY(1, 2);
+        NNB_SKINNY(2, 2);
+    }
+    const size_t items = ceil_div(out, 16) * n_mats;
+    if (items >= slots || nblk < 2) NNB_SKINNY(1, 1);
+    if (items * 2 >= slots || nblk < 4) NNB_SKINNY(2, 1);
+    if (items * 4 >= slots || nblk < 8) NNB_SKINNY(4, 1);
+    NNB_SKINNY(8, 1);
 #undef NNB_SKINNY
 }
 
