@@ -245,8 +245,16 @@ nnb_status nnb_attention_decode(nnb_engine* e, const float* d_qkv, void* d_kcach
     if (d_q8) {
         NNB_REQUIRE(!exact && d_s && d_qsum && attn_decode_fused_supported(n_head, dk) && (n_head * dk) % 64 == 0,
                     "attention_decode: the fused int8 output needs the fast mode, head dim 64 or 128, at most 32 heads");
-        return launch_attn_decode_fused(e, d_qkv, d_kcache, d_vcache, ctx_alloc, d_kpre, d_vpre, pre_len, pre_alloc, group,
-                                        d_rope_cos, d_rope_sin, d_pos, n_seq, n_head, dk, d_out, d_q8, d_s, d_qsum);
+        // the batched treatment of a shared prefix needs scratch for its partial softmax: stream-ordered here
+        float* tmp = nullptr;
+        const bool pre = pre_len > 0 && group > 1 && group <= 16;
+        const size_t n_o = n_seq * n_head * dk, n_ml = n_seq * n_head * 2;
+        if (pre) NNB_CUDA(cudaMallocAsync((void**)&tmp, (n_o + n_ml) * sizeof(float), e->stream));
+        const nnb_status st = launch_attn_decode_fused(e, d_qkv, d_kcache, d_vcache, ctx_alloc, d_kpre, d_vpre, pre_len, pre_alloc,
+                                                       group, d_rope_cos, d_rope_sin, d_pos, n_seq, n_head, dk, d_out, d_q8, d_s,
+                                                       d_qsum, tmp, tmp ? tmp + n_o : nullptr);
+        if (tmp) cudaFreeAsync(tmp, e->stream);
+        return st;
     }
     NNB_REQUIRE(d_out, "attention_decode: no output requested");
     return launch_attn_decode(e, exact != 0, d_qkv, d_kcache, d_vcache, ctx_alloc, d_kpre, d_vpre, pre_len, pre_alloc, group,

@@ -137,7 +137,8 @@ bool attn_decode_fused_supported(size_t H, size_t dk);
 nnb_status launch_attn_decode_fused(nnb_engine* e, const float* qkv, void* kcache, void* vcache, size_t own_alloc,
                                     const void* kpre, const void* vpre, size_t pre_len, size_t pre_alloc, size_t group,
                                     const float* rope_cos, const float* rope_sin, const int* d_pos, size_t B, size_t H,
-                                    size_t dk, float* att, int8_t* q8, float* s, int32_t* qsum);
+                                    size_t dk, float* att, int8_t* q8, float* s, int32_t* qsum, float* pre_o = nullptr,
+                                    float* pre_ml = nullptr);
 nnb_status launch_sample(nnb_engine* e, bool exact, const float* logits, size_t B, size_t V,
                          float temperature, int top_k, unsigned long long seed, unsigned seq0,
                          const int* d_pos, int prompt_len, int32_t* tokens, size_t tokens_stride,

@@ -623,6 +623,188 @@ static nnb_status launch_attn_decode_bf16(nnb_engine* e, const float* qkv, void*
     return NNB_OK;
 }
 
+// ---- attention of a whole group's new tokens over the group's shared prompt prefix
+__device__ __forceinline__ void ldsm_b16(uint32_t (&r)[4], const void* p)
+{
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldsm_t_b16(uint32_t (&r)[4], const void* p)
+{
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
+{
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// The sequences of a group (at most 16) share their prompt, so their new tokens attend to the same prefix
+// keys and values: one warp takes (group, head), holds the group's 16 rotated queries as one m16 tensor-core
+// tile and walks the prefix cache once, instead of every sequence reading it for itself.  It leaves, per
+// (sequence, head), the partial softmax over the prefix: pre_ml = (max scaled score, sum of exp) and
+// pre_o = sum_j exp(s_j - max) v_j (unnormalised), which attn_decode_fused_kernel merges with the
+// sequence's own positions.  grid (n_groups, H/4), 128 threads; queries are rounded to bf16 here.
+template <int DK>
+__global__ void __launch_bounds__(128)
+attn_prefix_kernel(const float* __restrict__ qkv, const __nv_bfloat16* __restrict__ kpre, const __nv_bfloat16* __restrict__ vpre,
+                   int pre_len, int pre_alloc, int group, const float* __restrict__ rope_cos, const float* __restrict__ rope_sin,
+                   const int* __restrict__ d_pos, int B, int H, float scale, float* __restrict__ pre_o, float* __restrict__ pre_ml)
+{
+    constexpr int LD = DK + 8, half = DK / 2, KT = 32;  // KT keys per tile
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw) + (size_t)warp * (16 + 2 * KT) * LD;
+    __nv_bfloat16* Ks = Qs + 16 * LD;
+    __nv_bfloat16* Vs = Ks + KT * LD;
+    const int grp = blockIdx.x, h = blockIdx.y * 4 + warp;
+    if (h >= H) return;
+    const int d = H * DK;
+    const int pos = *d_pos;
+
+    // the group's queries, rotated, as bf16 rows (rows beyond the group stay zero)
+    {
+        const int r = lane >> 1;               // member of the group
+        const int j0 = (lane & 1) * (half / 2);  // first of this lane's half/2 rotation pairs
+        const bool ok = r < group;
+        const float* qn = qkv + (size_t)(grp * group + (ok ? r : 0)) * d + (size_t)h * DK;
+        for (int j = j0; j < j0 + half / 2; j += 4) {
+            float4 a = make_float4(0.f, 0.f, 0.f, 0.f), bq = a;
+            if (ok) {
+                a = *reinterpret_cast<const float4*>(qn + j);
+                bq = *reinterpret_cast<const float4*>(qn + j + half);
+            }
+            float4 c = make_float4(1.f, 1.f, 1.f, 1.f), sn = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (rope_cos) {
+                c = *reinterpret_cast<const float4*>(rope_cos + (size_t)pos * half + j);
+                sn = *reinterpret_cast<const float4*>(rope_sin + (size_t)pos * half + j);
+            }
+            uint2 lo, hi;
+            lo.x = pack_bf16x2(a.x * c.x - bq.x * sn.x, a.y * c.y - bq.y * sn.y);
+            lo.y = pack_bf16x2(a.z * c.z - bq.z * sn.z, a.w * c.w - bq.w * sn.w);
+            hi.x = pack_bf16x2(bq.x * c.x + a.x * sn.x, bq.y * c.y + a.y * sn.y);
+            hi.y = pack_bf16x2(bq.z * c.z + a.z * sn.z, bq.w * c.w + a.w * sn.w);
+            *reinterpret_cast<uint2*>(Qs + r * LD + j) = lo;
+            *reinterpret_cast<uint2*>(Qs + r * LD + j + half) = hi;
+        }
+    }
+    __syncwarp();
+    uint32_t qf[DK / 16][4];
+#pragma unroll
+    for (int ks = 0; ks < DK / 16; ++ks) ldsm_b16(qf[ks], Qs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LD + ks * 16 + 8 * (lane >> 4));
+
+    const size_t pre_off = ((size_t)grp * H + h) * (size_t)pre_alloc * DK;
+    const __nv_bfloat16* kp = kpre + pre_off;
+    const __nv_bfloat16* vp = vpre + pre_off;
+    float o[DK / 8][4];
+#pragma unroll
+    for (int i = 0; i < DK / 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[i][j] = 0.0f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    constexpr int CH = DK / 8;  // 16-byte chunks per row
+    for (int j0 = 0; j0 < pre_len; j0 += KT) {
+        __syncwarp();
+        for (int i = lane; i < KT * CH; i += 32) {
+            const int r = i / CH, c = (i % CH) * 8;
+            uint4 kv4 = make_uint4(0u, 0u, 0u, 0u), vv4 = kv4;
+            if (j0 + r < pre_len) {
+                kv4 = *reinterpret_cast<const uint4*>(kp + (size_t)(j0 + r) * DK + c);
+                vv4 = *reinterpret_cast<const uint4*>(vp + (size_t)(j0 + r) * DK + c);
+            }
+            *reinterpret_cast<uint4*>(Ks + r * LD + c) = kv4;
+            *reinterpret_cast<uint4*>(Vs + r * LD + c) = vv4;
+        }
+        __syncwarp();
+        float s[KT / 8][4];
+#pragma unroll
+        for (int i = 0; i < KT / 8; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) s[i][j] = 0.0f;
+#pragma unroll
+        for (int ks = 0; ks < DK / 16; ++ks) {
+#pragma unroll
+            for (int np = 0; np < KT / 16; ++np) {
+                uint32_t bk[4];
+                ldsm_b16(bk, Ks + (np * 16 + (lane & 7) + 8 * (lane >> 4)) * LD + ks * 16 + 8 * ((lane >> 3) & 1));
+                mma_bf16(s[np * 2], qf[ks], bk[0], bk[1]);
+                mma_bf16(s[np * 2 + 1], qf[ks], bk[2], bk[3]);
+            }
+        }
+        float mxv[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nt = 0; nt < KT / 8; ++nt)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int key = j0 + nt * 8 + 2 * t4 + (c & 1);
+                s[nt][c] = key < pre_len ? s[nt][c] * scale : -INFINITY;
+                mxv[c >> 1] = fmaxf(mxv[c >> 1], s[nt][c]);
+            }
+        float corr[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            mxv[r] = fmaxf(mxv[r], __shfl_xor_sync(0xffffffffu, mxv[r], 1));
+            mxv[r] = fmaxf(mxv[r], __shfl_xor_sync(0xffffffffu, mxv[r], 2));
+            const float mnew = fmaxf(m[r], mxv[r]);
+            corr[r] = __expf(m[r] - mnew);  // m = -inf on the first tile: exp(-inf) = 0, and l, o are 0 anyway
+            m[r] = mnew;
+            l[r] *= corr[r];
+        }
+#pragma unroll
+        for (int i = 0; i < DK / 8; ++i) {
+            o[i][0] *= corr[0]; o[i][1] *= corr[0];
+            o[i][2] *= corr[1]; o[i][3] *= corr[1];
+        }
+#pragma unroll
+        for (int nt = 0; nt < KT / 8; ++nt)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const float pj = __expf(s[nt][c] - m[c >> 1]);
+                s[nt][c] = pj;
+                l[c >> 1] += pj;
+            }
+#pragma unroll
+        for (int kk = 0; kk < KT / 16; ++kk) {
+            uint32_t pa[4];
+            pa[0] = pack_bf16x2(s[2 * kk][0], s[2 * kk][1]);
+            pa[1] = pack_bf16x2(s[2 * kk][2], s[2 * kk][3]);
+            pa[2] = pack_bf16x2(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+            pa[3] = pack_bf16x2(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+            for (int np = 0; np < DK / 16; ++np) {
+                uint32_t bv[4];
+                ldsm_t_b16(bv, Vs + (kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LD + np * 16 + 8 * (lane >> 4));
+                mma_bf16(o[np * 2], pa, bv[0], bv[1]);
+                mma_bf16(o[np * 2 + 1], pa, bv[2], bv[3]);
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    }
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+        const int r = g + 8 * hh;
+        if (r >= group) continue;
+        const size_t bh = (size_t)(grp * group + r) * H + h;
+        float* dst = pre_o + bh * DK;
+#pragma unroll
+        for (int i = 0; i < DK / 8; ++i)
+            *reinterpret_cast<float2*>(dst + i * 8 + 2 * t4) = make_float2(o[i][hh * 2], o[i][hh * 2 + 1]);
+        if (t4 == 0) {
+            pre_ml[bh * 2] = m[hh];
+            pre_ml[bh * 2 + 1] = l[hh];
+        }
+    }
+}
+
 // Decode attention of ALL heads of a sequence in one CTA, one warp per head, followed by the int8
 // quantisation of the token's attention output (the input of the output projection): what
 // attn_decode_bf16_kernel + row_quant_fast_kernel<3> compute, in one launch and without block-wide
@@ -636,7 +818,7 @@ attn_decode_fused_kernel(const float* __restrict__ qkv, __nv_bfloat16* __restric
                          int pre_len, int pre_alloc, int group, const float* __restrict__ rope_cos,
                          const float* __restrict__ rope_sin, const int* __restrict__ d_pos, int B, int H, int ctx_pad,
                          float scale, float* __restrict__ att, int8_t* __restrict__ q8, float* __restrict__ s_out,
-                         int32_t* __restrict__ qsum_out)
+                         int32_t* __restrict__ qsum_out, const float* __restrict__ pre_o, const float* __restrict__ pre_ml)
 {
     constexpr int LPK = DK / 8;    // lanes per key
     constexpr int KPW = 32 / LPK;  // keys per warp-wide load
@@ -707,10 +889,13 @@ attn_decode_fused_kernel(const float* __restrict__ qkv, __nv_bfloat16* __restric
     }
     __syncwarp();
     const int n_keys = pos + 1;
+    // With pre_o / pre_ml the shared prefix has been attended to already (attn_prefix_kernel, all members of a
+    // group at once): this kernel covers the sequence's own positions and merges the two partial softmaxes.
+    const int j_first = pre_o ? pre_len : 0;
 
     // scores
     float mx = -INFINITY;
-    for (int base = 0; base < n_keys; base += KPW * U) {
+    for (int base = j_first; base < n_keys; base += KPW * U) {
         uint4 raw[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
@@ -738,18 +923,26 @@ attn_decode_fused_kernel(const float* __restrict__ qkv, __nv_bfloat16* __restric
     mx = warp_max(mx);
     __syncwarp();
     float sum = 0.0f;
-    for (int j = lane; j < n_keys; j += 32) {
+    for (int j = j_first + lane; j < n_keys; j += 32) {
         const float ev = __expf(sc[j] - mx);
         sc[j] = ev;
         sum += ev;
     }
     sum = warp_sum(sum);
+    float w_own = 1.0f, w_pre = 0.0f;
+    if (pre_o) {
+        const float m_pre = pre_ml[((size_t)b * H + h) * 2], l_pre = pre_ml[((size_t)b * H + h) * 2 + 1];
+        const float m_all = fmaxf(mx, m_pre);
+        w_own = __expf(mx - m_all);
+        w_pre = __expf(m_pre - m_all);
+        sum = w_own * sum + w_pre * l_pre;
+    }
     const float inv = 1.0f / sum;
     __syncwarp();
 
     // out = sum_j p_j v_j
     float o8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int base = 0; base < n_keys; base += KPW * U) {
+    for (int base = j_first; base < n_keys; base += KPW * U) {
         uint4 raw[U];
         float pj[U];
 #pragma unroll
@@ -775,6 +968,13 @@ attn_decode_fused_kernel(const float* __restrict__ qkv, __nv_bfloat16* __restric
 #pragma unroll
         for (int i = 0; i < 8; ++i) o8[i] += __shfl_xor_sync(0xffffffffu, o8[i], o);
     if (sub == 0) {
+        if (pre_o) {
+            const float* po = pre_o + ((size_t)b * H + h) * DK + e0;
+            const float4 p0 = *reinterpret_cast<const float4*>(po), p1 = *reinterpret_cast<const float4*>(po + 4);
+            const float pv[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o8[i] = w_own * o8[i] + w_pre * pv[i];
+        }
 #pragma unroll
         for (int i = 0; i < 8; ++i) o8[i] *= inv;
         float* dst = orow + h * DK + e0;
@@ -833,9 +1033,35 @@ bool attn_decode_fused_supported(size_t H, size_t dk) { return (dk == 64 || dk =
 nnb_status launch_attn_decode_fused(nnb_engine* e, const float* qkv, void* kcache, void* vcache, size_t own_alloc,
                                     const void* kpre, const void* vpre, size_t pre_len, size_t pre_alloc, size_t group,
                                     const float* rope_cos, const float* rope_sin, const int* d_pos, size_t B, size_t H,
-                                    size_t dk, float* att, int8_t* q8, float* s, int32_t* qsum)
+                                    size_t dk, float* att, int8_t* q8, float* s, int32_t* qsum, float* pre_o, float* pre_ml)
 {
     NNB_REQUIRE(attn_decode_fused_supported(H, dk), "attn_decode_fused: %zu heads of %zu features unsupported", H, dk);
+    NNB_REQUIRE((pre_o == nullptr) == (pre_ml == nullptr), "attn_decode_fused: pre_o and pre_ml go together");
+    // a shared prefix read by groups of at most 16 sequences is attended to once per group
+    const bool batched_prefix = pre_o && pre_len > 0 && group > 1 && group <= 16 && B % group == 0;
+    if (batched_prefix) {
+        const size_t smem_p = 4 * (16 + 64) * (dk + 8) * sizeof(__nv_bfloat16);
+        const float scale_p = 1.0f / sqrtf((float)dk);
+        dim3 grid_p((unsigned)(B / group), (unsigned)ceil_div(H, 4));
+        static bool cfg_p = false;
+        if (!cfg_p) {
+            NNB_CUDA(cudaFuncSetAttribute(attn_prefix_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * 80 * 136 * 2));
+            NNB_CUDA(cudaFuncSetAttribute(attn_prefix_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * 80 * 72 * 2));
+            cfg_p = true;
+        }
+        if (dk == 128)
+            attn_prefix_kernel<128><<<grid_p, 128, smem_p, e->stream>>>(qkv, (const __nv_bfloat16*)kpre, (const __nv_bfloat16*)vpre,
+                                                                       (int)pre_len, (int)pre_alloc, (int)group, rope_cos, rope_sin,
+                                                                       d_pos, (int)B, (int)H, scale_p, pre_o, pre_ml);
+        else
+            attn_prefix_kernel<64><<<grid_p, 128, smem_p, e->stream>>>(qkv, (const __nv_bfloat16*)kpre, (const __nv_bfloat16*)vpre,
+                                                                      (int)pre_len, (int)pre_alloc, (int)group, rope_cos, rope_sin,
+                                                                      d_pos, (int)B, (int)H, scale_p, pre_o, pre_ml);
+        e->launches++;
+        NNB_CHECK_LAUNCH("attn_prefix_kernel");
+    }
+    const float* use_o = batched_prefix ? pre_o : nullptr;
+    const float* use_ml = batched_prefix ? pre_ml : nullptr;
     NNB_REQUIRE(group >= 1 && (pre_len == 0 || (kpre && vpre)), "attn_decode_fused: bad prefix arguments");
     NNB_REQUIRE((q8 == nullptr) == (s == nullptr) && (q8 == nullptr) == (qsum == nullptr), "attn_decode_fused: q8, s, qsum go together");
     const size_t ctx_pad = (pre_len + own_alloc + 3) & ~(size_t)3;
@@ -852,7 +1078,8 @@ nnb_status launch_attn_decode_fused(nnb_engine* e, const float* qkv, void* kcach
         }                                                                                                                 \
         launch_ex(e, kern, dim3((unsigned)B), dim3((unsigned)(32 * H)), smem, qkv, (__nv_bfloat16*)kcache,                \
                   (__nv_bfloat16*)vcache, (int)own_alloc, (const __nv_bfloat16*)kpre, (const __nv_bfloat16*)vpre, (int)pre_len, \
-                  (int)pre_alloc, (int)group, rope_cos, rope_sin, d_pos, (int)B, (int)H, (int)ctx_pad, scale, att, q8, s, qsum); \
+                  (int)pre_alloc, (int)group, rope_cos, rope_sin, d_pos, (int)B, (int)H, (int)ctx_pad, scale, att, q8, s, qsum, \
+                  use_o, use_ml);                                                                                            \
     }
     if (dk == 128) NNB_FUSED(128) else NNB_FUSED(64)
 #undef NNB_FUSED

@@ -183,7 +183,7 @@ nnb_status policy_requantize(nnb_policy* p)
 static void free_decode(nnb_policy* p)
 {
     DecodeWs& w = p->dec;
-    void* ptrs[] = {w.k, w.v, w.k_pre, w.v_pre, w.tokens_pre, w.x, w.qkv, w.att, w.h1, w.logits, w.q8, w.s, w.qsum, w.d_pos,
+    void* ptrs[] = {w.k, w.v, w.k_pre, w.v_pre, w.tokens_pre, w.x, w.qkv, w.att, w.pre_ml, w.h1, w.logits, w.q8, w.s, w.qsum, w.d_pos,
                     w.tokens, w.logp};
     for (void* q : ptrs)
         if (q) cudaFree(q);
@@ -230,6 +230,7 @@ static nnb_status ensure_decode(nnb_policy* p, size_t B, size_t ctx_alloc, size_
     NNB_ALLOC(w.x, B * d * 4);
     NNB_ALLOC(w.qkv, 3 * B * d * 4);
     NNB_ALLOC(w.att, B * d * 4);
+    NNB_ALLOC(w.pre_ml, B * c.n_head * 2 * 4);
     NNB_ALLOC(w.h1, B * F1 * 4);
     NNB_ALLOC(w.logits, B * V * 4);
     NNB_ALLOC(w.q8, B * (F > d ? F : d));
@@ -310,7 +311,7 @@ static nnb_status decode_step(nnb_policy* p, const StepView& sv, bool with_head,
             // all heads of a sequence in one CTA, attention output quantised in the same launch
             NNB_TRY(launch_attn_decode_fused(e, w.qkv, kl, vl, sv.own_alloc, kpl, vpl, sv.pre_len, sv.pre_alloc, sv.group,
                                              c.pos == 1 ? p->rope_cos : nullptr, c.pos == 1 ? p->rope_sin : nullptr, w.d_pos, B, H,
-                                             dk, nullptr, w.q8, w.s, w.qsum));
+                                             dk, nullptr, w.q8, w.s, w.qsum, w.att, w.pre_ml));
         } else {
             NNB_TRY(launch_attn_decode(e, exact, w.qkv, kl, vl, sv.own_alloc, kpl, vpl, sv.pre_len, sv.pre_alloc, sv.group,
                                        p->rope_cos, p->rope_sin, w.d_pos, B, H, dk, w.att));

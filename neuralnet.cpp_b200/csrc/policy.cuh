@@ -31,6 +31,7 @@ struct DecodeWs {
     void *k_pre = nullptr, *v_pre = nullptr;  // (L, B/group, H, pre_len, dk): prompt prefix, one per group
     int32_t* tokens_pre = nullptr;            // (B/group, pre_len) prompt tokens of the group representatives
     float *x = nullptr, *qkv = nullptr, *att = nullptr, *h1 = nullptr, *logits = nullptr;
+    float* pre_ml = nullptr;  // (B, H, 2): partial softmax (max, sum) over the shared prefix; its values go to att
     int8_t* q8 = nullptr;
     float* s = nullptr;
     int32_t* qsum = nullptr;

@@ -150,7 +150,9 @@ def test_context_overflow_is_rejected(pkg, eng):
 @pytest.mark.parametrize("exact", [True, False])
 @pytest.mark.parametrize("P", [1, 2, 9])
 def test_grouped_rollout_equals_ungrouped(pkg, eng, exact, P):
-    """Sharing the prompt prefix inside a group changes where K/V are stored, not the arithmetic."""
+    """Sharing the prompt prefix inside a group changes where K/V are stored, not the arithmetic: bit-identical in
+    the exact mode.  The fast mode attends to the shared prefix for all members of a group at once on tensor cores
+    (queries rounded to bf16, the softmax merged from two parts), so there the logits agree to bf16 rounding."""
     cfg = pkg.GptConfig(n_layer=2, d_model=128, n_head=2, d_ff=256, vocab=300, ctx=48, act=1, pos=1, exact=exact)
     pol = pkg.Policy(eng, cfg)
     pol.upload_params(cfg.init_params(5, bias_std=0.01))
@@ -158,6 +160,10 @@ def test_grouped_rollout_equals_ungrouped(pkg, eng, exact, P):
     prompts = torch.from_numpy(np.repeat(base, 4, axis=0)).to(eng.device)  # 3 groups of 4
     a_tok, a_lp, a_lg = pol.rollout(prompts, 12, temperature=0.9, top_k=20, seed=5, seq0=7, want_logits=True)
     b_tok, b_lp, b_lg = pol.rollout(prompts, 12, temperature=0.9, top_k=20, seed=5, seq0=7, want_logits=True, group_size=4)
-    assert torch.equal(a_lg, b_lg) and torch.equal(a_tok, b_tok) and torch.equal(a_lp, b_lp)
+    if exact or P == 1:  # a one-token prompt leaves no prefix to share
+        assert torch.equal(a_lg, b_lg) and torch.equal(a_tok, b_tok) and torch.equal(a_lp, b_lp)
+    else:
+        # first generated step: same inputs on both paths (later steps follow whichever tokens were sampled)
+        assert (a_lg[:, 0] - b_lg[:, 0]).abs().max().item() <= 2e-2 * a_lg[:, 0].abs().max().item()
     with pytest.raises(pkg.NnbError):
         pol.rollout(prompts[:10].contiguous(), 4, group_size=4)
