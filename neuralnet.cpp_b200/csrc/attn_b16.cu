@@ -8,7 +8,8 @@
 // Operands are bf16 token-major (n*S, H*dk) matrices made once per layer by rope_pack_kernel from the f32
 // projections (RoPE applied to q and k on the way); dO is converted by the kernel that forms
 // D = rowsum(dO o O).  All kernels stage tiles with cp.async into padded shared memory and read fragments
-// with ldmatrix; K/V (forward, dQ) and Q/dO (dK/dV) tiles are double-buffered.  The backward is two
+// with ldmatrix; the forward double-buffers its K/V tiles, the backward kernels keep one tile in flight and run
+// two CTAs per SM.  The backward is two
 // kernels, one per output owner (key tiles own dK/dV, query tiles own dQ), so no atomics are needed; the
 // inverse rotation of dQ and dK happens in their epilogues, where a thread holds both halves of a pair.
 // Head dims 64 and 128.
@@ -433,8 +434,8 @@ __device__ __forceinline__ void store_rows(float (&acc)[DK / 16][4], float mul, 
 
 // dK, dV: grid (n*H, ceil(S/64)) over key tiles (late tiles, the short ones, last), 256 threads.  The key
 // tile's K and V stay in shared memory; Q and dO tiles of 64 queries stream through a double buffer.
-template <int DK>
-__global__ void __launch_bounds__(256)
+template <int DK, int NBUF>
+__global__ void __launch_bounds__(256, NBUF == 1 ? 2 : 1)
 attn_bwd_dkv_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v,
                     const bf16* __restrict__ dob, const float* __restrict__ lse, const float* __restrict__ delta,
                     const float* __restrict__ rope_cos, const float* __restrict__ rope_sin, const SeqMap map, size_t rows, int H,
@@ -445,12 +446,12 @@ attn_bwd_dkv_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, cons
     extern __shared__ __align__(16) unsigned char smraw[];
     bf16* Ks = reinterpret_cast<bf16*>(smraw);
     bf16* Vs = Ks + 64 * LD;
-    bf16* Qs = Vs + 64 * LD;        // [2][64*LD]
-    bf16* Gs = Qs + 2 * 64 * LD;    // [2][64*LD]  dO
-    bf16* Ps = Gs + 2 * 64 * LD;    // [q][key]
-    bf16* Ds = Ps + 64 * LP;        // dS [q][key]
-    float* Ls = reinterpret_cast<float*>(Ds + 64 * LP);  // [2][64]
-    float* Dl = Ls + 128;                                // [2][64]
+    bf16* Qs = Vs + 64 * LD;           // [NBUF][64*LD]
+    bf16* Gs = Qs + NBUF * 64 * LD;    // [NBUF][64*LD]  dO
+    bf16* Ps = Gs + NBUF * 64 * LD;    // [q][key]
+    bf16* Ds = Ps + 64 * LP;           // dS [q][key]
+    float* Ls = reinterpret_cast<float*>(Ds + 64 * LP);  // [NBUF][64]
+    float* Dl = Ls + NBUF * 64;                          // [NBUF][64]
     const int bh = blockIdx.x, b = bh / H, h = bh % H;
     const int d = H * DK;
     const int k0 = blockIdx.y * 64;
@@ -484,10 +485,12 @@ attn_bwd_dkv_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, cons
 #pragma unroll
         for (int j = 0; j < 4; ++j) adk[i][j] = adv[i][j] = 0.0f;
 
+    // NBUF == 2: the next Q / dO tile streams in while this one is used, one CTA per SM.  NBUF == 1: one tile in
+    // flight per CTA, two CTAs per SM, each covering the other's load.
     const int n_it = (S - q_start + 63) / 64;
     for (int it = 0; it < n_it; ++it) {
-        const int i0 = q_start + it * 64, buf = it & 1;
-        if (it + 1 < n_it) {
+        const int i0 = q_start + it * 64, buf = NBUF == 2 ? (it & 1) : 0;
+        if (NBUF == 2 && it + 1 < n_it) {
             load_q(i0 + 64, buf ^ 1);
             cp_commit();
             cp_wait<1>();
@@ -519,6 +522,10 @@ attn_bwd_dkv_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, cons
             }
         }
         __syncthreads();
+        if (NBUF == 1 && it + 1 < n_it) {
+            load_q(i0 + 64, 0);
+            cp_commit();
+        }
     }
     const int row_a = k0 + wr * 16 + g;
     if (prefix_tile) {
@@ -552,8 +559,8 @@ __global__ void prefix_sum_kernel(const float* __restrict__ part, const SeqMap m
 
 // dQ: grid (n*H, ceil(S/64)) over query tiles (late tiles first), 256 threads.  Q and dO of the tile stay
 // in shared memory; K and V tiles of 64 keys stream through a double buffer.
-template <int DK>
-__global__ void __launch_bounds__(256)
+template <int DK, int NBUF>
+__global__ void __launch_bounds__(256, NBUF == 1 ? 2 : 1)
 attn_bwd_dq_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v,
                    const bf16* __restrict__ dob, const float* __restrict__ lse, const float* __restrict__ delta,
                    const float* __restrict__ rope_cos, const float* __restrict__ rope_sin, const SeqMap map, size_t rows, int H,
@@ -564,9 +571,9 @@ attn_bwd_dq_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const
     extern __shared__ __align__(16) unsigned char smraw[];
     bf16* Qs = reinterpret_cast<bf16*>(smraw);
     bf16* Gs = Qs + 64 * LD;
-    bf16* Ks = Gs + 64 * LD;        // [2][64*LD]
-    bf16* Vs = Ks + 2 * 64 * LD;    // [2][64*LD]
-    bf16* Ds = Vs + 2 * 64 * LD;    // dS [q][key]
+    bf16* Ks = Gs + 64 * LD;           // [NBUF][64*LD]
+    bf16* Vs = Ks + NBUF * 64 * LD;    // [NBUF][64*LD]
+    bf16* Ds = Vs + NBUF * 64 * LD;    // dS [q][key]
     float* Ls = reinterpret_cast<float*>(Ds + 64 * LP);
     float* Dl = Ls + 64;
     const int bh = blockIdx.x, b = bh / H, h = bh % H;
@@ -597,8 +604,8 @@ attn_bwd_dq_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const
 
     const int n_it = min(i0 + 63, S - 1) / 64 + 1;
     for (int it = 0; it < n_it; ++it) {
-        const int k0 = it * 64, buf = it & 1;
-        if (it + 1 < n_it) {
+        const int k0 = it * 64, buf = NBUF == 2 ? (it & 1) : 0;
+        if (NBUF == 2 && it + 1 < n_it) {
             stage<DK, LD, 64, 256>(k, base, k0 + 64, S, d, col0, Ks + (buf ^ 1) * 64 * LD);
             stage<DK, LD, 64, 256>(v, base, k0 + 64, S, d, col0, Vs + (buf ^ 1) * 64 * LD);
             cp_commit();
@@ -627,6 +634,11 @@ attn_bwd_dq_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const
             }
         }
         __syncthreads();
+        if (NBUF == 1 && it + 1 < n_it) {
+            stage<DK, LD, 64, 256>(k, base, k0 + 64, S, d, col0, Ks);
+            stage<DK, LD, 64, 256>(v, base, k0 + 64, S, d, col0, Vs);
+            cp_commit();
+        }
     }
     store_rows<DK>(acc, scale, rope_cos, rope_sin, i0 + wr * 16 + g, first_row, S, base, d, col0, wc, dq);
 }
@@ -708,26 +720,30 @@ nnb_status launch_attn_bwd_b16(nnb_engine* e, const __nv_bfloat16* q, const __nv
     delta_pack_kernel<<<(unsigned)ceil_div(rows * H, 8), 256, 0, e->stream>>>(dout, out, (int)S, (int)H, (int)dk, rows,
                                                                              grouped ? 1 : 0, delta, dob);
     dim3 grid((unsigned)(n_seq * H), (unsigned)ceil_div(S, 64));
-    const size_t smem_kv = 6 * 64 * (dk + 8) * 2 + 2 * 64 * 72 * 2 + 256 * 4;
-    const size_t smem_q = 6 * 64 * (dk + 8) * 2 + 64 * 72 * 2 + 128 * 4;
+    // One buffer per streamed tile and two CTAs per SM, each covering the other's loads: measured 776 us against
+    // 1051 us for double-buffered tiles with one CTA per SM (16 x 640 x 16 heads x 128, pack and delta included).
+    constexpr int NBUF = 1;
+    auto smem_kv_of = [](size_t dkv) { return (2 + 2 * NBUF) * 64 * (dkv + 8) * 2 + 2 * 64 * 72 * 2 + 2 * NBUF * 64 * 4; };
+    auto smem_q_of = [](size_t dkv) { return (2 + 2 * NBUF) * 64 * (dkv + 8) * 2 + 64 * 72 * 2 + 128 * 4; };
+    const size_t smem_kv = smem_kv_of(dk), smem_q = smem_q_of(dk);
     static bool cfg = false;
     if (!cfg) {
-        NNB_TRY(set_smem(attn_bwd_dkv_kernel<128>, 6 * 64 * 136 * 2 + 2 * 64 * 72 * 2 + 256 * 4));
-        NNB_TRY(set_smem(attn_bwd_dkv_kernel<64>, 6 * 64 * 72 * 2 + 2 * 64 * 72 * 2 + 256 * 4));
-        NNB_TRY(set_smem(attn_bwd_dq_kernel<128>, 6 * 64 * 136 * 2 + 64 * 72 * 2 + 128 * 4));
-        NNB_TRY(set_smem(attn_bwd_dq_kernel<64>, 6 * 64 * 72 * 2 + 64 * 72 * 2 + 128 * 4));
+        NNB_TRY(set_smem(attn_bwd_dkv_kernel<128, NBUF>, smem_kv_of(128)));
+        NNB_TRY(set_smem(attn_bwd_dkv_kernel<64, NBUF>, smem_kv_of(64)));
+        NNB_TRY(set_smem(attn_bwd_dq_kernel<128, NBUF>, smem_q_of(128)));
+        NNB_TRY(set_smem(attn_bwd_dq_kernel<64, NBUF>, smem_q_of(64)));
         cfg = true;
     }
     if (dk == 128) {
-        attn_bwd_dkv_kernel<128><<<grid, 256, smem_kv, e->stream>>>(q, k, v, dob, lse, delta, rope_cos, rope_sin, m, rows, (int)H,
-                                                                    scale, dkk, dvv, part);
-        attn_bwd_dq_kernel<128><<<grid, 256, smem_q, e->stream>>>(q, k, v, dob, lse, delta, rope_cos, rope_sin, m, rows, (int)H,
-                                                                  scale, dq);
+        attn_bwd_dkv_kernel<128, NBUF><<<grid, 256, smem_kv, e->stream>>>(q, k, v, dob, lse, delta, rope_cos, rope_sin, m, rows, (int)H,
+                                                                          scale, dkk, dvv, part);
+        attn_bwd_dq_kernel<128, NBUF><<<grid, 256, smem_q, e->stream>>>(q, k, v, dob, lse, delta, rope_cos, rope_sin, m, rows, (int)H,
+                                                                        scale, dq);
     } else {
-        attn_bwd_dkv_kernel<64><<<grid, 256, smem_kv, e->stream>>>(q, k, v, dob, lse, delta, rope_cos, rope_sin, m, rows, (int)H,
-                                                                   scale, dkk, dvv, part);
-        attn_bwd_dq_kernel<64><<<grid, 256, smem_q, e->stream>>>(q, k, v, dob, lse, delta, rope_cos, rope_sin, m, rows, (int)H,
-                                                                 scale, dq);
+        attn_bwd_dkv_kernel<64, NBUF><<<grid, 256, smem_kv, e->stream>>>(q, k, v, dob, lse, delta, rope_cos, rope_sin, m, rows, (int)H,
+                                                                         scale, dkk, dvv, part);
+        attn_bwd_dq_kernel<64, NBUF><<<grid, 256, smem_q, e->stream>>>(q, k, v, dob, lse, delta, rope_cos, rope_sin, m, rows, (int)H,
+                                                                       scale, dq);
     }
     e->launches += 3;
     if (grouped) {
