@@ -811,8 +811,8 @@ attn_prefix_kernel(const float* __restrict__ qkv, const __nv_bfloat16* __restric
 // barriers inside the attention part.  grid = B, block = 32*H (H <= 32).  A warp streams its head's keys
 // and values with 16-byte loads, U keys in flight per lane group; with ~55 resident warps per SM that
 // keeps > 100 KB of cache reads outstanding per SM.  att (B, d) f32 is optional.
-template <int DK>
-__global__ void __launch_bounds__(1024)
+template <int DK, int U, int MAXT>
+__global__ void __launch_bounds__(MAXT)
 attn_decode_fused_kernel(const float* __restrict__ qkv, __nv_bfloat16* __restrict__ kcache, __nv_bfloat16* __restrict__ vcache,
                          int own_alloc, const __nv_bfloat16* __restrict__ kpre, const __nv_bfloat16* __restrict__ vpre,
                          int pre_len, int pre_alloc, int group, const float* __restrict__ rope_cos,
@@ -822,7 +822,8 @@ attn_decode_fused_kernel(const float* __restrict__ qkv, __nv_bfloat16* __restric
 {
     constexpr int LPK = DK / 8;    // lanes per key
     constexpr int KPW = 32 / LPK;  // keys per warp-wide load
-    constexpr int U = 4;           // keys in flight per lane group
+    // U = keys in flight per lane group: 4 when two 512-thread CTAs share an SM (64 registers per thread), 8 for
+    // batches of about one CTA per SM, where the loads of a single CTA have to cover the memory latency
     constexpr int half = DK / 2;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     float* orow = reinterpret_cast<float*>(smem_raw);  // d
@@ -1068,9 +1069,13 @@ nnb_status launch_attn_decode_fused(nnb_engine* e, const float* qkv, void* kcach
     const size_t smem = (H * dk + H * ctx_pad) * sizeof(float);
     NNB_REQUIRE(smem <= 200 * 1024, "attn_decode_fused: context %zu too long for one CTA", pre_len + own_alloc);
     const float scale = 1.0f / sqrtf((float)dk);
+    // few sequences (about one CTA per SM or less) and at most 16 heads: the variant with more loads in flight
+    const bool deep = H <= 16 && B <= (size_t)e->sm_count * 3 / 2;
 #define NNB_FUSED(DKV)                                                                                                    \
+    if (deep) NNB_FUSED_V(DKV, 8, 512) else NNB_FUSED_V(DKV, 4, 1024)
+#define NNB_FUSED_V(DKV, UV, MT)                                                                                          \
     {                                                                                                                     \
-        auto kern = attn_decode_fused_kernel<DKV>;                                                                        \
+        auto kern = attn_decode_fused_kernel<DKV, UV, MT>;                                                                \
         static size_t cfg = 0;                                                                                            \
         if (smem > cfg) {                                                                                                 \
             NNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                 \
@@ -1083,6 +1088,7 @@ nnb_status launch_attn_decode_fused(nnb_engine* e, const float* qkv, void* kcach
     }
     if (dk == 128) NNB_FUSED(128) else NNB_FUSED(64)
 #undef NNB_FUSED
+#undef NNB_FUSED_V
     e->launches++;
     NNB_CHECK_LAUNCH("attn_decode_fused_kernel");
     return NNB_OK;

@@ -307,7 +307,11 @@ static nnb_status decode_step(nnb_policy* p, const StepView& sv, bool with_head,
         // projection after it are launched the plain way: each starts on a drained GPU.
         const bool pdl_saved = e->pdl;
         e->pdl = false;
-        if (!exact && attn_decode_fused_supported(H, dk) && d % 64 == 0) {
+        // One CTA per sequence needs a few hundred sequences to fill the GPU.  Below about one wave of per-head CTAs
+        // (16 resident per SM) the kernel with one CTA per (sequence, head), four warps splitting the keys, has
+        // several times the loads in flight and wins, the separate quantisation launch included.
+        const bool few = B * H <= (size_t)e->sm_count * 16;
+        if (!exact && !few && attn_decode_fused_supported(H, dk) && d % 64 == 0) {
             // all heads of a sequence in one CTA, attention output quantised in the same launch
             NNB_TRY(launch_attn_decode_fused(e, w.qkv, kl, vl, sv.own_alloc, kpl, vpl, sv.pre_len, sv.pre_alloc, sv.group,
                                              c.pos == 1 ? p->rope_cos : nullptr, c.pos == 1 ? p->rope_sin : nullptr, w.d_pos, B, H,
