@@ -136,6 +136,22 @@ rope_pack_kernel(const float* __restrict__ q, const float* __restrict__ k, const
     }
 }
 
+// token-major bf16 keys / values (n*S, H*dk) -> decode cache layout (n, H, alloc, dk); one CTA per row
+__global__ void __launch_bounds__(256)
+kv_to_cache_kernel(const bf16* __restrict__ k, const bf16* __restrict__ v, int S, int H, int dk, int alloc,
+                   bf16* __restrict__ kc, bf16* __restrict__ vc)
+{
+    const size_t row = blockIdx.x;
+    const int b = (int)(row / S), pos = (int)(row % S);
+    const int d = H * dk;
+    for (int c = threadIdx.x * 8; c < d; c += 256 * 8) {
+        const int h = c / dk, cc = c % dk;
+        const size_t dst = (((size_t)b * H + h) * alloc + pos) * dk + cc;
+        *reinterpret_cast<uint4*>(kc + dst) = *reinterpret_cast<const uint4*>(k + row * d + c);
+        *reinterpret_cast<uint4*>(vc + dst) = *reinterpret_cast<const uint4*>(v + row * d + c);
+    }
+}
+
 // ------------------------------------------------------------------ forward
 // grid (n*H, ceil(S/128)), 128 threads: warp w owns query rows 32w..32w+31 of the tile (two m16 blocks);
 // key tiles of 64 rows, double-buffered.  Late query tiles (the long ones under the causal mask) are
@@ -663,6 +679,16 @@ nnb_status launch_rope_pack_b16(nnb_engine* e, const float* q, const float* k, c
     ab::rope_pack_kernel<<<(unsigned)T, 256, 0, e->stream>>>(q, k, v, rope_cos, rope_sin, row_pos, (int)S, (int)H, (int)dk, T, out);
     e->launches++;
     NNB_CHECK_LAUNCH("rope_pack_kernel");
+    return NNB_OK;
+}
+
+nnb_status launch_kv_to_cache(nnb_engine* e, const __nv_bfloat16* k, const __nv_bfloat16* v, size_t n_seq, size_t S, size_t H,
+                              size_t dk, __nv_bfloat16* kc, __nv_bfloat16* vc, size_t alloc)
+{
+    NNB_REQUIRE(dk % 8 == 0 && S <= alloc, "kv_to_cache: bad shape");
+    ab::kv_to_cache_kernel<<<(unsigned)(n_seq * S), 256, 0, e->stream>>>(k, v, (int)S, (int)H, (int)dk, (int)alloc, kc, vc);
+    e->launches++;
+    NNB_CHECK_LAUNCH("kv_to_cache_kernel");
     return NNB_OK;
 }
 

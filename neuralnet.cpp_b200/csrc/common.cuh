@@ -265,6 +265,8 @@ bool attn_b16_supported(size_t dk, size_t d);
 nnb_status launch_rope_pack_b16(nnb_engine* e, const float* q, const float* k, const float* v, const float* rope_cos,
                                 const float* rope_sin, size_t T, size_t S, size_t H, size_t dk, __nv_bfloat16* out,
                                 const int* row_pos = nullptr);
+nnb_status launch_kv_to_cache(nnb_engine* e, const __nv_bfloat16* k, const __nv_bfloat16* v, size_t n_seq, size_t S, size_t H,
+                              size_t dk, __nv_bfloat16* kc, __nv_bfloat16* vc, size_t alloc);
 nnb_status launch_attn_fwd_b16(nnb_engine* e, const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v,
                                size_t n_seq, size_t S, size_t H, size_t dk, float* out, float* lse, const SeqMap* map = nullptr);
 // with a grouped map, part (2 * n_seq * P * H*dk floats) receives every member's share of the prefix rows'

@@ -426,7 +426,15 @@ nnb_status policy_rollout(nnb_policy* p, const int32_t* d_prompts, size_t B, siz
                                        cudaMemcpyDeviceToDevice, e->stream));
         NNB_TRY(launch_set_int(e, w.d_pos, 0));
         const bool allow_graph = total >= 8;
-        for (size_t t = 0; t + 1 < total; ++t) {
+        size_t t0 = 0;
+        if (pre_len > 0 && policy_can_prefill(p)) {
+            // fast mode: the shared prompt prefixes go through one teacher-forced forward (all positions at once)
+            // that leaves every layer's keys and values in the prefix cache, instead of pre_len decode steps
+            NNB_TRY(policy_prefill_prefix(p, w.tokens_pre, Bg, pre_len, w.k_pre, w.v_pre, pre_len, Bg * d * pre_len * kv_elem));
+            NNB_TRY(launch_set_int(e, w.d_pos, (int)pre_len));
+            t0 = pre_len;
+        }
+        for (size_t t = t0; t + 1 < total; ++t) {
             if (t < pre_len) {
                 NNB_TRY(run_step(p, graphs[0], allow_graph, pre_view, false, temperature, top_k, seed, seq0, (int)P, false));
                 continue;

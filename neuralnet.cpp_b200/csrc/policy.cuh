@@ -62,12 +62,18 @@ struct nnb_policy {
     nnb::LinW head;
     std::vector<nnb::TensorInfo> tensors;
     nnb::DecodeWs dec;
-    void* train = nullptr;  // training workspace (train.cu)
+    void* train = nullptr;    // workspace of the teacher-forced passes (policy_train.cu)
+    void* prefill = nullptr;  // a second one, for the batched prompt prefill of the rollout
 };
 
 namespace nnb {
 nnb_status policy_requantize(nnb_policy* p);
 void policy_free_train(nnb_policy* p);
+// Fast mode: run the teacher-forced forward over n_seq prompts of L tokens and store every layer's rotated keys
+// and values as the (layer, n_seq, head, alloc, dk) bf16 prefix cache of a rollout, instead of L decode steps.
+bool policy_can_prefill(const nnb_policy* p);
+nnb_status policy_prefill_prefix(nnb_policy* p, const int32_t* d_tokens, size_t n_seq, size_t L, void* k_pre, void* v_pre,
+                                 size_t alloc, size_t layer_bytes);
 void policy_free_decode(nnb_policy* p);
 nnb_status policy_ensure_wb(nnb_policy* p);
 // y = [residual +] linear(q) through the fastest kernel for this mode and token count

@@ -9,6 +9,7 @@
 //
 // Decisions: sequence b of length S with a prompt of P tokens has G = S - P decisions; decision g
 // is taken at position P-1+g and its action is token P+g.  All per-decision vectors are (n_seq, G).
+#include <utility>
 #include <vector>
 
 #include "common.cuh"
@@ -31,6 +32,7 @@ struct TrainWs {
     int32_t *row_tok = nullptr, *row_pos = nullptr;  // token and position of every row
     float* part = nullptr;                           // per-member share of the prefix rows' dK, dV (grouped backward)
     bool saved_layers = false;
+    bool with_head = true;  // false: layers only (prompt prefill), no decision / logits buffers
     char* arena = nullptr;
     size_t arena_bytes = 0;
     std::vector<LayerSave> L;
@@ -50,16 +52,23 @@ struct TrainWs {
     bool b16_attn = false;
 };
 
-void policy_free_train(nnb_policy* p)
+static void free_ws(void*& slot)
 {
-    TrainWs* w = (TrainWs*)p->train;
+    TrainWs* w = (TrainWs*)slot;
     if (!w) return;
     if (w->arena) cudaFree(w->arena);
     delete w;
-    p->train = nullptr;
+    slot = nullptr;
 }
 
-static nnb_status ensure_train(nnb_policy* p, size_t n_seq, size_t S, size_t P, bool save_layers, size_t group)
+void policy_free_train(nnb_policy* p)
+{
+    free_ws(p->train);
+    free_ws(p->prefill);
+}
+
+static nnb_status ensure_train(nnb_policy* p, size_t n_seq, size_t S, size_t P, bool save_layers, size_t group,
+                               bool with_head = true)
 {
     TrainWs* w = (TrainWs*)p->train;
     {
@@ -70,15 +79,17 @@ static nnb_status ensure_train(nnb_policy* p, size_t n_seq, size_t S, size_t P, 
                          n_seq % group == 0;
         if (!can) group = 1;
     }
-    if (w && w->n_seq == n_seq && w->S == S && w->P == P && (size_t)w->map.group == group && (w->saved_layers || !save_layers))
+    if (w && w->n_seq == n_seq && w->S == S && w->P == P && (size_t)w->map.group == group && w->with_head == with_head &&
+        (w->saved_layers || !save_layers))
         return NNB_OK;
     NNB_CUDA(cudaStreamSynchronize(p->e->stream));
-    policy_free_train(p);
+    free_ws(p->train);
     w = new TrainWs();
     p->train = w;
     const nnb_gpt_config& c = p->cfg;
     const size_t d = c.d_model, F = c.d_ff, F1 = c.act == 1 ? 2 * F : F, V = c.vocab, H = c.n_head;
-    const size_t G = S - P, Td = n_seq * G;
+    const size_t G = S - P, Td = with_head ? n_seq * G : 0;
+    w->with_head = with_head;
     w->map = SeqMap{(int)S, (int)P, (int)G, (int)group};
     w->rows = map_rows_total(w->map, n_seq);
     const size_t T = w->rows;
@@ -160,14 +171,14 @@ static nnb_status ensure_train(nnb_policy* p, size_t n_seq, size_t S, size_t P, 
             size_t free_b = 0, total_b = 0;
             NNB_CUDA(cudaMemGetInfo(&free_b, &total_b));
             if (off + (256u << 20) > free_b) {
-                policy_free_train(p);
+                free_ws(p->train);
                 NNB_FAIL(NNB_ERR_OOM, "training workspace for %zu sequences x %zu needs %.1f GB, %.1f GB free: use smaller micro-batches",
                          n_seq, S, off / 1e9, free_b / 1e9);
             }
             cudaError_t er = cudaMalloc((void**)&w->arena, off);
             if (er != cudaSuccess) {
                 cudaGetLastError();
-                policy_free_train(p);
+                free_ws(p->train);
                 NNB_FAIL(NNB_ERR_OOM, "cudaMalloc(%zu) for the training workspace failed: %s", off, cudaGetErrorString(er));
             }
             w->arena_bytes = off;
@@ -195,8 +206,15 @@ static nnb_status lin_fwd(nnb_policy* p, const LinW& l, size_t n_mats, const int
     return policy_linear_fwd(p, l, n_mats, q, s, qsum, T, residual, y, y_stride);
 }
 
+// where the prompt prefill stores every layer's keys and values
+struct KvSink {
+    void *k, *v;
+    size_t alloc, layer_bytes;
+};
+
 // teacher-forced forward of n_seq sequences; fills w->logp / w->ent / w->value for the decisions
-static nnb_status forward(nnb_policy* p, const int32_t* tokens, size_t n_seq, size_t S, size_t P, bool want_entropy)
+static nnb_status forward(nnb_policy* p, const int32_t* tokens, size_t n_seq, size_t S, size_t P, bool want_entropy,
+                          const KvSink* sink = nullptr)
 {
     nnb_engine* e = p->e;
     const nnb_gpt_config& c = p->cfg;
@@ -220,6 +238,10 @@ static nnb_status forward(nnb_policy* p, const int32_t* tokens, size_t n_seq, si
         if (w->b16_attn) {
             NNB_TRY(launch_rope_pack_b16(e, s.qkv, s.qkv + T * d, s.qkv + 2 * T * d, c.pos == 1 ? p->rope_cos : nullptr,
                                          c.pos == 1 ? p->rope_sin : nullptr, T, S, H, dk, s.qkvb, w->row_pos));
+            if (sink)
+                NNB_TRY(launch_kv_to_cache(e, s.qkvb + T * d, s.qkvb + 2 * T * d, n_seq, S, H, dk,
+                                           (__nv_bfloat16*)((char*)sink->k + (size_t)l * sink->layer_bytes),
+                                           (__nv_bfloat16*)((char*)sink->v + (size_t)l * sink->layer_bytes), sink->alloc));
             NNB_TRY(launch_attn_fwd_b16(e, s.qkvb, s.qkvb + T * d, s.qkvb + 2 * T * d, n_seq, S, H, dk, s.att, s.lse, &w->map));
         } else {
             if (c.pos == 1) {
@@ -235,6 +257,7 @@ static nnb_status forward(nnb_policy* p, const int32_t* tokens, size_t n_seq, si
         NNB_TRY(launch_row_quant(e, c.act == 1 ? 2 : 1, exact, s.h1, nullptr, T, F, F1, s.q4, s.s4, w->qsum, nullptr));
         NNB_TRY(lin_fwd(p, LW.fc2, 1, s.q4, s.s4, w->qsum, T, s.x_mid, x_out, 0));
     }
+    if (!w->with_head) return NNB_OK;
     const float* x_final = w->x_last;
     if (!w->saved_layers) x_final = (c.n_layer % 2 == 1) ? w->x_last : w->L[0].x_in;
     if (grouped) NNB_TRY(launch_gather_decisions_map(e, x_final, w->map, n_seq, d, w->xd));
@@ -346,6 +369,30 @@ static nnb_status backward(nnb_policy* p, const int32_t* tokens, size_t n_seq, s
     }
     return launch_embed_rows_bwd(e, w->g, w->row_tok, w->row_pos, T, d, V, GG + p->tok_emb, c.pos == 0 ? GG + p->pos_emb : nullptr);
 }
+
+}  // namespace nnb
+
+bool nnb::policy_can_prefill(const nnb_policy* p)
+{
+    return !p->cfg.exact && attn_b16_supported((size_t)p->cfg.d_model / p->cfg.n_head, (size_t)p->cfg.d_model);
+}
+
+nnb_status nnb::policy_prefill_prefix(nnb_policy* p, const int32_t* d_tokens, size_t n_seq, size_t L, void* k_pre, void* v_pre,
+                                      size_t alloc, size_t layer_bytes)
+{
+    NNB_REQUIRE(policy_can_prefill(p) && n_seq > 0 && L > 0 && L <= alloc, "prefill: unsupported configuration");
+    // the prefill keeps a workspace of its own, so that the training workspace survives a rollout
+    std::swap(p->train, p->prefill);
+    nnb_status st = ensure_train(p, n_seq, L, 0, false, 1, /*with_head=*/false);
+    if (st == NNB_OK) {
+        const KvSink sink{k_pre, v_pre, alloc, layer_bytes};
+        st = forward(p, d_tokens, n_seq, L, 0, false, &sink);
+    }
+    std::swap(p->train, p->prefill);
+    return st;
+}
+
+namespace nnb {
 
 static nnb_status check_shape(nnb_policy* p, const int32_t* tokens, size_t n_seq, size_t S, size_t P)
 {
