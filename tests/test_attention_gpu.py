@@ -88,7 +88,7 @@ def _bf16_round(a):
 
 
 @pytest.mark.parametrize("n,H,dk,pos,pre_len,group", [(4, 4, 64, 17, 0, 1), (3, 16, 128, 40, 0, 1), (4, 2, 128, 21, 8, 2),
-                                                      (6, 3, 64, 9, 9, 3), (2, 2, 32, 5, 0, 1)])
+                                                      (6, 3, 64, 9, 9, 3), (2, 2, 32, 5, 0, 1), (2, 32, 100, 30, 0, 1)])
 def test_attention_decode_step(eng, n, H, dk, pos, pre_len, group):
     """One new token against the cache: rotation, append, attention over prefix + own positions; the exact path
     against float64, the bf16 paths (per-head kernel and all-heads kernel with the fused int8 output) within
