@@ -703,21 +703,42 @@ act_bwd_scale_colsum_kernel(const float* __restrict__ h, const float* __restrict
     }
 }
 
-// xs[t,k] = bf16(s[t] * q[t, perm(k)]) in natural feature order
-__global__ void dequant_to_bf16_kernel(const int8_t* __restrict__ q, const float* __restrict__ s, size_t T, int K,
-                                       __nv_bfloat16* __restrict__ out)
+// xs[t,k] = bf16(s[t] * q[t, perm(k)]) in natural feature order.  One thread per 64-feature block: it reads
+// the block's 64 permuted bytes with four 16-byte loads and writes 128 contiguous bytes of bf16, so that
+// both sides of the kernel move 16 bytes per lane.  Source feature j of a block sits at byte
+// 16*(j%4) + 4*(j/16) + (j/4)%4 (the layout act_quant writes).
+__global__ void __launch_bounds__(256)
+dequant_to_bf16_kernel(const int8_t* __restrict__ q, const float* __restrict__ s, size_t T, int K,
+                       __nv_bfloat16* __restrict__ out)
 {
-    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // one 32-bit word of q
-    if (idx >= T * (size_t)(K / 4)) return;
-    const size_t t = idx / (K / 4);
-    const int w = (int)(idx % (K / 4));
-    const int blk = w >> 4, wd = w & 15, i = wd >> 2, tt = wd & 3;  // dest word 4i+tt holds src 16tt + 4b + i
-    const uint32_t word = reinterpret_cast<const uint32_t*>(q + t * K)[w];
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // one 64-byte block of q
+    const int bpr = K / 64;
+    if (idx >= T * (size_t)bpr) return;
+    const size_t t = idx / bpr;
     const float sc = s[t];
+    const uint4* src = reinterpret_cast<const uint4*>(q) + idx * 4;
+    uint32_t w[16];
 #pragma unroll
-    for (int b = 0; b < 4; ++b) {
-        const float v = (float)(int8_t)((word >> (8 * b)) & 0xFFu) * sc;
-        out[t * K + blk * 64 + 16 * tt + 4 * b + i] = __float2bfloat16_rn(v);
+    for (int i = 0; i < 4; ++i) {
+        const uint4 v = src[i];
+        w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+    }
+    uint4* dst = reinterpret_cast<uint4*>(out) + idx * 8;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {  // output chunk c: features 8c .. 8c+7
+        float f[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const int j = 8 * c + e;
+            const int byte = 16 * (j % 4) + 4 * (j / 16) + (j / 4) % 4;
+            f[e] = (float)(int8_t)((w[byte >> 2] >> (8 * (byte & 3))) & 0xFFu) * sc;
+        }
+        uint4 o;
+        __nv_bfloat162 p0 = __floats2bfloat162_rn(f[0], f[1]), p1 = __floats2bfloat162_rn(f[2], f[3]);
+        __nv_bfloat162 p2 = __floats2bfloat162_rn(f[4], f[5]), p3 = __floats2bfloat162_rn(f[6], f[7]);
+        o.x = *reinterpret_cast<uint32_t*>(&p0); o.y = *reinterpret_cast<uint32_t*>(&p1);
+        o.z = *reinterpret_cast<uint32_t*>(&p2); o.w = *reinterpret_cast<uint32_t*>(&p3);
+        dst[c] = o;
     }
 }
 
@@ -762,7 +783,8 @@ nnb_status launch_scale_colsum(nnb_engine* e, const float* dy, const float* tau,
 
 nnb_status launch_dequant_to_bf16(nnb_engine* e, const int8_t* q, const float* s, size_t t, size_t k, __nv_bfloat16* xs)
 {
-    dequant_to_bf16_kernel<<<(unsigned)ceil_div(t * (k / 4), 256), 256, 0, e->stream>>>(q, s, t, (int)k, xs);
+    NNB_REQUIRE(k % 64 == 0 && (((uintptr_t)q | (uintptr_t)xs) & 15) == 0, "dequant_to_bf16: k=%zu must be a multiple of 64, operands 16-byte aligned", k);
+    dequant_to_bf16_kernel<<<(unsigned)ceil_div(t * (k / 64), 256), 256, 0, e->stream>>>(q, s, t, (int)k, xs);
     e->launches++;
     NNB_CHECK_LAUNCH("dequant_to_bf16_kernel");
     return NNB_OK;
