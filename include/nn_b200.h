@@ -299,6 +299,14 @@ nnb_status nnb_policy_logprobs_grouped(nnb_policy* p, const int32_t* d_tokens, s
                                        size_t group, float* d_logp, float* d_entropy, float* d_value);
 nnb_status nnb_policy_train_step_grouped(nnb_policy* p, const int32_t* d_tokens, size_t n_seq, size_t seq_len,
                                          size_t prompt_len, size_t group, const nnb_objective* obj, float* d_report);
+/* Supervised step on the same machinery: sparse cross-entropy of the next token
+ * (CrossEntropyLoss::fused_forward_sparse_, include/neuralnet.cpp/compute_loss.hpp:315-429): with the
+ * decisions and actions defined above (prompt_len = 1 covers every position of a sequence),
+ * loss = -sum mask * log softmax(logits)[label] / units, units <= 0 meaning the sum of the mask (the
+ * reference's num_valid); gradients are ADDED to the gradient buffer.  d_report[10] as in
+ * nnb_policy_train_step with the loss in d_report[0] and the units in d_report[7].  group as above. */
+nnb_status nnb_policy_sft_step(nnb_policy* p, const int32_t* d_tokens, size_t n_seq, size_t seq_len, size_t prompt_len,
+                               size_t group, const float* d_mask, float units, float* d_report);
 /* flat f32 gradient buffer, same layout as the parameters (allocated and zeroed on first use) */
 float* nnb_policy_grads(nnb_policy* p);
 nnb_status nnb_policy_zero_grad(nnb_policy* p);

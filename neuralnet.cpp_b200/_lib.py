@@ -74,6 +74,7 @@ _SIGNATURES = {
     "nnb_rollout": (_I, [_P, _P, _SZ, _SZ, _SZ, C.c_float, _I, C.c_uint64, C.c_uint32, _P, _P, _P]),
     "nnb_policy_logprobs": (_I, [_P, _P, _SZ, _SZ, _SZ, _P, _P, _P]),
     "nnb_policy_train_step": (_I, [_P, _P, _SZ, _SZ, _SZ, _P, _P]),
+    "nnb_policy_sft_step": (_I, [_P, _P, _SZ, _SZ, _SZ, _SZ, _P, C.c_float, _P]),
     "nnb_policy_logprobs_grouped": (_I, [_P, _P, _SZ, _SZ, _SZ, _SZ, _P, _P, _P]),
     "nnb_policy_train_step_grouped": (_I, [_P, _P, _SZ, _SZ, _SZ, _SZ, _P, _P]),
     "nnb_policy_grads": (_P, [_P]),

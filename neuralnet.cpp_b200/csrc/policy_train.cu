@@ -497,6 +497,23 @@ nnb_status nnb_policy_train_step_grouped(nnb_policy* p, const int32_t* d_tokens,
     return NNB_OK;
 }
 
+nnb_status nnb_policy_sft_step(nnb_policy* p, const int32_t* d_tokens, size_t n_seq, size_t seq_len, size_t prompt_len,
+                               size_t group, const float* d_mask, float units, float* d_report)
+{
+    NNB_TRY(check_shape(p, d_tokens, n_seq, seq_len, prompt_len));
+    NNB_REQUIRE(d_mask, "sft_step: mask is NULL");
+    NNB_REQUIRE(group >= 1 && n_seq % group == 0, "sft_step: %zu sequences are not whole groups of %zu", n_seq, group);
+    // -sum mask * logp / units is the sampled-KL term against a reference log-prob of zero with coefficient -1
+    NNB_TRY(ensure_train(p, n_seq, seq_len, prompt_len, true, group));
+    TrainWs* w = (TrainWs*)p->train;
+    const size_t Td = n_seq * (seq_len - prompt_len);
+    NNB_CUDA(cudaMemsetAsync(w->dvalue, 0, Td * 4, p->e->stream));  // read by the objective before anything rewrites it
+    const nnb_objective obj{d_mask, nullptr, nullptr, w->dvalue, nullptr, nullptr, units, 0.0f, -1.0f, 0.0f, 0.0f, 0.0f};
+    NNB_TRY(nnb_policy_train_step_grouped(p, d_tokens, n_seq, seq_len, prompt_len, group, &obj, d_report));
+    if (d_report) NNB_CUDA(cudaMemcpyAsync(d_report, d_report + 4, 4, cudaMemcpyDeviceToDevice, p->e->stream));
+    return NNB_OK;
+}
+
 nnb_status nnb_policy_optimizer_step(nnb_policy* p, float lr, float beta1, float beta2, float eps, float weight_decay,
                                      float max_grad_norm, float* d_norm_out)
 {

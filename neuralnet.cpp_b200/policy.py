@@ -237,6 +237,15 @@ def train_step(self, tokens: torch.Tensor, prompt_len: int, mask, old_logp=None,
     return report
 
 
+def sft_step(self, tokens: torch.Tensor, prompt_len: int, mask, units=0.0, group_size=1):
+    """Sparse cross-entropy of the next token on one micro-batch; gradients accumulate.  Returns report[10]
+    (loss in [0], units in [7])."""
+    n, S = tokens.shape
+    report = torch.empty(10, device=self.engine.device, dtype=torch.float32)
+    check(self._lib.nnb_policy_sft_step(self._h, _ptr(tokens), n, S, prompt_len, group_size, _ptr(mask), units, _ptr(report)))
+    return report
+
+
 def optimizer_step(self, lr, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01, max_grad_norm=0.0):
     norm = torch.empty(1, device=self.engine.device, dtype=torch.float32)
     check(self._lib.nnb_policy_optimizer_step(self._h, lr, beta1, beta2, eps, weight_decay, max_grad_norm, _ptr(norm)))
@@ -247,5 +256,5 @@ def release_workspaces(self):
     check(self._lib.nnb_policy_release_workspaces(self._h))
 
 
-for _f in (logprobs, grads_view, zero_grad, train_step, optimizer_step, release_workspaces):
+for _f in (logprobs, grads_view, zero_grad, train_step, sft_step, optimizer_step, release_workspaces):
     setattr(Policy, _f.__name__, _f)

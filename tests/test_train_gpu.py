@@ -279,3 +279,24 @@ def test_grouped_batch_matches_one_copy_per_sequence(pkg, eng, d, heads, P, G, g
     if P == 64:
         t2 = tokens[:, 3:].contiguous()
         assert torch.equal(pa.logprobs(t2, P - 3)[0], pb.logprobs(t2, P - 3, group_size=group)[0])
+
+
+@pytest.mark.parametrize("act,pos", [(0, 0), (1, 1)])
+def test_sparse_cross_entropy_step(pkg, eng, act, pos):
+    """Supervised step: loss = -sum mask*logp / num_valid over next-token labels (the reference's sparse
+    cross-entropy, compute_loss.hpp:315-429) and its gradients, against the restatement."""
+    cfg, pol, tr, tokens, _ = _case(pkg, eng, act, pos, False)
+    n, S = tokens.shape
+    P = 1  # every position predicts its successor
+    rng = np.random.default_rng(11)
+    mask = (rng.random((n, S - P)) < 0.8).astype(np.float32)
+    lp_ref, ent_ref, _ = tr.forward(tokens, P)
+    loss_ref = -(lp_ref.reshape(n, -1).astype(np.float64) * mask).sum() / mask.sum()
+    rep_ref, up_lp, _, _ = tr.objective(lp_ref, ent_ref, mask, ref_logp=np.zeros_like(lp_ref), kl_coef=-1.0)
+    assert abs(rep_ref["kl_loss"] - loss_ref) <= 1e-9 * abs(loss_ref)
+    g_ref = tr.backward(up_lp)
+    pol.zero_grad()
+    rep = pol.sft_step(dev(tokens, eng, np.int32), P, dev(mask, eng)).cpu().numpy()
+    assert abs(rep[0] - loss_ref) <= REL * abs(loss_ref)
+    assert abs(rep[7] - mask.sum()) < 0.5
+    _grad_check(pol, tr, cfg, pol.grads_view().cpu().numpy().astype(np.float64), g_ref)
