@@ -45,3 +45,32 @@ def test_engine_create_fails_loudly_without_gpu(pkg):
     st = pkg.lib().nnb_engine_create(0, ctypes.byref(h))
     assert st != 0 and not h.value
     assert b"no CPU fallback" in pkg.lib().nnb_last_error() or b"CUDA" in pkg.lib().nnb_last_error()
+
+
+def _compile_client(tmp_path, pkg):
+    import subprocess
+
+    libdir = os.path.dirname(pkg.lib_path())
+    exe = str(tmp_path / "client")
+    src = os.path.join(ROOT, "tests", "cabi", "client.c")
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-pedantic", "-I", os.path.join(ROOT, "include"), src, "-o", exe,
+                    "-L", libdir, "-lnn-b200", f"-Wl,-rpath,{libdir}"], check=True)
+    return exe
+
+
+def test_header_is_plain_c_and_a_c_client_links(pkg, tmp_path):
+    """include/nn_b200.h compiles as C99 and as C++17, and a C program links against the library; without a GPU
+    it gets the library's error, not a fallback."""
+    import subprocess
+
+    import torch
+
+    inc = os.path.join(ROOT, "include")
+    for lang, std in (("c", "-std=c99"), ("c++", "-std=c++17")):
+        subprocess.run(["gcc", "-x", lang, std, "-Wall", "-Werror", "-pedantic", "-fsyntax-only", "-I", inc,
+                        os.path.join(inc, "nn_b200.h")], check=True)
+    exe = _compile_client(tmp_path, pkg)
+    if torch.cuda.is_available():
+        return
+    r = subprocess.run([exe], capture_output=True, text=True)
+    assert r.returncode == 3 and "engine:" in r.stderr

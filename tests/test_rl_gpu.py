@@ -183,3 +183,19 @@ def test_adamw_and_clip(eng, rl):
         assert np.array_equal(dp.cpu().numpy().view(np.uint32), p.view(np.uint32))  # elementwise: bit-exact
         assert np.array_equal(dm.cpu().numpy().view(np.uint32), m.view(np.uint32))
         assert np.array_equal(dv.cpu().numpy().view(np.uint32), v.view(np.uint32))
+
+
+def test_plain_c_client_runs(pkg, tmp_path):
+    """The C99 client of tests/cabi/ against the GPU: engine description and the reference's group-advantage
+    known answer ({1,2,3} -> {-1/s, 0, 1/s}, s = sqrt(2/3); a constant group -> zeros)."""
+    import subprocess
+
+    from test_abi_symbols import _compile_client
+
+    r = subprocess.run([_compile_client(tmp_path, pkg)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    lines = r.stdout.strip().splitlines()
+    assert "nn-b200 engine" in lines[0]
+    got = [float(x) for x in lines[1].split()]
+    s = (2.0 / 3.0) ** 0.5
+    assert np.allclose(got, [-1 / s, 0, 1 / s, 0, 0, 0], atol=1e-5)
