@@ -179,6 +179,21 @@ def test_operator_sweep_accumulators_bit_exact(eng, orc, t, k, out):
     assert np.array_equal(_u32(y), y_ref.view(np.uint32))
 
 
+@pytest.mark.parametrize("k,out", [(2048, 2048), (2048, 5632), (5632, 2048)])
+@pytest.mark.parametrize("t", [64, 256, 2048])
+def test_operator_sweep_on_the_tcgen05_path(eng, orc, t, k, out):
+    """Same sweep through the Blackwell tensor-core forward (used from 64 tokens up): Y bitwise."""
+    W, tau, X, _ = _case_tm(orc, t, k, out, seed=4, ternary_iid=True)
+    packed = orc.trit_pack(W, tau)
+    q_ref, s_ref = orc.act_quant_tm(X)
+    y_ref = orc.bitlinear_i8_tm(packed, tau, None, q_ref, s_ref, want_acc=False)
+    q, s, _ = eng.act_quant_tm(_dev(X, eng))
+    w8, _ = eng.expand_weights(_dev(packed.view(np.int32), eng), k, want_bf16=False)
+    y = eng.bitlinear_fwd_tc(w8, _dev(tau, eng), None, q, s)
+    eng.check_device_errors()
+    assert np.array_equal(_u32(y), y_ref.view(np.uint32))
+
+
 def test_stack_equals_single(eng, orc):
     rng = np.random.default_rng(7)
     n_mats, t, k, out = 5, 4, 256, 96

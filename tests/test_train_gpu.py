@@ -300,3 +300,33 @@ def test_sparse_cross_entropy_step(pkg, eng, act, pos):
     assert abs(rep[0] - loss_ref) <= REL * abs(loss_ref)
     assert abs(rep[7] - mask.sum()) < 0.5
     _grad_check(pol, tr, cfg, pol.grads_view().cpu().numpy().astype(np.float64), g_ref)
+
+
+def test_full_size_micro_batch_grouped_equals_plain(pkg, eng):
+    """The benchmark's micro-batch on the ~1B policy (24 layers, d 2048, 16 heads, SwiGLU 5632, vocab 32000;
+    16 completions of one 128-token prompt, 640 tokens each), fast mode: computing the shared prompt once gives
+    the log-probs of the plain pass bit for bit, and both agree with the log-probs the rollout recorded."""
+    cfg = pkg.GptConfig(n_layer=24, d_model=2048, n_head=16, d_ff=5632, vocab=32000, ctx=640, act=1, pos=1, exact=False)
+    pol = pkg.Policy(eng, cfg)
+    g = torch.Generator(device=eng.device)
+    g.manual_seed(1)
+    pv = pol.params_view()
+    pv.normal_(0, 0.02, generator=g)
+    for name, off, shape in cfg.param_layout()[0]:
+        size = int(np.prod(shape))
+        if name.endswith("gamma"):
+            pv[off:off + size] = 1.0
+        elif name.endswith(".bias"):
+            pv[off:off + size] = 0.0
+    pol.requantize()
+    prompt = torch.randint(0, cfg.vocab, (1, 128), device=eng.device, dtype=torch.int32, generator=g)
+    prompts = prompt.repeat_interleave(16, dim=0).contiguous()
+    tokens, old_lp, _ = pol.rollout(prompts, 512, temperature=0.8, top_k=50, seed=3, group_size=16)
+    lp_plain, _, _ = pol.logprobs(tokens, 128)
+    lp_grouped, _, _ = pol.logprobs(tokens, 128, group_size=16)
+    eng.check_device_errors()
+    assert torch.equal(lp_plain, lp_grouped)
+    # rollout (bf16 cache, step-by-step attention) against the teacher-forced pass: int8 roundings may flip
+    diff = (lp_plain - old_lp).abs()
+    assert diff.mean().item() < 2e-2 and bool(torch.isfinite(lp_plain).all())
+    pol.release_workspaces()
