@@ -1141,6 +1141,10 @@ nnb_status launch_attn_decode(nnb_engine* e, bool exact, const float* qkv, void*
 }
 
 // ------------------------------------------------------------------ sampler
+__device__ __forceinline__ float key_float(uint32_t k)  // inverse of float_key
+{
+    return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
 __device__ __forceinline__ uint32_t float_key(float v)
 {
     // order-preserving map float -> uint32 (larger float -> larger key)
@@ -1284,7 +1288,9 @@ sample_kernel(const float* __restrict__ logits, int V, float temperature, int to
     } else {
         const float r = philox_uniform(seed, seq0 + (unsigned)b, (unsigned)gen);
         if (top_k > 0 && top_k < V) {
-            // radix select of the top_k-th largest key, 8 bits per pass
+            // radix select of the top_k-th largest key, 8 bits per pass; the row is turned into its keys once
+            uint32_t* lgk = reinterpret_cast<uint32_t*>(lg);
+            for (int i = tid; i < V; i += NT) lgk[i] = float_key(lg[i]);
             if (tid == 0) { sh_prefix = 0u; sh_need = top_k; }
             int* myhist = whist + warp * 256;
             for (int pass = 3; pass >= 0; --pass) {
@@ -1297,9 +1303,10 @@ sample_kernel(const float* __restrict__ logits, int V, float temperature, int to
                     const int i = i0 + tid;
                     int bin = -1;
                     if (i < V) {
-                        const uint32_t key = float_key(lg[i]);
+                        const uint32_t key = lgk[i];
                         if ((key & himask) == (prefix & himask)) bin = (int)((key >> (8 * pass)) & 0xFF);
                     }
+                    if (__ballot_sync(0xffffffffu, bin >= 0) == 0u) continue;  // after the first pass most warps have nothing
                     const unsigned peers = __match_any_sync(0xffffffffu, bin);
                     if (bin >= 0 && lane == __ffs(peers) - 1) atomicAdd(&myhist[bin], __popc(peers));
                 }
@@ -1331,7 +1338,7 @@ sample_kernel(const float* __restrict__ logits, int V, float temperature, int to
             const int lo = min(V, tid * chunk), hi = min(V, lo + chunk);
             int n_gt = 0, n_eq = 0;
             for (int i = lo; i < hi; ++i) {
-                const uint32_t key = float_key(lg[i]);
+                const uint32_t key = lgk[i];
                 n_gt += key > thr;
                 n_eq += key == thr;
             }
@@ -1342,7 +1349,7 @@ sample_kernel(const float* __restrict__ logits, int V, float temperature, int to
                 // selected count before this thread = gt before + min(eq before, need_eq)
                 int w = n_gt + min(eq_before, need_eq);
                 for (int i = lo; i < hi; ++i) {
-                    const uint32_t key = float_key(lg[i]);
+                    const uint32_t key = lgk[i];
                     if (key > thr) cand[w++] = i;
                     else if (key == thr) {
                         if (eq_before < need_eq) cand[w++] = i;
@@ -1354,14 +1361,14 @@ sample_kernel(const float* __restrict__ logits, int V, float temperature, int to
             // softmax over the candidates in ascending index order, f32, then inverse CDF
             const int nc = top_k;
             float m2 = -INFINITY;
-            for (int i = tid; i < nc; i += NT) m2 = fmaxf(m2, lg[cand[i]]);
+            for (int i = tid; i < nc; i += NT) m2 = fmaxf(m2, key_float(lgk[cand[i]]));
             m2 = warp_max(m2);
             if (lane == 0) red_f[warp] = m2;
             __syncthreads();
             m2 = red_f[0];
 #pragma unroll
             for (int w = 1; w < NW; ++w) m2 = fmaxf(m2, red_f[w]);
-            for (int i = tid; i < nc; i += NT) cval[i] = nnb_expf(__fsub_rn(lg[cand[i]], m2));
+            for (int i = tid; i < nc; i += NT) cval[i] = nnb_expf(__fsub_rn(key_float(lgk[cand[i]]), m2));
             __syncthreads();
             if (tid == 0) {
                 float sum = 0.0f;
