@@ -256,6 +256,15 @@ nnb_status nnb_rollout_host(nnb_policy* p, const int32_t* h_prompts, size_t n_se
                             size_t max_new, float temperature, int top_k, uint64_t seed, uint32_t seq0,
                             int32_t* h_tokens, float* h_logp);
 
+/* Measurement aid for the rollout (the reference times its decode loop per token on the host,
+ * src/layer_bench.cpp:702-715).  With stride > 0 every later rollout of this policy records a CUDA event
+ * on its stream before every stride-th decode step and after the last one; stride = 0 turns it off.
+ * nnb_rollout_step_times waits for the last rollout and returns, for segment i, h_ms[i] = device time of
+ * the steps between events i and i+1 and h_pos[i] = the position the first of those steps consumed
+ * (either array may be NULL; *n_out = number of segments, at most cap of them are written). */
+nnb_status nnb_rollout_set_step_timing(nnb_policy* p, size_t stride);
+nnb_status nnb_rollout_step_times(nnb_policy* p, float* h_ms, int32_t* h_pos, size_t cap, size_t* n_out);
+
 /* ---- training of the policy on micro-batches of whole sequences.
  * A sequence of seq_len tokens whose first prompt_len are the prompt has G = seq_len - prompt_len
  * decisions; decision g is taken at position prompt_len-1+g and its action is token prompt_len+g.
@@ -337,10 +346,14 @@ nnb_status nnb_group_advantage(nnb_engine* e, const float* d_returns, size_t n, 
  * It has no counterpart in the reference.  Same arguments and result as nnb_group_advantage; the
  * device copy of the span table lives in a fixed 128 KiB array inside the library (held by every GPU
  * that loads it, until exit), so the call does no cudaMalloc / cudaFree.  Limit: n_spans <= 16384,
- * larger requests are rejected with NNB_ERR_INVALID.  The first call on a device looks up the array's
- * device address (cudaGetSymbolAddress); make that first call before any stream capture begins.  All
- * calls share the one array: calls whose GPU work can overlap (different streams or engines on the
- * same device) race on it and must be serialised by the caller. */
+ * larger requests are rejected with NNB_ERR_INVALID.  The array's device address is looked up once per
+ * device (cudaGetSymbolAddress, with that device current; the caller's current device is put back):
+ * nnb_engine_create does it, and a call on a device where that has not happened yet does it first, so
+ * create the engine before any stream capture begins.  h_first / h_count are read during the call and
+ * may be reused once it returns.  All calls share the one array, which keeps the last call's table:
+ * the entries a call reads are rewritten by that call, nothing has to start at zero.  Calls whose GPU
+ * work can overlap (different streams or engines on the same device) race on it and must be serialised
+ * by the caller. */
 nnb_status nnb_group_advantage_noalloc(nnb_engine* e, const float* d_returns, size_t n, const int32_t* h_first,
                                        const int32_t* h_count, size_t n_spans, float eps, float* d_out);
 /* MaskedNormalizer::apply (rl_experience.hpp:456-498); mask may be NULL (all ones) */

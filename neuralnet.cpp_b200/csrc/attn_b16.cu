@@ -716,7 +716,7 @@ nnb_status launch_attn_fwd_b16(nnb_engine* e, const __nv_bfloat16* q, const __nv
     const float scale = 1.0f / sqrtf((float)dk);
     dim3 grid((unsigned)(n_seq * H), (unsigned)ceil_div(S, 128));
     const size_t smem = (128 + 4 * 64) * (dk + 8) * 2;
-    static bool cfg = false;
+    static bool cfg_dev[64] = {}; bool& cfg = cfg_dev[e->device & 63];  // the attribute is per device
     if (!cfg) {
         NNB_TRY(set_smem(attn_fwd_kernel<128>, (128 + 4 * 64) * 136 * 2));
         NNB_TRY(set_smem(attn_fwd_kernel<64>, (128 + 4 * 64) * 72 * 2));
@@ -752,7 +752,7 @@ nnb_status launch_attn_bwd_b16(nnb_engine* e, const __nv_bfloat16* q, const __nv
     auto smem_kv_of = [](size_t dkv) { return (2 + 2 * NBUF) * 64 * (dkv + 8) * 2 + 2 * 64 * 72 * 2 + 2 * NBUF * 64 * 4; };
     auto smem_q_of = [](size_t dkv) { return (2 + 2 * NBUF) * 64 * (dkv + 8) * 2 + 64 * 72 * 2 + 128 * 4; };
     const size_t smem_kv = smem_kv_of(dk), smem_q = smem_q_of(dk);
-    static bool cfg = false;
+    static bool cfg_dev[64] = {}; bool& cfg = cfg_dev[e->device & 63];  // the attribute is per device
     if (!cfg) {
         NNB_TRY(set_smem(attn_bwd_dkv_kernel<128, NBUF>, smem_kv_of(128)));
         NNB_TRY(set_smem(attn_bwd_dkv_kernel<64, NBUF>, smem_kv_of(64)));

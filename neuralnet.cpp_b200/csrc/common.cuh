@@ -98,6 +98,10 @@ inline cudaError_t launch_ex(nnb_engine* e, void (*kern)(KArgs...), dim3 grid, d
     return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
 
+// ---- no_alloc.cu: resolves, once per device, the device address of the fixed scratch array of
+// nnb_group_advantage_noalloc; leaves the caller's current device as it found it
+nnb_status noalloc_prepare(int device);
+
 // ---- ternary.cu: launchers (all enqueue on e->stream)
 nnb_status launch_absmean_tau(nnb_engine* e, const float* latent, size_t rows, size_t k, float* tau);
 nnb_status launch_trit_pack(nnb_engine* e, const float* latent, const float* tau, size_t rows,
@@ -132,7 +136,8 @@ nnb_status launch_row_quant(nnb_engine* e, int mode, bool exact, const float* in
 nnb_status launch_attn_decode(nnb_engine* e, bool exact, const float* qkv, void* kcache, void* vcache,
                               size_t own_alloc, const void* kpre, const void* vpre, size_t pre_len, size_t pre_alloc,
                               size_t group, const float* rope_cos, const float* rope_sin, const int* d_pos, size_t B,
-                              size_t H, size_t dk, float* out);
+                              size_t H, size_t dk, float* out, size_t kv_pitch = 0 /* elements per cached key; 0 = dk */);
+size_t attn_decode_kv_pitch(bool exact, size_t dk);
 bool attn_decode_fused_supported(size_t H, size_t dk);
 nnb_status launch_attn_decode_fused(nnb_engine* e, const float* qkv, void* kcache, void* vcache, size_t own_alloc,
                                     const void* kpre, const void* vpre, size_t pre_len, size_t pre_alloc, size_t group,

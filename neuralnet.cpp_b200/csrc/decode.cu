@@ -246,7 +246,7 @@ static nnb_status launch_row_quant_mode(nnb_engine* e, bool exact, const float* 
                                         int8_t* q, float* s, int32_t* qsum, float* f_out)
 {
     const size_t smem = k * sizeof(float);
-    static bool cfg = false;
+    static bool cfg_dev[64] = {}; bool& cfg = cfg_dev[e->device & 63];  // the attribute is per device
     if (!cfg) {
         NNB_CUDA(cudaFuncSetAttribute(row_quant_kernel<MODE, true>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
@@ -463,7 +463,9 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi)
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-template <int DK>
+// DK is the head size, DKP the row pitch of the caches in elements: DK rounded up to a multiple of 8, so that
+// every key starts on a 16-byte boundary (head size 100 -> pitch 104; the pad features are kept at zero).
+template <int DK, int DKP>
 __global__ void __launch_bounds__(128)
 attn_decode_bf16_kernel(const float* __restrict__ qkv, __nv_bfloat16* __restrict__ kcache, __nv_bfloat16* __restrict__ vcache,
                         int own_alloc, const __nv_bfloat16* __restrict__ kpre, const __nv_bfloat16* __restrict__ vpre,
@@ -471,14 +473,15 @@ attn_decode_bf16_kernel(const float* __restrict__ qkv, __nv_bfloat16* __restrict
                         const float* __restrict__ rope_sin, const int* __restrict__ d_pos, int B, int H, int ctx_total,
                         float scale, float* __restrict__ out)
 {
-    constexpr int LPK = DK / 8;    // lanes per key
-    constexpr int KPW = 32 / LPK;  // keys per warp-wide load
-    constexpr int G = 4 * KPW;     // lane groups per CTA
-    constexpr int U = 4;           // keys in flight per lane group
+    static_assert(DKP % 8 == 0 && DKP >= DK && DKP <= 128, "cache pitch: a multiple of 8 elements, at most 128");
+    constexpr int LPK = DKP <= 64 ? 8 : 16;  // lanes per key (a power of two; lanes past DKP/8 idle)
+    constexpr int KPW = 32 / LPK;            // keys per warp-wide load
+    constexpr int G = 4 * KPW;               // lane groups per CTA
+    constexpr int U = 4;                     // keys in flight per lane group
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    float* qs = reinterpret_cast<float*>(smem_raw);  // DK
-    float* red = qs + DK;                            // G * DK
-    float* sc = red + G * DK;                        // ctx_total
+    float* qs = reinterpret_cast<float*>(smem_raw);  // DKP
+    float* red = qs + DKP;                           // G * DKP
+    float* sc = red + G * DKP;                       // ctx_total
     __shared__ float bcast[4];
     __shared__ float bsum[4];
 
@@ -486,10 +489,10 @@ attn_decode_bf16_kernel(const float* __restrict__ qkv, __nv_bfloat16* __restrict
     const int d = H * DK;
     const int pos = *d_pos;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const size_t head_off = ((size_t)b * H + h) * (size_t)own_alloc * DK;
-    __nv_bfloat16* kc = kcache + head_off - (size_t)pre_len * DK;  // indexed by absolute position >= pre_len
-    __nv_bfloat16* vc = vcache + head_off - (size_t)pre_len * DK;
-    const size_t pre_off = ((size_t)(b / group) * H + h) * (size_t)pre_alloc * DK;
+    const size_t head_off = ((size_t)b * H + h) * (size_t)own_alloc * DKP;
+    __nv_bfloat16* kc = kcache + head_off - (size_t)pre_len * DKP;  // indexed by absolute position >= pre_len
+    __nv_bfloat16* vc = vcache + head_off - (size_t)pre_len * DKP;
+    const size_t pre_off = ((size_t)(b / group) * H + h) * (size_t)pre_alloc * DKP;
     const __nv_bfloat16* kp = kpre ? kpre + pre_off : nullptr;
     const __nv_bfloat16* vp = vpre ? vpre + pre_off : nullptr;
     const float* qn = qkv + (size_t)b * d + (size_t)h * DK;
@@ -504,24 +507,30 @@ attn_decode_bf16_kernel(const float* __restrict__ qkv, __nv_bfloat16* __restrict
             const float ka = kn[j], kb = kn[j + half];
             qs[j] = __fadd_rn(__fmul_rn(qa, c), __fmul_rn(-qb, sn));
             qs[j + half] = __fadd_rn(__fmul_rn(qb, c), __fmul_rn(qa, sn));
-            kc[(size_t)pos * DK + j] = __float2bfloat16_rn(__fadd_rn(__fmul_rn(ka, c), __fmul_rn(-kb, sn)));
-            kc[(size_t)pos * DK + j + half] = __float2bfloat16_rn(__fadd_rn(__fmul_rn(kb, c), __fmul_rn(ka, sn)));
+            kc[(size_t)pos * DKP + j] = __float2bfloat16_rn(__fadd_rn(__fmul_rn(ka, c), __fmul_rn(-kb, sn)));
+            kc[(size_t)pos * DKP + j + half] = __float2bfloat16_rn(__fadd_rn(__fmul_rn(kb, c), __fmul_rn(ka, sn)));
         }
     } else {
         for (int j = tid; j < DK; j += 128) {
             qs[j] = qn[j];
-            kc[(size_t)pos * DK + j] = __float2bfloat16_rn(kn[j]);
+            kc[(size_t)pos * DKP + j] = __float2bfloat16_rn(kn[j]);
         }
     }
-    for (int j = tid; j < DK; j += 128) vc[(size_t)pos * DK + j] = __float2bfloat16_rn(vn[j]);
+    for (int j = tid; j < DK; j += 128) vc[(size_t)pos * DKP + j] = __float2bfloat16_rn(vn[j]);
+    if (DKP > DK && tid < DKP - DK) {
+        qs[DK + tid] = 0.0f;
+        kc[(size_t)pos * DKP + DK + tid] = __float2bfloat16_rn(0.0f);
+        vc[(size_t)pos * DKP + DK + tid] = __float2bfloat16_rn(0.0f);
+    }
     __syncthreads();
 
     const int sub = lane / LPK, sl = lane % LPK;
     const int g = warp * KPW + sub;
     const int e0 = sl * 8;
+    const bool act = e0 < DKP;
     float qv[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) qv[i] = qs[e0 + i];
+    for (int i = 0; i < 8; ++i) qv[i] = act ? qs[e0 + i] : 0.0f;
     const int n_keys = pos + 1;
 
     // scores
@@ -531,7 +540,7 @@ attn_decode_bf16_kernel(const float* __restrict__ qkv, __nv_bfloat16* __restrict
         for (int u = 0; u < U; ++u) {
             const int j = base + u * G + g;
             raw[u] = make_uint4(0u, 0u, 0u, 0u);
-            if (j < n_keys) raw[u] = *reinterpret_cast<const uint4*>((j < pre_len ? kp : kc) + (size_t)j * DK + e0);
+            if (act && j < n_keys) raw[u] = *reinterpret_cast<const uint4*>((j < pre_len ? kp : kc) + (size_t)j * DKP + e0);
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
@@ -574,8 +583,8 @@ attn_decode_bf16_kernel(const float* __restrict__ qkv, __nv_bfloat16* __restrict
             const int j = base + u * G + g;
             raw[u] = make_uint4(0u, 0u, 0u, 0u);
             p[u] = 0.0f;
-            if (j < n_keys) {
-                raw[u] = *reinterpret_cast<const uint4*>((j < pre_len ? vp : vc) + (size_t)j * DK + e0);
+            if (act && j < n_keys) {
+                raw[u] = *reinterpret_cast<const uint4*>((j < pre_len ? vp : vc) + (size_t)j * DKP + e0);
                 p[u] = sc[j];
             }
         }
@@ -587,29 +596,31 @@ attn_decode_bf16_kernel(const float* __restrict__ qkv, __nv_bfloat16* __restrict
             for (int i = 0; i < 8; ++i) o8[i] = fmaf(p[u], vv[i], o8[i]);
         }
     }
+    if (act) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) red[g * DK + e0 + i] = o8[i];
+        for (int i = 0; i < 8; ++i) red[g * DKP + e0 + i] = o8[i];
+    }
     __syncthreads();
     for (int i = tid; i < DK; i += 128) {
         float a = 0.0f;
 #pragma unroll
-        for (int gi = 0; gi < G; ++gi) a += red[gi * DK + i];
+        for (int gi = 0; gi < G; ++gi) a += red[gi * DKP + i];
         out[(size_t)b * d + (size_t)h * DK + i] = a * inv;
     }
 }
 
-template <int DK>
+template <int DK, int DKP = DK>
 static nnb_status launch_attn_decode_bf16(nnb_engine* e, const float* qkv, void* kcache, void* vcache, size_t own_alloc,
                                           const void* kpre, const void* vpre, size_t pre_len, size_t pre_alloc, size_t group,
                                           const float* rope_cos, const float* rope_sin, const int* d_pos, size_t B, size_t H,
                                           float* out)
 {
     const size_t ctx_total = pre_len + own_alloc;
-    constexpr size_t G = 4 * (32 / (DK / 8));
-    const size_t smem = (DK + G * DK + ((ctx_total + 3) & ~(size_t)3)) * sizeof(float);
+    constexpr size_t G = 4 * (32 / (DKP <= 64 ? 8 : 16));
+    const size_t smem = (DKP + G * DKP + ((ctx_total + 3) & ~(size_t)3)) * sizeof(float);
     NNB_REQUIRE(smem <= 200 * 1024, "attn_decode: context %zu too long for one CTA", ctx_total);
-    auto kern = attn_decode_bf16_kernel<DK>;
-    static size_t cfg = 0;
+    auto kern = attn_decode_bf16_kernel<DK, DKP>;
+    static size_t cfg_dev[64] = {}; size_t& cfg = cfg_dev[e->device & 63];
     if (smem > cfg) {
         NNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         cfg = smem;
@@ -1044,7 +1055,7 @@ nnb_status launch_attn_decode_fused(nnb_engine* e, const float* qkv, void* kcach
         const size_t smem_p = 4 * (16 + 64) * (dk + 8) * sizeof(__nv_bfloat16);
         const float scale_p = 1.0f / sqrtf((float)dk);
         dim3 grid_p((unsigned)(B / group), (unsigned)ceil_div(H, 4));
-        static bool cfg_p = false;
+        static bool cfg_p_dev[64] = {}; bool& cfg_p = cfg_p_dev[e->device & 63];  // the attribute is per device
         if (!cfg_p) {
             NNB_CUDA(cudaFuncSetAttribute(attn_prefix_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * 80 * 136 * 2));
             NNB_CUDA(cudaFuncSetAttribute(attn_prefix_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * 80 * 72 * 2));
@@ -1076,7 +1087,7 @@ nnb_status launch_attn_decode_fused(nnb_engine* e, const float* qkv, void* kcach
 #define NNB_FUSED_V(DKV, UV, MT)                                                                                          \
     {                                                                                                                     \
         auto kern = attn_decode_fused_kernel<DKV, UV, MT>;                                                                \
-        static size_t cfg = 0;                                                                                            \
+        static size_t cfg_dev[64] = {}; size_t& cfg = cfg_dev[e->device & 63];                                                                                            \
         if (smem > cfg) {                                                                                                 \
             NNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                 \
             cfg = smem;                                                                                                   \
@@ -1094,11 +1105,18 @@ nnb_status launch_attn_decode_fused(nnb_engine* e, const float* qkv, void* kcach
     return NNB_OK;
 }
 
+// Row pitch, in elements, of the caches launch_attn_decode expects: the head size, except where the fast kernel
+// wants every key on a 16-byte boundary (bf16 caches, head size 100 -> 104, pad features zero).
+size_t attn_decode_kv_pitch(bool exact, size_t dk) { return (!exact && dk == 100) ? 104 : dk; }
+
 nnb_status launch_attn_decode(nnb_engine* e, bool exact, const float* qkv, void* kcache, void* vcache,
                               size_t own_alloc, const void* kpre, const void* vpre, size_t pre_len, size_t pre_alloc,
                               size_t group, const float* rope_cos, const float* rope_sin, const int* d_pos, size_t B,
-                              size_t H, size_t dk, float* out)
+                              size_t H, size_t dk, float* out, size_t kv_pitch)
 {
+    if (kv_pitch == 0) kv_pitch = dk;
+    NNB_REQUIRE(kv_pitch == dk || kv_pitch == attn_decode_kv_pitch(exact, dk), "attn_decode: cache pitch %zu unsupported for head size %zu",
+                kv_pitch, dk);
     NNB_REQUIRE(dk % 4 == 0 && dk <= 128 && dk >= 8, "attn_decode: head dim %zu unsupported (multiple of 4, <= 128)", dk);
     NNB_REQUIRE(group >= 1 && (pre_len == 0 || (kpre && vpre)), "attn_decode: bad prefix arguments");
     if (!exact && dk == 128)
@@ -1107,6 +1125,9 @@ nnb_status launch_attn_decode(nnb_engine* e, bool exact, const float* qkv, void*
     if (!exact && dk == 64)
         return launch_attn_decode_bf16<64>(e, qkv, kcache, vcache, own_alloc, kpre, vpre, pre_len, pre_alloc, group, rope_cos,
                                            rope_sin, d_pos, B, H, out);
+    if (!exact && dk == 100 && kv_pitch == 104)  // caches of pitch attn_decode_kv_pitch(false, 100)
+        return launch_attn_decode_bf16<100, 104>(e, qkv, kcache, vcache, own_alloc, kpre, vpre, pre_len, pre_alloc, group,
+                                                 rope_cos, rope_sin, d_pos, B, H, out);
     const float scale = 1.0f / sqrtf((float)dk);
     const size_t acc_sz = exact ? 8 : 4;
     const size_t ctx_total = pre_len + own_alloc;
@@ -1115,7 +1136,7 @@ nnb_status launch_attn_decode(nnb_engine* e, bool exact, const float* qkv, void*
     const unsigned grid = (unsigned)(B * H);
     if (exact) {
         auto kern = attn_decode_kernel<float, true>;
-        static size_t cfg = 0;
+        static size_t cfg_dev[64] = {}; size_t& cfg = cfg_dev[e->device & 63];
         if (smem > cfg) {
             NNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             cfg = smem;
@@ -1125,7 +1146,7 @@ nnb_status launch_attn_decode(nnb_engine* e, bool exact, const float* qkv, void*
                                              d_pos, (int)B, (int)H, (int)dk, (int)ctx_total, scale, out);
     } else {
         auto kern = attn_decode_kernel<__nv_bfloat16, false>;
-        static size_t cfg = 0;
+        static size_t cfg_dev[64] = {}; size_t& cfg = cfg_dev[e->device & 63];
         if (smem > cfg) {
             NNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             cfg = smem;
@@ -1451,7 +1472,7 @@ nnb_status launch_sample(nnb_engine* e, bool exact, const float* logits, size_t 
     NNB_REQUIRE(smem <= 220 * 1024, "sample: vocabulary %zu too large for one CTA", V);
     if (exact) {
         auto kern = sample_kernel<true>;
-        static size_t cfg = 0;
+        static size_t cfg_dev[64] = {}; size_t& cfg = cfg_dev[e->device & 63];
         if (smem > cfg) {
             NNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             cfg = smem;
@@ -1460,7 +1481,7 @@ nnb_status launch_sample(nnb_engine* e, bool exact, const float* logits, size_t 
                   tokens, (int)tokens_stride, logp, (int)logp_stride, entropy);
     } else {
         auto kern = sample_kernel<false>;
-        static size_t cfg = 0;
+        static size_t cfg_dev[64] = {}; size_t& cfg = cfg_dev[e->device & 63];
         if (smem > cfg) {
             NNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             cfg = smem;

@@ -97,6 +97,9 @@ nnb_status nnb_engine_create(int device, nnb_engine** out)
              prop.name, prop.major, prop.minor, prop.multiProcessorCount,
              (double)prop.totalGlobalMem / 1e9);
     e->describe_text = buf;
+    // the no-allocation entry point's scratch address is looked up now, so that its calls never touch the
+    // module loader; a failure here only surfaces if that entry point is used
+    if (nnb::noalloc_prepare(device) != NNB_OK) nnb::set_error("%s", "");
     *out = e;
     return NNB_OK;
 }

@@ -441,7 +441,7 @@ static nnb_status launch(nnb_engine* e, const CUtensorMap& ta, const CUtensorMap
 {
     auto kern = gemm_tc_kernel<KIND, A_MN, B_MN, EPI, BN>;
     constexpr int SMEM_BYTES = Tile<BN>::SMEM_BYTES;
-    static bool cfg = false;
+    static bool cfg_dev[64] = {}; bool& cfg = cfg_dev[e->device & 63];  // the attribute is per device
     if (!cfg) {
         NNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         cfg = true;
@@ -614,10 +614,13 @@ __global__ void scale_to_bf16_kernel(const float* __restrict__ dy, const float* 
 }
 
 // The two uses of dy in one pass: dyb[t,o] = bf16(dy[t,o] * tau[o]) and db[o] += sum_t dy[t,o].
-// grid (ceil(O/256), ceil(T/chunk)), 128 threads, two adjacent columns per thread.
+// grid (ceil(O/256), ceil(T/chunk)), 128 threads, two adjacent columns per thread.  The column sums of a
+// token chunk go to part[chunk][o]; colsum_finish_kernel adds the chunks in ascending order, so the bias
+// gradient does not depend on the order in which CTAs retire (row_reduce_sum of the reference,
+// include/neuralnet.cpp/compute_layer_bitlinear.hpp:538-541, is deterministic too).
 __global__ void __launch_bounds__(128)
 scale_colsum_kernel(const float* __restrict__ dy, const float* __restrict__ tau, int T, int O, int chunk,
-                    __nv_bfloat16* __restrict__ out, size_t ld, float* __restrict__ db)
+                    __nv_bfloat16* __restrict__ out, size_t ld, float* __restrict__ part)
 {
     const int o = (blockIdx.x * 128 + threadIdx.x) * 2;
     if (o >= O) return;
@@ -642,8 +645,18 @@ scale_colsum_kernel(const float* __restrict__ dy, const float* __restrict__ tau,
         sb += v.y;
         *reinterpret_cast<__nv_bfloat162*>(out + (size_t)t * ld + o) = __floats2bfloat162_rn(v.x * tv.x, v.y * tv.y);
     }
-    atomicAdd(db + o, sa);
-    atomicAdd(db + o + 1, sb);
+    *reinterpret_cast<float2*>(part + (size_t)blockIdx.y * O + o) = make_float2(sa, sb);
+}
+
+// db[o] += part[0][o] + part[1][o] + ... in that order
+__global__ void __launch_bounds__(256)
+colsum_finish_kernel(const float* __restrict__ part, int n_chunks, int O, float* __restrict__ db)
+{
+    const int o = blockIdx.x * 256 + threadIdx.x;
+    if (o >= O) return;
+    float acc = 0.0f;
+    for (int c = 0; c < n_chunks; ++c) acc += part[(size_t)c * O + o];
+    db[o] += acc;
 }
 
 // Activation backward fused with the preparation of the next GEMM's operand: with h (T, F1) the
@@ -653,7 +666,7 @@ scale_colsum_kernel(const float* __restrict__ dy, const float* __restrict__ tau,
 template <int MODE>
 __global__ void __launch_bounds__(128)
 act_bwd_scale_colsum_kernel(const float* __restrict__ h, const float* __restrict__ da, const float* __restrict__ tau, int T,
-                            int F, int chunk, __nv_bfloat16* __restrict__ out, float* __restrict__ db)
+                            int F, int chunk, __nv_bfloat16* __restrict__ out, float* __restrict__ part)
 {
     const int f = (blockIdx.x * 128 + threadIdx.x) * 2;
     if (f >= F) return;
@@ -695,12 +708,9 @@ act_bwd_scale_colsum_kernel(const float* __restrict__ h, const float* __restrict
             }
         }
     }
-    atomicAdd(db + f, sg0);
-    atomicAdd(db + f + 1, sg1);
-    if (MODE == 2) {
-        atomicAdd(db + F + f, su0);
-        atomicAdd(db + F + f + 1, su1);
-    }
+    float* prow = part + (size_t)blockIdx.y * F1;
+    *reinterpret_cast<float2*>(prow + f) = make_float2(sg0, sg1);
+    if (MODE == 2) *reinterpret_cast<float2*>(prow + F + f) = make_float2(su0, su1);
 }
 
 // xs[t,k] = bf16(s[t] * q[t, perm(k)]) in natural feature order.  One thread per 64-feature block: it reads
@@ -760,9 +770,13 @@ nnb_status launch_act_bwd_scale_colsum(nnb_engine* e, int mode, const float* h, 
     const int chunk = 128;
     dim3 grid((unsigned)ceil_div(F, 256), (unsigned)ceil_div(t, chunk));
     NNB_REQUIRE(grid.y <= 65535, "act_bwd_scale_colsum: too many tokens (%zu)", t);
-    if (mode == 2) act_bwd_scale_colsum_kernel<2><<<grid, 128, 0, e->stream>>>(h, da, tau, (int)t, (int)F, chunk, dyb, db);
-    else act_bwd_scale_colsum_kernel<1><<<grid, 128, 0, e->stream>>>(h, da, tau, (int)t, (int)F, chunk, dyb, db);
-    e->launches++;
+    const size_t F1 = mode == 2 ? 2 * F : F;
+    NNB_TRY(e->ensure_scratch((size_t)grid.y * F1 * sizeof(float)));
+    float* part = (float*)e->scratch;
+    if (mode == 2) act_bwd_scale_colsum_kernel<2><<<grid, 128, 0, e->stream>>>(h, da, tau, (int)t, (int)F, chunk, dyb, part);
+    else act_bwd_scale_colsum_kernel<1><<<grid, 128, 0, e->stream>>>(h, da, tau, (int)t, (int)F, chunk, dyb, part);
+    colsum_finish_kernel<<<(unsigned)ceil_div(F1, 256), 256, 0, e->stream>>>(part, (int)grid.y, (int)F1, db);
+    e->launches += 2;
     NNB_CHECK_LAUNCH("act_bwd_scale_colsum_kernel");
     return NNB_OK;
 }
@@ -775,8 +789,11 @@ nnb_status launch_scale_colsum(nnb_engine* e, const float* dy, const float* tau,
     const int chunk = 128;
     dim3 grid((unsigned)ceil_div(out, 256), (unsigned)ceil_div(t, chunk));
     NNB_REQUIRE(grid.y <= 65535, "scale_colsum: too many tokens (%zu)", t);
-    scale_colsum_kernel<<<grid, 128, 0, e->stream>>>(dy, tau, (int)t, (int)out, chunk, dyb, dyb_ld ? dyb_ld : out, db);
-    e->launches++;
+    NNB_TRY(e->ensure_scratch((size_t)grid.y * out * sizeof(float)));
+    float* part = (float*)e->scratch;
+    scale_colsum_kernel<<<grid, 128, 0, e->stream>>>(dy, tau, (int)t, (int)out, chunk, dyb, dyb_ld ? dyb_ld : out, part);
+    colsum_finish_kernel<<<(unsigned)ceil_div(out, 256), 256, 0, e->stream>>>(part, (int)grid.y, (int)out, db);
+    e->launches += 2;
     NNB_CHECK_LAUNCH("scale_colsum_kernel");
     return NNB_OK;
 }

@@ -23,6 +23,28 @@ int32_t* g_span_ptr[kMaxDevices] = {nullptr};
 
 }  // namespace
 
+// One-time set-up per device: resolve the device address of the array with `device` current, and put the
+// caller's current device back afterwards.  nnb_engine_create calls this, so that the lookup (which may make
+// the CUDA runtime load this module's image onto the device) is over before the first operator call.
+nnb_status nnb::noalloc_prepare(int device)
+{
+    NNB_REQUIRE(device >= 0 && device < kMaxDevices, "group_advantage_noalloc: device index %d out of range", device);
+    if (g_span_ptr[device]) return NNB_OK;
+    int prev = -1;
+    NNB_CUDA(cudaGetDevice(&prev));
+    if (prev != device) NNB_CUDA(cudaSetDevice(device));
+    int32_t* ptr = nullptr;
+    const cudaError_t err = cudaGetSymbolAddress((void**)&ptr, g_span_scratch);
+    if (prev != device) cudaSetDevice(prev);
+    if (err != cudaSuccess) {
+        cudaGetLastError();
+        NNB_FAIL(NNB_ERR_CUDA, "cudaGetSymbolAddress of the fixed span scratch failed on device %d: %s", device,
+                 cudaGetErrorString(err));
+    }
+    g_span_ptr[device] = ptr;
+    return NNB_OK;
+}
+
 extern "C" nnb_status nnb_group_advantage_noalloc(nnb_engine* e, const float* d_returns, size_t n, const int32_t* h_first,
                                                   const int32_t* h_count, size_t n_spans, float eps, float* d_out)
 {
@@ -39,14 +61,8 @@ extern "C" nnb_status nnb_group_advantage_noalloc(nnb_engine* e, const float* d_
         cursor += (size_t)h_count[s];
     }
     NNB_REQUIRE(cursor == n, "group_advantage_noalloc: group spans do not cover all %zu rows", n);
-    NNB_REQUIRE(e->device >= 0 && e->device < kMaxDevices, "group_advantage_noalloc: device index %d out of range", e->device);
-    if (!g_span_ptr[e->device]) {
-        // one-time set-up on this device, with this device current: resolve the device address of the array
-        NNB_CUDA(cudaSetDevice(e->device));
-        int32_t* ptr = nullptr;
-        NNB_CUDA(cudaGetSymbolAddress((void**)&ptr, g_span_scratch));
-        g_span_ptr[e->device] = ptr;
-    }
+    // normally resolved by nnb_engine_create; an engine made before this library version's set-up ran gets it here
+    NNB_TRY(noalloc_prepare(e->device));
     int32_t* d_first = g_span_ptr[e->device];
     int32_t* d_count = d_first + kMaxGroups;
     // Nothing in the array has to start at zero: the kernel reads only the first n_spans entries of each

@@ -202,8 +202,9 @@ static nnb_status ensure_decode(nnb_policy* p, size_t B, size_t ctx_alloc, size_
     const nnb_gpt_config& c = p->cfg;
     const size_t d = c.d_model, F = c.d_ff, V = c.vocab, F1 = c.act == 1 ? 2 * F : F;
     const size_t kv_elem = c.exact ? 4 : 2;
-    const size_t kv_bytes = (size_t)c.n_layer * B * d * ctx_alloc * kv_elem;
-    const size_t pre_bytes = (size_t)c.n_layer * (B / group) * d * pre_len * kv_elem;
+    const size_t dkv = c.n_head * attn_decode_kv_pitch(c.exact != 0, d / c.n_head);  // cached features per position
+    const size_t kv_bytes = (size_t)c.n_layer * B * dkv * ctx_alloc * kv_elem;
+    const size_t pre_bytes = (size_t)c.n_layer * (B / group) * dkv * pre_len * kv_elem;
     const size_t total = pre_len + ctx_alloc;
     size_t free_b = 0, total_b = 0;
     NNB_CUDA(cudaMemGetInfo(&free_b, &total_b));
@@ -318,7 +319,7 @@ static nnb_status decode_step(nnb_policy* p, const StepView& sv, bool with_head,
                                              dk, nullptr, w.q8, w.s, w.qsum, w.att, w.pre_ml));
         } else {
             NNB_TRY(launch_attn_decode(e, exact, w.qkv, kl, vl, sv.own_alloc, kpl, vpl, sv.pre_len, sv.pre_alloc, sv.group,
-                                       p->rope_cos, p->rope_sin, w.d_pos, B, H, dk, w.att));
+                                       p->rope_cos, p->rope_sin, w.d_pos, B, H, dk, w.att, attn_decode_kv_pitch(exact, dk)));
             NNB_TRY(launch_row_quant(e, 3, exact, w.att, nullptr, B, d, d, w.q8, w.s, w.qsum, nullptr));
         }
         {
@@ -402,10 +403,11 @@ nnb_status policy_rollout(nnb_policy* p, const int32_t* d_prompts, size_t B, siz
     DecodeWs& w = p->dec;
     const size_t V = c.vocab, d = c.d_model;
     const size_t kv_elem = c.exact ? 4 : 2;
+    const size_t dkv = c.n_head * attn_decode_kv_pitch(c.exact != 0, d / c.n_head);
     const size_t Bg = B / group;
-    StepView main_view{B, w.tokens, total, w.k, w.v, own, B * d * own * kv_elem, w.k_pre, w.v_pre, pre_len, pre_len,
-                       Bg * d * pre_len * kv_elem, group};
-    StepView pre_view{Bg, w.tokens_pre, pre_len, w.k_pre, w.v_pre, pre_len, Bg * d * pre_len * kv_elem, nullptr, nullptr, 0, 0, 0, 1};
+    StepView main_view{B, w.tokens, total, w.k, w.v, own, B * dkv * own * kv_elem, w.k_pre, w.v_pre, pre_len, pre_len,
+                       Bg * dkv * pre_len * kv_elem, group};
+    StepView pre_view{Bg, w.tokens_pre, pre_len, w.k_pre, w.v_pre, pre_len, Bg * dkv * pre_len * kv_elem, nullptr, nullptr, 0, 0, 0, 1};
 
     // the steps run on the engine's own stream (graph capture is not possible on the legacy default
     // stream); it is ordered after and before the caller's stream with events
@@ -430,11 +432,25 @@ nnb_status policy_rollout(nnb_policy* p, const int32_t* d_prompts, size_t B, siz
         if (pre_len > 0 && policy_can_prefill(p)) {
             // fast mode: the shared prompt prefixes go through one teacher-forced forward (all positions at once)
             // that leaves every layer's keys and values in the prefix cache, instead of pre_len decode steps
-            NNB_TRY(policy_prefill_prefix(p, w.tokens_pre, Bg, pre_len, w.k_pre, w.v_pre, pre_len, Bg * d * pre_len * kv_elem));
+            NNB_TRY(policy_prefill_prefix(p, w.tokens_pre, Bg, pre_len, w.k_pre, w.v_pre, pre_len, Bg * dkv * pre_len * kv_elem));
             NNB_TRY(launch_set_int(e, w.d_pos, (int)pre_len));
             t0 = pre_len;
         }
+        auto mark = [&](size_t t) -> nnb_status {
+            cudaEvent_t evt = nullptr;
+            NNB_CUDA(cudaEventCreate(&evt));
+            p->time_events.push_back(evt);
+            p->time_pos.push_back((int)t);
+            NNB_CUDA(cudaEventRecord(evt, e->stream));
+            return NNB_OK;
+        };
+        if (p->time_stride) {
+            for (cudaEvent_t evt : p->time_events) cudaEventDestroy(evt);
+            p->time_events.clear();
+            p->time_pos.clear();
+        }
         for (size_t t = t0; t + 1 < total; ++t) {
+            if (p->time_stride && (t - t0) % p->time_stride == 0) NNB_TRY(mark(t));
             if (t < pre_len) {
                 NNB_TRY(run_step(p, graphs[0], allow_graph, pre_view, false, temperature, top_k, seed, seq0, (int)P, false));
                 continue;
@@ -448,6 +464,7 @@ nnb_status policy_rollout(nnb_policy* p, const int32_t* d_prompts, size_t B, siz
                                            cudaMemcpyDeviceToDevice, e->stream));
             }
         }
+        if (p->time_stride) NNB_TRY(mark(total - 1));
         return NNB_OK;
     };
     const nnb_status st = run();
@@ -542,6 +559,7 @@ void nnb_policy_destroy(nnb_policy* p)
 {
     if (!p) return;
     cudaStreamSynchronize(p->e->stream);
+    for (cudaEvent_t evt : p->time_events) cudaEventDestroy(evt);
     free_decode(p);
     policy_free_train(p);
     void* ptrs[] = {p->params, p->grads, p->adam_m, p->adam_v, p->packed, p->tau, p->rope_cos, p->rope_sin, p->w8, p->wb};
@@ -597,6 +615,27 @@ nnb_status nnb_policy_linear(nnb_policy* p, int layer, int which, uint32_t** d_p
     if (d_tau) *d_tau = p->tau + l->tau_off;
     if (in) *in = l->in;
     if (out) *out = l->out;
+    return NNB_OK;
+}
+
+nnb_status nnb_rollout_set_step_timing(nnb_policy* p, size_t stride)
+{
+    NNB_REQUIRE(p, "policy is NULL");
+    p->time_stride = stride;
+    return NNB_OK;
+}
+
+nnb_status nnb_rollout_step_times(nnb_policy* p, float* h_ms, int32_t* h_pos, size_t cap, size_t* n_out)
+{
+    NNB_REQUIRE(p && n_out, "rollout_step_times: NULL argument");
+    const size_t n = p->time_events.size() > 1 ? p->time_events.size() - 1 : 0;
+    *n_out = n;
+    if (!h_ms || n == 0) return NNB_OK;
+    NNB_CUDA(cudaEventSynchronize(p->time_events.back()));
+    for (size_t i = 0; i < n && i < cap; ++i) {
+        NNB_CUDA(cudaEventElapsedTime(&h_ms[i], p->time_events[i], p->time_events[i + 1]));
+        if (h_pos) h_pos[i] = p->time_pos[i];
+    }
     return NNB_OK;
 }
 

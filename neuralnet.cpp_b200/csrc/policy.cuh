@@ -62,6 +62,10 @@ struct nnb_policy {
     nnb::LinW head;
     std::vector<nnb::TensorInfo> tensors;
     nnb::DecodeWs dec;
+    // optional timing of the rollout: a CUDA event every time_stride decode steps (0 = off)
+    size_t time_stride = 0;
+    std::vector<cudaEvent_t> time_events;
+    std::vector<int> time_pos;  // position consumed by the step that follows each event
     void* train = nullptr;    // workspace of the teacher-forced passes (policy_train.cu)
     void* prefill = nullptr;  // a second one, for the batched prompt prefill of the rollout
 };

@@ -160,7 +160,9 @@ static nnb_status ensure_train(nnb_policy* p, size_t n_seq, size_t S, size_t P, 
             w->dh1 = (float*)take(T * F1 * 4);
             w->delta = (float*)take(n_seq * H * S * 4);
             if (!c.exact) {
-                const size_t dyb_elems = T * F1 > Td * V ? T * F1 : Td * V;
+                // widest operand written into dyb: fc1's (T, F1), the merged q|k|v gradient (T, 3d), the head's (Td, V)
+                const size_t wide = F1 > 3 * d ? F1 : 3 * d;
+                const size_t dyb_elems = T * wide > Td * V ? T * wide : Td * V;
                 w->dyb = (__nv_bfloat16*)take(dyb_elems * 2);
                 w->xs = (__nv_bfloat16*)take(T * (F > d ? F : d) * 2);
                 if (w->b16_attn) w->dob = (__nv_bfloat16*)take(T * d * 2);
@@ -528,13 +530,15 @@ nnb_status nnb_policy_optimizer_step(nnb_policy* p, float lr, float beta1, float
         NNB_CUDA(cudaMemsetAsync(p->adam_m, 0, p->n_params * 4, e->stream));
         NNB_CUDA(cudaMemsetAsync(p->adam_v, 0, p->n_params * 4, e->stream));
     }
+    // a tensor-core GEMM that gave up on a bounded wait left garbage in the gradients: report it before
+    // anything is applied to the weights
+    if (!p->cfg.exact) NNB_TRY(tc_check_errors(e));
     if (max_grad_norm > 0.0f || d_norm_out) NNB_TRY(launch_clip_grad_norm(e, p->grads, p->n_params, max_grad_norm, d_norm_out));
     p->adam_t += 1;
     NNB_TRY(launch_adamw(e, p->params, p->grads, p->adam_m, p->adam_v, p->n_params, lr, beta1, beta2, eps, weight_decay,
                          p->adam_t));
     NNB_CUDA(cudaMemsetAsync(p->grads, 0, p->n_params * 4, e->stream));
-    NNB_TRY(policy_requantize(p));
-    return p->cfg.exact ? NNB_OK : tc_check_errors(e);
+    return policy_requantize(p);
 }
 
 nnb_status nnb_policy_release_workspaces(nnb_policy* p)

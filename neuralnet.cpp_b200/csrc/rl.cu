@@ -162,9 +162,9 @@ categorical_fwd_kernel(const float* __restrict__ logits, const int32_t* __restri
 
 // dlogits = (onehot - p) * up_lp + (-p * (log p + H)) * up_ent
 __global__ void __launch_bounds__(256)
-categorical_bwd_kernel(const float* __restrict__ logits, const int32_t* __restrict__ actions,
+categorical_bwd_kernel(const float* logits /* may be dlogits: in place */, const int32_t* __restrict__ actions,
                        const float* __restrict__ up_lp, const float* __restrict__ up_ent, size_t v,
-                       float* __restrict__ dlogits)
+                       float* dlogits)
 {
     __shared__ float red_f[8];
     __shared__ double red_d[2][8];

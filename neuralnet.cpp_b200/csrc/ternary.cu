@@ -855,7 +855,7 @@ nnb_status launch_act_quant_tm(nnb_engine* e, const void* x, nnb_dtype dtype, si
     NNB_REQUIRE(((uintptr_t)q & 15) == 0, "act_quant_tm: q must be 16-byte aligned");
     const size_t smem = k * sizeof(float);
     if (dtype == NNB_F32) {
-        static bool cfg = false;
+        static bool cfg_dev[64] = {}; bool& cfg = cfg_dev[e->device & 63];  // the attribute is per device
         if (!cfg) {
             NNB_CUDA(cudaFuncSetAttribute(act_quant_tm_kernel<float>,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
@@ -863,7 +863,7 @@ nnb_status launch_act_quant_tm(nnb_engine* e, const void* x, nnb_dtype dtype, si
         }
         act_quant_tm_kernel<float><<<(unsigned)t, 256, smem, e->stream>>>((const float*)x, (int)k, q, s, qsum);
     } else if (dtype == NNB_BF16) {
-        static bool cfg = false;
+        static bool cfg_dev[64] = {}; bool& cfg = cfg_dev[e->device & 63];  // the attribute is per device
         if (!cfg) {
             NNB_CUDA(cudaFuncSetAttribute(act_quant_tm_kernel<__nv_bfloat16>,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));

@@ -396,8 +396,8 @@ attn_bwd_dkv_kernel(const float* __restrict__ q, const float* __restrict__ k, co
 // gradients are reduced in shared memory and flushed with one atomic per feature per CTA.
 constexpr int RN_TOK = 16;
 __global__ void __launch_bounds__(256)
-rmsnorm_bwd_kernel(const float* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ dy,
-                   const float* __restrict__ residual, size_t T, int F, float* __restrict__ dx,
+rmsnorm_bwd_kernel(const float* x /* may be dx: in place */, const float* __restrict__ gamma, const float* __restrict__ dy,
+                   const float* __restrict__ residual, size_t T, int F, float* dx,
                    float* __restrict__ dgamma)
 {
     extern __shared__ float dg[];  // F
@@ -436,8 +436,8 @@ rmsnorm_bwd_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
 // tokens with a grid-wide stride, so there is one shared-memory reduction and one flush per CTA.
 template <int NV>
 __global__ void __launch_bounds__(256)
-rmsnorm_bwd_vec_kernel(const float* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ dy,
-                       const float* __restrict__ residual, size_t T, float* __restrict__ dx, float* __restrict__ dgamma)
+rmsnorm_bwd_vec_kernel(const float* x /* may be dx: in place */, const float* __restrict__ gamma, const float* __restrict__ dy,
+                       const float* __restrict__ residual, size_t T, float* dx, float* __restrict__ dgamma)
 {
     constexpr int F = 128 * NV;
     __shared__ float dg[F];
@@ -742,7 +742,7 @@ nnb_status launch_attn_fwd(nnb_engine* e, bool exact, const float* q, const floa
         return st;
     }
     const size_t smem = (2 * 32 * (dk + 1) + ATT_WARPS * dk) * sizeof(float);
-    static size_t cfg = 0;
+    static size_t cfg_dev[64] = {}; size_t& cfg = cfg_dev[e->device & 63];
     if (smem > cfg) {
         NNB_CUDA(cudaFuncSetAttribute(attn_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         NNB_CUDA(cudaFuncSetAttribute(attn_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -781,7 +781,7 @@ nnb_status launch_attn_bwd(nnb_engine* e, bool exact, const float* q, const floa
                                                                                  rows, delta);
     const size_t smem_q = (2 * 32 * (dk + 1) + 2 * ATT_WARPS * dk) * sizeof(float);
     const size_t smem_kv = (2 * 32 * (dk + 1) + 2 * ATT_WARPS * dk + 64) * sizeof(float);
-    static size_t cfg_q = 0, cfg_kv = 0;
+    static size_t cfg_q_dev[64] = {}, cfg_kv_dev[64] = {}; size_t &cfg_q = cfg_q_dev[e->device & 63], &cfg_kv = cfg_kv_dev[e->device & 63];
     if (smem_q > cfg_q) {
         NNB_CUDA(cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_q));
         cfg_q = smem_q;
@@ -814,7 +814,7 @@ nnb_status launch_rmsnorm_bwd(nnb_engine* e, const float* x, const float* gamma,
         return NNB_OK;
     }
     const size_t smem = F * sizeof(float);
-    static size_t cfg = 0;
+    static size_t cfg_dev[64] = {}; size_t& cfg = cfg_dev[e->device & 63];
     if (smem > cfg && smem > 48 * 1024) {
         NNB_CUDA(cudaFuncSetAttribute(rmsnorm_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         cfg = smem;

@@ -252,9 +252,28 @@ def optimizer_step(self, lr, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01
     return norm
 
 
+def set_step_timing(self, stride: int):
+    """Record a CUDA event every `stride` decode steps of the following rollouts (0 = off)."""
+    check(self._lib.nnb_rollout_set_step_timing(self._h, int(stride)))
+
+
+def step_times(self):
+    """(ms, pos) arrays of the last rollout's timed segments: device time of each run of `stride` decode steps and
+    the position its first step consumed."""
+    n = C.c_size_t()
+    check(self._lib.nnb_rollout_step_times(self._h, None, None, 0, C.byref(n)))
+    ms = np.zeros(n.value, np.float32)
+    pos = np.zeros(n.value, np.int32)
+    if n.value:
+        check(self._lib.nnb_rollout_step_times(self._h, ms.ctypes.data_as(C.c_void_p), pos.ctypes.data_as(C.c_void_p), n.value,
+                                               C.byref(n)))
+    return ms, pos
+
+
 def release_workspaces(self):
     check(self._lib.nnb_policy_release_workspaces(self._h))
 
 
-for _f in (logprobs, grads_view, zero_grad, train_step, sft_step, optimizer_step, release_workspaces):
+for _f in (logprobs, grads_view, zero_grad, train_step, sft_step, optimizer_step, release_workspaces, set_step_timing,
+           step_times):
     setattr(Policy, _f.__name__, _f)
