@@ -337,6 +337,10 @@ nnb_status nnb_policy_release_workspaces(nnb_policy* p);
 nnb_status nnb_gae(nnb_engine* e, const float* d_rewards, const float* d_values, const float* d_done,
                    const float* d_mask, const float* d_bootstrap, size_t steps, size_t batch, float gamma,
                    float lambda, float* d_advantage, float* d_returns);
+/* MonteCarloReturn::apply (rl_experience.hpp:395-440): ret_t = r_t + gamma * ret_{t+1} * (1 - done_t), each
+ * row multiplied by the mask before it is carried to the previous step; same layout as nnb_gae. */
+nnb_status nnb_monte_carlo_return(nnb_engine* e, const float* d_rewards, const float* d_done, const float* d_mask,
+                                  size_t steps, size_t batch, float gamma, float* d_returns);
 /* GroupAdvantage::apply (rl_experience.hpp:516-545): spans (first_row, row_count) given on the
  * host must be contiguous and cover all n rows, else NNB_ERR_INVALID. */
 nnb_status nnb_group_advantage(nnb_engine* e, const float* d_returns, size_t n, const int32_t* h_first,
@@ -382,6 +386,10 @@ nnb_status nnb_token_objective(nnb_engine* e, const float* d_logp, const float* 
 nnb_status nnb_clipped_value(nnb_engine* e, const float* d_value, const float* d_returns, const float* d_old_value,
                              const float* d_mask, size_t n, float units, float clip_eps, float coef, float* d_grad,
                              float* d_report);
+/* ValueRegressionObjective (rl_policy.hpp:393-439): loss = coef * sum (V-R)^2 mask / units,
+ * d_grad = (V-R) * mask * (2*coef/units); d_report[2] = loss, units (may be NULL) */
+nnb_status nnb_value_regression(nnb_engine* e, const float* d_value, const float* d_returns, const float* d_mask, size_t n,
+                                float units, float coef, float* d_grad, float* d_report);
 /* Optimizer::clip_grad_norm (include/neuralnet.cpp/compute_optimizer.hpp:134-187); the norm
  * before clipping is written to d_norm_out (may be NULL) */
 nnb_status nnb_clip_grad_norm(nnb_engine* e, float* d_grads, size_t n, float max_norm, float* d_norm_out);

@@ -89,6 +89,8 @@ _SIGNATURES = {
     "nnb_categorical_backward": (_I, [_P, _P, _P, _P, _P, _SZ, _SZ, _P]),
     "nnb_token_objective": (_I, [_P, _P, _P, _P, _P, _P, _P, _SZ, C.c_float, C.c_float, C.c_float, C.c_float, _P, _P, _P]),
     "nnb_clipped_value": (_I, [_P, _P, _P, _P, _P, _SZ, C.c_float, C.c_float, C.c_float, _P, _P]),
+    "nnb_value_regression": (_I, [_P, _P, _P, _P, _SZ, C.c_float, C.c_float, _P, _P]),
+    "nnb_monte_carlo_return": (_I, [_P, _P, _P, _P, _SZ, _SZ, C.c_float, _P]),
     "nnb_clip_grad_norm": (_I, [_P, _P, _SZ, C.c_float, _P]),
     "nnb_scale_inplace": (_I, [_P, _P, _SZ, C.c_float]),
     "nnb_adamw_step": (_I, [_P, _P, _P, _P, _P, _SZ, C.c_float, C.c_float, C.c_float, C.c_float, C.c_float, _I]),

@@ -46,6 +46,26 @@ __global__ void gae_kernel(const float* __restrict__ rewards, const float* __res
     }
 }
 
+// MonteCarloReturn::apply (include/neuralnet.cpp/rl_experience.hpp:395-440): ret_t = r_t + gamma * ret_{t+1} * cont,
+// cont = 1 - done, the row multiplied by the mask (and the masked row carried to the previous step).
+__global__ void mc_return_kernel(const float* __restrict__ rewards, const float* __restrict__ done,
+                                 const float* __restrict__ mask, size_t steps, size_t batch, float gamma,
+                                 float* __restrict__ out)
+{
+    const size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= batch) return;
+    float next = 0.0f;
+    for (size_t ti = steps; ti-- > 0;) {
+        const size_t i = ti * batch + b;
+        const float r = rewards[i];
+        const float cont = done ? __fsub_rn(__fadd_rn(__fmul_rn(r, 0.0f), 1.0f), done[i]) : 1.0f;
+        float row = __fadd_rn(r, __fmul_rn(__fmul_rn(next, gamma), cont));
+        if (mask) row = __fmul_rn(row, mask[i]);
+        out[i] = row;
+        next = row;
+    }
+}
+
 // ------------------------------------------------------- group advantages
 // One warp per contiguous span of rows: segmented warp reduction of sum, sum of squares and
 // count, then (x - mean) * (1/sqrt(var)); zero when the variance is <= eps^2.
@@ -330,6 +350,33 @@ __global__ void clipped_value_kernel(const float* __restrict__ value, const floa
     }
 }
 
+// ValueRegressionObjective (include/neuralnet.cpp/rl_policy.hpp:393-439): loss = coef * sum (v-R)^2 m / units,
+// grad = (v-R) * m * (2*coef/units); acc[0] = units, acc[1] = sum (v-R)^2 m
+__global__ void value_regression_kernel(const float* __restrict__ value, const float* __restrict__ returns,
+                                        const float* __restrict__ mask, size_t n, float coef, float* __restrict__ grad,
+                                        double* __restrict__ acc)
+{
+    const float units = (float)acc[0];
+    const bool live = units > 0.0f;
+    const float scale = live ? __fdiv_rn(__fmul_rn(2.0f, coef), units) : 0.0f;
+    double s0 = 0.0;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const float m = mask[i];
+        const float diff = __fsub_rn(value[i], returns[i]);
+        grad[i] = __fmul_rn(__fmul_rn(diff, m), scale);
+        s0 += (double)__fmul_rn(__fmul_rn(diff, diff), m);
+    }
+    s0 = warp_sum_d(s0);
+    if ((threadIdx.x & 31) == 0) atomicAdd(acc + 1, s0);
+}
+
+__global__ void value_regression_finalize_kernel(const double* __restrict__ acc, float coef, float* __restrict__ report)
+{
+    const float units = (float)acc[0];
+    report[0] = units > 0.0f ? __fdiv_rn(__fmul_rn(coef, (float)acc[1]), units) : 0.0f;
+    report[1] = units;
+}
+
 __global__ void clipped_value_finalize_kernel(const double* __restrict__ acc, float coef, float* __restrict__ report)
 {
     const float units = (float)acc[0];
@@ -507,6 +554,34 @@ nnb_status launch_clipped_value(nnb_engine* e, const float* value, const float* 
     return NNB_OK;
 }
 
+nnb_status launch_value_regression(nnb_engine* e, const float* value, const float* returns, const float* mask, size_t n,
+                                   float units_override, float coef, float* grad, float* report)
+{
+    NNB_REQUIRE(value && returns && mask && grad && n > 0, "value_regression: bad arguments");
+    double* acc;
+    NNB_TRY(acc_block(e, &acc));
+    if (units_override > 0.0f) set_double_kernel<<<1, 1, 0, e->stream>>>(acc, (double)units_override);
+    else sum_kernel<<<grid_for(e, n, 256), 256, 0, e->stream>>>(mask, n, acc);
+    value_regression_kernel<<<grid_for(e, n, 256), 256, 0, e->stream>>>(value, returns, mask, n, coef, grad, acc);
+    e->launches += 2;
+    if (report) {
+        value_regression_finalize_kernel<<<1, 1, 0, e->stream>>>(acc, coef, report);
+        e->launches++;
+    }
+    NNB_CHECK_LAUNCH("value_regression kernels");
+    return NNB_OK;
+}
+
+nnb_status launch_mc_return(nnb_engine* e, const float* rewards, const float* done, const float* mask, size_t steps,
+                            size_t batch, float gamma, float* out)
+{
+    NNB_REQUIRE(rewards && out && steps > 0 && batch > 0, "monte_carlo_return: rewards must not be empty");
+    mc_return_kernel<<<(unsigned)ceil_div(batch, 128), 128, 0, e->stream>>>(rewards, done, mask, steps, batch, gamma, out);
+    e->launches++;
+    NNB_CHECK_LAUNCH("mc_return_kernel");
+    return NNB_OK;
+}
+
 nnb_status launch_clip_grad_norm(nnb_engine* e, float* g, size_t n, float max_norm, float* norm_out)
 {
     NNB_REQUIRE(g && n > 0, "clip_grad_norm: bad arguments");
@@ -614,6 +689,20 @@ nnb_status nnb_clipped_value(nnb_engine* e, const float* d_value, const float* d
     NNB_REQUIRE(e, "engine is NULL");
     return launch_clipped_value(e, d_value, d_returns, d_old_value, d_mask, n, units, clip_eps, coef, d_grad,
                                 d_report);
+}
+
+nnb_status nnb_value_regression(nnb_engine* e, const float* d_value, const float* d_returns, const float* d_mask, size_t n,
+                                float units, float coef, float* d_grad, float* d_report)
+{
+    NNB_REQUIRE(e, "engine is NULL");
+    return launch_value_regression(e, d_value, d_returns, d_mask, n, units, coef, d_grad, d_report);
+}
+
+nnb_status nnb_monte_carlo_return(nnb_engine* e, const float* d_rewards, const float* d_done, const float* d_mask,
+                                  size_t steps, size_t batch, float gamma, float* d_returns)
+{
+    NNB_REQUIRE(e, "engine is NULL");
+    return launch_mc_return(e, d_rewards, d_done, d_mask, steps, batch, gamma, d_returns);
 }
 
 nnb_status nnb_clip_grad_norm(nnb_engine* e, float* d_grads, size_t n, float max_norm, float* d_norm_out)

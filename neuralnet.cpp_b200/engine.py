@@ -245,6 +245,23 @@ def clipped_value(self, value, returns, old_value, mask, units=0.0, clip_eps=0.2
     return grad, report
 
 
+def value_regression(self, value, returns, mask, units=0.0, coef=1.0):
+    """ValueRegressionObjective — returns (grad, report[2] = loss, units)."""
+    n = value.numel()
+    grad, report = _f32(self, n), _f32(self, 2)
+    check(self._lib.nnb_value_regression(self._h, _ptr(value), _ptr(returns), _ptr(mask), n, units, coef, _ptr(grad),
+                                         _ptr(report)))
+    return grad, report
+
+
+def monte_carlo_return(self, rewards, done=None, mask=None, gamma=0.99):
+    """MonteCarloReturn::apply — (steps, batch) tensors, row = time."""
+    steps, batch = rewards.shape
+    out = _f32(self, steps, batch)
+    check(self._lib.nnb_monte_carlo_return(self._h, _ptr(rewards), _ptr(done), _ptr(mask), steps, batch, gamma, _ptr(out)))
+    return out
+
+
 def clip_grad_norm(self, grads, max_norm):
     norm = _f32(self, 1)
     check(self._lib.nnb_clip_grad_norm(self._h, _ptr(grads), grads.numel(), max_norm, _ptr(norm)))
@@ -262,7 +279,8 @@ def adamw_step(self, params, grads, m, v, lr, t, beta1=0.9, beta2=0.999, eps=1e-
 
 
 for _f in (gae, group_advantage, masked_normalize, categorical_logp_entropy, categorical_backward,
-           token_objective, clipped_value, clip_grad_norm, scale_inplace, adamw_step):
+           token_objective, clipped_value, value_regression, monte_carlo_return, clip_grad_norm, scale_inplace,
+           adamw_step):
     setattr(Engine, _f.__name__, _f)
 
 

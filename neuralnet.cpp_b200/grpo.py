@@ -1,10 +1,16 @@
-"""GRPO / PPO step drivers: the consumer-side loop the reference leaves to the user of
-RLTrainingPipeline (include/neuralnet.cpp/rl_pipeline.hpp:312-350): rollout source -> rewards ->
-advantages -> micro-batched objective/backward -> gradient all-reduce -> optimizer step.
+"""GRPO step driver: the consumer side of the reference's RLTrainingPipeline
+(include/neuralnet.cpp/rl_pipeline.hpp:312-350) for GrpoObjective (rl_policy.hpp:866-953) on the ternary
+GPT policy: GptRolloutSource produces a TensorRecord on the device (rollout, rewards, GroupAdvantage,
+reference log-probs), update() runs the micro-batched objective / backward, the gradient all-reduce and
+the optimizer step.
 
 Sharding: whole prompt groups stay on one rank (GroupAdvantage needs no collective); the only
 collectives are the all-reduce (sum) of the flat gradient buffer and of a few report scalars.
 torch.distributed is plumbing only; every numeric step is a call into libnn-b200.so.
+
+The KL term against a frozen reference policy (kl_coef, ref_log_prob) is this engine's addition: the
+reference's GrpoObjective has the clipped policy term and the entropy bonus only, and its
+SampledKlObjective penalises logp - old_log_prob.  kl_coef = 0 gives the reference preset.
 """
 from __future__ import annotations
 
@@ -12,8 +18,24 @@ from dataclasses import dataclass
 
 import torch
 
-from ._lib import NnbError
+from .pipeline import GptRolloutSource, RolloutSpec, TensorRecord
 from .policy import Policy
+
+# names of the ten floats nnb_policy_train_step reports (PpoReport / GrpoReport fields of the reference,
+# rl_policy.hpp:787-797,858-864, plus the pieces they are sums of)
+REPORT_FIELDS = ("policy_loss", "ratio_mean", "approx_kl", "policy_clip_fraction", "kl_loss", "entropy_loss", "entropy",
+                 "units", "value_loss", "value_clip_fraction")
+
+
+def report_dict(report: torch.Tensor) -> dict:
+    """The report vector as the reference's report structs name it: PpoReport.loss = policy + entropy + value
+    terms (plus this engine's KL term), PpoReport.policy_loss = clipped term + entropy term."""
+    v = [float(x) for x in report.detach().cpu().tolist()]
+    d = dict(zip(REPORT_FIELDS, v))
+    d["clipped_policy_loss"] = d["policy_loss"]
+    d["policy_loss"] = d["clipped_policy_loss"] + d["entropy_loss"]
+    d["loss"] = d["policy_loss"] + d["value_loss"] + d["kl_loss"]
+    return d
 
 
 @dataclass
@@ -44,77 +66,54 @@ def hash_reward(tokens_gen: torch.Tensor, seed: int, p: float = 0.3) -> torch.Te
     return ((h % 1000003).to(torch.float32) / 1000003.0 < p).to(torch.float32)
 
 
-class GrpoTrainer:
-    def __init__(self, policy: Policy, ref_policy: Policy | None, cfg: GrpoConfig, dist_group=None):
-        self.policy, self.ref, self.cfg = policy, ref_policy, cfg
+class _DistMixin:
+    def _init_dist(self, dist_group):
         self.dist = dist_group if dist_group is not None else (
             torch.distributed if torch.distributed.is_available() and torch.distributed.is_initialized() else None)
         self.rank = self.dist.get_rank() if self.dist else 0
         self.world = self.dist.get_world_size() if self.dist else 1
-        self.timings = {}
-        self._chunk = cfg.rollout_chunk  # shrinks if a KV cache of that many sequences does not fit
 
     def _allreduce(self, t):
         if self.dist and self.world > 1:
             self.dist.all_reduce(t)
         return t
 
-    def rollout(self, prompts: torch.Tensor, seed: int, seq0: int):
-        """prompts (n_groups_local, P) -> tokens (N, P+G), old_logp (N, G); groups are contiguous rows."""
-        c = self.cfg
-        rep = prompts.repeat_interleave(c.group_size, dim=0).contiguous()
-        n = rep.shape[0]
-        chunk = max(c.group_size, (min(self._chunk, n) // c.group_size) * c.group_size)
-        while True:
-            toks, lps = [], []
-            try:
-                for a in range(0, n, chunk):
-                    t, lp, _ = self.policy.rollout(rep[a:a + chunk].contiguous(), c.max_new, temperature=c.temperature,
-                                                   top_k=c.top_k, seed=seed, seq0=seq0 + a, group_size=c.group_size)
-                    toks.append(t)
-                    lps.append(lp)
-                return torch.cat(toks), torch.cat(lps)
-            except NnbError as ex:
-                # the engine refuses a KV cache that does not fit (status -4) before allocating it: decode
-                # fewer sequences together.  The samples do not depend on the chunking (Philox counters are
-                # per sequence), so the retry reproduces the same rollout.
-                if getattr(ex, "status", 0) != -4 or chunk <= c.group_size:
-                    raise
-                chunk = max(c.group_size, (chunk // 2 // c.group_size) * c.group_size)
-                self._chunk = chunk
 
-    def step(self, prompts: torch.Tensor, reward_fn, seed: int, timers=None):
-        """One GRPO step on this rank's prompt groups.  reward_fn(tokens (N,S)) -> (N,) f32 on the device."""
-        c, pol, eng = self.cfg, self.policy, self.policy.engine
-        n_groups = prompts.shape[0]
-        N = n_groups * c.group_size
-        seq0 = self.rank * N
+class GrpoTrainer(_DistMixin):
+    def __init__(self, policy: Policy, ref_policy: Policy | None, cfg: GrpoConfig, dist_group=None):
+        self.policy, self.ref, self.cfg = policy, ref_policy, cfg
+        self._init_dist(dist_group)
+        spec = RolloutSpec(prompt_len=cfg.prompt_len, max_new=cfg.max_new, group_size=cfg.group_size,
+                           temperature=cfg.temperature, top_k=cfg.top_k, rollout_chunk=cfg.rollout_chunk,
+                           advantage="group", advantage_eps=cfg.advantage_eps, eval_micro_batch=cfg.micro_batch)
+        self.source = GptRolloutSource(policy, spec, None, None, ref_policy if cfg.kl_coef != 0.0 else None)
+
+    def collect(self, prompts: torch.Tensor, reward_fn, seed: int, timers=None) -> TensorRecord:
+        """This rank's prompt groups -> TensorRecord (tokens, action_mask, advantage, old_log_prob, ref_log_prob)."""
+        src = self.source
+        src.reward_fn = reward_fn
+        src.seq0 = self.rank * prompts.shape[0] * self.cfg.group_size
+        src.on_phase = (lambda name: timers.mark(name)) if timers else None
+        return src.rollout(None, prompts=prompts, seed=seed)
+
+    def update(self, record: TensorRecord, timers=None):
+        c, pol = self.cfg, self.policy
         ev = (lambda name: timers.mark(name)) if timers else (lambda name: None)
-        ev("start")
-        tokens, old_lp = self.rollout(prompts, seed, seq0)
-        ev("rollout")
-        rewards = reward_fn(tokens).contiguous()
-        adv_seq = eng.group_advantage(rewards, [(g * c.group_size, c.group_size) for g in range(n_groups)],
-                                      eps=c.advantage_eps)
-        adv = adv_seq[:, None].expand(N, c.max_new).contiguous()
-        mask = torch.ones((N, c.max_new), device=tokens.device, dtype=torch.float32)
+        tokens, mask = record["tokens"], record["action_mask"]
+        N = tokens.shape[0]
         units = torch.tensor([float(N * c.max_new)], device=tokens.device)
         units_global = float(self._allreduce(units).item()) if self.world > 1 else float(N * c.max_new)
-        ev("advantage")
         mb = c.micro_batch
         # micro-batches made of whole groups let the engine compute a group's shared prompt once
         gs = c.group_size if mb % c.group_size == 0 else 1
-        ref_lp = None
-        if self.ref is not None and c.kl_coef != 0.0:
-            parts = [self.ref.logprobs(tokens[a:a + mb].contiguous(), c.prompt_len, group_size=gs)[0] for a in range(0, N, mb)]
-            ref_lp = torch.cat(parts)
-        ev("reference")
+        ref_lp = record.get("ref_log_prob")
         pol.zero_grad()
         report = torch.zeros(10, device=tokens.device)
         for a in range(0, N, mb):
             sl = slice(a, a + mb)
             report += pol.train_step(tokens[sl].contiguous(), c.prompt_len, mask[sl].contiguous(),
-                                     old_logp=old_lp[sl].contiguous(), advantage=adv[sl].contiguous(),
+                                     old_logp=record["old_log_prob"][sl].contiguous(),
+                                     advantage=record["advantage"][sl].contiguous(),
                                      ref_logp=None if ref_lp is None else ref_lp[sl].contiguous(),
                                      units=units_global, clip_eps=c.clip_eps, kl_coef=c.kl_coef,
                                      entropy_coef=c.entropy_coef, group_size=gs)
@@ -127,4 +126,11 @@ class GrpoTrainer:
         ev("allreduce")
         norm = pol.optimizer_step(c.lr, weight_decay=c.weight_decay, max_grad_norm=c.max_grad_norm)
         ev("optimizer")
-        return {"report": report, "grad_norm": norm, "reward_mean": rewards.mean(), "tokens": tokens}
+        return {"report": report, "grad_norm": norm}
+
+    def step(self, prompts: torch.Tensor, reward_fn, seed: int, timers=None):
+        """One GRPO step on this rank's prompt groups.  reward_fn(tokens (N,S)) -> (N,) f32 on the device."""
+        record = self.collect(prompts, reward_fn, seed, timers)
+        out = self.update(record, timers)
+        out.update(reward_mean=record["reward"].mean(), tokens=record["tokens"], record=record)
+        return out

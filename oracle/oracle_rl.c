@@ -55,6 +55,45 @@ ORC_API void orc_gae(const float* rewards, const float* values, const float* don
     }
 }
 
+/* MonteCarloReturn::apply (include/neuralnet.cpp/rl_experience.hpp:395-440) */
+ORC_API void orc_mc_return(const float* rewards, const float* done, const float* mask, size_t steps, size_t batch,
+                           float gamma, float* out)
+{
+    for (size_t b = 0; b < batch; ++b) {
+        float next = 0.0f;
+        for (size_t ti = steps; ti-- > 0;) {
+            const size_t i = ti * batch + b;
+            const float r = rewards[i];
+            const float cont = done ? (r * 0.0f + 1.0f - done[i]) : 1.0f;
+            float row = r + next * gamma * cont;
+            if (mask) row = row * mask[i];
+            out[i] = row;
+            next = row;
+        }
+    }
+}
+
+/* ValueRegressionObjective (include/neuralnet.cpp/rl_policy.hpp:393-439); returns the loss */
+ORC_API float orc_value_regression(const float* value, const float* returns, const float* mask, size_t n, float coef,
+                                   float* grad)
+{
+    double units_d = 0.0;
+    for (size_t i = 0; i < n; ++i) units_d += (double)mask[i];
+    const float units = (float)units_d;
+    if (units <= 0.0f) {
+        for (size_t i = 0; i < n; ++i) grad[i] = 0.0f;
+        return 0.0f;
+    }
+    double loss_sum = 0.0;
+    const float scale = 2.0f * coef / units;
+    for (size_t i = 0; i < n; ++i) {
+        const float diff = value[i] - returns[i];
+        loss_sum += (double)(diff * diff * mask[i]);
+        grad[i] = diff * mask[i] * scale;
+    }
+    return coef * (float)loss_sum / units;
+}
+
 /* population mean / variance over masked entries; zeros when count <= 0 or var <= eps^2;
  * (x - mean) * (1/sqrt(var)) * mask otherwise (no eps in the divisor) */
 ORC_API void orc_masked_normalize(const float* values, const float* mask, size_t n, float eps, float* out)

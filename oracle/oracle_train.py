@@ -78,13 +78,20 @@ def act_quant(x):
 
 
 class Linear:
-    def __init__(self, w, b):
-        self.w, self.b = w, b
+    """BitLinear with int8 activations.  smooth=True replaces it by the dense float64 linear y = x W^T + b with its
+    exact derivative: the model around it then has no quantiser, so that finite differences apply to it (the
+    reference's gradient checks run on dense layers for the same reason, src/gpt_gradcheck.cpp:1-20)."""
+
+    def __init__(self, w, b, smooth=False):
+        self.w, self.b, self.smooth = w, b, smooth
         self.tau = absmean_tau(w)
         self.trit = ternarise(w, self.tau)
 
     def forward(self, x):
         """x (T,K) f32 -> y (T,out) f32 evaluated like the engine: (tau*s)*float(acc) + b in f32."""
+        if self.smooth:
+            self.x64 = np.asarray(x, np.float64)
+            return self.x64 @ self.w.astype(np.float64).T + self.b.astype(np.float64)[None, :]
         q, s = act_quant(x)
         acc = q.astype(np.float64) @ self.trit.astype(np.float64).T  # exact integers
         y = (self.tau[None, :] * s[:, None]).astype(F32) * acc.astype(F32)
@@ -94,6 +101,10 @@ class Linear:
 
     def backward(self, dy):
         """dy (T,out) f64 -> dx (T,K); accumulates dw, db (STE, int8 path)."""
+        if self.smooth:
+            self.dw = dy.T @ self.x64
+            self.db = dy.sum(0)
+            return dy @ self.w.astype(np.float64)
         t = self.tau.astype(np.float64)
         dx = (dy * t[None, :]) @ self.trit.astype(np.float64)
         self.dw = ((dy * self.s.astype(np.float64)[:, None]).T @ self.q.astype(np.float64)) * t[:, None]
@@ -101,8 +112,13 @@ class Linear:
         return dx
 
 
-def rmsnorm_fwd(x, g):
-    """Output in the engine's f32 rounding order (it feeds a quantiser); cache in float64."""
+def rmsnorm_fwd(x, g, smooth=False):
+    """Output in the engine's f32 rounding order (it feeds a quantiser); cache in float64.
+    smooth=True: everything in float64, no f32 rounding."""
+    if smooth:
+        x64 = np.asarray(x, np.float64)
+        sinv = 1.0 / np.sqrt((x64 * x64).mean(-1, keepdims=True) + 1e-5)
+        return x64 * sinv * np.asarray(g, np.float64), (x64 * sinv, sinv)
     x = x.astype(F32)
     f = x.shape[-1]
     ss = (x * x).astype(np.float64).sum(-1, keepdims=True).astype(F32)
@@ -148,15 +164,18 @@ def rope_apply(x, cos, sin, sign=1.0):
 class OracleTrainer:
     """Holds the parameters (dict of f32 arrays in the engine's flat layout) and runs forward/backward."""
 
-    def __init__(self, cfg, flat):
+    def __init__(self, cfg, flat, smooth=False):
+        """smooth=True: dense float64 linears and no f32 roundings anywhere (flat may then be float64) — the
+        differentiable twin of the model, on which the backward pass is checked by finite differences."""
         self.cfg = cfg
-        self.flat = np.ascontiguousarray(flat, F32)
+        self.smooth = smooth
+        self.flat = np.ascontiguousarray(flat, np.float64 if smooth else F32)
         self.p = unflatten(cfg, self.flat)
         self.lin = {}
         for name in list(self.p):
             if name.endswith(".weight") and not name.startswith("value_head"):
                 base = name[:-7]
-                self.lin[base] = Linear(self.p[name], self.p[base + ".bias"])
+                self.lin[base] = Linear(self.p[name], self.p[base + ".bias"], smooth)
 
     # ------------------------------------------------------------------ forward
     def forward(self, tokens, prompt_len):
@@ -166,9 +185,12 @@ class OracleTrainer:
         dk = d // H
         F = cfg.d_ff
         self.tokens, self.P = tokens, prompt_len
+        sm = self.smooth
+        R = (lambda a: np.asarray(a, np.float64)) if sm else (lambda a: np.asarray(a).astype(F32))  # the engine's f32 rounding
+        ex = np.exp if sm else expf32
         x = p["tok_emb"][tokens]  # (n,S,d) f32
         if cfg.pos == 0:
-            x = (x + p["pos_emb"][None, :S]).astype(F32)
+            x = R(x + p["pos_emb"][None, :S])
         self.cache = []
         cos = sin = None
         if cfg.pos == 1:
@@ -179,7 +201,7 @@ class OracleTrainer:
             pre = f"blocks.{l}."
             c = {}
             c["x_in"] = x
-            n1, c["n1"] = rmsnorm_fwd(x, p[pre + "ln1.gamma"])
+            n1, c["n1"] = rmsnorm_fwd(x, p[pre + "ln1.gamma"], sm)
             flat1 = n1.reshape(n * S, d)
             q = self.lin[pre + "attn.q"].forward(flat1).reshape(n, S, H, dk)
             k = self.lin[pre + "attn.k"].forward(flat1).reshape(n, S, H, dk)
@@ -187,7 +209,7 @@ class OracleTrainer:
             if cfg.pos == 1:
                 q, k = rope_apply(q, cos, sin), rope_apply(k, cos, sin)
             # the reference folds the scale into Q after RoPE (one f32 multiply)
-            qs = (q * F32(1.0 / np.sqrt(F32(dk)))).astype(F32).astype(np.float64)
+            qs = R(q * (1.0 / np.sqrt(np.float64(dk)) if sm else F32(1.0 / np.sqrt(F32(dk))))).astype(np.float64)
             k = k.astype(np.float64)
             sc = np.einsum("bihd,bjhd->bhij", qs, k)
             sc = np.where(causal[None, None], sc, -np.inf)
@@ -196,26 +218,27 @@ class OracleTrainer:
             w = w / w.sum(-1, keepdims=True)
             att = np.einsum("bhij,bjhd->bihd", w, v)
             c.update(qs=qs, k=k, v=v, w=w)
-            a = att.reshape(n * S, d).astype(F32)
+            a = R(att.reshape(n * S, d))
             o = self.lin[pre + "attn.o"].forward(a)
-            x_mid = (x + o.reshape(n, S, d)).astype(F32)
+            x_mid = R(x + o.reshape(n, S, d))
             c["x_mid"] = x_mid
-            n2, c["n2"] = rmsnorm_fwd(x_mid, p[pre + "ln2.gamma"])
+            n2, c["n2"] = rmsnorm_fwd(x_mid, p[pre + "ln2.gamma"], sm)
             h1 = self.lin[pre + "ffn.fc1"].forward(n2.reshape(n * S, d))
             c["h1"] = h1
+            one = 1.0 if sm else F32(1.0)
             if cfg.act == 0:
-                act = (h1 / (F32(1.0) + expf32(-(h1 * F32(1.702)).astype(F32))).astype(F32)).astype(F32)
+                act = R(h1 / R(one + ex(-R(h1 * (1.702 if sm else F32(1.702))))))
             else:
                 g, u = h1[:, :F], h1[:, F:]
-                sg = (F32(1.0) / (F32(1.0) + expf32(-g)).astype(F32)).astype(F32)
-                act = ((g * sg).astype(F32) * u).astype(F32)
-            f2 = self.lin[pre + "ffn.fc2"].forward(act.astype(F32))
-            x = (x_mid + f2.reshape(n, S, d)).astype(F32)
+                sg = R(one / R(one + ex(-g)))
+                act = R(R(g * sg) * u)
+            f2 = self.lin[pre + "ffn.fc2"].forward(R(act))
+            x = R(x_mid + f2.reshape(n, S, d))
             self.cache.append(c)
         self.x_final = x
         G = S - prompt_len
         xd = x[:, prompt_len - 1:S - 1].reshape(n * G, d)
-        hn, self.cf = rmsnorm_fwd(xd, p["ln_f.gamma"])
+        hn, self.cf = rmsnorm_fwd(xd, p["ln_f.gamma"], sm)
         self.hn = hn
         logits = self.lin["lm_head"].forward(hn).astype(np.float64)
         self.logits = logits

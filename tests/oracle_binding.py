@@ -328,6 +328,9 @@ class OracleRL:
         L.orc_entropy_bonus.argtypes = [_f32p, _f32p, _SZ, C.c_float, _f32p]
         L.orc_sampled_kl.restype = C.c_float
         L.orc_sampled_kl.argtypes = [_f32p, _f32p, _f32p, _SZ, C.c_float, _f32p]
+        L.orc_mc_return.argtypes = [_f32p, vp, vp, _SZ, _SZ, C.c_float, _f32p]
+        L.orc_value_regression.restype = C.c_float
+        L.orc_value_regression.argtypes = [_f32p, _f32p, _f32p, _SZ, C.c_float, _f32p]
         L.orc_clipped_value.restype = C.c_float
         L.orc_clipped_value.argtypes = [_f32p, _f32p, _f32p, _f32p, _SZ, C.c_float, C.c_float, _f32p,
                                         C.POINTER(C.c_float)]
@@ -405,6 +408,21 @@ class OracleRL:
         loss = self.L.orc_clipped_value(_c(value, np.float32), _c(returns, np.float32), _c(old_value, np.float32),
                                         _c(mask, np.float32), n, clip_eps, coef, grad, C.byref(cf))
         return float(loss), grad, cf.value
+
+    def value_regression(self, value, returns, mask, coef=1.0):
+        n = len(value)
+        grad = np.empty(n, np.float32)
+        loss = self.L.orc_value_regression(_c(value, np.float32), _c(returns, np.float32), _c(mask, np.float32), n, coef, grad)
+        return float(loss), grad
+
+    def mc_return(self, rewards, done=None, mask=None, gamma=0.99):
+        r = _c(rewards, np.float32)
+        steps, batch = r.shape
+        out = np.empty_like(r)
+        keep = [_c(x, np.float32) if x is not None else None for x in (done, mask)]
+        ptr = [k.ctypes.data_as(C.c_void_p) if k is not None else None for k in keep]
+        self.L.orc_mc_return(r, ptr[0], ptr[1], steps, batch, gamma, out)
+        return out
 
     def clip_grad_norm(self, g, max_norm):
         g = np.ascontiguousarray(g, np.float32).copy()

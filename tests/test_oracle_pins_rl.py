@@ -143,3 +143,19 @@ def test_clip_grad_norm(rl):
     assert abs(norm - 5.0) < 1e-6 and near(g, [0.6, 0.8], 1e-6)
     g, norm = rl.clip_grad_norm([0.3, 0.4], 1.0)
     assert np.array_equal(g, np.array([0.3, 0.4], np.float32))  # below the limit: untouched
+
+
+# src/rl_experience_test.cpp:160-169: rewards {1,2,3}, gamma 0.5 -> {2.75, 3.5, 3.0}
+def test_monte_carlo_return_known_answer(rl):
+    assert near(rl.mc_return([[1], [2], [3]], gamma=0.5).ravel(), [2.75, 3.5, 3.0])
+    # done stops the carry, the mask zeroes the row and what is carried
+    assert near(rl.mc_return([[1], [2], [3]], done=[[0], [1], [0]], gamma=1.0).ravel(), [3.0, 2.0, 3.0])
+    assert near(rl.mc_return([[1], [2], [3]], mask=[[1], [0], [1]], gamma=1.0).ravel(), [1.0, 0.0, 3.0])
+
+
+# src/rl_policy_test.cpp:301-307: value {0.5, 1}, returns {1, 2}, coefficient 2 -> loss 1.25, gradient {-1, -2}
+def test_value_regression_known_answer(rl):
+    loss, grad = rl.value_regression([0.5, 1.0], [1.0, 2.0], [1.0, 1.0], coef=2.0)
+    assert abs(loss - 1.25) < 1e-6 and near(grad, [-1.0, -2.0])
+    loss, grad = rl.value_regression([0.5, 1.0], [1.0, 2.0], [0.0, 0.0], coef=2.0)
+    assert loss == 0.0 and near(grad, [0.0, 0.0])

@@ -165,6 +165,29 @@ def test_clipped_value_random(eng, rl):
     assert abs(rep.cpu().numpy()[0] - loss) <= REL * abs(loss) and abs(rep.cpu().numpy()[1] - cf) <= 1e-5
 
 
+def test_monte_carlo_return_and_value_regression(eng, rl):
+    # src/rl_experience_test.cpp:160-169 and src/rl_policy_test.cpp:301-307 on the GPU, then random cases bit for bit
+    out = eng.monte_carlo_return(dev([[1], [2], [3]], eng), gamma=0.5)
+    assert np.allclose(out.cpu().numpy().ravel(), [2.75, 3.5, 3.0], atol=1e-6)
+    g, rep = eng.value_regression(dev([0.5, 1.0], eng), dev([1.0, 2.0], eng), dev([1.0, 1.0], eng), coef=2.0)
+    assert np.allclose(g.cpu().numpy(), [-1.0, -2.0], atol=1e-6) and abs(rep.cpu().numpy()[0] - 1.25) < 1e-6
+    rng = np.random.default_rng(11)
+    steps, batch = 256, 256
+    r = rng.normal(0, 1, (steps, batch)).astype(np.float32)
+    done = (rng.uniform(size=(steps, batch)) < 0.02).astype(np.float32)
+    mask = (rng.uniform(size=(steps, batch)) < 0.9).astype(np.float32)
+    for d, m in ((None, None), (done, None), (done, mask)):
+        want = rl.mc_return(r, d, m, gamma=0.99)
+        got = eng.monte_carlo_return(dev(r, eng), None if d is None else dev(d, eng), None if m is None else dev(m, eng), gamma=0.99)
+        assert np.array_equal(got.cpu().numpy().view(np.uint32), want.view(np.uint32))
+    n = 5000
+    v, ret = (rng.normal(0, 1, n).astype(np.float32) for _ in range(2))
+    m = (rng.uniform(size=n) < 0.9).astype(np.float32)
+    loss, grad = rl.value_regression(v, ret, m, coef=0.5)
+    g, rep = eng.value_regression(dev(v, eng), dev(ret, eng), dev(m, eng), coef=0.5)
+    assert close(g, grad) and abs(rep.cpu().numpy()[0] - loss) <= REL * abs(loss)
+
+
 def test_adamw_and_clip(eng, rl):
     rng = np.random.default_rng(6)
     n = 100003

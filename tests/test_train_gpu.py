@@ -330,3 +330,59 @@ def test_full_size_micro_batch_grouped_equals_plain(pkg, eng):
     diff = (lp_plain - old_lp).abs()
     assert diff.mean().item() < 2e-2 and bool(torch.isfinite(lp_plain).all())
     pol.release_workspaces()
+
+
+def test_fast_mode_deviation_from_the_restatement_on_the_tiny_configuration(pkg, eng):
+    """The numeric mode the benchmark runs, measured against the CPU restatement on the tiny GRPO configuration
+    (2 groups x 8, prompt 32 + 64): log-probs, loss and gradients.  The bounds are what bf16 attention / backward
+    operands and the int8 activations they flip cost; the exact mode meets 1e-3 on the same inputs."""
+    from neuralnet_cpp_b200.parity import compare_gradients, fast_vs_exact
+
+    dev_stats, st = fast_vs_exact(pkg, eng)
+    cfg = st["cfg"]
+    tr = ot.OracleTrainer(cfg, st["flat"])
+    tok = st["tokens"].cpu().numpy()
+    lp_ref, ent_ref, _ = tr.forward(tok, 32)
+    rep_ref, up_lp, _, _ = tr.objective(lp_ref, ent_ref, st["mask"].cpu().numpy(), st["old_lp"].cpu().numpy(), st["adv"].cpu().numpy(),
+                                        clip_eps=0.2)
+    g_ref = tr.backward(up_lp)
+    # exact mode: the stated gate
+    assert rel_err(st["lp_exact"], lp_ref) <= REL
+    ge = compare_gradients(cfg, st["g_exact"], g_ref)
+    assert ge["grad_rel_max"] <= REL, ge
+    # fast mode: measured deviation (printed with -s), bounded
+    lp_dev = np.abs(st["lp_fast"] - lp_ref).max()
+    gf = compare_gradients(cfg, st["g_fast"], g_ref)
+    loss_dev = abs(st["rep_fast"][0] - rep_ref["policy_loss"])
+    print(f"fast mode vs restatement: logp max abs {lp_dev:.3e}, loss abs {loss_dev:.3e}, grad rel max {gf['grad_rel_max']:.3e} "
+          f"({gf['grad_rel_max_tensor']}), grad rel rms {gf['grad_rel_rms']:.3e} ({gf['grad_rel_rms_tensor']})")
+    assert lp_dev <= 5e-2 and loss_dev <= 5e-3
+    assert gf["grad_rel_rms"] <= 0.25, gf
+
+
+def test_fast_mode_backward_with_a_feed_forward_narrower_than_three_model_widths(pkg, eng):
+    """QuickGELU with d_ff = d_model at more than 64 rows and a small vocabulary: the merged q|k|v gradient
+    (rows x 3d) is the widest bf16 operand of the backward, wider than fc1's and the head's."""
+    kw = dict(n_layer=2, d_model=128, n_head=2, d_ff=128, vocab=64, ctx=48, act=0, pos=0)
+    cfg_e, cfg_f = pkg.GptConfig(exact=True, **kw), pkg.GptConfig(exact=False, **kw)
+    flat = cfg_e.init_params(4, bias_std=0.01)
+    pe, pf = pkg.Policy(eng, cfg_e), pkg.Policy(eng, cfg_f)
+    pe.upload_params(flat)
+    pf.upload_params(flat)
+    rng = np.random.default_rng(8)
+    n, S, P = 4, 40, 8
+    tokens = dev(rng.integers(0, 64, (n, S)), eng, np.int32)
+    lp, _, _ = pe.logprobs(tokens, P)
+    old = lp + dev(rng.normal(0, 0.2, (n, S - P)), eng)
+    adv = dev(rng.normal(0, 1, (n, S - P)), eng)
+    mask = dev(np.ones((n, S - P)), eng)
+    for pol in (pe, pf):
+        pol.zero_grad()
+        pol.train_step(tokens, P, mask, old_logp=old, advantage=adv)
+    eng.check_device_errors()
+    ge, gf = pe.grads_view().cpu().numpy(), pf.grads_view().cpu().numpy()
+    for name, off, shape in cfg_e.param_layout()[0]:
+        size = int(np.prod(shape))
+        a, b = ge[off:off + size].astype(np.float64), gf[off:off + size].astype(np.float64)
+        rms = np.sqrt(((a - b) ** 2).mean()) / max(np.sqrt((a ** 2).mean()), 1e-12)
+        assert rms <= 0.2, f"{name}: rms relative difference {rms:.3f}"
