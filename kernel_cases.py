@@ -1,6 +1,6 @@
 """Runs one kernel (or one phase) of the RL-step path a few times on its benchmark shape.
 
-    python neuralnet.cpp_b200/kernel_cases.py <case> [args]
+    python kernel_cases.py <case> [args]
 
 Used for Nsight Compute captures and quick timing; every case prints its CUDA-event time.  Cases:
   fwd          int8 ternary forward GEMM (tcgen05), T=10240 K=2048 O=11264
@@ -9,6 +9,7 @@ Used for Nsight Compute captures and quick timing; every case prints its CUDA-ev
   attn_decode  decode attention of 512 sequences x 16 heads x 128 at position 400, fused int8 output
   train [n]    reference log-probs + one training micro-batch of n (16) sequences x 640 on the 1B policy
   rollout [B P new]   batched rollout on the 1B policy (default 512 16 24)
+  rollout3b [B P new] batched rollout on the 3B-shaped decode policy (26 layers, d 3200, 32 heads of 100; default 128 16 48)
 """
 import os
 import sys
@@ -16,10 +17,11 @@ import sys
 import numpy as np
 import torch
 
-sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 from __graft_entry__ import load_package  # noqa: E402
 
 MODEL_1B = dict(n_layer=24, d_model=2048, n_head=16, d_ff=5632, vocab=32000, ctx=640, act=1, pos=1)
+MODEL_3B = dict(n_layer=26, d_model=3200, n_head=32, d_ff=8640, vocab=32002, ctx=2048, act=1, pos=1)
 
 
 def _rand_packed(dev, *shape):
@@ -42,8 +44,8 @@ def _timed(name, fn, reps=4):
     print(f"{name}: {a.elapsed_time(b) / reps * 1e3:.1f} us per call")
 
 
-def _policy(pkg, eng):
-    cfg = pkg.GptConfig(exact=False, **MODEL_1B)
+def _policy(pkg, eng, model=MODEL_1B):
+    cfg = pkg.GptConfig(exact=False, **model)
     pol = pkg.Policy(eng, cfg)
     g = torch.Generator(device=eng.device)
     g.manual_seed(1)
@@ -118,6 +120,14 @@ def main(argv):
         cfg, pol, g = _policy(pkg, eng)
         prompts = torch.randint(0, cfg.vocab, (B, P), device=dev, dtype=torch.int32, generator=g)
         _timed(f"rollout {B} x ({P}+{new})", lambda: pol.rollout(prompts, new, temperature=0.8, top_k=50, seed=1), reps=1)
+    elif case == "rollout3b":
+        B, P, new = (int(a) for a in argv[2:5]) if len(argv) > 4 else (128, 16, 48)
+        cfg, pol, g = _policy(pkg, eng, MODEL_3B)
+        prompts = torch.randint(0, cfg.vocab, (B, P), device=dev, dtype=torch.int32, generator=g)
+        pol.set_step_timing(8)
+        _timed(f"3B-shaped rollout {B} x ({P}+{new})", lambda: pol.rollout(prompts, new, temperature=0.8, top_k=50, seed=1), reps=1)
+        ms, pos = pol.step_times()
+        print("ms per step by position:", " ".join(f"{p}:{m / 8:.3f}" for m, p in zip(ms, pos)))
     else:
         raise SystemExit(__doc__)
     eng.check_device_errors()
