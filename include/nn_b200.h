@@ -251,6 +251,31 @@ nnb_status nnb_rollout(nnb_policy* p, const int32_t* d_prompts, size_t n_seq, si
 nnb_status nnb_rollout_grouped(nnb_policy* p, const int32_t* d_prompts, size_t n_seq, size_t prompt_len, size_t max_new,
                                size_t group_size, float temperature, int top_k, uint64_t seed, uint32_t seq0,
                                int32_t* d_tokens, float* d_logp, float* d_logits);
+/* SamplingConfig of the reference (include/neuralnet.cpp/compute_layer_base.hpp:1002-1022) for the batched
+ * rollout; the sampler applies its fields in the reference's order (compute_layer_base.hpp:1025-1163):
+ * logit bias -> repeat penalty over the distinct tokens of the last repeat_window tokens of the sequence so far
+ * (0 = all of it; positive logits are divided by the penalty, the others multiplied) -> temperature -> top-k ->
+ * softmax over the candidates -> top-p -> greedy (temperature <= 0) or inverse CDF.
+ * d_logit_bias (vocab) f32, optional, is added to the raw logits first: the device-side form of the reference's
+ * host hook logits_transform (-inf forbids a token).  top_p < 1 needs at most 1024 candidates (top_k in 1..1024,
+ * or a vocabulary of at most 1024), otherwise NNB_ERR_UNSUPPORTED.  eos_token >= 0: a sequence that samples it
+ * at a generated index >= min_new_tokens is finished (GPTModel::generate, compute_layer_gpt.hpp:826-828); its
+ * later tokens are eos_token with log-prob 0, and d_gen_len[b] = tokens generated before it (max_new if never). */
+typedef struct nnb_sampling_config {
+    float temperature; /* <= 0: greedy */
+    int32_t top_k;     /* 0: off */
+    float top_p;       /* >= 1: off */
+    float repeat_penalty; /* <= 0 or 1: off */
+    int32_t repeat_window;
+    uint64_t seed;
+    const float* d_logit_bias;
+    int32_t eos_token; /* < 0: none */
+    int32_t min_new_tokens;
+} nnb_sampling_config;
+/* nnb_rollout_grouped with the full sampling configuration; d_gen_len (n_seq) may be NULL */
+nnb_status nnb_rollout_sampled(nnb_policy* p, const int32_t* d_prompts, size_t n_seq, size_t prompt_len, size_t max_new,
+                               size_t group_size, const nnb_sampling_config* cfg, uint32_t seq0, int32_t* d_tokens,
+                               float* d_logp, float* d_logits, int32_t* d_gen_len);
 /* the same with host buffers: copies prompts in and tokens / log-probs out, and synchronises */
 nnb_status nnb_rollout_host(nnb_policy* p, const int32_t* h_prompts, size_t n_seq, size_t prompt_len,
                             size_t max_new, float temperature, int top_k, uint64_t seed, uint32_t seq0,

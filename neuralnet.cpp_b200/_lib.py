@@ -95,6 +95,7 @@ _SIGNATURES = {
     "nnb_scale_inplace": (_I, [_P, _P, _SZ, C.c_float]),
     "nnb_adamw_step": (_I, [_P, _P, _P, _P, _P, _SZ, C.c_float, C.c_float, C.c_float, C.c_float, C.c_float, _I]),
     "nnb_rollout_grouped": (_I, [_P, _P, _SZ, _SZ, _SZ, _SZ, C.c_float, _I, C.c_uint64, C.c_uint32, _P, _P, _P]),
+    "nnb_rollout_sampled": (_I, [_P, _P, _SZ, _SZ, _SZ, _SZ, _P, C.c_uint32, _P, _P, _P, _P]),
     "nnb_rollout_set_step_timing": (_I, [_P, _SZ]),
     "nnb_rollout_step_times": (_I, [_P, _P, _P, _SZ, C.POINTER(_SZ)]),
     "nnb_rollout_host": (_I, [_P, _P, _SZ, _SZ, _SZ, C.c_float, _I, C.c_uint64, C.c_uint32, _P, _P]),

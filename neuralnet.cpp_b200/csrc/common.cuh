@@ -144,11 +144,27 @@ nnb_status launch_attn_decode_fused(nnb_engine* e, const float* qkv, void* kcach
                                     const float* rope_cos, const float* rope_sin, const int* d_pos, size_t B, size_t H,
                                     size_t dk, float* att, int8_t* q8, float* s, int32_t* qsum, float* pre_o = nullptr,
                                     float* pre_ml = nullptr);
+// what the sampler applies beyond temperature and top-k (defaults = off); see sample_kernel
+struct SampleOpts {
+    float temperature = 1.0f;
+    int top_k = 0;
+    float top_p = 1.0f;
+    float repeat_penalty = 1.0f;
+    int repeat_window = 0;
+    const float* logit_bias = nullptr;  // (V) added to the raw logits before everything else
+    int eos = -1, min_new = 0;
+    int32_t* done = nullptr;     // (B) set once a sequence has sampled eos; NULL = no end-of-sequence handling
+    int32_t* gen_len = nullptr;  // (B) tokens generated before eos
+};
+nnb_status launch_sample_opts(nnb_engine* e, bool exact, const float* logits, size_t B, size_t V, const SampleOpts& o,
+                              unsigned long long seed, unsigned seq0, const int* d_pos, int prompt_len, int32_t* tokens,
+                              size_t tokens_stride, float* logp, size_t logp_stride, float* entropy);
 nnb_status launch_sample(nnb_engine* e, bool exact, const float* logits, size_t B, size_t V,
                          float temperature, int top_k, unsigned long long seed, unsigned seq0,
                          const int* d_pos, int prompt_len, int32_t* tokens, size_t tokens_stride,
                          float* logp, size_t logp_stride, float* entropy);
 nnb_status launch_set_int(nnb_engine* e, int* p, int v);
+nnb_status launch_fill_int(nnb_engine* e, int* p, size_t n, int v);
 nnb_status launch_add_int(nnb_engine* e, int* p, int v);
 nnb_status launch_embed(nnb_engine* e, const float* tok_emb, const float* pos_emb, const int32_t* tokens,
                         size_t tokens_stride, const int* d_pos, size_t B, size_t d, size_t vocab, float* x);

@@ -1213,13 +1213,23 @@ __device__ __forceinline__ void block_scan2(int& a, int& b, int* wa, int* wb, in
     b = wb[warp] + ib - b;
 }
 
+// SamplingConfig beyond temperature and top-k, in the reference's order (compute_layer_base.hpp:1025-1163):
+// logit bias (the device-side stand-in for the host logits_transform hook) -> repeat penalty over the distinct
+// tokens of the history window (the sequence so far, prompt included; positive logits are divided, others
+// multiplied) -> temperature -> top-k -> softmax over the candidates -> top-p (smallest prefix, by probability
+// descending and index ascending, whose running sum of p reaches top_p; at least one; the kept set is
+// renormalised in ascending index order) -> greedy or inverse CDF.  End of sequence: once a sequence has
+// sampled `eos` at a generated index >= min_new it is marked done, its length is recorded, and every later
+// token of it is `eos` (GPTModel::generate stops there, compute_layer_gpt.hpp:826-828).
 template <bool EXACT>
 __global__ void __launch_bounds__(SAMPLE_NT)
-sample_kernel(const float* __restrict__ logits, int V, float temperature, int top_k,
+sample_kernel(const float* __restrict__ logits, int V, SampleOpts o,
               unsigned long long seed, unsigned seq0, const int* __restrict__ d_pos, int prompt_len,
               int32_t* __restrict__ tokens, int tokens_stride, float* __restrict__ logp, int logp_stride,
               float* __restrict__ entropy)
 {
+    const float temperature = o.temperature;
+    const int top_k = o.top_k;
     typedef typename AccT<EXACT>::type acc_t;
     constexpr int NT = SAMPLE_NT, NW = SAMPLE_NW;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -1280,6 +1290,29 @@ sample_kernel(const float* __restrict__ logits, int V, float temperature, int to
     const float lse = logf((float)se_tot);  // log sum exp(x - mx)
     __syncthreads();
 
+    if (o.logit_bias) {
+        for (int i = tid; i < V; i += NT) lg[i] = __fadd_rn(lg[i], o.logit_bias[i]);
+        __syncthreads();
+    }
+    if (o.repeat_penalty > 0.0f && o.repeat_penalty != 1.0f) {
+        // one bit per vocabulary entry (the histogram area is free here): whoever sets a token's bit first applies
+        // the penalty, so every distinct token of the window is penalised exactly once
+        uint32_t* seen = reinterpret_cast<uint32_t*>(whist);
+        const int n_words = (V + 31) >> 5;
+        for (int i = tid; i < n_words; i += NT) seen[i] = 0u;
+        __syncthreads();
+        const int hist_len = pos + 1;  // the sequence so far: tokens[b, 0 .. pos]
+        const int hbeg = (o.repeat_window > 0 && hist_len > o.repeat_window) ? hist_len - o.repeat_window : 0;
+        const int32_t* hist = tokens + (size_t)b * tokens_stride;
+        for (int i = hbeg + tid; i < hist_len; i += NT) {
+            const int t = hist[i];
+            if (t < 0 || t >= V) continue;  // ids outside the vocabulary are looked at, not penalised
+            const uint32_t bit = 1u << (t & 31);
+            const uint32_t old = atomicOr(&seen[t >> 5], bit);
+            if (!(old & bit)) lg[t] = lg[t] > 0.0f ? __fdiv_rn(lg[t], o.repeat_penalty) : __fmul_rn(lg[t], o.repeat_penalty);
+        }
+        __syncthreads();
+    }
     const bool scale_t = temperature > 0.0f && temperature != 1.0f;
     if (scale_t)
         for (int i = tid; i < V; i += NT) lg[i] = __fdiv_rn(lg[i], temperature);
@@ -1308,11 +1341,17 @@ sample_kernel(const float* __restrict__ logits, int V, float temperature, int to
         __syncthreads();
     } else {
         const float r = philox_uniform(seed, seq0 + (unsigned)b, (unsigned)gen);
-        if (top_k > 0 && top_k < V) {
+        const bool trunc = top_k > 0 && top_k < V;
+        const bool nucleus = o.top_p < 1.0f;
+        if (trunc || (nucleus && V <= 1024)) {
             // radix select of the top_k-th largest key, 8 bits per pass; the row is turned into its keys once
             uint32_t* lgk = reinterpret_cast<uint32_t*>(lg);
             for (int i = tid; i < V; i += NT) lgk[i] = float_key(lg[i]);
             if (tid == 0) { sh_prefix = 0u; sh_need = top_k; }
+            if (!trunc) {  // every entry is a candidate (nucleus sampling over a small vocabulary)
+                for (int i = tid; i < V; i += NT) cand[i] = i;
+                __syncthreads();
+            } else {
             int* myhist = whist + warp * 256;
             for (int pass = 3; pass >= 0; --pass) {
                 for (int i = lane; i < 256; i += 32) myhist[i] = 0;
@@ -1379,8 +1418,9 @@ sample_kernel(const float* __restrict__ logits, int V, float temperature, int to
                 }
             }
             __syncthreads();
+            }  // trunc
             // softmax over the candidates in ascending index order, f32, then inverse CDF
-            const int nc = top_k;
+            const int nc = trunc ? top_k : V;
             float m2 = -INFINITY;
             for (int i = tid; i < nc; i += NT) m2 = fmaxf(m2, key_float(lgk[cand[i]]));
             m2 = warp_max(m2);
@@ -1397,15 +1437,71 @@ sample_kernel(const float* __restrict__ logits, int V, float temperature, int to
                 red_f[0] = sum;
             }
             __syncthreads();
-            const float sum = red_f[0];
-            for (int i = tid; i < nc; i += NT) cval[i] = __fdiv_rn(cval[i], sum);
+            float sum = red_f[0];
+            __syncthreads();
+            if (nucleus && nc > 1) {
+                // candidates ordered by (exponential descending, index ascending): bitonic sort of their slots
+                int* ord = whist;          // 1024 slots
+                int* keepf = whist + 1024; // 1024 flags
+                int n2 = 2;
+                while (n2 < nc) n2 <<= 1;
+                for (int i = tid; i < n2; i += NT) ord[i] = i < nc ? i : -1;
+                auto before = [&](int a, int c) {
+                    if (a < 0) return false;
+                    if (c < 0) return true;
+                    if (cval[a] != cval[c]) return cval[a] > cval[c];
+                    return a < c;
+                };
+                for (int k = 2; k <= n2; k <<= 1)
+                    for (int j = k >> 1; j > 0; j >>= 1) {
+                        __syncthreads();
+                        const int i = tid, ixj = tid ^ j;
+                        if (i < n2 && ixj > i) {
+                            const int a = ord[i], c = ord[ixj];
+                            const bool up = (i & k) == 0;
+                            if (up ? before(c, a) : before(a, c)) { ord[i] = c; ord[ixj] = a; }
+                        }
+                    }
+                __syncthreads();
+                if (tid == 0) {
+                    const float want = o.top_p > 0.0f ? o.top_p : 0.0f;
+                    float cum = 0.0f;
+                    int keep = 0;
+                    for (; keep < nc; ++keep) {
+                        cum = __fadd_rn(cum, __fdiv_rn(cval[ord[keep]], sum));
+                        if (cum >= want) { ++keep; break; }
+                    }
+                    if (keep == 0) keep = 1;
+                    sh_need = keep;
+                }
+                for (int i = tid; i < nc; i += NT) keepf[i] = 0;
+                __syncthreads();
+                const int keep = sh_need;
+                for (int i = tid; i < keep; i += NT) keepf[ord[i]] = 1;
+                __syncthreads();
+                if (tid == 0) {
+                    float ks = 0.0f;
+                    for (int i = 0; i < nc; ++i)
+                        if (keepf[i]) ks = __fadd_rn(ks, cval[i]);
+                    red_f[0] = ks;
+                }
+                __syncthreads();
+                sum = red_f[0];
+                for (int i = tid; i < nc; i += NT)
+                    if (!keepf[i]) cval[i] = -1.0f;  // dropped from the candidate set
+                __syncthreads();
+            }
+            for (int i = tid; i < nc; i += NT)
+                if (cval[i] >= 0.0f) cval[i] = __fdiv_rn(cval[i], sum);
             __syncthreads();
             if (tid == 0) {
                 float cum = 0.0f;
-                int next = cand[nc - 1];
+                int next = -1;
                 for (int i = 0; i < nc; ++i) {
+                    if (cval[i] < 0.0f) continue;
+                    next = cand[i];  // stays the last kept candidate if the draw is never reached
                     cum = __fadd_rn(cum, cval[i]);
-                    if (r <= cum) { next = cand[i]; break; }
+                    if (r <= cum) break;
                 }
                 sh_tok = next;
             }
@@ -1454,10 +1550,20 @@ sample_kernel(const float* __restrict__ logits, int V, float temperature, int to
         }
     }
     if (tid == 0) {
-        const int tok = sh_tok;
+        int tok = sh_tok;
+        bool finished = false;
+        if (o.done) {
+            if (o.done[b]) {
+                finished = true;
+                tok = o.eos;
+            } else if (tok == o.eos && gen >= o.min_new) {
+                o.done[b] = 1;
+                o.gen_len[b] = gen;  // tokens generated before the end-of-sequence token
+            }
+        }
         tokens[(size_t)b * tokens_stride + pos + 1] = tok;
-        if (logp) logp[(size_t)b * logp_stride + gen] = (row[tok] - mx) - lse;
-        if (entropy) entropy[(size_t)b * logp_stride + gen] = lse - (float)(sxe_tot / se_tot);
+        if (logp) logp[(size_t)b * logp_stride + gen] = finished ? 0.0f : (row[tok] - mx) - lse;
+        if (entropy) entropy[(size_t)b * logp_stride + gen] = finished ? 0.0f : lse - (float)(sxe_tot / se_tot);
     }
 }
 
@@ -1466,8 +1572,24 @@ nnb_status launch_sample(nnb_engine* e, bool exact, const float* logits, size_t 
                          const int* d_pos, int prompt_len, int32_t* tokens, size_t tokens_stride,
                          float* logp, size_t logp_stride, float* entropy)
 {
+    SampleOpts o;
+    o.temperature = temperature;
+    o.top_k = top_k;
+    return launch_sample_opts(e, exact, logits, B, V, o, seed, seq0, d_pos, prompt_len, tokens, tokens_stride, logp, logp_stride,
+                              entropy);
+}
+
+nnb_status launch_sample_opts(nnb_engine* e, bool exact, const float* logits, size_t B, size_t V, const SampleOpts& o,
+                              unsigned long long seed, unsigned seq0, const int* d_pos, int prompt_len, int32_t* tokens,
+                              size_t tokens_stride, float* logp, size_t logp_stride, float* entropy)
+{
+    const int top_k = o.top_k;
     NNB_REQUIRE(logits && tokens && B > 0 && V > 0, "sample: bad arguments");
     NNB_REQUIRE(top_k >= 0 && top_k <= 1024, "sample: top_k=%d out of range (0..1024)", top_k);
+    NNB_REQUIRE(V <= 8192 * 32, "sample: vocabulary %zu too large", V);
+    if (o.top_p < 1.0f && o.temperature > 0.0f && !((top_k > 0 && (size_t)top_k < V) || V <= 1024))
+        NNB_FAIL(NNB_ERR_UNSUPPORTED, "sample: top_p needs at most 1024 candidates (set top_k <= 1024; vocabulary is %zu)", V);
+    NNB_REQUIRE((o.done == nullptr) == (o.gen_len == nullptr), "sample: done flags and lengths go together");
     const size_t smem = ((V + 3) & ~(size_t)3) * 4 + 2 * 1024 * 4 + SAMPLE_NW * 256 * 4;
     NNB_REQUIRE(smem <= 220 * 1024, "sample: vocabulary %zu too large for one CTA", V);
     if (exact) {
@@ -1477,7 +1599,7 @@ nnb_status launch_sample(nnb_engine* e, bool exact, const float* logits, size_t 
             NNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             cfg = smem;
         }
-        launch_ex(e, kern, dim3((unsigned)B), dim3(SAMPLE_NT), smem, logits, (int)V, temperature, top_k, seed, seq0, d_pos, prompt_len,
+        launch_ex(e, kern, dim3((unsigned)B), dim3(SAMPLE_NT), smem, logits, (int)V, o, seed, seq0, d_pos, prompt_len,
                   tokens, (int)tokens_stride, logp, (int)logp_stride, entropy);
     } else {
         auto kern = sample_kernel<false>;
@@ -1486,7 +1608,7 @@ nnb_status launch_sample(nnb_engine* e, bool exact, const float* logits, size_t 
             NNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             cfg = smem;
         }
-        launch_ex(e, kern, dim3((unsigned)B), dim3(SAMPLE_NT), smem, logits, (int)V, temperature, top_k, seed, seq0, d_pos, prompt_len,
+        launch_ex(e, kern, dim3((unsigned)B), dim3(SAMPLE_NT), smem, logits, (int)V, o, seed, seq0, d_pos, prompt_len,
                   tokens, (int)tokens_stride, logp, (int)logp_stride, entropy);
     }
     e->launches++;
@@ -1495,6 +1617,18 @@ nnb_status launch_sample(nnb_engine* e, bool exact, const float* logits, size_t 
 }
 
 __global__ void set_int_kernel(int* p, int v) { *p = v; }
+__global__ void fill_int_kernel(int* p, int n, int v)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) p[i] = v;
+}
+nnb_status launch_fill_int(nnb_engine* e, int* p, size_t n, int v)
+{
+    fill_int_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, e->stream>>>(p, (int)n, v);
+    e->launches++;
+    NNB_CHECK_LAUNCH("fill_int_kernel");
+    return NNB_OK;
+}
 __global__ void add_int_kernel(int* p, int v)
 {
     pdl_wait();

@@ -184,7 +184,7 @@ static void free_decode(nnb_policy* p)
 {
     DecodeWs& w = p->dec;
     void* ptrs[] = {w.k, w.v, w.k_pre, w.v_pre, w.tokens_pre, w.x, w.qkv, w.att, w.pre_ml, w.h1, w.logits, w.q8, w.s, w.qsum, w.d_pos,
-                    w.tokens, w.logp};
+                    w.tokens, w.logp, w.done, w.gen_len};
     for (void* q : ptrs)
         if (q) cudaFree(q);
     w = DecodeWs();
@@ -240,6 +240,8 @@ static nnb_status ensure_decode(nnb_policy* p, size_t B, size_t ctx_alloc, size_
     NNB_ALLOC(w.d_pos, 16);
     NNB_ALLOC(w.tokens, B * total * 4);
     NNB_ALLOC(w.logp, B * total * 4);
+    NNB_ALLOC(w.done, B * 4);
+    NNB_ALLOC(w.gen_len, B * 4);
 #undef NNB_ALLOC
     w.B = B;
     w.ctx_alloc = ctx_alloc;
@@ -273,7 +275,7 @@ static bool pdl_enabled()
 
 // one decode step at the position stored in d_pos: consumes tokens[:, pos], appends to the KV
 // cache and, when with_head, samples tokens[:, pos+1]
-static nnb_status decode_step(nnb_policy* p, const StepView& sv, bool with_head, float temperature, int top_k,
+static nnb_status decode_step(nnb_policy* p, const StepView& sv, bool with_head, const SampleOpts& so,
                               unsigned long long seed, unsigned seq0, int prompt_len, bool want_logp)
 {
     nnb_engine* e = p->e;
@@ -336,8 +338,8 @@ static nnb_status decode_step(nnb_policy* p, const StepView& sv, bool with_head,
         const size_t total = w.pre_len + w.ctx_alloc;
         NNB_TRY(launch_row_quant(e, 0, exact, w.x, P + p->lnf_g, B, d, d, w.q8, w.s, w.qsum, nullptr));
         NNB_TRY(policy_linear_fwd(p, p->head, 1, w.q8, w.s, w.qsum, B, nullptr, w.logits, 0));
-        NNB_TRY(launch_sample(e, exact, w.logits, B, V, temperature, top_k, seed, seq0, w.d_pos, prompt_len, w.tokens, total,
-                              want_logp ? w.logp : nullptr, total, nullptr));
+        NNB_TRY(launch_sample_opts(e, exact, w.logits, B, V, so, seed, seq0, w.d_pos, prompt_len, w.tokens, total,
+                                   want_logp ? w.logp : nullptr, total, nullptr));
     }
     return launch_add_int(e, w.d_pos, 1);  // the position lives on the device so a captured step can be replayed
 }
@@ -351,8 +353,8 @@ struct StepGraph {
     int seen = 0;
 };
 
-static nnb_status run_step(nnb_policy* p, StepGraph& g, bool allow_graph, const StepView& sv, bool with_head, float temperature,
-                           int top_k, unsigned long long seed, unsigned seq0, int prompt_len, bool want_logp)
+static nnb_status run_step(nnb_policy* p, StepGraph& g, bool allow_graph, const StepView& sv, bool with_head, const SampleOpts& so,
+                           unsigned long long seed, unsigned seq0, int prompt_len, bool want_logp)
 {
     nnb_engine* e = p->e;
     if (g.exec) {
@@ -362,11 +364,11 @@ static nnb_status run_step(nnb_policy* p, StepGraph& g, bool allow_graph, const 
     }
     if (g.seen == 0 || !allow_graph) {
         g.seen = 1;
-        return decode_step(p, sv, with_head, temperature, top_k, seed, seq0, prompt_len, want_logp);
+        return decode_step(p, sv, with_head, so, seed, seq0, prompt_len, want_logp);
     }
     NNB_CUDA(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
     const unsigned long long l0 = e->launches;
-    const nnb_status cs = decode_step(p, sv, with_head, temperature, top_k, seed, seq0, prompt_len, want_logp);
+    const nnb_status cs = decode_step(p, sv, with_head, so, seed, seq0, prompt_len, want_logp);
     cudaGraph_t graph = nullptr;
     const cudaError_t ce = cudaStreamEndCapture(e->stream, &graph);
     if (cs != NNB_OK) {
@@ -386,8 +388,8 @@ static nnb_status run_step(nnb_policy* p, StepGraph& g, bool allow_graph, const 
 // positions are computed once per group (batch B/group) into a prefix cache that all members read;
 // from position P-1 on every sequence runs on its own.  The arithmetic per sequence is unchanged.
 nnb_status policy_rollout(nnb_policy* p, const int32_t* d_prompts, size_t B, size_t P, size_t max_new, size_t group,
-                          float temperature, int top_k, unsigned long long seed, unsigned seq0,
-                          int32_t* d_tokens, float* d_logp, float* d_logits)
+                          const SampleOpts& so_in, unsigned long long seed, unsigned seq0,
+                          int32_t* d_tokens, float* d_logp, float* d_logits, int32_t* d_gen_len)
 {
     NNB_REQUIRE(p && d_prompts && d_tokens, "rollout: NULL argument");
     NNB_REQUIRE(B > 0 && P > 0 && max_new > 0, "rollout: empty shape");
@@ -401,6 +403,11 @@ nnb_status policy_rollout(nnb_policy* p, const int32_t* d_prompts, size_t B, siz
     const size_t own = total - pre_len;
     NNB_TRY(ensure_decode(p, B, own, group, pre_len));
     DecodeWs& w = p->dec;
+    SampleOpts so = so_in;
+    if (so.eos >= 0 || d_gen_len) {
+        so.done = w.done;
+        so.gen_len = w.gen_len;
+    }
     const size_t V = c.vocab, d = c.d_model;
     const size_t kv_elem = c.exact ? 4 : 2;
     const size_t dkv = c.n_head * attn_decode_kv_pitch(c.exact != 0, d / c.n_head);
@@ -427,6 +434,10 @@ nnb_status policy_rollout(nnb_policy* p, const int32_t* d_prompts, size_t B, siz
             NNB_CUDA(cudaMemcpy2DAsync(w.tokens_pre, pre_len * 4, d_prompts, group * P * 4, pre_len * 4, Bg,
                                        cudaMemcpyDeviceToDevice, e->stream));
         NNB_TRY(launch_set_int(e, w.d_pos, 0));
+        if (so.done) {
+            NNB_CUDA(cudaMemsetAsync(w.done, 0, B * 4, e->stream));
+            NNB_TRY(launch_fill_int(e, w.gen_len, B, (int)max_new));
+        }
         const bool allow_graph = total >= 8;
         size_t t0 = 0;
         if (pre_len > 0 && policy_can_prefill(p)) {
@@ -452,11 +463,11 @@ nnb_status policy_rollout(nnb_policy* p, const int32_t* d_prompts, size_t B, siz
         for (size_t t = t0; t + 1 < total; ++t) {
             if (p->time_stride && (t - t0) % p->time_stride == 0) NNB_TRY(mark(t));
             if (t < pre_len) {
-                NNB_TRY(run_step(p, graphs[0], allow_graph, pre_view, false, temperature, top_k, seed, seq0, (int)P, false));
+                NNB_TRY(run_step(p, graphs[0], allow_graph, pre_view, false, so, seed, seq0, (int)P, false));
                 continue;
             }
             const bool with_head = t + 1 >= P;
-            NNB_TRY(run_step(p, graphs[with_head ? 2 : 1], allow_graph, main_view, with_head, temperature, top_k, seed, seq0,
+            NNB_TRY(run_step(p, graphs[with_head ? 2 : 1], allow_graph, main_view, with_head, so, seed, seq0,
                              (int)P, d_logp != nullptr));
             if (with_head && d_logits) {
                 const size_t gi = t + 1 - P;
@@ -485,6 +496,7 @@ nnb_status policy_rollout(nnb_policy* p, const int32_t* d_prompts, size_t B, siz
     if (d_logp)
         NNB_CUDA(cudaMemcpy2DAsync(d_logp, max_new * 4, w.logp, total * 4, max_new * 4, B,
                                    cudaMemcpyDeviceToDevice, e->stream));
+    if (d_gen_len) NNB_CUDA(cudaMemcpyAsync(d_gen_len, w.gen_len, B * 4, cudaMemcpyDeviceToDevice, e->stream));
     if (swap) {
         NNB_CUDA(cudaEventRecord(ev, e->own_stream));
         NNB_CUDA(cudaStreamWaitEvent(user, ev, 0));
@@ -643,16 +655,40 @@ nnb_status nnb_rollout(nnb_policy* p, const int32_t* d_prompts, size_t n_seq, si
                        size_t max_new, float temperature, int top_k, uint64_t seed, uint32_t seq0,
                        int32_t* d_tokens, float* d_logp, float* d_logits)
 {
-    return policy_rollout(p, d_prompts, n_seq, prompt_len, max_new, 1, temperature, top_k, seed, seq0, d_tokens,
-                          d_logp, d_logits);
+    SampleOpts so;
+    so.temperature = temperature;
+    so.top_k = top_k;
+    return policy_rollout(p, d_prompts, n_seq, prompt_len, max_new, 1, so, seed, seq0, d_tokens, d_logp, d_logits, nullptr);
+}
+
+nnb_status nnb_rollout_sampled(nnb_policy* p, const int32_t* d_prompts, size_t n_seq, size_t prompt_len, size_t max_new,
+                               size_t group_size, const nnb_sampling_config* cfg, uint32_t seq0, int32_t* d_tokens,
+                               float* d_logp, float* d_logits, int32_t* d_gen_len)
+{
+    NNB_REQUIRE(cfg, "rollout_sampled: sampling configuration is NULL");
+    NNB_REQUIRE(cfg->top_k >= 0 && cfg->repeat_window >= 0 && cfg->min_new_tokens >= 0, "rollout_sampled: negative count");
+    SampleOpts so;
+    so.temperature = cfg->temperature;
+    so.top_k = cfg->top_k;
+    so.top_p = cfg->top_p;
+    so.repeat_penalty = cfg->repeat_penalty;
+    so.repeat_window = cfg->repeat_window;
+    so.logit_bias = cfg->d_logit_bias;
+    so.eos = cfg->eos_token;
+    so.min_new = cfg->min_new_tokens;
+    return policy_rollout(p, d_prompts, n_seq, prompt_len, max_new, group_size ? group_size : 1, so, cfg->seed, seq0, d_tokens,
+                          d_logp, d_logits, d_gen_len);
 }
 
 nnb_status nnb_rollout_grouped(nnb_policy* p, const int32_t* d_prompts, size_t n_seq, size_t prompt_len, size_t max_new,
                                size_t group_size, float temperature, int top_k, uint64_t seed, uint32_t seq0,
                                int32_t* d_tokens, float* d_logp, float* d_logits)
 {
-    return policy_rollout(p, d_prompts, n_seq, prompt_len, max_new, group_size, temperature, top_k, seed, seq0, d_tokens,
-                          d_logp, d_logits);
+    SampleOpts so;
+    so.temperature = temperature;
+    so.top_k = top_k;
+    return policy_rollout(p, d_prompts, n_seq, prompt_len, max_new, group_size, so, seed, seq0, d_tokens, d_logp, d_logits,
+                          nullptr);
 }
 
 nnb_status nnb_rollout_host(nnb_policy* p, const int32_t* h_prompts, size_t n_seq, size_t prompt_len,
@@ -670,8 +706,11 @@ nnb_status nnb_rollout_host(nnb_policy* p, const int32_t* h_prompts, size_t n_se
     int32_t* d_tokens = (int32_t*)(base + pb);
     float* d_logp = (float*)(base + pb + tb);
     NNB_CUDA(cudaMemcpyAsync(d_prompts, h_prompts, n_seq * prompt_len * 4, cudaMemcpyHostToDevice, e->stream));
-    NNB_TRY(policy_rollout(p, d_prompts, n_seq, prompt_len, max_new, 1, temperature, top_k, seed, seq0, d_tokens,
-                           h_logp ? d_logp : nullptr, nullptr));
+    SampleOpts so;
+    so.temperature = temperature;
+    so.top_k = top_k;
+    NNB_TRY(policy_rollout(p, d_prompts, n_seq, prompt_len, max_new, 1, so, seed, seq0, d_tokens, h_logp ? d_logp : nullptr,
+                           nullptr, nullptr));
     NNB_CUDA(cudaMemcpyAsync(h_tokens, d_tokens, n_seq * total * 4, cudaMemcpyDeviceToHost, e->stream));
     if (h_logp)
         NNB_CUDA(cudaMemcpyAsync(h_logp, d_logp, n_seq * max_new * 4, cudaMemcpyDeviceToHost, e->stream));

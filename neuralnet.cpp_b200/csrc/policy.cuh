@@ -38,6 +38,7 @@ struct DecodeWs {
     int* d_pos = nullptr;
     int32_t* tokens = nullptr;  // (B, ctx_alloc)
     float* logp = nullptr;      // (B, ctx_alloc), generated index
+    int32_t *done = nullptr, *gen_len = nullptr;  // (B) end-of-sequence flags and generated lengths
 };
 
 }  // namespace nnb

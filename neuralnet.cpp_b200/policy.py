@@ -187,6 +187,44 @@ def _alias(ptr: int, numel: int, dtype, device) -> torch.Tensor:
     return torch.as_tensor(holder, device=device)
 
 
+class _CSampling(C.Structure):
+    _fields_ = [("temperature", C.c_float), ("top_k", C.c_int32), ("top_p", C.c_float), ("repeat_penalty", C.c_float),
+                ("repeat_window", C.c_int32), ("seed", C.c_uint64), ("d_logit_bias", C.c_void_p), ("eos_token", C.c_int32),
+                ("min_new_tokens", C.c_int32)]
+
+
+@dataclass
+class SamplingConfig:
+    """SamplingConfig of the reference (compute_layer_base.hpp:1002-1022); logit_bias (vocab,) f32 on the device stands
+    for its host hook logits_transform; eos_token / min_new_tokens are GPTModel::generate's arguments."""
+    temperature: float = 1.0
+    top_k: int = 0
+    top_p: float = 1.0
+    repeat_penalty: float = 1.0
+    repeat_window: int = 0
+    seed: int = 0
+    logit_bias: torch.Tensor | None = None
+    eos_token: int = -1
+    min_new_tokens: int = 0
+
+
+def rollout_sampled(self, prompts: torch.Tensor, max_new: int, cfg: SamplingConfig, seq0: int = 0, group_size: int = 1,
+                    want_logits: bool = False):
+    """Batched generate with the full sampling configuration -> tokens (B, P+max_new), logp (B, max_new),
+    gen_len (B,) tokens generated before the end-of-sequence token, [logits]."""
+    B, P = prompts.shape
+    dev = self.engine.device
+    tokens = torch.empty((B, P + max_new), device=dev, dtype=torch.int32)
+    logp = torch.empty((B, max_new), device=dev, dtype=torch.float32)
+    glen = torch.empty((B,), device=dev, dtype=torch.int32)
+    logits = torch.empty((B, max_new, self.cfg.vocab), device=dev, dtype=torch.float32) if want_logits else None
+    cc = _CSampling(cfg.temperature, cfg.top_k, cfg.top_p, cfg.repeat_penalty, cfg.repeat_window, cfg.seed,
+                    None if cfg.logit_bias is None else cfg.logit_bias.data_ptr(), cfg.eos_token, cfg.min_new_tokens)
+    check(self._lib.nnb_rollout_sampled(self._h, _ptr(prompts), B, P, max_new, int(group_size), C.byref(cc), C.c_uint32(seq0),
+                                        _ptr(tokens), _ptr(logp), _ptr(logits), _ptr(glen)))
+    return tokens, logp, glen, logits
+
+
 class _CObjective(C.Structure):
     _fields_ = [("d_mask", C.c_void_p), ("d_old_logp", C.c_void_p), ("d_advantage", C.c_void_p),
                 ("d_ref_logp", C.c_void_p), ("d_returns", C.c_void_p), ("d_old_value", C.c_void_p),
@@ -274,6 +312,6 @@ def release_workspaces(self):
     check(self._lib.nnb_policy_release_workspaces(self._h))
 
 
-for _f in (logprobs, grads_view, zero_grad, train_step, sft_step, optimizer_step, release_workspaces, set_step_timing,
+for _f in (rollout_sampled, logprobs, grads_view, zero_grad, train_step, sft_step, optimizer_step, release_workspaces, set_step_timing,
            step_times):
     setattr(Policy, _f.__name__, _f)

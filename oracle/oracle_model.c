@@ -470,6 +470,87 @@ ORC_API int orc_sample_token(float* logits, int n, float temperature, int top_k,
     return next;
 }
 
+/* sample_next_token_ with the whole SamplingConfig (include/neuralnet.cpp/compute_layer_base.hpp:1025-1163):
+ * bias (stands for the logits_transform hook) -> repeat penalty over the distinct tokens of the history window ->
+ * temperature -> top-k -> softmax over the candidates in ascending index order -> top-p -> greedy / inverse CDF.
+ * Greedy takes the largest (penalised) logit among the candidates, ties to the smallest index. */
+ORC_API int orc_sample_token_cfg(float* logits, int n, float temperature, int top_k, float top_p, float repeat_penalty,
+                                 int repeat_window, const float* bias, const int32_t* history, int hist_len, float r)
+{
+    if (bias)
+        for (int i = 0; i < n; ++i) logits[i] += bias[i];
+    if (repeat_penalty > 0.0f && repeat_penalty != 1.0f && hist_len > 0) {
+        const int begin = (repeat_window > 0 && hist_len > repeat_window) ? hist_len - repeat_window : 0;
+        unsigned char* seen = (unsigned char*)calloc((size_t)n, 1);
+        for (int i = begin; i < hist_len; ++i) {
+            const int t = history[i];
+            if (t < 0 || t >= n || seen[t]) continue;
+            seen[t] = 1;
+            logits[t] = (logits[t] > 0.0f) ? logits[t] / repeat_penalty : logits[t] * repeat_penalty;
+        }
+        free(seen);
+    }
+    if (temperature > 0.0f && temperature != 1.0f)
+        for (int i = 0; i < n; ++i) logits[i] /= temperature;
+    int* cand = (int*)malloc(sizeof(int) * (size_t)n);
+    int nc = n;
+    if (top_k > 0 && top_k < n) {
+        cand_t* order = (cand_t*)malloc(sizeof(cand_t) * (size_t)n);
+        for (int i = 0; i < n; ++i) { order[i].v = logits[i]; order[i].i = i; }
+        qsort(order, (size_t)n, sizeof(cand_t), cand_cmp);
+        nc = top_k;
+        for (int i = 0; i < nc; ++i) cand[i] = order[i].i;
+        qsort(cand, (size_t)nc, sizeof(int), int_cmp);
+        free(order);
+    } else {
+        for (int i = 0; i < n; ++i) cand[i] = i;
+    }
+    int next;
+    if (!(temperature > 0.0f)) {
+        next = cand[0];
+        float best = logits[cand[0]];
+        for (int i = 1; i < nc; ++i) if (logits[cand[i]] > best) { best = logits[cand[i]]; next = cand[i]; }
+        free(cand);
+        return next;
+    }
+    float mx = logits[cand[0]];
+    for (int i = 1; i < nc; ++i) if (logits[cand[i]] > mx) mx = logits[cand[i]];
+    float sum = 0.0f;
+    for (int i = 0; i < nc; ++i) { logits[cand[i]] = orc_expf(logits[cand[i]] - mx); sum += logits[cand[i]]; }
+    if (top_p < 1.0f && nc > 1) {
+        cand_t* by = (cand_t*)malloc(sizeof(cand_t) * (size_t)nc);
+        for (int i = 0; i < nc; ++i) { by[i].v = logits[cand[i]]; by[i].i = cand[i]; }
+        qsort(by, (size_t)nc, sizeof(cand_t), cand_cmp);
+        const float want = top_p > 0.0f ? top_p : 0.0f;
+        float cum = 0.0f;
+        int keep = 0;
+        for (; keep < nc; ++keep) {
+            cum += by[keep].v / sum;
+            if (cum >= want) { ++keep; break; }
+        }
+        if (keep == 0) keep = 1;
+        unsigned char* in_keep = (unsigned char*)calloc((size_t)n, 1);
+        for (int i = 0; i < keep; ++i) in_keep[by[i].i] = 1;
+        float kept_sum = 0.0f;
+        int nk = 0;
+        for (int i = 0; i < nc; ++i)
+            if (in_keep[cand[i]]) { kept_sum += logits[cand[i]]; cand[nk++] = cand[i]; }
+        nc = nk;
+        sum = kept_sum;
+        free(in_keep);
+        free(by);
+    }
+    for (int i = 0; i < nc; ++i) logits[cand[i]] /= sum;
+    float cum = 0.0f;
+    next = cand[nc - 1];
+    for (int i = 0; i < nc; ++i) {
+        cum += logits[cand[i]];
+        if (r <= cum) { next = cand[i]; break; }
+    }
+    free(cand);
+    return next;
+}
+
 /* log softmax(logits)[token] and entropy of the raw (untempered) distribution;
  * CategoricalDistribution::log_prob / entropy, include/neuralnet.cpp/rl_policy.hpp:92-143 */
 ORC_API void orc_logprob_entropy(const float* logits, int n, int token, float* logp, float* entropy)
@@ -518,6 +599,53 @@ ORC_API int orc_gpt_rollout(const orc_gpt* m, const int32_t* prompts, int B, int
             const int tok = orc_sample_token(work, V, temperature, top_k, r);
             if (logp_out) orc_logprob_entropy(logits, V, tok, logp_out + (size_t)b * max_new + t, NULL);
             out[P + t] = tok;
+            if (t + 1 < max_new) forward_step(m, st, tok, P + t, logits);
+        }
+        free(logits); free(work);
+        state_free(st);
+    }
+    return 0;
+}
+
+/* orc_gpt_rollout with the whole sampling configuration and end-of-sequence handling: after a sequence samples
+ * `eos` at a generated index >= min_new it is finished (compute_layer_gpt.hpp:826-828); the rest of its row is
+ * filled with eos, log-prob 0, and gen_len_out[b] = tokens generated before it (max_new if never). */
+ORC_API int orc_gpt_rollout_cfg(const orc_gpt* m, const int32_t* prompts, int B, int P, int max_new, float temperature,
+                                int top_k, float top_p, float repeat_penalty, int repeat_window, const float* bias,
+                                int eos, int min_new, uint64_t seed, uint32_t seq0, int32_t* tokens_out, float* logp_out,
+                                int32_t* gen_len_out)
+{
+    const int V = m->cfg.vocab;
+    if (P + max_new > m->cfg.ctx || P < 1) return -1;
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int b = 0; b < B; ++b) {
+        orc_state* st = state_new(m);
+        float* logits = (float*)malloc(sizeof(float) * (size_t)V);
+        float* work = (float*)malloc(sizeof(float) * (size_t)V);
+        int32_t* out = tokens_out + (size_t)b * (P + max_new);
+        for (int t = 0; t < P; ++t) {
+            out[t] = prompts[(size_t)b * P + t];
+            forward_step(m, st, out[t], t, logits);
+        }
+        int done = 0;
+        if (gen_len_out) gen_len_out[b] = max_new;
+        for (int t = 0; t < max_new; ++t) {
+            if (done) {
+                out[P + t] = eos;
+                if (logp_out) logp_out[(size_t)b * max_new + t] = 0.0f;
+                continue;
+            }
+            memcpy(work, logits, sizeof(float) * (size_t)V);
+            const float r = orc_philox_uniform(seed, seq0 + (uint32_t)b, (uint32_t)t);
+            const int tok = orc_sample_token_cfg(work, V, temperature, top_k, top_p, repeat_penalty, repeat_window, bias, out,
+                                                 P + t, r);
+            if (logp_out) orc_logprob_entropy(logits, V, tok, logp_out + (size_t)b * max_new + t, NULL);
+            out[P + t] = tok;
+            if (eos >= 0 && tok == eos && t >= min_new) {
+                done = 1;
+                if (gen_len_out) gen_len_out[b] = t;
+                continue;
+            }
             if (t + 1 < max_new) forward_step(m, st, tok, P + t, logits);
         }
         free(logits); free(work);

@@ -237,6 +237,23 @@ class OracleGpt:
         assert rc == 0
         return tokens, logp, logits
 
+    def rollout_cfg(self, prompts, max_new, temperature=1.0, top_k=0, top_p=1.0, repeat_penalty=1.0, repeat_window=0,
+                    bias=None, eos=-1, min_new=0, seed=0, seq0=0):
+        prompts = np.ascontiguousarray(prompts, np.int32)
+        B, P = prompts.shape
+        L = self.L
+        L.orc_gpt_rollout_cfg.restype = C.c_int
+        L.orc_gpt_rollout_cfg.argtypes = [C.c_void_p, _i32p, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, C.c_float, C.c_float,
+                                          C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_uint64, C.c_uint32, _i32p, _f32p, _i32p]
+        tokens = np.empty((B, P + max_new), np.int32)
+        logp = np.empty((B, max_new), np.float32)
+        glen = np.empty(B, np.int32)
+        b = np.ascontiguousarray(bias, np.float32) if bias is not None else None
+        rc = L.orc_gpt_rollout_cfg(self.h, prompts, B, P, max_new, temperature, top_k, top_p, repeat_penalty, repeat_window,
+                                   b.ctypes.data if b is not None else None, eos, min_new, seed, seq0, tokens, logp, glen)
+        assert rc == 0
+        return tokens, logp, glen
+
     def step_logits(self, tokens):
         tokens = np.ascontiguousarray(tokens, np.int32)
         out = np.empty((len(tokens), self.cfg.vocab), np.float32)
@@ -296,7 +313,20 @@ def _init(self):
 Oracle.__init__ = _init
 Oracle.expf = _expf
 Oracle.philox_uniform = _philox
+def _sample_cfg(self, logits, temperature=1.0, top_k=0, top_p=1.0, repeat_penalty=1.0, repeat_window=0, bias=None,
+                history=(), r=0.5):
+    work = np.ascontiguousarray(logits, np.float32).copy()
+    hist = np.ascontiguousarray(history, np.int32)
+    self.L.orc_sample_token_cfg.restype = C.c_int
+    self.L.orc_sample_token_cfg.argtypes = [_f32p, C.c_int, C.c_float, C.c_int, C.c_float, C.c_float, C.c_int, C.c_void_p,
+                                            _i32p, C.c_int, C.c_float]
+    b = np.ascontiguousarray(bias, np.float32) if bias is not None else None
+    return int(self.L.orc_sample_token_cfg(work, len(work), temperature, top_k, top_p, repeat_penalty, repeat_window,
+                                           b.ctypes.data if b is not None else None, hist, len(hist), r))
+
+
 Oracle.sample_token = _sample
+Oracle.sample_token_cfg = _sample_cfg
 Oracle.rmsnorm = _rmsnorm
 Oracle.logprob_entropy = _logprob_entropy
 

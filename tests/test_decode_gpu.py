@@ -70,6 +70,44 @@ def test_top_k_sampled_rollout_token_identical(pkg, eng, temperature, top_k):
     assert np.abs(lp.cpu().numpy() - lp_ref).max() <= 1e-3 * np.abs(lp_ref).max()
 
 
+@pytest.mark.parametrize("kw", [dict(temperature=0.9, top_k=40, top_p=0.7), dict(temperature=1.0, top_k=0, top_p=0.5),
+                                dict(temperature=0.0, repeat_penalty=4.0), dict(temperature=0.8, top_k=20, repeat_penalty=1.5, repeat_window=6),
+                                dict(temperature=1.0, top_k=30, top_p=0.9, repeat_penalty=1.3, bias=True),
+                                dict(temperature=1.0, top_k=8, eos_token=5, min_new_tokens=2)])
+def test_sampling_config_rollout_token_identical(pkg, eng, kw):
+    """top-p, repeat penalty / window, the logit bias and end-of-sequence handling of SamplingConfig / generate, in the
+    reference's order: rollouts token for token against the CPU restatement."""
+    kw = dict(kw)
+    cfg = pkg.GptConfig(n_layer=2, d_model=64, n_head=2, d_ff=128, vocab=300, ctx=40, act=1, pos=1)
+    pol, m, _ = _setup(pkg, eng, cfg)
+    prompts = _prompts(cfg, 12, 5, seed=4)
+    bias = None
+    if kw.pop("bias", False):
+        bias = np.zeros(300, np.float32)
+        bias[::3] = -np.inf  # a third of the vocabulary is forbidden
+        bias[7] = 2.5
+    eos, min_new = kw.pop("eos_token", -1), kw.pop("min_new_tokens", 0)
+    tok_ref, lp_ref, len_ref = m.rollout_cfg(prompts, 20, bias=bias, eos=eos, min_new=min_new, seed=77, seq0=3, **kw)
+    sc = pkg.SamplingConfig(seed=77, eos_token=eos, min_new_tokens=min_new,
+                            logit_bias=None if bias is None else torch.from_numpy(bias).to(eng.device), **kw)
+    tok, lp, glen, _ = pol.rollout_sampled(torch.from_numpy(prompts).to(eng.device), 20, sc, seq0=3)
+    assert np.array_equal(tok.cpu().numpy(), tok_ref)
+    assert np.array_equal(glen.cpu().numpy(), len_ref)
+    assert np.abs(lp.cpu().numpy() - lp_ref).max() <= 1e-3 * max(np.abs(lp_ref).max(), 1e-6)
+    if bias is not None:
+        assert not np.isin(tok_ref[:, 5:], np.arange(0, 300, 3)).any()
+    if eos >= 0:
+        assert (len_ref < 20).any()  # the case does exercise an early end
+
+
+def test_top_p_over_a_large_vocabulary_without_top_k_is_refused(pkg, eng):
+    cfg = pkg.GptConfig(n_layer=1, d_model=64, n_head=2, d_ff=128, vocab=2000, ctx=24, act=0, pos=0)
+    pol, _, _ = _setup(pkg, eng, cfg)
+    p = torch.from_numpy(_prompts(cfg, 2, 4, seed=6)).to(eng.device)
+    with pytest.raises(pkg.NnbError):
+        pol.rollout_sampled(p, 4, pkg.SamplingConfig(top_p=0.5))
+
+
 def test_full_vocab_sampled_rollout_agrees(pkg, eng):
     # without top-k the CDF is accumulated in f64 by chunks on the GPU and in f32 sequentially by the
     # reference rule: tokens agree except where the draw falls within rounding of a CDF step

@@ -112,3 +112,39 @@ def test_rollout_is_consistent_with_teacher_forced_step_logits(pkg, act, pos):
     t2, _, _ = m.rollout(prompts, 6, 1.0, 10, seed=7)
     t3, _, _ = m.rollout(prompts, 6, 1.0, 10, seed=8)
     assert np.array_equal(t1, t2) and not np.array_equal(t1, t3)
+
+
+# src/sampling_test.cpp:153-176: nucleus sampling
+def test_sampler_top_p(orc):
+    rs = np.random.default_rng(1).uniform(size=300).astype(np.float32)
+    assert {orc.sample_token_cfg([10.0, 0.0, 0.0, 0.0], top_p=0.5, r=float(r)) for r in rs} == {0}  # near one-hot: the peak only
+    assert 0 in {orc.sample_token_cfg([10.0, 0.0, 0.0, 0.0], top_p=1e-9, r=float(r)) for r in rs[:50]}  # never an empty set
+    flat = {orc.sample_token_cfg([1.0, 1.0, 1.0, 1.0], top_p=0.5, r=float(r)) for r in rs}
+    assert len(flat) <= 2 and flat <= {0, 1}  # four equal entries, p = 0.5: two kept, ties to the smaller indices
+
+
+# src/sampling_test.cpp:178-222: repeat penalty, window, and the multiplicative branch for negative logits
+def test_sampler_repeat_penalty(orc):
+    assert orc.sample_token_cfg([5.0, 4.0], temperature=0.0, history=[0]) == 0
+    assert orc.sample_token_cfg([5.0, 4.0], temperature=0.0, repeat_penalty=10.0, history=[0]) == 1
+    assert orc.sample_token_cfg([5.0, 4.0], temperature=0.0, repeat_penalty=10.0, repeat_window=1, history=[1, 0]) == 1
+    assert orc.sample_token_cfg([5.0, 4.0], temperature=0.0, repeat_penalty=10.0, repeat_window=0, history=[1, 0]) == 0
+    assert orc.sample_token_cfg([-1.0, -5.0], temperature=0.0, repeat_penalty=10.0, history=[1]) == 0
+    # a token that occurs twice in the window is penalised once
+    assert orc.sample_token_cfg([5.0, 0.6], temperature=0.0, repeat_penalty=3.0, history=[0, 0]) == 0  # 5/3 > 0.6, 5/9 < 0.6
+
+
+# logits_transform (src/sampling_test.cpp, the hook runs before every other rule): a bias of -inf forbids a token
+def test_sampler_bias_comes_first(orc):
+    bias = np.array([-np.inf, 0.0, 0.0], np.float32)
+    assert orc.sample_token_cfg([9.0, 1.0, 2.0], temperature=0.0, bias=bias) == 2
+    rs = np.random.default_rng(2).uniform(size=100).astype(np.float32)
+    assert {orc.sample_token_cfg([9.0, 1.0, 2.0], bias=bias, r=float(r)) for r in rs} <= {1, 2}
+
+
+def test_sampler_cfg_defaults_equal_the_plain_sampler(orc):
+    rng = np.random.default_rng(3)
+    for _ in range(50):
+        lg = rng.normal(0, 2, 40).astype(np.float32)
+        r = float(rng.uniform())
+        assert orc.sample_token_cfg(lg, temperature=0.7, top_k=5, r=r) == orc.sample_token(lg, 0.7, 5, r)
