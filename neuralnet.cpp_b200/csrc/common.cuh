@@ -164,6 +164,7 @@ nnb_status launch_sample(nnb_engine* e, bool exact, const float* logits, size_t 
                          const int* d_pos, int prompt_len, int32_t* tokens, size_t tokens_stride,
                          float* logp, size_t logp_stride, float* entropy);
 nnb_status launch_set_int(nnb_engine* e, int* p, int v);
+nnb_status launch_set_int2(nnb_engine* e, int* p, int v, int v1);
 nnb_status launch_fill_int(nnb_engine* e, int* p, size_t n, int v);
 nnb_status launch_add_int(nnb_engine* e, int* p, int v);
 nnb_status launch_embed(nnb_engine* e, const float* tok_emb, const float* pos_emb, const int32_t* tokens,

@@ -20,7 +20,8 @@
 namespace nnb {
 
 // ---------------------------------------------------------------- embedding
-// x[b,:] = tok_emb[token[b, pos],:] (+ pos_emb[pos,:])
+// x[b,:] = tok_emb[token[b, col],:] (+ pos_emb[pos,:]) with d_pos = {pos, col}: the position inside the context
+// window and the column of the token buffer.  They differ only after the window of a long generation has slid.
 __global__ void embed_kernel(const float* __restrict__ tok_emb, const float* __restrict__ pos_emb,
                              const int32_t* __restrict__ tokens, int tokens_stride,
                              const int* __restrict__ d_pos, int d, int vocab, float* __restrict__ x)
@@ -28,8 +29,8 @@ __global__ void embed_kernel(const float* __restrict__ tok_emb, const float* __r
     const int b = blockIdx.x;
     pdl_launch();
     pdl_wait();
-    const int pos = *d_pos;
-    int tok = tokens[(size_t)b * tokens_stride + pos];
+    const int pos = d_pos[0];
+    int tok = tokens[(size_t)b * tokens_stride + d_pos[1]];
     tok = min(max(tok, 0), vocab - 1);
     const float* e = tok_emb + (size_t)tok * d;
     const float* p = pos_emb ? pos_emb + (size_t)pos * d : nullptr;
@@ -1249,7 +1250,7 @@ sample_kernel(const float* __restrict__ logits, int V, SampleOpts o,
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     pdl_launch();
     pdl_wait();
-    const int pos = *d_pos;
+    const int pos = d_pos[1];  // the column of the token buffer this step consumed (d_pos[0] is its window position)
     const int gen = pos + 1 - prompt_len;
     const float* row = logits + (size_t)b * V;
 
@@ -1616,7 +1617,7 @@ nnb_status launch_sample_opts(nnb_engine* e, bool exact, const float* logits, si
     return NNB_OK;
 }
 
-__global__ void set_int_kernel(int* p, int v) { *p = v; }
+__global__ void set_int_kernel(int* p, int v, int v1) { p[0] = v; p[1] = v1; }
 __global__ void fill_int_kernel(int* p, int n, int v)
 {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -1632,12 +1633,15 @@ nnb_status launch_fill_int(nnb_engine* e, int* p, size_t n, int v)
 __global__ void add_int_kernel(int* p, int v)
 {
     pdl_wait();
-    *p += v;
+    p[0] += v;
+    p[1] += v;
 }
 
-nnb_status launch_set_int(nnb_engine* e, int* p, int v)
+// p = {window position, token column}; both move together (launch_add_int) until the window slides
+nnb_status launch_set_int(nnb_engine* e, int* p, int v) { return launch_set_int2(e, p, v, v); }
+nnb_status launch_set_int2(nnb_engine* e, int* p, int v, int v1)
 {
-    set_int_kernel<<<1, 1, 0, e->stream>>>(p, v);
+    set_int_kernel<<<1, 1, 0, e->stream>>>(p, v, v1);
     e->launches++;
     NNB_CHECK_LAUNCH("set_int_kernel");
     return NNB_OK;

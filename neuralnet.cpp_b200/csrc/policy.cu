@@ -193,10 +193,12 @@ static void free_decode(nnb_policy* p)
 void policy_free_decode(nnb_policy* p) { free_decode(p); }
 
 // total positions = pre_len (shared prefix, one copy per group) + ctx_alloc (per sequence)
-static nnb_status ensure_decode(nnb_policy* p, size_t B, size_t ctx_alloc, size_t group, size_t pre_len)
+// tok_cols: columns of the token / log-prob buffers (the whole sequence, which outgrows the cache once the
+// context window slides)
+static nnb_status ensure_decode(nnb_policy* p, size_t B, size_t ctx_alloc, size_t group, size_t pre_len, size_t tok_cols)
 {
     DecodeWs& w = p->dec;
-    if (w.B == B && w.ctx_alloc == ctx_alloc && w.group == group && w.pre_len == pre_len) return NNB_OK;
+    if (w.B == B && w.ctx_alloc == ctx_alloc && w.group == group && w.pre_len == pre_len && w.tok_cols == tok_cols) return NNB_OK;
     NNB_CUDA(cudaStreamSynchronize(p->e->stream));
     free_decode(p);
     const nnb_gpt_config& c = p->cfg;
@@ -205,7 +207,7 @@ static nnb_status ensure_decode(nnb_policy* p, size_t B, size_t ctx_alloc, size_
     const size_t dkv = c.n_head * attn_decode_kv_pitch(c.exact != 0, d / c.n_head);  // cached features per position
     const size_t kv_bytes = (size_t)c.n_layer * B * dkv * ctx_alloc * kv_elem;
     const size_t pre_bytes = (size_t)c.n_layer * (B / group) * dkv * pre_len * kv_elem;
-    const size_t total = pre_len + ctx_alloc;
+    const size_t total = tok_cols;
     size_t free_b = 0, total_b = 0;
     NNB_CUDA(cudaMemGetInfo(&free_b, &total_b));
     const size_t need = 2 * (kv_bytes + pre_bytes) + B * (d * 4 * 5 + F1 * 4 + V * 4 + (F > d ? F : d) + total * 8) + (64u << 20);
@@ -247,6 +249,7 @@ static nnb_status ensure_decode(nnb_policy* p, size_t B, size_t ctx_alloc, size_
     w.ctx_alloc = ctx_alloc;
     w.group = group;
     w.pre_len = pre_len;
+    w.tok_cols = tok_cols;
     return NNB_OK;
 }
 
@@ -394,14 +397,20 @@ nnb_status policy_rollout(nnb_policy* p, const int32_t* d_prompts, size_t B, siz
     NNB_REQUIRE(p && d_prompts && d_tokens, "rollout: NULL argument");
     NNB_REQUIRE(B > 0 && P > 0 && max_new > 0, "rollout: empty shape");
     NNB_REQUIRE(group >= 1 && B % group == 0, "rollout: %zu sequences do not divide into groups of %zu", B, group);
-    NNB_REQUIRE(P + max_new <= (size_t)p->cfg.ctx, "rollout: prompt %zu + %zu new tokens exceeds the context %d",
-                P, max_new, p->cfg.ctx);
+    NNB_REQUIRE(p->cfg.ctx >= 2 || P + max_new <= (size_t)p->cfg.ctx, "rollout: a context of %d cannot slide", p->cfg.ctx);
     nnb_engine* e = p->e;
     const nnb_gpt_config& c = p->cfg;
     const size_t total = P + max_new;
+    // A sequence that outgrows the context is generated the way GPTModel::generate does it
+    // (include/neuralnet.cpp/compute_layer_gpt.hpp:768-818): the window keeps the last ctx-1 tokens and is rebuilt
+    // from position 0 before every further token.  Positions then differ between the members of a group only by
+    // their tokens, but the shared prefix cache assumes fixed positions, so it is not used in that case.
+    const size_t ctx = (size_t)c.ctx;
+    const bool windowed = total > ctx;
+    if (windowed) group = 1;
     const size_t pre_len = (group > 1 && P > 1) ? P - 1 : 0;
-    const size_t own = total - pre_len;
-    NNB_TRY(ensure_decode(p, B, own, group, pre_len));
+    const size_t own = (windowed ? ctx : total) - pre_len;
+    NNB_TRY(ensure_decode(p, B, own, group, pre_len, total));
     DecodeWs& w = p->dec;
     SampleOpts so = so_in;
     if (so.eos >= 0 || d_gen_len) {
@@ -459,6 +468,31 @@ nnb_status policy_rollout(nnb_policy* p, const int32_t* d_prompts, size_t B, siz
             for (cudaEvent_t evt : p->time_events) cudaEventDestroy(evt);
             p->time_events.clear();
             p->time_pos.clear();
+        }
+        if (windowed) {
+            size_t cur = 0;  // tokens in the window = position of the next one
+            const size_t col0 = P > ctx ? P - ctx : 0;  // a prompt longer than the context is cut to its tail
+            NNB_TRY(launch_set_int2(e, w.d_pos, 0, (int)col0));
+            for (size_t col = col0; col + 1 < total; ++col) {
+                const bool with_head = col + 1 >= P;
+                if (with_head && cur + 1 >= ctx) {
+                    // the window is full: it becomes the ctx-1 tokens that end at this column, from position 0
+                    const size_t start = col + 1 - (ctx - 1);
+                    NNB_TRY(launch_set_int2(e, w.d_pos, 0, (int)start));
+                    cur = 0;
+                    for (size_t i = start; i < col; ++i, ++cur)
+                        NNB_TRY(run_step(p, graphs[1], allow_graph, main_view, false, so, seed, seq0, (int)P, false));
+                }
+                NNB_TRY(run_step(p, graphs[with_head ? 2 : 1], allow_graph, main_view, with_head, so, seed, seq0, (int)P,
+                                 d_logp != nullptr));
+                ++cur;
+                if (with_head && d_logits) {
+                    const size_t gi = col + 1 - P;
+                    NNB_CUDA(cudaMemcpy2DAsync(d_logits + gi * V, max_new * V * 4, w.logits, V * 4, V * 4, B,
+                                               cudaMemcpyDeviceToDevice, e->stream));
+                }
+            }
+            return NNB_OK;
         }
         for (size_t t = t0; t + 1 < total; ++t) {
             if (p->time_stride && (t - t0) % p->time_stride == 0) NNB_TRY(mark(t));

@@ -26,6 +26,7 @@ struct TensorInfo {
 
 struct DecodeWs {
     size_t B = 0, ctx_alloc = 0;     // sequences; positions held by the per-sequence cache
+    size_t tok_cols = 0;             // columns of tokens / logp: the whole sequence
     size_t group = 1, pre_len = 0;   // sequences per shared prompt; positions held by the shared prefix cache
     void *k = nullptr, *v = nullptr;  // (L, B, H, ctx_alloc, dk), f32 in the exact mode else bf16
     void *k_pre = nullptr, *v_pre = nullptr;  // (L, B/group, H, pre_len, dk): prompt prefix, one per group
@@ -36,8 +37,8 @@ struct DecodeWs {
     float* s = nullptr;
     int32_t* qsum = nullptr;
     int* d_pos = nullptr;
-    int32_t* tokens = nullptr;  // (B, ctx_alloc)
-    float* logp = nullptr;      // (B, ctx_alloc), generated index
+    int32_t* tokens = nullptr;  // (B, tok_cols)
+    float* logp = nullptr;      // (B, tok_cols), generated index
     int32_t *done = nullptr, *gen_len = nullptr;  // (B) end-of-sequence flags and generated lengths
 };
 

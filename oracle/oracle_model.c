@@ -616,17 +616,19 @@ ORC_API int orc_gpt_rollout_cfg(const orc_gpt* m, const int32_t* prompts, int B,
                                 int32_t* gen_len_out)
 {
     const int V = m->cfg.vocab;
-    if (P + max_new > m->cfg.ctx || P < 1) return -1;
+    const int ctx = m->cfg.ctx;
+    if (P < 1 || (P + max_new > ctx && ctx < 2)) return -1;
 #pragma omp parallel for schedule(dynamic, 1)
     for (int b = 0; b < B; ++b) {
         orc_state* st = state_new(m);
         float* logits = (float*)malloc(sizeof(float) * (size_t)V);
         float* work = (float*)malloc(sizeof(float) * (size_t)V);
         int32_t* out = tokens_out + (size_t)b * (P + max_new);
-        for (int t = 0; t < P; ++t) {
-            out[t] = prompts[(size_t)b * P + t];
-            forward_step(m, st, out[t], t, logits);
-        }
+        for (int t = 0; t < P; ++t) out[t] = prompts[(size_t)b * P + t];
+        /* GPTModel::generate (include/neuralnet.cpp/compute_layer_gpt.hpp:768-818): a prompt longer than the context
+         * is cut to its tail; cur_len counts the tokens in the KV cache */
+        int cur_len = 0;
+        for (int t = (P > ctx ? P - ctx : 0); t < P; ++t) forward_step(m, st, out[t], cur_len++, logits);
         int done = 0;
         if (gen_len_out) gen_len_out[b] = max_new;
         for (int t = 0; t < max_new; ++t) {
@@ -634,6 +636,12 @@ ORC_API int orc_gpt_rollout_cfg(const orc_gpt* m, const int32_t* prompts, int B,
                 out[P + t] = eos;
                 if (logp_out) logp_out[(size_t)b * max_new + t] = 0.0f;
                 continue;
+            }
+            if (cur_len >= ctx) {
+                /* sliding window: the cache is rebuilt from the last ctx-1 tokens, positions from 0 */
+                cur_len = 0;
+                const int size = P + t, keep = ctx - 1;
+                for (int i = (size > keep ? size - keep : 0); i < size; ++i) forward_step(m, st, out[i], cur_len++, logits);
             }
             memcpy(work, logits, sizeof(float) * (size_t)V);
             const float r = orc_philox_uniform(seed, seq0 + (uint32_t)b, (uint32_t)t);
@@ -646,7 +654,7 @@ ORC_API int orc_gpt_rollout_cfg(const orc_gpt* m, const int32_t* prompts, int B,
                 if (gen_len_out) gen_len_out[b] = t;
                 continue;
             }
-            if (t + 1 < max_new) forward_step(m, st, tok, P + t, logits);
+            if (t + 1 < max_new) forward_step(m, st, tok, cur_len++, logits);
         }
         free(logits); free(work);
         state_free(st);

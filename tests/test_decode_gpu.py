@@ -100,6 +100,26 @@ def test_sampling_config_rollout_token_identical(pkg, eng, kw):
         assert (len_ref < 20).any()  # the case does exercise an early end
 
 
+@pytest.mark.parametrize("pos,P,max_new,kw", [(0, 5, 14, dict(temperature=0.0)), (1, 5, 14, dict(temperature=0.9, top_k=12)),
+                                              (1, 15, 6, dict(temperature=0.0)), (0, 12, 3, dict(temperature=1.0, top_k=5))])
+def test_generation_past_the_context_slides_the_window_like_the_reference(pkg, eng, pos, P, max_new, kw):
+    """GPTModel::generate beyond seq_len (compute_layer_gpt.hpp:768-818): a prompt longer than the context is cut to its
+    tail, and once the cache is full every further token is sampled after rebuilding it from the last ctx-1 tokens at
+    positions 0..ctx-2.  Context 12 here; tokens against the CPU restatement."""
+    cfg = pkg.GptConfig(n_layer=2, d_model=64, n_head=2, d_ff=128, vocab=211, ctx=12, act=1, pos=pos)
+    pol, m, _ = _setup(pkg, eng, cfg)
+    prompts = _prompts(cfg, 4, P, seed=8)
+    tok_ref, lp_ref, _ = m.rollout_cfg(prompts, max_new, seed=5, seq0=2, **kw)
+    tok, lp, _, _ = pol.rollout_sampled(torch.from_numpy(prompts).to(eng.device), max_new, pkg.SamplingConfig(seed=5, **kw), seq0=2)
+    assert np.array_equal(tok.cpu().numpy(), tok_ref)
+    assert np.abs(lp.cpu().numpy() - lp_ref).max() <= 1e-3 * np.abs(lp_ref).max()
+    # grouped prompts fall back to one window per sequence and give the same tokens
+    rep = np.repeat(prompts[:2], 2, axis=0)
+    a, _, _, _ = pol.rollout_sampled(torch.from_numpy(rep).to(eng.device), max_new, pkg.SamplingConfig(seed=5, **kw), group_size=2)
+    b, _, _, _ = pol.rollout_sampled(torch.from_numpy(rep).to(eng.device), max_new, pkg.SamplingConfig(seed=5, **kw))
+    assert torch.equal(a, b)
+
+
 def test_top_p_over_a_large_vocabulary_without_top_k_is_refused(pkg, eng):
     cfg = pkg.GptConfig(n_layer=1, d_model=64, n_head=2, d_ff=128, vocab=2000, ctx=24, act=0, pos=0)
     pol, _, _ = _setup(pkg, eng, cfg)
@@ -177,13 +197,15 @@ def test_host_rollout_entry_point(pkg, eng):
     assert np.array_equal(h_t.numpy(), tok_ref)
 
 
-def test_context_overflow_is_rejected(pkg, eng):
+def test_context_overflow_slides_in_the_rollout_and_is_rejected_by_the_teacher_forced_pass(pkg, eng):
     cfg = pkg.GptConfig(n_layer=1, d_model=64, n_head=2, d_ff=128, vocab=300, ctx=8, act=0, pos=0)
     pol = pkg.Policy(eng, cfg)
     pol.upload_params(cfg.init_params(0))
     p = torch.zeros((2, 4), dtype=torch.int32, device=eng.device)
+    tok, _, _ = pol.rollout(p, 8)  # 12 tokens through a window of 8, as GPTModel::generate does
+    assert tok.shape == (2, 12)
     with pytest.raises(pkg.NnbError):
-        pol.rollout(p, 8)
+        pol.logprobs(tok, 4)  # the teacher-forced pass takes whole sequences within the context only
 
 
 @pytest.mark.parametrize("exact", [True, False])
