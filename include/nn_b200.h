@@ -70,6 +70,74 @@ nnb_status nnb_upload(nnb_engine* e, void* d_dst, const void* h_src, size_t byte
 nnb_status nnb_download(nnb_engine* e, void* h_dst, const void* d_src, size_t bytes);
 nnb_status nnb_zero(nnb_engine* e, void* d_ptr, size_t bytes);
 
+/* ================= tensors and engine primitives, reference layout ========
+ * The reference's Tensor is a value over refcounted storage with a write epoch that every writing engine
+ * entry bumps (AGENTS.md:158-164; BitLinear's quantisation cache compares it,
+ * include/neuralnet.cpp/compute_layer_bitlinear.hpp:607-615).  nnb_tensor is that storage: row-major
+ * (rows, cols) f32 on the engine's device (ternary and int8 containers are uint32 words bit-cast into f32
+ * tensors, as in the reference).  Functions that return a tensor create it; the caller destroys every
+ * handle it received.  Operands of one call must belong to the same engine (NNB_ERR_INVALID otherwise:
+ * the reference's cross-domain rule, docs/development/07-engine-ownership.md:14-24).  The verbs are those
+ * of docs/usage/03-compute-engine-usage.md:1080-1187 (candidate C list:
+ * docs/internal/34-engine-link-abi-boundary.md:36-74). */
+typedef struct nnb_tensor nnb_tensor;
+nnb_status nnb_tensor_create(nnb_engine* e, size_t rows, size_t cols, nnb_tensor** out); /* zero-filled */
+void nnb_tensor_destroy(nnb_tensor* t);
+size_t nnb_tensor_rows(const nnb_tensor* t);
+size_t nnb_tensor_cols(const nnb_tensor* t);
+float* nnb_tensor_data(nnb_tensor* t); /* device pointer; after writing through it call nnb_tensor_mark_written */
+unsigned long long nnb_tensor_write_epoch(const nnb_tensor* t);
+nnb_status nnb_tensor_mark_written(nnb_tensor* t);
+nnb_status nnb_tensor_upload(nnb_tensor* t, const float* h_src, size_t count);   /* upload_span / copy_from */
+nnb_status nnb_tensor_download(const nnb_tensor* t, float* h_dst, size_t count); /* download_span / to_matrix */
+nnb_status nnb_t_zero(nnb_tensor* t);
+nnb_status nnb_t_clone(const nnb_tensor* src, nnb_tensor** out);
+nnb_status nnb_t_copy_into(nnb_tensor* dst, const nnb_tensor* src);
+nnb_status nnb_t_transpose(const nnb_tensor* src, nnb_tensor** out);
+/* rows [start_row, start_row + count) as a new (count, cols) tensor / all rows of src written at dst_start_row */
+nnb_status nnb_t_slice_rows(const nnb_tensor* src, size_t start_row, size_t count, nnb_tensor** out);
+nnb_status nnb_t_insert_rows(nnb_tensor* dst, size_t dst_start_row, const nnb_tensor* src);
+/* out[i] = table[indices[i]] (indices are f32 values, any shape; out of range -> zero row) and its adjoint
+ * dst[indices[i]] += grad[i] (repeated indices accumulate) */
+nnb_status nnb_t_gather_rows(const nnb_tensor* table, const nnb_tensor* indices, nnb_tensor** out);
+nnb_status nnb_t_scatter_add_rows(nnb_tensor* dst, const nnb_tensor* indices, const nnb_tensor* grad);
+/* (M, B*N) -> (B*M, N): out[b*M + m, n] = in[m, b*N + n]; inverse != 0 the other way */
+nnb_status nnb_t_rearrange_3d(const nnb_tensor* x, size_t M, size_t B, size_t N, int inverse, nnb_tensor** out);
+nnb_status nnb_t_scale_inplace(nnb_tensor* t, float s);
+nnb_status nnb_t_accumulate(nnb_tensor* dst, const nnb_tensor* src);
+nnb_status nnb_t_col_reduce_max(const nnb_tensor* t, nnb_tensor** out); /* (1, cols): max over the rows */
+nnb_status nnb_t_row_reduce_sum(const nnb_tensor* t, nnb_tensor** out); /* (rows, 1) */
+/* the ternary primitives BitLinear calls (compute_layer_bitlinear.hpp:443-464,494,516,637-650) on tensors */
+nnb_status nnb_t_absmean_tau(const nnb_tensor* latent, nnb_tensor** tau);
+nnb_status nnb_t_trit_pack(const nnb_tensor* latent, const nnb_tensor* tau, nnb_tensor** packed);
+nnb_status nnb_t_trit_pack_into(const nnb_tensor* latent, const nnb_tensor* tau, nnb_tensor* packed);
+nnb_status nnb_t_matmul_q(const nnb_tensor* packed, const nnb_tensor* tau, const nnb_tensor* x, nnb_tensor** out);
+nnb_status nnb_t_matmul_q_t(const nnb_tensor* packed, const nnb_tensor* tau, const nnb_tensor* b, size_t m_cols, nnb_tensor** out);
+nnb_status nnb_t_quantize_i8(const nnb_tensor* x, const nnb_tensor* scale, int col_scale, nnb_tensor** out);
+nnb_status nnb_t_unpack_i8(const nnb_tensor* packed, size_t cols, nnb_tensor** out);
+nnb_status nnb_t_matmul_q_i8(const nnb_tensor* packed, const nnb_tensor* tau, const nnb_tensor* xq, const nnb_tensor* s, nnb_tensor** out);
+/* the three expression-DSL compositions of BitLinear::forward / backward, one kernel each (the expression JIT
+ * itself is not part of this engine): |x| (:441), y + row_broadcast(b) (:455), and
+ * grad_w + ((dy o col_broadcast(s)) . x^T) o row_broadcast(tau) (:518-534; s may be NULL) */
+nnb_status nnb_t_abs(const nnb_tensor* src, nnb_tensor** out);
+nnb_status nnb_t_add_row_broadcast(nnb_tensor* y, const nnb_tensor* b);
+nnb_status nnb_t_bitlinear_dw_accumulate(nnb_tensor* grad_w, const nnb_tensor* dy, const nnb_tensor* s, const nnb_tensor* x,
+                                         const nnb_tensor* tau);
+
+/* ---- standalone RMSNorm and rotary embedding, token-major (rows = tokens).
+ * RMSNorm::forward / backward (include/neuralnet.cpp/compute_layer_mlp.hpp:686-746): y = x * rsqrt(mean(x^2) + 1e-5) * gamma;
+ * the backward writes d_dx and ADDS the gain gradient to d_dgamma.  f must be a multiple of 64 in the forward.
+ * RotaryEmbedding (compute_position_encoding.hpp:64-80,126-168): tables (ctx, dk/2) of cos / sin of pos / 10000^(2j/dk);
+ * apply rotates, in place, rows of n_head blocks of dk features, row r being at position r % seq_len (backward != 0: the
+ * inverse rotation, which is the gradient); step rotates every row as position `pos` (apply_step). */
+nnb_status nnb_rmsnorm_fwd(nnb_engine* e, const float* d_x, const float* d_gamma, size_t t, size_t f, float* d_y);
+nnb_status nnb_rmsnorm_bwd(nnb_engine* e, const float* d_x, const float* d_gamma, const float* d_dy, size_t t, size_t f, float* d_dx,
+                           float* d_dgamma);
+nnb_status nnb_rope_tables(nnb_engine* e, size_t dk, size_t ctx, float* d_cos, float* d_sin);
+nnb_status nnb_rope_apply(nnb_engine* e, float* d_x, const float* d_cos, const float* d_sin, size_t n_rows, size_t seq_len, size_t n_head,
+                          size_t dk, int backward);
+nnb_status nnb_rope_step(nnb_engine* e, float* d_x, const float* d_cos, const float* d_sin, size_t n_seq, size_t pos, size_t n_head, size_t dk);
+
 /* ================= ternary linear, reference layout =======================
  * One entry per ComputeEngine primitive that BitLinear calls
  * (include/neuralnet.cpp/compute_layer_bitlinear.hpp:443-464,494,516,637-650). */
@@ -308,7 +376,11 @@ typedef struct nnb_objective {
     const float* d_mask;       /* action mask, required */
     const float* d_old_logp;   /* with d_advantage: clipped policy term; both NULL to skip */
     const float* d_advantage;
-    const float* d_ref_logp;   /* KL term (kl_coef != 0) */
+    const float* d_ref_logp;   /* KL term (kl_coef != 0): kl_coef * mean(logp - ref_logp).  An addition of this engine
+                                  for a frozen reference policy: the reference's GrpoObjective has no KL term
+                                  (rl_policy.hpp:934-951) and its SampledKlObjective (:503-530) penalises
+                                  logp - old_log_prob, which is d_ref_logp = d_old_logp here; kl_coef = 0 is the
+                                  reference's GRPO preset */
     const float* d_returns;    /* value term (value_coef != 0): returns and old values */
     const float* d_old_value;
     float units;               /* normalisation count; <= 0 = sum of this micro-batch's mask.  Pass the
@@ -317,9 +389,26 @@ typedef struct nnb_objective {
     float clip_eps, kl_coef, entropy_coef, value_coef, value_clip_eps;
 } nnb_objective;
 
+/* The ten floats a training call reports, named after the reference's report structs (PpoReport / GrpoReport and
+ * PpoPolicyMetrics, include/neuralnet.cpp/rl_policy.hpp:787-797,858-864): PpoReport.policy_loss =
+ * [NNB_REPORT_CLIPPED_POLICY_LOSS] + [NNB_REPORT_ENTROPY_LOSS], PpoReport.value_loss = [NNB_REPORT_VALUE_LOSS],
+ * PpoReport.loss = their sum (+ [NNB_REPORT_KL_LOSS], this engine's addition), PpoReport.entropy =
+ * [NNB_REPORT_ENTROPY], approx_kl, policy_clip_fraction and value_clip_fraction as named. */
+enum {
+    NNB_REPORT_CLIPPED_POLICY_LOSS = 0, /* ClippedPolicyObjective loss */
+    NNB_REPORT_RATIO_MEAN = 1,          /* PpoPolicyMetrics.ratio_mean */
+    NNB_REPORT_APPROX_KL = 2,
+    NNB_REPORT_POLICY_CLIP_FRACTION = 3,
+    NNB_REPORT_KL_LOSS = 4,     /* kl_coef * mean(logp - ref_logp) */
+    NNB_REPORT_ENTROPY_LOSS = 5, /* -entropy_coef * mean entropy */
+    NNB_REPORT_ENTROPY = 6,
+    NNB_REPORT_UNITS = 7,        /* the normalisation count */
+    NNB_REPORT_VALUE_LOSS = 8,
+    NNB_REPORT_VALUE_CLIP_FRACTION = 9,
+    NNB_REPORT_COUNT = 10
+};
 /* forward + objective + GPTModel::backward (compute_layer_gpt.hpp:545-636): gradients are ADDED to the
- * policy's gradient buffer.  d_report[10] (may be NULL) = policy_loss, ratio_mean, approx_kl,
- * clip_fraction, kl_loss, entropy_loss, mean entropy, units, value_loss, value clip_fraction. */
+ * policy's gradient buffer.  d_report[NNB_REPORT_COUNT] (may be NULL) as named above. */
 nnb_status nnb_policy_train_step(nnb_policy* p, const int32_t* d_tokens, size_t n_seq, size_t seq_len,
                                  size_t prompt_len, const nnb_objective* obj, float* d_report);
 /* The same two calls for a batch whose sequences come in groups of `group` consecutive rows that share

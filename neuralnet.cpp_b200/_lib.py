@@ -36,6 +36,44 @@ _SIGNATURES = {
     "nnb_upload": (_I, [_P, _P, _P, _SZ]),
     "nnb_download": (_I, [_P, _P, _P, _SZ]),
     "nnb_zero": (_I, [_P, _P, _SZ]),
+    "nnb_tensor_create": (_I, [_P, _SZ, _SZ, C.POINTER(_P)]),
+    "nnb_tensor_destroy": (None, [_P]),
+    "nnb_tensor_rows": (_SZ, [_P]),
+    "nnb_tensor_cols": (_SZ, [_P]),
+    "nnb_tensor_data": (_P, [_P]),
+    "nnb_tensor_write_epoch": (C.c_ulonglong, [_P]),
+    "nnb_tensor_mark_written": (_I, [_P]),
+    "nnb_tensor_upload": (_I, [_P, _P, _SZ]),
+    "nnb_tensor_download": (_I, [_P, _P, _SZ]),
+    "nnb_t_zero": (_I, [_P]),
+    "nnb_t_clone": (_I, [_P, C.POINTER(_P)]),
+    "nnb_t_copy_into": (_I, [_P, _P]),
+    "nnb_t_transpose": (_I, [_P, C.POINTER(_P)]),
+    "nnb_t_slice_rows": (_I, [_P, _SZ, _SZ, C.POINTER(_P)]),
+    "nnb_t_insert_rows": (_I, [_P, _SZ, _P]),
+    "nnb_t_gather_rows": (_I, [_P, _P, C.POINTER(_P)]),
+    "nnb_t_scatter_add_rows": (_I, [_P, _P, _P]),
+    "nnb_t_rearrange_3d": (_I, [_P, _SZ, _SZ, _SZ, _I, C.POINTER(_P)]),
+    "nnb_t_scale_inplace": (_I, [_P, C.c_float]),
+    "nnb_t_accumulate": (_I, [_P, _P]),
+    "nnb_t_col_reduce_max": (_I, [_P, C.POINTER(_P)]),
+    "nnb_t_row_reduce_sum": (_I, [_P, C.POINTER(_P)]),
+    "nnb_t_absmean_tau": (_I, [_P, C.POINTER(_P)]),
+    "nnb_t_trit_pack": (_I, [_P, _P, C.POINTER(_P)]),
+    "nnb_t_trit_pack_into": (_I, [_P, _P, _P]),
+    "nnb_t_matmul_q": (_I, [_P, _P, _P, C.POINTER(_P)]),
+    "nnb_t_matmul_q_t": (_I, [_P, _P, _P, _SZ, C.POINTER(_P)]),
+    "nnb_t_quantize_i8": (_I, [_P, _P, _I, C.POINTER(_P)]),
+    "nnb_t_unpack_i8": (_I, [_P, _SZ, C.POINTER(_P)]),
+    "nnb_t_matmul_q_i8": (_I, [_P, _P, _P, _P, C.POINTER(_P)]),
+    "nnb_t_abs": (_I, [_P, C.POINTER(_P)]),
+    "nnb_t_add_row_broadcast": (_I, [_P, _P]),
+    "nnb_t_bitlinear_dw_accumulate": (_I, [_P, _P, _P, _P, _P]),
+    "nnb_rmsnorm_fwd": (_I, [_P, _P, _P, _SZ, _SZ, _P]),
+    "nnb_rmsnorm_bwd": (_I, [_P, _P, _P, _P, _SZ, _SZ, _P, _P]),
+    "nnb_rope_tables": (_I, [_P, _SZ, _SZ, _P, _P]),
+    "nnb_rope_apply": (_I, [_P, _P, _P, _P, _SZ, _SZ, _SZ, _SZ, _I]),
+    "nnb_rope_step": (_I, [_P, _P, _P, _P, _SZ, _SZ, _SZ, _SZ]),
     "nnb_absmean_tau": (_I, [_P, _P, _SZ, _SZ, _P]),
     "nnb_trit_pack": (_I, [_P, _P, _P, _SZ, _SZ, _P]),
     "nnb_col_absmax_scale": (_I, [_P, _P, _SZ, _SZ, _P]),

@@ -272,6 +272,14 @@ nnb_status launch_tc_dx(nnb_engine* e, const __nv_bfloat16* dyb, const __nv_bflo
                         float* dx, bool accumulate);
 nnb_status launch_tc_dw(nnb_engine* e, const __nv_bfloat16* dyb, const __nv_bfloat16* xs, size_t t, size_t k, size_t out,
                         float* dw);
+// LM head fused with log-softmax (fast mode): forward leaves log-prob / entropy / log-sum-exp per row, backward the
+// bf16 operand of the head's backward GEMMs and the bias gradient; scratch holds tc_lmhead_scratch_floats floats
+size_t tc_lmhead_scratch_floats(size_t t, size_t v);
+nnb_status launch_tc_lmhead_fwd(nnb_engine* e, const int8_t* q, const int8_t* w8, const float* tau, const float* s, const float* bias,
+                                const int32_t* actions, size_t t, size_t k, size_t v, float* scratch, float* lse, float* logp, float* ent);
+nnb_status launch_tc_lmhead_bwd(nnb_engine* e, const int8_t* q, const int8_t* w8, const float* tau, const float* s, const float* bias,
+                                const int32_t* actions, const float* lse, const float* ent, const float* up_lp, const float* up_ent,
+                                size_t t, size_t k, size_t v, float* scratch, __nv_bfloat16* dyb, float* db);
 nnb_status tc_check_errors(nnb_engine* e);
 nnb_status tc_set_forward_tile(int bn);
 nnb_status launch_expand_weights(nnb_engine* e, const uint32_t* wq, size_t rows, size_t k, int8_t* w8, __nv_bfloat16* wb);

@@ -1508,8 +1508,9 @@ sample_kernel(const float* __restrict__ logits, int V, SampleOpts o,
             }
             __syncthreads();
         } else {
-            // full vocabulary: p_i = exp(x_i - max)/sum with the sum and the CDF accumulated in
-            // f64 by 256 contiguous chunks (the reference walks them in f32, ascending index)
+            // full vocabulary: p_i = exp(x_i - max)/sum.  Every thread owns a contiguous chunk of the row: the sum and
+            // the CDF are accumulated in f64, chunk by chunk, and joined by a block-wide scan (the reference walks the
+            // row in f32, ascending index; the draw lands on the same token except within rounding of a CDF step)
             float m2 = -INFINITY;
             for (int i = tid; i < V; i += NT) m2 = fmaxf(m2, lg[i]);
             m2 = warp_max(m2);
@@ -1518,34 +1519,46 @@ sample_kernel(const float* __restrict__ logits, int V, SampleOpts o,
             m2 = red_f[0];
 #pragma unroll
             for (int w = 1; w < NW; ++w) m2 = fmaxf(m2, red_f[w]);
-            __shared__ double dsum[256];
-            const int chunk = (V + 255) / 256;
-            if (tid < 256) {
-                const int lo = min(V, tid * chunk), hi = min(V, lo + chunk);
-                double part = 0.0;
-                for (int i = lo; i < hi; ++i) {
-                    const float ev = nnb_expf(__fsub_rn(lg[i], m2));
-                    lg[i] = ev;
-                    part += (double)ev;
-                }
-                dsum[tid] = part;
+            __shared__ double dsum[NW + 1];
+            const int chunk = (V + NT - 1) / NT;
+            const int lo = min(V, tid * chunk), hi = min(V, lo + chunk);
+            double part = 0.0;
+            for (int i = lo; i < hi; ++i) {
+                const float ev = nnb_expf(__fsub_rn(lg[i], m2));
+                lg[i] = ev;
+                part += (double)ev;
             }
+            part = warp_sum_d(part);
+            if (lane == 0) dsum[warp] = part;
+            if (tid == 0) sh_tok = V - 1;  // the fallback when the draw is never reached
             __syncthreads();
-            if (tid == 0) {
-                double tot = 0.0;
-                for (int t = 0; t < 256; ++t) tot += dsum[t];
-                const float sumf = (float)tot;
-                double cum = 0.0;
-                int next = V - 1;
-                bool found = false;
-                for (int t = 0; t < 256 && !found; ++t) {
-                    const int l2 = min(V, t * chunk), h2 = min(V, l2 + chunk);
-                    for (int i = l2; i < h2; ++i) {
-                        cum += (double)__fdiv_rn(lg[i], sumf);
-                        if ((double)r <= cum) { next = i; found = true; break; }
+            double tot = 0.0;
+#pragma unroll
+            for (int w = 0; w < NW; ++w) tot += dsum[w];
+            const float sumf = (float)tot;
+            __syncthreads();
+            double cpart = 0.0;
+            for (int i = lo; i < hi; ++i) cpart += (double)__fdiv_rn(lg[i], sumf);
+            // exclusive scan of the chunks' probability mass over the block
+            double incl = cpart;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const double up = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += up;
+            }
+            if (lane == 31) dsum[warp] = incl;
+            __syncthreads();
+            double base = 0.0;
+            for (int w = 0; w < warp; ++w) base += dsum[w];
+            double cum = base + incl - cpart;
+            if ((double)r <= base + incl) {  // the first crossing can only lie in a chunk whose end reaches the draw
+                for (int i = lo; i < hi; ++i) {
+                    cum += (double)__fdiv_rn(lg[i], sumf);
+                    if ((double)r <= cum) {
+                        atomicMin(&sh_tok, i);
+                        break;
                     }
                 }
-                sh_tok = next;
             }
             __syncthreads();
         }

@@ -142,6 +142,17 @@ struct Epi {
     // row * n_mat + c % n_mat (n_mat = N and mat_stride = 0 for a single matrix)
     int n_mat;
     size_t mat_stride;
+    // LM head fused with the categorical distribution (EPI 2 and 3): the logits x = (tau*s)*acc + bias never
+    // reach memory.  EPI 2 leaves, per (row, half column tile), the partial log-sum-exp triple
+    // (max, sum e^(x-max), sum (x-max) e^(x-max)) in part_m / part_s / part_u [(2*tile + half) * M + row] and the
+    // action's logit in act_logit[row].  EPI 3 recomputes x and writes d loss / d logits, already multiplied by
+    // tau and rounded to bf16 (the operand of the head's backward GEMMs), to dyb (M, N), and the column sums of
+    // every 32-row block to db_part[(row / 32) * N + col] (the bias gradient, finished in a fixed order).
+    const int32_t* actions;
+    float *part_m, *part_s, *part_u, *act_logit;
+    const float *lse, *ent, *up_lp, *up_ent;
+    __nv_bfloat16* dyb;
+    float* db_part;
 };
 
 // KIND 0: int8 (A, B K-major, 128 k per stage).  KIND 1: bf16 (64 k per stage), A/B K- or MN-major.
@@ -279,6 +290,150 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const int row0 = tm * BM + quarter * 32;
             const int row = row0 + lane;
             constexpr int NCHUNK = BN / 64;  // 32-column chunks per warp
+            if constexpr (EPI == 2 || EPI == 3) {
+                // ---- LM head fused with log-softmax: a thread owns one row of the accumulator (what tcgen05.ld hands it)
+                const bool valid = row < M;
+                const float srow = valid ? ep.s[row] : 0.0f;
+                const int act = valid ? ep.actions[row] : -1;
+                float m_run = -INFINITY, s_run = 0.0f, u_run = 0.0f, ax = 0.0f;
+                bool have_ax = false;
+                float lse_r = 0.0f, h_r = 0.0f, ul = 0.0f, ue = 0.0f;
+                if (EPI == 3 && valid) {
+                    lse_r = ep.lse[row];
+                    ul = ep.up_lp[row];
+                    if (ep.up_ent) {
+                        ue = ep.up_ent[row];
+                        h_r = ep.ent[row];
+                    }
+                }
+                const bool vec_ok = (((uintptr_t)ep.tau | (uintptr_t)ep.bias) & 15) == 0;
+                if (!mbar_wait(&acc_full[acc], (tcount >> 1) & 1, abort_flag)) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+#pragma unroll 1
+                for (int ci = 0; ci < NCHUNK; ++ci) {
+                    const int c0 = chalf * (BN / 2) + ci * 32;
+                    const int col0 = tn * BN + c0;
+                    uint32_t r[32];
+                    tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + c0, r);
+                    if (col0 >= N) continue;  // warp-uniform
+                    const bool full = col0 + 32 <= N;
+                    float x[32];
+                    if (full && vec_ok) {
+#pragma unroll
+                        for (int j4 = 0; j4 < 8; ++j4) {
+                            const float4 t4 = *reinterpret_cast<const float4*>(ep.tau + col0 + 4 * j4);
+                            const float4 b4 = ep.bias ? *reinterpret_cast<const float4*>(ep.bias + col0 + 4 * j4) : make_float4(0.f, 0.f, 0.f, 0.f);
+                            x[4 * j4 + 0] = __fadd_rn(__fmul_rn(__fmul_rn(t4.x, srow), (float)(int)r[4 * j4 + 0]), b4.x);
+                            x[4 * j4 + 1] = __fadd_rn(__fmul_rn(__fmul_rn(t4.y, srow), (float)(int)r[4 * j4 + 1]), b4.y);
+                            x[4 * j4 + 2] = __fadd_rn(__fmul_rn(__fmul_rn(t4.z, srow), (float)(int)r[4 * j4 + 2]), b4.z);
+                            x[4 * j4 + 3] = __fadd_rn(__fmul_rn(__fmul_rn(t4.w, srow), (float)(int)r[4 * j4 + 3]), b4.w);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const int col = col0 + j;
+                            x[j] = col < N ? __fadd_rn(__fmul_rn(__fmul_rn(ep.tau[col], srow), (float)(int)r[j]), ep.bias ? ep.bias[col] : 0.0f)
+                                           : -INFINITY;
+                        }
+                    }
+                    if constexpr (EPI == 2) {
+                        float cm = x[0];
+#pragma unroll
+                        for (int j = 1; j < 32; ++j) cm = fmaxf(cm, x[j]);
+                        if (cm > m_run) {
+                            if (m_run > -INFINITY) {
+                                const float f = __expf(m_run - cm);
+                                u_run = f * (u_run + (m_run - cm) * s_run);
+                                s_run *= f;
+                            }
+                            m_run = cm;
+                        }
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const float d = x[j] - m_run;  // -inf for a column past the vocabulary
+                            const float ev = __expf(d);
+                            s_run += ev;
+                            u_run += ev > 0.0f ? d * ev : 0.0f;
+                            if (col0 + j == act) { ax = x[j]; have_ax = true; }
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const bool in = full || col0 + j < N;
+                            const float lp = x[j] - lse_r;
+                            const float pr = in ? __expf(lp) : 0.0f;
+                            float dl = ul * ((col0 + j == act ? 1.0f : 0.0f) - pr);
+                            if (ue != 0.0f) dl -= ue * pr * (lp + h_r);
+                            r[j] = __float_as_uint(in ? dl : 0.0f);
+                        }
+                        // transpose the 32 x 32 block through the staging tile: afterwards a lane holds 4 columns of 8 rows
+#pragma unroll
+                        for (int c4 = 0; c4 < 8; ++c4)
+                            *reinterpret_cast<uint4*>(stg + lane * 32 + ((c4 ^ (lane & 7)) << 2)) =
+                                make_uint4(r[4 * c4], r[4 * c4 + 1], r[4 * c4 + 2], r[4 * c4 + 3]);
+                        __syncwarp();
+                        float4 cs = make_float4(0.f, 0.f, 0.f, 0.f);
+                        float4 t4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                        const int colb = col0 + lc;
+                        if (vec_ok && colb + 3 < N) t4 = *reinterpret_cast<const float4*>(ep.tau + colb);
+                        else {
+                            if (colb + 3 < N) t4.w = ep.tau[colb + 3];
+                            if (colb < N) t4.x = ep.tau[colb];
+                            if (colb + 1 < N) t4.y = ep.tau[colb + 1];
+                            if (colb + 2 < N) t4.z = ep.tau[colb + 2];
+                        }
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int rr = i * 4 + lr;
+                            const float4 a = *reinterpret_cast<const float4*>(stg + rr * 32 + (((lane & 7) ^ (rr & 7)) << 2));
+                            cs.x += a.x; cs.y += a.y; cs.z += a.z; cs.w += a.w;
+                            if (row0 + rr < M) {
+                                __nv_bfloat16* dst = ep.dyb + (size_t)(row0 + rr) * N + colb;
+                                if (colb + 3 < N) {
+                                    const __nv_bfloat162 p0 = __floats2bfloat162_rn(a.x * t4.x, a.y * t4.y);
+                                    const __nv_bfloat162 p1 = __floats2bfloat162_rn(a.z * t4.z, a.w * t4.w);
+                                    uint2 o;
+                                    o.x = *reinterpret_cast<const uint32_t*>(&p0);
+                                    o.y = *reinterpret_cast<const uint32_t*>(&p1);
+                                    *reinterpret_cast<uint2*>(dst) = o;
+                                } else {
+                                    if (colb < N) dst[0] = __float2bfloat16_rn(a.x * t4.x);
+                                    if (colb + 1 < N) dst[1] = __float2bfloat16_rn(a.y * t4.y);
+                                    if (colb + 2 < N) dst[2] = __float2bfloat16_rn(a.z * t4.z);
+                                }
+                            }
+                        }
+                        // column sums over the block's 32 rows: the four lane groups (lr = 0..3) hold 8 rows each
+                        cs.x += __shfl_xor_sync(0xffffffffu, cs.x, 8); cs.y += __shfl_xor_sync(0xffffffffu, cs.y, 8);
+                        cs.z += __shfl_xor_sync(0xffffffffu, cs.z, 8); cs.w += __shfl_xor_sync(0xffffffffu, cs.w, 8);
+                        cs.x += __shfl_xor_sync(0xffffffffu, cs.x, 16); cs.y += __shfl_xor_sync(0xffffffffu, cs.y, 16);
+                        cs.z += __shfl_xor_sync(0xffffffffu, cs.z, 16); cs.w += __shfl_xor_sync(0xffffffffu, cs.w, 16);
+                        if (lr == 0 && row0 < M) {
+                            float* dp = ep.db_part + (size_t)(row0 >> 5) * N + colb;
+                            if (colb + 3 < N) *reinterpret_cast<float4*>(dp) = cs;
+                            else {
+                                if (colb < N) dp[0] = cs.x;
+                                if (colb + 1 < N) dp[1] = cs.y;
+                                if (colb + 2 < N) dp[2] = cs.z;
+                            }
+                        }
+                        __syncwarp();
+                    }
+                }
+                if constexpr (EPI == 2) {
+                    if (valid) {
+                        const size_t pi = (size_t)(tn * 2 + chalf) * M + row;
+                        ep.part_m[pi] = m_run;
+                        ep.part_s[pi] = s_run;
+                        ep.part_u[pi] = u_run;
+                        if (have_ax) ep.act_logit[row] = ax;
+                    }
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[acc]);
+                continue;
+            }
             // what a chunk needs from global memory (tau, bias, and the residual or the values to accumulate
             // into) is fetched one chunk ahead, the first chunk's before the accumulator is even ready, so
             // that DRAM latency stays off the path between tcgen05.ld and the stores
@@ -517,6 +672,114 @@ nnb_status tc_set_forward_tile(int bn)
 {
     NNB_REQUIRE(bn == 0 || bn == 64 || bn == 128 || bn == 192 || bn == 256, "forward tile width %d: 0 (automatic), 64, 128, 192 or 256", bn);
     g_forward_bn_override = bn;
+    return NNB_OK;
+}
+
+// ---- LM head fused with CategoricalDistribution (include/neuralnet.cpp/rl_policy.hpp:92-187; the reference's own
+// pattern for not re-reading (V, T) logits is the online log-sum-exp fold of its sparse cross-entropy,
+// include/neuralnet.cpp/compute_loss.hpp:315-429).
+// merge of the per-tile partials: lse = m + log s, logp = x_action - lse, H = log s - u / s
+__global__ void __launch_bounds__(256)
+lmhead_merge_kernel(const float* __restrict__ pm, const float* __restrict__ ps, const float* __restrict__ pu,
+                    const float* __restrict__ act_logit, int n_part, int M, float* __restrict__ lse, float* __restrict__ logp,
+                    float* __restrict__ ent)
+{
+    const int row = blockIdx.x * 256 + threadIdx.x;
+    if (row >= M) return;
+    float m = -INFINITY;
+    for (int p = 0; p < n_part; ++p) m = fmaxf(m, pm[(size_t)p * M + row]);
+    float s = 0.0f, u = 0.0f;
+    for (int p = 0; p < n_part; ++p) {
+        const float sp = ps[(size_t)p * M + row];
+        if (sp > 0.0f) {
+            const float dm = pm[(size_t)p * M + row] - m;
+            const float f = __expf(dm);
+            s += sp * f;
+            u += (pu[(size_t)p * M + row] + dm * sp) * f;
+        }
+    }
+    const float ls = __logf(s);
+    lse[row] = m + ls;
+    if (logp) logp[row] = act_logit[row] - (m + ls);
+    if (ent) ent[row] = ls - u / s;
+}
+
+size_t tc_lmhead_scratch_floats(size_t t, size_t v)
+{
+    const size_t n_part = 2 * ceil_div(v, (size_t)256);
+    const size_t fwd = 3 * n_part * t + t;             // partial triples + the action's logit
+    const size_t bwd = ceil_div(t, (size_t)32) * v;    // column sums per 32-row block
+    return fwd > bwd ? fwd : bwd;
+}
+
+// forward: log-prob of the action, entropy (optional) and log-sum-exp of every row, logits never stored.
+// scratch: tc_lmhead_scratch_floats(t, v) floats
+nnb_status launch_tc_lmhead_fwd(nnb_engine* e, const int8_t* q, const int8_t* w8, const float* tau, const float* s, const float* bias,
+                                const int32_t* actions, size_t t, size_t k, size_t v, float* scratch, float* lse, float* logp, float* ent)
+{
+    using namespace tc;
+    constexpr int BN = 256;
+    const size_t n_part = 2 * ceil_div(v, (size_t)BN);
+    CUtensorMap ta, tb;
+    NNB_TRY(make_map(&ta, q, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, t, k, 128, BM));
+    NNB_TRY(make_map(&tb, w8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, v, k, 128, BN));
+    Epi ep{};
+    ep.tau = tau;
+    ep.s = s;
+    ep.bias = bias;
+    ep.n_mat = (int)v;
+    ep.actions = actions;
+    ep.part_m = scratch;
+    ep.part_s = scratch + n_part * t;
+    ep.part_u = scratch + 2 * n_part * t;
+    ep.act_logit = scratch + 3 * n_part * t;
+    NNB_TRY((launch<0, false, false, 2, BN>(e, ta, tb, ep, t, v, k)));
+    lmhead_merge_kernel<<<(unsigned)ceil_div(t, 256), 256, 0, e->stream>>>(ep.part_m, ep.part_s, ep.part_u, ep.act_logit, (int)n_part, (int)t,
+                                                                          lse, logp, ent);
+    e->launches++;
+    NNB_CHECK_LAUNCH("lmhead_merge_kernel");
+    return NNB_OK;
+}
+
+__global__ void __launch_bounds__(256)
+colsum_blocks_kernel(const float* __restrict__ part, int n_blocks, int O, float* __restrict__ db)
+{
+    const int o = blockIdx.x * 256 + threadIdx.x;
+    if (o >= O) return;
+    float acc = 0.0f;
+    for (int c = 0; c < n_blocks; ++c) acc += part[(size_t)c * O + o];
+    db[o] += acc;
+}
+
+// backward: dyb (t, v) bf16 = bf16(d loss / d logits * tau) with d logits = (onehot - p) * up_lp - p * (log p + H) * up_ent
+// recomputed from the same integer GEMM, and db += column sums of d logits.  v % 4 == 0.
+nnb_status launch_tc_lmhead_bwd(nnb_engine* e, const int8_t* q, const int8_t* w8, const float* tau, const float* s, const float* bias,
+                                const int32_t* actions, const float* lse, const float* ent, const float* up_lp, const float* up_ent,
+                                size_t t, size_t k, size_t v, float* scratch, __nv_bfloat16* dyb, float* db)
+{
+    using namespace tc;
+    constexpr int BN = 256;
+    NNB_REQUIRE(v % 4 == 0 && (((uintptr_t)dyb | (uintptr_t)scratch) & 15) == 0, "fused LM-head backward: vocabulary %zu must be a multiple of 4", v);
+    CUtensorMap ta, tb;
+    NNB_TRY(make_map(&ta, q, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, t, k, 128, BM));
+    NNB_TRY(make_map(&tb, w8, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, v, k, 128, BN));
+    Epi ep{};
+    ep.tau = tau;
+    ep.s = s;
+    ep.bias = bias;
+    ep.n_mat = (int)v;
+    ep.actions = actions;
+    ep.lse = lse;
+    ep.ent = ent;
+    ep.up_lp = up_lp;
+    ep.up_ent = up_ent;
+    ep.dyb = dyb;
+    ep.db_part = scratch;
+    NNB_TRY((launch<0, false, false, 3, BN>(e, ta, tb, ep, t, v, k)));
+    const size_t n_blocks = ceil_div(t, (size_t)32);
+    colsum_blocks_kernel<<<(unsigned)ceil_div(v, 256), 256, 0, e->stream>>>(scratch, (int)n_blocks, (int)v, db);
+    e->launches++;
+    NNB_CHECK_LAUNCH("colsum_blocks_kernel");
     return NNB_OK;
 }
 

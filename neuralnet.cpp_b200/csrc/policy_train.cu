@@ -50,6 +50,10 @@ struct TrainWs {
     __nv_bfloat16 *dyb = nullptr, *xs = nullptr;  // bf16 operand scratch of the tcgen05 backward GEMMs
     __nv_bfloat16* dob = nullptr;                 // bf16 copy of the attention output gradient
     bool b16_attn = false;
+    // fast mode: the LM head's GEMM computes log-prob / entropy in its epilogue and its backward operand is recomputed
+    // from the same integer GEMM, so the (decisions x vocabulary) f32 logits do not exist
+    bool fused_head = false;
+    float *lse = nullptr, *head_scratch = nullptr;
 };
 
 static void free_ws(void*& slot)
@@ -97,6 +101,7 @@ static nnb_status ensure_train(nnb_policy* p, size_t n_seq, size_t S, size_t P, 
     // fast mode: attention runs on bf16 copies of q, k, v; those are what a layer keeps for its backward,
     // and the f32 projections become one buffer shared by all layers
     w->b16_attn = !c.exact && attn_b16_supported(d / H, d);
+    w->fused_head = with_head && !c.exact && p->w8 != nullptr && V % 8 == 0 && Td >= 64;
     // carve one arena: first pass measures, second assigns
     for (int pass = 0; pass < 2; ++pass) {
         size_t off = 0;
@@ -140,7 +145,12 @@ static nnb_status ensure_train(nnb_policy* p, size_t n_seq, size_t S, size_t P, 
         w->hn = (float*)take(Td * d * 4);
         w->qh = (int8_t*)take(Td * d);
         w->sh = (float*)take(Td * 4);
-        w->logits = (float*)take(Td * V * 4);
+        if (w->fused_head) {
+            w->lse = (float*)take(Td * 4);
+            w->head_scratch = (float*)take(tc_lmhead_scratch_floats(Td, V) * 4);
+        } else {
+            w->logits = (float*)take(Td * V * 4);
+        }
         w->logp = (float*)take(Td * 4);
         w->ent = (float*)take(Td * 4);
         w->value = (float*)take(Td * 4);
@@ -267,8 +277,13 @@ static nnb_status forward(nnb_policy* p, const int32_t* tokens, size_t n_seq, si
     gather_actions_kernel<<<(unsigned)ceil_div(Td, 256), 256, 0, e->stream>>>(tokens, (int)S, (int)P, (int)G, Td, w->actions);
     e->launches++;
     NNB_TRY(launch_row_quant(e, 0, exact, w->xd, PP + p->lnf_g, Td, d, d, w->qh, w->sh, w->qsum, w->hn));
-    NNB_TRY(lin_fwd(p, p->head, 1, w->qh, w->sh, w->qsum, Td, nullptr, w->logits, 0));
-    NNB_TRY(launch_categorical_fwd(e, w->logits, w->actions, Td, V, w->logp, want_entropy ? w->ent : nullptr));
+    if (w->fused_head) {
+        NNB_TRY(launch_tc_lmhead_fwd(e, w->qh, p->w8 + p->head.packed_off * 16, p->tau + p->head.tau_off, w->sh, PP + p->head.b_off,
+                                     w->actions, Td, d, V, w->head_scratch, w->lse, w->logp, want_entropy ? w->ent : nullptr));
+    } else {
+        NNB_TRY(lin_fwd(p, p->head, 1, w->qh, w->sh, w->qsum, Td, nullptr, w->logits, 0));
+        NNB_TRY(launch_categorical_fwd(e, w->logits, w->actions, Td, V, w->logp, want_entropy ? w->ent : nullptr));
+    }
     if (c.value_head) NNB_TRY(launch_value_fwd(e, w->hn, PP + p->value_w, PP + p->value_b, Td, d, w->value));
     return NNB_OK;
 }
@@ -318,8 +333,14 @@ static nnb_status backward(nnb_policy* p, const int32_t* tokens, size_t n_seq, s
     const bool grouped = w->map.group > 1;
     const float* PP = p->params;
     float* GG = p->grads;
-    // head: logits buffer now holds dlogits
-    NNB_TRY(lin_bwd(p, p->head, w->logits, w->qh, w->sh, Td, w->dhn, false));
+    if (w->fused_head) {
+        // w->dyb already holds bf16(dlogits * tau) and the bias gradient is done (launch_tc_lmhead_bwd)
+        NNB_REQUIRE(tc_bwd_ok(p, V, Td), "fused LM head: the tensor-core backward is not available");
+        NNB_TRY(lin_bwd_gemms(p, p->head, V, w->qh, w->sh, Td, w->dhn, false));
+    } else {
+        // head: logits buffer now holds dlogits
+        NNB_TRY(lin_bwd(p, p->head, w->logits, w->qh, w->sh, Td, w->dhn, false));
+    }
     if (c.value_head)
         NNB_TRY(launch_value_bwd(e, w->hn, PP + p->value_w, w->dvalue, Td, d, w->dhn, GG + p->value_w, GG + p->value_b));
     NNB_TRY(launch_rmsnorm_bwd(e, w->xd, PP + p->lnf_g, w->dhn, nullptr, Td, d, w->xd, GG + p->lnf_g));
@@ -487,7 +508,13 @@ nnb_status nnb_policy_train_step_grouped(nnb_policy* p, const int32_t* d_tokens,
         NNB_CUDA(cudaMemsetAsync(w->dvalue, 0, Td * 4, e->stream));
         NNB_CUDA(cudaMemsetAsync(w->vreport, 0, 8, e->stream));
     }
-    NNB_TRY(launch_categorical_bwd(e, w->logits, w->actions, w->up_lp, use_ent ? w->up_ent : nullptr, Td, V, w->logits));
+    if (w->fused_head) {
+        NNB_TRY(launch_tc_lmhead_bwd(e, w->qh, p->w8 + p->head.packed_off * 16, p->tau + p->head.tau_off, w->sh,
+                                     p->params + p->head.b_off, w->actions, w->lse, w->ent, w->up_lp, use_ent ? w->up_ent : nullptr, Td,
+                                     (size_t)p->cfg.d_model, V, w->head_scratch, w->dyb, p->grads + p->head.b_off));
+    } else {
+        NNB_TRY(launch_categorical_bwd(e, w->logits, w->actions, w->up_lp, use_ent ? w->up_ent : nullptr, Td, V, w->logits));
+    }
     NNB_TRY(backward(p, d_tokens, n_seq, seq_len, prompt_len));
     if (d_report) {
         NNB_CUDA(cudaMemcpyAsync(d_report, w->report, 8 * 4, cudaMemcpyDeviceToDevice, e->stream));

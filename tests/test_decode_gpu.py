@@ -87,6 +87,9 @@ def test_sampling_config_rollout_token_identical(pkg, eng, kw):
         bias[::3] = -np.inf  # a third of the vocabulary is forbidden
         bias[7] = 2.5
     eos, min_new = kw.pop("eos_token", -1), kw.pop("min_new_tokens", 0)
+    if eos >= 0:  # an end-of-sequence id that the rollout does sample: the most frequent token of the unconstrained run
+        free_run, _, _ = m.rollout_cfg(prompts, 20, seed=77, seq0=3, **kw)
+        eos = int(np.bincount(free_run[:, 5 + min_new:5 + 12].ravel()).argmax())
     tok_ref, lp_ref, len_ref = m.rollout_cfg(prompts, 20, bias=bias, eos=eos, min_new=min_new, seed=77, seq0=3, **kw)
     sc = pkg.SamplingConfig(seed=77, eos_token=eos, min_new_tokens=min_new,
                             logit_bias=None if bias is None else torch.from_numpy(bias).to(eng.device), **kw)

@@ -222,3 +222,16 @@ def test_plain_c_client_runs(pkg, tmp_path):
     got = [float(x) for x in lines[1].split()]
     s = (2.0 / 3.0) ** 0.5
     assert np.allclose(got, [-1 / s, 0, 1 / s, 0, 0, 0], atol=1e-5)
+
+
+def test_cpp_engine_shim_runs(pkg, tmp_path):
+    """tests/cabi/shim_test.cpp on the GPU: BitLinear forward (Y bitwise) / backward through the reference's call
+    sequence, the write-epoch cache, the data-movement verbs, and RLTrainingPipeline::run over a device-side rollout
+    source with a GRPO-style update."""
+    import subprocess
+
+    from test_abi_symbols import _compile_shim_test
+
+    r = subprocess.run([_compile_shim_test(tmp_path, pkg)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr + r.stdout
+    assert "shim ok" in r.stdout
