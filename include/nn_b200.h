@@ -216,6 +216,21 @@ nnb_status nnb_expand_weights(nnb_engine* e, const uint32_t* d_wq, size_t rows, 
 nnb_status nnb_bitlinear_fwd_tc(nnb_engine* e, const int8_t* d_w8, const float* d_tau, const float* d_bias,
                                 const float* d_residual, const int8_t* d_q, const float* d_s, size_t t, size_t k,
                                 size_t out, float* d_y);
+/* The LM head fused with CategoricalDistribution::log_prob / entropy and their gradients
+ * (include/neuralnet.cpp/rl_policy.hpp:92-187): the logits x = (tau*s)*acc + bias of nnb_bitlinear_fwd_tc are consumed in
+ * the GEMM's epilogue and never stored, as the reference's sparse cross-entropy folds its log-sum-exp online instead of
+ * re-reading (V, T) logits (include/neuralnet.cpp/compute_loss.hpp:315-429).
+ * fwd: d_logp[t] = x[t, action] - lse, d_entropy[t] = -sum p log p (may be NULL), d_lse[t] = log sum exp(x[t, :]).
+ * bwd: d logits = (onehot - p) * up_logp + (-p * (log p + H)) * up_entropy, recomputed from the same integer GEMM;
+ * d_dyb (t, v) bf16 receives d logits * tau, the operand nnb_bitlinear_bwd_tc takes with d_dy == NULL, and d_dbias (v)
+ * is incremented by the column sums of d logits.  d_up_entropy may be NULL.  Requires v % 4 == 0 in the backward. */
+nnb_status nnb_lmhead_logprob_entropy_fwd(nnb_engine* e, const int8_t* d_w8, const float* d_tau, const float* d_bias, const int8_t* d_q,
+                                          const float* d_s, const int32_t* d_actions, size_t t, size_t k, size_t v, float* d_logp,
+                                          float* d_entropy, float* d_lse);
+nnb_status nnb_lmhead_logprob_entropy_bwd(nnb_engine* e, const int8_t* d_w8, const float* d_tau, const float* d_bias, const int8_t* d_q,
+                                          const float* d_s, const int32_t* d_actions, const float* d_lse, const float* d_entropy,
+                                          const float* d_up_logp, const float* d_up_entropy, size_t t, size_t k, size_t v, void* d_dyb,
+                                          float* d_dbias);
 /* Tuning knob, process-wide: width of the 128 x bn output tile of nnb_bitlinear_fwd_tc (64, 128, 192 or
  * 256); 0 restores the automatic choice from the problem shape.  Results do not depend on it. */
 nnb_status nnb_tc_set_forward_tile(int bn);

@@ -93,6 +93,8 @@ _SIGNATURES = {
     "nnb_tc_set_forward_tile": (_I, [_I]),
     "nnb_bitlinear_fwd_tc": (_I, [_P, _P, _P, _P, _P, _P, _P, _SZ, _SZ, _SZ, _P]),
     "nnb_bitlinear_bwd_tc": (_I, [_P, _P, _P, _P, _P, _P, _SZ, _SZ, _SZ, _P, _P, _P, _I, _P]),
+    "nnb_lmhead_logprob_entropy_fwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _SZ, _SZ, _SZ, _P, _P, _P]),
+    "nnb_lmhead_logprob_entropy_bwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _SZ, _SZ, _SZ, _P, _P]),
     "nnb_engine_check": (_I, [_P]),
     "nnb_attention_fwd": (_I, [_P, _P, _P, _P, _SZ, _SZ, _SZ, _SZ, _I, _P, _P]),
     "nnb_attention_bwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _SZ, _SZ, _SZ, _SZ, _I, _P, _P, _P, _P]),

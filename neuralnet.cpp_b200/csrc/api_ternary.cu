@@ -127,6 +127,30 @@ nnb_status nnb_bitlinear_fwd_tc(nnb_engine* e, const int8_t* d_w8, const float* 
 
 nnb_status nnb_tc_set_forward_tile(int bn) { return tc_set_forward_tile(bn); }
 
+nnb_status nnb_lmhead_logprob_entropy_fwd(nnb_engine* e, const int8_t* d_w8, const float* d_tau, const float* d_bias, const int8_t* d_q,
+                                          const float* d_s, const int32_t* d_actions, size_t t, size_t k, size_t v, float* d_logp,
+                                          float* d_entropy, float* d_lse)
+{
+    NNB_REQUIRE(e && d_w8 && d_tau && d_q && d_s && d_actions && d_logp && d_lse, "lmhead_logprob_entropy_fwd: NULL argument");
+    NNB_REQUIRE(t > 0 && v > 0 && k > 0 && k % 64 == 0, "lmhead_logprob_entropy_fwd: k=%zu must be a multiple of 64", k);
+    NNB_TRY(e->ensure_scratch(tc_lmhead_scratch_floats(t, v) * sizeof(float)));
+    return launch_tc_lmhead_fwd(e, d_q, d_w8, d_tau, d_s, d_bias, d_actions, t, k, v, (float*)e->scratch, d_lse, d_logp, d_entropy);
+}
+
+nnb_status nnb_lmhead_logprob_entropy_bwd(nnb_engine* e, const int8_t* d_w8, const float* d_tau, const float* d_bias, const int8_t* d_q,
+                                          const float* d_s, const int32_t* d_actions, const float* d_lse, const float* d_entropy,
+                                          const float* d_up_logp, const float* d_up_entropy, size_t t, size_t k, size_t v, void* d_dyb,
+                                          float* d_dbias)
+{
+    NNB_REQUIRE(e && d_w8 && d_tau && d_q && d_s && d_actions && d_lse && d_up_logp && d_dyb && d_dbias,
+                "lmhead_logprob_entropy_bwd: NULL argument");
+    NNB_REQUIRE(d_up_entropy == nullptr || d_entropy, "lmhead_logprob_entropy_bwd: the entropy gradient needs the forward's entropy");
+    NNB_REQUIRE(t > 0 && v > 0 && v % 4 == 0 && k > 0 && k % 64 == 0, "lmhead_logprob_entropy_bwd: needs k %% 64 == 0 and v %% 4 == 0");
+    NNB_TRY(e->ensure_scratch(tc_lmhead_scratch_floats(t, v) * sizeof(float)));
+    return launch_tc_lmhead_bwd(e, d_q, d_w8, d_tau, d_s, d_bias, d_actions, d_lse, d_entropy, d_up_logp, d_up_entropy, t, k, v,
+                                (float*)e->scratch, (__nv_bfloat16*)d_dyb, d_dbias);
+}
+
 nnb_status nnb_bitlinear_bwd_tc(nnb_engine* e, const float* d_dy, const float* d_tau, const void* d_wb,
                                 const int8_t* d_q, const float* d_s, size_t t, size_t k, size_t out, void* d_dyb,
                                 void* d_xs, float* d_dx, int accumulate_dx, float* d_dw)

@@ -325,6 +325,29 @@ def bitlinear_fwd_tc(self, w8, tau, bias, q, s, residual=None, y=None):
     return y
 
 
+def lmhead_logprob_entropy(self, w8, tau, bias, q, s, actions, want_entropy=True):
+    """LM head fused with log-prob / entropy: returns (logp, entropy, lse), each (t,)."""
+    t, k = q.shape
+    v = w8.shape[0]
+    logp, lse = _f32(self, t), _f32(self, t)
+    ent = _f32(self, t) if want_entropy else None
+    check(self._lib.nnb_lmhead_logprob_entropy_fwd(self._h, _ptr(w8), _ptr(tau), _ptr(bias), _ptr(q), _ptr(s), _ptr(actions), t, k, v,
+                                                   _ptr(logp), _ptr(ent), _ptr(lse)))
+    return logp, ent, lse
+
+
+def lmhead_logprob_entropy_backward(self, w8, tau, bias, q, s, actions, lse, ent, up_logp, up_entropy=None, dbias=None):
+    """Returns (dyb (t, v) bf16 = d logits * tau, dbias (v) incremented by the column sums of d logits)."""
+    t, k = q.shape
+    v = w8.shape[0]
+    dyb = torch.empty((t, v), device=self.device, dtype=torch.bfloat16)
+    if dbias is None:
+        dbias = torch.zeros(v, device=self.device, dtype=torch.float32)
+    check(self._lib.nnb_lmhead_logprob_entropy_bwd(self._h, _ptr(w8), _ptr(tau), _ptr(bias), _ptr(q), _ptr(s), _ptr(actions), _ptr(lse),
+                                                   _ptr(ent), _ptr(up_logp), _ptr(up_entropy), t, k, v, _ptr(dyb), _ptr(dbias)))
+    return dyb, dbias
+
+
 def set_tc_forward_tile(self, bn: int = 0):
     """Process-wide width of the tensor-core forward's output tile (64/128/192/256; 0 = automatic)."""
     check(self._lib.nnb_tc_set_forward_tile(int(bn)))
@@ -422,3 +445,7 @@ Engine.attention_fwd = attention_fwd
 Engine.attention_bwd = attention_bwd
 Engine.attention_rope_fwd = attention_rope_fwd
 Engine.attention_rope_bwd = attention_rope_bwd
+
+
+for _f in (lmhead_logprob_entropy, lmhead_logprob_entropy_backward):
+    setattr(Engine, _f.__name__, _f)

@@ -91,3 +91,49 @@ def test_backward_tc(eng, orc, t, k, out):
     dx2, dw2 = eng.bitlinear_bwd_tc(_dev(dY, eng), _dev(tau, eng), wb, q, s, k, dw=dw, dx=dx, accumulate_dx=True)
     assert np.abs(dx2.cpu().numpy() - 2 * dx_ref).max() <= 2e-2 * 2 * np.abs(dx_ref).max()
     assert np.abs(dw2.cpu().numpy() - 2 * dw_ref).max() <= 2e-2 * 2 * np.abs(dw_ref).max()
+
+
+@pytest.mark.parametrize("t,k,v", [(128, 128, 256), (200, 192, 536), (1024, 2048, 32000), (70, 256, 10000)])
+def test_lmhead_fused_logprob_entropy_forward_and_backward(eng, orc, t, k, v):
+    """The LM head fused with CategoricalDistribution::log_prob / entropy and their gradients: logits are never stored.
+    Against the same quantities computed in f64 from the materialised logits of the bit-exact forward: log-prob, entropy
+    and log-sum-exp within 1e-5 of the logits' range, the bf16 backward operand within bf16 rounding, the bias gradient
+    within 1e-3 (ragged last tiles: 536 = 2 x 256 + 24, 10000 = 39 x 256 + 16)."""
+    W, tau, X, bias = _case(orc, t, k, v, t + k + v)
+    packed = orc.trit_pack(W, tau)
+    q, s, _ = eng.act_quant_tm(_dev(X, eng))
+    w8, _ = eng.expand_weights(_dev(packed.view(np.int32), eng), k, want_bf16=False)
+    d_tau, d_bias = _dev(tau, eng), _dev(bias, eng)
+    rng = np.random.default_rng(7)
+    actions = rng.integers(0, v, t).astype(np.int32)
+    actions[:4] = [0, v - 1, 255 % v, 256 % v]  # tile borders
+    d_act = _dev(actions, eng)
+    logits = eng.bitlinear_fwd_tc(w8, d_tau, d_bias, q, s).double()
+    lse_ref = torch.logsumexp(logits, 1)
+    lp_all = logits - lse_ref[:, None]
+    p = lp_all.exp()
+    ent_ref = -(p * lp_all).sum(1)
+    idx = torch.arange(t, device=eng.device)
+    logp_ref = lp_all[idx, d_act.long()]
+    logp, ent, lse = eng.lmhead_logprob_entropy(w8, d_tau, d_bias, q, s, d_act)
+    eng.check_device_errors()
+    scale = float(logits.abs().max())
+    assert (lse.double() - lse_ref).abs().max().item() <= 1e-5 * max(scale, 1.0)
+    assert (logp.double() - logp_ref).abs().max().item() <= 2e-5 * max(scale, 1.0)
+    assert (ent.double() - ent_ref).abs().max().item() <= 1e-4 * max(float(ent_ref.abs().max()), 1.0)
+    up_lp = _dev(rng.normal(0, 1, t).astype(np.float32), eng)
+    up_ent = _dev(rng.normal(0, 0.1, t).astype(np.float32), eng)
+    for ue in (None, up_ent):
+        onehot = torch.zeros_like(p)
+        onehot[idx, d_act.long()] = 1.0
+        dl = (onehot - p) * up_lp.double()[:, None]
+        if ue is not None:
+            dl = dl - p * (lp_all + ent_ref[:, None]) * ue.double()[:, None]
+        dyb_ref = dl * d_tau.double()[None, :]
+        db0 = _dev(rng.normal(0, 1, v).astype(np.float32), eng)
+        dyb, db = eng.lmhead_logprob_entropy_backward(w8, d_tau, d_bias, q, s, d_act, lse, ent, up_lp, ue, dbias=db0.clone())
+        eng.check_device_errors()
+        err = (dyb.double() - dyb_ref).abs().max().item()
+        assert err <= 2.0 ** -7 * float(dyb_ref.abs().max()), err  # bf16 rounding of the operand
+        db_ref = dl.sum(0) + db0.double()
+        assert (db.double() - db_ref).abs().max().item() <= 1e-3 * float(db_ref.abs().max())
