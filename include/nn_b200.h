@@ -313,6 +313,23 @@ nnb_status nnb_policy_upload_params(nnb_policy* p, const float* h_params);
 /* BitLinear::quantize_weights_ for every linear (compute_layer_bitlinear.hpp:627-674):
  * call after the master weights changed */
 nnb_status nnb_policy_requantize(nnb_policy* p);
+/* Model files in the reference's two roles (include/neuralnet.cpp/model_serialization.hpp:40-89; parameter entries
+ * :581-589 byte for byte).  role 0 = model (.nnmodel): ternary weights as TernaryPacked3 (base-3, 1.6 bits per weight)
+ * plus tau; role 1 = checkpoint (.nnckpt): ternary weights as their f32 latent.  Loading a model-role file restores a
+ * trainable policy the way WeightLoadIntent::Trainable does (compute_layer_bitlinear.hpp:262-300): latent = trit *
+ * (tau * K / n), the quantiser's fixed point, with the file's tau and trits seeding the packed weights, so the first
+ * forward reproduces the saved model bit for bit.  The spec record's byte layout and the base-3 digit order live in
+ * modules absent from the reference tree and are this library's own.  The file is verified (tail marker, SHA-256)
+ * before anything is read from it. */
+nnb_status nnb_policy_save(nnb_policy* p, const char* path, int role);
+nnb_status nnb_policy_load(nnb_policy* p, const char* path);
+/* nn::trit_pack row codecs on the host: base-3 disk form <-> 2-bit container, and the dequantisation
+ * L = trit * latent_row_scale, latent_row_scale = tau * K / n (0 for an all-zero row) (src/ternary_gemm_test.cpp:658-735) */
+size_t nnb_trit_base3_bytes_per_row(size_t k);
+void nnb_trit_pack_row_base3(const uint32_t* words, size_t k, uint8_t* out);
+void nnb_trit_unpack_row_base3(const uint8_t* in, size_t k, uint32_t* words);
+float nnb_trit_latent_row_scale(const uint32_t* words, size_t k, float tau);
+void nnb_trit_dequant_row(const uint32_t* words, size_t k, float tau, float* latent);
 /* device pointers of one linear's container and scales; layer < 0 selects the head,
  * which in 0..5 = q, k, v, o, fc1, fc2 */
 nnb_status nnb_policy_linear(nnb_policy* p, int layer, int which, uint32_t** d_packed, float** d_tau,

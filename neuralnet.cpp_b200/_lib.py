@@ -110,6 +110,13 @@ _SIGNATURES = {
     "nnb_policy_tensor_info": (_I, [_P, _SZ, C.c_char_p, _SZ, C.POINTER(_SZ), C.POINTER(_SZ), C.POINTER(_SZ)]),
     "nnb_policy_upload_params": (_I, [_P, _P]),
     "nnb_policy_requantize": (_I, [_P]),
+    "nnb_policy_save": (_I, [_P, C.c_char_p, _I]),
+    "nnb_policy_load": (_I, [_P, C.c_char_p]),
+    "nnb_trit_base3_bytes_per_row": (_SZ, [_SZ]),
+    "nnb_trit_pack_row_base3": (None, [_P, _SZ, _P]),
+    "nnb_trit_unpack_row_base3": (None, [_P, _SZ, _P]),
+    "nnb_trit_latent_row_scale": (C.c_float, [_P, _SZ, C.c_float]),
+    "nnb_trit_dequant_row": (None, [_P, _SZ, C.c_float, _P]),
     "nnb_policy_linear": (_I, [_P, _I, _I, C.POINTER(_P), C.POINTER(_P), C.POINTER(_SZ), C.POINTER(_SZ)]),
     "nnb_rollout": (_I, [_P, _P, _SZ, _SZ, _SZ, C.c_float, _I, C.c_uint64, C.c_uint32, _P, _P, _P]),
     "nnb_policy_logprobs": (_I, [_P, _P, _SZ, _SZ, _SZ, _P, _P, _P]),

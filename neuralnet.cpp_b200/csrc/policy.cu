@@ -154,18 +154,22 @@ nnb_status policy_linear_fwd(nnb_policy* p, const LinW& l, size_t n_mats, const 
                                    nullptr);
 }
 
-nnb_status policy_requantize(nnb_policy* p)
+// seeded = true: tau and the containers were just written from a model file and are authoritative (the first forward
+// then reproduces the saved model bit for bit, compute_layer_bitlinear.hpp:276-300); only the derived copies are rebuilt
+nnb_status policy_requantize(nnb_policy* p, bool seeded)
 {
     p->wb_valid = false;
-    for (auto& L : p->layers) {
-        NNB_TRY(requantize_linear(p, L.q));
-        NNB_TRY(requantize_linear(p, L.k));
-        NNB_TRY(requantize_linear(p, L.v));
-        NNB_TRY(requantize_linear(p, L.o));
-        NNB_TRY(requantize_linear(p, L.fc1));
-        NNB_TRY(requantize_linear(p, L.fc2));
+    if (!seeded) {
+        for (auto& L : p->layers) {
+            NNB_TRY(requantize_linear(p, L.q));
+            NNB_TRY(requantize_linear(p, L.k));
+            NNB_TRY(requantize_linear(p, L.v));
+            NNB_TRY(requantize_linear(p, L.o));
+            NNB_TRY(requantize_linear(p, L.fc1));
+            NNB_TRY(requantize_linear(p, L.fc2));
+        }
+        NNB_TRY(requantize_linear(p, p->head));
     }
-    NNB_TRY(requantize_linear(p, p->head));
     if (!p->cfg.exact) {
         if (!p->w8) {
             cudaError_t er = cudaMalloc((void**)&p->w8, p->packed_words * 16);

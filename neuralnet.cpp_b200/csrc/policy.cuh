@@ -73,7 +73,7 @@ struct nnb_policy {
 };
 
 namespace nnb {
-nnb_status policy_requantize(nnb_policy* p);
+nnb_status policy_requantize(nnb_policy* p, bool seeded = false);
 void policy_free_train(nnb_policy* p);
 // Fast mode: run the teacher-forced forward over n_seq prompts of L tokens and store every layer's rotated keys
 // and values as the (layer, n_seq, head, alloc, dk) bf16 prefix cache of a rollout, instead of L decode steps.

@@ -308,10 +308,21 @@ def step_times(self):
     return ms, pos
 
 
+def save(self, path: str, role: str = "model"):
+    """Write the policy as a model file: role "model" (ternary weights packed base-3 + tau) or "checkpoint" (f32 latent)."""
+    check(self._lib.nnb_policy_save(self._h, str(path).encode(), {"model": 0, "checkpoint": 1}[role]))
+
+
+def load(self, path: str):
+    """Read a model file of either role into this policy (same architecture); a model-role file comes back trainable
+    with bit-identical packed weights."""
+    check(self._lib.nnb_policy_load(self._h, str(path).encode()))
+
+
 def release_workspaces(self):
     check(self._lib.nnb_policy_release_workspaces(self._h))
 
 
-for _f in (rollout_sampled, logprobs, grads_view, zero_grad, train_step, sft_step, optimizer_step, release_workspaces, set_step_timing,
+for _f in (save, load, rollout_sampled, logprobs, grads_view, zero_grad, train_step, sft_step, optimizer_step, release_workspaces, set_step_timing,
            step_times):
     setattr(Policy, _f.__name__, _f)
