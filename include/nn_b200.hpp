@@ -145,7 +145,8 @@ public:
     Result<Tensor> create_tensor(std::size_t rows, std::size_t cols)
     {
         nnb_tensor* t = nullptr;
-        return made(nnb_tensor_create(e_, rows, cols, &t), t, "create_tensor");
+        const nnb_status st = nnb_tensor_create(e_, rows, cols, &t);
+        return made(st, t, "create_tensor");
     }
     Result<Tensor> try_create_tensor(std::size_t rows, std::size_t cols) { return create_tensor(rows, cols); }
     Result<Tensor> from_vector(std::size_t rows, std::size_t cols, const std::vector<float>& values)
@@ -167,24 +168,28 @@ public:
     Result<Tensor> clone(const Tensor& src)
     {
         nnb_tensor* t = nullptr;
-        return made(nnb_t_clone(src.raw(), &t), t, "clone");
+        const nnb_status st = nnb_t_clone(src.raw(), &t);
+        return made(st, t, "clone");
     }
     Result<void> copy_into(const Tensor& src, Tensor& dst) { return done(nnb_t_copy_into(dst.raw(), src.raw()), "copy_into"); }
     Result<Tensor> transpose(const Tensor& src)
     {
         nnb_tensor* t = nullptr;
-        return made(nnb_t_transpose(src.raw(), &t), t, "transpose");
+        const nnb_status st = nnb_t_transpose(src.raw(), &t);
+        return made(st, t, "transpose");
     }
     Result<Tensor> slice_rows(const Tensor& src, std::size_t start_row, std::size_t count)
     {
         nnb_tensor* t = nullptr;
-        return made(nnb_t_slice_rows(src.raw(), start_row, count, &t), t, "slice_rows");
+        const nnb_status st = nnb_t_slice_rows(src.raw(), start_row, count, &t);
+        return made(st, t, "slice_rows");
     }
     Result<void> insert_rows(Tensor& dst, std::size_t row, const Tensor& src) { return done(nnb_t_insert_rows(dst.raw(), row, src.raw()), "insert_rows"); }
     Result<Tensor> gather_rows(const Tensor& table, const Tensor& indices)
     {
         nnb_tensor* t = nullptr;
-        return made(nnb_t_gather_rows(table.raw(), indices.raw(), &t), t, "gather_rows");
+        const nnb_status st = nnb_t_gather_rows(table.raw(), indices.raw(), &t);
+        return made(st, t, "gather_rows");
     }
     Result<void> scatter_add_rows(Tensor& dst, const Tensor& indices, const Tensor& grad)
     {
@@ -193,30 +198,35 @@ public:
     Result<Tensor> rearrange_3d(const Tensor& x, std::size_t M, std::size_t B, std::size_t N, bool inverse = false)
     {
         nnb_tensor* t = nullptr;
-        return made(nnb_t_rearrange_3d(x.raw(), M, B, N, inverse ? 1 : 0, &t), t, "rearrange_3d");
+        const nnb_status st = nnb_t_rearrange_3d(x.raw(), M, B, N, inverse ? 1 : 0, &t);
+        return made(st, t, "rearrange_3d");
     }
     Result<void> scale_inplace(Tensor& t, float s) { return done(nnb_t_scale_inplace(t.raw(), s), "scale_inplace"); }
     Result<void> accumulate(Tensor& dst, const Tensor& src) { return done(nnb_t_accumulate(dst.raw(), src.raw()), "accumulate"); }
     Result<Tensor> col_reduce_max(const Tensor& t)
     {
         nnb_tensor* o = nullptr;
-        return made(nnb_t_col_reduce_max(t.raw(), &o), o, "col_reduce_max");
+        const nnb_status st = nnb_t_col_reduce_max(t.raw(), &o);
+        return made(st, o, "col_reduce_max");
     }
     Result<Tensor> row_reduce_sum(const Tensor& t)
     {
         nnb_tensor* o = nullptr;
-        return made(nnb_t_row_reduce_sum(t.raw(), &o), o, "row_reduce_sum");
+        const nnb_status st = nnb_t_row_reduce_sum(t.raw(), &o);
+        return made(st, o, "row_reduce_sum");
     }
     // ---- ternary primitives (compute_layer_bitlinear.hpp:443-464,494,516,637-650)
     Result<Tensor> absmean_tau(const Tensor& latent)
     {
         nnb_tensor* o = nullptr;
-        return made(nnb_t_absmean_tau(latent.raw(), &o), o, "absmean_tau");
+        const nnb_status st = nnb_t_absmean_tau(latent.raw(), &o);
+        return made(st, o, "absmean_tau");
     }
     Result<Tensor> trit_pack(const Tensor& latent, const Tensor& tau)
     {
         nnb_tensor* o = nullptr;
-        return made(nnb_t_trit_pack(latent.raw(), tau.raw(), &o), o, "trit_pack");
+        const nnb_status st = nnb_t_trit_pack(latent.raw(), tau.raw(), &o);
+        return made(st, o, "trit_pack");
     }
     Result<void> trit_pack_into(const Tensor& latent, const Tensor& tau, Tensor& dst)
     {
@@ -225,33 +235,39 @@ public:
     Result<Tensor> matmul_q(const Tensor& packed, const Tensor& tau, const Tensor& x)
     {
         nnb_tensor* o = nullptr;
-        return made(nnb_t_matmul_q(packed.raw(), tau.raw(), x.raw(), &o), o, "matmul_q");
+        const nnb_status st = nnb_t_matmul_q(packed.raw(), tau.raw(), x.raw(), &o);
+        return made(st, o, "matmul_q");
     }
     Result<Tensor> matmul_q_t(const Tensor& packed, const Tensor& tau, const Tensor& dy, std::size_t m_cols)
     {
         nnb_tensor* o = nullptr;
-        return made(nnb_t_matmul_q_t(packed.raw(), tau.raw(), dy.raw(), m_cols, &o), o, "matmul_q_t");
+        const nnb_status st = nnb_t_matmul_q_t(packed.raw(), tau.raw(), dy.raw(), m_cols, &o);
+        return made(st, o, "matmul_q_t");
     }
     Result<Tensor> quantize_i8(const Tensor& x, const Tensor& scale, bool col_scale)
     {
         nnb_tensor* o = nullptr;
-        return made(nnb_t_quantize_i8(x.raw(), scale.raw(), col_scale ? 1 : 0, &o), o, "quantize_i8");
+        const nnb_status st = nnb_t_quantize_i8(x.raw(), scale.raw(), col_scale ? 1 : 0, &o);
+        return made(st, o, "quantize_i8");
     }
     Result<Tensor> unpack_i8(const Tensor& packed, std::size_t cols)
     {
         nnb_tensor* o = nullptr;
-        return made(nnb_t_unpack_i8(packed.raw(), cols, &o), o, "unpack_i8");
+        const nnb_status st = nnb_t_unpack_i8(packed.raw(), cols, &o);
+        return made(st, o, "unpack_i8");
     }
     Result<Tensor> matmul_q_i8(const Tensor& packed, const Tensor& tau, const Tensor& xq, const Tensor& s)
     {
         nnb_tensor* o = nullptr;
-        return made(nnb_t_matmul_q_i8(packed.raw(), tau.raw(), xq.raw(), s.raw(), &o), o, "matmul_q_i8");
+        const nnb_status st = nnb_t_matmul_q_i8(packed.raw(), tau.raw(), xq.raw(), s.raw(), &o);
+        return made(st, o, "matmul_q_i8");
     }
     // ---- the three DSL compositions of BitLinear as verbs
     Result<Tensor> abs(const Tensor& x)
     {
         nnb_tensor* o = nullptr;
-        return made(nnb_t_abs(x.raw(), &o), o, "abs");
+        const nnb_status st = nnb_t_abs(x.raw(), &o);
+        return made(st, o, "abs");
     }
     Result<void> add_row_broadcast(Tensor& y, const Tensor& b) { return done(nnb_t_add_row_broadcast(y.raw(), b.raw()), "add_row_broadcast"); }
     Result<void> bitlinear_dw_accumulate(Tensor& grad_w, const Tensor& dy, const Tensor* s, const Tensor& x, const Tensor& tau)

@@ -342,7 +342,7 @@ static nnb_status decode_step(nnb_policy* p, const StepView& sv, bool with_head,
         NNB_TRY(policy_linear_fwd(p, L.fc2, 1, w.q8, w.s, w.qsum, B, w.x, w.x, 0));
     }
     if (with_head) {
-        const size_t total = w.pre_len + w.ctx_alloc;
+        const size_t total = w.tok_cols;  // row pitch of the token / log-prob buffers
         NNB_TRY(launch_row_quant(e, 0, exact, w.x, P + p->lnf_g, B, d, d, w.q8, w.s, w.qsum, nullptr));
         NNB_TRY(policy_linear_fwd(p, p->head, 1, w.q8, w.s, w.qsum, B, nullptr, w.logits, 0));
         NNB_TRY(launch_sample_opts(e, exact, w.logits, B, V, so, seed, seq0, w.d_pos, prompt_len, w.tokens, total,

@@ -380,9 +380,9 @@ def test_fast_mode_backward_with_a_feed_forward_narrower_than_three_model_widths
         pol.zero_grad()
         pol.train_step(tokens, P, mask, old_logp=old, advantage=adv)
     eng.check_device_errors()
-    ge, gf = pe.grads_view().cpu().numpy(), pf.grads_view().cpu().numpy()
-    for name, off, shape in cfg_e.param_layout()[0]:
-        size = int(np.prod(shape))
-        a, b = ge[off:off + size].astype(np.float64), gf[off:off + size].astype(np.float64)
-        rms = np.sqrt(((a - b) ** 2).mean()) / max(np.sqrt((a ** 2).mean()), 1e-12)
-        assert rms <= 0.2, f"{name}: rms relative difference {rms:.3f}"
+    from neuralnet_cpp_b200.parity import compare_gradients
+
+    # (the key bias has an analytically zero gradient with learned positions: deviations are measured against the model's
+    # gradient scale, as compare_gradients does)
+    dev_stats = compare_gradients(cfg_e, pf.grads_view().cpu().numpy(), pe.grads_view().cpu().numpy())
+    assert dev_stats["grad_rel_rms"] <= 0.2, dev_stats

@@ -33,7 +33,10 @@ def _spans(sizes):
     return spans
 
 
-def test_noalloc_matches_allocating_entry_point_and_oracle_twice(pkg, eng, orc):
+def test_noalloc_matches_allocating_entry_point_and_oracle_twice(pkg, eng):
+    from oracle_binding import OracleRL
+
+    orc = OracleRL()
     rng = np.random.default_rng(0)
     for sizes in ([16] * 64, [3, 70, 1, 5, 8] * 7):  # two calls in a row, different shapes and data
         spans = _spans(sizes)
