@@ -6,6 +6,7 @@
 #include <stdio.h>
 
 #include <string>
+#include <vector>
 
 #include "nn_b200.h"
 
@@ -284,10 +285,27 @@ nnb_status tc_check_errors(nnb_engine* e);
 nnb_status tc_set_forward_tile(int bn);
 nnb_status launch_expand_weights(nnb_engine* e, const uint32_t* wq, size_t rows, size_t k, int8_t* w8, __nv_bfloat16* wb);
 nnb_status launch_scale_to_bf16(nnb_engine* e, const float* dy, const float* tau, size_t t, size_t out, __nv_bfloat16* dyb);
+// Where the per-token-chunk column sums of several launches wait to be added to their bias gradients by ONE
+// finishing launch (launch_colsum_finish_all) instead of one small launch each.  buf / d_descs are device memory owned
+// by the caller; the partial sums stay valid until the finishing launch.
+struct ColsumDesc {
+    const float* part;
+    float* db;
+    int n_chunks, out;
+};
+struct ColsumSink {
+    float* buf = nullptr;
+    size_t cap = 0, used = 0;  // floats
+    ColsumDesc* d_descs = nullptr;
+    size_t desc_cap = 0;
+    std::vector<ColsumDesc> descs;
+};
+nnb_status launch_colsum_finish_all(nnb_engine* e, ColsumSink* sink);
+// sink == NULL: the bias gradient is finished by the call itself
 nnb_status launch_scale_colsum(nnb_engine* e, const float* dy, const float* tau, size_t t, size_t out, __nv_bfloat16* dyb,
-                               float* db, size_t dyb_ld = 0);
+                               float* db, size_t dyb_ld = 0, ColsumSink* sink = nullptr);
 nnb_status launch_act_bwd_scale_colsum(nnb_engine* e, int mode, const float* h, const float* da, const float* tau, size_t t,
-                                       size_t F, __nv_bfloat16* dyb, float* db);
+                                       size_t F, __nv_bfloat16* dyb, float* db, ColsumSink* sink = nullptr);
 nnb_status launch_dequant_to_bf16(nnb_engine* e, const int8_t* q, const float* s, size_t t, size_t k, __nv_bfloat16* xs);
 
 // ---- attn_b16.cu (bf16 tensor-core attention of the teacher-forced pass, head dims 64 and 128)

@@ -684,24 +684,52 @@ lmhead_merge_kernel(const float* __restrict__ pm, const float* __restrict__ ps, 
                     const float* __restrict__ act_logit, int n_part, int M, float* __restrict__ lse, float* __restrict__ logp,
                     float* __restrict__ ent)
 {
-    const int row = blockIdx.x * 256 + threadIdx.x;
-    if (row >= M) return;
-    float m = -INFINITY;
-    for (int p = 0; p < n_part; ++p) m = fmaxf(m, pm[(size_t)p * M + row]);
-    float s = 0.0f, u = 0.0f;
-    for (int p = 0; p < n_part; ++p) {
-        const float sp = ps[(size_t)p * M + row];
-        if (sp > 0.0f) {
-            const float dm = pm[(size_t)p * M + row] - m;
-            const float f = __expf(dm);
+    // 32 rows per CTA (lanes = rows, so that the partial arrays are read along their contiguous axis), 8 warps splitting
+    // the partials; the warps' results are merged in a fixed order
+    __shared__ float sm_m[8][32], sm_s[8][32], sm_u[8][32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int row = blockIdx.x * 32 + lane;
+    float m = -INFINITY, s = 0.0f, u = 0.0f;
+    if (row < M) {
+        for (int p = warp; p < n_part; p += 8) {
+            const float sp = ps[(size_t)p * M + row];
+            if (!(sp > 0.0f)) continue;
+            const float mp = pm[(size_t)p * M + row], up = pu[(size_t)p * M + row];
+            if (mp > m) {
+                if (m > -INFINITY) {
+                    const float f = __expf(m - mp);
+                    u = f * (u + (m - mp) * s);
+                    s *= f;
+                }
+                m = mp;
+            }
+            const float dm = mp - m, f = __expf(dm);
             s += sp * f;
-            u += (pu[(size_t)p * M + row] + dm * sp) * f;
+            u += (up + dm * sp) * f;
         }
     }
-    const float ls = __logf(s);
-    lse[row] = m + ls;
-    if (logp) logp[row] = act_logit[row] - (m + ls);
-    if (ent) ent[row] = ls - u / s;
+    sm_m[warp][lane] = m;
+    sm_s[warp][lane] = s;
+    sm_u[warp][lane] = u;
+    __syncthreads();
+    if (warp != 0 || row >= M) return;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) mm = fmaxf(mm, sm_m[w][lane]);
+    float ss = 0.0f, uu = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+        const float sw = sm_s[w][lane];
+        if (sw > 0.0f) {
+            const float dm = sm_m[w][lane] - mm, f = __expf(dm);
+            ss += sw * f;
+            uu += (sm_u[w][lane] + dm * sw) * f;
+        }
+    }
+    const float ls = __logf(ss);
+    lse[row] = mm + ls;
+    if (logp) logp[row] = act_logit[row] - (mm + ls);
+    if (ent) ent[row] = ls - uu / ss;
 }
 
 size_t tc_lmhead_scratch_floats(size_t t, size_t v)
@@ -734,7 +762,7 @@ nnb_status launch_tc_lmhead_fwd(nnb_engine* e, const int8_t* q, const int8_t* w8
     ep.part_u = scratch + 2 * n_part * t;
     ep.act_logit = scratch + 3 * n_part * t;
     NNB_TRY((launch<0, false, false, 2, BN>(e, ta, tb, ep, t, v, k)));
-    lmhead_merge_kernel<<<(unsigned)ceil_div(t, 256), 256, 0, e->stream>>>(ep.part_m, ep.part_s, ep.part_u, ep.act_logit, (int)n_part, (int)t,
+    lmhead_merge_kernel<<<(unsigned)ceil_div(t, 32), 256, 0, e->stream>>>(ep.part_m, ep.part_s, ep.part_u, ep.act_logit, (int)n_part, (int)t,
                                                                           lse, logp, ent);
     e->launches++;
     NNB_CHECK_LAUNCH("lmhead_merge_kernel");
@@ -911,6 +939,45 @@ scale_colsum_kernel(const float* __restrict__ dy, const float* __restrict__ tau,
     *reinterpret_cast<float2*>(part + (size_t)blockIdx.y * O + o) = make_float2(sa, sb);
 }
 
+// the same with four adjacent columns per thread (16-byte loads, four rows in flight): out, ld multiples of 4
+__global__ void __launch_bounds__(128)
+scale_colsum4_kernel(const float* __restrict__ dy, const float* __restrict__ tau, int T, int O, int chunk,
+                     __nv_bfloat16* __restrict__ out, size_t ld, float* __restrict__ part)
+{
+    const int o = (blockIdx.x * 128 + threadIdx.x) * 4;
+    if (o >= O) return;
+    const int t0 = blockIdx.y * chunk, t1 = min(T, t0 + chunk);
+    const float4 tv = *reinterpret_cast<const float4*>(tau + o);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    int t = t0;
+    for (; t + 4 <= t1; t += 4) {
+        float4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) v[u] = *reinterpret_cast<const float4*>(dy + (size_t)(t + u) * O + o);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w;
+            const __nv_bfloat162 p0 = __floats2bfloat162_rn(v[u].x * tv.x, v[u].y * tv.y);
+            const __nv_bfloat162 p1 = __floats2bfloat162_rn(v[u].z * tv.z, v[u].w * tv.w);
+            uint2 w;
+            w.x = *reinterpret_cast<const uint32_t*>(&p0);
+            w.y = *reinterpret_cast<const uint32_t*>(&p1);
+            *reinterpret_cast<uint2*>(out + (size_t)(t + u) * ld + o) = w;
+        }
+    }
+    for (; t < t1; ++t) {
+        const float4 v = *reinterpret_cast<const float4*>(dy + (size_t)t * O + o);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        const __nv_bfloat162 p0 = __floats2bfloat162_rn(v.x * tv.x, v.y * tv.y);
+        const __nv_bfloat162 p1 = __floats2bfloat162_rn(v.z * tv.z, v.w * tv.w);
+        uint2 w;
+        w.x = *reinterpret_cast<const uint32_t*>(&p0);
+        w.y = *reinterpret_cast<const uint32_t*>(&p1);
+        *reinterpret_cast<uint2*>(out + (size_t)t * ld + o) = w;
+    }
+    *reinterpret_cast<float4*>(part + (size_t)blockIdx.y * O + o) = acc;
+}
+
 // db[o] += part[0][o] + part[1][o] + ... in that order
 __global__ void __launch_bounds__(256)
 colsum_finish_kernel(const float* __restrict__ part, int n_chunks, int O, float* __restrict__ db)
@@ -920,6 +987,49 @@ colsum_finish_kernel(const float* __restrict__ part, int n_chunks, int O, float*
     float acc = 0.0f;
     for (int c = 0; c < n_chunks; ++c) acc += part[(size_t)c * O + o];
     db[o] += acc;
+}
+
+// one launch for the bias gradients of many linears: blockIdx.y selects the descriptor
+__global__ void __launch_bounds__(256)
+colsum_finish_multi_kernel(const ColsumDesc* __restrict__ descs)
+{
+    const ColsumDesc d = descs[blockIdx.y];
+    const int o = blockIdx.x * 256 + threadIdx.x;
+    if (o >= d.out) return;
+    float acc = 0.0f;
+    for (int c = 0; c < d.n_chunks; ++c) acc += d.part[(size_t)c * d.out + o];
+    d.db[o] += acc;
+}
+
+nnb_status launch_colsum_finish_all(nnb_engine* e, ColsumSink* sink)
+{
+    if (!sink || sink->descs.empty()) return NNB_OK;
+    NNB_REQUIRE(sink->descs.size() <= sink->desc_cap, "colsum sink: %zu descriptors, room for %zu", sink->descs.size(), sink->desc_cap);
+    int max_out = 0;
+    for (const ColsumDesc& d : sink->descs) max_out = d.out > max_out ? d.out : max_out;
+    NNB_CUDA(cudaMemcpyAsync(sink->d_descs, sink->descs.data(), sink->descs.size() * sizeof(ColsumDesc), cudaMemcpyHostToDevice, e->stream));
+    dim3 grid((unsigned)ceil_div((size_t)max_out, 256), (unsigned)sink->descs.size());
+    colsum_finish_multi_kernel<<<grid, 256, 0, e->stream>>>(sink->d_descs);
+    e->launches++;
+    NNB_CHECK_LAUNCH("colsum_finish_multi_kernel");
+    sink->descs.clear();
+    sink->used = 0;
+    return NNB_OK;
+}
+
+// where a launch puts its partial sums: the sink's buffer (finished later) or the engine's scratch (finished at once)
+static nnb_status colsum_part(nnb_engine* e, ColsumSink* sink, size_t n_chunks, size_t out, float* db, float** part)
+{
+    const size_t need = n_chunks * out;
+    if (sink && sink->used + need <= sink->cap && sink->descs.size() < sink->desc_cap) {
+        *part = sink->buf + sink->used;
+        sink->used += (need + 3) & ~(size_t)3;
+        sink->descs.push_back(ColsumDesc{*part, db, (int)n_chunks, (int)out});
+        return NNB_OK;
+    }
+    NNB_TRY(e->ensure_scratch(need * sizeof(float)));
+    *part = (float*)e->scratch;
+    return 1;  // caller finishes immediately
 }
 
 // Activation backward fused with the preparation of the next GEMM's operand: with h (T, F1) the
@@ -1027,36 +1137,51 @@ nnb_status launch_scale_to_bf16(nnb_engine* e, const float* dy, const float* tau
 
 // mode 1 QuickGELU, 2 SwiGLU; F even
 nnb_status launch_act_bwd_scale_colsum(nnb_engine* e, int mode, const float* h, const float* da, const float* tau, size_t t,
-                                       size_t F, __nv_bfloat16* dyb, float* db)
+                                       size_t F, __nv_bfloat16* dyb, float* db, ColsumSink* sink)
 {
     NNB_REQUIRE(F % 2 == 0 && (mode == 1 || mode == 2), "act_bwd_scale_colsum: bad arguments");
     const int chunk = 128;
     dim3 grid((unsigned)ceil_div(F, 256), (unsigned)ceil_div(t, chunk));
     NNB_REQUIRE(grid.y <= 65535, "act_bwd_scale_colsum: too many tokens (%zu)", t);
     const size_t F1 = mode == 2 ? 2 * F : F;
-    NNB_TRY(e->ensure_scratch((size_t)grid.y * F1 * sizeof(float)));
-    float* part = (float*)e->scratch;
+    float* part = nullptr;
+    const nnb_status where = colsum_part(e, sink, grid.y, F1, db, &part);
+    if (where < 0) return where;
     if (mode == 2) act_bwd_scale_colsum_kernel<2><<<grid, 128, 0, e->stream>>>(h, da, tau, (int)t, (int)F, chunk, dyb, part);
     else act_bwd_scale_colsum_kernel<1><<<grid, 128, 0, e->stream>>>(h, da, tau, (int)t, (int)F, chunk, dyb, part);
-    colsum_finish_kernel<<<(unsigned)ceil_div(F1, 256), 256, 0, e->stream>>>(part, (int)grid.y, (int)F1, db);
-    e->launches += 2;
+    e->launches++;
+    if (where == 1) {
+        colsum_finish_kernel<<<(unsigned)ceil_div(F1, 256), 256, 0, e->stream>>>(part, (int)grid.y, (int)F1, db);
+        e->launches++;
+    }
     NNB_CHECK_LAUNCH("act_bwd_scale_colsum_kernel");
     return NNB_OK;
 }
 
 // dyb_ld: row pitch of dyb in elements (0 = out), so that several matrices' gradients can sit side by side
 nnb_status launch_scale_colsum(nnb_engine* e, const float* dy, const float* tau, size_t t, size_t out, __nv_bfloat16* dyb,
-                               float* db, size_t dyb_ld)
+                               float* db, size_t dyb_ld, ColsumSink* sink)
 {
     NNB_REQUIRE(out % 2 == 0 && dyb_ld % 2 == 0, "scale_colsum: out=%zu must be even", out);
     const int chunk = 128;
     dim3 grid((unsigned)ceil_div(out, 256), (unsigned)ceil_div(t, chunk));
     NNB_REQUIRE(grid.y <= 65535, "scale_colsum: too many tokens (%zu)", t);
-    NNB_TRY(e->ensure_scratch((size_t)grid.y * out * sizeof(float)));
-    float* part = (float*)e->scratch;
-    scale_colsum_kernel<<<grid, 128, 0, e->stream>>>(dy, tau, (int)t, (int)out, chunk, dyb, dyb_ld ? dyb_ld : out, part);
-    colsum_finish_kernel<<<(unsigned)ceil_div(out, 256), 256, 0, e->stream>>>(part, (int)grid.y, (int)out, db);
-    e->launches += 2;
+    float* part = nullptr;
+    const nnb_status where = colsum_part(e, sink, grid.y, out, db, &part);
+    if (where < 0) return where;
+    const size_t ld = dyb_ld ? dyb_ld : out;
+    const bool vec4 = out % 4 == 0 && ld % 4 == 0 && (((uintptr_t)dy | (uintptr_t)tau | (uintptr_t)part) & 15) == 0 && ((uintptr_t)dyb & 7) == 0;
+    if (vec4) {
+        dim3 grid4((unsigned)ceil_div(out, 512), grid.y);
+        scale_colsum4_kernel<<<grid4, 128, 0, e->stream>>>(dy, tau, (int)t, (int)out, chunk, dyb, ld, part);
+    } else {
+        scale_colsum_kernel<<<grid, 128, 0, e->stream>>>(dy, tau, (int)t, (int)out, chunk, dyb, ld, part);
+    }
+    e->launches++;
+    if (where == 1) {
+        colsum_finish_kernel<<<(unsigned)ceil_div(out, 256), 256, 0, e->stream>>>(part, (int)grid.y, (int)out, db);
+        e->launches++;
+    }
     NNB_CHECK_LAUNCH("scale_colsum_kernel");
     return NNB_OK;
 }

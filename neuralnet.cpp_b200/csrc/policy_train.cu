@@ -54,6 +54,7 @@ struct TrainWs {
     // from the same integer GEMM, so the (decisions x vocabulary) f32 logits do not exist
     bool fused_head = false;
     float *lse = nullptr, *head_scratch = nullptr;
+    ColsumSink bias_sink;  // bias-gradient partial sums of a whole backward pass, finished by one launch
 };
 
 static void free_ws(void*& slot)
@@ -177,6 +178,12 @@ static nnb_status ensure_train(nnb_policy* p, size_t n_seq, size_t S, size_t P, 
                 w->xs = (__nv_bfloat16*)take(T * (F > d ? F : d) * 2);
                 if (w->b16_attn) w->dob = (__nv_bfloat16*)take(T * d * 2);
                 if (group > 1) w->part = (float*)take(2 * n_seq * P * d * 4);
+                // per linear: ceil(T / 128) chunks x out partial sums (q|k|v, o, fc1, fc2 of every layer)
+                const size_t chunks = (T + 127) / 128;
+                w->bias_sink.cap = chunks * (size_t)c.n_layer * (3 * d + d + F1 + d) + 64;
+                w->bias_sink.buf = (float*)take(w->bias_sink.cap * 4);
+                w->bias_sink.desc_cap = (size_t)c.n_layer * 6 + 8;
+                w->bias_sink.d_descs = (ColsumDesc*)take(w->bias_sink.desc_cap * sizeof(ColsumDesc));
             }
         }
         if (pass == 0) {
@@ -294,6 +301,9 @@ static bool tc_bwd_ok(const nnb_policy* p, size_t out, size_t T)
     return !p->cfg.exact && p->wb && p->wb_valid && out % 8 == 0 && T >= 64;
 }
 
+// the layers' linears (T rows) park their bias-gradient partial sums in the workspace; the head (Td rows) finishes its own
+static ColsumSink* sink_of(TrainWs* w, size_t rows) { return (w->bias_sink.buf && rows == w->rows) ? &w->bias_sink : nullptr; }
+
 // the two GEMMs of a linear's backward on operands already prepared in the workspace: w->dyb (T, out) =
 // bf16(dy*tau).  `out` may span several matrices stored one after the other (their weights, and so their
 // weight gradients, are contiguous): one dX over the concatenated contraction, one dW for all rows.
@@ -315,7 +325,7 @@ static nnb_status lin_bwd(nnb_policy* p, const LinW& l, const float* dy, const i
     TrainWs* w = (TrainWs*)p->train;
     if (tc_bwd_ok(p, l.out, T)) {
         // tcgen05 path: dyb = bf16(dy*tau) serves both GEMMs, xs = bf16(s*q) in natural feature order
-        NNB_TRY(launch_scale_colsum(e, dy, p->tau + l.tau_off, T, l.out, w->dyb, p->grads + l.b_off));
+        NNB_TRY(launch_scale_colsum(e, dy, p->tau + l.tau_off, T, l.out, w->dyb, p->grads + l.b_off, 0, sink_of(w, T)));
         return lin_bwd_gemms(p, l, l.out, q, s, T, dx, accumulate_dx);
     }
     if (dx) NNB_TRY(launch_bitlinear_dx(e, exact, dy, p->packed + l.packed_off, p->tau + l.tau_off, T, l.in, l.out, dx, accumulate_dx));
@@ -333,6 +343,8 @@ static nnb_status backward(nnb_policy* p, const int32_t* tokens, size_t n_seq, s
     const bool grouped = w->map.group > 1;
     const float* PP = p->params;
     float* GG = p->grads;
+    w->bias_sink.descs.clear();
+    w->bias_sink.used = 0;
     if (w->fused_head) {
         // w->dyb already holds bf16(dlogits * tau) and the bias gradient is done (launch_tc_lmhead_bwd)
         NNB_REQUIRE(tc_bwd_ok(p, V, Td), "fused LM head: the tensor-core backward is not available");
@@ -354,7 +366,7 @@ static nnb_status backward(nnb_policy* p, const int32_t* tokens, size_t n_seq, s
         if (tc_bwd_ok(p, LW.fc1.out, T) && F % 2 == 0) {
             // the activation's backward writes the GEMM operand directly (no f32 round trip of dh1)
             NNB_TRY(launch_act_bwd_scale_colsum(e, c.act == 1 ? 2 : 1, s.h1, w->da, p->tau + LW.fc1.tau_off, T, F, w->dyb,
-                                                GG + LW.fc1.b_off));
+                                                GG + LW.fc1.b_off, sink_of(w, T)));
             NNB_TRY(lin_bwd_gemms(p, LW.fc1, LW.fc1.out, s.q3, s.s3, T, w->dn, false));
         } else {
             NNB_TRY(launch_act_bwd(e, c.act == 1 ? 2 : 1, s.h1, w->da, T, F, w->dh1));
@@ -381,7 +393,7 @@ static nnb_status backward(nnb_policy* p, const int32_t* tokens, size_t n_seq, s
             // backward is one dX GEMM over the concatenated contraction and one dW GEMM for all three
             for (int m = 0; m < 3; ++m)
                 NNB_TRY(launch_scale_colsum(e, w->dqkv + m * T * d, p->tau + LW.q.tau_off + m * d, T, d, w->dyb + m * d,
-                                            GG + LW.q.b_off + m * d, 3 * d));
+                                            GG + LW.q.b_off + m * d, 3 * d, sink_of(w, T)));
             NNB_TRY(lin_bwd_gemms(p, LW.q, 3 * d, s.q1, s.s1, T, w->dn, false));
         } else {
             NNB_TRY(lin_bwd(p, LW.q, w->dqkv, s.q1, s.s1, T, w->dn, false));
@@ -390,6 +402,7 @@ static nnb_status backward(nnb_policy* p, const int32_t* tokens, size_t n_seq, s
         }
         NNB_TRY(launch_rmsnorm_bwd(e, s.x_in, PP + LW.ln1_g, w->dn, w->g2, T, d, w->g, GG + LW.ln1_g));
     }
+    NNB_TRY(launch_colsum_finish_all(e, &w->bias_sink));
     return launch_embed_rows_bwd(e, w->g, w->row_tok, w->row_pos, T, d, V, GG + p->tok_emb, c.pos == 0 ? GG + p->pos_emb : nullptr);
 }
 
