@@ -291,7 +291,8 @@ nnb_status nnb_bitlinear_fwd_host(nnb_engine* e, const uint32_t* d_wq, const flo
  * untied BitLinear head; every linear is a BitLinear with bias and int8 activations. */
 typedef struct nnb_gpt_config {
     int32_t n_layer, d_model, n_head, d_ff, vocab, ctx;
-    int32_t act;        /* 0 = QuickGELU (GeLU layer of the reference), 1 = SwiGLU */
+    int32_t act;        /* 0 = QuickGELU (GeLU layer of the reference), 1 = SwiGLU, 2 = ReLU2GLU: relu(gate)^2 * up
+                           (include/neuralnet.cpp/compute_layer_mlp.hpp:384-440, the BitNet 2B4T feed-forward) */
     int32_t pos;        /* 0 = learned additive positions, 1 = RoPE */
     int32_t value_head; /* 1 adds a Linear(d_model -> 1) port on the final-norm output */
     int32_t exact;      /* 1: f32 activations and KV cache, f64-accumulated reductions (the mode

@@ -8,7 +8,7 @@ first use.  There is no CPU fallback: without the library, or without a B200, ca
 """
 from ._lib import lib, lib_path, NnbError  # noqa: F401
 from .engine import Engine  # noqa: F401
-from .policy import GptConfig, Policy, SamplingConfig, GELU, SWIGLU, LEARNED, ROPE  # noqa: F401
+from .policy import GptConfig, Policy, SamplingConfig, GELU, SWIGLU, RELU2, LEARNED, ROPE  # noqa: F401
 from .grpo import GrpoConfig, GrpoTrainer, hash_reward, report_dict, REPORT_FIELDS  # noqa: F401
 from .ppo import PpoConfig, PpoTrainer  # noqa: F401
 from .pipeline import (CollectingMetricSink, DeterministicRng, ExperienceBuffer, GptRolloutSource, PipelineError,  # noqa: F401

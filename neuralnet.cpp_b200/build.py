@@ -72,11 +72,13 @@ def build(force: bool = False, verbose: bool = False) -> str:
                 if rc != 0:
                     raise RuntimeError(f"nvcc failed on {name}")
     if jobs or force or not _newer(LIB, objs):
-        cmd = [nvcc, "-shared", "-o", LIB, *objs, "-lcudart"]
+        tmp = LIB + ".tmp"  # link beside the target and rename: a reader never sees a half-written library
+        cmd = [nvcc, "-shared", "-o", tmp, *objs, "-lcudart"]
         p = subprocess.run(cmd, capture_output=True, text=True)
         if p.returncode != 0:
             sys.stderr.write(p.stdout + p.stderr)
             raise RuntimeError("link of libnn-b200.so failed")
+        os.replace(tmp, LIB)
     return LIB
 
 

@@ -43,7 +43,7 @@ __global__ void embed_kernel(const float* __restrict__ tok_emb, const float* __r
 
 // -------------------------------------------- row transform + quantisation
 // One CTA per token.  MODE 0: RMSNorm(x)*gamma.  MODE 1: QuickGELU(h).  MODE 2: SwiGLU(h) with
-// h = (gate | up).  MODE 3: identity.  The transformed row is quantised to the engine's int8
+// h = (gate | up).  MODE 3: identity.  MODE 4: ReLU2GLU(h) = relu(gate)^2 * up (include/neuralnet.cpp/compute_layer_mlp.hpp:384-440).  The transformed row is quantised to the engine's int8
 // layout (see ternary.cu) and optionally also written as f32 (`f_out`).
 template <int MODE, bool EXACT>
 __global__ void __launch_bounds__(256)
@@ -105,6 +105,9 @@ row_quant_kernel(const float* __restrict__ in, const float* __restrict__ gamma, 
             const float gv = xr[i], uv = xr[k + i];
             const float sig = __fdiv_rn(1.0f, __fadd_rn(1.0f, nnb_expf(-gv)));
             v = __fmul_rn(__fmul_rn(gv, sig), uv);
+        } else if (MODE == 4) {
+            const float rv = fmaxf(xr[i], 0.0f), uv = xr[k + i];
+            v = __fmul_rn(__fmul_rn(rv, rv), uv);
         } else {
             v = xr[i];
         }
@@ -198,6 +201,11 @@ row_quant_fast_kernel(const float* __restrict__ in, const float* __restrict__ ga
             const float4 g = x4[c], u = x4[nv + c];
             v = make_float4(__fdividef(g.x, 1.0f + __expf(-g.x)) * u.x, __fdividef(g.y, 1.0f + __expf(-g.y)) * u.y,
                             __fdividef(g.z, 1.0f + __expf(-g.z)) * u.z, __fdividef(g.w, 1.0f + __expf(-g.w)) * u.w);
+        } else if (MODE == 4) {
+            const float4 g = x4[c], u = x4[nv + c];
+            const float4 r = make_float4(fmaxf(g.x, 0.f), fmaxf(g.y, 0.f), fmaxf(g.z, 0.f), fmaxf(g.w, 0.f));
+            v = make_float4(__fmul_rn(__fmul_rn(r.x, r.x), u.x), __fmul_rn(__fmul_rn(r.y, r.y), u.y),
+                            __fmul_rn(__fmul_rn(r.z, r.z), u.z), __fmul_rn(__fmul_rn(r.w, r.w), u.w));
         } else {
             v = x4[c];
         }
@@ -283,6 +291,7 @@ nnb_status launch_row_quant(nnb_engine* e, int mode, bool exact, const float* in
         case 1: return launch_row_quant_mode<1>(e, exact, in, gamma, t, k, in_stride, q, s, qsum, f_out);
         case 2: return launch_row_quant_mode<2>(e, exact, in, gamma, t, k, in_stride, q, s, qsum, f_out);
         case 3: return launch_row_quant_mode<3>(e, exact, in, gamma, t, k, in_stride, q, s, qsum, f_out);
+        case 4: return launch_row_quant_mode<4>(e, exact, in, gamma, t, k, in_stride, q, s, qsum, f_out);
     }
     NNB_FAIL(NNB_ERR_INVALID, "row_quant: unknown mode %d", mode);
 }

@@ -1043,10 +1043,10 @@ act_bwd_scale_colsum_kernel(const float* __restrict__ h, const float* __restrict
 {
     const int f = (blockIdx.x * 128 + threadIdx.x) * 2;
     if (f >= F) return;
-    const int F1 = MODE == 2 ? 2 * F : F;
+    const int F1 = MODE >= 2 ? 2 * F : F;
     const int t0 = blockIdx.y * chunk, t1 = min(T, t0 + chunk);
     const float2 tg = *reinterpret_cast<const float2*>(tau + f);
-    const float2 tu = MODE == 2 ? *reinterpret_cast<const float2*>(tau + F + f) : make_float2(0.f, 0.f);
+    const float2 tu = MODE >= 2 ? *reinterpret_cast<const float2*>(tau + F + f) : make_float2(0.f, 0.f);
     float sg0 = 0.f, sg1 = 0.f, su0 = 0.f, su1 = 0.f;
     for (int t = t0; t < t1; t += 2) {
         float2 gv[2], uv[2], go[2];
@@ -1054,14 +1054,20 @@ act_bwd_scale_colsum_kernel(const float* __restrict__ h, const float* __restrict
         for (int u = 0; u < 2; ++u) {
             const int tt = min(t + u, t1 - 1);
             gv[u] = *reinterpret_cast<const float2*>(h + (size_t)tt * F1 + f);
-            uv[u] = MODE == 2 ? *reinterpret_cast<const float2*>(h + (size_t)tt * F1 + F + f) : make_float2(0.f, 0.f);
+            uv[u] = MODE >= 2 ? *reinterpret_cast<const float2*>(h + (size_t)tt * F1 + F + f) : make_float2(0.f, 0.f);
             go[u] = *reinterpret_cast<const float2*>(da + (size_t)tt * F + f);
         }
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
             if (t + u >= t1) break;
             float dgx, dgy, dux = 0.f, duy = 0.f;
-            if (MODE == 2) {
+            if (MODE == 3) {
+                const float r0 = fmaxf(gv[u].x, 0.0f), r1 = fmaxf(gv[u].y, 0.0f);
+                dgx = go[u].x * uv[u].x * (2.0f * r0);
+                dgy = go[u].y * uv[u].y * (2.0f * r1);
+                dux = go[u].x * (r0 * r0);
+                duy = go[u].y * (r1 * r1);
+            } else if (MODE == 2) {
                 const float s0 = __fdividef(1.0f, 1.0f + __expf(-gv[u].x)), s1 = __fdividef(1.0f, 1.0f + __expf(-gv[u].y));
                 dgx = go[u].x * uv[u].x * (s0 * (1.0f + gv[u].x * (1.0f - s0)));
                 dgy = go[u].y * uv[u].y * (s1 * (1.0f + gv[u].y * (1.0f - s1)));
@@ -1075,7 +1081,7 @@ act_bwd_scale_colsum_kernel(const float* __restrict__ h, const float* __restrict
             }
             sg0 += dgx; sg1 += dgy;
             *reinterpret_cast<__nv_bfloat162*>(out + (size_t)(t + u) * F1 + f) = __floats2bfloat162_rn(dgx * tg.x, dgy * tg.y);
-            if (MODE == 2) {
+            if (MODE >= 2) {
                 su0 += dux; su1 += duy;
                 *reinterpret_cast<__nv_bfloat162*>(out + (size_t)(t + u) * F1 + F + f) = __floats2bfloat162_rn(dux * tu.x, duy * tu.y);
             }
@@ -1083,7 +1089,7 @@ act_bwd_scale_colsum_kernel(const float* __restrict__ h, const float* __restrict
     }
     float* prow = part + (size_t)blockIdx.y * F1;
     *reinterpret_cast<float2*>(prow + f) = make_float2(sg0, sg1);
-    if (MODE == 2) *reinterpret_cast<float2*>(prow + F + f) = make_float2(su0, su1);
+    if (MODE >= 2) *reinterpret_cast<float2*>(prow + F + f) = make_float2(su0, su1);
 }
 
 // xs[t,k] = bf16(s[t] * q[t, perm(k)]) in natural feature order.  One thread per 64-feature block: it reads
@@ -1135,19 +1141,20 @@ nnb_status launch_scale_to_bf16(nnb_engine* e, const float* dy, const float* tau
     return NNB_OK;
 }
 
-// mode 1 QuickGELU, 2 SwiGLU; F even
+// mode 1 QuickGELU, 2 SwiGLU, 3 ReLU2GLU; F even
 nnb_status launch_act_bwd_scale_colsum(nnb_engine* e, int mode, const float* h, const float* da, const float* tau, size_t t,
                                        size_t F, __nv_bfloat16* dyb, float* db, ColsumSink* sink)
 {
-    NNB_REQUIRE(F % 2 == 0 && (mode == 1 || mode == 2), "act_bwd_scale_colsum: bad arguments");
+    NNB_REQUIRE(F % 2 == 0 && mode >= 1 && mode <= 3, "act_bwd_scale_colsum: bad arguments");
     const int chunk = 128;
     dim3 grid((unsigned)ceil_div(F, 256), (unsigned)ceil_div(t, chunk));
     NNB_REQUIRE(grid.y <= 65535, "act_bwd_scale_colsum: too many tokens (%zu)", t);
-    const size_t F1 = mode == 2 ? 2 * F : F;
+    const size_t F1 = mode >= 2 ? 2 * F : F;
     float* part = nullptr;
     const nnb_status where = colsum_part(e, sink, grid.y, F1, db, &part);
     if (where < 0) return where;
     if (mode == 2) act_bwd_scale_colsum_kernel<2><<<grid, 128, 0, e->stream>>>(h, da, tau, (int)t, (int)F, chunk, dyb, part);
+    else if (mode == 3) act_bwd_scale_colsum_kernel<3><<<grid, 128, 0, e->stream>>>(h, da, tau, (int)t, (int)F, chunk, dyb, part);
     else act_bwd_scale_colsum_kernel<1><<<grid, 128, 0, e->stream>>>(h, da, tau, (int)t, (int)F, chunk, dyb, part);
     e->launches++;
     if (where == 1) {

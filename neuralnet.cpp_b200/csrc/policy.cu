@@ -28,7 +28,7 @@ static void build_layout(nnb_policy* p)
 {
     const nnb_gpt_config& c = p->cfg;
     const size_t d = c.d_model, F = c.d_ff, V = c.vocab;
-    const size_t F1 = c.act == 1 ? 2 * F : F;
+    const size_t F1 = act_gated(c.act) ? 2 * F : F;
     size_t o = 0, po = 0, to = 0;
     auto lin = [&](LinW& l, const std::string& nm, size_t w_off, size_t b_off, size_t in, size_t out) {
         l.w_off = w_off;
@@ -206,7 +206,7 @@ static nnb_status ensure_decode(nnb_policy* p, size_t B, size_t ctx_alloc, size_
     NNB_CUDA(cudaStreamSynchronize(p->e->stream));
     free_decode(p);
     const nnb_gpt_config& c = p->cfg;
-    const size_t d = c.d_model, F = c.d_ff, V = c.vocab, F1 = c.act == 1 ? 2 * F : F;
+    const size_t d = c.d_model, F = c.d_ff, V = c.vocab, F1 = act_gated(c.act) ? 2 * F : F;
     const size_t kv_elem = c.exact ? 4 : 2;
     const size_t dkv = c.n_head * attn_decode_kv_pitch(c.exact != 0, d / c.n_head);  // cached features per position
     const size_t kv_bytes = (size_t)c.n_layer * B * dkv * ctx_alloc * kv_elem;
@@ -289,7 +289,7 @@ static nnb_status decode_step(nnb_policy* p, const StepView& sv, bool with_head,
     const nnb_gpt_config& c = p->cfg;
     DecodeWs& w = p->dec;
     const size_t B = sv.B, d = c.d_model, F = c.d_ff, V = c.vocab, H = c.n_head, dk = d / H;
-    const size_t F1 = c.act == 1 ? 2 * F : F;
+    const size_t F1 = act_gated(c.act) ? 2 * F : F;
     const bool exact = c.exact != 0;
     const float* P = p->params;
     // The fast mode's step is ~200 short kernels, each of which waits for the one before it (pdl_wait) before
@@ -338,7 +338,7 @@ static nnb_status decode_step(nnb_policy* p, const StepView& sv, bool with_head,
         }
         NNB_TRY(launch_row_quant(e, 0, exact, w.x, P + L.ln2_g, B, d, d, w.q8, w.s, w.qsum, nullptr));
         NNB_TRY(policy_linear_fwd(p, L.fc1, 1, w.q8, w.s, w.qsum, B, nullptr, w.h1, 0));
-        NNB_TRY(launch_row_quant(e, c.act == 1 ? 2 : 1, exact, w.h1, nullptr, B, F, F1, w.q8, w.s, w.qsum, nullptr));
+        NNB_TRY(launch_row_quant(e, act_quant_mode(c.act), exact, w.h1, nullptr, B, F, F1, w.q8, w.s, w.qsum, nullptr));
         NNB_TRY(policy_linear_fwd(p, L.fc2, 1, w.q8, w.s, w.qsum, B, w.x, w.x, 0));
     }
     if (with_head) {
@@ -562,7 +562,7 @@ nnb_status nnb_policy_create(nnb_engine* e, const nnb_gpt_config* cfg, nnb_polic
                 "policy_create: d_model and d_ff must be multiples of 64 (got %d, %d)", c.d_model, c.d_ff);
     const int dk = c.d_model / c.n_head;
     NNB_REQUIRE(dk % 4 == 0 && dk <= 128, "policy_create: head dim %d unsupported (multiple of 4, <= 128)", dk);
-    NNB_REQUIRE(c.act == 0 || c.act == 1, "policy_create: act must be 0 (QuickGELU) or 1 (SwiGLU)");
+    NNB_REQUIRE(c.act >= 0 && c.act <= 2, "policy_create: act must be 0 (QuickGELU), 1 (SwiGLU) or 2 (ReLU2GLU)");
     NNB_REQUIRE(c.pos == 0 || c.pos == 1, "policy_create: pos must be 0 (learned) or 1 (RoPE)");
     NNB_REQUIRE(c.pos == 0 || dk % 2 == 0, "policy_create: RoPE needs an even head dim");
     nnb_policy* p = new nnb_policy();

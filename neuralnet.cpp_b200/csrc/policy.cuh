@@ -73,6 +73,10 @@ struct nnb_policy {
 };
 
 namespace nnb {
+// nnb_gpt_config.act: 0 QuickGELU, 1 SwiGLU, 2 ReLU2GLU.  The gated ones take fc1 rows (gate | up), 2 * d_ff wide.
+inline bool act_gated(int act) { return act >= 1; }
+inline int act_quant_mode(int act) { return act == 0 ? 1 : (act == 1 ? 2 : 4); }  // mode of launch_row_quant
+inline int act_bwd_mode(int act) { return act == 0 ? 1 : (act == 1 ? 2 : 3); }    // mode of launch_act_bwd[_scale_colsum]
 nnb_status policy_requantize(nnb_policy* p, bool seeded = false);
 void policy_free_train(nnb_policy* p);
 // Fast mode: run the teacher-forced forward over n_seq prompts of L tokens and store every layer's rotated keys

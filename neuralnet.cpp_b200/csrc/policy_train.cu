@@ -92,7 +92,7 @@ static nnb_status ensure_train(nnb_policy* p, size_t n_seq, size_t S, size_t P, 
     w = new TrainWs();
     p->train = w;
     const nnb_gpt_config& c = p->cfg;
-    const size_t d = c.d_model, F = c.d_ff, F1 = c.act == 1 ? 2 * F : F, V = c.vocab, H = c.n_head;
+    const size_t d = c.d_model, F = c.d_ff, F1 = act_gated(c.act) ? 2 * F : F, V = c.vocab, H = c.n_head;
     const size_t G = S - P, Td = with_head ? n_seq * G : 0;
     w->with_head = with_head;
     w->map = SeqMap{(int)S, (int)P, (int)G, (int)group};
@@ -238,7 +238,7 @@ static nnb_status forward(nnb_policy* p, const int32_t* tokens, size_t n_seq, si
     nnb_engine* e = p->e;
     const nnb_gpt_config& c = p->cfg;
     TrainWs* w = (TrainWs*)p->train;
-    const size_t d = c.d_model, F = c.d_ff, F1 = c.act == 1 ? 2 * F : F, V = c.vocab, H = c.n_head, dk = d / H;
+    const size_t d = c.d_model, F = c.d_ff, F1 = act_gated(c.act) ? 2 * F : F, V = c.vocab, H = c.n_head, dk = d / H;
     const size_t T = w->rows, G = S - P, Td = n_seq * G;
     const bool exact = c.exact != 0;
     const bool grouped = w->map.group > 1;
@@ -273,7 +273,7 @@ static nnb_status forward(nnb_policy* p, const int32_t* tokens, size_t n_seq, si
         NNB_TRY(lin_fwd(p, LW.o, 1, s.q2, s.s2, w->qsum, T, x_in, s.x_mid, 0));
         NNB_TRY(launch_row_quant(e, 0, exact, s.x_mid, PP + LW.ln2_g, T, d, d, s.q3, s.s3, w->qsum, nullptr));
         NNB_TRY(lin_fwd(p, LW.fc1, 1, s.q3, s.s3, w->qsum, T, nullptr, s.h1, 0));
-        NNB_TRY(launch_row_quant(e, c.act == 1 ? 2 : 1, exact, s.h1, nullptr, T, F, F1, s.q4, s.s4, w->qsum, nullptr));
+        NNB_TRY(launch_row_quant(e, act_quant_mode(c.act), exact, s.h1, nullptr, T, F, F1, s.q4, s.s4, w->qsum, nullptr));
         NNB_TRY(lin_fwd(p, LW.fc2, 1, s.q4, s.s4, w->qsum, T, s.x_mid, x_out, 0));
     }
     if (!w->with_head) return NNB_OK;
@@ -365,11 +365,11 @@ static nnb_status backward(nnb_policy* p, const int32_t* tokens, size_t n_seq, s
         NNB_TRY(lin_bwd(p, LW.fc2, w->g, s.q4, s.s4, T, w->da, false));
         if (tc_bwd_ok(p, LW.fc1.out, T) && F % 2 == 0) {
             // the activation's backward writes the GEMM operand directly (no f32 round trip of dh1)
-            NNB_TRY(launch_act_bwd_scale_colsum(e, c.act == 1 ? 2 : 1, s.h1, w->da, p->tau + LW.fc1.tau_off, T, F, w->dyb,
+            NNB_TRY(launch_act_bwd_scale_colsum(e, act_bwd_mode(c.act), s.h1, w->da, p->tau + LW.fc1.tau_off, T, F, w->dyb,
                                                 GG + LW.fc1.b_off, sink_of(w, T)));
             NNB_TRY(lin_bwd_gemms(p, LW.fc1, LW.fc1.out, s.q3, s.s3, T, w->dn, false));
         } else {
-            NNB_TRY(launch_act_bwd(e, c.act == 1 ? 2 : 1, s.h1, w->da, T, F, w->dh1));
+            NNB_TRY(launch_act_bwd(e, act_bwd_mode(c.act), s.h1, w->da, T, F, w->dh1));
             NNB_TRY(lin_bwd(p, LW.fc1, w->dh1, s.q3, s.s3, T, w->dn, false));
         }
         NNB_TRY(launch_rmsnorm_bwd(e, s.x_mid, PP + LW.ln2_g, w->dn, w->g, T, d, w->g2, GG + LW.ln2_g));

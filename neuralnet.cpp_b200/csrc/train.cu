@@ -499,6 +499,7 @@ rmsnorm_bwd_vec_kernel(const float* x /* may be dx: in place */, const float* __
 // ------------------------------------------------------- activation backward
 // MODE 1 QuickGELU: dh = da * s*(1 + bx*(1-s)), s = sigmoid(bx), bx = 1.702 h
 // MODE 2 SwiGLU: h = (gate|up): dgate = da*up*s*(1+gate*(1-s)), dup = da*gate*s
+// MODE 3 ReLU2GLU: h = (gate|up), r = relu(gate): dgate = da*up*2r, dup = da*r*r (compute_layer_mlp.hpp:425-440)
 template <int MODE>
 __global__ void act_bwd_kernel(const float* __restrict__ h, const float* __restrict__ da, size_t T, int F,
                                float* __restrict__ dh)
@@ -514,10 +515,16 @@ __global__ void act_bwd_kernel(const float* __restrict__ h, const float* __restr
         dh[idx] = da[idx] * (sg * (1.0f + bx * (1.0f - sg)));
     } else {
         const float gv = h[t * 2 * F + f], uv = h[t * 2 * F + F + f];
-        const float sg = 1.0f / (1.0f + nnb_expf(-gv));
         const float go = da[idx];
-        dh[t * 2 * F + f] = go * uv * (sg * (1.0f + gv * (1.0f - sg)));
-        dh[t * 2 * F + F + f] = go * gv * sg;
+        if (MODE == 3) {
+            const float rv = fmaxf(gv, 0.0f);
+            dh[t * 2 * F + f] = go * uv * (2.0f * rv);
+            dh[t * 2 * F + F + f] = go * (rv * rv);
+        } else {
+            const float sg = 1.0f / (1.0f + nnb_expf(-gv));
+            dh[t * 2 * F + f] = go * uv * (sg * (1.0f + gv * (1.0f - sg)));
+            dh[t * 2 * F + F + f] = go * gv * sg;
+        }
     }
 }
 
@@ -551,9 +558,15 @@ act_bwd_vec_kernel(const float* __restrict__ h, const float* __restrict__ da, si
         float og[4], ou[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const float sg = 1.0f / (1.0f + nnb_expf(-ga[i]));
-            og[i] = g4[i] * ua[i] * (sg * (1.0f + ga[i] * (1.0f - sg)));
-            ou[i] = g4[i] * ga[i] * sg;
+            if (MODE == 3) {
+                const float rv = fmaxf(ga[i], 0.0f);
+                og[i] = g4[i] * ua[i] * (2.0f * rv);
+                ou[i] = g4[i] * (rv * rv);
+            } else {
+                const float sg = 1.0f / (1.0f + nnb_expf(-ga[i]));
+                og[i] = g4[i] * ua[i] * (sg * (1.0f + ga[i] * (1.0f - sg)));
+                ou[i] = g4[i] * ga[i] * sg;
+            }
         }
         reinterpret_cast<float4*>(dh + t * 2 * F)[f] = make_float4(og[0], og[1], og[2], og[3]);
         reinterpret_cast<float4*>(dh + t * 2 * F + F)[f] = make_float4(ou[0], ou[1], ou[2], ou[3]);
@@ -831,6 +844,7 @@ nnb_status launch_act_bwd(nnb_engine* e, int mode, const float* h, const float* 
     if (F % 4 == 0 && (((uintptr_t)h | (uintptr_t)da | (uintptr_t)dh) & 15) == 0) {
         const unsigned g4 = (unsigned)ceil_div(T * (F / 4), 256);
         if (mode == 1) act_bwd_vec_kernel<1><<<g4, 256, 0, e->stream>>>(h, da, T, (int)F, dh);
+        else if (mode == 3) act_bwd_vec_kernel<3><<<g4, 256, 0, e->stream>>>(h, da, T, (int)F, dh);
         else act_bwd_vec_kernel<2><<<g4, 256, 0, e->stream>>>(h, da, T, (int)F, dh);
         e->launches++;
         NNB_CHECK_LAUNCH("act_bwd_vec_kernel");
@@ -838,6 +852,7 @@ nnb_status launch_act_bwd(nnb_engine* e, int mode, const float* h, const float* 
     }
     const unsigned grid = (unsigned)ceil_div(T * F, 256);
     if (mode == 1) act_bwd_kernel<1><<<grid, 256, 0, e->stream>>>(h, da, T, (int)F, dh);
+    else if (mode == 3) act_bwd_kernel<3><<<grid, 256, 0, e->stream>>>(h, da, T, (int)F, dh);
     else act_bwd_kernel<2><<<grid, 256, 0, e->stream>>>(h, da, T, (int)F, dh);
     e->launches++;
     NNB_CHECK_LAUNCH("act_bwd_kernel");

@@ -15,7 +15,7 @@ import torch
 from ._lib import NnbError, check, lib
 from .engine import Engine, _ptr
 
-GELU, SWIGLU = 0, 1
+GELU, SWIGLU, RELU2 = 0, 1, 2
 LEARNED, ROPE = 0, 1
 
 
@@ -44,7 +44,7 @@ class GptConfig:
     def param_layout(self):
         """(name, offset, shape) of every tensor in the flat parameter buffer, in order."""
         d, F, V = self.d_model, self.d_ff, self.vocab
-        F1 = 2 * F if self.act == SWIGLU else F
+        F1 = 2 * F if self.act in (SWIGLU, RELU2) else F
         out, o = [], 0
 
         def add(name, *shape):

@@ -148,7 +148,7 @@ static size_t lin_setup(orc_lin* l, const float* base, size_t off_w, size_t off_
 ORC_API size_t orc_gpt_param_count(const orc_gpt_cfg* c)
 {
     const size_t d = c->d_model, F = c->d_ff, V = c->vocab;
-    const size_t F1 = c->act == 1 ? 2 * F : F;
+    const size_t F1 = c->act >= 1 ? 2 * F : F;
     size_t n = V * d;
     if (c->pos == 0) n += (size_t)c->ctx * d;
     n += (size_t)c->n_layer * (d + 3 * d * d + 3 * d + d * d + d + d + F1 * d + F1 + d * F + d);
@@ -162,7 +162,7 @@ ORC_API orc_gpt* orc_gpt_create(const orc_gpt_cfg* c, const float* params)
     orc_gpt* m = (orc_gpt*)calloc(1, sizeof(orc_gpt));
     m->cfg = *c;
     const size_t d = c->d_model, F = c->d_ff, V = c->vocab;
-    const size_t F1 = c->act == 1 ? 2 * F : F;
+    const size_t F1 = c->act >= 1 ? 2 * F : F;
     size_t o = 0;
     m->tok_emb = params + o; o += V * d;
     if (c->pos == 0) { m->pos_emb = params + o; o += (size_t)c->ctx * d; }
@@ -316,7 +316,7 @@ typedef struct {
 static orc_state* state_new(const orc_gpt* m)
 {
     const orc_gpt_cfg* c = &m->cfg;
-    const size_t d = c->d_model, F = c->d_ff, F1 = c->act == 1 ? 2 * F : F;
+    const size_t d = c->d_model, F = c->d_ff, F1 = c->act >= 1 ? 2 * F : F;
     orc_state* s = (orc_state*)calloc(1, sizeof(orc_state));
     s->k = (float*)malloc(sizeof(float) * (size_t)c->n_layer * c->ctx * d);
     s->v = (float*)malloc(sizeof(float) * (size_t)c->n_layer * c->ctx * d);
@@ -398,6 +398,13 @@ static void forward_step(const orc_gpt* m, orc_state* st, int token, int cur_len
             for (int i = 0; i < F; ++i) {
                 const float xv = st->h1[i];
                 st->h2[i] = xv / (1.0f + orc_expf(-(xv * 1.702f)));
+            }
+        } else if (c->act == 2) {
+            /* ReLU2GLU (include/neuralnet.cpp/compute_layer_mlp.hpp:384-440): relu(gate)^2 * up */
+            for (int i = 0; i < F; ++i) {
+                const float gv = st->h1[i], uv = st->h1[F + i];
+                const float rv = gv > 0.0f ? gv : 0.0f;
+                st->h2[i] = rv * rv * uv;
             }
         } else {
             for (int i = 0; i < F; ++i) {

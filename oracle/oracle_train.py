@@ -228,6 +228,10 @@ class OracleTrainer:
             one = 1.0 if sm else F32(1.0)
             if cfg.act == 0:
                 act = R(h1 / R(one + ex(-R(h1 * (1.702 if sm else F32(1.702))))))
+            elif cfg.act == 2:  # ReLU2GLU (compute_layer_mlp.hpp:384-440): relu(gate)^2 * up
+                g, u = h1[:, :F], h1[:, F:]
+                r = np.maximum(g, 0)
+                act = R(R(r * r) * u)
             else:
                 g, u = h1[:, :F], h1[:, F:]
                 sg = R(one / R(one + ex(-g)))
@@ -349,6 +353,10 @@ class OracleTrainer:
                 bx = h * 1.702
                 s = sigmoid(bx)
                 dh = da * (s * (1 + bx * (1 - s)))
+            elif cfg.act == 2:
+                gt, up = h[:, :F], h[:, F:]
+                r = np.maximum(gt, 0)
+                dh = np.concatenate([da * up * (2 * r), da * r * r], 1)
             else:
                 gt, up = h[:, :F], h[:, F:]
                 s = sigmoid(gt)

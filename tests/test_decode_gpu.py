@@ -45,7 +45,8 @@ def test_requantisation_matches_oracle(pkg, eng, orc, act, pos):
 
 
 @pytest.mark.parametrize("act,pos,heads,d", [(0, 0, 2, 64), (1, 1, 2, 64), (1, 1, 1, 128), (0, 1, 4, 256),
-                                             (1, 1, 16, 1600)])  # last: head dim 100, the 3B decode shape's
+                                             (1, 1, 16, 1600),  # head dim 100, the 3B decode shape's
+                                             (2, 1, 2, 128)])   # ReLU2GLU feed-forward
 def test_greedy_rollout_token_identical_and_logits_bitwise(pkg, eng, act, pos, heads, d):
     cfg = pkg.GptConfig(n_layer=2, d_model=d, n_head=heads, d_ff=2 * d, vocab=211, ctx=40, act=act, pos=pos)
     pol, m, _ = _setup(pkg, eng, cfg)

@@ -28,7 +28,7 @@ def _loss(cfg, flat, tokens, P, up_lp, up_ent, dv):
     return total
 
 
-@pytest.mark.parametrize("act,pos,value_head", [(0, 0, False), (1, 1, True), (0, 1, True), (1, 0, False)])
+@pytest.mark.parametrize("act,pos,value_head", [(0, 0, False), (1, 1, True), (0, 1, True), (1, 0, False), (2, 1, False)])
 def test_whole_model_backward_by_finite_differences(pkg, act, pos, value_head):
     cfg = pkg.GptConfig(n_layer=2, d_model=16, n_head=2, d_ff=24, vocab=13, ctx=8, act=act, pos=pos, value_head=value_head)
     rng = np.random.default_rng(10 + act + 2 * pos)

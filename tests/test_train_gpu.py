@@ -78,7 +78,7 @@ def _grad_check(pol, tr, cfg, got_flat, ref_flat):
     return worst
 
 
-@pytest.mark.parametrize("act,pos,value_head", [(0, 0, False), (1, 1, False), (1, 1, True), (0, 1, True)])
+@pytest.mark.parametrize("act,pos,value_head", [(0, 0, False), (1, 1, False), (1, 1, True), (0, 1, True), (2, 1, False)])
 def test_train_step_gradients(pkg, eng, act, pos, value_head):
     cfg, pol, tr, tokens, P = _case(pkg, eng, act, pos, value_head)
     n, S = tokens.shape
@@ -386,3 +386,30 @@ def test_fast_mode_backward_with_a_feed_forward_narrower_than_three_model_widths
     # gradient scale, as compare_gradients does)
     dev_stats = compare_gradients(cfg_e, pf.grads_view().cpu().numpy(), pe.grads_view().cpu().numpy())
     assert dev_stats["grad_rel_rms"] <= 0.2, dev_stats
+
+
+def test_fast_mode_relu2_glu_feed_forward(pkg, eng):
+    """ReLU2GLU (relu(gate)^2 * up, the BitNet 2B4T feed-forward) through the fused tensor-core backward: against the exact mode."""
+    from neuralnet_cpp_b200.parity import compare_gradients
+
+    kw = dict(n_layer=2, d_model=128, n_head=2, d_ff=256, vocab=536, ctx=48, act=2, pos=1)
+    cfg_e, cfg_f = pkg.GptConfig(exact=True, **kw), pkg.GptConfig(exact=False, **kw)
+    flat = cfg_e.init_params(4, linear_std=0.05, bias_std=0.01)
+    pe, pf = pkg.Policy(eng, cfg_e), pkg.Policy(eng, cfg_f)
+    pe.upload_params(flat)
+    pf.upload_params(flat)
+    rng = np.random.default_rng(8)
+    n, S, P = 4, 40, 8
+    tokens = dev(rng.integers(0, 536, (n, S)), eng, np.int32)
+    lp, _, _ = pe.logprobs(tokens, P)
+    lp_f, _, _ = pf.logprobs(tokens, P)
+    assert (lp - lp_f).abs().max().item() <= 3e-2 * lp.abs().max().item()
+    old = lp + dev(rng.normal(0, 0.2, (n, S - P)), eng)
+    adv = dev(rng.normal(0, 1, (n, S - P)), eng)
+    mask = dev(np.ones((n, S - P)), eng)
+    for pol in (pe, pf):
+        pol.zero_grad()
+        pol.train_step(tokens, P, mask, old_logp=old, advantage=adv)
+    eng.check_device_errors()
+    stats = compare_gradients(cfg_e, pf.grads_view().cpu().numpy(), pe.grads_view().cpu().numpy())
+    assert stats["grad_rel_rms"] <= 0.2, stats
