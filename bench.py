@@ -60,6 +60,20 @@ WORKLOADS = {
                      text="rollout-only decode, BitNet-b1.58-3B-shaped ternary policy (26 layers, d 3200, 32 heads, SwiGLU 8640, "
                           "vocab 32002), 512 sequences, prompt 256, 1792 generated, bf16 KV cache to ctx 2048, top-k 50, T 0.8, "
                           "decoded in chunks of <= 128 sequences per GPU"),
+    # the structure of BitNet b1.58 2B4T: SubLN, grouped-query attention (20 heads on 5 KV heads), tied embeddings, ReLU2GLU
+    "grpo2b4t": dict(kind="grpo", model=dict(n_layer=30, d_model=2560, n_head=20, n_head_kv=5, d_ff=6912, vocab=128256, ctx=640,
+                                             act=2, pos=1, sub_ln=True, tie_embeddings=True),
+                     groups=64, group_size=16, prompt_len=128, max_new=512, temperature=0.8, top_k=50, kl_coef=0.04,
+                     micro_batch=16, rollout_chunk=1024,
+                     text="GRPO step, BitNet-b1.58-2B4T-structured ternary policy (30 layers, d 2560, 20 heads on 5 KV heads, RoPE, "
+                          "SubLN, ReLU2GLU 6912, tied embeddings, vocab 128256), 64 prompts x group 16, prompt 128, 512 generated, "
+                          "top-k 50, T 0.8, clip 0.2, KL 0.04 vs frozen initial policy"),
+    "decode2b4t": dict(kind="decode", model=dict(n_layer=30, d_model=2560, n_head=20, n_head_kv=5, d_ff=6912, vocab=128256, ctx=2048,
+                                                 act=2, pos=1, sub_ln=True, tie_embeddings=True),
+                       n_seq=512, prompt_len=256, max_new=1792, temperature=0.8, top_k=50, chunk=128,
+                       text="rollout-only decode, BitNet-b1.58-2B4T-structured ternary policy (30 layers, d 2560, 20 heads on 5 KV "
+                            "heads, SubLN, ReLU2GLU 6912, tied embeddings, vocab 128256), 512 sequences, prompt 256, 1792 generated, "
+                            "bf16 KV cache to ctx 2048, top-k 50, T 0.8, decoded in chunks of <= 128 sequences per GPU"),
 }
 
 

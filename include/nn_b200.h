@@ -297,6 +297,17 @@ typedef struct nnb_gpt_config {
     int32_t value_head; /* 1 adds a Linear(d_model -> 1) port on the final-norm output */
     int32_t exact;      /* 1: f32 activations and KV cache, f64-accumulated reductions (the mode
                            compared token by token with the CPU restatement); 0: bf16 KV cache */
+    /* The structure switches of BitNet b1.58 2B4T (all 0: the layout above, bit for bit). */
+    int32_t sub_ln;     /* 1: an RMSNorm inside each sub-layer, between the heads' output and the o projection
+                           (include/neuralnet.cpp/compute_layer_attention.hpp:482-489,820-826) and between the activated
+                           hidden and fc2 (include/neuralnet.cpp/compute_layer_feedforward.hpp:37-47,201-206); adds the
+                           tensors blocks.N.attn.sub_norm.gamma (d_model) and blocks.N.ffn.sub_norm.gamma (d_ff) */
+    int32_t n_head_kv;  /* grouped-query attention: key / value heads (0 = n_head); must divide n_head; query head h reads
+                           KV head h / (n_head / n_head_kv) (include/neuralnet.cpp/compute_layer_attention.hpp:444-454);
+                           the k and v projections are (n_head_kv * d_k, d_model) */
+    int32_t tie_embeddings; /* 1: logits = tok_emb . ln_f(x), a dense product without bias; no lm_head tensors; the
+                           head's weight gradient adds into tok_emb's (include/neuralnet.cpp/compute_layer_gpt.hpp:286-297,
+                           556-575) */
 } nnb_gpt_config;
 
 typedef struct nnb_policy nnb_policy;

@@ -170,7 +170,7 @@ static const LinW* find_linear(const nnb_policy* p, size_t w_off)
     for (const auto& L : p->layers)
         for (const LinW* l : {&L.q, &L.k, &L.v, &L.o, &L.fc1, &L.fc2})
             if (l->w_off == w_off) return l;
-    return p->head.w_off == w_off ? &p->head : nullptr;
+    return (p->head.out > 0 && p->head.w_off == w_off) ? &p->head : nullptr;
 }
 
 static std::string spec_text(const nnb_policy* p, int role)
@@ -179,7 +179,7 @@ static std::string spec_text(const nnb_policy* p, int role)
     std::ostringstream s;
     s << "model=gpt_t1_58\nn_layer=" << c.n_layer << "\nd_model=" << c.d_model << "\nn_head=" << c.n_head << "\nd_ff=" << c.d_ff
       << "\nvocab=" << c.vocab << "\nctx=" << c.ctx << "\nact=" << c.act << "\npos=" << c.pos << "\nvalue_head=" << c.value_head
-      << "\nrole=" << role << "\nentries=" << p->tensors.size() << "\n";
+      << "\nsub_ln=" << c.sub_ln << "\nn_head_kv=" << nnb::cfg_kv_heads(c) << "\ntie_embeddings=" << c.tie_embeddings << "\nrole=" << role << "\nentries=" << p->tensors.size() << "\n";
     return s.str();
 }
 

@@ -307,6 +307,17 @@ nnb_status launch_scale_colsum(nnb_engine* e, const float* dy, const float* tau,
 nnb_status launch_act_bwd_scale_colsum(nnb_engine* e, int mode, const float* h, const float* da, const float* tau, size_t t,
                                        size_t F, __nv_bfloat16* dyb, float* db, ColsumSink* sink = nullptr);
 nnb_status launch_dequant_to_bf16(nnb_engine* e, const int8_t* q, const float* s, size_t t, size_t k, __nv_bfloat16* xs);
+// c (T, N) f32 = a (T, K) bf16 . b (N, K)^T bf16 on tcgen05 (T >= 64, K % 8 == 0, N % 4 == 0)
+nnb_status launch_tc_nt(nnb_engine* e, const __nv_bfloat16* a, const __nv_bfloat16* b, size_t t, size_t k, size_t n, float* c);
+// struct_ops.cu: grouped-query attention (replicate the KV heads of (T, d + 2 dkv) into planes (3, T, d); fold the
+// replicas' gradients back) and the dense products of the tied head
+nnb_status launch_gqa_expand(nnb_engine* e, const float* raw, size_t T, size_t H, size_t Hkv, size_t dk, float* planes);
+nnb_status launch_gqa_reduce(nnb_engine* e, const float* planes, size_t T, size_t H, size_t Hkv, size_t dk, float* raw);
+nnb_status launch_f32_to_bf16(nnb_engine* e, const float* x, size_t n, __nv_bfloat16* y);
+nnb_status launch_dense_nt(nnb_engine* e, bool exact, const float* A, const float* B, size_t T, size_t N, size_t K, float* C);
+nnb_status launch_dense_nt_bf16(nnb_engine* e, const __nv_bfloat16* A, const __nv_bfloat16* B, size_t T, size_t N, size_t K, float* C);
+nnb_status launch_dense_nn(nnb_engine* e, bool exact, const float* G, const float* B, size_t T, size_t N, size_t K, float* C);
+nnb_status launch_dense_tn_acc(nnb_engine* e, bool exact, const float* G, const float* X, size_t T, size_t N, size_t K, float* D);
 
 // ---- attn_b16.cu (bf16 tensor-core attention of the teacher-forced pass, head dims 64 and 128)
 bool attn_b16_supported(size_t dk, size_t d);

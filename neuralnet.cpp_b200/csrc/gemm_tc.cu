@@ -823,6 +823,19 @@ nnb_status launch_tc_dx(nnb_engine* e, const __nv_bfloat16* dyb, const __nv_bflo
     return launch<1, false, true, 1, 256>(e, ta, tb, ep, t, k, out);
 }
 
+// c (T,N) f32 = a (T,K) bf16 . b (N,K)^T bf16: both operands K-major (the dense head of tied embeddings)
+nnb_status launch_tc_nt(nnb_engine* e, const __nv_bfloat16* a, const __nv_bfloat16* b, size_t t, size_t k, size_t n, float* c)
+{
+    using namespace tc;
+    NNB_REQUIRE(k % 8 == 0 && n % 4 == 0 && (((uintptr_t)a | (uintptr_t)b | (uintptr_t)c) & 15) == 0,
+                "tc_nt: K must be a multiple of 8, N of 4, operands 16-byte aligned");
+    CUtensorMap ta, tb;
+    NNB_TRY(make_map(&ta, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, t, k, 64, BM));
+    NNB_TRY(make_map(&tb, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, n, k, 64, 256));
+    Epi ep{c, nullptr, nullptr, nullptr, nullptr, 0, (int)n, 0};
+    return launch<1, false, false, 1, 256>(e, ta, tb, ep, t, n, k);
+}
+
 // dW: dyb (T,OUT) bf16, xs (T,K) bf16; dw (OUT,K) f32 +=
 nnb_status launch_tc_dw(nnb_engine* e, const __nv_bfloat16* dyb, const __nv_bfloat16* xs, size_t t, size_t k, size_t out,
                         float* dw)

@@ -29,6 +29,7 @@ static void build_layout(nnb_policy* p)
     const nnb_gpt_config& c = p->cfg;
     const size_t d = c.d_model, F = c.d_ff, V = c.vocab;
     const size_t F1 = act_gated(c.act) ? 2 * F : F;
+    const size_t dkv = cfg_kv_heads(c) * (d / c.n_head);
     size_t o = 0, po = 0, to = 0;
     auto lin = [&](LinW& l, const std::string& nm, size_t w_off, size_t b_off, size_t in, size_t out) {
         l.w_off = w_off;
@@ -58,13 +59,20 @@ static void build_layout(nnb_policy* p)
         L.ln1_g = o;
         add_tensor(p, pre + "ln1.gamma", o, d, 1);
         o += d;
-        const size_t wq = o, wk = o + d * d, wv = o + 2 * d * d;
-        o += 3 * d * d;
-        const size_t bq = o, bk = o + d, bv = o + 2 * d;
-        o += 3 * d;
+        const size_t wq = o, wk = o + d * d, wv = wk + dkv * d;
+        o += (d + 2 * dkv) * d;
+        const size_t bq = o, bk = o + d, bv = bk + dkv;
+        o += d + 2 * dkv;
         lin(L.q, pre + "attn.q", wq, bq, d, d);
-        lin(L.k, pre + "attn.k", wk, bk, d, d);
-        lin(L.v, pre + "attn.v", wv, bv, d, d);
+        lin(L.k, pre + "attn.k", wk, bk, d, dkv);
+        lin(L.v, pre + "attn.v", wv, bv, d, dkv);
+        L.qkv = L.q;
+        L.qkv.out = d + 2 * dkv;
+        if (c.sub_ln) {
+            L.attn_sub_g = o;
+            add_tensor(p, pre + "attn.sub_norm.gamma", o, d, 1);
+            o += d;
+        }
         const size_t wo = o;
         o += d * d;
         const size_t bo = o;
@@ -78,6 +86,11 @@ static void build_layout(nnb_policy* p)
         const size_t b1 = o;
         o += F1;
         lin(L.fc1, pre + "ffn.fc1", w1, b1, d, F1);
+        if (c.sub_ln) {
+            L.ffn_sub_g = o;
+            add_tensor(p, pre + "ffn.sub_norm.gamma", o, F, 1);
+            o += F;
+        }
         const size_t w2 = o;
         o += d * F;
         const size_t b2 = o;
@@ -87,11 +100,13 @@ static void build_layout(nnb_policy* p)
     p->lnf_g = o;
     add_tensor(p, "ln_f.gamma", o, d, 1);
     o += d;
-    const size_t hw = o;
-    o += V * d;
-    const size_t hb = o;
-    o += V;
-    lin(p->head, "lm_head", hw, hb, d, V);
+    if (!c.tie_embeddings) {
+        const size_t hw = o;
+        o += V * d;
+        const size_t hb = o;
+        o += V;
+        lin(p->head, "lm_head", hw, hb, d, V);
+    }
     p->value_w = p->value_b = (size_t)-1;
     if (c.value_head) {
         p->value_w = o;
@@ -168,7 +183,7 @@ nnb_status policy_requantize(nnb_policy* p, bool seeded)
             NNB_TRY(requantize_linear(p, L.fc1));
             NNB_TRY(requantize_linear(p, L.fc2));
         }
-        NNB_TRY(requantize_linear(p, p->head));
+        if (!p->cfg.tie_embeddings) NNB_TRY(requantize_linear(p, p->head));
     }
     if (!p->cfg.exact) {
         if (!p->w8) {
@@ -180,15 +195,36 @@ nnb_status policy_requantize(nnb_policy* p, bool seeded)
         }
         NNB_TRY(expand_all(p, true, p->wb != nullptr));
         p->wb_valid = p->wb != nullptr;
+        if (p->cfg.tie_embeddings) {
+            const size_t n = (size_t)p->cfg.vocab * p->cfg.d_model;
+            if (!p->eb) {
+                cudaError_t er = cudaMalloc((void**)&p->eb, n * sizeof(__nv_bfloat16));
+                if (er != cudaSuccess) {
+                    cudaGetLastError();
+                    NNB_FAIL(NNB_ERR_OOM, "out of device memory for the bf16 embedding copy");
+                }
+            }
+            NNB_TRY(launch_f32_to_bf16(p->e, p->params + p->tok_emb, n, p->eb));
+        }
     }
     return NNB_OK;
+}
+
+nnb_status policy_tied_head_fwd(nnb_policy* p, const float* hn, __nv_bfloat16* hnb, size_t T, float* logits)
+{
+    const size_t d = p->cfg.d_model, V = p->cfg.vocab;
+    if (p->cfg.exact) return launch_dense_nt(p->e, true, hn, p->params + p->tok_emb, T, V, d, logits);
+    NNB_REQUIRE(p->eb && hnb, "tied head: the bf16 embedding copy is missing");
+    NNB_TRY(launch_f32_to_bf16(p->e, hn, T * d, hnb));
+    if (T >= 64 && d % 8 == 0 && V % 4 == 0) return launch_tc_nt(p->e, hnb, p->eb, T, d, V, logits);
+    return launch_dense_nt_bf16(p->e, hnb, p->eb, T, V, d, logits);
 }
 
 static void free_decode(nnb_policy* p)
 {
     DecodeWs& w = p->dec;
     void* ptrs[] = {w.k, w.v, w.k_pre, w.v_pre, w.tokens_pre, w.x, w.qkv, w.att, w.pre_ml, w.h1, w.logits, w.q8, w.s, w.qsum, w.d_pos,
-                    w.tokens, w.logp, w.done, w.gen_len};
+                    w.tokens, w.logp, w.done, w.gen_len, w.qkv_raw, w.act, w.hn, w.hnb};
     for (void* q : ptrs)
         if (q) cudaFree(q);
     w = DecodeWs();
@@ -248,6 +284,12 @@ static nnb_status ensure_decode(nnb_policy* p, size_t B, size_t ctx_alloc, size_
     NNB_ALLOC(w.logp, B * total * 4);
     NNB_ALLOC(w.done, B * 4);
     NNB_ALLOC(w.gen_len, B * 4);
+    if (cfg_gqa(c)) NNB_ALLOC(w.qkv_raw, B * (d + 2 * cfg_kv_heads(c) * (d / c.n_head)) * 4);
+    if (c.sub_ln) NNB_ALLOC(w.act, B * F * 4);
+    if (c.tie_embeddings) {
+        NNB_ALLOC(w.hn, B * d * 4);
+        NNB_ALLOC(w.hnb, B * d * 2);
+    }
 #undef NNB_ALLOC
     w.B = B;
     w.ctx_alloc = ctx_alloc;
@@ -290,6 +332,8 @@ static nnb_status decode_step(nnb_policy* p, const StepView& sv, bool with_head,
     DecodeWs& w = p->dec;
     const size_t B = sv.B, d = c.d_model, F = c.d_ff, V = c.vocab, H = c.n_head, dk = d / H;
     const size_t F1 = act_gated(c.act) ? 2 * F : F;
+    const size_t Hkv = cfg_kv_heads(c);
+    const bool gqa = cfg_gqa(c);
     const bool exact = c.exact != 0;
     const float* P = p->params;
     // The fast mode's step is ~200 short kernels, each of which waits for the one before it (pdl_wait) before
@@ -306,8 +350,15 @@ static nnb_status decode_step(nnb_policy* p, const StepView& sv, bool with_head,
     for (int l = 0; l < c.n_layer; ++l) {
         const LayerW& L = p->layers[l];
         NNB_TRY(launch_row_quant(e, 0, exact, w.x, P + L.ln1_g, B, d, d, w.q8, w.s, w.qsum, nullptr));
-        // q, k, v projections: three equally shaped matrices stored back to back, one launch
-        NNB_TRY(policy_linear_fwd(p, L.q, 3, w.q8, w.s, w.qsum, B, nullptr, w.qkv, B * d));
+        if (gqa) {
+            // one matrix of d + 2 dkv rows, then the KV heads are replicated to the query heads' count: the attention
+            // kernels and the cache see plain multi-head attention, as the reference's gather_rows expansion does
+            NNB_TRY(policy_linear_fwd(p, L.qkv, 1, w.q8, w.s, w.qsum, B, nullptr, w.qkv_raw, 0));
+            NNB_TRY(launch_gqa_expand(e, w.qkv_raw, B, H, Hkv, dk, w.qkv));
+        } else {
+            // q, k, v projections: three equally shaped matrices stored back to back, one launch
+            NNB_TRY(policy_linear_fwd(p, L.q, 3, w.q8, w.s, w.qsum, B, nullptr, w.qkv, B * d));
+        }
         void* kl = (char*)sv.k + (size_t)l * sv.layer_bytes;
         void* vl = (char*)sv.v + (size_t)l * sv.layer_bytes;
         const void* kpl = sv.k_pre ? (const char*)sv.k_pre + (size_t)l * sv.pre_layer_bytes : nullptr;
@@ -321,7 +372,7 @@ static nnb_status decode_step(nnb_policy* p, const StepView& sv, bool with_head,
         // (16 resident per SM) the kernel with one CTA per (sequence, head), four warps splitting the keys, has
         // several times the loads in flight and wins, the separate quantisation launch included.
         const bool few = B * H <= (size_t)e->sm_count * 16;
-        if (!exact && !few && attn_decode_fused_supported(H, dk) && d % 64 == 0) {
+        if (!exact && !few && !c.sub_ln && attn_decode_fused_supported(H, dk) && d % 64 == 0) {
             // all heads of a sequence in one CTA, attention output quantised in the same launch
             NNB_TRY(launch_attn_decode_fused(e, w.qkv, kl, vl, sv.own_alloc, kpl, vpl, sv.pre_len, sv.pre_alloc, sv.group,
                                              c.pos == 1 ? p->rope_cos : nullptr, c.pos == 1 ? p->rope_sin : nullptr, w.d_pos, B, H,
@@ -329,7 +380,9 @@ static nnb_status decode_step(nnb_policy* p, const StepView& sv, bool with_head,
         } else {
             NNB_TRY(launch_attn_decode(e, exact, w.qkv, kl, vl, sv.own_alloc, kpl, vpl, sv.pre_len, sv.pre_alloc, sv.group,
                                        p->rope_cos, p->rope_sin, w.d_pos, B, H, dk, w.att, attn_decode_kv_pitch(exact, dk)));
-            NNB_TRY(launch_row_quant(e, 3, exact, w.att, nullptr, B, d, d, w.q8, w.s, w.qsum, nullptr));
+            // SubLN: the heads' output is normalised before it is quantised for the o projection
+            NNB_TRY(launch_row_quant(e, c.sub_ln ? 0 : 3, exact, w.att, c.sub_ln ? P + L.attn_sub_g : nullptr, B, d, d, w.q8, w.s,
+                                     w.qsum, nullptr));
         }
         {
             const nnb_status so = policy_linear_fwd(p, L.o, 1, w.q8, w.s, w.qsum, B, w.x, w.x, 0);
@@ -338,13 +391,16 @@ static nnb_status decode_step(nnb_policy* p, const StepView& sv, bool with_head,
         }
         NNB_TRY(launch_row_quant(e, 0, exact, w.x, P + L.ln2_g, B, d, d, w.q8, w.s, w.qsum, nullptr));
         NNB_TRY(policy_linear_fwd(p, L.fc1, 1, w.q8, w.s, w.qsum, B, nullptr, w.h1, 0));
-        NNB_TRY(launch_row_quant(e, act_quant_mode(c.act), exact, w.h1, nullptr, B, F, F1, w.q8, w.s, w.qsum, nullptr));
+        NNB_TRY(launch_row_quant(e, act_quant_mode(c.act), exact, w.h1, nullptr, B, F, F1, w.q8, w.s, w.qsum, c.sub_ln ? w.act : nullptr));
+        if (c.sub_ln)  // SubLN: the activated hidden is normalised, then quantised for fc2
+            NNB_TRY(launch_row_quant(e, 0, exact, w.act, P + L.ffn_sub_g, B, F, F, w.q8, w.s, w.qsum, nullptr));
         NNB_TRY(policy_linear_fwd(p, L.fc2, 1, w.q8, w.s, w.qsum, B, w.x, w.x, 0));
     }
     if (with_head) {
         const size_t total = w.tok_cols;  // row pitch of the token / log-prob buffers
-        NNB_TRY(launch_row_quant(e, 0, exact, w.x, P + p->lnf_g, B, d, d, w.q8, w.s, w.qsum, nullptr));
-        NNB_TRY(policy_linear_fwd(p, p->head, 1, w.q8, w.s, w.qsum, B, nullptr, w.logits, 0));
+        NNB_TRY(launch_row_quant(e, 0, exact, w.x, P + p->lnf_g, B, d, d, w.q8, w.s, w.qsum, c.tie_embeddings ? w.hn : nullptr));
+        if (c.tie_embeddings) NNB_TRY(policy_tied_head_fwd(p, w.hn, w.hnb, B, w.logits));
+        else NNB_TRY(policy_linear_fwd(p, p->head, 1, w.q8, w.s, w.qsum, B, nullptr, w.logits, 0));
         NNB_TRY(launch_sample_opts(e, exact, w.logits, B, V, so, seed, seq0, w.d_pos, prompt_len, w.tokens, total,
                                    want_logp ? w.logp : nullptr, total, nullptr));
     }
@@ -565,6 +621,8 @@ nnb_status nnb_policy_create(nnb_engine* e, const nnb_gpt_config* cfg, nnb_polic
     NNB_REQUIRE(c.act >= 0 && c.act <= 2, "policy_create: act must be 0 (QuickGELU), 1 (SwiGLU) or 2 (ReLU2GLU)");
     NNB_REQUIRE(c.pos == 0 || c.pos == 1, "policy_create: pos must be 0 (learned) or 1 (RoPE)");
     NNB_REQUIRE(c.pos == 0 || dk % 2 == 0, "policy_create: RoPE needs an even head dim");
+    NNB_REQUIRE(c.n_head_kv >= 0 && (c.n_head_kv == 0 || (c.n_head_kv <= c.n_head && c.n_head % c.n_head_kv == 0)),
+                "policy_create: n_head_kv %d must divide n_head %d", c.n_head_kv, c.n_head);
     nnb_policy* p = new nnb_policy();
     p->e = e;
     p->cfg = c;
@@ -612,7 +670,7 @@ void nnb_policy_destroy(nnb_policy* p)
     for (cudaEvent_t evt : p->time_events) cudaEventDestroy(evt);
     free_decode(p);
     policy_free_train(p);
-    void* ptrs[] = {p->params, p->grads, p->adam_m, p->adam_v, p->packed, p->tau, p->rope_cos, p->rope_sin, p->w8, p->wb};
+    void* ptrs[] = {p->params, p->grads, p->adam_m, p->adam_v, p->packed, p->tau, p->rope_cos, p->rope_sin, p->w8, p->wb, p->eb};
     for (void* q : ptrs)
         if (q) cudaFree(q);
     delete p;
@@ -654,8 +712,10 @@ nnb_status nnb_policy_linear(nnb_policy* p, int layer, int which, uint32_t** d_p
 {
     NNB_REQUIRE(p, "policy is NULL");
     const LinW* l = nullptr;
-    if (layer < 0) l = &p->head;
-    else {
+    if (layer < 0) {
+        NNB_REQUIRE(!p->cfg.tie_embeddings, "policy_linear: a policy with tied embeddings has no head linear");
+        l = &p->head;
+    } else {
         NNB_REQUIRE(layer < p->cfg.n_layer && which >= 0 && which < 6, "policy_linear: bad index");
         LayerW& L = p->layers[layer];
         const LinW* all[6] = {&L.q, &L.k, &L.v, &L.o, &L.fc1, &L.fc2};

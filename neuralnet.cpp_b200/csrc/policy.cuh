@@ -16,7 +16,9 @@ struct LinW {
 
 struct LayerW {
     size_t ln1_g = 0, ln2_g = 0;
+    size_t attn_sub_g = 0, ffn_sub_g = 0;  // SubLN gains (d_model), (d_ff); only with cfg.sub_ln
     LinW q, k, v, o, fc1, fc2;
+    LinW qkv;  // q, k and v as one matrix of d + 2 * dkv rows (their weights, scales and biases are contiguous)
 };
 
 struct TensorInfo {
@@ -32,6 +34,10 @@ struct DecodeWs {
     void *k_pre = nullptr, *v_pre = nullptr;  // (L, B/group, H, pre_len, dk): prompt prefix, one per group
     int32_t* tokens_pre = nullptr;            // (B/group, pre_len) prompt tokens of the group representatives
     float *x = nullptr, *qkv = nullptr, *att = nullptr, *h1 = nullptr, *logits = nullptr;
+    float* qkv_raw = nullptr;  // grouped-query attention: (B, d + 2 dkv) projections before the KV heads are replicated
+    float* act = nullptr;      // SubLN: (B, d_ff) activated hidden before its norm
+    float* hn = nullptr;       // tied embeddings: (B, d) final-norm output, the dense head's operand
+    __nv_bfloat16* hnb = nullptr;
     float* pre_ml = nullptr;  // (B, H, 2): partial softmax (max, sum) over the shared prefix; its values go to att
     int8_t* q8 = nullptr;
     float* s = nullptr;
@@ -57,6 +63,7 @@ struct nnb_policy {
     int8_t* w8 = nullptr;           // fast mode: int8 trits, K permuted like the activations (tcgen05 forward)
     __nv_bfloat16* wb = nullptr;    // fast mode, trainable policies: bf16 trits (tcgen05 dX)
     bool wb_valid = false;
+    __nv_bfloat16* eb = nullptr;    // fast mode, tied embeddings: bf16 copy of tok_emb, the dense head's weight
     float* tau = nullptr;
     float *rope_cos = nullptr, *rope_sin = nullptr;  // (ctx, dk/2)
     size_t tok_emb = 0, pos_emb = 0, lnf_g = 0, value_w = 0, value_b = 0;
@@ -75,6 +82,8 @@ struct nnb_policy {
 namespace nnb {
 // nnb_gpt_config.act: 0 QuickGELU, 1 SwiGLU, 2 ReLU2GLU.  The gated ones take fc1 rows (gate | up), 2 * d_ff wide.
 inline bool act_gated(int act) { return act >= 1; }
+inline size_t cfg_kv_heads(const nnb_gpt_config& c) { return c.n_head_kv > 0 ? (size_t)c.n_head_kv : (size_t)c.n_head; }
+inline bool cfg_gqa(const nnb_gpt_config& c) { return cfg_kv_heads(c) != (size_t)c.n_head; }
 inline int act_quant_mode(int act) { return act == 0 ? 1 : (act == 1 ? 2 : 4); }  // mode of launch_row_quant
 inline int act_bwd_mode(int act) { return act == 0 ? 1 : (act == 1 ? 2 : 3); }    // mode of launch_act_bwd[_scale_colsum]
 nnb_status policy_requantize(nnb_policy* p, bool seeded = false);
@@ -86,6 +95,9 @@ nnb_status policy_prefill_prefix(nnb_policy* p, const int32_t* d_tokens, size_t 
                                  size_t alloc, size_t layer_bytes);
 void policy_free_decode(nnb_policy* p);
 nnb_status policy_ensure_wb(nnb_policy* p);
+// tied embeddings: logits (T, V) = hn (T, d) . tok_emb^T.  Exact mode: f64-accumulated CUDA-core product of the f32
+// operands.  Fast mode: bf16 operands (hnb is scratch for T * d elements), tcgen05 from 64 rows up.
+nnb_status policy_tied_head_fwd(nnb_policy* p, const float* hn, __nv_bfloat16* hnb, size_t T, float* logits);
 // y = [residual +] linear(q) through the fastest kernel for this mode and token count
 nnb_status policy_linear_fwd(nnb_policy* p, const LinW& l, size_t n_mats, const int8_t* q, const float* s,
                              const int32_t* qsum, size_t T, const float* residual, float* y, size_t y_stride);

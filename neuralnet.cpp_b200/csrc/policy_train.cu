@@ -55,6 +55,10 @@ struct TrainWs {
     bool fused_head = false;
     float *lse = nullptr, *head_scratch = nullptr;
     ColsumSink bias_sink;  // bias-gradient partial sums of a whole backward pass, finished by one launch
+    // structure switches
+    float* qkv_raw = nullptr;  // grouped-query attention: (T, d + 2 dkv) projections (forward) / their gradients (backward)
+    float *act = nullptr, *dact = nullptr;  // SubLN: (T, d_ff) activated hidden before its norm, and its gradient
+    __nv_bfloat16* hnb = nullptr;           // tied embeddings, fast mode: bf16 copy of the head's input (Td, d)
 };
 
 static void free_ws(void*& slot)
@@ -94,6 +98,8 @@ static nnb_status ensure_train(nnb_policy* p, size_t n_seq, size_t S, size_t P, 
     const nnb_gpt_config& c = p->cfg;
     const size_t d = c.d_model, F = c.d_ff, F1 = act_gated(c.act) ? 2 * F : F, V = c.vocab, H = c.n_head;
     const size_t G = S - P, Td = with_head ? n_seq * G : 0;
+    const size_t wqkv = d + 2 * cfg_kv_heads(c) * (d / H);
+    const bool tie = c.tie_embeddings != 0;
     w->with_head = with_head;
     w->map = SeqMap{(int)S, (int)P, (int)G, (int)group};
     w->rows = map_rows_total(w->map, n_seq);
@@ -102,7 +108,7 @@ static nnb_status ensure_train(nnb_policy* p, size_t n_seq, size_t S, size_t P, 
     // fast mode: attention runs on bf16 copies of q, k, v; those are what a layer keeps for its backward,
     // and the f32 projections become one buffer shared by all layers
     w->b16_attn = !c.exact && attn_b16_supported(d / H, d);
-    w->fused_head = with_head && !c.exact && p->w8 != nullptr && V % 8 == 0 && Td >= 64;
+    w->fused_head = with_head && !tie && !c.exact && p->w8 != nullptr && V % 8 == 0 && Td >= 64;
     // carve one arena: first pass measures, second assigns
     for (int pass = 0; pass < 2; ++pass) {
         size_t off = 0;
@@ -138,6 +144,9 @@ static nnb_status ensure_train(nnb_policy* p, size_t n_seq, size_t S, size_t P, 
         if (!save_layers)
             for (int l = 1; l < c.n_layer; ++l) w->L[l] = w->L[0];
         w->x_last = (float*)take(T * d * 4);
+        if (cfg_gqa(c)) w->qkv_raw = (float*)take(T * wqkv * 4);
+        if (c.sub_ln) w->act = (float*)take(T * F * 4);
+        if (tie && !c.exact) w->hnb = (__nv_bfloat16*)take(Td * d * 2);
         w->qsum = (int32_t*)take(T * 4);
         w->row_tok = (int32_t*)take(T * 4);
         w->row_pos = (int32_t*)take(T * 4);
@@ -170,6 +179,7 @@ static nnb_status ensure_train(nnb_policy* p, size_t n_seq, size_t S, size_t P, 
             w->da = (float*)take(T * F * 4);
             w->dh1 = (float*)take(T * F1 * 4);
             w->delta = (float*)take(n_seq * H * S * 4);
+            if (c.sub_ln) w->dact = (float*)take(T * F * 4);
             if (!c.exact) {
                 // widest operand written into dyb: fc1's (T, F1), the merged q|k|v gradient (T, 3d), the head's (Td, V)
                 const size_t wide = F1 > 3 * d ? F1 : 3 * d;
@@ -242,6 +252,8 @@ static nnb_status forward(nnb_policy* p, const int32_t* tokens, size_t n_seq, si
     const size_t T = w->rows, G = S - P, Td = n_seq * G;
     const bool exact = c.exact != 0;
     const bool grouped = w->map.group > 1;
+    const size_t Hkv = cfg_kv_heads(c);
+    const bool gqa = cfg_gqa(c);
     const float* PP = p->params;
     NNB_TRY(launch_build_rows(e, tokens, w->map, n_seq, w->row_tok, w->row_pos));
     NNB_TRY(launch_embed_rows_fwd(e, PP + p->tok_emb, c.pos == 0 ? PP + p->pos_emb : nullptr, w->row_tok, w->row_pos, T, d, V,
@@ -253,7 +265,13 @@ static nnb_status forward(nnb_policy* p, const int32_t* tokens, size_t n_seq, si
         if (!w->saved_layers) x_out = (l % 2 == 0) ? w->x_last : w->L[0].x_in;  // ping-pong when nothing is kept
         const float* x_in = (!w->saved_layers) ? ((l % 2 == 0) ? w->L[0].x_in : w->x_last) : s.x_in;
         NNB_TRY(launch_row_quant(e, 0, exact, x_in, PP + LW.ln1_g, T, d, d, s.q1, s.s1, w->qsum, nullptr));
-        NNB_TRY(lin_fwd(p, LW.q, 3, s.q1, s.s1, w->qsum, T, nullptr, s.qkv, T * d));
+        if (gqa) {
+            // one matrix of d + 2 dkv rows, then the KV heads are replicated: attention below is plain multi-head
+            NNB_TRY(lin_fwd(p, LW.qkv, 1, s.q1, s.s1, w->qsum, T, nullptr, w->qkv_raw, 0));
+            NNB_TRY(launch_gqa_expand(e, w->qkv_raw, T, H, Hkv, dk, s.qkv));
+        } else {
+            NNB_TRY(lin_fwd(p, LW.q, 3, s.q1, s.s1, w->qsum, T, nullptr, s.qkv, T * d));
+        }
         if (w->b16_attn) {
             NNB_TRY(launch_rope_pack_b16(e, s.qkv, s.qkv + T * d, s.qkv + 2 * T * d, c.pos == 1 ? p->rope_cos : nullptr,
                                          c.pos == 1 ? p->rope_sin : nullptr, T, S, H, dk, s.qkvb, w->row_pos));
@@ -269,11 +287,16 @@ static nnb_status forward(nnb_policy* p, const int32_t* tokens, size_t n_seq, si
             }
             NNB_TRY(launch_attn_fwd(e, exact, s.qkv, s.qkv + T * d, s.qkv + 2 * T * d, n_seq, S, H, dk, s.att, s.lse));
         }
-        NNB_TRY(launch_row_quant(e, 3, exact, s.att, nullptr, T, d, d, s.q2, s.s2, w->qsum, nullptr));
+        // SubLN: the heads' output is normalised before it is quantised for the o projection
+        NNB_TRY(launch_row_quant(e, c.sub_ln ? 0 : 3, exact, s.att, c.sub_ln ? PP + LW.attn_sub_g : nullptr, T, d, d, s.q2, s.s2,
+                                 w->qsum, nullptr));
         NNB_TRY(lin_fwd(p, LW.o, 1, s.q2, s.s2, w->qsum, T, x_in, s.x_mid, 0));
         NNB_TRY(launch_row_quant(e, 0, exact, s.x_mid, PP + LW.ln2_g, T, d, d, s.q3, s.s3, w->qsum, nullptr));
         NNB_TRY(lin_fwd(p, LW.fc1, 1, s.q3, s.s3, w->qsum, T, nullptr, s.h1, 0));
-        NNB_TRY(launch_row_quant(e, act_quant_mode(c.act), exact, s.h1, nullptr, T, F, F1, s.q4, s.s4, w->qsum, nullptr));
+        NNB_TRY(launch_row_quant(e, act_quant_mode(c.act), exact, s.h1, nullptr, T, F, F1, s.q4, s.s4, w->qsum,
+                                 c.sub_ln ? w->act : nullptr));
+        if (c.sub_ln)  // SubLN: the activated hidden is normalised, then quantised for fc2
+            NNB_TRY(launch_row_quant(e, 0, exact, w->act, PP + LW.ffn_sub_g, T, F, F, s.q4, s.s4, w->qsum, nullptr));
         NNB_TRY(lin_fwd(p, LW.fc2, 1, s.q4, s.s4, w->qsum, T, s.x_mid, x_out, 0));
     }
     if (!w->with_head) return NNB_OK;
@@ -288,7 +311,8 @@ static nnb_status forward(nnb_policy* p, const int32_t* tokens, size_t n_seq, si
         NNB_TRY(launch_tc_lmhead_fwd(e, w->qh, p->w8 + p->head.packed_off * 16, p->tau + p->head.tau_off, w->sh, PP + p->head.b_off,
                                      w->actions, Td, d, V, w->head_scratch, w->lse, w->logp, want_entropy ? w->ent : nullptr));
     } else {
-        NNB_TRY(lin_fwd(p, p->head, 1, w->qh, w->sh, w->qsum, Td, nullptr, w->logits, 0));
+        if (c.tie_embeddings) NNB_TRY(policy_tied_head_fwd(p, w->hn, w->hnb, Td, w->logits));
+        else NNB_TRY(lin_fwd(p, p->head, 1, w->qh, w->sh, w->qsum, Td, nullptr, w->logits, 0));
         NNB_TRY(launch_categorical_fwd(e, w->logits, w->actions, Td, V, w->logp, want_entropy ? w->ent : nullptr));
     }
     if (c.value_head) NNB_TRY(launch_value_fwd(e, w->hn, PP + p->value_w, PP + p->value_b, Td, d, w->value));
@@ -345,7 +369,20 @@ static nnb_status backward(nnb_policy* p, const int32_t* tokens, size_t n_seq, s
     float* GG = p->grads;
     w->bias_sink.descs.clear();
     w->bias_sink.used = 0;
-    if (w->fused_head) {
+    const size_t Hkv = cfg_kv_heads(c), F1 = act_gated(c.act) ? 2 * F : F;
+    const bool gqa = cfg_gqa(c), exact = c.exact != 0;
+    if (c.tie_embeddings) {
+        // the logits buffer holds d loss / d logits (Td, V).  dX = g . E and dE += g^T . hn, into the gradient that the
+        // embedding lookup's backward adds to as well (compute_layer_gpt.hpp:556-575)
+        if (!exact && p->eb && Td >= 64 && V % 8 == 0) {
+            NNB_TRY(launch_f32_to_bf16(e, w->logits, Td * V, w->dyb));
+            NNB_TRY(launch_tc_dx(e, w->dyb, p->eb, Td, d, V, w->dhn, false));
+            NNB_TRY(launch_tc_dw(e, w->dyb, w->hnb, Td, d, V, GG + p->tok_emb));
+        } else {
+            NNB_TRY(launch_dense_nn(e, exact, w->logits, PP + p->tok_emb, Td, V, d, w->dhn));
+            NNB_TRY(launch_dense_tn_acc(e, exact, w->logits, w->hn, Td, V, d, GG + p->tok_emb));
+        }
+    } else if (w->fused_head) {
         // w->dyb already holds bf16(dlogits * tau) and the bias gradient is done (launch_tc_lmhead_bwd)
         NNB_REQUIRE(tc_bwd_ok(p, V, Td), "fused LM head: the tensor-core backward is not available");
         NNB_TRY(lin_bwd_gemms(p, p->head, V, w->qh, w->sh, Td, w->dhn, false));
@@ -363,32 +400,50 @@ static nnb_status backward(nnb_policy* p, const int32_t* tokens, size_t n_seq, s
         LayerSave& s = w->L[l];
         // feed-forward branch
         NNB_TRY(lin_bwd(p, LW.fc2, w->g, s.q4, s.s4, T, w->da, false));
+        const float* da = w->da;
+        if (c.sub_ln) {
+            // SubLN: the activated hidden is recomputed from h1 (fc2's operands q4 / s4 are spent by now and serve as the
+            // quantiser's scratch), the norm's backward turns d(normed) into d(activated)
+            NNB_TRY(launch_row_quant(e, act_quant_mode(c.act), exact, s.h1, nullptr, T, F, F1, s.q4, s.s4, w->qsum, w->act));
+            NNB_TRY(launch_rmsnorm_bwd(e, w->act, PP + LW.ffn_sub_g, w->da, nullptr, T, F, w->dact, GG + LW.ffn_sub_g));
+            da = w->dact;
+        }
         if (tc_bwd_ok(p, LW.fc1.out, T) && F % 2 == 0) {
             // the activation's backward writes the GEMM operand directly (no f32 round trip of dh1)
-            NNB_TRY(launch_act_bwd_scale_colsum(e, act_bwd_mode(c.act), s.h1, w->da, p->tau + LW.fc1.tau_off, T, F, w->dyb,
+            NNB_TRY(launch_act_bwd_scale_colsum(e, act_bwd_mode(c.act), s.h1, da, p->tau + LW.fc1.tau_off, T, F, w->dyb,
                                                 GG + LW.fc1.b_off, sink_of(w, T)));
             NNB_TRY(lin_bwd_gemms(p, LW.fc1, LW.fc1.out, s.q3, s.s3, T, w->dn, false));
         } else {
-            NNB_TRY(launch_act_bwd(e, act_bwd_mode(c.act), s.h1, w->da, T, F, w->dh1));
+            NNB_TRY(launch_act_bwd(e, act_bwd_mode(c.act), s.h1, da, T, F, w->dh1));
             NNB_TRY(lin_bwd(p, LW.fc1, w->dh1, s.q3, s.s3, T, w->dn, false));
         }
         NNB_TRY(launch_rmsnorm_bwd(e, s.x_mid, PP + LW.ln2_g, w->dn, w->g, T, d, w->g2, GG + LW.ln2_g));
         // attention branch
         NNB_TRY(lin_bwd(p, LW.o, w->g2, s.q2, s.s2, T, w->datt, false));
+        const float* datt = w->datt;
+        if (c.sub_ln) {
+            // SubLN: d(normed heads' output) -> d(heads' output); w->dn is free between the two branches
+            NNB_TRY(launch_rmsnorm_bwd(e, s.att, PP + LW.attn_sub_g, w->datt, nullptr, T, d, w->dn, GG + LW.attn_sub_g));
+            datt = w->dn;
+        }
         if (w->b16_attn) {
             // the inverse rotation of dq and dk is part of the kernels' epilogues
-            NNB_TRY(launch_attn_bwd_b16(e, s.qkvb, s.qkvb + T * d, s.qkvb + 2 * T * d, s.att, w->datt, s.lse, w->delta, w->dob,
+            NNB_TRY(launch_attn_bwd_b16(e, s.qkvb, s.qkvb + T * d, s.qkvb + 2 * T * d, s.att, datt, s.lse, w->delta, w->dob,
                                         c.pos == 1 ? p->rope_cos : nullptr, c.pos == 1 ? p->rope_sin : nullptr, n_seq, S, H, dk,
                                         w->dqkv, w->dqkv + T * d, w->dqkv + 2 * T * d, &w->map, w->part));
         } else {
-            NNB_TRY(launch_attn_bwd(e, c.exact != 0, s.qkv, s.qkv + T * d, s.qkv + 2 * T * d, s.att, w->datt, s.lse, w->delta, n_seq,
+            NNB_TRY(launch_attn_bwd(e, c.exact != 0, s.qkv, s.qkv + T * d, s.qkv + 2 * T * d, s.att, datt, s.lse, w->delta, n_seq,
                                     S, H, dk, w->dqkv, w->dqkv + T * d, w->dqkv + 2 * T * d));
             if (c.pos == 1) {
                 NNB_TRY(launch_rope(e, w->dqkv, p->rope_cos, p->rope_sin, T, S, H, dk, true));
                 NNB_TRY(launch_rope(e, w->dqkv + T * d, p->rope_cos, p->rope_sin, T, S, H, dk, true));
             }
         }
-        if (tc_bwd_ok(p, 3 * d, T)) {
+        if (gqa) {
+            // fold the replicas' dK, dV onto their KV heads; q | k | v then go back as one matrix of d + 2 dkv rows
+            NNB_TRY(launch_gqa_reduce(e, w->dqkv, T, H, Hkv, dk, w->qkv_raw));
+            NNB_TRY(lin_bwd(p, LW.qkv, w->qkv_raw, s.q1, s.s1, T, w->dn, false));
+        } else if (tc_bwd_ok(p, 3 * d, T)) {
             // q, k, v share their input: their gradients go side by side into one (T, 3d) operand, so the
             // backward is one dX GEMM over the concatenated contraction and one dW GEMM for all three
             for (int m = 0; m < 3; ++m)

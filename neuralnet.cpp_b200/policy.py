@@ -21,7 +21,8 @@ LEARNED, ROPE = 0, 1
 
 class _CConfig(C.Structure):
     _fields_ = [(n, C.c_int32) for n in
-                ("n_layer", "d_model", "n_head", "d_ff", "vocab", "ctx", "act", "pos", "value_head", "exact")]
+                ("n_layer", "d_model", "n_head", "d_ff", "vocab", "ctx", "act", "pos", "value_head", "exact",
+                 "sub_ln", "n_head_kv", "tie_embeddings")]
 
 
 @dataclass
@@ -36,15 +37,24 @@ class GptConfig:
     pos: int = LEARNED
     value_head: bool = False
     exact: bool = True
+    sub_ln: bool = False          # RMSNorm between the heads' output and the o projection, and before fc2
+    n_head_kv: int = 0            # grouped-query attention: KV heads (0 = n_head); query head h reads h // (H / Hkv)
+    tie_embeddings: bool = False  # logits = tok_emb . ln_f(x): a dense head without bias, no lm_head tensors
+
+    @property
+    def kv_heads(self) -> int:
+        return self.n_head_kv if self.n_head_kv > 0 else self.n_head
 
     def to_c(self) -> _CConfig:
         return _CConfig(self.n_layer, self.d_model, self.n_head, self.d_ff, self.vocab, self.ctx,
-                        self.act, self.pos, int(self.value_head), int(self.exact))
+                        self.act, self.pos, int(self.value_head), int(self.exact),
+                        int(self.sub_ln), int(self.n_head_kv), int(self.tie_embeddings))
 
     def param_layout(self):
         """(name, offset, shape) of every tensor in the flat parameter buffer, in order."""
         d, F, V = self.d_model, self.d_ff, self.vocab
         F1 = 2 * F if self.act in (SWIGLU, RELU2) else F
+        dkv = self.kv_heads * (d // self.n_head)
         out, o = [], 0
 
         def add(name, *shape):
@@ -58,14 +68,19 @@ class GptConfig:
         for l in range(self.n_layer):
             p = f"blocks.{l}."
             add(p + "ln1.gamma", d)
-            add(p + "attn.q.weight", d, d); add(p + "attn.k.weight", d, d); add(p + "attn.v.weight", d, d)
-            add(p + "attn.q.bias", d); add(p + "attn.k.bias", d); add(p + "attn.v.bias", d)
+            add(p + "attn.q.weight", d, d); add(p + "attn.k.weight", dkv, d); add(p + "attn.v.weight", dkv, d)
+            add(p + "attn.q.bias", d); add(p + "attn.k.bias", dkv); add(p + "attn.v.bias", dkv)
+            if self.sub_ln:
+                add(p + "attn.sub_norm.gamma", d)
             add(p + "attn.o.weight", d, d); add(p + "attn.o.bias", d)
             add(p + "ln2.gamma", d)
             add(p + "ffn.fc1.weight", F1, d); add(p + "ffn.fc1.bias", F1)
+            if self.sub_ln:
+                add(p + "ffn.sub_norm.gamma", F)
             add(p + "ffn.fc2.weight", d, F); add(p + "ffn.fc2.bias", d)
         add("ln_f.gamma", d)
-        add("lm_head.weight", V, d); add("lm_head.bias", V)
+        if not self.tie_embeddings:
+            add("lm_head.weight", V, d); add("lm_head.bias", V)
         if self.value_head:
             add("value_head.weight", 1, d); add("value_head.bias", 1)
         return out, o

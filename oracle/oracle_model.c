@@ -42,7 +42,17 @@ typedef struct {
     int act;        /* 0 = QuickGELU, 1 = SwiGLU */
     int pos;        /* 0 = learned additive, 1 = RoPE */
     int value_head; /* 0 / 1 */
+    /* BitNet 2B4T structure switches (docs/internal/22-bitnet-2b4t-architecture.md):
+     * sub_ln: an RMSNorm inside each sub-layer, before its output projection (attention output of width d before the
+     *   o projection, compute_layer_attention.hpp:482-552,820; activated hidden of width d_ff before fc2,
+     *   compute_layer_feedforward.hpp:37-65,201);
+     * n_head_kv: grouped-query attention, query head h reads KV head h / (n_head / n_head_kv)
+     *   (compute_layer_attention.hpp:444-454); 0 = n_head;
+     * tie: the LM head is the token embedding, logits = E x, no head parameters (compute_layer_gpt.hpp:258-264). */
+    int sub_ln, n_head_kv, tie;
 } orc_gpt_cfg;
+
+static int cfg_hkv(const orc_gpt_cfg* c) { return c->n_head_kv > 0 ? c->n_head_kv : c->n_head; }
 
 typedef struct {
     int in, out;
@@ -57,6 +67,8 @@ typedef struct {
     orc_lin q, k, v, o;
     const float* ln2_g;
     orc_lin fc1, fc2;
+    const float* attn_sub_g; /* (d), sub_ln only */
+    const float* ffn_sub_g;  /* (d_ff), sub_ln only */
 } orc_layer;
 
 typedef struct {
@@ -151,8 +163,11 @@ ORC_API size_t orc_gpt_param_count(const orc_gpt_cfg* c)
     const size_t F1 = c->act >= 1 ? 2 * F : F;
     size_t n = V * d;
     if (c->pos == 0) n += (size_t)c->ctx * d;
-    n += (size_t)c->n_layer * (d + 3 * d * d + 3 * d + d * d + d + d + F1 * d + F1 + d * F + d);
-    n += d + V * d + V;
+    const size_t dkv = (size_t)cfg_hkv(c) * (d / c->n_head);
+    n += (size_t)c->n_layer * (d + (d + 2 * dkv) * d + (d + 2 * dkv) + d * d + d + d + F1 * d + F1 + d * F + d);
+    if (c->sub_ln) n += (size_t)c->n_layer * (d + F);
+    n += d;
+    if (!c->tie) n += V * d + V;
     if (c->value_head) n += d + 1;
     return n;
 }
@@ -170,11 +185,13 @@ ORC_API orc_gpt* orc_gpt_create(const orc_gpt_cfg* c, const float* params)
     for (int l = 0; l < c->n_layer; ++l) {
         orc_layer* L = &m->layers[l];
         L->ln1_g = params + o; o += d;
-        const size_t wq = o, wk = o + d * d, wv = o + 2 * d * d; o += 3 * d * d;
-        const size_t bq = o, bk = o + d, bv = o + 2 * d; o += 3 * d;
+        const size_t dkv = (size_t)cfg_hkv(c) * (d / c->n_head);
+        const size_t wq = o, wk = o + d * d, wv = wk + dkv * d; o += (d + 2 * dkv) * d;
+        const size_t bq = o, bk = o + d, bv = bk + dkv; o += d + 2 * dkv;
         lin_setup(&L->q, params, wq, bq, (int)d, (int)d);
-        lin_setup(&L->k, params, wk, bk, (int)d, (int)d);
-        lin_setup(&L->v, params, wv, bv, (int)d, (int)d);
+        lin_setup(&L->k, params, wk, bk, (int)d, (int)dkv);
+        lin_setup(&L->v, params, wv, bv, (int)d, (int)dkv);
+        if (c->sub_ln) { L->attn_sub_g = params + o; o += d; }
         const size_t wo = o; o += d * d;
         const size_t bo = o; o += d;
         lin_setup(&L->o, params, wo, bo, (int)d, (int)d);
@@ -182,14 +199,17 @@ ORC_API orc_gpt* orc_gpt_create(const orc_gpt_cfg* c, const float* params)
         const size_t w1 = o; o += F1 * d;
         const size_t b1 = o; o += F1;
         lin_setup(&L->fc1, params, w1, b1, (int)d, (int)F1);
+        if (c->sub_ln) { L->ffn_sub_g = params + o; o += F; }
         const size_t w2 = o; o += d * F;
         const size_t b2 = o; o += d;
         lin_setup(&L->fc2, params, w2, b2, (int)F, (int)d);
     }
     m->lnf_g = params + o; o += d;
-    const size_t hw = o; o += V * d;
-    const size_t hb = o; o += V;
-    lin_setup(&m->head, params, hw, hb, (int)d, (int)V);
+    if (!c->tie) {
+        const size_t hw = o; o += V * d;
+        const size_t hb = o; o += V;
+        lin_setup(&m->head, params, hw, hb, (int)d, (int)V);
+    }
     if (c->value_head) { m->value_w = params + o; o += d; m->value_b = params + o; o += 1; }
     m->n_params = o;
     if (c->pos == 1) {
@@ -217,7 +237,7 @@ ORC_API void orc_gpt_destroy(orc_gpt* m)
         lin_free(&L->q); lin_free(&L->k); lin_free(&L->v); lin_free(&L->o);
         lin_free(&L->fc1); lin_free(&L->fc2);
     }
-    lin_free(&m->head);
+    if (!m->cfg.tie) lin_free(&m->head);
     free(m->layers); free(m->rope_cos); free(m->rope_sin);
     free(m);
 }
@@ -288,9 +308,9 @@ ORC_API void orc_gpt_linear_forward(const orc_gpt* m, int layer, int which, cons
     free(q);
 }
 
-static void rope_apply(const orc_gpt* m, float* x /* (H*dk) */, int pos)
+static void rope_apply(const orc_gpt* m, float* x /* (H*dk) */, int pos, int H)
 {
-    const int H = m->cfg.n_head, dk = m->cfg.d_model / H, half = dk / 2;
+    const int dk = m->cfg.d_model / m->cfg.n_head, half = dk / 2;
     const float* c = m->rope_cos + (size_t)pos * half;
     const float* s = m->rope_sin + (size_t)pos * half;
     for (int h = 0; h < H; ++h) {
@@ -345,7 +365,7 @@ static void state_free(orc_state* s)
 static void forward_step(const orc_gpt* m, orc_state* st, int token, int cur_len, float* logits)
 {
     const orc_gpt_cfg* c = &m->cfg;
-    const int d = c->d_model, H = c->n_head, dk = d / H, F = c->d_ff;
+    const int d = c->d_model, H = c->n_head, dk = d / H, F = c->d_ff, Hkv = cfg_hkv(c);
     const float scale = 1.0f / sqrtf((float)dk);
     float s;
     for (int i = 0; i < d; ++i) {
@@ -362,15 +382,17 @@ static void forward_step(const orc_gpt* m, orc_state* st, int token, int cur_len
         lin_forward_q(&L->q, st->q8, s, st->qv);
         lin_forward_q(&L->k, st->q8, s, st->kv);
         lin_forward_q(&L->v, st->q8, s, st->vv);
-        if (c->pos == 1) { rope_apply(m, st->qv, cur_len); rope_apply(m, st->kv, cur_len); }
-        memcpy(kc + (size_t)cur_len * d, st->kv, sizeof(float) * d);
-        memcpy(vc + (size_t)cur_len * d, st->vv, sizeof(float) * d);
+        if (c->pos == 1) { rope_apply(m, st->qv, cur_len, H); rope_apply(m, st->kv, cur_len, Hkv); }
+        /* the cache holds the n_head_kv heads; query head h reads KV head h / (H / Hkv) */
+        memcpy(kc + (size_t)cur_len * d, st->kv, sizeof(float) * (size_t)Hkv * dk);
+        memcpy(vc + (size_t)cur_len * d, st->vv, sizeof(float) * (size_t)Hkv * dk);
         const int n_keys = cur_len + 1;
         for (int h = 0; h < H; ++h) {
             const float* qh = st->qv + (size_t)h * dk;
+            const int hk = h / (H / Hkv);
             float mx = -INFINITY;
             for (int j = 0; j < n_keys; ++j) {
-                const float* kj = kc + (size_t)j * d + (size_t)h * dk;
+                const float* kj = kc + (size_t)j * d + (size_t)hk * dk;
                 double acc = 0.0;
                 for (int i = 0; i < dk; ++i) acc += (double)qh[i] * (double)kj[i];
                 const float sc = (float)acc * scale;
@@ -384,9 +406,13 @@ static void forward_step(const orc_gpt* m, orc_state* st, int token, int cur_len
             for (int i = 0; i < dk; ++i) {
                 double acc = 0.0;
                 for (int j = 0; j < n_keys; ++j)
-                    acc += (double)st->sc[j] * (double)vc[(size_t)j * d + (size_t)h * dk + i];
+                    acc += (double)st->sc[j] * (double)vc[(size_t)j * d + (size_t)hk * dk + i];
                 st->att[(size_t)h * dk + i] = (float)acc;
             }
+        }
+        if (c->sub_ln) {  /* SubLN: the heads' output is normalised before the output projection */
+            orc_rmsnorm(st->att, L->attn_sub_g, d, 1e-5f, st->n);
+            memcpy(st->att, st->n, sizeof(float) * (size_t)d);
         }
         quantise_token(st->att, d, st->q8, &s);
         lin_forward_q(&L->o, st->q8, s, st->tmp);
@@ -412,14 +438,28 @@ static void forward_step(const orc_gpt* m, orc_state* st, int token, int cur_len
                 st->h2[i] = gv * (1.0f / (1.0f + orc_expf(-gv))) * uv;
             }
         }
+        if (c->sub_ln) {  /* SubLN: the activated hidden is normalised before fc2 */
+            orc_rmsnorm(st->h2, L->ffn_sub_g, F, 1e-5f, st->h1);
+            memcpy(st->h2, st->h1, sizeof(float) * (size_t)F);
+        }
         quantise_token(st->h2, F, st->q8, &s);
         lin_forward_q(&L->fc2, st->q8, s, st->tmp);
         for (int i = 0; i < d; ++i) st->x[i] = st->x[i] + st->tmp[i];
     }
     if (logits) {
         orc_rmsnorm(st->x, m->lnf_g, d, 1e-5f, st->n);
-        quantise_token(st->n, d, st->q8, &s);
-        lin_forward_q(&m->head, st->q8, s, logits);
+        if (c->tie) {
+            /* tied embeddings: logits = E . ln_f(x), a dense f32 product with the embedding table, no bias */
+            for (int v = 0; v < c->vocab; ++v) {
+                const float* ev = m->tok_emb + (size_t)v * d;
+                double acc = 0.0;
+                for (int i = 0; i < d; ++i) acc += (double)ev[i] * (double)st->n[i];
+                logits[v] = (float)acc;
+            }
+        } else {
+            quantise_token(st->n, d, st->q8, &s);
+            lin_forward_q(&m->head, st->q8, s, logits);
+        }
     }
 }
 

@@ -184,6 +184,12 @@ class OracleTrainer:
         d, H = cfg.d_model, cfg.n_head
         dk = d // H
         F = cfg.d_ff
+        # grouped-query attention (compute_layer_attention.hpp:444-454): Hkv key/value heads, query head h reads
+        # KV head h // (H / Hkv); the reference expands K and V to H heads (gather_rows) and runs plain MHA
+        Hkv = getattr(cfg, "n_head_kv", 0) or H
+        rep = H // Hkv
+        sub_ln = bool(getattr(cfg, "sub_ln", False))
+        tie = bool(getattr(cfg, "tie_embeddings", False))
         self.tokens, self.P = tokens, prompt_len
         sm = self.smooth
         R = (lambda a: np.asarray(a, np.float64)) if sm else (lambda a: np.asarray(a).astype(F32))  # the engine's f32 rounding
@@ -204,10 +210,12 @@ class OracleTrainer:
             n1, c["n1"] = rmsnorm_fwd(x, p[pre + "ln1.gamma"], sm)
             flat1 = n1.reshape(n * S, d)
             q = self.lin[pre + "attn.q"].forward(flat1).reshape(n, S, H, dk)
-            k = self.lin[pre + "attn.k"].forward(flat1).reshape(n, S, H, dk)
-            v = self.lin[pre + "attn.v"].forward(flat1).astype(np.float64).reshape(n, S, H, dk)
+            k = self.lin[pre + "attn.k"].forward(flat1).reshape(n, S, Hkv, dk)
+            v = self.lin[pre + "attn.v"].forward(flat1).astype(np.float64).reshape(n, S, Hkv, dk)
             if cfg.pos == 1:
                 q, k = rope_apply(q, cos, sin), rope_apply(k, cos, sin)
+            if rep > 1:
+                k, v = np.repeat(k, rep, axis=2), np.repeat(v, rep, axis=2)
             # the reference folds the scale into Q after RoPE (one f32 multiply)
             qs = R(q * (1.0 / np.sqrt(np.float64(dk)) if sm else F32(1.0 / np.sqrt(F32(dk))))).astype(np.float64)
             k = k.astype(np.float64)
@@ -219,6 +227,8 @@ class OracleTrainer:
             att = np.einsum("bhij,bjhd->bihd", w, v)
             c.update(qs=qs, k=k, v=v, w=w)
             a = R(att.reshape(n * S, d))
+            if sub_ln:  # SubLN (compute_layer_attention.hpp:482-489,820-826): heads' output -> norm -> o projection
+                a, c["sn_a"] = rmsnorm_fwd(a, p[pre + "attn.sub_norm.gamma"], sm)
             o = self.lin[pre + "attn.o"].forward(a)
             x_mid = R(x + o.reshape(n, S, d))
             c["x_mid"] = x_mid
@@ -236,7 +246,10 @@ class OracleTrainer:
                 g, u = h1[:, :F], h1[:, F:]
                 sg = R(one / R(one + ex(-g)))
                 act = R(R(g * sg) * u)
-            f2 = self.lin[pre + "ffn.fc2"].forward(R(act))
+            act = R(act)
+            if sub_ln:  # SubLN (compute_layer_feedforward.hpp:37-47,201-206): activated hidden -> norm -> fc2
+                act, c["sn_f"] = rmsnorm_fwd(act, p[pre + "ffn.sub_norm.gamma"], sm)
+            f2 = self.lin[pre + "ffn.fc2"].forward(act)
             x = R(x_mid + f2.reshape(n, S, d))
             self.cache.append(c)
         self.x_final = x
@@ -244,7 +257,13 @@ class OracleTrainer:
         xd = x[:, prompt_len - 1:S - 1].reshape(n * G, d)
         hn, self.cf = rmsnorm_fwd(xd, p["ln_f.gamma"], sm)
         self.hn = hn
-        logits = self.lin["lm_head"].forward(hn).astype(np.float64)
+        if tie:
+            # tied embeddings (compute_layer_gpt.hpp:286-297): logits = tok_emb . hn, a dense product, no bias
+            logits = hn.astype(np.float64) @ p["tok_emb"].astype(np.float64).T
+            if not sm:
+                logits = logits.astype(F32).astype(np.float64)
+        else:
+            logits = self.lin["lm_head"].forward(hn).astype(np.float64)
         self.logits = logits
         actions = tokens[:, prompt_len:].reshape(-1)
         self.actions = actions
@@ -324,10 +343,18 @@ class OracleTrainer:
         if up_ent is not None:
             ent = -(prob * self.logp_all).sum(1)
             dlogits += -prob * (self.logp_all + ent[:, None]) * up_ent[:, None]
-        head = self.lin["lm_head"]
-        dhn = head.backward(dlogits)
-        grads["lm_head.weight"] += head.dw
-        grads["lm_head.bias"] += head.db
+        Hkv = getattr(cfg, "n_head_kv", 0) or H
+        rep = H // Hkv
+        sub_ln = bool(getattr(cfg, "sub_ln", False))
+        if getattr(cfg, "tie_embeddings", False):
+            # dX = g . E ; dE += g^T . hn, into the same gradient as the embedding lookup (compute_layer_gpt.hpp:556-575)
+            dhn = dlogits @ p["tok_emb"].astype(np.float64)
+            grads["tok_emb"] += dlogits.T @ np.asarray(self.hn, np.float64)
+        else:
+            head = self.lin["lm_head"]
+            dhn = head.backward(dlogits)
+            grads["lm_head.weight"] += head.dw
+            grads["lm_head.bias"] += head.db
         if cfg.value_head and dvalue is not None:
             w = p["value_head.weight"].astype(np.float64).reshape(-1)
             dhn = dhn + dvalue[:, None] * w[None, :]
@@ -348,6 +375,9 @@ class OracleTrainer:
             da = fc2.backward(g.reshape(n * S, d))
             grads[pre + "ffn.fc2.weight"] += fc2.dw
             grads[pre + "ffn.fc2.bias"] += fc2.db
+            if sub_ln:
+                da, dg = rmsnorm_bwd(da, p[pre + "ffn.sub_norm.gamma"].astype(np.float64), c["sn_f"])
+                grads[pre + "ffn.sub_norm.gamma"] += dg
             h = c["h1"].astype(np.float64)
             if cfg.act == 0:
                 bx = h * 1.702
@@ -368,9 +398,13 @@ class OracleTrainer:
             grads[pre + "ln2.gamma"] += dg
             g2 = g + dx
             lo = self.lin[pre + "attn.o"]
-            datt = lo.backward(g2.reshape(n * S, d)).reshape(n, S, H, dk)
+            datt = lo.backward(g2.reshape(n * S, d))
             grads[pre + "attn.o.weight"] += lo.dw
             grads[pre + "attn.o.bias"] += lo.db
+            if sub_ln:
+                datt, dg = rmsnorm_bwd(datt, p[pre + "attn.sub_norm.gamma"].astype(np.float64), c["sn_a"])
+                grads[pre + "attn.sub_norm.gamma"] += dg
+            datt = datt.reshape(n, S, H, dk)
             w, qs, k, v = c["w"], c["qs"], c["k"], c["v"]
             dv = np.einsum("bhij,bihd->bjhd", w, datt)
             dp = np.einsum("bihd,bjhd->bhij", datt, v)
@@ -378,12 +412,15 @@ class OracleTrainer:
             xs = w * (dp - r)
             dq = np.einsum("bhij,bjhd->bihd", xs, k) * scale
             dk_ = np.einsum("bhij,bihd->bjhd", xs, qs)
+            if rep > 1:  # the replicas of a KV head sum (scatter_add_rows of the reference)
+                dk_ = dk_.reshape(n, S, Hkv, rep, dk).sum(3)
+                dv = dv.reshape(n, S, Hkv, rep, dk).sum(3)
             if cfg.pos == 1:
                 dq, dk_ = rope_apply(dq, cos, sin, -1.0), rope_apply(dk_, cos, sin, -1.0)
             dn1 = 0
             for nm, dd in (("attn.q", dq), ("attn.k", dk_), ("attn.v", dv)):
                 li = self.lin[pre + nm]
-                dn1 = dn1 + li.backward(dd.reshape(n * S, d))
+                dn1 = dn1 + li.backward(dd.reshape(n * S, -1))
                 grads[pre + nm + ".weight"] += li.dw
                 grads[pre + nm + ".bias"] += li.db
             dx, dg = rmsnorm_bwd(dn1.reshape(n, S, d), p[pre + "ln1.gamma"].astype(np.float64), c["n1"])

@@ -181,7 +181,8 @@ class Oracle:
 # ------------------------------------------------------------------ GPT model (oracle_model.c)
 class _OrcCfg(C.Structure):
     _fields_ = [(n, C.c_int) for n in
-                ("n_layer", "d_model", "n_head", "d_ff", "vocab", "ctx", "act", "pos", "value_head")]
+                ("n_layer", "d_model", "n_head", "d_ff", "vocab", "ctx", "act", "pos", "value_head",
+                 "sub_ln", "n_head_kv", "tie")]
 
 
 class OracleGpt:
@@ -193,7 +194,8 @@ class OracleGpt:
         self.L = L
         self.cfg = cfg
         self._c = _OrcCfg(cfg.n_layer, cfg.d_model, cfg.n_head, cfg.d_ff, cfg.vocab, cfg.ctx, cfg.act, cfg.pos,
-                          int(cfg.value_head))
+                          int(cfg.value_head), int(getattr(cfg, "sub_ln", False)),
+                          int(getattr(cfg, "n_head_kv", 0)), int(getattr(cfg, "tie_embeddings", False)))
         L.orc_gpt_param_count.restype = _SZ
         L.orc_gpt_param_count.argtypes = [C.POINTER(_OrcCfg)]
         L.orc_gpt_create.restype = C.c_void_p

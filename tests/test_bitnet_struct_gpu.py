@@ -1,0 +1,324 @@
+"""The structure switches of BitNet b1.58 2B4T on the CUDA path: SubLN, grouped-query attention, tied embeddings (and the
+ReLU2GLU feed-forward with them).  Against the CPU restatements, and restating the reference's own checks of these
+switches (src/bitnet_struct_test.cpp): parameter counts [1][10], n_head_kv == n_head is plain multi-head attention bit for
+bit [7], grouped-query attention equals multi-head attention with block-replicated KV weights and its K/V weight gradient is
+the sum over each group [8], the tied head's two gradient paths add into one tensor [10], model files remember the
+switches [4][9][11]."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, os.path.join(ROOT, "oracle"))
+import oracle_train as ot  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+REL = 1e-3
+
+SWITCHES = [dict(sub_ln=True), dict(n_head=4, n_head_kv=2), dict(n_head=4, n_head_kv=1), dict(tie_embeddings=True),
+            dict(sub_ln=True, n_head=4, n_head_kv=2, tie_embeddings=True, act=2)]
+IDS = ["subln", "gqa2", "mqa", "tied", "all"]
+
+
+def dev(a, eng, dt=np.float32):
+    return torch.from_numpy(np.ascontiguousarray(a, dt)).to(eng.device)
+
+
+def _cfg(pkg, extra, **over):
+    kw = dict(n_layer=2, d_model=128, n_head=2, d_ff=256, vocab=211, ctx=40, act=1, pos=1)
+    kw.update(extra)
+    kw.update(over)
+    return pkg.GptConfig(**kw)
+
+
+def _init(cfg, seed):
+    """Seeded parameters with norm gains away from 1, so that a missing or misplaced gain shows."""
+    flat = cfg.init_params(seed, bias_std=0.01)
+    rng = np.random.default_rng(seed + 100)
+    for name, off, shape in cfg.param_layout()[0]:
+        if name.endswith("gamma"):
+            n = int(np.prod(shape))
+            flat[off:off + n] = 1.0 + rng.normal(0, 0.1, n).astype(np.float32)
+    return flat
+
+
+def test_parameter_counts_follow_the_switches(pkg, eng):
+    base = _cfg(pkg, {})
+    n0 = base.param_layout()[1]
+    L, d, F, V = base.n_layer, base.d_model, base.d_ff, base.vocab
+    assert _cfg(pkg, dict(sub_ln=True)).param_layout()[1] == n0 + L * (d + F)
+    assert n0 - _cfg(pkg, dict(tie_embeddings=True)).param_layout()[1] == V * d + V
+    dk = d // 4
+    n_mha = _cfg(pkg, dict(n_head=4)).param_layout()[1]
+    assert n_mha - _cfg(pkg, dict(n_head=4, n_head_kv=1)).param_layout()[1] == L * 2 * (3 * dk) * (d + 1)
+    for extra in SWITCHES:
+        cfg = _cfg(pkg, extra)
+        pol = pkg.Policy(eng, cfg)
+        layout, n = cfg.param_layout()
+        assert pol.n_params == n
+        got = pol.tensors()
+        assert [g[0] for g in got] == [l[0] for l in layout] and [g[1] for g in got] == [l[1] for l in layout]
+
+
+@pytest.mark.parametrize("extra", SWITCHES, ids=IDS)
+def test_greedy_rollout_matches_the_restatement(pkg, eng, extra):
+    from oracle_binding import OracleGpt
+
+    cfg = _cfg(pkg, extra)
+    flat = _init(cfg, 1)
+    pol = pkg.Policy(eng, cfg)
+    pol.upload_params(flat)
+    m = OracleGpt(cfg, flat)
+    prompts = np.random.default_rng(3).integers(0, cfg.vocab, (5, 7)).astype(np.int32)
+    tok_ref, lp_ref, lg_ref = m.rollout(prompts, 12, 0.0, 0, seed=0, want_logits=True)
+    tok, lp, lg = pol.rollout(torch.from_numpy(prompts).to(eng.device), 12, temperature=0.0, want_logits=True)
+    torch.cuda.synchronize()
+    if cfg.tie_embeddings:
+        # the dense head sums d_model products in f64 in another order than the restatement: equal up to the last f32 bit
+        assert np.abs(lg.cpu().numpy() - lg_ref).max() <= 2e-7 * np.abs(lg_ref).max()
+    else:
+        assert np.array_equal(lg.cpu().numpy().view(np.uint32), lg_ref.view(np.uint32)), "logits differ bitwise"
+    assert np.array_equal(tok.cpu().numpy(), tok_ref)
+    assert np.abs(lp.cpu().numpy() - lp_ref).max() <= 1e-3 * np.abs(lp_ref).max()
+
+
+def test_sampled_grouped_rollout_with_all_switches(pkg, eng):
+    """top-k sampling and shared prompt prefixes (4 sequences per prompt) on the full structure"""
+    from oracle_binding import OracleGpt
+
+    cfg = _cfg(pkg, SWITCHES[-1])
+    flat = _init(cfg, 2)
+    pol = pkg.Policy(eng, cfg)
+    pol.upload_params(flat)
+    m = OracleGpt(cfg, flat)
+    prompts = np.repeat(np.random.default_rng(5).integers(0, cfg.vocab, (2, 6)).astype(np.int32), 4, axis=0)
+    tok_ref, lp_ref, _ = m.rollout(prompts, 10, 0.9, 20, seed=7)
+    tok, lp, _ = pol.rollout(torch.from_numpy(prompts).to(eng.device), 10, temperature=0.9, top_k=20, seed=7, group_size=4)
+    assert np.array_equal(tok.cpu().numpy(), tok_ref)
+    assert np.abs(lp.cpu().numpy() - lp_ref).max() <= 1e-3 * np.abs(lp_ref).max()
+
+
+def _objective_case(cfg, tr, tokens, P, value_head):
+    n, S = tokens.shape
+    G = S - P
+    rng = np.random.default_rng(5)
+    lp_ref, ent_ref, val_ref = tr.forward(tokens, P)
+    old = lp_ref + rng.normal(0, 0.3, (n, G))
+    ref = lp_ref + rng.normal(0, 0.1, (n, G))
+    adv = rng.normal(0, 1, (n, G))
+    mask = (rng.uniform(size=(n, G)) < 0.8).astype(np.float64)
+    kw = dict(clip_eps=0.2, kl_coef=0.04, entropy_coef=0.01)
+    ret = oldv = None
+    if value_head:
+        ret = val_ref + rng.normal(0, 0.5, (n, G))
+        oldv = val_ref + rng.normal(0, 0.3, (n, G))
+        kw.update(value_coef=0.5, value_clip_eps=0.2)
+    rep_ref, up_lp, up_ent, dv = tr.objective(lp_ref, ent_ref, mask, old, adv, ref, val_ref, ret, oldv, **kw)
+    return lp_ref, ent_ref, old, ref, adv, mask, ret, oldv, kw, rep_ref, tr.backward(up_lp, up_ent, dv)
+
+
+@pytest.mark.parametrize("extra", SWITCHES, ids=IDS)
+def test_train_step_gradients_match_the_restatement(pkg, eng, extra):
+    cfg = _cfg(pkg, extra, d_model=64, d_ff=128, vocab=97, ctx=16, value_head=True)
+    flat = _init(cfg, 1)
+    off_vw = {nm: off for nm, off, _ in cfg.param_layout()[0]}["value_head.weight"]
+    flat[off_vw:off_vw + cfg.d_model] = np.random.default_rng(9).normal(0, 0.1, cfg.d_model)
+    pol = pkg.Policy(eng, cfg)
+    pol.upload_params(flat)
+    tr = ot.OracleTrainer(cfg, flat)
+    tokens = np.random.default_rng(2).integers(0, cfg.vocab, (3, 12)).astype(np.int32)
+    P = 4
+    lp_ref, ent_ref, old, ref, adv, mask, ret, oldv, kw, rep_ref, g_ref = _objective_case(cfg, tr, tokens, P, True)
+    lp, ent, _ = pol.logprobs(dev(tokens, eng, np.int32), P, want_entropy=True)
+    assert np.abs(lp.cpu().numpy() - lp_ref).max() <= REL * np.abs(lp_ref).max()
+    assert np.abs(ent.cpu().numpy() - ent_ref).max() <= REL * np.abs(ent_ref).max()
+    pol.zero_grad()
+    rep = pol.train_step(dev(tokens, eng, np.int32), P, dev(mask, eng), old_logp=dev(old, eng), advantage=dev(adv, eng),
+                         ref_logp=dev(ref, eng), returns=dev(ret, eng), old_value=dev(oldv, eng), **kw).cpu().numpy()
+    for i, nm in enumerate(["policy_loss", "ratio_mean", "approx_kl", "clip_fraction", "kl_loss", "entropy_loss"]):
+        assert abs(rep[i] - rep_ref[nm]) <= REL * max(abs(rep_ref[nm]), 1e-2), nm
+    g = pol.grads_view().cpu().numpy().astype(np.float64)
+    for name, off, shape in cfg.param_layout()[0]:
+        size = int(np.prod(shape))
+        a, r = g[off:off + size], g_ref[off:off + size]
+        scale = np.abs(r).max()
+        if scale < 1e-12:
+            assert np.abs(a).max() < 1e-9, name
+            continue
+        assert np.abs(a - r).max() / scale <= REL, f"{name}: rel err {np.abs(a - r).max() / scale:.2e}"
+        if "sub_norm" in name:
+            assert scale > 0, f"{name} takes part in the backward pass"
+
+
+def _grads_and_logp(pkg, eng, cfg, flat, tokens, P):
+    pol = pkg.Policy(eng, cfg)
+    pol.upload_params(flat)
+    t = dev(tokens, eng, np.int32)
+    lp, _, _ = pol.logprobs(t, P)
+    n, G = lp.shape
+    rng = np.random.default_rng(11)
+    old = lp + dev(rng.normal(0, 0.2, (n, G)), eng)
+    adv = dev(rng.normal(0, 1, (n, G)), eng)
+    pol.zero_grad()
+    pol.train_step(t, P, dev(np.ones((n, G)), eng), old_logp=old, advantage=adv)
+    eng.check_device_errors()
+    return lp.cpu().numpy(), pol.grads_view().cpu().numpy().astype(np.float64)
+
+
+@pytest.mark.parametrize("exact", [True, False])
+def test_gqa_with_as_many_kv_heads_as_heads_is_multi_head_attention_bit_for_bit(pkg, eng, exact):
+    a = _cfg(pkg, dict(n_head=4), exact=exact)
+    b = _cfg(pkg, dict(n_head=4, n_head_kv=4), exact=exact)
+    flat = _init(a, 3)
+    tokens = np.random.default_rng(1).integers(0, a.vocab, (3, 20)).astype(np.int32)
+    lp_a, g_a = _grads_and_logp(pkg, eng, a, flat, tokens, 6)
+    lp_b, g_b = _grads_and_logp(pkg, eng, b, flat, tokens, 6)
+    assert np.array_equal(lp_a, lp_b)
+    # (norm-gain gradients are summed with atomics: equal up to the order of a few f32 additions)
+    assert np.abs(g_a - g_b).max() <= 1e-6 * np.abs(g_a).max()
+
+
+def test_gqa_equals_multi_head_attention_with_block_replicated_kv_weights(pkg, eng):
+    """query head h reads KV head h // (H / Hkv): replicating each KV head's weight rows H / Hkv times gives the same
+    forward (a row's ternarisation depends on that row only), and the K/V weight and bias gradients are the sums over a group"""
+    H, Hkv = 4, 2
+    rep = H // Hkv
+    g_cfg = _cfg(pkg, dict(n_head=H, n_head_kv=Hkv))
+    m_cfg = _cfg(pkg, dict(n_head=H))
+    dk = g_cfg.d_model // H
+    flat_g = _init(g_cfg, 4)
+    lay_g = {nm: (off, shape) for nm, off, shape in g_cfg.param_layout()[0]}
+    lay_m = m_cfg.param_layout()[0]
+    flat_m = np.zeros(m_cfg.param_layout()[1], np.float32)
+
+    def expand(a):  # (Hkv*dk, ...) -> (H*dk, ...), block map
+        return np.repeat(a.reshape(Hkv, dk, -1), rep, axis=0).reshape(H * dk, -1)
+
+    for name, off, shape in lay_m:
+        o, s = lay_g[name]
+        src = flat_g[o:o + int(np.prod(s))].reshape(s)
+        if ".attn.k." in name or ".attn.v." in name:
+            src = expand(src)
+        flat_m[off:off + int(np.prod(shape))] = src.reshape(-1)
+    tokens = np.random.default_rng(1).integers(0, g_cfg.vocab, (3, 20)).astype(np.int32)
+    lp_g, gr_g = _grads_and_logp(pkg, eng, g_cfg, flat_g, tokens, 6)
+    lp_m, gr_m = _grads_and_logp(pkg, eng, m_cfg, flat_m, tokens, 6)
+    assert np.array_equal(lp_g, lp_m)
+    scale = np.abs(gr_m).max()
+    for name, off, shape in lay_m:
+        o, s = lay_g[name]
+        gm = gr_m[off:off + int(np.prod(shape))].reshape(shape if len(shape) > 1 else (shape[0], 1))
+        gg = gr_g[o:o + int(np.prod(s))].reshape(s if len(s) > 1 else (s[0], 1))
+        if ".attn.k." in name or ".attn.v." in name:
+            gm = gm.reshape(Hkv, rep, dk, -1).sum(1).reshape(Hkv * dk, -1)
+        assert np.abs(gm - gg).max() <= 1e-5 * scale, name
+
+
+def test_tied_head_adds_both_gradient_paths_into_the_embedding(pkg, eng):
+    """d tok_emb = (embedding lookup's scatter) + (head's g^T . x): with the head's path alone removed (zero upstream on the
+    decisions) the lookup path remains; with both, the restatement's sum"""
+    cfg = _cfg(pkg, dict(tie_embeddings=True), d_model=64, d_ff=128, vocab=97, ctx=16)
+    flat = _init(cfg, 5)
+    tr = ot.OracleTrainer(cfg, flat)
+    tokens = np.random.default_rng(2).integers(0, cfg.vocab, (3, 12)).astype(np.int32)
+    lp_ref, ent_ref, _ = tr.forward(tokens, 4)
+    rng = np.random.default_rng(6)
+    old, adv = lp_ref + rng.normal(0, 0.2, lp_ref.shape), rng.normal(0, 1, lp_ref.shape)
+    mask = np.ones_like(lp_ref)
+    _, up_lp, up_ent, _ = tr.objective(lp_ref, ent_ref, mask, old, adv)
+    g_ref = tr.backward(up_lp, up_ent)
+    pol = pkg.Policy(eng, cfg)
+    pol.upload_params(flat)
+    pol.zero_grad()
+    pol.train_step(dev(tokens, eng, np.int32), 4, dev(mask, eng), old_logp=dev(old, eng), advantage=dev(adv, eng))
+    g = pol.grads_view().cpu().numpy().astype(np.float64)
+    n_emb = cfg.vocab * cfg.d_model
+    assert np.abs(g[:n_emb] - g_ref[:n_emb]).max() <= REL * np.abs(g_ref[:n_emb]).max()
+    # rows of tokens that never occur as inputs still receive the head's gradient
+    unused = sorted(set(range(cfg.vocab)) - set(tokens.reshape(-1).tolist()))
+    assert unused and np.abs(g[:n_emb].reshape(cfg.vocab, -1)[unused]).max() > 0
+
+
+@pytest.mark.parametrize("extra", SWITCHES, ids=IDS)
+def test_fast_mode_is_close_to_the_exact_mode(pkg, eng, extra):
+    """tcgen05 paths: the merged q|k|v matrix of d + 2 dkv rows, the tied head's bf16 product (forward and both backward
+    GEMMs, 128 decisions), the SubLN recomputation in the backward"""
+    from neuralnet_cpp_b200.parity import compare_gradients
+
+    kw = dict(vocab=536, ctx=48)
+    cfg_e, cfg_f = _cfg(pkg, extra, exact=True, **kw), _cfg(pkg, extra, exact=False, **kw)
+    flat = cfg_e.init_params(4, linear_std=0.05, bias_std=0.01)
+    pe, pf = pkg.Policy(eng, cfg_e), pkg.Policy(eng, cfg_f)
+    pe.upload_params(flat)
+    pf.upload_params(flat)
+    rng = np.random.default_rng(8)
+    n, S, P = 4, 40, 8
+    tokens = dev(rng.integers(0, 536, (n, S)), eng, np.int32)
+    lp, ent, _ = pe.logprobs(tokens, P, want_entropy=True)
+    lp_f, ent_f, _ = pf.logprobs(tokens, P, want_entropy=True)
+    assert (lp - lp_f).abs().max().item() <= 3e-2 * lp.abs().max().item()
+    assert (ent - ent_f).abs().max().item() <= 3e-2 * ent.abs().max().item()
+    old = lp + dev(rng.normal(0, 0.2, (n, S - P)), eng)
+    adv = dev(rng.normal(0, 1, (n, S - P)), eng)
+    mask = dev(np.ones((n, S - P)), eng)
+    for pol in (pe, pf):
+        pol.zero_grad()
+        pol.train_step(tokens, P, mask, old_logp=old, advantage=adv, entropy_coef=0.01)
+    eng.check_device_errors()
+    stats = compare_gradients(cfg_e, pf.grads_view().cpu().numpy(), pe.grads_view().cpu().numpy())
+    assert stats["grad_rel_rms"] <= 0.2, stats
+    # the rollout's recorded log-probs equal the teacher-forced ones in the fast mode too (ratio = 1 at the first epoch),
+    # with few sequences (CUDA-core head) and with 64 (tensor-core head)
+    for n_seq in (6, 64):
+        prompts = dev(rng.integers(0, 536, (n_seq, 5)), eng, np.int32)
+        toks, old_lp, _ = pf.rollout(prompts, 10, temperature=1.0, top_k=20, seed=1)
+        lp2, _, _ = pf.logprobs(toks, 5)
+        assert (lp2 - old_lp).abs().max().item() <= 2e-2 * max(old_lp.abs().max().item(), 1.0)
+    eng.check_device_errors()
+
+
+def test_optimizer_step_refreshes_the_tied_head(pkg, eng):
+    """after AdamW moves tok_emb the fast mode's bf16 head copy follows: logits change and stay close to the exact mode's"""
+    extra = SWITCHES[-1]
+    cfg_e, cfg_f = _cfg(pkg, extra, exact=True, vocab=536), _cfg(pkg, extra, exact=False, vocab=536)
+    flat = _init(cfg_e, 7)
+    pols = []
+    rng = np.random.default_rng(3)
+    tokens = dev(rng.integers(0, 536, (4, 30)), eng, np.int32)
+    for cfg in (cfg_e, cfg_f):
+        pol = pkg.Policy(eng, cfg)
+        pol.upload_params(flat)
+        lp0, _, _ = pol.logprobs(tokens, 6)
+        adv = dev(np.random.default_rng(4).normal(0, 1, tuple(lp0.shape)), eng)
+        pol.zero_grad()
+        pol.train_step(tokens, 6, torch.ones_like(lp0), old_logp=lp0.clone(), advantage=adv)
+        pol.optimizer_step(lr=1e-2)
+        lp1, _, _ = pol.logprobs(tokens, 6)
+        assert (lp1 - lp0).abs().max().item() > 1e-3
+        pols.append((pol, lp1))
+    assert (pols[0][1] - pols[1][1]).abs().max().item() <= 5e-2 * pols[0][1].abs().max().item()
+
+
+def test_model_files_remember_the_switches(pkg, eng, tmp_path):
+    cfg = _cfg(pkg, SWITCHES[-1])
+    a, b = pkg.Policy(eng, cfg), pkg.Policy(eng, cfg)
+    a.upload_params(_init(cfg, 1))
+    b.upload_params(_init(cfg, 2))
+    prompts = dev(np.random.default_rng(0).integers(0, cfg.vocab, (3, 5)), eng, np.int32)
+    _, _, lg_a = a.rollout(prompts, 8, temperature=0.0, want_logits=True)
+    for role in ("model", "checkpoint"):
+        path = str(tmp_path / f"p.{role}")
+        a.save(path, role)
+        b.upload_params(_init(cfg, 2))
+        b.load(path)
+        _, _, lg_b = b.rollout(prompts, 8, temperature=0.0, want_logits=True)
+        assert torch.equal(lg_a, lg_b), role
+        # a policy of another structure refuses the file
+        for other in (dict(sub_ln=False), dict(n_head_kv=4), dict(tie_embeddings=False)):
+            kw = dict(SWITCHES[-1])
+            kw.update(other)
+            with pytest.raises(pkg.NnbError):
+                pkg.Policy(eng, _cfg(pkg, kw)).load(path)

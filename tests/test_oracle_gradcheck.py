@@ -28,9 +28,17 @@ def _loss(cfg, flat, tokens, P, up_lp, up_ent, dv):
     return total
 
 
-@pytest.mark.parametrize("act,pos,value_head", [(0, 0, False), (1, 1, True), (0, 1, True), (1, 0, False), (2, 1, False)])
-def test_whole_model_backward_by_finite_differences(pkg, act, pos, value_head):
-    cfg = pkg.GptConfig(n_layer=2, d_model=16, n_head=2, d_ff=24, vocab=13, ctx=8, act=act, pos=pos, value_head=value_head)
+# the last cases switch on, one at a time and then together, the structure of BitNet b1.58 2B4T: SubLN, grouped-query
+# attention, tied embeddings (the reference exercises them in src/bitnet_struct_test.cpp: gradients reach the sub-norm
+# gains, GQA equals MHA with block-replicated KV weights, the tied head's two gradient paths sum in one tensor)
+@pytest.mark.parametrize("act,pos,value_head,extra", [
+    (0, 0, False, {}), (1, 1, True, {}), (0, 1, True, {}), (1, 0, False, {}), (2, 1, False, {}),
+    (1, 1, False, dict(sub_ln=True)), (1, 1, False, dict(n_head=4, n_head_kv=2)), (0, 0, True, dict(tie_embeddings=True)),
+    (2, 1, True, dict(sub_ln=True, n_head=4, n_head_kv=1, tie_embeddings=True))])
+def test_whole_model_backward_by_finite_differences(pkg, act, pos, value_head, extra):
+    kw = dict(n_layer=2, d_model=16, n_head=2, d_ff=24, vocab=13, ctx=8, act=act, pos=pos, value_head=value_head)
+    kw.update(extra)
+    cfg = pkg.GptConfig(**kw)
     rng = np.random.default_rng(10 + act + 2 * pos)
     layout, n_params = cfg.param_layout()
     flat = rng.normal(0, 0.3, n_params)
@@ -85,13 +93,16 @@ def test_quantised_model_reduces_to_its_twin_where_nothing_is_quantised(pkg):
     assert np.abs(lp_a - lp_b).max() < 5e-2
 
 
-@pytest.mark.parametrize("act,pos", [(0, 0), (1, 1)])
-def test_decode_step_logits_within_the_reference_bound_of_the_full_forward(pkg, act, pos):
+@pytest.mark.parametrize("act,pos,extra", [(0, 0, {}), (1, 1, {}),
+                                           (2, 1, dict(sub_ln=True, n_head=4, n_head_kv=2, tie_embeddings=True))])
+def test_decode_step_logits_within_the_reference_bound_of_the_full_forward(pkg, act, pos, extra):
     """src/attn_consistency_test.cpp:262-264: KV-cache decode and the full causal forward may differ by at most
     5e-2 on any logit.  The C restatement of the step path against the numpy restatement of the full forward."""
     from oracle_binding import OracleGpt
 
-    cfg = pkg.GptConfig(n_layer=2, d_model=64, n_head=2, d_ff=128, vocab=97, ctx=24, act=act, pos=pos)
+    kw = dict(n_layer=2, d_model=64, n_head=2, d_ff=128, vocab=97, ctx=24, act=act, pos=pos)
+    kw.update(extra)
+    cfg = pkg.GptConfig(**kw)
     flat = cfg.init_params(1, bias_std=0.01)
     tr = ot.OracleTrainer(cfg, flat)
     m = OracleGpt(cfg, flat)
