@@ -474,6 +474,15 @@ nnb_status nnb_policy_train_step_grouped(nnb_policy* p, const int32_t* d_tokens,
  * nnb_policy_train_step with the loss in d_report[0] and the units in d_report[7].  group as above. */
 nnb_status nnb_policy_sft_step(nnb_policy* p, const int32_t* d_tokens, size_t n_seq, size_t seq_len, size_t prompt_len,
                                size_t group, const float* d_mask, float units, float* d_report);
+
+/* After a training micro-batch (nnb_policy_train_step* / nnb_policy_sft_step): the int8 activations that layer `layer`
+ * kept for its backward pass, in the engine's K-permuted layout, and their per-token scales.  which: 0 = input of
+ * q|k|v (ln1 output), 1 = input of o, 2 = input of fc1 (ln2 output), 3 = input of fc2.  *rows / *cols receive the
+ * shape; d_q (rows * cols bytes) and d_s (rows floats) may be NULL to query the shape only.  Two policies in
+ * different numeric modes given the same tokens can be compared entry by entry with it (how many int8 activations
+ * the fast mode flips). */
+nnb_status nnb_policy_cached_activation(nnb_policy* p, int layer, int which, int8_t* d_q, float* d_s, size_t* rows,
+                                        size_t* cols);
 /* flat f32 gradient buffer, same layout as the parameters (allocated and zeroed on first use) */
 float* nnb_policy_grads(nnb_policy* p);
 nnb_status nnb_policy_zero_grad(nnb_policy* p);

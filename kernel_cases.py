@@ -9,7 +9,9 @@ Used for Nsight Compute captures and quick timing; every case prints its CUDA-ev
   attn_decode  decode attention of 512 sequences x 16 heads x 128 at position 400, fused int8 output
   train [n]    reference log-probs + one training micro-batch of n (16) sequences x 640 on the 1B policy
   rollout [B P new]   batched rollout on the 1B policy (default 512 16 24)
-  rollout3b [B P new] batched rollout on the 3B-shaped decode policy (26 layers, d 3200, 32 heads of 100; default 128 16 48)
+  rollout3b [B P new [layers]] batched rollout on the 3B-shaped decode policy (26 layers, d 3200, 32 heads of 100;
+               default 128 16 48); `layers` cuts the depth (same kernels, less memory: for profiler captures)
+  lmhead [T]   LM head fused with log-prob / entropy, forward and backward, T (8192) decisions x d 2048 x vocab 32000
 """
 import os
 import sys
@@ -122,12 +124,26 @@ def main(argv):
         _timed(f"rollout {B} x ({P}+{new})", lambda: pol.rollout(prompts, new, temperature=0.8, top_k=50, seed=1), reps=1)
     elif case == "rollout3b":
         B, P, new = (int(a) for a in argv[2:5]) if len(argv) > 4 else (128, 16, 48)
-        cfg, pol, g = _policy(pkg, eng, MODEL_3B)
+        model = dict(MODEL_3B, n_layer=int(argv[5])) if len(argv) > 5 else MODEL_3B
+        cfg, pol, g = _policy(pkg, eng, model)
         prompts = torch.randint(0, cfg.vocab, (B, P), device=dev, dtype=torch.int32, generator=g)
         pol.set_step_timing(8)
         _timed(f"3B-shaped rollout {B} x ({P}+{new})", lambda: pol.rollout(prompts, new, temperature=0.8, top_k=50, seed=1), reps=1)
         ms, pos = pol.step_times()
         print("ms per step by position:", " ".join(f"{p}:{m / 8:.3f}" for m, p in zip(ms, pos)))
+    elif case == "lmhead":
+        T, k, V = int(argv[2]) if len(argv) > 2 else 8192, 2048, 32000
+        w8, _ = eng.expand_weights(_rand_packed(dev, V, k // 16), k)
+        tau = torch.rand(V, device=dev) * 0.05 + 0.01
+        bias = torch.randn(V, device=dev) * 0.01
+        q, s, _ = eng.act_quant_tm(torch.randn(T, k, device=dev))
+        actions = torch.randint(0, V, (T,), device=dev, dtype=torch.int32)
+        up_lp, up_ent = torch.randn(T, device=dev), torch.randn(T, device=dev) * 0.01
+        logp, ent, lse = eng.lmhead_logprob_entropy(w8, tau, bias, q, s, actions)
+        dbias = torch.zeros(V, device=dev)
+        _timed("fused LM head forward (log-prob, entropy)", lambda: eng.lmhead_logprob_entropy(w8, tau, bias, q, s, actions))
+        _timed("fused LM head backward (bf16 d logits * tau, bias gradient)",
+               lambda: eng.lmhead_logprob_entropy_backward(w8, tau, bias, q, s, actions, lse, ent, up_lp, up_ent, dbias=dbias))
     else:
         raise SystemExit(__doc__)
     eng.check_device_errors()

@@ -122,6 +122,7 @@ _SIGNATURES = {
     "nnb_policy_logprobs": (_I, [_P, _P, _SZ, _SZ, _SZ, _P, _P, _P]),
     "nnb_policy_train_step": (_I, [_P, _P, _SZ, _SZ, _SZ, _P, _P]),
     "nnb_policy_sft_step": (_I, [_P, _P, _SZ, _SZ, _SZ, _SZ, _P, C.c_float, _P]),
+    "nnb_policy_cached_activation": (_I, [_P, C.c_int, C.c_int, _P, _P, _P, _P]),
     "nnb_policy_logprobs_grouped": (_I, [_P, _P, _SZ, _SZ, _SZ, _SZ, _P, _P, _P]),
     "nnb_policy_train_step_grouped": (_I, [_P, _P, _SZ, _SZ, _SZ, _SZ, _P, _P]),
     "nnb_policy_grads": (_P, [_P]),

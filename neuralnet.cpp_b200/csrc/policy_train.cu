@@ -594,6 +594,23 @@ nnb_status nnb_policy_train_step_grouped(nnb_policy* p, const int32_t* d_tokens,
     return NNB_OK;
 }
 
+nnb_status nnb_policy_cached_activation(nnb_policy* p, int layer, int which, int8_t* d_q, float* d_s, size_t* rows, size_t* cols)
+{
+    NNB_REQUIRE(p, "policy is NULL");
+    TrainWs* w = (TrainWs*)p->train;
+    NNB_REQUIRE(w && w->saved_layers, "cached_activation: no training micro-batch has run on this policy");
+    NNB_REQUIRE(layer >= 0 && layer < p->cfg.n_layer && which >= 0 && which < 4, "cached_activation: bad index");
+    const LayerSave& s = w->L[layer];
+    const int8_t* qs[4] = {s.q1, s.q2, s.q3, s.q4};
+    const float* ss[4] = {s.s1, s.s2, s.s3, s.s4};
+    const size_t k = which == 3 ? (size_t)p->cfg.d_ff : (size_t)p->cfg.d_model;
+    if (rows) *rows = w->rows;
+    if (cols) *cols = k;
+    if (d_q) NNB_CUDA(cudaMemcpyAsync(d_q, qs[which], w->rows * k, cudaMemcpyDeviceToDevice, p->e->stream));
+    if (d_s) NNB_CUDA(cudaMemcpyAsync(d_s, ss[which], w->rows * 4, cudaMemcpyDeviceToDevice, p->e->stream));
+    return NNB_OK;
+}
+
 nnb_status nnb_policy_sft_step(nnb_policy* p, const int32_t* d_tokens, size_t n_seq, size_t seq_len, size_t prompt_len,
                                size_t group, const float* d_mask, float units, float* d_report)
 {

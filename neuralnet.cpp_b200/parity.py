@@ -51,7 +51,7 @@ def fast_vs_exact(pkg, eng, groups: int = 2, group_size: int = 8, prompt_len: in
     adv = adv_seq[:, None].expand(n, max_new).contiguous()
     mask = torch.ones((n, max_new), device=eng.device)
     out = {}
-    lps, grads, reps = [], [], []
+    lps, grads, reps, acts = [], [], [], []
     for pol in (pe, pf):
         lp, _, _ = pol.logprobs(tokens, prompt_len)
         pol.zero_grad()
@@ -59,7 +59,23 @@ def fast_vs_exact(pkg, eng, groups: int = 2, group_size: int = 8, prompt_len: in
         lps.append(lp.cpu().numpy().astype(np.float64))
         grads.append(pol.grads_view().cpu().numpy())
         reps.append(rep.cpu().numpy().astype(np.float64))
+        acts.append([[pol.cached_activation(l, w)[0] for w in range(4)] for l in range(cfg_e.n_layer)])
     eng.check_device_errors()
+    # how many of the int8 activations that feed the linears differ between the modes (both keep them in the same
+    # layout), over all layers; and by more than one quantisation step
+    flipped = big = total = 0
+    first = None
+    for l in range(cfg_e.n_layer):
+        for w in range(4):
+            diff = (acts[0][l][w].to(torch.int16) - acts[1][l][w].to(torch.int16)).abs()
+            flipped += int((diff > 0).sum())
+            big += int((diff > 1).sum())
+            total += diff.numel()
+            if first is None:
+                first = float((diff > 0).float().mean())  # layer 0's ln1 output: before any bf16 arithmetic
+    out["int8_flip_fraction"] = flipped / total
+    out["int8_flip_gt1_fraction"] = big / total
+    out["int8_flip_fraction_first_input"] = first
     out["logp_max_abs"] = float(np.abs(lps[1] - lps[0]).max())
     out["logp_mean_abs"] = float(np.abs(lps[1] - lps[0]).mean())
     out["loss_abs"] = float(abs(reps[1][0] - reps[0][0]))

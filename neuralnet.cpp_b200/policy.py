@@ -299,6 +299,17 @@ def sft_step(self, tokens: torch.Tensor, prompt_len: int, mask, units=0.0, group
     return report
 
 
+def cached_activation(self, layer: int, which: int):
+    """(q int8 (rows, cols) in the engine's K-permuted layout, s f32 (rows)) kept by the last training micro-batch for
+    layer `layer`: which 0 = input of q|k|v, 1 = input of o, 2 = input of fc1, 3 = input of fc2."""
+    rows, cols = C.c_size_t(), C.c_size_t()
+    check(self._lib.nnb_policy_cached_activation(self._h, layer, which, None, None, C.byref(rows), C.byref(cols)))
+    q = torch.empty((rows.value, cols.value), device=self.engine.device, dtype=torch.int8)
+    s = torch.empty(rows.value, device=self.engine.device, dtype=torch.float32)
+    check(self._lib.nnb_policy_cached_activation(self._h, layer, which, _ptr(q), _ptr(s), None, None))
+    return q, s
+
+
 def optimizer_step(self, lr, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01, max_grad_norm=0.0):
     norm = torch.empty(1, device=self.engine.device, dtype=torch.float32)
     check(self._lib.nnb_policy_optimizer_step(self._h, lr, beta1, beta2, eps, weight_decay, max_grad_norm, _ptr(norm)))
@@ -339,5 +350,5 @@ def release_workspaces(self):
 
 
 for _f in (save, load, rollout_sampled, logprobs, grads_view, zero_grad, train_step, sft_step, optimizer_step, release_workspaces, set_step_timing,
-           step_times):
+           step_times, cached_activation):
     setattr(Policy, _f.__name__, _f)
