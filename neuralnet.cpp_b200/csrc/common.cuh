@@ -156,7 +156,11 @@ struct SampleOpts {
     int eos = -1, min_new = 0;
     int32_t* done = nullptr;     // (B) set once a sequence has sampled eos; NULL = no end-of-sequence handling
     int32_t* gen_len = nullptr;  // (B) tokens generated before eos
+    // Working copy of the logits, (B, V rounded up to 4) f32, for vocabularies whose row does not fit a CTA's shared
+    // memory (sample_row_in_smem(V) false); the kernel then keeps the row there (L2) instead
+    float* row_scratch = nullptr;
 };
+bool sample_row_in_smem(size_t V);
 nnb_status launch_sample_opts(nnb_engine* e, bool exact, const float* logits, size_t B, size_t V, const SampleOpts& o,
                               unsigned long long seed, unsigned seq0, const int* d_pos, int prompt_len, int32_t* tokens,
                               size_t tokens_stride, float* logp, size_t logp_stride, float* entropy);

@@ -1243,8 +1243,10 @@ sample_kernel(const float* __restrict__ logits, int V, SampleOpts o,
     typedef typename AccT<EXACT>::type acc_t;
     constexpr int NT = SAMPLE_NT, NW = SAMPLE_NW;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    float* lg = reinterpret_cast<float*>(smem_raw);            // V (raw, then scaled) logits
-    int* cand = reinterpret_cast<int*>(lg + ((V + 3) & ~3));   // up to 1024 candidates
+    // V (raw, then scaled) logits: in shared memory, or in the caller's scratch when a row is too large for it
+    const int Vp = (V + 3) & ~3;
+    float* lg = o.row_scratch ? o.row_scratch + (size_t)blockIdx.x * Vp : reinterpret_cast<float*>(smem_raw);
+    int* cand = reinterpret_cast<int*>(reinterpret_cast<float*>(smem_raw) + (o.row_scratch ? 0 : Vp));  // up to 1024 candidates
     float* cval = reinterpret_cast<float*>(cand + 1024);       // their exponentials, then probabilities
     int* whist = reinterpret_cast<int*>(cval + 1024);          // NW x 256 per-warp histograms
     __shared__ int hist[256];
@@ -1602,6 +1604,8 @@ nnb_status launch_sample(nnb_engine* e, bool exact, const float* logits, size_t 
                               entropy);
 }
 
+bool sample_row_in_smem(size_t V) { return ((V + 3) & ~(size_t)3) * 4 + 2 * 1024 * 4 + SAMPLE_NW * 256 * 4 <= 220 * 1024; }
+
 nnb_status launch_sample_opts(nnb_engine* e, bool exact, const float* logits, size_t B, size_t V, const SampleOpts& o,
                               unsigned long long seed, unsigned seq0, const int* d_pos, int prompt_len, int32_t* tokens,
                               size_t tokens_stride, float* logp, size_t logp_stride, float* entropy)
@@ -1613,8 +1617,11 @@ nnb_status launch_sample_opts(nnb_engine* e, bool exact, const float* logits, si
     if (o.top_p < 1.0f && o.temperature > 0.0f && !((top_k > 0 && (size_t)top_k < V) || V <= 1024))
         NNB_FAIL(NNB_ERR_UNSUPPORTED, "sample: top_p needs at most 1024 candidates (set top_k <= 1024; vocabulary is %zu)", V);
     NNB_REQUIRE((o.done == nullptr) == (o.gen_len == nullptr), "sample: done flags and lengths go together");
-    const size_t smem = ((V + 3) & ~(size_t)3) * 4 + 2 * 1024 * 4 + SAMPLE_NW * 256 * 4;
-    NNB_REQUIRE(smem <= 220 * 1024, "sample: vocabulary %zu too large for one CTA", V);
+    const bool in_smem = sample_row_in_smem(V);
+    NNB_REQUIRE(in_smem || o.row_scratch, "sample: a vocabulary of %zu needs the row scratch buffer", V);
+    SampleOpts oo = o;
+    if (in_smem) oo.row_scratch = nullptr;
+    const size_t smem = (in_smem ? ((V + 3) & ~(size_t)3) * 4 : 0) + 2 * 1024 * 4 + SAMPLE_NW * 256 * 4;
     if (exact) {
         auto kern = sample_kernel<true>;
         static size_t cfg_dev[64] = {}; size_t& cfg = cfg_dev[e->device & 63];
@@ -1622,7 +1629,7 @@ nnb_status launch_sample_opts(nnb_engine* e, bool exact, const float* logits, si
             NNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             cfg = smem;
         }
-        launch_ex(e, kern, dim3((unsigned)B), dim3(SAMPLE_NT), smem, logits, (int)V, o, seed, seq0, d_pos, prompt_len,
+        launch_ex(e, kern, dim3((unsigned)B), dim3(SAMPLE_NT), smem, logits, (int)V, oo, seed, seq0, d_pos, prompt_len,
                   tokens, (int)tokens_stride, logp, (int)logp_stride, entropy);
     } else {
         auto kern = sample_kernel<false>;
@@ -1631,7 +1638,7 @@ nnb_status launch_sample_opts(nnb_engine* e, bool exact, const float* logits, si
             NNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             cfg = smem;
         }
-        launch_ex(e, kern, dim3((unsigned)B), dim3(SAMPLE_NT), smem, logits, (int)V, o, seed, seq0, d_pos, prompt_len,
+        launch_ex(e, kern, dim3((unsigned)B), dim3(SAMPLE_NT), smem, logits, (int)V, oo, seed, seq0, d_pos, prompt_len,
                   tokens, (int)tokens_stride, logp, (int)logp_stride, entropy);
     }
     e->launches++;

@@ -224,7 +224,7 @@ static void free_decode(nnb_policy* p)
 {
     DecodeWs& w = p->dec;
     void* ptrs[] = {w.k, w.v, w.k_pre, w.v_pre, w.tokens_pre, w.x, w.qkv, w.att, w.pre_ml, w.h1, w.logits, w.q8, w.s, w.qsum, w.d_pos,
-                    w.tokens, w.logp, w.done, w.gen_len, w.qkv_raw, w.act, w.hn, w.hnb};
+                    w.tokens, w.logp, w.done, w.gen_len, w.qkv_raw, w.act, w.hn, w.hnb, w.sample_rows};
     for (void* q : ptrs)
         if (q) cudaFree(q);
     w = DecodeWs();
@@ -286,6 +286,7 @@ static nnb_status ensure_decode(nnb_policy* p, size_t B, size_t ctx_alloc, size_
     NNB_ALLOC(w.gen_len, B * 4);
     if (cfg_gqa(c)) NNB_ALLOC(w.qkv_raw, B * (d + 2 * cfg_kv_heads(c) * (d / c.n_head)) * 4);
     if (c.sub_ln) NNB_ALLOC(w.act, B * F * 4);
+    if (!sample_row_in_smem(V)) NNB_ALLOC(w.sample_rows, B * ((V + 3) & ~(size_t)3) * 4);
     if (c.tie_embeddings) {
         NNB_ALLOC(w.hn, B * d * 4);
         NNB_ALLOC(w.hnb, B * d * 2);
@@ -401,7 +402,9 @@ static nnb_status decode_step(nnb_policy* p, const StepView& sv, bool with_head,
         NNB_TRY(launch_row_quant(e, 0, exact, w.x, P + p->lnf_g, B, d, d, w.q8, w.s, w.qsum, c.tie_embeddings ? w.hn : nullptr));
         if (c.tie_embeddings) NNB_TRY(policy_tied_head_fwd(p, w.hn, w.hnb, B, w.logits));
         else NNB_TRY(policy_linear_fwd(p, p->head, 1, w.q8, w.s, w.qsum, B, nullptr, w.logits, 0));
-        NNB_TRY(launch_sample_opts(e, exact, w.logits, B, V, so, seed, seq0, w.d_pos, prompt_len, w.tokens, total,
+        SampleOpts so_rows = so;
+        so_rows.row_scratch = w.sample_rows;
+        NNB_TRY(launch_sample_opts(e, exact, w.logits, B, V, so_rows, seed, seq0, w.d_pos, prompt_len, w.tokens, total,
                                    want_logp ? w.logp : nullptr, total, nullptr));
     }
     return launch_add_int(e, w.d_pos, 1);  // the position lives on the device so a captured step can be replayed

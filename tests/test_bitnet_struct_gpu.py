@@ -272,20 +272,23 @@ def _fast_vs_exact(pkg, eng, extra):
 _BASE = {}
 
 
-@pytest.mark.parametrize("extra", SWITCHES, ids=IDS)
+@pytest.mark.parametrize("extra", SWITCHES + [dict(act=2)], ids=IDS + ["relu2"])
 def test_fast_mode_is_close_to_the_exact_mode(pkg, eng, extra):
     """tcgen05 paths: the merged q|k|v matrix of d + 2 dkv rows, the tied head's bf16 product (forward and both backward
     GEMMs, 128 decisions), the SubLN recomputation in the backward.  bf16 attention perturbs the forward activations and
     with them int8 roundings, so whole-model gradients of the two modes differ by a few per cent to a few tens of per cent
     on small tensors whatever the structure; the bound here is that a switch does not move that deviation far from the
-    plain model's on the same inputs (a wrong branch moves it to order one)."""
+    plain model's on the same inputs (a wrong branch moves it to order one).  Measured: plain 1 %, SubLN 2.8 %, grouped
+    queries 0.6 %, tied 1.2 %; ReLU2GLU, cubic in its input, multiplies the perturbation (all switches together: 17 % rms
+    on a sub-norm gain, 32 % of the largest entry on the embedding gradient), hence its own bound."""
     if not _BASE:
         _BASE.update(_fast_vs_exact(pkg, eng, {})[0])
     stats, pf, rng = _fast_vs_exact(pkg, eng, extra)
     print("plain model:", _BASE, "\nwith", extra, ":", stats)
     assert stats["logp"] <= 3e-2 and stats["entropy"] <= 3e-2
-    assert stats["grad_rel_rms"] <= max(0.2, 2.5 * _BASE["grad_rel_rms"]), (stats, _BASE)
-    assert stats["grad_rel_max"] <= max(0.2, 2.5 * _BASE["grad_rel_max"]), (stats, _BASE)
+    cubic = extra.get("act") == 2
+    assert stats["grad_rel_rms"] <= (0.3 if cubic else 0.1), (stats, _BASE)
+    assert stats["grad_rel_max"] <= (0.5 if cubic else 0.1), (stats, _BASE)
     # the rollout's recorded log-probs equal the teacher-forced ones in the fast mode too (ratio = 1 at the first epoch),
     # with few sequences (CUDA-core head) and with 64 (tensor-core head)
     for n_seq in (6, 64):

@@ -132,6 +132,20 @@ def test_top_p_over_a_large_vocabulary_without_top_k_is_refused(pkg, eng):
         pol.rollout_sampled(p, 4, pkg.SamplingConfig(top_p=0.5))
 
 
+@pytest.mark.parametrize("kw", [dict(temperature=0.0), dict(temperature=0.9, top_k=40), dict(temperature=1.0, top_k=0),
+                                dict(temperature=0.8, top_k=64, top_p=0.8, repeat_penalty=1.2, repeat_window=6)])
+def test_vocabulary_larger_than_a_ctas_shared_memory(pkg, eng, kw):
+    """70 000 logits (280 KB) do not fit one CTA's shared memory: the sampler keeps its working row in a scratch buffer
+    instead and must choose the same tokens"""
+    cfg = pkg.GptConfig(n_layer=1, d_model=64, n_head=2, d_ff=128, vocab=70000, ctx=24, act=1, pos=1)
+    pol, m, _ = _setup(pkg, eng, cfg)
+    prompts = _prompts(cfg, 4, 5, seed=9)
+    ref_tok, ref_lp, _ = m.rollout_cfg(prompts, 10, seed=4, **kw)
+    tok, lp, _, _ = pol.rollout_sampled(torch.from_numpy(prompts).to(eng.device), 10, pkg.SamplingConfig(seed=4, **kw))
+    assert np.array_equal(tok.cpu().numpy(), ref_tok)
+    assert np.abs(lp.cpu().numpy() - ref_lp).max() <= 1e-3 * np.abs(ref_lp).max()
+
+
 def test_full_vocab_sampled_rollout_agrees(pkg, eng):
     # without top-k the CDF is accumulated in f64 by chunks on the GPU and in f32 sequentially by the
     # reference rule: tokens agree except where the draw falls within rounding of a CDF step
