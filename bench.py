@@ -247,7 +247,7 @@ def _kernel_rooflines(torch, pkg, eng, pol, wl, peaks):
     wst = (wst & 0xFFFFFFFF)
     wst = torch.where(wst >= 2**31, wst - 2**32, wst).to(torch.int32).contiguous()
     taus = torch.rand((n_mats, O), device=dev) * 0.09 + 0.01
-    for mtok in (1, 16):
+    for mtok in (1, 4, 16):
         xq = torch.randn((mtok, d), device=dev)
         q1, s1, qs1 = eng.act_quant_tm(xq)
         ys = torch.empty((n_mats, mtok, O), device=dev)
@@ -255,7 +255,8 @@ def _kernel_rooflines(torch, pkg, eng, pol, wl, peaks):
         alg = n_mats * (d * O / 4 + 4 * O + mtok * d + 4 * mtok + 4 * mtok * O)
         ach = alg / (ms * 1e-3) / 1e9
         out[f"roofline_gemv_m{mtok}"] = {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                                          "frac": ach / peaks["hbm_gbs"], "kernel": "bitlinear_skinny_kernel",
+                                          "frac": ach / peaks["hbm_gbs"],
+                                          "kernel": "bitlinear_gemv_kernel (dp4a)" if mtok <= 4 else "bitlinear_skinny_kernel",
                                           "kernel_ms": ms, "shape": f"M={mtok} K={d} N={O} x{n_mats}"}
     return out
 
@@ -466,14 +467,23 @@ class DecodeJob:
         L, d, H = m["n_layer"], m["d_model"], m["n_head"]
         kv_per_pos = self.chunk * L * 2 * d * 2  # algorithmic bytes per cached position per step (bf16 K and V)
         F = m["d_ff"]
-        packed = (L * (4 * d * d + 3 * d * F) + m["vocab"] * d) / 4
+        dk = d // H
+        dkv = (m.get("n_head_kv") or H) * dk
+        # packed bytes of the linears: q and o (d x d), k and v (dkv x d), fc1 (gate | up) and fc2, the head unless tied
+        packed = (L * (2 * d * d + 2 * dkv * d + 3 * d * F) + (0 if m.get("tie_embeddings") else m["vocab"] * d)) / 4
+        if dk == 100:
+            kernel, pad = "attn_decode_bf16_kernel<100,104>", " (the cache rows are padded from 100 to 104 features: 4 % more is actually read)"
+        else:
+            kernel, pad = f"attn_decode_bf16_kernel<{dk},{dk}>", ""
+        if m.get("n_head_kv"):
+            pad += f"; grouped-query attention runs on the cache expanded to {H} heads, so these are the bytes of {H} heads"
         attn = kv_per_pos / (b * 1e-3) / 1e9
         wstream = packed / (a * 1e-3) / 1e9
         return {"roofline": {"bound": "hbm", "achieved": attn, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": attn / peaks["hbm_gbs"],
-                             "traffic": None, "kernel": "attn_decode_bf16_kernel<100,104>",
+                             "traffic": None, "kernel": kernel,
                              "how": "slope of the per-step time over the context, measured with CUDA events every 64 steps inside a "
-                                    f"rollout of {self.chunk} sequences; algorithmic bytes = 2 x ctx x d x 2 B per sequence and layer "
-                                    "(the cache rows are padded from 100 to 104 features: 4 % more is actually read)",
+                                    f"rollout of {self.chunk} sequences; algorithmic bytes = 2 x ctx x d x 2 B per sequence and layer"
+                                    + pad,
                              "ms_per_step_per_position": float(b), "peak_source": peaks["src"] + " copy bandwidth"},
                 "roofline_weight_stream": {"bound": "hbm", "achieved": wstream, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                                            "frac": wstream / peaks["hbm_gbs"], "packed_bytes": int(packed),

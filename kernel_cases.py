@@ -5,7 +5,7 @@
 Used for Nsight Compute captures and quick timing; every case prints its CUDA-event time.  Cases:
   fwd          int8 ternary forward GEMM (tcgen05), T=10240 K=2048 O=11264
   dx | dw      bf16 backward GEMMs (tcgen05) of the same linear
-  gemv         2-bit packed weight stream, 16 tokens, stack of 64 matrices (2048 x 11264)
+  gemv [M]     2-bit packed weight stream, M (16) tokens, stack of 64 matrices (2048 x 11264)
   attn_decode  decode attention of 512 sequences x 16 heads x 128 at position 400, fused int8 output
   train [n]    reference log-probs + one training micro-batch of n (16) sequences x 640 on the 1B policy
   rollout [B P new]   batched rollout on the 1B policy (default 512 16 24)
@@ -91,8 +91,9 @@ def main(argv):
         k, out, n = 2048, 11264, 64
         wst = _rand_packed(dev, n, out, k // 16)
         taus = torch.rand(n, out, device=dev) * 0.05 + 0.01
-        q, s, qs = eng.act_quant_tm(torch.randn(16, k, device=dev))
-        ys = torch.empty(n, 16, out, device=dev)
+        m = int(argv[2]) if len(argv) > 2 else 16
+        q, s, qs = eng.act_quant_tm(torch.randn(m, k, device=dev))
+        ys = torch.empty(n, m, out, device=dev)
         _timed("packed GEMV stack", lambda: eng.bitlinear_fwd_tm_stack(wst, taus, None, q, s, qs, ys))
     elif case == "attn_decode":
         B, H, dk, ctx, pos = 512, 16, 128, 512, 400

@@ -653,7 +653,7 @@ static nnb_status launch_skinny(nnb_engine* e, const uint32_t* wq, size_t wq_str
     constexpr int GROUPS = 8 / WK;
     const size_t smem = (size_t)NT * 8 * (k + 16) + (size_t)8 * 32 * MS * NT * 4 * sizeof(int);
     auto kern = bitlinear_skinny_kernel<NT, WK, MS, OutT>;
-    static size_t configured = 0;
+    static size_t cfg_dev[64] = {}; size_t& configured = cfg_dev[e->device & 63];  // the attribute is per device
     if (smem > configured) {
         NNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured = smem;
@@ -685,7 +685,7 @@ static nnb_status launch_cfg(nnb_engine* e, const uint32_t* wq, size_t wq_stride
     constexpr size_t red = WK > 1 ? (size_t)(WM * WN) * (WK - 1) * 32 * ((BM / WM / 16) * (BN / WN / 8) * 4) * 4 : 0;
     constexpr size_t smem = pipe > red ? pipe : red;
     auto kern = bitlinear_mma_kernel<BM, BN, BK, STAGES, WM, WN, WK, OutT>;
-    static bool configured = false;
+    static bool cfg_dev[64] = {}; bool& configured = cfg_dev[e->device & 63];  // the attribute is per device
     if (!configured) {
         NNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured = true;
@@ -697,6 +697,189 @@ static nnb_status launch_cfg(nnb_engine* e, const uint32_t* wq, size_t wq_stride
                                              (int)k, (int)out, y, y_stride, acc);
     e->launches++;
     NNB_CHECK_LAUNCH("bitlinear_mma_kernel");
+    return NNB_OK;
+}
+
+
+// ------------------------------------------------------- CUDA-core GEMV (one to four tokens)
+// At a handful of tokens the tensor-core kernels spend their shared-memory bandwidth on activation fragments that are
+// mostly padding (token tiles of 8): the shared-memory pipe, not HBM, bounds them.  Here nothing but the packed weights
+// moves inside the loop.  A warp owns a slab of output rows; its 32 lanes split K in 64-feature blocks; a lane keeps
+// the int8 activations of its block in registers (16 words per token), reads its 16 bytes of every row (the warp reads
+// 512 contiguous bytes of a row), unpacks the 2-bit codes with shift + mask (the activation layout pairs
+// (w >> 2c) & 0x03030303 of word i with activation word 4c + i of the block) and multiplies with dp4a, unsigned codes x
+// signed activations; 2 * rowsum comes off afterwards, as in the mma kernels.  Eight rows are in flight per lane while
+// the previous eight are multiplied; their partial sums are folded across the lanes by a reduce-scatter (9 shuffles per
+// token for 8 rows).  K beyond 2048 is walked in chunks of 32 blocks, the rows' totals waiting in shared memory.
+__device__ __forceinline__ int dp4a_us(uint32_t a_u8, uint32_t b_s8, int c)
+{
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;\n" : "=r"(d) : "r"(a_u8), "r"(b_s8), "r"(c));
+    return d;
+}
+
+constexpr int GEMV_SR_MAX = 256;  // rows per work item at most (totals kept per warp in shared memory)
+
+template <int MT, typename OutT>
+__global__ void __launch_bounds__(256)
+bitlinear_gemv_kernel(const uint32_t* __restrict__ wq, size_t wq_stride_words, const float* __restrict__ tau,
+                      const float* __restrict__ bias, const float* __restrict__ residual, const int8_t* __restrict__ q,
+                      const float* __restrict__ s, const int32_t* __restrict__ qsum, int T, int K, int OUT, int n_mats, int SR,
+                      OutT* __restrict__ y, size_t y_stride_elems, int32_t* __restrict__ acc_out)
+{
+    __shared__ int tot_s[8][MT][GEMV_SR_MAX];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nblk = K / 64, NC = (nblk + 31) / 32;
+    const int rstride = K / 64;  // 16-byte units per row
+    const int slabs = (OUT + SR - 1) / SR;
+    const int n_items = slabs * n_mats;
+    int(*tot)[GEMV_SR_MAX] = tot_s[warp];
+    // which of a group's 8 rows this lane ends up holding after the reduce-scatter
+    const int b0 = lane & 1, b1 = (lane >> 1) & 1, b2 = (lane >> 2) & 1;
+    const int myrow = 4 * b0 + 2 * b1 + b2;
+    constexpr uint32_t MSK = 0x03030303u;
+
+    for (int item = blockIdx.x * 8 + warp; item < n_items; item += gridDim.x * 8) {
+        const int mat = item / slabs, sl = item - mat * slabs;
+        const int row0 = sl * SR;
+        const int nrows = min(SR, OUT - row0);
+        const int ngroups = (nrows + 7) >> 3;
+        const uint4* wm = reinterpret_cast<const uint4*>(wq + (size_t)mat * wq_stride_words) + (size_t)row0 * rstride;
+        for (int c = 0; c < NC; ++c) {
+            const int bi = c * 32 + lane;
+            const bool bok = bi < nblk;
+            uint32_t A[MT][16];
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+                if (bok && m < T) {
+                    const uint4* ap = reinterpret_cast<const uint4*>(q + (size_t)m * K + (size_t)bi * 64);
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const uint4 a4 = __ldg(ap + u);
+                        A[m][4 * u + 0] = a4.x; A[m][4 * u + 1] = a4.y; A[m][4 * u + 2] = a4.z; A[m][4 * u + 3] = a4.w;
+                    }
+                } else {
+#pragma unroll
+                    for (int u = 0; u < 16; ++u) A[m][u] = 0u;
+                }
+            }
+            const uint4* wp = wm + bi;
+            uint4 cur[8], nxt[8];
+            auto fetch = [&](int g, uint4(&dst)[8]) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int r = g * 8 + j;
+                    dst[j] = (bok && r < nrows) ? __ldg(wp + (size_t)r * rstride) : make_uint4(0u, 0u, 0u, 0u);
+                }
+            };
+            fetch(0, cur);
+            for (int g = 0; g < ngroups; ++g) {
+                if (g + 1 < ngroups) fetch(g + 1, nxt);
+                int v[MT][8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const uint32_t w[4] = {cur[j].x, cur[j].y, cur[j].z, cur[j].w};
+                    uint32_t f[16];  // f[4c + i] = codes c, c+4, c+8, c+12 of word i
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        f[i] = w[i] & MSK;
+                        f[4 + i] = (w[i] >> 2) & MSK;
+                        f[8 + i] = (w[i] >> 4) & MSK;
+                        f[12 + i] = (w[i] >> 6) & MSK;
+                    }
+#pragma unroll
+                    for (int m = 0; m < MT; ++m) {
+                        int a = 0;
+#pragma unroll
+                        for (int u = 0; u < 16; ++u) a = dp4a_us(f[u], A[m][u], a);
+                        v[m][j] = a;
+                    }
+                }
+#pragma unroll
+                for (int m = 0; m < MT; ++m) {
+                    // reduce-scatter over lane bits 0..2 (8 -> 4 -> 2 -> 1 values), then a plain sum over bits 3, 4
+                    int u4[4], u2[2], u1;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int send = b0 ? v[m][i] : v[m][i + 4], keep = b0 ? v[m][i + 4] : v[m][i];
+                        u4[i] = keep + __shfl_xor_sync(0xffffffffu, send, 1);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        const int send = b1 ? u4[i] : u4[i + 2], keep = b1 ? u4[i + 2] : u4[i];
+                        u2[i] = keep + __shfl_xor_sync(0xffffffffu, send, 2);
+                    }
+                    {
+                        const int send = b2 ? u2[0] : u2[1], keep = b2 ? u2[1] : u2[0];
+                        u1 = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+                    }
+                    u1 += __shfl_xor_sync(0xffffffffu, u1, 8);
+                    u1 += __shfl_xor_sync(0xffffffffu, u1, 16);
+                    if (lane < 8) {
+                        if (c == 0) tot[m][g * 8 + myrow] = u1;
+                        else tot[m][g * 8 + myrow] += u1;
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) cur[j] = nxt[j];
+            }
+        }
+        __syncwarp();
+        const float* tau_m = tau + (size_t)mat * OUT;
+        const float* bias_m = bias ? bias + (size_t)mat * OUT : nullptr;
+        OutT* y_m = y + (size_t)mat * y_stride_elems;
+        for (int i = lane; i < nrows; i += 32) {
+            const int row = row0 + i;
+            const float tr = tau_m[row];
+            const float br = bias_m ? bias_m[row] : 0.0f;
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+                if (m >= T) break;
+                const int a = tot[m][i] - 2 * qsum[m];
+                float val = __fmul_rn(__fmul_rn(tr, s[m]), (float)a);
+                if (bias_m) val = __fadd_rn(val, br);
+                if (residual) val = __fadd_rn(residual[(size_t)m * OUT + row], val);
+                store_out<OutT>(y_m + (size_t)m * OUT + row, val);
+                if (acc_out) acc_out[(size_t)m * OUT + row] = a;
+            }
+        }
+        __syncwarp();
+    }
+}
+
+// NNB_GEMV_MAX_T in the environment: largest token count served by the CUDA-core GEMV (0 turns it off; for A/B timing)
+static int gemv_max_tokens()
+{
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("NNB_GEMV_MAX_T");
+        v = e ? atoi(e) : 4;
+        if (v < 0) v = 0;
+        if (v > 4) v = 4;
+    }
+    return v;
+}
+
+template <int MT, typename OutT>
+static nnb_status launch_gemv(nnb_engine* e, const uint32_t* wq, size_t wq_stride, const float* tau, const float* bias,
+                              const float* residual, const int8_t* q, const float* s, const int32_t* qsum, size_t n_mats,
+                              size_t t, size_t k, size_t out, OutT* y, size_t y_stride, int32_t* acc)
+{
+    // register budget (125 registers at one token, about 180 beyond): 2 CTAs of 256 threads per SM, or 1
+    const size_t ctas_per_sm = MT == 1 ? 2 : 1;
+    const size_t warps = (size_t)e->sm_count * ctas_per_sm * 8;
+    // rows per work item: about four items per warp, whole groups of 8 rows, at most GEMV_SR_MAX
+    size_t sr = (out * n_mats) / (warps * 4);
+    sr = (sr + 7) & ~(size_t)7;
+    if (sr < 8) sr = 8;
+    if (sr > GEMV_SR_MAX) sr = GEMV_SR_MAX;
+    const size_t items = ceil_div(out, sr) * n_mats;
+    size_t grid = ceil_div(items, 8);
+    if (grid > (size_t)e->sm_count * ctas_per_sm) grid = (size_t)e->sm_count * ctas_per_sm;
+    bitlinear_gemv_kernel<MT, OutT><<<(unsigned)grid, 256, 0, e->stream>>>(wq, wq_stride, tau, bias, residual, q, s, qsum, (int)t,
+                                                                           (int)k, (int)out, (int)n_mats, (int)sr, y, y_stride, acc);
+    e->launches++;
+    NNB_CHECK_LAUNCH("bitlinear_gemv_kernel");
     return NNB_OK;
 }
 
@@ -741,6 +924,11 @@ static nnb_status dispatch_fwd(nnb_engine* e, const uint32_t* wq, size_t wq_stri
                                size_t k, size_t out, OutT* y, size_t y_stride, int32_t* acc)
 {
     const size_t skinny_limit = 200 * 1024;
+    if ((int)t <= gemv_max_tokens()) {
+        if (t == 1) return launch_gemv<1, OutT>(e, wq, wq_stride, tau, bias, residual, q, s, qsum, n_mats, t, k, out, y, y_stride, acc);
+        if (t == 2) return launch_gemv<2, OutT>(e, wq, wq_stride, tau, bias, residual, q, s, qsum, n_mats, t, k, out, y, y_stride, acc);
+        return launch_gemv<4, OutT>(e, wq, wq_stride, tau, bias, residual, q, s, qsum, n_mats, t, k, out, y, y_stride, acc);
+    }
     if (t <= 8 && 8 * (k + 16) + 4096 <= skinny_limit)
         return dispatch_skinny<1, OutT>(e, wq, wq_stride, tau, bias, residual, q, s, qsum, n_mats, t,
                                         k, out, y, y_stride, acc);

@@ -139,7 +139,9 @@ def _case_tm(orc, t, k, out, seed, ternary_iid=False):
 
 
 @pytest.mark.parametrize("t,k,out", [
-    (1, 64, 32), (1, 256, 33), (3, 128, 100), (8, 256, 64), (9, 320, 48), (16, 512, 130),
+    (1, 64, 32), (1, 256, 33), (3, 128, 100), (8, 256, 64),
+    # one to four tokens run on the CUDA-core GEMV: K beyond one chunk of 32 blocks, ragged row counts, one group of rows
+    (2, 2112, 77), (4, 5632, 300), (1, 2048, 1000), (2, 64, 8), (4, 4096, 5), (1, 8640, 129), (9, 320, 48), (16, 512, 130),
     (17, 192, 96), (32, 1024, 256), (33, 256, 64), (64, 448, 200), (65, 256, 129),
     (130, 384, 257), (300, 2048, 384),
 ])
