@@ -5,7 +5,7 @@
 Used for Nsight Compute captures and quick timing; every case prints its CUDA-event time.  Cases:
   fwd          int8 ternary forward GEMM (tcgen05), T=10240 K=2048 O=11264
   dx | dw      bf16 backward GEMMs (tcgen05) of the same linear
-  gemv [M]     2-bit packed weight stream, M (16) tokens, stack of 64 matrices (2048 x 11264)
+  gemv [M [K N]]  2-bit packed weight stream, M (16) tokens, stack of 64 matrices (K 2048 x N 11264)
   attn_decode  decode attention of 512 sequences x 16 heads x 128 at position 400, fused int8 output
   train [n]    reference log-probs + one training micro-batch of n (16) sequences x 640 on the 1B policy
   rollout [B P new]   batched rollout on the 1B policy (default 512 16 24)
@@ -88,13 +88,14 @@ def main(argv):
                 _timed("bf16 dW GEMM", lambda: eng.bitlinear_bwd_tc(dy, tau, wb, q, s, k, want_dx=False, dw=dw, scratch=scratch,
                                                                     prepared=True))
     elif case == "gemv":
-        k, out, n = 2048, 11264, 64
+        k, out, n = (int(argv[3]), int(argv[4]), 64) if len(argv) > 4 else (2048, 11264, 64)
         wst = _rand_packed(dev, n, out, k // 16)
         taus = torch.rand(n, out, device=dev) * 0.05 + 0.01
         m = int(argv[2]) if len(argv) > 2 else 16
         q, s, qs = eng.act_quant_tm(torch.randn(m, k, device=dev))
         ys = torch.empty(n, m, out, device=dev)
-        _timed("packed GEMV stack", lambda: eng.bitlinear_fwd_tm_stack(wst, taus, None, q, s, qs, ys))
+        _timed(f"packed GEMV stack, {m} token(s), K {k}, N {out}, {n * (k * out // 4 + 4 * out * (1 + m)) / 1e6:.0f} MB",
+               lambda: eng.bitlinear_fwd_tm_stack(wst, taus, None, q, s, qs, ys), reps=10)
     elif case == "attn_decode":
         B, H, dk, ctx, pos = 512, 16, 128, 512, 400
         kc = torch.randn(B, H, ctx, dk, device=dev).to(torch.bfloat16)

@@ -136,19 +136,21 @@ rope_pack_kernel(const float* __restrict__ q, const float* __restrict__ k, const
     }
 }
 
-// token-major bf16 keys / values (n*S, H*dk) -> decode cache layout (n, H, alloc, dk); one CTA per row
+// token-major bf16 keys / values (n*S, H*dk) -> decode cache layout (n, H / kv_rep, alloc, dk); one CTA per row.
+// kv_rep > 1 (grouped-query attention): the rows hold every KV head kv_rep times, the cache one copy (the first).
 __global__ void __launch_bounds__(256)
-kv_to_cache_kernel(const bf16* __restrict__ k, const bf16* __restrict__ v, int S, int H, int dk, int alloc,
+kv_to_cache_kernel(const bf16* __restrict__ k, const bf16* __restrict__ v, int S, int H, int dk, int alloc, int kv_rep,
                    bf16* __restrict__ kc, bf16* __restrict__ vc)
 {
     const size_t row = blockIdx.x;
     const int b = (int)(row / S), pos = (int)(row % S);
-    const int d = H * dk;
-    for (int c = threadIdx.x * 8; c < d; c += 256 * 8) {
-        const int h = c / dk, cc = c % dk;
-        const size_t dst = (((size_t)b * H + h) * alloc + pos) * dk + cc;
-        *reinterpret_cast<uint4*>(kc + dst) = *reinterpret_cast<const uint4*>(k + row * d + c);
-        *reinterpret_cast<uint4*>(vc + dst) = *reinterpret_cast<const uint4*>(v + row * d + c);
+    const int d = H * dk, Hkv = H / kv_rep;
+    for (int c = threadIdx.x * 8; c < Hkv * dk; c += 256 * 8) {
+        const int hk = c / dk, cc = c % dk;
+        const size_t dst = (((size_t)b * Hkv + hk) * alloc + pos) * dk + cc;
+        const size_t src = row * d + (size_t)hk * kv_rep * dk + cc;
+        *reinterpret_cast<uint4*>(kc + dst) = *reinterpret_cast<const uint4*>(k + src);
+        *reinterpret_cast<uint4*>(vc + dst) = *reinterpret_cast<const uint4*>(v + src);
     }
 }
 
@@ -683,10 +685,10 @@ nnb_status launch_rope_pack_b16(nnb_engine* e, const float* q, const float* k, c
 }
 
 nnb_status launch_kv_to_cache(nnb_engine* e, const __nv_bfloat16* k, const __nv_bfloat16* v, size_t n_seq, size_t S, size_t H,
-                              size_t dk, __nv_bfloat16* kc, __nv_bfloat16* vc, size_t alloc)
+                              size_t dk, __nv_bfloat16* kc, __nv_bfloat16* vc, size_t alloc, size_t kv_rep)
 {
-    NNB_REQUIRE(dk % 8 == 0 && S <= alloc, "kv_to_cache: bad shape");
-    ab::kv_to_cache_kernel<<<(unsigned)(n_seq * S), 256, 0, e->stream>>>(k, v, (int)S, (int)H, (int)dk, (int)alloc, kc, vc);
+    NNB_REQUIRE(dk % 8 == 0 && S <= alloc && kv_rep >= 1 && H % kv_rep == 0, "kv_to_cache: bad shape");
+    ab::kv_to_cache_kernel<<<(unsigned)(n_seq * S), 256, 0, e->stream>>>(k, v, (int)S, (int)H, (int)dk, (int)alloc, (int)kv_rep, kc, vc);
     e->launches++;
     NNB_CHECK_LAUNCH("kv_to_cache_kernel");
     return NNB_OK;

@@ -134,17 +134,29 @@ nnb_status launch_bitlinear_fwd_tm(nnb_engine* e, const uint32_t* wq, size_t wq_
 nnb_status launch_row_quant(nnb_engine* e, int mode, bool exact, const float* in, const float* gamma,
                             size_t t, size_t k, size_t in_stride, int8_t* q, float* s,
                             int32_t* qsum, float* f_out);
+// Where a decode step's new projections live and how the heads map: q, k, v point at sequence 0 (rows `stride` floats
+// apart); kv_rep query heads read one key / value head (grouped-query attention; 1 = multi-head), the caches then hold
+// H / kv_rep heads.  Without it the launchers take qkv as three (B, d) planes.
+struct AttnIn {
+    const float *q, *k, *v;
+    int stride, kv_rep;
+};
+inline AttnIn attn_in_or_planes(const AttnIn* in, const float* qkv, size_t B, size_t d)
+{
+    return in ? *in : AttnIn{qkv, qkv + B * d, qkv + 2 * B * d, (int)d, 1};
+}
 nnb_status launch_attn_decode(nnb_engine* e, bool exact, const float* qkv, void* kcache, void* vcache,
                               size_t own_alloc, const void* kpre, const void* vpre, size_t pre_len, size_t pre_alloc,
                               size_t group, const float* rope_cos, const float* rope_sin, const int* d_pos, size_t B,
-                              size_t H, size_t dk, float* out, size_t kv_pitch = 0 /* elements per cached key; 0 = dk */);
+                              size_t H, size_t dk, float* out, size_t kv_pitch = 0 /* elements per cached key; 0 = dk */,
+                              const AttnIn* in = nullptr);
 size_t attn_decode_kv_pitch(bool exact, size_t dk);
 bool attn_decode_fused_supported(size_t H, size_t dk);
 nnb_status launch_attn_decode_fused(nnb_engine* e, const float* qkv, void* kcache, void* vcache, size_t own_alloc,
                                     const void* kpre, const void* vpre, size_t pre_len, size_t pre_alloc, size_t group,
                                     const float* rope_cos, const float* rope_sin, const int* d_pos, size_t B, size_t H,
                                     size_t dk, float* att, int8_t* q8, float* s, int32_t* qsum, float* pre_o = nullptr,
-                                    float* pre_ml = nullptr);
+                                    float* pre_ml = nullptr, const AttnIn* in = nullptr);
 // what the sampler applies beyond temperature and top-k (defaults = off); see sample_kernel
 struct SampleOpts {
     float temperature = 1.0f;
@@ -329,7 +341,7 @@ nnb_status launch_rope_pack_b16(nnb_engine* e, const float* q, const float* k, c
                                 const float* rope_sin, size_t T, size_t S, size_t H, size_t dk, __nv_bfloat16* out,
                                 const int* row_pos = nullptr);
 nnb_status launch_kv_to_cache(nnb_engine* e, const __nv_bfloat16* k, const __nv_bfloat16* v, size_t n_seq, size_t S, size_t H,
-                              size_t dk, __nv_bfloat16* kc, __nv_bfloat16* vc, size_t alloc);
+                              size_t dk, __nv_bfloat16* kc, __nv_bfloat16* vc, size_t alloc, size_t kv_rep = 1);
 nnb_status launch_attn_fwd_b16(nnb_engine* e, const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v,
                                size_t n_seq, size_t S, size_t H, size_t dk, float* out, float* lse, const SeqMap* map = nullptr);
 // with a grouped map, part (2 * n_seq * P * H*dk floats) receives every member's share of the prefix rows'

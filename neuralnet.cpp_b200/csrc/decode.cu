@@ -335,7 +335,7 @@ __device__ __forceinline__ float from_kv<__nv_bfloat16>(__nv_bfloat16 v) { retur
 // 2. scores_j = (q . k_j) * scale for j <= pos; softmax; out = sum_j p_j v_j
 template <typename KV, bool EXACT>
 __global__ void __launch_bounds__(128)
-attn_decode_kernel(const float* __restrict__ qkv, KV* __restrict__ kcache, KV* __restrict__ vcache, int own_alloc,
+attn_decode_kernel(const AttnIn in, KV* __restrict__ kcache, KV* __restrict__ vcache, int own_alloc,
                    const KV* __restrict__ kpre, const KV* __restrict__ vpre, int pre_len, int pre_alloc, int group,
                    const float* __restrict__ rope_cos, const float* __restrict__ rope_sin,
                    const int* __restrict__ d_pos, int B, int H, int dk, int ctx_total, float scale,
@@ -353,15 +353,16 @@ attn_decode_kernel(const float* __restrict__ qkv, KV* __restrict__ kcache, KV* _
     const int d = H * dk;
     const int pos = *d_pos;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const size_t head_off = ((size_t)b * H + h) * (size_t)own_alloc * dk;
+    const int Hkv = H / in.kv_rep, hk = h / in.kv_rep;  // grouped-query attention: kv_rep query heads read one KV head
+    const size_t head_off = ((size_t)b * Hkv + hk) * (size_t)own_alloc * dk;
     KV* kc = kcache + head_off - (size_t)pre_len * dk;   // indexed by absolute position >= pre_len
     KV* vc = vcache + head_off - (size_t)pre_len * dk;
-    const size_t pre_off = ((size_t)(b / group) * H + h) * (size_t)pre_alloc * dk;
+    const size_t pre_off = ((size_t)(b / group) * Hkv + hk) * (size_t)pre_alloc * dk;
     const KV* kp = kpre ? kpre + pre_off : nullptr;
     const KV* vp = vpre ? vpre + pre_off : nullptr;
-    const float* qn = qkv + (size_t)b * d + (size_t)h * dk;
-    const float* kn = qkv + (size_t)B * d + (size_t)b * d + (size_t)h * dk;
-    const float* vn = qkv + 2 * (size_t)B * d + (size_t)b * d + (size_t)h * dk;
+    const float* qn = in.q + (size_t)b * in.stride + (size_t)h * dk;
+    const float* kn = in.k + (size_t)b * in.stride + (size_t)hk * dk;
+    const float* vn = in.v + (size_t)b * in.stride + (size_t)hk * dk;
 
     // 1. RoPE + append
     if (rope_cos) {
@@ -477,7 +478,7 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi)
 // every key starts on a 16-byte boundary (head size 100 -> pitch 104; the pad features are kept at zero).
 template <int DK, int DKP>
 __global__ void __launch_bounds__(128)
-attn_decode_bf16_kernel(const float* __restrict__ qkv, __nv_bfloat16* __restrict__ kcache, __nv_bfloat16* __restrict__ vcache,
+attn_decode_bf16_kernel(const AttnIn in, __nv_bfloat16* __restrict__ kcache, __nv_bfloat16* __restrict__ vcache,
                         int own_alloc, const __nv_bfloat16* __restrict__ kpre, const __nv_bfloat16* __restrict__ vpre,
                         int pre_len, int pre_alloc, int group, const float* __restrict__ rope_cos,
                         const float* __restrict__ rope_sin, const int* __restrict__ d_pos, int B, int H, int ctx_total,
@@ -499,15 +500,16 @@ attn_decode_bf16_kernel(const float* __restrict__ qkv, __nv_bfloat16* __restrict
     const int d = H * DK;
     const int pos = *d_pos;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const size_t head_off = ((size_t)b * H + h) * (size_t)own_alloc * DKP;
+    const int Hkv = H / in.kv_rep, hk = h / in.kv_rep;  // grouped-query attention: kv_rep query heads read one KV head
+    const size_t head_off = ((size_t)b * Hkv + hk) * (size_t)own_alloc * DKP;
     __nv_bfloat16* kc = kcache + head_off - (size_t)pre_len * DKP;  // indexed by absolute position >= pre_len
     __nv_bfloat16* vc = vcache + head_off - (size_t)pre_len * DKP;
-    const size_t pre_off = ((size_t)(b / group) * H + h) * (size_t)pre_alloc * DKP;
+    const size_t pre_off = ((size_t)(b / group) * Hkv + hk) * (size_t)pre_alloc * DKP;
     const __nv_bfloat16* kp = kpre ? kpre + pre_off : nullptr;
     const __nv_bfloat16* vp = vpre ? vpre + pre_off : nullptr;
-    const float* qn = qkv + (size_t)b * d + (size_t)h * DK;
-    const float* kn = qkv + (size_t)B * d + (size_t)b * d + (size_t)h * DK;
-    const float* vn = qkv + 2 * (size_t)B * d + (size_t)b * d + (size_t)h * DK;
+    const float* qn = in.q + (size_t)b * in.stride + (size_t)h * DK;
+    const float* kn = in.k + (size_t)b * in.stride + (size_t)hk * DK;
+    const float* vn = in.v + (size_t)b * in.stride + (size_t)hk * DK;
 
     if (rope_cos) {
         constexpr int half = DK / 2;
@@ -623,7 +625,7 @@ template <int DK, int DKP = DK>
 static nnb_status launch_attn_decode_bf16(nnb_engine* e, const float* qkv, void* kcache, void* vcache, size_t own_alloc,
                                           const void* kpre, const void* vpre, size_t pre_len, size_t pre_alloc, size_t group,
                                           const float* rope_cos, const float* rope_sin, const int* d_pos, size_t B, size_t H,
-                                          float* out)
+                                          float* out, const AttnIn& in)
 {
     const size_t ctx_total = pre_len + own_alloc;
     constexpr size_t G = 4 * (32 / (DKP <= 64 ? 8 : 16));
@@ -635,7 +637,8 @@ static nnb_status launch_attn_decode_bf16(nnb_engine* e, const float* qkv, void*
         NNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         cfg = smem;
     }
-    kern<<<(unsigned)(B * H), 128, smem, e->stream>>>(qkv, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, (int)own_alloc,
+    (void)qkv;
+    kern<<<(unsigned)(B * H), 128, smem, e->stream>>>(in, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, (int)own_alloc,
                                                       (const __nv_bfloat16*)kpre, (const __nv_bfloat16*)vpre, (int)pre_len,
                                                       (int)pre_alloc, (int)group, rope_cos, rope_sin, d_pos, (int)B, (int)H,
                                                       (int)ctx_total, 1.0f / sqrtf((float)DK), out);
@@ -673,7 +676,7 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
 // sequence's own positions.  grid (n_groups, H/4), 128 threads; queries are rounded to bf16 here.
 template <int DK>
 __global__ void __launch_bounds__(128)
-attn_prefix_kernel(const float* __restrict__ qkv, const __nv_bfloat16* __restrict__ kpre, const __nv_bfloat16* __restrict__ vpre,
+attn_prefix_kernel(const AttnIn in, const __nv_bfloat16* __restrict__ kpre, const __nv_bfloat16* __restrict__ vpre,
                    int pre_len, int pre_alloc, int group, const float* __restrict__ rope_cos, const float* __restrict__ rope_sin,
                    const int* __restrict__ d_pos, int B, int H, float scale, float* __restrict__ pre_o, float* __restrict__ pre_ml)
 {
@@ -693,7 +696,7 @@ attn_prefix_kernel(const float* __restrict__ qkv, const __nv_bfloat16* __restric
         const int r = lane >> 1;               // member of the group
         const int j0 = (lane & 1) * (half / 2);  // first of this lane's half/2 rotation pairs
         const bool ok = r < group;
-        const float* qn = qkv + (size_t)(grp * group + (ok ? r : 0)) * d + (size_t)h * DK;
+        const float* qn = in.q + (size_t)(grp * group + (ok ? r : 0)) * in.stride + (size_t)h * DK;
         for (int j = j0; j < j0 + half / 2; j += 4) {
             float4 a = make_float4(0.f, 0.f, 0.f, 0.f), bq = a;
             if (ok) {
@@ -719,7 +722,7 @@ attn_prefix_kernel(const float* __restrict__ qkv, const __nv_bfloat16* __restric
 #pragma unroll
     for (int ks = 0; ks < DK / 16; ++ks) ldsm_b16(qf[ks], Qs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LD + ks * 16 + 8 * (lane >> 4));
 
-    const size_t pre_off = ((size_t)grp * H + h) * (size_t)pre_alloc * DK;
+    const size_t pre_off = ((size_t)grp * (H / in.kv_rep) + h / in.kv_rep) * (size_t)pre_alloc * DK;
     const __nv_bfloat16* kp = kpre + pre_off;
     const __nv_bfloat16* vp = vpre + pre_off;
     float o[DK / 8][4];
@@ -834,7 +837,7 @@ attn_prefix_kernel(const float* __restrict__ qkv, const __nv_bfloat16* __restric
 // keeps > 100 KB of cache reads outstanding per SM.  att (B, d) f32 is optional.
 template <int DK, int U, int MAXT>
 __global__ void __launch_bounds__(MAXT)
-attn_decode_fused_kernel(const float* __restrict__ qkv, __nv_bfloat16* __restrict__ kcache, __nv_bfloat16* __restrict__ vcache,
+attn_decode_fused_kernel(const AttnIn in, __nv_bfloat16* __restrict__ kcache, __nv_bfloat16* __restrict__ vcache,
                          int own_alloc, const __nv_bfloat16* __restrict__ kpre, const __nv_bfloat16* __restrict__ vpre,
                          int pre_len, int pre_alloc, int group, const float* __restrict__ rope_cos,
                          const float* __restrict__ rope_sin, const int* __restrict__ d_pos, int B, int H, int ctx_pad,
@@ -858,15 +861,16 @@ attn_decode_fused_kernel(const float* __restrict__ qkv, __nv_bfloat16* __restric
     pdl_wait();
     const int pos = *d_pos;
     float* sc = sc_all + (size_t)h * ctx_pad;
-    const size_t head_off = ((size_t)b * H + h) * (size_t)own_alloc * DK;
+    const int Hkv = H / in.kv_rep, hk = h / in.kv_rep;  // the warps of a KV group append the same key and value
+    const size_t head_off = ((size_t)b * Hkv + hk) * (size_t)own_alloc * DK;
     __nv_bfloat16* kc = kcache + head_off - (size_t)pre_len * DK;  // indexed by absolute position >= pre_len
     __nv_bfloat16* vc = vcache + head_off - (size_t)pre_len * DK;
-    const size_t pre_off = ((size_t)(b / group) * H + h) * (size_t)pre_alloc * DK;
+    const size_t pre_off = ((size_t)(b / group) * Hkv + hk) * (size_t)pre_alloc * DK;
     const __nv_bfloat16* kp = kpre ? kpre + pre_off : nullptr;
     const __nv_bfloat16* vp = vpre ? vpre + pre_off : nullptr;
-    const float* qn = qkv + (size_t)b * d + (size_t)h * DK;
-    const float* kn = qkv + (size_t)B * d + (size_t)b * d + (size_t)h * DK;
-    const float* vn = qkv + 2 * (size_t)B * d + (size_t)b * d + (size_t)h * DK;
+    const float* qn = in.q + (size_t)b * in.stride + (size_t)h * DK;
+    const float* kn = in.k + (size_t)b * in.stride + (size_t)hk * DK;
+    const float* vn = in.v + (size_t)b * in.stride + (size_t)hk * DK;
 
     const int sub = lane / LPK, sl = lane % LPK;
     const int e0 = sl * 8;
@@ -1055,9 +1059,12 @@ bool attn_decode_fused_supported(size_t H, size_t dk) { return (dk == 64 || dk =
 nnb_status launch_attn_decode_fused(nnb_engine* e, const float* qkv, void* kcache, void* vcache, size_t own_alloc,
                                     const void* kpre, const void* vpre, size_t pre_len, size_t pre_alloc, size_t group,
                                     const float* rope_cos, const float* rope_sin, const int* d_pos, size_t B, size_t H,
-                                    size_t dk, float* att, int8_t* q8, float* s, int32_t* qsum, float* pre_o, float* pre_ml)
+                                    size_t dk, float* att, int8_t* q8, float* s, int32_t* qsum, float* pre_o, float* pre_ml,
+                                    const AttnIn* in_opt)
 {
     NNB_REQUIRE(attn_decode_fused_supported(H, dk), "attn_decode_fused: %zu heads of %zu features unsupported", H, dk);
+    const AttnIn in = attn_in_or_planes(in_opt, qkv, B, H * dk);
+    NNB_REQUIRE(in.kv_rep >= 1 && H % (size_t)in.kv_rep == 0, "attn_decode_fused: %zu heads do not divide into KV groups of %d", H, in.kv_rep);
     NNB_REQUIRE((pre_o == nullptr) == (pre_ml == nullptr), "attn_decode_fused: pre_o and pre_ml go together");
     // a shared prefix read by groups of at most 16 sequences is attended to once per group
     const bool batched_prefix = pre_o && pre_len > 0 && group > 1 && group <= 16 && B % group == 0;
@@ -1072,11 +1079,11 @@ nnb_status launch_attn_decode_fused(nnb_engine* e, const float* qkv, void* kcach
             cfg_p = true;
         }
         if (dk == 128)
-            attn_prefix_kernel<128><<<grid_p, 128, smem_p, e->stream>>>(qkv, (const __nv_bfloat16*)kpre, (const __nv_bfloat16*)vpre,
+            attn_prefix_kernel<128><<<grid_p, 128, smem_p, e->stream>>>(in, (const __nv_bfloat16*)kpre, (const __nv_bfloat16*)vpre,
                                                                        (int)pre_len, (int)pre_alloc, (int)group, rope_cos, rope_sin,
                                                                        d_pos, (int)B, (int)H, scale_p, pre_o, pre_ml);
         else
-            attn_prefix_kernel<64><<<grid_p, 128, smem_p, e->stream>>>(qkv, (const __nv_bfloat16*)kpre, (const __nv_bfloat16*)vpre,
+            attn_prefix_kernel<64><<<grid_p, 128, smem_p, e->stream>>>(in, (const __nv_bfloat16*)kpre, (const __nv_bfloat16*)vpre,
                                                                       (int)pre_len, (int)pre_alloc, (int)group, rope_cos, rope_sin,
                                                                       d_pos, (int)B, (int)H, scale_p, pre_o, pre_ml);
         e->launches++;
@@ -1102,7 +1109,7 @@ nnb_status launch_attn_decode_fused(nnb_engine* e, const float* qkv, void* kcach
             NNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                 \
             cfg = smem;                                                                                                   \
         }                                                                                                                 \
-        launch_ex(e, kern, dim3((unsigned)B), dim3((unsigned)(32 * H)), smem, qkv, (__nv_bfloat16*)kcache,                \
+        launch_ex(e, kern, dim3((unsigned)B), dim3((unsigned)(32 * H)), smem, in, (__nv_bfloat16*)kcache,                 \
                   (__nv_bfloat16*)vcache, (int)own_alloc, (const __nv_bfloat16*)kpre, (const __nv_bfloat16*)vpre, (int)pre_len, \
                   (int)pre_alloc, (int)group, rope_cos, rope_sin, d_pos, (int)B, (int)H, (int)ctx_pad, scale, att, q8, s, qsum, \
                   use_o, use_ml);                                                                                            \
@@ -1122,22 +1129,24 @@ size_t attn_decode_kv_pitch(bool exact, size_t dk) { return (!exact && dk == 100
 nnb_status launch_attn_decode(nnb_engine* e, bool exact, const float* qkv, void* kcache, void* vcache,
                               size_t own_alloc, const void* kpre, const void* vpre, size_t pre_len, size_t pre_alloc,
                               size_t group, const float* rope_cos, const float* rope_sin, const int* d_pos, size_t B,
-                              size_t H, size_t dk, float* out, size_t kv_pitch)
+                              size_t H, size_t dk, float* out, size_t kv_pitch, const AttnIn* in_opt)
 {
     if (kv_pitch == 0) kv_pitch = dk;
+    const AttnIn in = attn_in_or_planes(in_opt, qkv, B, H * dk);
+    NNB_REQUIRE(in.kv_rep >= 1 && H % (size_t)in.kv_rep == 0, "attn_decode: %zu heads do not divide into KV groups of %d", H, in.kv_rep);
     NNB_REQUIRE(kv_pitch == dk || kv_pitch == attn_decode_kv_pitch(exact, dk), "attn_decode: cache pitch %zu unsupported for head size %zu",
                 kv_pitch, dk);
     NNB_REQUIRE(dk % 4 == 0 && dk <= 128 && dk >= 8, "attn_decode: head dim %zu unsupported (multiple of 4, <= 128)", dk);
     NNB_REQUIRE(group >= 1 && (pre_len == 0 || (kpre && vpre)), "attn_decode: bad prefix arguments");
     if (!exact && dk == 128)
         return launch_attn_decode_bf16<128>(e, qkv, kcache, vcache, own_alloc, kpre, vpre, pre_len, pre_alloc, group, rope_cos,
-                                            rope_sin, d_pos, B, H, out);
+                                            rope_sin, d_pos, B, H, out, in);
     if (!exact && dk == 64)
         return launch_attn_decode_bf16<64>(e, qkv, kcache, vcache, own_alloc, kpre, vpre, pre_len, pre_alloc, group, rope_cos,
-                                           rope_sin, d_pos, B, H, out);
+                                           rope_sin, d_pos, B, H, out, in);
     if (!exact && dk == 100 && kv_pitch == 104)  // caches of pitch attn_decode_kv_pitch(false, 100)
         return launch_attn_decode_bf16<100, 104>(e, qkv, kcache, vcache, own_alloc, kpre, vpre, pre_len, pre_alloc, group,
-                                                 rope_cos, rope_sin, d_pos, B, H, out);
+                                                 rope_cos, rope_sin, d_pos, B, H, out, in);
     const float scale = 1.0f / sqrtf((float)dk);
     const size_t acc_sz = exact ? 8 : 4;
     const size_t ctx_total = pre_len + own_alloc;
@@ -1151,7 +1160,7 @@ nnb_status launch_attn_decode(nnb_engine* e, bool exact, const float* qkv, void*
             NNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             cfg = smem;
         }
-        kern<<<grid, 128, smem, e->stream>>>(qkv, (float*)kcache, (float*)vcache, (int)own_alloc, (const float*)kpre,
+        kern<<<grid, 128, smem, e->stream>>>(in, (float*)kcache, (float*)vcache, (int)own_alloc, (const float*)kpre,
                                              (const float*)vpre, (int)pre_len, (int)pre_alloc, (int)group, rope_cos, rope_sin,
                                              d_pos, (int)B, (int)H, (int)dk, (int)ctx_total, scale, out);
     } else {
@@ -1161,7 +1170,7 @@ nnb_status launch_attn_decode(nnb_engine* e, bool exact, const float* qkv, void*
             NNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             cfg = smem;
         }
-        kern<<<grid, 128, smem, e->stream>>>(qkv, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, (int)own_alloc,
+        kern<<<grid, 128, smem, e->stream>>>(in, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, (int)own_alloc,
                                              (const __nv_bfloat16*)kpre, (const __nv_bfloat16*)vpre, (int)pre_len,
                                              (int)pre_alloc, (int)group, rope_cos, rope_sin, d_pos, (int)B, (int)H, (int)dk,
                                              (int)ctx_total, scale, out);

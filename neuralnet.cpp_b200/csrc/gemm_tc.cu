@@ -952,7 +952,7 @@ scale_colsum_kernel(const float* __restrict__ dy, const float* __restrict__ tau,
     *reinterpret_cast<float2*>(part + (size_t)blockIdx.y * O + o) = make_float2(sa, sb);
 }
 
-// the same with four adjacent columns per thread (16-byte loads, four rows in flight): out, ld multiples of 4
+// the same with four adjacent columns per thread (16-byte loads, eight rows in flight): out, ld multiples of 4
 __global__ void __launch_bounds__(128)
 scale_colsum4_kernel(const float* __restrict__ dy, const float* __restrict__ tau, int T, int O, int chunk,
                      __nv_bfloat16* __restrict__ out, size_t ld, float* __restrict__ part)
@@ -963,12 +963,12 @@ scale_colsum4_kernel(const float* __restrict__ dy, const float* __restrict__ tau
     const float4 tv = *reinterpret_cast<const float4*>(tau + o);
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     int t = t0;
-    for (; t + 4 <= t1; t += 4) {
-        float4 v[4];
+    for (; t + 8 <= t1; t += 8) {
+        float4 v[8];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) v[u] = *reinterpret_cast<const float4*>(dy + (size_t)(t + u) * O + o);
+        for (int u = 0; u < 8; ++u) v[u] = *reinterpret_cast<const float4*>(dy + (size_t)(t + u) * O + o);
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < 8; ++u) {
             acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w;
             const __nv_bfloat162 p0 = __floats2bfloat162_rn(v[u].x * tv.x, v[u].y * tv.y);
             const __nv_bfloat162 p1 = __floats2bfloat162_rn(v[u].z * tv.z, v[u].w * tv.w);

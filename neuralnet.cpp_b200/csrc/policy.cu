@@ -244,7 +244,7 @@ static nnb_status ensure_decode(nnb_policy* p, size_t B, size_t ctx_alloc, size_
     const nnb_gpt_config& c = p->cfg;
     const size_t d = c.d_model, F = c.d_ff, V = c.vocab, F1 = act_gated(c.act) ? 2 * F : F;
     const size_t kv_elem = c.exact ? 4 : 2;
-    const size_t dkv = c.n_head * attn_decode_kv_pitch(c.exact != 0, d / c.n_head);  // cached features per position
+    const size_t dkv = cfg_kv_heads(c) * attn_decode_kv_pitch(c.exact != 0, d / c.n_head);  // cached features per position
     const size_t kv_bytes = (size_t)c.n_layer * B * dkv * ctx_alloc * kv_elem;
     const size_t pre_bytes = (size_t)c.n_layer * (B / group) * dkv * pre_len * kv_elem;
     const size_t total = tok_cols;
@@ -351,11 +351,13 @@ static nnb_status decode_step(nnb_policy* p, const StepView& sv, bool with_head,
     for (int l = 0; l < c.n_layer; ++l) {
         const LayerW& L = p->layers[l];
         NNB_TRY(launch_row_quant(e, 0, exact, w.x, P + L.ln1_g, B, d, d, w.q8, w.s, w.qsum, nullptr));
+        AttnIn ain = attn_in_or_planes(nullptr, w.qkv, B, d);
         if (gqa) {
-            // one matrix of d + 2 dkv rows, then the KV heads are replicated to the query heads' count: the attention
-            // kernels and the cache see plain multi-head attention, as the reference's gather_rows expansion does
+            // one matrix of d + 2 dkv rows; the attention kernels map query head h to KV head h / (H / Hkv) themselves and
+            // the cache holds the Hkv heads only (the reference expands K and V to H heads instead: same numbers)
+            const size_t wq = d + 2 * Hkv * dk;
             NNB_TRY(policy_linear_fwd(p, L.qkv, 1, w.q8, w.s, w.qsum, B, nullptr, w.qkv_raw, 0));
-            NNB_TRY(launch_gqa_expand(e, w.qkv_raw, B, H, Hkv, dk, w.qkv));
+            ain = AttnIn{w.qkv_raw, w.qkv_raw + d, w.qkv_raw + d + Hkv * dk, (int)wq, (int)(H / Hkv)};
         } else {
             // q, k, v projections: three equally shaped matrices stored back to back, one launch
             NNB_TRY(policy_linear_fwd(p, L.q, 3, w.q8, w.s, w.qsum, B, nullptr, w.qkv, B * d));
@@ -377,10 +379,10 @@ static nnb_status decode_step(nnb_policy* p, const StepView& sv, bool with_head,
             // all heads of a sequence in one CTA, attention output quantised in the same launch
             NNB_TRY(launch_attn_decode_fused(e, w.qkv, kl, vl, sv.own_alloc, kpl, vpl, sv.pre_len, sv.pre_alloc, sv.group,
                                              c.pos == 1 ? p->rope_cos : nullptr, c.pos == 1 ? p->rope_sin : nullptr, w.d_pos, B, H,
-                                             dk, nullptr, w.q8, w.s, w.qsum, w.att, w.pre_ml));
+                                             dk, nullptr, w.q8, w.s, w.qsum, w.att, w.pre_ml, &ain));
         } else {
             NNB_TRY(launch_attn_decode(e, exact, w.qkv, kl, vl, sv.own_alloc, kpl, vpl, sv.pre_len, sv.pre_alloc, sv.group,
-                                       p->rope_cos, p->rope_sin, w.d_pos, B, H, dk, w.att, attn_decode_kv_pitch(exact, dk)));
+                                       p->rope_cos, p->rope_sin, w.d_pos, B, H, dk, w.att, attn_decode_kv_pitch(exact, dk), &ain));
             // SubLN: the heads' output is normalised before it is quantised for the o projection
             NNB_TRY(launch_row_quant(e, c.sub_ln ? 0 : 3, exact, w.att, c.sub_ln ? P + L.attn_sub_g : nullptr, B, d, d, w.q8, w.s,
                                      w.qsum, nullptr));
@@ -482,7 +484,7 @@ nnb_status policy_rollout(nnb_policy* p, const int32_t* d_prompts, size_t B, siz
     }
     const size_t V = c.vocab, d = c.d_model;
     const size_t kv_elem = c.exact ? 4 : 2;
-    const size_t dkv = c.n_head * attn_decode_kv_pitch(c.exact != 0, d / c.n_head);
+    const size_t dkv = cfg_kv_heads(c) * attn_decode_kv_pitch(c.exact != 0, d / c.n_head);
     const size_t Bg = B / group;
     StepView main_view{B, w.tokens, total, w.k, w.v, own, B * dkv * own * kv_elem, w.k_pre, w.v_pre, pre_len, pre_len,
                        Bg * dkv * pre_len * kv_elem, group};

@@ -278,7 +278,7 @@ static nnb_status forward(nnb_policy* p, const int32_t* tokens, size_t n_seq, si
             if (sink)
                 NNB_TRY(launch_kv_to_cache(e, s.qkvb + T * d, s.qkvb + 2 * T * d, n_seq, S, H, dk,
                                            (__nv_bfloat16*)((char*)sink->k + (size_t)l * sink->layer_bytes),
-                                           (__nv_bfloat16*)((char*)sink->v + (size_t)l * sink->layer_bytes), sink->alloc));
+                                           (__nv_bfloat16*)((char*)sink->v + (size_t)l * sink->layer_bytes), sink->alloc, H / Hkv));
             NNB_TRY(launch_attn_fwd_b16(e, s.qkvb, s.qkvb + T * d, s.qkvb + 2 * T * d, n_seq, S, H, dk, s.att, s.lse, &w->map));
         } else {
             if (c.pos == 1) {

@@ -701,6 +701,223 @@ static nnb_status launch_cfg(nnb_engine* e, const uint32_t* wq, size_t wq_stride
 }
 
 
+// ------------------------------------------------------- weight streamer with register-resident activations
+// The skinny kernel above reads an activation fragment from shared memory for every weight word it multiplies, which
+// makes the shared-memory pipe its bound (measured 90 % busy at half of the HBM rate).  Here the eight warps of a CTA
+// split K once and for all: a warp owns at most BPW 64-feature blocks and keeps their activation fragments (4
+// registers per block and token tile) for the CTA's lifetime, loaded once through the same shared-memory staging and
+// ldmatrix addressing.  Inside the loop nothing but packed weights moves: every lane fetches the two words per block and
+// 16-row slab it needs for the next item while the tensor cores work on the current one; the warps' partial sums meet in
+// shared memory once per item (MS slabs of 16 rows).
+template <int NT, int BPW, int MS, typename OutT>
+__global__ void __launch_bounds__(256)
+bitlinear_stream_kernel(const uint32_t* __restrict__ wq, size_t wq_stride_words, const float* __restrict__ tau,
+                        const float* __restrict__ bias, const float* __restrict__ residual, const int8_t* __restrict__ q,
+                        const float* __restrict__ s, const int32_t* __restrict__ qsum, int T, int K, int OUT, int n_mats,
+                        OutT* __restrict__ y, size_t y_stride_elems, int32_t* __restrict__ acc_out)
+{
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int row_stride = K + 16;
+    unsigned char* Bs = smem;
+    const int tid = threadIdx.x, lane = tid & 31, wk = tid >> 5;
+    const int g = lane >> 2, t4 = lane & 3;
+    {
+        const int units_per_row = K / 16;
+        const int total = NT * 8 * units_per_row;
+        for (int i = tid; i < total; i += 256) {
+            const int r = i / units_per_row, u = i - r * units_per_row;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (r < T) v = *reinterpret_cast<const uint4*>(q + (size_t)r * K + u * 16);
+            *reinterpret_cast<uint4*>(Bs + (size_t)r * row_stride + u * 16) = v;
+        }
+    }
+    __syncthreads();
+    const int words_per_row = K / 16;
+    const int nblk = K / 64;
+    const int blk_lo = (int)(((long long)nblk * wk) / 8);
+    const int blk_hi = (int)(((long long)nblk * (wk + 1)) / 8);
+    uint32_t frag[BPW][NT][4];
+    {
+        const unsigned char* b_lane = Bs + (size_t)(lane & 7) * row_stride + (lane >> 3) * 16;
+#pragma unroll
+        for (int u = 0; u < BPW; ++u)
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                if (blk_lo + u < blk_hi) {
+                    ldmatrix_x4(frag[u][nt], b_lane + (size_t)nt * 8 * row_stride + (size_t)(blk_lo + u) * 64);
+                } else {
+                    frag[u][nt][0] = frag[u][nt][1] = frag[u][nt][2] = frag[u][nt][3] = 0u;
+                }
+            }
+    }
+    __syncthreads();
+    // the staging area is free now: it holds the warps' partial sums
+    int* red = reinterpret_cast<int*>(smem);
+
+    const int mtiles = (OUT + 16 * MS - 1) / (16 * MS);
+    const int n_items = mtiles * n_mats;
+    uint32_t cur[MS][BPW][2], nxt[MS][BPW][2];
+    auto fetch = [&](int item, uint32_t(&dst)[MS][BPW][2]) {
+        const int mat = item / mtiles, mt = item - mat * mtiles;
+        const uint32_t* wm = wq + (size_t)mat * wq_stride_words;
+#pragma unroll
+        for (int ms = 0; ms < MS; ++ms) {
+            const int r_lo = (mt * MS + ms) * 16 + g, r_hi = r_lo + 8;
+            const uint32_t* p_lo = wm + (size_t)(r_lo < OUT ? r_lo : 0) * words_per_row + t4;
+            const uint32_t* p_hi = wm + (size_t)(r_hi < OUT ? r_hi : 0) * words_per_row + t4;
+#pragma unroll
+            for (int u = 0; u < BPW; ++u) {
+                const int b = blk_lo + u;
+                const bool in = b < blk_hi && item < n_items;
+                dst[ms][u][0] = (in && r_lo < OUT) ? __ldg(p_lo + 4 * b) : 0u;
+                dst[ms][u][1] = (in && r_hi < OUT) ? __ldg(p_hi + 4 * b) : 0u;
+            }
+        }
+    };
+    int item = blockIdx.x;
+    fetch(item, cur);
+    for (; item < n_items; item += gridDim.x) {
+        fetch(item + gridDim.x, nxt);
+        int acc[MS][NT][4];
+#pragma unroll
+        for (int ms = 0; ms < MS; ++ms)
+#pragma unroll
+            for (int j = 0; j < NT; ++j)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) acc[ms][j][c] = 0;
+        constexpr uint32_t MSK = 0x03030303u;
+#pragma unroll
+        for (int u = 0; u < BPW; ++u)
+#pragma unroll
+            for (int ms = 0; ms < MS; ++ms) {
+                const uint32_t w_lo = cur[ms][u][0], w_hi = cur[ms][u][1];
+                const uint32_t a0 = w_lo & MSK, a1 = w_hi & MSK, a2 = (w_lo >> 2) & MSK, a3 = (w_hi >> 2) & MSK;
+                const uint32_t c0 = (w_lo >> 4) & MSK, c1 = (w_hi >> 4) & MSK, c2 = (w_lo >> 6) & MSK, c3 = (w_hi >> 6) & MSK;
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    mma_u8s8(acc[ms][nt], a0, a1, a2, a3, frag[u][nt][0], frag[u][nt][1]);
+                    mma_u8s8(acc[ms][nt], c0, c1, c2, c3, frag[u][nt][2], frag[u][nt][3]);
+                }
+            }
+        // warps 1..7 park their partial sums, warp 0 adds them up and writes the rows
+        constexpr int PER = MS * NT * 4;
+        if (wk > 0) {
+            int* slot = red + ((size_t)(wk - 1) * 32 + lane) * PER;
+#pragma unroll
+            for (int ms = 0; ms < MS; ++ms)
+#pragma unroll
+                for (int j = 0; j < NT; ++j)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) slot[(ms * NT + j) * 4 + c] = acc[ms][j][c];
+        }
+        __syncthreads();
+        if (wk == 0) {
+#pragma unroll
+            for (int o = 0; o < 7; ++o) {
+                const int* src = red + ((size_t)o * 32 + lane) * PER;
+#pragma unroll
+                for (int ms = 0; ms < MS; ++ms)
+#pragma unroll
+                    for (int j = 0; j < NT; ++j)
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) acc[ms][j][c] += src[(ms * NT + j) * 4 + c];
+            }
+            const int mat = item / mtiles, mt = item - mat * mtiles;
+            const float* tau_m = tau + (size_t)mat * OUT;
+            const float* bias_m = bias ? bias + (size_t)mat * OUT : nullptr;
+            OutT* y_m = y + (size_t)mat * y_stride_elems;
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+                for (int cc = 0; cc < 2; ++cc) {
+                    const int tok = nt * 8 + t4 * 2 + cc;
+                    if (tok >= T) continue;
+                    const int qs2 = 2 * qsum[tok];
+                    const float st = s[tok];
+#pragma unroll
+                    for (int ms = 0; ms < MS; ++ms) {
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const int row = (mt * MS + ms) * 16 + g + h * 8;
+                            if (row >= OUT) continue;
+                            const int a = acc[ms][nt][h * 2 + cc] - qs2;
+                            float v = __fmul_rn(__fmul_rn(tau_m[row], st), (float)a);
+                            if (bias_m) v = __fadd_rn(v, bias_m[row]);
+                            if (residual) v = __fadd_rn(residual[(size_t)tok * OUT + row], v);
+                            store_out<OutT>(y_m + (size_t)tok * OUT + row, v);
+                            if (acc_out) acc_out[(size_t)tok * OUT + row] = a;
+                        }
+                    }
+                }
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int ms = 0; ms < MS; ++ms)
+#pragma unroll
+            for (int u = 0; u < BPW; ++u) {
+                cur[ms][u][0] = nxt[ms][u][0];
+                cur[ms][u][1] = nxt[ms][u][1];
+            }
+    }
+}
+
+// NNB_STREAM=0 in the environment turns the register-resident streamer off (for A/B timing)
+static bool stream_enabled()
+{
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("NNB_STREAM");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v != 0;
+}
+
+template <int NT, int BPW, int MS, typename OutT>
+static nnb_status launch_stream(nnb_engine* e, const uint32_t* wq, size_t wq_stride, const float* tau, const float* bias,
+                                const float* residual, const int8_t* q, const float* s, const int32_t* qsum, size_t n_mats,
+                                size_t t, size_t k, size_t out, OutT* y, size_t y_stride, int32_t* acc)
+{
+    const size_t stage = (size_t)NT * 8 * (k + 16), red = (size_t)7 * 32 * MS * NT * 4 * sizeof(int);
+    const size_t smem = stage > red ? stage : red;
+    auto kern = bitlinear_stream_kernel<NT, BPW, MS, OutT>;
+    static size_t cfg_dev[64] = {}; size_t& configured = cfg_dev[e->device & 63];  // the attribute is per device
+    if (smem > configured) {
+        NNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = smem;
+    }
+    const size_t n_items = ceil_div(out, 16 * MS) * n_mats;
+    // persistent CTAs: as many as are resident together (registers and shared memory decide), each walks the items
+    int resident = 0;
+    NNB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kern, 256, smem));
+    if (resident < 1) resident = 1;
+    if (resident > 4) resident = 4;
+    size_t grid = n_items;
+    if (grid > (size_t)e->sm_count * resident) grid = (size_t)e->sm_count * resident;
+    kern<<<(unsigned)grid, 256, smem, e->stream>>>(wq, wq_stride, tau, bias, residual, q, s, qsum, (int)t, (int)k, (int)out,
+                                                   (int)n_mats, y, y_stride, acc);
+    e->launches++;
+    NNB_CHECK_LAUNCH("bitlinear_stream_kernel");
+    return NNB_OK;
+}
+
+// picks the streamer's shape: eight warps split the K / 64 blocks, at most BPW each
+template <int NT, typename OutT>
+static bool try_stream(nnb_engine* e, const uint32_t* wq, size_t wq_stride, const float* tau, const float* bias,
+                       const float* residual, const int8_t* q, const float* s, const int32_t* qsum, size_t n_mats, size_t t,
+                       size_t k, size_t out, OutT* y, size_t y_stride, int32_t* acc, nnb_status* st)
+{
+    if (!stream_enabled()) return false;
+    const size_t bpw = ceil_div(k / 64, 8);
+    // enough items to give every CTA a few rounds; small problems stay on the kernels that split K less
+    if (ceil_div(out, 32) * n_mats < (size_t)e->sm_count * 4) return false;
+    if (bpw <= 4) *st = launch_stream<NT, 4, 2, OutT>(e, wq, wq_stride, tau, bias, residual, q, s, qsum, n_mats, t, k, out, y, y_stride, acc);
+    else if (bpw <= 8) *st = launch_stream<NT, 8, 2, OutT>(e, wq, wq_stride, tau, bias, residual, q, s, qsum, n_mats, t, k, out, y, y_stride, acc);
+    else if (bpw <= 12 && NT == 1) *st = launch_stream<NT, 12, 1, OutT>(e, wq, wq_stride, tau, bias, residual, q, s, qsum, n_mats, t, k, out, y, y_stride, acc);
+    else return false;
+    return true;
+}
+
 // ------------------------------------------------------- CUDA-core GEMV (one to four tokens)
 // At a handful of tokens the tensor-core kernels spend their shared-memory bandwidth on activation fragments that are
 // mostly padding (token tiles of 8): the shared-memory pipe, not HBM, bounds them.  Here nothing but the packed weights
@@ -853,7 +1070,7 @@ static int gemv_max_tokens()
     static int v = -1;
     if (v < 0) {
         const char* e = getenv("NNB_GEMV_MAX_T");
-        v = e ? atoi(e) : 4;
+        v = e ? atoi(e) : 1;
         if (v < 0) v = 0;
         if (v > 4) v = 4;
     }
@@ -924,10 +1141,21 @@ static nnb_status dispatch_fwd(nnb_engine* e, const uint32_t* wq, size_t wq_stri
                                size_t k, size_t out, OutT* y, size_t y_stride, int32_t* acc)
 {
     const size_t skinny_limit = 200 * 1024;
-    if ((int)t <= gemv_max_tokens()) {
+    // CUDA-core GEMV: measured against the tensor-core kernels on stacks of 64 matrices it wins at one token when K fills
+    // the lanes (K 2048: 84 against 114 us, K 5632: 55 against 106 us) and loses from two tokens on (ALU-bound)
+    if ((int)t <= gemv_max_tokens() && (k / 64) * 4 >= ceil_div(k / 64, 32) * 32 * 3) {
         if (t == 1) return launch_gemv<1, OutT>(e, wq, wq_stride, tau, bias, residual, q, s, qsum, n_mats, t, k, out, y, y_stride, acc);
         if (t == 2) return launch_gemv<2, OutT>(e, wq, wq_stride, tau, bias, residual, q, s, qsum, n_mats, t, k, out, y, y_stride, acc);
         return launch_gemv<4, OutT>(e, wq, wq_stride, tau, bias, residual, q, s, qsum, n_mats, t, k, out, y, y_stride, acc);
+    }
+    {
+        nnb_status st = NNB_OK;
+        if (t <= 8 && 8 * (k + 16) <= skinny_limit &&
+            try_stream<1, OutT>(e, wq, wq_stride, tau, bias, residual, q, s, qsum, n_mats, t, k, out, y, y_stride, acc, &st))
+            return st;
+        if (t > 8 && t <= 16 && 16 * (k + 16) <= skinny_limit &&
+            try_stream<2, OutT>(e, wq, wq_stride, tau, bias, residual, q, s, qsum, n_mats, t, k, out, y, y_stride, acc, &st))
+            return st;
     }
     if (t <= 8 && 8 * (k + 16) + 4096 <= skinny_limit)
         return dispatch_skinny<1, OutT>(e, wq, wq_stride, tau, bias, residual, q, s, qsum, n_mats, t,

@@ -146,6 +146,19 @@ def _case_tm(orc, t, k, out, seed, ternary_iid=False):
     (130, 384, 257), (300, 2048, 384),
 ])
 def test_bitlinear_fwd_tm_bitwise(eng, orc, t, k, out):
+    _bitwise_case(eng, orc, t, k, out)
+
+
+# shapes with enough row slabs for the persistent weight streamer with register-resident activations (it takes over from
+# about 19 000 output rows per launch): 4, 8 and 12 blocks of K per warp, one and two token tiles, ragged rows, warps
+# without any block of their own (K 192)
+@pytest.mark.parametrize("t,k,out", [(1, 2560, 19000), (8, 3200, 19000), (16, 2048, 19010), (12, 4096, 19001), (7, 5632, 19003),
+                                     (3, 192, 20000), (2, 2048, 19040)])
+def test_bitlinear_fwd_tm_bitwise_on_the_streamer(eng, orc, t, k, out):
+    _bitwise_case(eng, orc, t, k, out)
+
+
+def _bitwise_case(eng, orc, t, k, out):
     W, tau, X, bias = _case_tm(orc, t, k, out, seed=t * 1000 + k + out)
     packed = orc.trit_pack(W, tau)
     q_ref, s_ref = orc.act_quant_tm(X)
