@@ -465,10 +465,10 @@ class DecodeJob:
         gen = pos >= self.P  # steps that also run the head and the sampler
         b, a = np.polyfit(mid[gen], per_step[gen], 1)
         L, d, H = m["n_layer"], m["d_model"], m["n_head"]
-        kv_per_pos = self.chunk * L * 2 * d * 2  # algorithmic bytes per cached position per step (bf16 K and V)
         F = m["d_ff"]
         dk = d // H
         dkv = (m.get("n_head_kv") or H) * dk
+        kv_per_pos = self.chunk * L * 2 * dkv * 2  # algorithmic bytes per cached position per step (bf16 K and V heads)
         # packed bytes of the linears: q and o (d x d), k and v (dkv x d), fc1 (gate | up) and fc2, the head unless tied
         packed = (L * (2 * d * d + 2 * dkv * d + 3 * d * F) + (0 if m.get("tie_embeddings") else m["vocab"] * d)) / 4
         if dk == 100:
@@ -476,13 +476,14 @@ class DecodeJob:
         else:
             kernel, pad = f"attn_decode_bf16_kernel<{dk},{dk}>", ""
         if m.get("n_head_kv"):
-            pad += f"; grouped-query attention runs on the cache expanded to {H} heads, so these are the bytes of {H} heads"
+            pad += (f"; grouped-query attention: the cache holds {m['n_head_kv']} KV heads, read once from DRAM and shared by the "
+                    f"{H // m['n_head_kv']} query heads of a group")
         attn = kv_per_pos / (b * 1e-3) / 1e9
         wstream = packed / (a * 1e-3) / 1e9
         return {"roofline": {"bound": "hbm", "achieved": attn, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": attn / peaks["hbm_gbs"],
                              "traffic": None, "kernel": kernel,
                              "how": "slope of the per-step time over the context, measured with CUDA events every 64 steps inside a "
-                                    f"rollout of {self.chunk} sequences; algorithmic bytes = 2 x ctx x d x 2 B per sequence and layer"
+                                    f"rollout of {self.chunk} sequences; algorithmic bytes = 2 x ctx x (KV heads x dk) x 2 B per sequence and layer"
                                     + pad,
                              "ms_per_step_per_position": float(b), "peak_source": peaks["src"] + " copy bandwidth"},
                 "roofline_weight_stream": {"bound": "hbm", "achieved": wstream, "peak": peaks["hbm_gbs"], "unit": "GB/s",

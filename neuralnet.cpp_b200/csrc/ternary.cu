@@ -911,9 +911,11 @@ static bool try_stream(nnb_engine* e, const uint32_t* wq, size_t wq_stride, cons
     const size_t bpw = ceil_div(k / 64, 8);
     // enough items to give every CTA a few rounds; small problems stay on the kernels that split K less
     if (ceil_div(out, 32) * n_mats < (size_t)e->sm_count * 4) return false;
-    if (bpw <= 4) *st = launch_stream<NT, 4, 2, OutT>(e, wq, wq_stride, tau, bias, residual, q, s, qsum, n_mats, t, k, out, y, y_stride, acc);
-    else if (bpw <= 8) *st = launch_stream<NT, 8, 2, OutT>(e, wq, wq_stride, tau, bias, residual, q, s, qsum, n_mats, t, k, out, y, y_stride, acc);
-    else if (bpw <= 12 && NT == 1) *st = launch_stream<NT, 12, 1, OutT>(e, wq, wq_stride, tau, bias, residual, q, s, qsum, n_mats, t, k, out, y, y_stride, acc);
+    // measured on stacks of 64 matrices at 1 to 8 tokens: K 5632 (11 blocks per warp) 80-86 us against 108-111 us for the
+    // skinny kernel; at K 2048-3200 (4 to 7 blocks per warp) the two barriers per 32-row item cost more than the saved
+    // shared-memory reads (160-210 us against 115-142 us), so those shapes stay on the skinny kernel
+    if (bpw > 8 && bpw <= 12 && NT == 1)
+        *st = launch_stream<NT, 12, 1, OutT>(e, wq, wq_stride, tau, bias, residual, q, s, qsum, n_mats, t, k, out, y, y_stride, acc);
     else return false;
     return true;
 }
@@ -1118,6 +1120,14 @@ static nnb_status dispatch_skinny(nnb_engine* e, const uint32_t* wq, size_t wq_s
 #define NNB_SKINNY(WK_, MS_)                                                                            \
     return launch_skinny<NT, WK_, MS_, OutT>(e, wq, wq_stride, tau, bias, residual, q, s, qsum, n_mats, \
                                              t, k, out, y, y_stride, acc)
+    {
+        static int ms4 = -1;
+        if (ms4 < 0) {
+            const char* ev = getenv("NNB_SKINNY_MS4");
+            ms4 = (ev && ev[0] == '1') ? 1 : 0;
+        }
+        if (ms4 && NT == 1 && ceil_div(out, 64) * n_mats >= slots) NNB_SKINNY(1, 4);
+    }
     const size_t items2 = ceil_div(out, 32) * n_mats;
     // (measured on 2048 x 11264 stacks: 0.51-0.53 of the copy bandwidth at 1-8 tokens against 0.49-0.50 with
     // one slab, 0.35 against 0.30 at 32 tokens; at 9-16 tokens the extra registers cost more occupancy than the
