@@ -1120,14 +1120,7 @@ static nnb_status dispatch_skinny(nnb_engine* e, const uint32_t* wq, size_t wq_s
 #define NNB_SKINNY(WK_, MS_)                                                                            \
     return launch_skinny<NT, WK_, MS_, OutT>(e, wq, wq_stride, tau, bias, residual, q, s, qsum, n_mats, \
                                              t, k, out, y, y_stride, acc)
-    {
-        static int ms4 = -1;
-        if (ms4 < 0) {
-            const char* ev = getenv("NNB_SKINNY_MS4");
-            ms4 = (ev && ev[0] == '1') ? 1 : 0;
-        }
-        if (ms4 && NT == 1 && ceil_div(out, 64) * n_mats >= slots) NNB_SKINNY(1, 4);
-    }
+    // (four slabs per warp were measured too: 6 to 8 % slower than two at 1 to 8 tokens)
     const size_t items2 = ceil_div(out, 32) * n_mats;
     // (measured on 2048 x 11264 stacks: 0.51-0.53 of the copy bandwidth at 1-8 tokens against 0.49-0.50 with
     // one slab, 0.35 against 0.30 at 32 tokens; at 9-16 tokens the extra registers cost more occupancy than the
