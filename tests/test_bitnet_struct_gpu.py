@@ -299,6 +299,30 @@ def test_fast_mode_is_close_to_the_exact_mode(pkg, eng, extra):
     eng.check_device_errors()
 
 
+@pytest.mark.parametrize("d,heads,kv", [(256, 4, 1), (512, 4, 2), (512, 8, 1), (256, 4, 2)])
+@pytest.mark.parametrize("group_size", [1, 4])
+def test_grouped_query_decode_kernel_in_the_fast_mode(pkg, eng, d, heads, kv, group_size):
+    """head sizes 64 and 128 with 2, 4 or 8 query heads per KV head on the bf16 decode kernels and the batched prompt
+    prefill (cache of the KV heads only): logits after a prompt against the exact mode, and the rollout's log-probs
+    against the teacher-forced pass of the same policy; also with a prompt prefix shared by 4 sequences"""
+    kw = dict(n_layer=2, d_model=d, n_head=heads, n_head_kv=kv, d_ff=2 * d, vocab=500, ctx=64, act=1, pos=1)
+    cfg_e, cfg_f = pkg.GptConfig(exact=True, **kw), pkg.GptConfig(exact=False, **kw)
+    flat = cfg_e.init_params(3, bias_std=0.01)
+    pe, pf = pkg.Policy(eng, cfg_e), pkg.Policy(eng, cfg_f)
+    pe.upload_params(flat)
+    pf.upload_params(flat)
+    rng = np.random.default_rng(8)
+    prompts = np.repeat(rng.integers(0, 500, (8 // group_size, 21)), group_size, axis=0).astype(np.int32)
+    p = dev(prompts, eng, np.int32)
+    _, _, lg_e = pe.rollout(p, 1, 0.0, want_logits=True, group_size=group_size)
+    _, _, lg_f = pf.rollout(p, 1, 0.0, want_logits=True, group_size=group_size)
+    assert (lg_e - lg_f).abs().max().item() <= 0.05 * lg_e.abs().max().item()
+    toks, old_lp, _ = pf.rollout(p, 30, temperature=1.0, top_k=20, seed=1, group_size=group_size)
+    lp2, _, _ = pf.logprobs(toks, 21)
+    assert (lp2 - old_lp).abs().max().item() <= 2e-2 * max(old_lp.abs().max().item(), 1.0)
+    eng.check_device_errors()
+
+
 def test_optimizer_step_refreshes_the_tied_head(pkg, eng):
     """after AdamW moves tok_emb the fast mode's bf16 head copy follows: logits change and stay close to the exact mode's"""
     extra = SWITCHES[-1]
