@@ -829,6 +829,214 @@ attn_prefix_kernel(const AttnIn in, const __nv_bfloat16* __restrict__ kpre, cons
     }
 }
 
+// Grouped-query decode attention on tensor cores: one CTA per (sequence, KV head).  The REP query heads of the group are
+// the rows of one m16 tile (rows beyond REP stay zero), so every cached key and value is loaded once and serves the whole
+// group through `mma.sync` bf16; the CTA's 4 warps split the key tiles (32 keys each), each keeps an online softmax over
+// its tiles, and the four partial results are merged in shared memory.  Appends the new token's key and value first.
+// The cache holds the KV heads only.  Queries are rounded to bf16 here, as in attn_prefix_kernel.
+template <int DK>
+__global__ void __launch_bounds__(128)
+attn_decode_gqa_kernel(const AttnIn in, __nv_bfloat16* __restrict__ kcache, __nv_bfloat16* __restrict__ vcache, int own_alloc,
+                       const __nv_bfloat16* __restrict__ kpre, const __nv_bfloat16* __restrict__ vpre, int pre_len, int pre_alloc,
+                       int group, const float* __restrict__ rope_cos, const float* __restrict__ rope_sin,
+                       const int* __restrict__ d_pos, int B, int H, float scale, float* __restrict__ out)
+{
+    constexpr int LD = DK + 8, half = DK / 2, KT = 32, CH = DK / 8;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);                 // 16 x LD, shared by the warps
+    __nv_bfloat16* Ks = Qs + 16 * LD + (size_t)warp * 2 * KT * LD;                  // this warp's key tile
+    __nv_bfloat16* Vs = Ks + KT * LD;                                               // and value tile
+    float* mo = reinterpret_cast<float*>(Qs + 16 * LD + 4 * 2 * KT * LD);           // 4 warps x 16 rows x (DK + 2) partials
+    const int REP = in.kv_rep, Hkv = H / REP;
+    const int b = blockIdx.x / Hkv, hk = blockIdx.x % Hkv;
+    const int d = H * DK;
+    const int pos = *d_pos;
+    const size_t head_off = ((size_t)b * Hkv + hk) * (size_t)own_alloc * DK;
+    __nv_bfloat16* kc = kcache + head_off - (size_t)pre_len * DK;  // indexed by absolute position >= pre_len
+    __nv_bfloat16* vc = vcache + head_off - (size_t)pre_len * DK;
+    const size_t pre_off = ((size_t)(b / group) * Hkv + hk) * (size_t)pre_alloc * DK;
+    const __nv_bfloat16* kp = kpre ? kpre + pre_off : nullptr;
+    const __nv_bfloat16* vp = vpre ? vpre + pre_off : nullptr;
+    const float* qn = in.q + (size_t)b * in.stride + (size_t)hk * REP * DK;  // the group's query heads are adjacent
+    const float* kn = in.k + (size_t)b * in.stride + (size_t)hk * DK;
+    const float* vn = in.v + (size_t)b * in.stride + (size_t)hk * DK;
+
+    // rotated queries as bf16 rows of the m16 tile, the new key and value into the cache
+    for (int i = tid; i < 16 * half; i += 128) {
+        const int r = i / half, j = i % half;
+        float c = 1.0f, sn = 0.0f;
+        if (rope_cos) {
+            c = rope_cos[(size_t)pos * half + j];
+            sn = rope_sin[(size_t)pos * half + j];
+        }
+        float qa = 0.0f, qb = 0.0f;
+        if (r < REP) {
+            qa = qn[r * DK + j];
+            qb = qn[r * DK + j + half];
+        }
+        Qs[r * LD + j] = __float2bfloat16_rn(__fadd_rn(__fmul_rn(qa, c), __fmul_rn(-qb, sn)));
+        Qs[r * LD + j + half] = __float2bfloat16_rn(__fadd_rn(__fmul_rn(qb, c), __fmul_rn(qa, sn)));
+        if (r == 0) {
+            const float ka = kn[j], kb = kn[j + half];
+            kc[(size_t)pos * DK + j] = __float2bfloat16_rn(__fadd_rn(__fmul_rn(ka, c), __fmul_rn(-kb, sn)));
+            kc[(size_t)pos * DK + j + half] = __float2bfloat16_rn(__fadd_rn(__fmul_rn(kb, c), __fmul_rn(ka, sn)));
+            vc[(size_t)pos * DK + j] = __float2bfloat16_rn(vn[j]);
+            vc[(size_t)pos * DK + j + half] = __float2bfloat16_rn(vn[j + half]);
+        }
+    }
+    __syncthreads();
+    uint32_t qf[DK / 16][4];
+#pragma unroll
+    for (int ks = 0; ks < DK / 16; ++ks) ldsm_b16(qf[ks], Qs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LD + ks * 16 + 8 * (lane >> 4));
+
+    const int n_keys = pos + 1;
+    float o[DK / 8][4];
+#pragma unroll
+    for (int i = 0; i < DK / 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[i][j] = 0.0f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    for (int j0 = warp * KT; j0 < n_keys; j0 += 4 * KT) {
+        __syncwarp();
+        for (int i = lane; i < KT * CH; i += 32) {
+            const int r = i / CH, c = (i % CH) * 8;
+            const int j = j0 + r;
+            uint4 kv4 = make_uint4(0u, 0u, 0u, 0u), vv4 = kv4;
+            if (j < n_keys) {
+                kv4 = *reinterpret_cast<const uint4*>((j < pre_len ? kp : kc) + (size_t)j * DK + c);
+                vv4 = *reinterpret_cast<const uint4*>((j < pre_len ? vp : vc) + (size_t)j * DK + c);
+            }
+            *reinterpret_cast<uint4*>(Ks + r * LD + c) = kv4;
+            *reinterpret_cast<uint4*>(Vs + r * LD + c) = vv4;
+        }
+        __syncwarp();
+        float s[KT / 8][4];
+#pragma unroll
+        for (int i = 0; i < KT / 8; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) s[i][j] = 0.0f;
+#pragma unroll
+        for (int ks = 0; ks < DK / 16; ++ks) {
+#pragma unroll
+            for (int np = 0; np < KT / 16; ++np) {
+                uint32_t bk[4];
+                ldsm_b16(bk, Ks + (np * 16 + (lane & 7) + 8 * (lane >> 4)) * LD + ks * 16 + 8 * ((lane >> 3) & 1));
+                mma_bf16(s[np * 2], qf[ks], bk[0], bk[1]);
+                mma_bf16(s[np * 2 + 1], qf[ks], bk[2], bk[3]);
+            }
+        }
+        float mxv[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nt = 0; nt < KT / 8; ++nt)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int key = j0 + nt * 8 + 2 * t4 + (c & 1);
+                s[nt][c] = key < n_keys ? s[nt][c] * scale : -INFINITY;
+                mxv[c >> 1] = fmaxf(mxv[c >> 1], s[nt][c]);
+            }
+        float corr[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            mxv[r] = fmaxf(mxv[r], __shfl_xor_sync(0xffffffffu, mxv[r], 1));
+            mxv[r] = fmaxf(mxv[r], __shfl_xor_sync(0xffffffffu, mxv[r], 2));
+            const float mnew = fmaxf(m[r], mxv[r]);
+            corr[r] = __expf(m[r] - mnew);  // m = -inf on the first tile: exp(-inf) = 0, and l, o are 0 anyway
+            m[r] = mnew;
+            l[r] *= corr[r];
+        }
+#pragma unroll
+        for (int i = 0; i < DK / 8; ++i) {
+            o[i][0] *= corr[0]; o[i][1] *= corr[0];
+            o[i][2] *= corr[1]; o[i][3] *= corr[1];
+        }
+#pragma unroll
+        for (int nt = 0; nt < KT / 8; ++nt)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const float pj = __expf(s[nt][c] - m[c >> 1]);
+                s[nt][c] = pj;
+                l[c >> 1] += pj;
+            }
+#pragma unroll
+        for (int kk = 0; kk < KT / 16; ++kk) {
+            uint32_t pa[4];
+            pa[0] = pack_bf16x2(s[2 * kk][0], s[2 * kk][1]);
+            pa[1] = pack_bf16x2(s[2 * kk][2], s[2 * kk][3]);
+            pa[2] = pack_bf16x2(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+            pa[3] = pack_bf16x2(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+            for (int np = 0; np < DK / 16; ++np) {
+                uint32_t bv[4];
+                ldsm_t_b16(bv, Vs + (kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LD + np * 16 + 8 * (lane >> 4));
+                mma_bf16(o[np * 2], pa, bv[0], bv[1]);
+                mma_bf16(o[np * 2 + 1], pa, bv[2], bv[3]);
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    }
+    // park this warp's partial (o, m, l) of the real rows; a warp without any tile leaves m = -inf, l = 0
+    constexpr int PW = DK + 2;
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+        const int r = g + 8 * hh;
+        if (r >= REP) continue;
+        float* dst = mo + ((size_t)warp * 16 + r) * PW;
+#pragma unroll
+        for (int i = 0; i < DK / 8; ++i) {
+            dst[i * 8 + 2 * t4] = o[i][hh * 2];
+            dst[i * 8 + 2 * t4 + 1] = o[i][hh * 2 + 1];
+        }
+        if (t4 == 0) {
+            dst[DK] = m[hh];
+            dst[DK + 1] = l[hh];
+        }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < REP * DK; idx += 128) {
+        const int r = idx / DK, i = idx % DK;
+        float mall = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) mall = fmaxf(mall, mo[((size_t)w * 16 + r) * PW + DK]);
+        float num = 0.0f, den = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float* src = mo + ((size_t)w * 16 + r) * PW;
+            const float wgt = __expf(src[DK] - mall);  // exp(-inf) = 0 for a warp that saw no key
+            num = fmaf(wgt, src[i], num);
+            den = fmaf(wgt, src[DK + 1], den);
+        }
+        out[(size_t)b * d + (size_t)(hk * REP + r) * DK + i] = num / den;
+    }
+}
+
+template <int DK>
+static nnb_status launch_attn_decode_gqa(nnb_engine* e, void* kcache, void* vcache, size_t own_alloc, const void* kpre,
+                                         const void* vpre, size_t pre_len, size_t pre_alloc, size_t group, const float* rope_cos,
+                                         const float* rope_sin, const int* d_pos, size_t B, size_t H, float* out, const AttnIn& in)
+{
+    constexpr size_t LD = DK + 8;
+    const size_t smem = (16 * LD + 4 * 2 * 32 * LD) * sizeof(__nv_bfloat16) + 4 * 16 * (DK + 2) * sizeof(float);
+    auto kern = attn_decode_gqa_kernel<DK>;
+    static bool cfg_dev[64] = {}; bool& cfg = cfg_dev[e->device & 63];  // the attribute is per device
+    if (!cfg) {
+        NNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        cfg = true;
+    }
+    kern<<<(unsigned)(B * (H / (size_t)in.kv_rep)), 128, smem, e->stream>>>(in, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache,
+                                                                            (int)own_alloc, (const __nv_bfloat16*)kpre,
+                                                                            (const __nv_bfloat16*)vpre, (int)pre_len, (int)pre_alloc,
+                                                                            (int)group, rope_cos, rope_sin, d_pos, (int)B, (int)H,
+                                                                            1.0f / sqrtf((float)DK), out);
+    e->launches++;
+    NNB_CHECK_LAUNCH("attn_decode_gqa_kernel");
+    return NNB_OK;
+}
+
 // Decode attention of ALL heads of a sequence in one CTA, one warp per head, followed by the int8
 // quantisation of the token's attention output (the input of the output projection): what
 // attn_decode_bf16_kernel + row_quant_fast_kernel<3> compute, in one launch and without block-wide
@@ -1138,10 +1346,20 @@ nnb_status launch_attn_decode(nnb_engine* e, bool exact, const float* qkv, void*
                 kv_pitch, dk);
     NNB_REQUIRE(dk % 4 == 0 && dk <= 128 && dk >= 8, "attn_decode: head dim %zu unsupported (multiple of 4, <= 128)", dk);
     NNB_REQUIRE(group >= 1 && (pre_len == 0 || (kpre && vpre)), "attn_decode: bad prefix arguments");
-    // Grouped queries keep one CTA per query head: the heads of a group read the same cache rows, once from DRAM and
-    // then from L2.  A kernel with one CTA per KV head serving the whole group (every row loaded once, 4 dot products
-    // per key on CUDA cores) was measured on the 2B4T shape and lost: 0.0059 ms per position against 0.0051 — at 4 query
-    // heads per KV head the dot products, not the cache reads, bound it; that shape wants tensor cores.
+    // Grouped queries on head sizes 64 / 128 (2 to 16 query heads per KV head): the tensor-core kernel that serves a whole
+    // group per CTA.  NNB_GQA_KERNEL=0 in the environment keeps one CTA per query head instead (for A/B timing).
+    static int gqa_kernel = -1;
+    if (gqa_kernel < 0) {
+        const char* ev = getenv("NNB_GQA_KERNEL");
+        gqa_kernel = (ev && ev[0] == '0') ? 0 : 1;
+    }
+    if (!exact && gqa_kernel && in.kv_rep >= 2 && in.kv_rep <= 16 && (dk == 128 || dk == 64)) {
+        if (dk == 128)
+            return launch_attn_decode_gqa<128>(e, kcache, vcache, own_alloc, kpre, vpre, pre_len, pre_alloc, group, rope_cos,
+                                               rope_sin, d_pos, B, H, out, in);
+        return launch_attn_decode_gqa<64>(e, kcache, vcache, own_alloc, kpre, vpre, pre_len, pre_alloc, group, rope_cos, rope_sin,
+                                          d_pos, B, H, out, in);
+    }
     if (!exact && dk == 128)
         return launch_attn_decode_bf16<128>(e, qkv, kcache, vcache, own_alloc, kpre, vpre, pre_len, pre_alloc, group, rope_cos,
                                             rope_sin, d_pos, B, H, out, in);
