@@ -256,7 +256,7 @@ def _kernel_rooflines(torch, pkg, eng, pol, wl, peaks):
         ach = alg / (ms * 1e-3) / 1e9
         out[f"roofline_gemv_m{mtok}"] = {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                                           "frac": ach / peaks["hbm_gbs"],
-                                          "kernel": "bitlinear_gemv_kernel (dp4a)" if mtok <= 4 else "bitlinear_skinny_kernel",
+                                          "kernel": "bitlinear_gemv_kernel (dp4a)" if mtok == 1 else "bitlinear_skinny_kernel",
                                           "kernel_ms": ms, "shape": f"M={mtok} K={d} N={O} x{n_mats}"}
     return out
 

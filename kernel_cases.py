@@ -11,6 +11,8 @@ Used for Nsight Compute captures and quick timing; every case prints its CUDA-ev
   rollout [B P new]   batched rollout on the 1B policy (default 512 16 24)
   rollout3b [B P new [layers]] batched rollout on the 3B-shaped decode policy (26 layers, d 3200, 32 heads of 100;
                default 128 16 48); `layers` cuts the depth (same kernels, less memory: for profiler captures)
+  rollout2b4t [B P new [layers]] the same on the BitNet-b1.58-2B4T structure (30 layers, d 2560, 20 heads on 5 KV heads of
+               128, SubLN, ReLU2GLU, tied embeddings, vocab 128256)
   lmhead [T]   LM head fused with log-prob / entropy, forward and backward, T (8192) decisions x d 2048 x vocab 32000
 """
 import os
@@ -24,6 +26,8 @@ from __graft_entry__ import load_package  # noqa: E402
 
 MODEL_1B = dict(n_layer=24, d_model=2048, n_head=16, d_ff=5632, vocab=32000, ctx=640, act=1, pos=1)
 MODEL_3B = dict(n_layer=26, d_model=3200, n_head=32, d_ff=8640, vocab=32002, ctx=2048, act=1, pos=1)
+MODEL_2B4T = dict(n_layer=30, d_model=2560, n_head=20, n_head_kv=5, d_ff=6912, vocab=128256, ctx=2048, act=2, pos=1,
+                  sub_ln=True, tie_embeddings=True)
 
 
 def _rand_packed(dev, *shape):
@@ -124,13 +128,14 @@ def main(argv):
         cfg, pol, g = _policy(pkg, eng)
         prompts = torch.randint(0, cfg.vocab, (B, P), device=dev, dtype=torch.int32, generator=g)
         _timed(f"rollout {B} x ({P}+{new})", lambda: pol.rollout(prompts, new, temperature=0.8, top_k=50, seed=1), reps=1)
-    elif case == "rollout3b":
+    elif case in ("rollout3b", "rollout2b4t"):
         B, P, new = (int(a) for a in argv[2:5]) if len(argv) > 4 else (128, 16, 48)
-        model = dict(MODEL_3B, n_layer=int(argv[5])) if len(argv) > 5 else MODEL_3B
+        base = MODEL_3B if case == "rollout3b" else MODEL_2B4T
+        model = dict(base, n_layer=int(argv[5])) if len(argv) > 5 else base
         cfg, pol, g = _policy(pkg, eng, model)
         prompts = torch.randint(0, cfg.vocab, (B, P), device=dev, dtype=torch.int32, generator=g)
         pol.set_step_timing(8)
-        _timed(f"3B-shaped rollout {B} x ({P}+{new})", lambda: pol.rollout(prompts, new, temperature=0.8, top_k=50, seed=1), reps=1)
+        _timed(f"{case[7:]}-shaped rollout {B} x ({P}+{new})", lambda: pol.rollout(prompts, new, temperature=0.8, top_k=50, seed=1), reps=1)
         ms, pos = pol.step_times()
         print("ms per step by position:", " ".join(f"{p}:{m / 8:.3f}" for m, p in zip(ms, pos)))
     elif case == "lmhead":

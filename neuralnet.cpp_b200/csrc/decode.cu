@@ -829,6 +829,13 @@ attn_prefix_kernel(const AttnIn in, const __nv_bfloat16* __restrict__ kpre, cons
     }
 }
 
+__device__ __forceinline__ void cp_async16_zfill(void* smem, const void* gmem, bool valid)
+{
+    const uint32_t sa = (uint32_t)__cvta_generic_to_shared(smem);
+    const int sz = valid ? 16 : 0;  // 0 source bytes: the 16 destination bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(sa), "l"(gmem), "r"(sz) : "memory");
+}
+
 // Grouped-query decode attention on tensor cores: one CTA per (sequence, KV head).  The REP query heads of the group are
 // the rows of one m16 tile (rows beyond REP stay zero), so every cached key and value is loaded once and serves the whole
 // group through `mma.sync` bf16; the CTA's 4 warps split the key tiles (32 keys each), each keeps an online softmax over
@@ -847,7 +854,10 @@ attn_decode_gqa_kernel(const AttnIn in, __nv_bfloat16* __restrict__ kcache, __nv
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);                 // 16 x LD, shared by the warps
     __nv_bfloat16* Ks = Qs + 16 * LD + (size_t)warp * 2 * KT * LD;                  // this warp's key tile
     __nv_bfloat16* Vs = Ks + KT * LD;                                               // and value tile
-    float* mo = reinterpret_cast<float*>(Qs + 16 * LD + 4 * 2 * KT * LD);           // 4 warps x 16 rows x (DK + 2) partials
+    // after its last tile a warp parks its partial (o, m, l) over its own key tile: 16 rows x (DK + 2) floats fit in it
+    constexpr int PW = DK + 2;
+    static_assert(16 * PW * 4 <= KT * LD * 2, "a warp's partial results fit in its key tile");
+    float* mo_w = reinterpret_cast<float*>(Ks);
     const int REP = in.kv_rep, Hkv = H / REP;
     const int b = blockIdx.x / Hkv, hk = blockIdx.x % Hkv;
     const int d = H * DK;
@@ -897,19 +907,27 @@ attn_decode_gqa_kernel(const AttnIn in, __nv_bfloat16* __restrict__ kcache, __nv
 #pragma unroll
         for (int j = 0; j < 4; ++j) o[i][j] = 0.0f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-    for (int j0 = warp * KT; j0 < n_keys; j0 += 4 * KT) {
-        __syncwarp();
-        for (int i = lane; i < KT * CH; i += 32) {
-            const int r = i / CH, c = (i % CH) * 8;
-            const int j = j0 + r;
-            uint4 kv4 = make_uint4(0u, 0u, 0u, 0u), vv4 = kv4;
-            if (j < n_keys) {
-                kv4 = *reinterpret_cast<const uint4*>((j < pre_len ? kp : kc) + (size_t)j * DK + c);
-                vv4 = *reinterpret_cast<const uint4*>((j < pre_len ? vp : vc) + (size_t)j * DK + c);
+    // Tiles travel global -> shared memory with cp.async, one commit group per key tile and per value tile, in the order
+    // K(t), V(t), K(t+1), V(t+1), ...: the next key tile is requested as soon as the scores of the current one are formed
+    // (its buffer is free then), the next value tile right after the P.V product, so a warp always has a tile in flight
+    // while it computes.  Rows past the last key are zero-filled.
+    auto request = [&](int j0, const __nv_bfloat16* pre, __nv_bfloat16* own, __nv_bfloat16* dst) {
+        if (j0 < n_keys) {
+            for (int i = lane; i < KT * CH; i += 32) {
+                const int r = i / CH, c = (i % CH) * 8;
+                const int j = j0 + r;
+                const bool ok = j < n_keys;
+                // (an unread source still has to be an address inside the cache)
+                const __nv_bfloat16* src = ok ? (j < pre_len ? pre : own) + (size_t)j * DK + c : own + (size_t)pre_len * DK;
+                cp_async16_zfill(dst + r * LD + c, src, ok);
             }
-            *reinterpret_cast<uint4*>(Ks + r * LD + c) = kv4;
-            *reinterpret_cast<uint4*>(Vs + r * LD + c) = vv4;
         }
+        asm volatile("cp.async.commit_group;\n" ::);
+    };
+    request(warp * KT, kp, kc, Ks);
+    request(warp * KT, vp, vc, Vs);
+    for (int j0 = warp * KT; j0 < n_keys; j0 += 4 * KT) {
+        asm volatile("cp.async.wait_group 1;\n" ::: "memory");  // K(t) has landed (V(t) may still be on its way)
         __syncwarp();
         float s[KT / 8][4];
 #pragma unroll
@@ -926,6 +944,8 @@ attn_decode_gqa_kernel(const AttnIn in, __nv_bfloat16* __restrict__ kcache, __nv
                 mma_bf16(s[np * 2 + 1], qf[ks], bk[2], bk[3]);
             }
         }
+        __syncwarp();
+        request(j0 + 4 * KT, kp, kc, Ks);
         float mxv[2] = {-INFINITY, -INFINITY};
 #pragma unroll
         for (int nt = 0; nt < KT / 8; ++nt)
@@ -958,6 +978,8 @@ attn_decode_gqa_kernel(const AttnIn in, __nv_bfloat16* __restrict__ kcache, __nv
                 s[nt][c] = pj;
                 l[c >> 1] += pj;
             }
+        asm volatile("cp.async.wait_group 1;\n" ::: "memory");  // V(t) has landed (K(t+1) may still be on its way)
+        __syncwarp();
 #pragma unroll
         for (int kk = 0; kk < KT / 16; ++kk) {
             uint32_t pa[4];
@@ -973,19 +995,22 @@ attn_decode_gqa_kernel(const AttnIn in, __nv_bfloat16* __restrict__ kcache, __nv
                 mma_bf16(o[np * 2 + 1], pa, bv[2], bv[3]);
             }
         }
+        __syncwarp();
+        request(j0 + 4 * KT, vp, vc, Vs);
     }
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
         l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
     }
     // park this warp's partial (o, m, l) of the real rows; a warp without any tile leaves m = -inf, l = 0
-    constexpr int PW = DK + 2;
+    __syncwarp();
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
         const int r = g + 8 * hh;
         if (r >= REP) continue;
-        float* dst = mo + ((size_t)warp * 16 + r) * PW;
+        float* dst = mo_w + (size_t)r * PW;
 #pragma unroll
         for (int i = 0; i < DK / 8; ++i) {
             dst[i * 8 + 2 * t4] = o[i][hh * 2];
@@ -999,13 +1024,16 @@ attn_decode_gqa_kernel(const AttnIn in, __nv_bfloat16* __restrict__ kcache, __nv
     __syncthreads();
     for (int idx = tid; idx < REP * DK; idx += 128) {
         const int r = idx / DK, i = idx % DK;
+        // warp w's partials live in its key tile
+        const float* mo0 = reinterpret_cast<const float*>(Qs + 16 * LD);
+        constexpr size_t WSTRIDE = (size_t)2 * KT * LD / 2;  // floats between two warps' tiles
         float mall = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) mall = fmaxf(mall, mo[((size_t)w * 16 + r) * PW + DK]);
+        for (int w = 0; w < 4; ++w) mall = fmaxf(mall, mo0[w * WSTRIDE + (size_t)r * PW + DK]);
         float num = 0.0f, den = 0.0f;
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
-            const float* src = mo + ((size_t)w * 16 + r) * PW;
+            const float* src = mo0 + w * WSTRIDE + (size_t)r * PW;
             const float wgt = __expf(src[DK] - mall);  // exp(-inf) = 0 for a warp that saw no key
             num = fmaf(wgt, src[i], num);
             den = fmaf(wgt, src[DK + 1], den);
@@ -1020,7 +1048,7 @@ static nnb_status launch_attn_decode_gqa(nnb_engine* e, void* kcache, void* vcac
                                          const float* rope_sin, const int* d_pos, size_t B, size_t H, float* out, const AttnIn& in)
 {
     constexpr size_t LD = DK + 8;
-    const size_t smem = (16 * LD + 4 * 2 * 32 * LD) * sizeof(__nv_bfloat16) + 4 * 16 * (DK + 2) * sizeof(float);
+    const size_t smem = (16 * LD + 4 * 2 * 32 * LD) * sizeof(__nv_bfloat16);
     auto kern = attn_decode_gqa_kernel<DK>;
     static bool cfg_dev[64] = {}; bool& cfg = cfg_dev[e->device & 63];  // the attribute is per device
     if (!cfg) {
