@@ -475,9 +475,11 @@ class DecodeJob:
             kernel, pad = "attn_decode_bf16_kernel<100,104>", " (the cache rows are padded from 100 to 104 features: 4 % more is actually read)"
         else:
             kernel, pad = f"attn_decode_bf16_kernel<{dk},{dk}>", ""
-        if m.get("n_head_kv"):
-            pad += (f"; grouped-query attention: the cache holds {m['n_head_kv']} KV heads, read once from DRAM and shared by the "
-                    f"{H // m['n_head_kv']} query heads of a group")
+        if m.get("n_head_kv") and m["n_head_kv"] != H:
+            if dk in (64, 128):
+                kernel = f"attn_decode_gqa_kernel<{dk}>"
+            pad += (f"; grouped-query attention: the cache holds {m['n_head_kv']} KV heads, each row loaded once for the "
+                    f"{H // m['n_head_kv']} query heads of its group")
         attn = kv_per_pos / (b * 1e-3) / 1e9
         wstream = packed / (a * 1e-3) / 1e9
         return {"roofline": {"bound": "hbm", "achieved": attn, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": attn / peaks["hbm_gbs"],
