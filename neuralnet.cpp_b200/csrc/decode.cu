@@ -841,37 +841,53 @@ __device__ __forceinline__ void cp_async16_zfill(void* smem, const void* gmem, b
 // group through `mma.sync` bf16; the CTA's 4 warps split the key tiles (32 keys each), each keeps an online softmax over
 // its tiles, and the four partial results are merged in shared memory.  Appends the new token's key and value first.
 // The cache holds the KV heads only.  Queries are rounded to bf16 here, as in attn_prefix_kernel.
-template <int DK>
+// DK: head size; DKP: row pitch of the caches (DK rounded up to 8 elements, pad features zero); DKM: DK rounded up to the
+// 16 features of an mma k-step (the tiles' pad columns stay zero in shared memory).  One query head per KV head (plain
+// multi-head attention) is the case REP = 1: the kernel then is a tensor-core streamer for head sizes the CUDA-core
+// kernels serve badly (100: 13 of 16 lanes busy there).
+template <int DK, int DKP = DK, int DKM = DK>
 __global__ void __launch_bounds__(128)
 attn_decode_gqa_kernel(const AttnIn in, __nv_bfloat16* __restrict__ kcache, __nv_bfloat16* __restrict__ vcache, int own_alloc,
                        const __nv_bfloat16* __restrict__ kpre, const __nv_bfloat16* __restrict__ vpre, int pre_len, int pre_alloc,
                        int group, const float* __restrict__ rope_cos, const float* __restrict__ rope_sin,
                        const int* __restrict__ d_pos, int B, int H, float scale, float* __restrict__ out)
 {
-    constexpr int LD = DK + 8, half = DK / 2, KT = 32, CH = DK / 8;
+    static_assert(DKP % 8 == 0 && DKM % 16 == 0 && DK <= DKP && DKP <= DKM && DKM - DKP <= 8, "pitch and mma padding");
+    constexpr int LD = DKM + 8, half = DK / 2, KT = 32, CH = DKP / 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);                 // 16 x LD, shared by the warps
     __nv_bfloat16* Ks = Qs + 16 * LD + (size_t)warp * 2 * KT * LD;                  // this warp's key tile
     __nv_bfloat16* Vs = Ks + KT * LD;                                               // and value tile
     // after its last tile a warp parks its partial (o, m, l) over its own key tile: 16 rows x (DK + 2) floats fit in it
-    constexpr int PW = DK + 2;
+    constexpr int PW = DKM + 2;
     static_assert(16 * PW * 4 <= KT * LD * 2, "a warp's partial results fit in its key tile");
     float* mo_w = reinterpret_cast<float*>(Ks);
     const int REP = in.kv_rep, Hkv = H / REP;
     const int b = blockIdx.x / Hkv, hk = blockIdx.x % Hkv;
     const int d = H * DK;
     const int pos = *d_pos;
-    const size_t head_off = ((size_t)b * Hkv + hk) * (size_t)own_alloc * DK;
-    __nv_bfloat16* kc = kcache + head_off - (size_t)pre_len * DK;  // indexed by absolute position >= pre_len
-    __nv_bfloat16* vc = vcache + head_off - (size_t)pre_len * DK;
-    const size_t pre_off = ((size_t)(b / group) * Hkv + hk) * (size_t)pre_alloc * DK;
+    const size_t head_off = ((size_t)b * Hkv + hk) * (size_t)own_alloc * DKP;
+    __nv_bfloat16* kc = kcache + head_off - (size_t)pre_len * DKP;  // indexed by absolute position >= pre_len
+    __nv_bfloat16* vc = vcache + head_off - (size_t)pre_len * DKP;
+    const size_t pre_off = ((size_t)(b / group) * Hkv + hk) * (size_t)pre_alloc * DKP;
     const __nv_bfloat16* kp = kpre ? kpre + pre_off : nullptr;
     const __nv_bfloat16* vp = vpre ? vpre + pre_off : nullptr;
     const float* qn = in.q + (size_t)b * in.stride + (size_t)hk * REP * DK;  // the group's query heads are adjacent
     const float* kn = in.k + (size_t)b * in.stride + (size_t)hk * DK;
     const float* vn = in.v + (size_t)b * in.stride + (size_t)hk * DK;
 
+    // pad columns: of the query tile, of every warp's key / value tile (cp.async never writes them), of the cache row
+    if (DKM > DK) {
+        for (int i = tid; i < 16 * (DKM - DK); i += 128) Qs[(i / (DKM - DK)) * LD + DK + i % (DKM - DK)] = __float2bfloat16_rn(0.0f);
+        if (DKM > DKP)
+            for (int i = tid; i < 4 * 2 * KT; i += 128)
+                *reinterpret_cast<uint4*>(Qs + (16 + i) * LD + DKP) = make_uint4(0u, 0u, 0u, 0u);
+        if (DKP > DK && tid < DKP - DK) {
+            kc[(size_t)pos * DKP + DK + tid] = __float2bfloat16_rn(0.0f);
+            vc[(size_t)pos * DKP + DK + tid] = __float2bfloat16_rn(0.0f);
+        }
+    }
     // rotated queries as bf16 rows of the m16 tile, the new key and value into the cache
     for (int i = tid; i < 16 * half; i += 128) {
         const int r = i / half, j = i % half;
@@ -889,21 +905,21 @@ attn_decode_gqa_kernel(const AttnIn in, __nv_bfloat16* __restrict__ kcache, __nv
         Qs[r * LD + j + half] = __float2bfloat16_rn(__fadd_rn(__fmul_rn(qb, c), __fmul_rn(qa, sn)));
         if (r == 0) {
             const float ka = kn[j], kb = kn[j + half];
-            kc[(size_t)pos * DK + j] = __float2bfloat16_rn(__fadd_rn(__fmul_rn(ka, c), __fmul_rn(-kb, sn)));
-            kc[(size_t)pos * DK + j + half] = __float2bfloat16_rn(__fadd_rn(__fmul_rn(kb, c), __fmul_rn(ka, sn)));
-            vc[(size_t)pos * DK + j] = __float2bfloat16_rn(vn[j]);
-            vc[(size_t)pos * DK + j + half] = __float2bfloat16_rn(vn[j + half]);
+            kc[(size_t)pos * DKP + j] = __float2bfloat16_rn(__fadd_rn(__fmul_rn(ka, c), __fmul_rn(-kb, sn)));
+            kc[(size_t)pos * DKP + j + half] = __float2bfloat16_rn(__fadd_rn(__fmul_rn(kb, c), __fmul_rn(ka, sn)));
+            vc[(size_t)pos * DKP + j] = __float2bfloat16_rn(vn[j]);
+            vc[(size_t)pos * DKP + j + half] = __float2bfloat16_rn(vn[j + half]);
         }
     }
     __syncthreads();
-    uint32_t qf[DK / 16][4];
+    uint32_t qf[DKM / 16][4];
 #pragma unroll
-    for (int ks = 0; ks < DK / 16; ++ks) ldsm_b16(qf[ks], Qs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LD + ks * 16 + 8 * (lane >> 4));
+    for (int ks = 0; ks < DKM / 16; ++ks) ldsm_b16(qf[ks], Qs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LD + ks * 16 + 8 * (lane >> 4));
 
     const int n_keys = pos + 1;
-    float o[DK / 8][4];
+    float o[DKM / 8][4];
 #pragma unroll
-    for (int i = 0; i < DK / 8; ++i)
+    for (int i = 0; i < DKM / 8; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) o[i][j] = 0.0f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
@@ -918,7 +934,7 @@ attn_decode_gqa_kernel(const AttnIn in, __nv_bfloat16* __restrict__ kcache, __nv
                 const int j = j0 + r;
                 const bool ok = j < n_keys;
                 // (an unread source still has to be an address inside the cache)
-                const __nv_bfloat16* src = ok ? (j < pre_len ? pre : own) + (size_t)j * DK + c : own + (size_t)pre_len * DK;
+                const __nv_bfloat16* src = ok ? (j < pre_len ? pre : own) + (size_t)j * DKP + c : own + (size_t)pre_len * DKP;
                 cp_async16_zfill(dst + r * LD + c, src, ok);
             }
         }
@@ -935,7 +951,7 @@ attn_decode_gqa_kernel(const AttnIn in, __nv_bfloat16* __restrict__ kcache, __nv
 #pragma unroll
             for (int j = 0; j < 4; ++j) s[i][j] = 0.0f;
 #pragma unroll
-        for (int ks = 0; ks < DK / 16; ++ks) {
+        for (int ks = 0; ks < DKM / 16; ++ks) {
 #pragma unroll
             for (int np = 0; np < KT / 16; ++np) {
                 uint32_t bk[4];
@@ -966,7 +982,7 @@ attn_decode_gqa_kernel(const AttnIn in, __nv_bfloat16* __restrict__ kcache, __nv
             l[r] *= corr[r];
         }
 #pragma unroll
-        for (int i = 0; i < DK / 8; ++i) {
+        for (int i = 0; i < DKM / 8; ++i) {
             o[i][0] *= corr[0]; o[i][1] *= corr[0];
             o[i][2] *= corr[1]; o[i][3] *= corr[1];
         }
@@ -988,7 +1004,7 @@ attn_decode_gqa_kernel(const AttnIn in, __nv_bfloat16* __restrict__ kcache, __nv
             pa[2] = pack_bf16x2(s[2 * kk + 1][0], s[2 * kk + 1][1]);
             pa[3] = pack_bf16x2(s[2 * kk + 1][2], s[2 * kk + 1][3]);
 #pragma unroll
-            for (int np = 0; np < DK / 16; ++np) {
+            for (int np = 0; np < DKM / 16; ++np) {
                 uint32_t bv[4];
                 ldsm_t_b16(bv, Vs + (kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LD + np * 16 + 8 * (lane >> 4));
                 mma_bf16(o[np * 2], pa, bv[0], bv[1]);
@@ -1012,13 +1028,13 @@ attn_decode_gqa_kernel(const AttnIn in, __nv_bfloat16* __restrict__ kcache, __nv
         if (r >= REP) continue;
         float* dst = mo_w + (size_t)r * PW;
 #pragma unroll
-        for (int i = 0; i < DK / 8; ++i) {
+        for (int i = 0; i < DKM / 8; ++i) {
             dst[i * 8 + 2 * t4] = o[i][hh * 2];
             dst[i * 8 + 2 * t4 + 1] = o[i][hh * 2 + 1];
         }
         if (t4 == 0) {
-            dst[DK] = m[hh];
-            dst[DK + 1] = l[hh];
+            dst[DKM] = m[hh];
+            dst[DKM + 1] = l[hh];
         }
     }
     __syncthreads();
@@ -1029,27 +1045,27 @@ attn_decode_gqa_kernel(const AttnIn in, __nv_bfloat16* __restrict__ kcache, __nv
         constexpr size_t WSTRIDE = (size_t)2 * KT * LD / 2;  // floats between two warps' tiles
         float mall = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) mall = fmaxf(mall, mo0[w * WSTRIDE + (size_t)r * PW + DK]);
+        for (int w = 0; w < 4; ++w) mall = fmaxf(mall, mo0[w * WSTRIDE + (size_t)r * PW + DKM]);
         float num = 0.0f, den = 0.0f;
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
             const float* src = mo0 + w * WSTRIDE + (size_t)r * PW;
-            const float wgt = __expf(src[DK] - mall);  // exp(-inf) = 0 for a warp that saw no key
+            const float wgt = __expf(src[DKM] - mall);  // exp(-inf) = 0 for a warp that saw no key
             num = fmaf(wgt, src[i], num);
-            den = fmaf(wgt, src[DK + 1], den);
+            den = fmaf(wgt, src[DKM + 1], den);
         }
         out[(size_t)b * d + (size_t)(hk * REP + r) * DK + i] = num / den;
     }
 }
 
-template <int DK>
+template <int DK, int DKP = DK, int DKM = DK>
 static nnb_status launch_attn_decode_gqa(nnb_engine* e, void* kcache, void* vcache, size_t own_alloc, const void* kpre,
                                          const void* vpre, size_t pre_len, size_t pre_alloc, size_t group, const float* rope_cos,
                                          const float* rope_sin, const int* d_pos, size_t B, size_t H, float* out, const AttnIn& in)
 {
-    constexpr size_t LD = DK + 8;
+    constexpr size_t LD = DKM + 8;
     const size_t smem = (16 * LD + 4 * 2 * 32 * LD) * sizeof(__nv_bfloat16);
-    auto kern = attn_decode_gqa_kernel<DK>;
+    auto kern = attn_decode_gqa_kernel<DK, DKP, DKM>;
     static bool cfg_dev[64] = {}; bool& cfg = cfg_dev[e->device & 63];  // the attribute is per device
     if (!cfg) {
         NNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -1394,6 +1410,16 @@ nnb_status launch_attn_decode(nnb_engine* e, bool exact, const float* qkv, void*
     if (!exact && dk == 64)
         return launch_attn_decode_bf16<64>(e, qkv, kcache, vcache, own_alloc, kpre, vpre, pre_len, pre_alloc, group, rope_cos,
                                            rope_sin, d_pos, B, H, out, in);
+    // head size 100 (caches of pitch attn_decode_kv_pitch(false, 100) = 104): the tensor-core streamer, multi-head or
+    // grouped; NNB_MMA_DK100=0 in the environment keeps the CUDA-core kernel (for A/B timing)
+    static int mma100 = -1;
+    if (mma100 < 0) {
+        const char* ev = getenv("NNB_MMA_DK100");
+        mma100 = (ev && ev[0] == '0') ? 0 : 1;
+    }
+    if (!exact && dk == 100 && kv_pitch == 104 && mma100 && in.kv_rep <= 16)
+        return launch_attn_decode_gqa<100, 104, 112>(e, kcache, vcache, own_alloc, kpre, vpre, pre_len, pre_alloc, group, rope_cos,
+                                                     rope_sin, d_pos, B, H, out, in);
     if (!exact && dk == 100 && kv_pitch == 104)  // caches of pitch attn_decode_kv_pitch(false, 100)
         return launch_attn_decode_bf16<100, 104>(e, qkv, kcache, vcache, own_alloc, kpre, vpre, pre_len, pre_alloc, group,
                                                  rope_cos, rope_sin, d_pos, B, H, out, in);

@@ -210,6 +210,28 @@ def test_fast_mode_runs_and_is_close(pkg, eng):
     assert err < 0.05  # bf16 KV cache, f32 accumulation
 
 
+@pytest.mark.parametrize("group_size", [1, 4])
+def test_fast_mode_head_size_100(pkg, eng, group_size):
+    """the 3B decode shape's head size in the fast mode: bf16 cache rows padded from 100 to 104 features, attention on the
+    tensor-core streamer (tiles padded to 112 features in shared memory); logits after a prompt against the exact mode, and
+    the rollout's log-probs against the teacher-forced pass; also with a prompt prefix shared by 4 sequences"""
+    kw = dict(n_layer=2, d_model=1600, n_head=16, d_ff=3200, vocab=500, ctx=80, act=1, pos=1)
+    cfg_e, cfg_f = pkg.GptConfig(exact=True, **kw), pkg.GptConfig(exact=False, **kw)
+    flat = cfg_e.init_params(3, bias_std=0.01)
+    pe, pf = pkg.Policy(eng, cfg_e), pkg.Policy(eng, cfg_f)
+    pe.upload_params(flat)
+    pf.upload_params(flat)
+    prompts = np.repeat(_prompts(cfg_e, 8 // group_size, 37, seed=8), group_size, axis=0)
+    p = torch.from_numpy(prompts).to(eng.device)
+    _, _, lg_e = pe.rollout(p, 1, 0.0, want_logits=True, group_size=group_size)
+    _, _, lg_f = pf.rollout(p, 1, 0.0, want_logits=True, group_size=group_size)
+    assert (lg_e - lg_f).abs().max().item() <= 0.05 * lg_e.abs().max().item()
+    toks, old_lp, _ = pf.rollout(p, 40, temperature=1.0, top_k=20, seed=1, group_size=group_size)
+    lp2, _, _ = pf.logprobs(toks, 37)
+    assert (lp2 - old_lp).abs().max().item() <= 2e-2 * max(old_lp.abs().max().item(), 1.0)
+    eng.check_device_errors()
+
+
 def test_host_rollout_entry_point(pkg, eng):
     cfg = pkg.GptConfig(n_layer=1, d_model=64, n_head=2, d_ff=128, vocab=300, ctx=24, act=0, pos=0)
     pol, m, _ = _setup(pkg, eng, cfg)
