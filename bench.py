@@ -472,12 +472,12 @@ class DecodeJob:
         # packed bytes of the linears: q and o (d x d), k and v (dkv x d), fc1 (gate | up) and fc2, the head unless tied
         packed = (L * (2 * d * d + 2 * dkv * d + 3 * d * F) + (0 if m.get("tie_embeddings") else m["vocab"] * d)) / 4
         if dk == 100:
-            kernel, pad = "attn_decode_bf16_kernel<100,104>", " (the cache rows are padded from 100 to 104 features: 4 % more is actually read)"
+            kernel, pad = "attn_decode_mma_kernel<100,104,112>", " (the cache rows are padded from 100 to 104 features: 4 % more is actually read)"
         else:
             kernel, pad = f"attn_decode_bf16_kernel<{dk},{dk}>", ""
         if m.get("n_head_kv") and m["n_head_kv"] != H:
             if dk in (64, 128):
-                kernel = f"attn_decode_gqa_kernel<{dk}>"
+                kernel = f"attn_decode_mma_kernel<{dk}>"
             pad += (f"; grouped-query attention: the cache holds {m['n_head_kv']} KV heads, each row loaded once for the "
                     f"{H // m['n_head_kv']} query heads of its group")
         attn = kv_per_pos / (b * 1e-3) / 1e9

@@ -127,7 +127,10 @@ def main(argv):
         B, P, new = (int(a) for a in argv[2:5]) if len(argv) > 4 else (512, 16, 24)
         cfg, pol, g = _policy(pkg, eng)
         prompts = torch.randint(0, cfg.vocab, (B, P), device=dev, dtype=torch.int32, generator=g)
+        pol.set_step_timing(32)
         _timed(f"rollout {B} x ({P}+{new})", lambda: pol.rollout(prompts, new, temperature=0.8, top_k=50, seed=1), reps=1)
+        ms, pos = pol.step_times()
+        print("ms per step by position:", " ".join(f"{p}:{m / 32:.3f}" for m, p in zip(ms, pos)))
     elif case in ("rollout3b", "rollout2b4t"):
         B, P, new = (int(a) for a in argv[2:5]) if len(argv) > 4 else (128, 16, 48)
         base = MODEL_3B if case == "rollout3b" else MODEL_2B4T

@@ -847,7 +847,7 @@ __device__ __forceinline__ void cp_async16_zfill(void* smem, const void* gmem, b
 // kernels serve badly (100: 13 of 16 lanes busy there).
 template <int DK, int DKP = DK, int DKM = DK>
 __global__ void __launch_bounds__(128)
-attn_decode_gqa_kernel(const AttnIn in, __nv_bfloat16* __restrict__ kcache, __nv_bfloat16* __restrict__ vcache, int own_alloc,
+attn_decode_mma_kernel(const AttnIn in, __nv_bfloat16* __restrict__ kcache, __nv_bfloat16* __restrict__ vcache, int own_alloc,
                        const __nv_bfloat16* __restrict__ kpre, const __nv_bfloat16* __restrict__ vpre, int pre_len, int pre_alloc,
                        int group, const float* __restrict__ rope_cos, const float* __restrict__ rope_sin,
                        const int* __restrict__ d_pos, int B, int H, float scale, float* __restrict__ out)
@@ -877,9 +877,12 @@ attn_decode_gqa_kernel(const AttnIn in, __nv_bfloat16* __restrict__ kcache, __nv
     const float* kn = in.k + (size_t)b * in.stride + (size_t)hk * DK;
     const float* vn = in.v + (size_t)b * in.stride + (size_t)hk * DK;
 
-    // pad columns: of the query tile, of every warp's key / value tile (cp.async never writes them), of the cache row
+    // rows of the query tile beyond the group's heads: zero
+    for (int i = tid; i < (16 - REP) * (LD / 8); i += 128)
+        reinterpret_cast<uint4*>(Qs + REP * LD)[i] = make_uint4(0u, 0u, 0u, 0u);
+    // pad columns: of the query rows, of every warp's key / value tile (cp.async never writes them), of the cache row
     if (DKM > DK) {
-        for (int i = tid; i < 16 * (DKM - DK); i += 128) Qs[(i / (DKM - DK)) * LD + DK + i % (DKM - DK)] = __float2bfloat16_rn(0.0f);
+        for (int i = tid; i < REP * (DKM - DK); i += 128) Qs[(i / (DKM - DK)) * LD + DK + i % (DKM - DK)] = __float2bfloat16_rn(0.0f);
         if (DKM > DKP)
             for (int i = tid; i < 4 * 2 * KT; i += 128)
                 *reinterpret_cast<uint4*>(Qs + (16 + i) * LD + DKP) = make_uint4(0u, 0u, 0u, 0u);
@@ -888,19 +891,15 @@ attn_decode_gqa_kernel(const AttnIn in, __nv_bfloat16* __restrict__ kcache, __nv
             vc[(size_t)pos * DKP + DK + tid] = __float2bfloat16_rn(0.0f);
         }
     }
-    // rotated queries as bf16 rows of the m16 tile, the new key and value into the cache
-    for (int i = tid; i < 16 * half; i += 128) {
+    // the group's rotated queries as bf16 rows of the m16 tile, the new key and value into the cache
+    for (int i = tid; i < REP * half; i += 128) {
         const int r = i / half, j = i % half;
         float c = 1.0f, sn = 0.0f;
         if (rope_cos) {
             c = rope_cos[(size_t)pos * half + j];
             sn = rope_sin[(size_t)pos * half + j];
         }
-        float qa = 0.0f, qb = 0.0f;
-        if (r < REP) {
-            qa = qn[r * DK + j];
-            qb = qn[r * DK + j + half];
-        }
+        const float qa = qn[r * DK + j], qb = qn[r * DK + j + half];
         Qs[r * LD + j] = __float2bfloat16_rn(__fadd_rn(__fmul_rn(qa, c), __fmul_rn(-qb, sn)));
         Qs[r * LD + j + half] = __float2bfloat16_rn(__fadd_rn(__fmul_rn(qb, c), __fmul_rn(qa, sn)));
         if (r == 0) {
@@ -1059,13 +1058,13 @@ attn_decode_gqa_kernel(const AttnIn in, __nv_bfloat16* __restrict__ kcache, __nv
 }
 
 template <int DK, int DKP = DK, int DKM = DK>
-static nnb_status launch_attn_decode_gqa(nnb_engine* e, void* kcache, void* vcache, size_t own_alloc, const void* kpre,
+static nnb_status launch_attn_decode_mma(nnb_engine* e, void* kcache, void* vcache, size_t own_alloc, const void* kpre,
                                          const void* vpre, size_t pre_len, size_t pre_alloc, size_t group, const float* rope_cos,
                                          const float* rope_sin, const int* d_pos, size_t B, size_t H, float* out, const AttnIn& in)
 {
     constexpr size_t LD = DKM + 8;
     const size_t smem = (16 * LD + 4 * 2 * 32 * LD) * sizeof(__nv_bfloat16);
-    auto kern = attn_decode_gqa_kernel<DK, DKP, DKM>;
+    auto kern = attn_decode_mma_kernel<DK, DKP, DKM>;
     static bool cfg_dev[64] = {}; bool& cfg = cfg_dev[e->device & 63];  // the attribute is per device
     if (!cfg) {
         NNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -1077,7 +1076,7 @@ static nnb_status launch_attn_decode_gqa(nnb_engine* e, void* kcache, void* vcac
                                                                             (int)group, rope_cos, rope_sin, d_pos, (int)B, (int)H,
                                                                             1.0f / sqrtf((float)DK), out);
     e->launches++;
-    NNB_CHECK_LAUNCH("attn_decode_gqa_kernel");
+    NNB_CHECK_LAUNCH("attn_decode_mma_kernel");
     return NNB_OK;
 }
 
@@ -1397,11 +1396,22 @@ nnb_status launch_attn_decode(nnb_engine* e, bool exact, const float* qkv, void*
         const char* ev = getenv("NNB_GQA_KERNEL");
         gqa_kernel = (ev && ev[0] == '0') ? 0 : 1;
     }
-    if (!exact && gqa_kernel && in.kv_rep >= 2 && in.kv_rep <= 16 && (dk == 128 || dk == 64)) {
+    // NNB_MMA_MHA=1 / 0: plain multi-head attention always / never on it (for A/B timing against the CUDA-core kernels)
+    static int mma_mha = -1, mma_mha_off = 0;
+    if (mma_mha < 0) {
+        const char* ev = getenv("NNB_MMA_MHA");
+        mma_mha = (ev && ev[0] == '1') ? 1 : 0;
+        mma_mha_off = (ev && ev[0] == '0') ? 1 : 0;
+    }
+    // Plain multi-head attention takes this kernel too when the cache is roomy: measured at 128 sequences x 16 heads of
+    // 128, it streams the cache a third faster than the CUDA-core kernel (0.0035 against 0.0052 ms per position over 24
+    // layers) but its larger CTAs cost 0.3 ms more per step at short contexts; the break-even is near 200 positions.
+    const bool roomy = pre_len + own_alloc >= 512 && !mma_mha_off;
+    if (!exact && gqa_kernel && (in.kv_rep >= 2 || mma_mha || roomy) && in.kv_rep <= 16 && (dk == 128 || dk == 64)) {
         if (dk == 128)
-            return launch_attn_decode_gqa<128>(e, kcache, vcache, own_alloc, kpre, vpre, pre_len, pre_alloc, group, rope_cos,
+            return launch_attn_decode_mma<128>(e, kcache, vcache, own_alloc, kpre, vpre, pre_len, pre_alloc, group, rope_cos,
                                                rope_sin, d_pos, B, H, out, in);
-        return launch_attn_decode_gqa<64>(e, kcache, vcache, own_alloc, kpre, vpre, pre_len, pre_alloc, group, rope_cos, rope_sin,
+        return launch_attn_decode_mma<64>(e, kcache, vcache, own_alloc, kpre, vpre, pre_len, pre_alloc, group, rope_cos, rope_sin,
                                           d_pos, B, H, out, in);
     }
     if (!exact && dk == 128)
@@ -1417,8 +1427,10 @@ nnb_status launch_attn_decode(nnb_engine* e, bool exact, const float* qkv, void*
         const char* ev = getenv("NNB_MMA_DK100");
         mma100 = (ev && ev[0] == '0') ? 0 : 1;
     }
-    if (!exact && dk == 100 && kv_pitch == 104 && mma100 && in.kv_rep <= 16)
-        return launch_attn_decode_gqa<100, 104, 112>(e, kcache, vcache, own_alloc, kpre, vpre, pre_len, pre_alloc, group, rope_cos,
+    // (below a few hundred cached positions the CUDA-core kernel's lighter prologue wins: measured crossover at ~150
+    // positions for 128 sequences x 32 heads; the choice goes by the cache's capacity, known on the host)
+    if (!exact && dk == 100 && kv_pitch == 104 && mma100 && in.kv_rep <= 16 && pre_len + own_alloc >= 512)
+        return launch_attn_decode_mma<100, 104, 112>(e, kcache, vcache, own_alloc, kpre, vpre, pre_len, pre_alloc, group, rope_cos,
                                                      rope_sin, d_pos, B, H, out, in);
     if (!exact && dk == 100 && kv_pitch == 104)  // caches of pitch attn_decode_kv_pitch(false, 100)
         return launch_attn_decode_bf16<100, 104>(e, qkv, kcache, vcache, own_alloc, kpre, vpre, pre_len, pre_alloc, group,

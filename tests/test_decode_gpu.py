@@ -232,6 +232,30 @@ def test_fast_mode_head_size_100(pkg, eng, group_size):
     eng.check_device_errors()
 
 
+@pytest.mark.parametrize("d,heads,kv", [(256, 4, 0), (512, 4, 0), (1600, 16, 0), (512, 4, 2)])
+@pytest.mark.parametrize("group_size", [1, 4])
+def test_tensor_core_decode_attention_with_a_roomy_cache(pkg, eng, d, heads, kv, group_size):
+    """from 512 cached positions of capacity on, the fast mode's decode attention runs on the tensor-core streamer for
+    head sizes 64, 128 and 100, multi-head or grouped: logits after a prompt of 490 tokens against the exact mode, and the
+    rollout's log-probs against the teacher-forced pass; also with the prompt shared by 4 sequences"""
+    kw = dict(n_layer=2, d_model=d, n_head=heads, n_head_kv=kv, d_ff=2 * d, vocab=500, ctx=520, act=1, pos=1)
+    cfg_e, cfg_f = pkg.GptConfig(exact=True, **kw), pkg.GptConfig(exact=False, **kw)
+    flat = cfg_e.init_params(3, bias_std=0.01)
+    pe, pf = pkg.Policy(eng, cfg_e), pkg.Policy(eng, cfg_f)
+    pe.upload_params(flat)
+    pf.upload_params(flat)
+    prompts = np.repeat(_prompts(cfg_e, 8 // group_size, 490, seed=8), group_size, axis=0)
+    p = torch.from_numpy(prompts).to(eng.device)
+    _, _, lg_e = pe.rollout(p, 30, 0.0, want_logits=True, group_size=group_size)
+    _, _, lg_f = pf.rollout(p, 30, 0.0, want_logits=True, group_size=group_size)
+    # the first generated position: both modes have consumed the same tokens there
+    assert (lg_e[:, 0] - lg_f[:, 0]).abs().max().item() <= 0.05 * lg_e[:, 0].abs().max().item()
+    toks, old_lp, _ = pf.rollout(p, 30, temperature=1.0, top_k=20, seed=1, group_size=group_size)
+    lp2, _, _ = pf.logprobs(toks, 490)
+    assert (lp2 - old_lp).abs().max().item() <= 2e-2 * max(old_lp.abs().max().item(), 1.0)
+    eng.check_device_errors()
+
+
 def test_host_rollout_entry_point(pkg, eng):
     cfg = pkg.GptConfig(n_layer=1, d_model=64, n_head=2, d_ff=128, vocab=300, ctx=24, act=0, pos=0)
     pol, m, _ = _setup(pkg, eng, cfg)
