@@ -519,6 +519,8 @@ def run_ours(args):
     dev = eng.device
     peaks = _peaks()
     wl = WORKLOADS[args.workload]
+    if args.groups and wl["kind"] == "grpo":
+        wl = dict(wl, groups=args.groups, text=wl["text"] + f" [prompt groups overridden: {args.groups}]")
     job = JOBS[wl["kind"]](torch, pkg, eng, wl, rank, world)
 
     def barrier():
@@ -836,6 +838,9 @@ def main():
     ap.add_argument("--workload", default="grpo1b", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true")
+    ap.add_argument("--groups", type=int, default=0,
+                    help="GRPO workloads: prompt groups instead of the workload's own count (e.g. 8 = one GPU's share of "
+                         "grpo1b at 8 GPUs); the line's config says so and is not the benchmark's")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
