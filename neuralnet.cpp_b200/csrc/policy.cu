@@ -220,8 +220,9 @@ nnb_status policy_tied_head_fwd(nnb_policy* p, const float* hn, __nv_bfloat16* h
     return launch_dense_nt_bf16(p->e, hnb, p->eb, T, V, d, logits);
 }
 
-static void free_ws(DecodeWs& w)
+static void free_decode(nnb_policy* p)
 {
+    DecodeWs& w = p->dec;
     void* ptrs[] = {w.k, w.v, w.k_pre, w.v_pre, w.tokens_pre, w.x, w.qkv, w.att, w.pre_ml, w.h1, w.logits, w.q8, w.s, w.qsum, w.d_pos,
                     w.tokens, w.logp, w.done, w.gen_len, w.qkv_raw, w.act, w.hn, w.hnb, w.sample_rows};
     for (void* q : ptrs)
@@ -229,22 +230,17 @@ static void free_ws(DecodeWs& w)
     w = DecodeWs();
 }
 
-static void free_decode(nnb_policy* p)
-{
-    free_ws(p->dec);
-    free_ws(p->dec2);
-}
-
 void policy_free_decode(nnb_policy* p) { free_decode(p); }
 
 // total positions = pre_len (shared prefix, one copy per group) + ctx_alloc (per sequence)
 // tok_cols: columns of the token / log-prob buffers (the whole sequence, which outgrows the cache once the
 // context window slides)
-static nnb_status ensure_decode(nnb_policy* p, DecodeWs& w, size_t B, size_t ctx_alloc, size_t group, size_t pre_len, size_t tok_cols)
+static nnb_status ensure_decode(nnb_policy* p, size_t B, size_t ctx_alloc, size_t group, size_t pre_len, size_t tok_cols)
 {
+    DecodeWs& w = p->dec;
     if (w.B == B && w.ctx_alloc == ctx_alloc && w.group == group && w.pre_len == pre_len && w.tok_cols == tok_cols) return NNB_OK;
     NNB_CUDA(cudaStreamSynchronize(p->e->stream));
-    free_ws(w);
+    free_decode(p);
     const nnb_gpt_config& c = p->cfg;
     const size_t d = c.d_model, F = c.d_ff, V = c.vocab, F1 = act_gated(c.act) ? 2 * F : F;
     const size_t kv_elem = c.exact ? 4 : 2;
@@ -263,7 +259,7 @@ static nnb_status ensure_decode(nnb_policy* p, DecodeWs& w, size_t B, size_t ctx
         cudaError_t er__ = cudaMalloc((void**)&(ptr), (bytes));                        \
         if (er__ != cudaSuccess) {                                                     \
             cudaGetLastError();                                                        \
-            free_ws(w);                                                                \
+            free_decode(p);                                                            \
             NNB_FAIL(NNB_ERR_OOM, "cudaMalloc(%zu) failed: %s", (size_t)(bytes), cudaGetErrorString(er__)); \
         }                                                                              \
     } while (0)
@@ -329,11 +325,12 @@ static bool pdl_enabled()
 
 // one decode step at the position stored in d_pos: consumes tokens[:, pos], appends to the KV
 // cache and, when with_head, samples tokens[:, pos+1]
-static nnb_status decode_step(nnb_policy* p, DecodeWs& w, const StepView& sv, bool with_head, const SampleOpts& so,
+static nnb_status decode_step(nnb_policy* p, const StepView& sv, bool with_head, const SampleOpts& so,
                               unsigned long long seed, unsigned seq0, int prompt_len, bool want_logp)
 {
     nnb_engine* e = p->e;
     const nnb_gpt_config& c = p->cfg;
+    DecodeWs& w = p->dec;
     const size_t B = sv.B, d = c.d_model, F = c.d_ff, V = c.vocab, H = c.n_head, dk = d / H;
     const size_t F1 = act_gated(c.act) ? 2 * F : F;
     const size_t Hkv = cfg_kv_heads(c);
@@ -426,44 +423,7 @@ struct StepGraph {
     int seen = 0;
 };
 
-// A rollout runs as one lane (all sequences) or as two lanes of half the sequences each: with few sequences a decode
-// step is a chain of ~220 short launches that leaves most of the GPU idle, so two independent chains side by side (two
-// streams forked and joined inside the step, hence two parallel branches of the captured graph) overlap one lane's
-// cache-bound attention with the other's latency-bound linears.  Per sequence nothing changes: every kernel's result for
-// a sequence is independent of which other sequences share its launch.
-struct Lane {
-    DecodeWs* w;
-    size_t row0, B;  // the lane's sequences in the caller's batch
-    StepView main_view, pre_view;
-    SampleOpts so;
-};
-
-static nnb_status step_lanes(nnb_policy* p, std::vector<Lane>& lanes, bool prefix_fill, bool with_head, unsigned long long seed,
-                             unsigned seq0, int prompt_len, bool want_logp)
-{
-    nnb_engine* e = p->e;
-    if (lanes.size() == 1) {
-        Lane& l = lanes[0];
-        return decode_step(p, *l.w, prefix_fill ? l.pre_view : l.main_view, with_head, l.so, seed, seq0, prompt_len, want_logp);
-    }
-    cudaStream_t main = e->stream;
-    NNB_CUDA(cudaEventRecord(p->lane_fork, main));
-    NNB_CUDA(cudaStreamWaitEvent(p->lane_stream, p->lane_fork, 0));
-    nnb_status st = NNB_OK;
-    for (size_t i = 0; i < lanes.size() && st == NNB_OK; ++i) {
-        Lane& l = lanes[i];
-        e->stream = i == 0 ? main : p->lane_stream;
-        st = decode_step(p, *l.w, prefix_fill ? l.pre_view : l.main_view, with_head, l.so, seed, seq0 + (unsigned)l.row0, prompt_len,
-                         want_logp);
-    }
-    e->stream = main;
-    // the join is recorded even after a failed launch, so that a capture in progress can be ended
-    cudaEventRecord(p->lane_join, p->lane_stream);
-    cudaStreamWaitEvent(main, p->lane_join, 0);
-    return st;
-}
-
-static nnb_status run_step(nnb_policy* p, StepGraph& g, bool allow_graph, std::vector<Lane>& lanes, bool prefix_fill, bool with_head,
+static nnb_status run_step(nnb_policy* p, StepGraph& g, bool allow_graph, const StepView& sv, bool with_head, const SampleOpts& so,
                            unsigned long long seed, unsigned seq0, int prompt_len, bool want_logp)
 {
     nnb_engine* e = p->e;
@@ -474,11 +434,11 @@ static nnb_status run_step(nnb_policy* p, StepGraph& g, bool allow_graph, std::v
     }
     if (g.seen == 0 || !allow_graph) {
         g.seen = 1;
-        return step_lanes(p, lanes, prefix_fill, with_head, seed, seq0, prompt_len, want_logp);
+        return decode_step(p, sv, with_head, so, seed, seq0, prompt_len, want_logp);
     }
     NNB_CUDA(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
     const unsigned long long l0 = e->launches;
-    const nnb_status cs = step_lanes(p, lanes, prefix_fill, with_head, seed, seq0, prompt_len, want_logp);
+    const nnb_status cs = decode_step(p, sv, with_head, so, seed, seq0, prompt_len, want_logp);
     cudaGraph_t graph = nullptr;
     const cudaError_t ce = cudaStreamEndCapture(e->stream, &graph);
     if (cs != NNB_OK) {
@@ -492,17 +452,6 @@ static nnb_status run_step(nnb_policy* p, StepGraph& g, bool allow_graph, std::v
     if (ie != cudaSuccess) NNB_FAIL(NNB_ERR_CUDA, "cudaGraphInstantiate failed: %s", cudaGetErrorString(ie));
     NNB_CUDA(cudaGraphLaunch(g.exec, e->stream));
     return NNB_OK;
-}
-
-// NNB_ROLLOUT_SPLIT=0 in the environment keeps every rollout on one lane (for A/B timing)
-static bool split_enabled()
-{
-    static int v = -1;
-    if (v < 0) {
-        const char* s = getenv("NNB_ROLLOUT_SPLIT");
-        v = (s && s[0] == '0') ? 0 : 1;
-    }
-    return v != 0;
 }
 
 // group > 1: sequences [g*group, (g+1)*group) were given the same prompt.  Their first P-1 prompt
@@ -528,37 +477,20 @@ nnb_status policy_rollout(nnb_policy* p, const int32_t* d_prompts, size_t B, siz
     if (windowed) group = 1;
     const size_t pre_len = (group > 1 && P > 1) ? P - 1 : 0;
     const size_t own = (windowed ? ctx : total) - pre_len;
+    NNB_TRY(ensure_decode(p, B, own, group, pre_len, total));
+    DecodeWs& w = p->dec;
+    SampleOpts so = so_in;
+    if (so.eos >= 0 || d_gen_len) {
+        so.done = w.done;
+        so.gen_len = w.gen_len;
+    }
     const size_t V = c.vocab, d = c.d_model;
     const size_t kv_elem = c.exact ? 4 : 2;
     const size_t dkv = cfg_kv_heads(c) * attn_decode_kv_pitch(c.exact != 0, d / c.n_head);
-    // Two lanes: few sequences (one wave of per-head attention CTAs at most) but enough for the tensor-core linears in
-    // each half (64 rows), whole groups per lane, no step timing (its events sit on one stream)
-    const bool split = split_enabled() && !windowed && !p->time_stride && B >= 128 && (B / group) % 2 == 0 &&
-                       B * (size_t)c.n_head <= (size_t)e->sm_count * 16;
-    if (split && !p->lane_stream) {
-        NNB_CUDA(cudaStreamCreateWithFlags(&p->lane_stream, cudaStreamNonBlocking));
-        NNB_CUDA(cudaEventCreateWithFlags(&p->lane_fork, cudaEventDisableTiming));
-        NNB_CUDA(cudaEventCreateWithFlags(&p->lane_join, cudaEventDisableTiming));
-    }
-    std::vector<Lane> lanes(split ? 2 : 1);
-    for (size_t i = 0; i < lanes.size(); ++i) {
-        Lane& l = lanes[i];
-        l.w = i == 0 ? &p->dec : &p->dec2;
-        l.B = B / lanes.size();
-        l.row0 = i * l.B;
-        NNB_TRY(ensure_decode(p, *l.w, l.B, own, group, pre_len, total));
-        DecodeWs& w = *l.w;
-        l.so = so_in;
-        if (l.so.eos >= 0 || d_gen_len) {
-            l.so.done = w.done;
-            l.so.gen_len = w.gen_len;
-        }
-        const size_t Bg = l.B / group;
-        l.main_view = StepView{l.B, w.tokens, total, w.k, w.v, own, l.B * dkv * own * kv_elem, w.k_pre, w.v_pre, pre_len, pre_len,
-                               Bg * dkv * pre_len * kv_elem, group};
-        l.pre_view = StepView{Bg, w.tokens_pre, pre_len, w.k_pre, w.v_pre, pre_len, Bg * dkv * pre_len * kv_elem, nullptr, nullptr, 0, 0, 0, 1};
-    }
-    if (!split) free_ws(p->dec2);
+    const size_t Bg = B / group;
+    StepView main_view{B, w.tokens, total, w.k, w.v, own, B * dkv * own * kv_elem, w.k_pre, w.v_pre, pre_len, pre_len,
+                       Bg * dkv * pre_len * kv_elem, group};
+    StepView pre_view{Bg, w.tokens_pre, pre_len, w.k_pre, w.v_pre, pre_len, Bg * dkv * pre_len * kv_elem, nullptr, nullptr, 0, 0, 0, 1};
 
     // the steps run on the engine's own stream (graph capture is not possible on the legacy default
     // stream); it is ordered after and before the caller's stream with events
@@ -573,30 +505,24 @@ nnb_status policy_rollout(nnb_policy* p, const int32_t* d_prompts, size_t B, siz
     }
     StepGraph graphs[3];  // prefix fill, own steps without head, own steps with head
     auto run = [&]() -> nnb_status {
-        bool prefilled = pre_len > 0 && policy_can_prefill(p);
-        for (Lane& l : lanes) {
-            DecodeWs& w = *l.w;
-            const int32_t* src = d_prompts + l.row0 * P;
-            const size_t Bg = l.B / group;
-            NNB_CUDA(cudaMemcpy2DAsync(w.tokens, total * 4, src, P * 4, P * 4, l.B, cudaMemcpyDeviceToDevice, e->stream));
-            if (pre_len > 0)  // prompt of the first member of every group, without its last token
-                NNB_CUDA(cudaMemcpy2DAsync(w.tokens_pre, pre_len * 4, src, group * P * 4, pre_len * 4, Bg, cudaMemcpyDeviceToDevice,
-                                           e->stream));
-            NNB_TRY(launch_set_int(e, w.d_pos, 0));
-            if (l.so.done) {
-                NNB_CUDA(cudaMemsetAsync(w.done, 0, l.B * 4, e->stream));
-                NNB_TRY(launch_fill_int(e, w.gen_len, l.B, (int)max_new));
-            }
-            if (prefilled) {
-                // fast mode: the shared prompt prefixes go through one teacher-forced forward (all positions at once)
-                // that leaves every layer's keys and values in the prefix cache, instead of pre_len decode steps
-                // (the lanes share the prefill workspace, so their prefills run one after the other on this stream)
-                NNB_TRY(policy_prefill_prefix(p, w.tokens_pre, Bg, pre_len, w.k_pre, w.v_pre, pre_len, Bg * dkv * pre_len * kv_elem));
-                NNB_TRY(launch_set_int(e, w.d_pos, (int)pre_len));
-            }
+        NNB_CUDA(cudaMemcpy2DAsync(w.tokens, total * 4, d_prompts, P * 4, P * 4, B, cudaMemcpyDeviceToDevice, e->stream));
+        if (pre_len > 0)  // prompt of the first member of every group, without its last token
+            NNB_CUDA(cudaMemcpy2DAsync(w.tokens_pre, pre_len * 4, d_prompts, group * P * 4, pre_len * 4, Bg,
+                                       cudaMemcpyDeviceToDevice, e->stream));
+        NNB_TRY(launch_set_int(e, w.d_pos, 0));
+        if (so.done) {
+            NNB_CUDA(cudaMemsetAsync(w.done, 0, B * 4, e->stream));
+            NNB_TRY(launch_fill_int(e, w.gen_len, B, (int)max_new));
         }
         const bool allow_graph = total >= 8;
-        const size_t t0 = prefilled ? pre_len : 0;
+        size_t t0 = 0;
+        if (pre_len > 0 && policy_can_prefill(p)) {
+            // fast mode: the shared prompt prefixes go through one teacher-forced forward (all positions at once)
+            // that leaves every layer's keys and values in the prefix cache, instead of pre_len decode steps
+            NNB_TRY(policy_prefill_prefix(p, w.tokens_pre, Bg, pre_len, w.k_pre, w.v_pre, pre_len, Bg * dkv * pre_len * kv_elem));
+            NNB_TRY(launch_set_int(e, w.d_pos, (int)pre_len));
+            t0 = pre_len;
+        }
         auto mark = [&](size_t t) -> nnb_status {
             cudaEvent_t evt = nullptr;
             NNB_CUDA(cudaEventCreate(&evt));
@@ -610,14 +536,7 @@ nnb_status policy_rollout(nnb_policy* p, const int32_t* d_prompts, size_t B, siz
             p->time_events.clear();
             p->time_pos.clear();
         }
-        auto copy_logits = [&](size_t gi) -> nnb_status {
-            for (Lane& l : lanes)
-                NNB_CUDA(cudaMemcpy2DAsync(d_logits + (l.row0 * max_new + gi) * V, max_new * V * 4, l.w->logits, V * 4, V * 4, l.B,
-                                           cudaMemcpyDeviceToDevice, e->stream));
-            return NNB_OK;
-        };
         if (windowed) {
-            DecodeWs& w = *lanes[0].w;
             size_t cur = 0;  // tokens in the window = position of the next one
             const size_t col0 = P > ctx ? P - ctx : 0;  // a prompt longer than the context is cut to its tail
             NNB_TRY(launch_set_int2(e, w.d_pos, 0, (int)col0));
@@ -629,24 +548,33 @@ nnb_status policy_rollout(nnb_policy* p, const int32_t* d_prompts, size_t B, siz
                     NNB_TRY(launch_set_int2(e, w.d_pos, 0, (int)start));
                     cur = 0;
                     for (size_t i = start; i < col; ++i, ++cur)
-                        NNB_TRY(run_step(p, graphs[1], allow_graph, lanes, false, false, seed, seq0, (int)P, false));
+                        NNB_TRY(run_step(p, graphs[1], allow_graph, main_view, false, so, seed, seq0, (int)P, false));
                 }
-                NNB_TRY(run_step(p, graphs[with_head ? 2 : 1], allow_graph, lanes, false, with_head, seed, seq0, (int)P,
+                NNB_TRY(run_step(p, graphs[with_head ? 2 : 1], allow_graph, main_view, with_head, so, seed, seq0, (int)P,
                                  d_logp != nullptr));
                 ++cur;
-                if (with_head && d_logits) NNB_TRY(copy_logits(col + 1 - P));
+                if (with_head && d_logits) {
+                    const size_t gi = col + 1 - P;
+                    NNB_CUDA(cudaMemcpy2DAsync(d_logits + gi * V, max_new * V * 4, w.logits, V * 4, V * 4, B,
+                                               cudaMemcpyDeviceToDevice, e->stream));
+                }
             }
             return NNB_OK;
         }
         for (size_t t = t0; t + 1 < total; ++t) {
             if (p->time_stride && (t - t0) % p->time_stride == 0) NNB_TRY(mark(t));
             if (t < pre_len) {
-                NNB_TRY(run_step(p, graphs[0], allow_graph, lanes, true, false, seed, seq0, (int)P, false));
+                NNB_TRY(run_step(p, graphs[0], allow_graph, pre_view, false, so, seed, seq0, (int)P, false));
                 continue;
             }
             const bool with_head = t + 1 >= P;
-            NNB_TRY(run_step(p, graphs[with_head ? 2 : 1], allow_graph, lanes, false, with_head, seed, seq0, (int)P, d_logp != nullptr));
-            if (with_head && d_logits) NNB_TRY(copy_logits(t + 1 - P));
+            NNB_TRY(run_step(p, graphs[with_head ? 2 : 1], allow_graph, main_view, with_head, so, seed, seq0,
+                             (int)P, d_logp != nullptr));
+            if (with_head && d_logits) {
+                const size_t gi = t + 1 - P;
+                NNB_CUDA(cudaMemcpy2DAsync(d_logits + gi * V, max_new * V * 4, w.logits, V * 4, V * 4, B,
+                                           cudaMemcpyDeviceToDevice, e->stream));
+            }
         }
         if (p->time_stride) NNB_TRY(mark(total - 1));
         return NNB_OK;
@@ -658,7 +586,6 @@ nnb_status policy_rollout(nnb_policy* p, const int32_t* d_prompts, size_t B, siz
             cudaGraphExecDestroy(g.exec);
         }
     if (st != NNB_OK) {
-        if (p->lane_stream) cudaStreamSynchronize(p->lane_stream);
         if (swap) {
             cudaStreamSynchronize(e->own_stream);
             e->stream = user;
@@ -666,14 +593,11 @@ nnb_status policy_rollout(nnb_policy* p, const int32_t* d_prompts, size_t B, siz
         }
         return st;
     }
-    for (Lane& l : lanes) {
-        DecodeWs& w = *l.w;
-        NNB_CUDA(cudaMemcpyAsync(d_tokens + l.row0 * total, w.tokens, l.B * total * 4, cudaMemcpyDeviceToDevice, e->stream));
-        if (d_logp)
-            NNB_CUDA(cudaMemcpy2DAsync(d_logp + l.row0 * max_new, max_new * 4, w.logp, total * 4, max_new * 4, l.B,
-                                       cudaMemcpyDeviceToDevice, e->stream));
-        if (d_gen_len) NNB_CUDA(cudaMemcpyAsync(d_gen_len + l.row0, w.gen_len, l.B * 4, cudaMemcpyDeviceToDevice, e->stream));
-    }
+    NNB_CUDA(cudaMemcpyAsync(d_tokens, w.tokens, B * total * 4, cudaMemcpyDeviceToDevice, e->stream));
+    if (d_logp)
+        NNB_CUDA(cudaMemcpy2DAsync(d_logp, max_new * 4, w.logp, total * 4, max_new * 4, B,
+                                   cudaMemcpyDeviceToDevice, e->stream));
+    if (d_gen_len) NNB_CUDA(cudaMemcpyAsync(d_gen_len, w.gen_len, B * 4, cudaMemcpyDeviceToDevice, e->stream));
     if (swap) {
         NNB_CUDA(cudaEventRecord(ev, e->own_stream));
         NNB_CUDA(cudaStreamWaitEvent(user, ev, 0));
@@ -751,9 +675,6 @@ void nnb_policy_destroy(nnb_policy* p)
     if (!p) return;
     cudaStreamSynchronize(p->e->stream);
     for (cudaEvent_t evt : p->time_events) cudaEventDestroy(evt);
-    if (p->lane_stream) cudaStreamDestroy(p->lane_stream);
-    if (p->lane_fork) cudaEventDestroy(p->lane_fork);
-    if (p->lane_join) cudaEventDestroy(p->lane_join);
     free_decode(p);
     policy_free_train(p);
     void* ptrs[] = {p->params, p->grads, p->adam_m, p->adam_v, p->packed, p->tau, p->rope_cos, p->rope_sin, p->w8, p->wb, p->eb};

@@ -72,10 +72,6 @@ struct nnb_policy {
     nnb::LinW head;
     std::vector<nnb::TensorInfo> tensors;
     nnb::DecodeWs dec;
-    // second decode workspace and stream: a rollout of few sequences runs as two half-batches side by side
-    nnb::DecodeWs dec2;
-    cudaStream_t lane_stream = nullptr;
-    cudaEvent_t lane_fork = nullptr, lane_join = nullptr;
     // optional timing of the rollout: a CUDA event every time_stride decode steps (0 = off)
     size_t time_stride = 0;
     std::vector<cudaEvent_t> time_events;

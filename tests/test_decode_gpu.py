@@ -258,9 +258,9 @@ def test_tensor_core_decode_attention_with_a_roomy_cache(pkg, eng, d, heads, kv,
 
 @pytest.mark.parametrize("group_size,kw", [(1, dict(temperature=0.9, top_k=30)), (4, dict(temperature=1.0, top_k=12)),
                                            (4, dict(temperature=1.0, top_k=8, eos=True))])
-def test_rollout_of_128_sequences_runs_as_two_lanes_and_matches_the_restatement(pkg, eng, group_size, kw):
-    """from 128 sequences (and few heads) a rollout runs as two half-batches on two streams inside every step: tokens,
-    log-probs, lengths and logits must be those of the CPU restatement for every row, in the caller's order"""
+def test_rollout_of_128_sequences_matches_the_restatement(pkg, eng, group_size, kw):
+    """128 sequences, alone and in groups of 4 with a shared prompt prefix: tokens, log-probs, lengths and logits are those
+    of the CPU restatement for every row, in the caller's order"""
     kw = dict(kw)
     use_eos = kw.pop("eos", False)
     cfg = pkg.GptConfig(n_layer=1, d_model=64, n_head=2, d_ff=128, vocab=300, ctx=32, act=1, pos=1)
@@ -281,22 +281,6 @@ def test_rollout_of_128_sequences_runs_as_two_lanes_and_matches_the_restatement(
     tok2, _, lg = pol.rollout(torch.from_numpy(prompts).to(eng.device), 4, temperature=0.0, want_logits=True, group_size=group_size)
     assert np.array_equal(tok2.cpu().numpy(), tok_g)
     assert np.array_equal(lg.cpu().numpy().view(np.uint32), lg_ref.view(np.uint32))
-
-
-def test_two_lane_rollout_in_the_fast_mode_equals_its_halves_run_alone(pkg, eng):
-    """fast mode, 128 sequences in groups of 4: the two-lane rollout gives, row for row, what two rollouts of 64 sequences
-    (one lane each: below 128 sequences nothing is split) give with the matching sequence offsets"""
-    cfg = pkg.GptConfig(n_layer=2, d_model=128, n_head=2, d_ff=256, vocab=500, ctx=48, act=1, pos=1, exact=False)
-    pol = pkg.Policy(eng, cfg)
-    pol.upload_params(cfg.init_params(3, bias_std=0.01))
-    prompts = torch.from_numpy(np.repeat(_prompts(cfg, 32, 9, seed=2), 4, axis=0)).to(eng.device)
-    tok, lp, _ = pol.rollout(prompts, 20, temperature=0.9, top_k=25, seed=4, seq0=100, group_size=4)
-    for half in range(2):
-        rows = slice(64 * half, 64 * half + 64)
-        t2, l2, _ = pol.rollout(prompts[rows].contiguous(), 20, temperature=0.9, top_k=25, seed=4, seq0=100 + 64 * half, group_size=4)
-        assert torch.equal(tok[rows], t2)
-        assert torch.equal(lp[rows], l2)
-    eng.check_device_errors()
 
 
 def test_host_rollout_entry_point(pkg, eng):
