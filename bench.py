@@ -708,8 +708,9 @@ class CpuArm:
         self.rng = np.random.default_rng(1)
         model = dict(wl["model"])
         self.layer_scale = 1.0
-        if workload == "decode3b":
-            model["n_layer"] = 2  # 2 of 26 layers (1.8 GB of f32 weights instead of 13 GB); the per-layer cost is scaled
+        if model["n_layer"] > 24:
+            # 2 of the layers (a couple of GB of f32 weights instead of 10+ GB); the per-layer cost is scaled
+            model["n_layer"] = 2
             self.layer_scale = wl["model"]["n_layer"] / 2.0
         self.cfg = self.pkg.GptConfig(exact=True, **model)
         self.flat = _cpu_flat(self.cfg)
@@ -723,15 +724,23 @@ class CpuArm:
         t0 = time.perf_counter()
         self.gpt.rollout(prompts, G_s, wl["temperature"], wl["top_k"], seed=1)
         t_roll = time.perf_counter() - t0
-        per_tok_decode = t_roll / (n_seq * (P_s + G_s - 1)) * self.layer_scale
+        # the sample's time per token splits into the layers (scaled to the full depth) and the head (not scaled), by
+        # their multiply-accumulate counts
+        m = wl["model"]
+        dm, Fm, Hm = m["d_model"], m["d_ff"], m["n_head"]
+        dkv_m = (m.get("n_head_kv") or Hm) * (dm // Hm)
+        layer_macs = 2 * dm * dm + 2 * dkv_m * dm + (3 if m["act"] >= 1 else 2) * dm * Fm
+        head_frac = m["vocab"] * dm / (m["vocab"] * dm + cfg.n_layer * layer_macs)
+        per_tok_decode = t_roll / (n_seq * (P_s + G_s - 1)) * ((1.0 - head_frac) * self.layer_scale + head_frac)
         S = wl["prompt_len"] + wl["max_new"]
         if wl["kind"] == "decode":
             N = wl["n_seq"]
             est = per_tok_decode * N * (S - 1)
             return {"step_s": est, "value": N * wl["max_new"] / est, "extrapolated": True,
-                    "sample": f"C step-path rollout of {n_seq} seqs x {P_s + G_s} tokens on 2 of the 26 layers ({t_roll:.1f} s), scaled by "
-                              f"13 and per token to 512 x 2047 token-steps (attention cost at the sample's short context; the head's "
-                              f"cost is scaled with the layers, which overstates the CPU time by < 10 %)"}
+                    "sample": f"C step-path rollout of {n_seq} seqs x {P_s + G_s} tokens on 2 of the {wl['model']['n_layer']} layers "
+                              f"({t_roll:.1f} s), the layers scaled by {self.layer_scale:g}, and per token to {N} x {S - 1} token-steps (attention cost at "
+                              f"the sample's short context; the head's share of the sample, {head_frac:.2f} by multiply-accumulates, is "
+                              f"not scaled)"}
         if self.name == "tiny":  # small enough to run whole: a measured step, nothing extrapolated
             c1 = cpu_config1_step(self.pkg, self.ob, self.ot)
             return {"step_s": c1["step_s"], "value": 1.0 / c1["step_s"], "extrapolated": False,
@@ -752,14 +761,15 @@ class CpuArm:
         if wl["kind"] == "grpo":
             N = wl["groups"] * wl["group_size"]
             n_ref = 1 if wl["kl_coef"] != 0.0 else 0
-            est = per_tok_decode * N * (S - 1) + (t_fwd / rows) * N * S * (1 + n_ref) + (t_bwd / rows) * N * S
+            est = per_tok_decode * N * (S - 1) + self.layer_scale * ((t_fwd / rows) * N * S * (1 + n_ref) + (t_bwd / rows) * N * S)
         else:
             N = wl["n_seq"]
             est = per_tok_decode * N * (S - 1) + (t_fwd / rows) * N * S * (1 + wl["epochs"]) + (t_bwd / rows) * N * S * wl["epochs"]
         return {"step_s": est, "value": 1.0 / est, "extrapolated": True,
                 "sample": f"C step-path rollout of {n_seq} seqs x {P_s + G_s} tokens ({t_roll:.1f} s), numpy forward+backward of {n_t} x {S_t} "
                           f"tokens ({t_fwd:.1f}+{t_bwd:.1f} s), extrapolated per token to the full step (attention cost at the "
-                          "sample's short context)"}
+                          "sample's short context)" + (f"; 2 of the {wl['model']['n_layer']} layers, scaled by {self.layer_scale:g}"
+                                                       if self.layer_scale != 1.0 else "")}
 
 
 def cpu_baseline(workload: str, gpu=None):
