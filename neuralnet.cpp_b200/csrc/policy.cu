@@ -374,7 +374,13 @@ static nnb_status decode_step(nnb_policy* p, const StepView& sv, bool with_head,
         // One CTA per sequence needs a few hundred sequences to fill the GPU.  Below about one wave of per-head CTAs
         // (16 resident per SM) the kernel with one CTA per (sequence, head), four warps splitting the keys, has
         // several times the loads in flight and wins, the separate quantisation launch included.
-        const bool few = B * H <= (size_t)e->sm_count * 16;
+        static int few_ctas = -1;  // NNB_FEW_CTAS in the environment: (sequence, head) CTAs per SM up to which the per-head path runs
+        if (few_ctas < 0) {
+            const char* ev = getenv("NNB_FEW_CTAS");
+            few_ctas = ev ? atoi(ev) : 16;
+            if (few_ctas < 0) few_ctas = 0;
+        }
+        const bool few = B * H <= (size_t)e->sm_count * (size_t)few_ctas;
         if (!exact && !few && !c.sub_ln && !gqa && attn_decode_fused_supported(H, dk) && d % 64 == 0) {
             // all heads of a sequence in one CTA, attention output quantised in the same launch.  (Not with SubLN, which
             // normalises the row first, nor with grouped queries: measured on the 2B4T shape, the warps of a KV group drift
