@@ -133,7 +133,7 @@ nnb_status launch_bitlinear_fwd_tm(nnb_engine* e, const uint32_t* wq, size_t wq_
 // quantises the transformed row; f_out (t,k) optional copy of the transformed row
 nnb_status launch_row_quant(nnb_engine* e, int mode, bool exact, const float* in, const float* gamma,
                             size_t t, size_t k, size_t in_stride, int8_t* q, float* s,
-                            int32_t* qsum, float* f_out);
+                            int32_t* qsum, float* f_out, bool norm_after = false);
 // Where a decode step's new projections live and how the heads map: q, k, v point at sequence 0 (rows `stride` floats
 // apart); kv_rep query heads read one key / value head (grouped-query attention; 1 = multi-head), the caches then hold
 // H / kv_rep heads.  Without it the launchers take qkv as three (B, d) planes.

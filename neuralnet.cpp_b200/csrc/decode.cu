@@ -45,7 +45,10 @@ __global__ void embed_kernel(const float* __restrict__ tok_emb, const float* __r
 // One CTA per token.  MODE 0: RMSNorm(x)*gamma.  MODE 1: QuickGELU(h).  MODE 2: SwiGLU(h) with
 // h = (gate | up).  MODE 3: identity.  MODE 4: ReLU2GLU(h) = relu(gate)^2 * up (include/neuralnet.cpp/compute_layer_mlp.hpp:384-440).  The transformed row is quantised to the engine's int8
 // layout (see ternary.cu) and optionally also written as f32 (`f_out`).
-template <int MODE, bool EXACT>
+// NORM (MODE 1, 2, 4 only): the activated row goes through RMSNorm(.)*gamma before it is quantised (SubLN of the
+// feed-forward, include/neuralnet.cpp/compute_layer_feedforward.hpp:201-206); f_out then receives the activated row
+// before the norm, which is what the norm's backward needs.
+template <int MODE, bool EXACT, bool NORM = false>
 __global__ void __launch_bounds__(256)
 row_quant_kernel(const float* __restrict__ in, const float* __restrict__ gamma, int k, int in_stride,
                  int8_t* __restrict__ q, float* __restrict__ s, int32_t* __restrict__ qsum,
@@ -94,6 +97,8 @@ row_quant_kernel(const float* __restrict__ in, const float* __restrict__ gamma, 
         __syncthreads();
     }
     float mx = 0.0f;
+    double ss_act = 0.0;
+    float ssf_act = 0.0f;
     for (int i = tid; i < k; i += 256) {
         float v;
         if (MODE == 0) {
@@ -113,8 +118,43 @@ row_quant_kernel(const float* __restrict__ in, const float* __restrict__ gamma, 
         }
         row[i] = v;
         if (f_out) f_out[tok * (size_t)k + i] = v;
-        const float a = fabsf(v);
-        if (a > mx) mx = a;
+        if (NORM) {
+            if (EXACT) ss_act += (double)__fmul_rn(v, v);
+            else ssf_act = fmaf(v, v, ssf_act);
+        } else {
+            const float a = fabsf(v);
+            if (a > mx) mx = a;
+        }
+    }
+    if (NORM) {
+        // the same statistics and roundings as MODE 0, on the activated row
+        float ssf;
+        if (EXACT) {
+            ss_act = warp_sum_d(ss_act);
+            if (lane == 0) red_d[warp] = ss_act;
+            __syncthreads();
+            double t = 0.0;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) t += red_d[w];
+            ssf = (float)t;
+        } else {
+            ssf_act = warp_sum(ssf_act);
+            if (lane == 0) red_f[warp] = ssf_act;
+            __syncthreads();
+            float t = 0.0f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) t += red_f[w];
+            ssf = t;
+        }
+        const float vn = __fadd_rn(__fmul_rn(ssf, __frcp_rn((float)k)), 1e-5f);
+        const float sinv_a = __frcp_rn(__fsqrt_rn(vn));
+        __syncthreads();
+        for (int i = tid; i < k; i += 256) {
+            const float v = __fmul_rn(__fmul_rn(row[i], sinv_a), gamma[i]);
+            row[i] = v;
+            const float a = fabsf(v);
+            if (a > mx) mx = a;
+        }
     }
     mx = warp_max(mx);
     if (lane == 0) red_f[warp] = mx;
@@ -152,7 +192,7 @@ row_quant_kernel(const float* __restrict__ in, const float* __restrict__ gamma, 
 // Fast-mode variant of row_quant_kernel: same layout and outputs, 16-byte loads and stores, hardware
 // exp / divide approximations and f32 sums (the exact mode keeps the kernel above, whose every rounding
 // step follows the reference).
-template <int MODE>
+template <int MODE, bool NORM = false>
 __global__ void __launch_bounds__(256)
 row_quant_fast_kernel(const float* __restrict__ in, const float* __restrict__ gamma, int k, int in_stride,
                       int8_t* __restrict__ q, float* __restrict__ s, int32_t* __restrict__ qsum, float* __restrict__ f_out)
@@ -186,7 +226,7 @@ row_quant_fast_kernel(const float* __restrict__ in, const float* __restrict__ ga
         sinv = rsqrtf(ss / (float)k + 1e-5f);
         __syncthreads();
     }
-    float mx = 0.0f;
+    float mx = 0.0f, ss_act = 0.0f;
     for (int c = tid; c < nv; c += 256) {
         float4 v;
         if (MODE == 0) {
@@ -211,7 +251,25 @@ row_quant_fast_kernel(const float* __restrict__ in, const float* __restrict__ ga
         }
         row4[c] = v;
         if (f4) f4[c] = v;
-        mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+        if (NORM) ss_act = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss_act))));
+        else mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+    }
+    if (NORM) {
+        ss_act = warp_sum(ss_act);
+        if (lane == 0) red_f[warp] = ss_act;
+        __syncthreads();
+        float t = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) t += red_f[w];
+        const float sinv_a = rsqrtf(t / (float)k + 1e-5f);
+        __syncthreads();
+        for (int c = tid; c < nv; c += 256) {
+            const float4 x = row4[c];
+            const float4 g = reinterpret_cast<const float4*>(gamma)[c];
+            const float4 v = make_float4(x.x * sinv_a * g.x, x.y * sinv_a * g.y, x.z * sinv_a * g.z, x.w * sinv_a * g.w);
+            row4[c] = v;
+            mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+        }
     }
     mx = warp_max(mx);
     if (lane == 0) red_f[warp] = mx;
@@ -249,7 +307,7 @@ row_quant_fast_kernel(const float* __restrict__ in, const float* __restrict__ ga
     }
 }
 
-template <int MODE>
+template <int MODE, bool NORM = false>
 static nnb_status launch_row_quant_mode(nnb_engine* e, bool exact, const float* in,
                                         const float* gamma, size_t t, size_t k, size_t in_stride,
                                         int8_t* q, float* s, int32_t* qsum, float* f_out)
@@ -257,33 +315,41 @@ static nnb_status launch_row_quant_mode(nnb_engine* e, bool exact, const float* 
     const size_t smem = k * sizeof(float);
     static bool cfg_dev[64] = {}; bool& cfg = cfg_dev[e->device & 63];  // the attribute is per device
     if (!cfg) {
-        NNB_CUDA(cudaFuncSetAttribute(row_quant_kernel<MODE, true>,
+        NNB_CUDA(cudaFuncSetAttribute(row_quant_kernel<MODE, true, NORM>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
-        NNB_CUDA(cudaFuncSetAttribute(row_quant_kernel<MODE, false>,
+        NNB_CUDA(cudaFuncSetAttribute(row_quant_kernel<MODE, false, NORM>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
-        NNB_CUDA(cudaFuncSetAttribute(row_quant_fast_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+        NNB_CUDA(cudaFuncSetAttribute(row_quant_fast_kernel<MODE, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
         cfg = true;
     }
     const bool aligned = in_stride % 4 == 0 && ((uintptr_t)in & 15) == 0 && (!f_out || ((uintptr_t)f_out & 15) == 0) &&
-                         (MODE != 0 || ((uintptr_t)gamma & 15) == 0);
+                         ((MODE != 0 && !NORM) || ((uintptr_t)gamma & 15) == 0);
     if (exact)
-        row_quant_kernel<MODE, true><<<(unsigned)t, 256, smem, e->stream>>>(in, gamma, (int)k, (int)in_stride, q, s, qsum, f_out);
+        row_quant_kernel<MODE, true, NORM><<<(unsigned)t, 256, smem, e->stream>>>(in, gamma, (int)k, (int)in_stride, q, s, qsum, f_out);
     else if (aligned)
-        launch_ex(e, row_quant_fast_kernel<MODE>, dim3((unsigned)t), dim3(256), smem, in, gamma, (int)k, (int)in_stride, q, s, qsum,
-                  f_out);
+        launch_ex(e, row_quant_fast_kernel<MODE, NORM>, dim3((unsigned)t), dim3(256), smem, in, gamma, (int)k, (int)in_stride, q, s,
+                  qsum, f_out);
     else
-        row_quant_kernel<MODE, false><<<(unsigned)t, 256, smem, e->stream>>>(in, gamma, (int)k, (int)in_stride, q, s, qsum, f_out);
+        row_quant_kernel<MODE, false, NORM><<<(unsigned)t, 256, smem, e->stream>>>(in, gamma, (int)k, (int)in_stride, q, s, qsum,
+                                                                                   f_out);
     e->launches++;
     NNB_CHECK_LAUNCH("row_quant_kernel");
     return NNB_OK;
 }
 
+// norm_after: modes 1, 2, 4 only; the activated row is RMS-normalised with gamma before it is quantised
 nnb_status launch_row_quant(nnb_engine* e, int mode, bool exact, const float* in, const float* gamma,
                             size_t t, size_t k, size_t in_stride, int8_t* q, float* s,
-                            int32_t* qsum, float* f_out)
+                            int32_t* qsum, float* f_out, bool norm_after)
 {
     NNB_REQUIRE(in && q && s && qsum && t > 0, "row_quant: bad arguments");
     NNB_REQUIRE(k > 0 && k % 64 == 0 && k * 4 <= 96 * 1024, "row_quant: k=%zu must be a multiple of 64 (<= 24576)", k);
+    NNB_REQUIRE(!norm_after || (gamma && (mode == 1 || mode == 2 || mode == 4)), "row_quant: the norm after an activation needs gamma");
+    if (norm_after) switch (mode) {
+            case 1: return launch_row_quant_mode<1, true>(e, exact, in, gamma, t, k, in_stride, q, s, qsum, f_out);
+            case 2: return launch_row_quant_mode<2, true>(e, exact, in, gamma, t, k, in_stride, q, s, qsum, f_out);
+            default: return launch_row_quant_mode<4, true>(e, exact, in, gamma, t, k, in_stride, q, s, qsum, f_out);
+        }
     switch (mode) {
         case 0:
             NNB_REQUIRE(gamma, "row_quant: RMSNorm needs gamma");

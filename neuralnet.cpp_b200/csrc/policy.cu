@@ -285,7 +285,6 @@ static nnb_status ensure_decode(nnb_policy* p, size_t B, size_t ctx_alloc, size_
     NNB_ALLOC(w.done, B * 4);
     NNB_ALLOC(w.gen_len, B * 4);
     if (cfg_gqa(c)) NNB_ALLOC(w.qkv_raw, B * (d + 2 * cfg_kv_heads(c) * (d / c.n_head)) * 4);
-    if (c.sub_ln) NNB_ALLOC(w.act, B * F * 4);
     if (!sample_row_in_smem(V)) NNB_ALLOC(w.sample_rows, B * ((V + 3) & ~(size_t)3) * 4);
     if (c.tie_embeddings) {
         NNB_ALLOC(w.hn, B * d * 4);
@@ -402,9 +401,9 @@ static nnb_status decode_step(nnb_policy* p, const StepView& sv, bool with_head,
         }
         NNB_TRY(launch_row_quant(e, 0, exact, w.x, P + L.ln2_g, B, d, d, w.q8, w.s, w.qsum, nullptr));
         NNB_TRY(policy_linear_fwd(p, L.fc1, 1, w.q8, w.s, w.qsum, B, nullptr, w.h1, 0));
-        NNB_TRY(launch_row_quant(e, act_quant_mode(c.act), exact, w.h1, nullptr, B, F, F1, w.q8, w.s, w.qsum, c.sub_ln ? w.act : nullptr));
-        if (c.sub_ln)  // SubLN: the activated hidden is normalised, then quantised for fc2
-            NNB_TRY(launch_row_quant(e, 0, exact, w.act, P + L.ffn_sub_g, B, F, F, w.q8, w.s, w.qsum, nullptr));
+        // SubLN: the activated hidden is normalised, then quantised for fc2, in the same launch
+        NNB_TRY(launch_row_quant(e, act_quant_mode(c.act), exact, w.h1, c.sub_ln ? P + L.ffn_sub_g : nullptr, B, F, F1, w.q8, w.s,
+                                 w.qsum, nullptr, c.sub_ln != 0));
         NNB_TRY(policy_linear_fwd(p, L.fc2, 1, w.q8, w.s, w.qsum, B, w.x, w.x, 0));
     }
     if (with_head) {

@@ -35,7 +35,7 @@ struct DecodeWs {
     int32_t* tokens_pre = nullptr;            // (B/group, pre_len) prompt tokens of the group representatives
     float *x = nullptr, *qkv = nullptr, *att = nullptr, *h1 = nullptr, *logits = nullptr;
     float* qkv_raw = nullptr;  // grouped-query attention: (B, d + 2 dkv) projections before the KV heads are replicated
-    float* act = nullptr;      // SubLN: (B, d_ff) activated hidden before its norm
+    float* act = nullptr;      // (unused: the feed-forward SubLN is applied inside the quantiser launch)
     float* sample_rows = nullptr;  // (B, V) the sampler's working rows when a row does not fit shared memory
     float* hn = nullptr;       // tied embeddings: (B, d) final-norm output, the dense head's operand
     __nv_bfloat16* hnb = nullptr;

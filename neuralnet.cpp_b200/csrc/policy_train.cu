@@ -293,10 +293,9 @@ static nnb_status forward(nnb_policy* p, const int32_t* tokens, size_t n_seq, si
         NNB_TRY(lin_fwd(p, LW.o, 1, s.q2, s.s2, w->qsum, T, x_in, s.x_mid, 0));
         NNB_TRY(launch_row_quant(e, 0, exact, s.x_mid, PP + LW.ln2_g, T, d, d, s.q3, s.s3, w->qsum, nullptr));
         NNB_TRY(lin_fwd(p, LW.fc1, 1, s.q3, s.s3, w->qsum, T, nullptr, s.h1, 0));
-        NNB_TRY(launch_row_quant(e, act_quant_mode(c.act), exact, s.h1, nullptr, T, F, F1, s.q4, s.s4, w->qsum,
-                                 c.sub_ln ? w->act : nullptr));
-        if (c.sub_ln)  // SubLN: the activated hidden is normalised, then quantised for fc2
-            NNB_TRY(launch_row_quant(e, 0, exact, w->act, PP + LW.ffn_sub_g, T, F, F, s.q4, s.s4, w->qsum, nullptr));
+        // SubLN: the activated hidden is normalised, then quantised for fc2, in the same launch
+        NNB_TRY(launch_row_quant(e, act_quant_mode(c.act), exact, s.h1, c.sub_ln ? PP + LW.ffn_sub_g : nullptr, T, F, F1, s.q4, s.s4,
+                                 w->qsum, nullptr, c.sub_ln != 0));
         NNB_TRY(lin_fwd(p, LW.fc2, 1, s.q4, s.s4, w->qsum, T, s.x_mid, x_out, 0));
     }
     if (!w->with_head) return NNB_OK;
