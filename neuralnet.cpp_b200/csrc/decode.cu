@@ -754,7 +754,6 @@ attn_prefix_kernel(const AttnIn in, const __nv_bfloat16* __restrict__ kpre, cons
     __nv_bfloat16* Vs = Ks + KT * LD;
     const int grp = blockIdx.x, h = blockIdx.y * 4 + warp;
     if (h >= H) return;
-    const int d = H * DK;
     const int pos = *d_pos;
 
     // the group's queries, rotated, as bf16 rows (rows beyond the group stay zero)
@@ -947,9 +946,10 @@ attn_decode_mma_kernel(const AttnIn in, __nv_bfloat16* __restrict__ kcache, __nv
     for (int i = tid; i < (16 - REP) * (LD / 8); i += 128)
         reinterpret_cast<uint4*>(Qs + REP * LD)[i] = make_uint4(0u, 0u, 0u, 0u);
     // pad columns: of the query rows, of every warp's key / value tile (cp.async never writes them), of the cache row
-    if (DKM > DK) {
-        for (int i = tid; i < REP * (DKM - DK); i += 128) Qs[(i / (DKM - DK)) * LD + DK + i % (DKM - DK)] = __float2bfloat16_rn(0.0f);
-        if (DKM > DKP)
+    if constexpr (DKM > DK) {
+        constexpr int QPAD = DKM - DK;
+        for (int i = tid; i < REP * QPAD; i += 128) Qs[(i / QPAD) * LD + DK + i % QPAD] = __float2bfloat16_rn(0.0f);
+        if constexpr (DKM > DKP)
             for (int i = tid; i < 4 * 2 * KT; i += 128)
                 *reinterpret_cast<uint4*>(Qs + (16 + i) * LD + DKP) = make_uint4(0u, 0u, 0u, 0u);
         if (DKP > DK && tid < DKP - DK) {
