@@ -133,17 +133,25 @@ def test_top_p_over_a_large_vocabulary_without_top_k_is_refused(pkg, eng):
 
 
 @pytest.mark.parametrize("kw", [dict(temperature=0.0), dict(temperature=0.9, top_k=40), dict(temperature=1.0, top_k=0),
-                                dict(temperature=0.8, top_k=64, top_p=0.8, repeat_penalty=1.2, repeat_window=6)])
+                                dict(temperature=0.8, top_k=64, top_p=0.8, repeat_penalty=1.2, repeat_window=6),
+                                dict(temperature=0.0, repeat_penalty=3.0), dict(temperature=1.1, top_k=30, repeat_penalty=1.5, bias=True)])
 def test_vocabulary_larger_than_a_ctas_shared_memory(pkg, eng, kw):
     """70 000 logits (280 KB) do not fit one CTA's shared memory: the sampler keeps its working row in a scratch buffer
     instead and must choose the same tokens"""
     cfg = pkg.GptConfig(n_layer=1, d_model=64, n_head=2, d_ff=128, vocab=70000, ctx=24, act=1, pos=1)
     pol, m, _ = _setup(pkg, eng, cfg)
     prompts = _prompts(cfg, 4, 5, seed=9)
+    kw = dict(kw)
+    bias = None
+    if kw.pop("bias", False):
+        bias = np.zeros(70000, np.float32)
+        bias[::2] = -np.inf  # half of the vocabulary is forbidden
+        bias[12345] = 1.5
     whole_vocab = kw.get("temperature", 1.0) > 0 and kw.get("top_k", 0) == 0
     n_new = 1 if whole_vocab else 10
-    ref_tok, ref_lp, _ = m.rollout_cfg(prompts, n_new, seed=4, **kw)
-    tok, lp, _, _ = pol.rollout_sampled(torch.from_numpy(prompts).to(eng.device), n_new, pkg.SamplingConfig(seed=4, **kw))
+    ref_tok, ref_lp, _ = m.rollout_cfg(prompts, n_new, seed=4, bias=bias, **kw)
+    sc = pkg.SamplingConfig(seed=4, logit_bias=None if bias is None else torch.from_numpy(bias).to(eng.device), **kw)
+    tok, lp, _, _ = pol.rollout_sampled(torch.from_numpy(prompts).to(eng.device), n_new, sc)
     if whole_vocab:
         # 70 000 nearly equal probabilities summed sequentially in f32 by the reference rule and in f64 by chunks here:
         # the draw lands within a few dozen entries of the same place in the cumulative distribution
@@ -151,6 +159,8 @@ def test_vocabulary_larger_than_a_ctas_shared_memory(pkg, eng, kw):
         return
     assert np.array_equal(tok.cpu().numpy(), ref_tok)
     assert np.abs(lp.cpu().numpy() - ref_lp).max() <= 1e-3 * np.abs(ref_lp).max()
+    if bias is not None:
+        assert not (ref_tok[:, 5:] % 2 == 0).any()
 
 
 def test_full_vocab_sampled_rollout_agrees(pkg, eng):
