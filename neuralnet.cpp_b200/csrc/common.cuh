@@ -133,7 +133,7 @@ nnb_status launch_bitlinear_fwd_tm(nnb_engine* e, const uint32_t* wq, size_t wq_
 // quantises the transformed row; f_out (t,k) optional copy of the transformed row
 nnb_status launch_row_quant(nnb_engine* e, int mode, bool exact, const float* in, const float* gamma,
                             size_t t, size_t k, size_t in_stride, int8_t* q, float* s,
-                            int32_t* qsum, float* f_out, bool norm_after = false);
+                            int32_t* qsum, float* f_out, bool norm_after = false, bool in_bf16 = false /* modes 1, 2, 4 */);
 // Where a decode step's new projections live and how the heads map: q, k, v point at sequence 0 (rows `stride` floats
 // apart); kv_rep query heads read one key / value head (grouped-query attention; 1 = multi-head), the caches then hold
 // H / kv_rep heads.  Without it the launchers take qkv as three (B, d) planes.
@@ -284,7 +284,7 @@ nnb_status launch_add(nnb_engine* e, float* dst, const float* src, size_t n);
 // ---- gemm_tc.cu (tcgen05 / TMEM / TMA GEMMs)
 nnb_status launch_tc_forward(nnb_engine* e, const int8_t* q, const int8_t* w8, const float* tau, const float* s,
                              const float* bias, const float* residual, size_t t, size_t k, size_t out, float* y,
-                             size_t n_mats = 1, size_t y_stride = 0);
+                             size_t n_mats = 1, size_t y_stride = 0, __nv_bfloat16* y_bf16 = nullptr /* instead of y */);
 nnb_status launch_tc_dx(nnb_engine* e, const __nv_bfloat16* dyb, const __nv_bfloat16* wb, size_t t, size_t k, size_t out,
                         float* dx, bool accumulate);
 nnb_status launch_tc_dw(nnb_engine* e, const __nv_bfloat16* dyb, const __nv_bfloat16* xs, size_t t, size_t k, size_t out,
@@ -321,7 +321,7 @@ nnb_status launch_colsum_finish_all(nnb_engine* e, ColsumSink* sink);
 nnb_status launch_scale_colsum(nnb_engine* e, const float* dy, const float* tau, size_t t, size_t out, __nv_bfloat16* dyb,
                                float* db, size_t dyb_ld = 0, ColsumSink* sink = nullptr);
 nnb_status launch_act_bwd_scale_colsum(nnb_engine* e, int mode, const float* h, const float* da, const float* tau, size_t t,
-                                       size_t F, __nv_bfloat16* dyb, float* db, ColsumSink* sink = nullptr);
+                                       size_t F, __nv_bfloat16* dyb, float* db, ColsumSink* sink = nullptr, bool h_bf16 = false);
 nnb_status launch_dequant_to_bf16(nnb_engine* e, const int8_t* q, const float* s, size_t t, size_t k, __nv_bfloat16* xs);
 // c (T, N) f32 = a (T, K) bf16 . b (N, K)^T bf16 on tcgen05 (T >= 64, K % 8 == 0, N % 4 == 0)
 nnb_status launch_tc_nt(nnb_engine* e, const __nv_bfloat16* a, const __nv_bfloat16* b, size_t t, size_t k, size_t n, float* c);

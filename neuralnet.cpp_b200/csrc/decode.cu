@@ -48,9 +48,28 @@ __global__ void embed_kernel(const float* __restrict__ tok_emb, const float* __r
 // NORM (MODE 1, 2, 4 only): the activated row goes through RMSNorm(.)*gamma before it is quantised (SubLN of the
 // feed-forward, include/neuralnet.cpp/compute_layer_feedforward.hpp:201-206); f_out then receives the activated row
 // before the norm, which is what the norm's backward needs.
-template <int MODE, bool EXACT, bool NORM = false>
+template <typename InT>
+__device__ __forceinline__ float ld_in(const InT* p);
+template <>
+__device__ __forceinline__ float ld_in<float>(const float* p) { return *p; }
+template <>
+__device__ __forceinline__ float ld_in<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <typename InT>
+__device__ __forceinline__ float4 ld_in4(const InT* p);  // four consecutive elements, p aligned to four of them
+template <>
+__device__ __forceinline__ float4 ld_in4<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <>
+__device__ __forceinline__ float4 ld_in4<__nv_bfloat16>(const __nv_bfloat16* p)
+{
+    const uint2 t = *reinterpret_cast<const uint2*>(p);
+    return make_float4(__uint_as_float(t.x << 16), __uint_as_float(t.x & 0xffff0000u), __uint_as_float(t.y << 16),
+                       __uint_as_float(t.y & 0xffff0000u));
+}
+
+// InT: the input's type; bf16 where the producing GEMM stored its result so (the fc1 output in the fast mode)
+template <int MODE, bool EXACT, bool NORM = false, typename InT = float>
 __global__ void __launch_bounds__(256)
-row_quant_kernel(const float* __restrict__ in, const float* __restrict__ gamma, int k, int in_stride,
+row_quant_kernel(const InT* __restrict__ in, const float* __restrict__ gamma, int k, int in_stride,
                  int8_t* __restrict__ q, float* __restrict__ s, int32_t* __restrict__ qsum,
                  float* __restrict__ f_out)
 {
@@ -59,7 +78,7 @@ row_quant_kernel(const float* __restrict__ in, const float* __restrict__ gamma, 
     __shared__ float red_f[8];
     __shared__ int red_i[8];
     const size_t tok = blockIdx.x;
-    const float* xr = in + tok * (size_t)in_stride;
+    const InT* xr = in + tok * (size_t)in_stride;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
     float sinv = 0.0f;
@@ -68,7 +87,7 @@ row_quant_kernel(const float* __restrict__ in, const float* __restrict__ gamma, 
         if (EXACT) {
             double ss = 0.0;
             for (int i = tid; i < k; i += 256) {
-                const float v = xr[i];
+                const float v = ld_in<InT>(xr + i);
                 ss += (double)__fmul_rn(v, v);
             }
             ss = warp_sum_d(ss);
@@ -81,7 +100,7 @@ row_quant_kernel(const float* __restrict__ in, const float* __restrict__ gamma, 
         } else {
             float ss = 0.0f;
             for (int i = tid; i < k; i += 256) {
-                const float v = xr[i];
+                const float v = ld_in<InT>(xr + i);
                 ss = fmaf(v, v, ss);
             }
             ss = warp_sum(ss);
@@ -102,19 +121,19 @@ row_quant_kernel(const float* __restrict__ in, const float* __restrict__ gamma, 
     for (int i = tid; i < k; i += 256) {
         float v;
         if (MODE == 0) {
-            v = __fmul_rn(__fmul_rn(xr[i], sinv), gamma[i]);
+            v = __fmul_rn(__fmul_rn(ld_in<InT>(xr + i), sinv), gamma[i]);
         } else if (MODE == 1) {
-            const float xv = xr[i];
+            const float xv = ld_in<InT>(xr + i);
             v = __fdiv_rn(xv, __fadd_rn(1.0f, nnb_expf(-__fmul_rn(xv, 1.702f))));
         } else if (MODE == 2) {
-            const float gv = xr[i], uv = xr[k + i];
+            const float gv = ld_in<InT>(xr + i), uv = ld_in<InT>(xr + k + i);
             const float sig = __fdiv_rn(1.0f, __fadd_rn(1.0f, nnb_expf(-gv)));
             v = __fmul_rn(__fmul_rn(gv, sig), uv);
         } else if (MODE == 4) {
-            const float rv = fmaxf(xr[i], 0.0f), uv = xr[k + i];
+            const float rv = fmaxf(ld_in<InT>(xr + i), 0.0f), uv = ld_in<InT>(xr + k + i);
             v = __fmul_rn(__fmul_rn(rv, rv), uv);
         } else {
-            v = xr[i];
+            v = ld_in<InT>(xr + i);
         }
         row[i] = v;
         if (f_out) f_out[tok * (size_t)k + i] = v;
@@ -192,16 +211,16 @@ row_quant_kernel(const float* __restrict__ in, const float* __restrict__ gamma, 
 // Fast-mode variant of row_quant_kernel: same layout and outputs, 16-byte loads and stores, hardware
 // exp / divide approximations and f32 sums (the exact mode keeps the kernel above, whose every rounding
 // step follows the reference).
-template <int MODE, bool NORM = false>
+template <int MODE, bool NORM = false, typename InT = float>
 __global__ void __launch_bounds__(256)
-row_quant_fast_kernel(const float* __restrict__ in, const float* __restrict__ gamma, int k, int in_stride,
+row_quant_fast_kernel(const InT* __restrict__ in, const float* __restrict__ gamma, int k, int in_stride,
                       int8_t* __restrict__ q, float* __restrict__ s, int32_t* __restrict__ qsum, float* __restrict__ f_out)
 {
     extern __shared__ __align__(16) float row[];
     __shared__ float red_f[8];
     __shared__ int red_i[8];
     const size_t tok = blockIdx.x;
-    const float4* x4 = reinterpret_cast<const float4*>(in + tok * (size_t)in_stride);
+    const InT* xr = in + tok * (size_t)in_stride;
     float4* row4 = reinterpret_cast<float4*>(row);
     float4* f4 = f_out ? reinterpret_cast<float4*>(f_out + tok * (size_t)k) : nullptr;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -213,7 +232,7 @@ row_quant_fast_kernel(const float* __restrict__ in, const float* __restrict__ ga
     if (MODE == 0) {
         float ss = 0.0f;
         for (int c = tid; c < nv; c += 256) {
-            const float4 v = x4[c];
+            const float4 v = ld_in4<InT>(xr + 4 * c);
             row4[c] = v;
             ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
         }
@@ -234,20 +253,20 @@ row_quant_fast_kernel(const float* __restrict__ in, const float* __restrict__ ga
             const float4 g = reinterpret_cast<const float4*>(gamma)[c];
             v = make_float4(x.x * sinv * g.x, x.y * sinv * g.y, x.z * sinv * g.z, x.w * sinv * g.w);
         } else if (MODE == 1) {
-            const float4 x = x4[c];
+            const float4 x = ld_in4<InT>(xr + 4 * c);
             v = make_float4(__fdividef(x.x, 1.0f + __expf(-1.702f * x.x)), __fdividef(x.y, 1.0f + __expf(-1.702f * x.y)),
                             __fdividef(x.z, 1.0f + __expf(-1.702f * x.z)), __fdividef(x.w, 1.0f + __expf(-1.702f * x.w)));
         } else if (MODE == 2) {
-            const float4 g = x4[c], u = x4[nv + c];
+            const float4 g = ld_in4<InT>(xr + 4 * c), u = ld_in4<InT>(xr + 4 * (nv + c));
             v = make_float4(__fdividef(g.x, 1.0f + __expf(-g.x)) * u.x, __fdividef(g.y, 1.0f + __expf(-g.y)) * u.y,
                             __fdividef(g.z, 1.0f + __expf(-g.z)) * u.z, __fdividef(g.w, 1.0f + __expf(-g.w)) * u.w);
         } else if (MODE == 4) {
-            const float4 g = x4[c], u = x4[nv + c];
+            const float4 g = ld_in4<InT>(xr + 4 * c), u = ld_in4<InT>(xr + 4 * (nv + c));
             const float4 r = make_float4(fmaxf(g.x, 0.f), fmaxf(g.y, 0.f), fmaxf(g.z, 0.f), fmaxf(g.w, 0.f));
             v = make_float4(__fmul_rn(__fmul_rn(r.x, r.x), u.x), __fmul_rn(__fmul_rn(r.y, r.y), u.y),
                             __fmul_rn(__fmul_rn(r.z, r.z), u.z), __fmul_rn(__fmul_rn(r.w, r.w), u.w));
         } else {
-            v = x4[c];
+            v = ld_in4<InT>(xr + 4 * c);
         }
         row4[c] = v;
         if (f4) f4[c] = v;
@@ -307,57 +326,75 @@ row_quant_fast_kernel(const float* __restrict__ in, const float* __restrict__ ga
     }
 }
 
-template <int MODE, bool NORM = false>
-static nnb_status launch_row_quant_mode(nnb_engine* e, bool exact, const float* in,
+template <int MODE, bool NORM = false, typename InT = float>
+static nnb_status launch_row_quant_mode(nnb_engine* e, bool exact, const InT* in,
                                         const float* gamma, size_t t, size_t k, size_t in_stride,
                                         int8_t* q, float* s, int32_t* qsum, float* f_out)
 {
     const size_t smem = k * sizeof(float);
     static bool cfg_dev[64] = {}; bool& cfg = cfg_dev[e->device & 63];  // the attribute is per device
     if (!cfg) {
-        NNB_CUDA(cudaFuncSetAttribute(row_quant_kernel<MODE, true, NORM>,
+        NNB_CUDA(cudaFuncSetAttribute(row_quant_kernel<MODE, true, NORM, InT>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
-        NNB_CUDA(cudaFuncSetAttribute(row_quant_kernel<MODE, false, NORM>,
+        NNB_CUDA(cudaFuncSetAttribute(row_quant_kernel<MODE, false, NORM, InT>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
-        NNB_CUDA(cudaFuncSetAttribute(row_quant_fast_kernel<MODE, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+        NNB_CUDA(cudaFuncSetAttribute(row_quant_fast_kernel<MODE, NORM, InT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
         cfg = true;
     }
     const bool aligned = in_stride % 4 == 0 && ((uintptr_t)in & 15) == 0 && (!f_out || ((uintptr_t)f_out & 15) == 0) &&
                          ((MODE != 0 && !NORM) || ((uintptr_t)gamma & 15) == 0);
     if (exact)
-        row_quant_kernel<MODE, true, NORM><<<(unsigned)t, 256, smem, e->stream>>>(in, gamma, (int)k, (int)in_stride, q, s, qsum, f_out);
+        row_quant_kernel<MODE, true, NORM, InT><<<(unsigned)t, 256, smem, e->stream>>>(in, gamma, (int)k, (int)in_stride, q, s, qsum,
+                                                                                        f_out);
     else if (aligned)
-        launch_ex(e, row_quant_fast_kernel<MODE, NORM>, dim3((unsigned)t), dim3(256), smem, in, gamma, (int)k, (int)in_stride, q, s,
-                  qsum, f_out);
+        launch_ex(e, row_quant_fast_kernel<MODE, NORM, InT>, dim3((unsigned)t), dim3(256), smem, in, gamma, (int)k, (int)in_stride, q,
+                  s, qsum, f_out);
     else
-        row_quant_kernel<MODE, false, NORM><<<(unsigned)t, 256, smem, e->stream>>>(in, gamma, (int)k, (int)in_stride, q, s, qsum,
-                                                                                   f_out);
+        row_quant_kernel<MODE, false, NORM, InT><<<(unsigned)t, 256, smem, e->stream>>>(in, gamma, (int)k, (int)in_stride, q, s, qsum,
+                                                                                         f_out);
     e->launches++;
     NNB_CHECK_LAUNCH("row_quant_kernel");
     return NNB_OK;
 }
 
-// norm_after: modes 1, 2, 4 only; the activated row is RMS-normalised with gamma before it is quantised
+template <typename InT>
+static nnb_status launch_row_quant_act(nnb_engine* e, int mode, bool norm_after, bool exact, const InT* in, const float* gamma,
+                                       size_t t, size_t k, size_t in_stride, int8_t* q, float* s, int32_t* qsum, float* f_out)
+{
+    if (norm_after) switch (mode) {
+            case 1: return launch_row_quant_mode<1, true, InT>(e, exact, in, gamma, t, k, in_stride, q, s, qsum, f_out);
+            case 2: return launch_row_quant_mode<2, true, InT>(e, exact, in, gamma, t, k, in_stride, q, s, qsum, f_out);
+            default: return launch_row_quant_mode<4, true, InT>(e, exact, in, gamma, t, k, in_stride, q, s, qsum, f_out);
+        }
+    switch (mode) {
+        case 1: return launch_row_quant_mode<1, false, InT>(e, exact, in, gamma, t, k, in_stride, q, s, qsum, f_out);
+        case 2: return launch_row_quant_mode<2, false, InT>(e, exact, in, gamma, t, k, in_stride, q, s, qsum, f_out);
+        default: return launch_row_quant_mode<4, false, InT>(e, exact, in, gamma, t, k, in_stride, q, s, qsum, f_out);
+    }
+}
+
+// norm_after: modes 1, 2, 4 only; the activated row is RMS-normalised with gamma before it is quantised.
+// in_bf16: modes 1, 2, 4 only; `in` points at bf16 elements (in_stride counts elements)
 nnb_status launch_row_quant(nnb_engine* e, int mode, bool exact, const float* in, const float* gamma,
                             size_t t, size_t k, size_t in_stride, int8_t* q, float* s,
-                            int32_t* qsum, float* f_out, bool norm_after)
+                            int32_t* qsum, float* f_out, bool norm_after, bool in_bf16)
 {
     NNB_REQUIRE(in && q && s && qsum && t > 0, "row_quant: bad arguments");
     NNB_REQUIRE(k > 0 && k % 64 == 0 && k * 4 <= 96 * 1024, "row_quant: k=%zu must be a multiple of 64 (<= 24576)", k);
-    NNB_REQUIRE(!norm_after || (gamma && (mode == 1 || mode == 2 || mode == 4)), "row_quant: the norm after an activation needs gamma");
-    if (norm_after) switch (mode) {
-            case 1: return launch_row_quant_mode<1, true>(e, exact, in, gamma, t, k, in_stride, q, s, qsum, f_out);
-            case 2: return launch_row_quant_mode<2, true>(e, exact, in, gamma, t, k, in_stride, q, s, qsum, f_out);
-            default: return launch_row_quant_mode<4, true>(e, exact, in, gamma, t, k, in_stride, q, s, qsum, f_out);
-        }
+    const bool act_mode = mode == 1 || mode == 2 || mode == 4;
+    NNB_REQUIRE(!norm_after || (gamma && act_mode), "row_quant: the norm after an activation needs gamma");
+    NNB_REQUIRE(!in_bf16 || (act_mode && !exact), "row_quant: bf16 input is for the activation modes of the fast mode");
+    if (act_mode) {
+        if (in_bf16)
+            return launch_row_quant_act<__nv_bfloat16>(e, mode, norm_after, exact, reinterpret_cast<const __nv_bfloat16*>(in), gamma, t, k,
+                                                       in_stride, q, s, qsum, f_out);
+        return launch_row_quant_act<float>(e, mode, norm_after, exact, in, gamma, t, k, in_stride, q, s, qsum, f_out);
+    }
     switch (mode) {
         case 0:
             NNB_REQUIRE(gamma, "row_quant: RMSNorm needs gamma");
             return launch_row_quant_mode<0>(e, exact, in, gamma, t, k, in_stride, q, s, qsum, f_out);
-        case 1: return launch_row_quant_mode<1>(e, exact, in, gamma, t, k, in_stride, q, s, qsum, f_out);
-        case 2: return launch_row_quant_mode<2>(e, exact, in, gamma, t, k, in_stride, q, s, qsum, f_out);
         case 3: return launch_row_quant_mode<3>(e, exact, in, gamma, t, k, in_stride, q, s, qsum, f_out);
-        case 4: return launch_row_quant_mode<4>(e, exact, in, gamma, t, k, in_stride, q, s, qsum, f_out);
     }
     NNB_FAIL(NNB_ERR_INVALID, "row_quant: unknown mode %d", mode);
 }

@@ -153,6 +153,8 @@ struct Epi {
     const float *lse, *ent, *up_lp, *up_ent;
     __nv_bfloat16* dyb;
     float* db_part;
+    // EPI 0: when set, the result is rounded to bf16 and stored here (same indexing) instead of `out`
+    __nv_bfloat16* out_b;
 };
 
 // KIND 0: int8 (A, B K-major, 128 k per stage).  KIND 1: bf16 (64 k per stage), A/B K- or MN-major.
@@ -281,6 +283,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         float* stg = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES + 256) + (warp - 2) * 1024;
         const int lc = (lane & 7) * 4, lr = lane >> 3;
         const bool aligned = (((uintptr_t)ep.out | (uintptr_t)ep.tau | (uintptr_t)ep.bias | (uintptr_t)ep.residual) & 15) == 0 &&
+                             ((uintptr_t)ep.out_b & 7) == 0 &&
                              (ep.n_mat & 3) == 0 && (ep.mat_stride & 3) == 0;
         uint32_t tcount = 0;
         bool ok = true;
@@ -507,7 +510,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                                     o.x += p4.x; o.y += p4.y; o.z += p4.z; o.w += p4.w;
                                 }
                             }
-                            *reinterpret_cast<float4*>(ep.out + off) = o;
+                            if (EPI == 0 && ep.out_b) {
+                                const __nv_bfloat162 lo = __floats2bfloat162_rn(o.x, o.y), hi = __floats2bfloat162_rn(o.z, o.w);
+                                uint2 w2;
+                                w2.x = *reinterpret_cast<const uint32_t*>(&lo);
+                                w2.y = *reinterpret_cast<const uint32_t*>(&hi);
+                                *reinterpret_cast<uint2*>(ep.out_b + off) = w2;
+                            } else {
+                                *reinterpret_cast<float4*>(ep.out + off) = o;
+                            }
                         }
                     }
                     __syncwarp();
@@ -526,7 +537,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                             x = __uint_as_float(r[j]);
                             if (ep.accumulate) x += ep.out[off + j];
                         }
-                        ep.out[off + j] = x;
+                        if (EPI == 0 && ep.out_b) ep.out_b[off + j] = __float2bfloat16_rn(x);
+                        else ep.out[off + j] = x;
                     }
                 }
             }
@@ -650,8 +662,9 @@ static nnb_status tc_forward_bn(nnb_engine* e, const int8_t* q, const int8_t* w8
 // (t, out) block at y + m * y_stride; one launch covers them all when out is a multiple of 32
 nnb_status launch_tc_forward(nnb_engine* e, const int8_t* q, const int8_t* w8, const float* tau, const float* s,
                              const float* bias, const float* residual, size_t t, size_t k, size_t out, float* y,
-                             size_t n_mats, size_t y_stride)
+                             size_t n_mats, size_t y_stride, __nv_bfloat16* y_bf16)
 {
+    NNB_REQUIRE(!y_bf16 || (n_mats == 1 && !residual), "tc_forward: the bf16 output takes one matrix and no residual");
     if (n_mats > 1 && out % 32 != 0) {
         for (size_t m = 0; m < n_mats; ++m)
             NNB_TRY(launch_tc_forward(e, q, w8 + m * out * k, tau + m * out, s, bias ? bias + m * out : nullptr,
@@ -659,6 +672,7 @@ nnb_status launch_tc_forward(nnb_engine* e, const int8_t* q, const int8_t* w8, c
         return NNB_OK;
     }
     tc::Epi ep{y, tau, s, bias, residual, 0, (int)out, n_mats > 1 ? y_stride : 0};
+    ep.out_b = y_bf16;
     out *= n_mats;
     switch (choose_forward_bn(t, k, out, e->sm_count)) {
         case 64: return tc_forward_bn<64>(e, q, w8, ep, t, k, out);
@@ -1049,9 +1063,20 @@ static nnb_status colsum_part(nnb_engine* e, ColsumSink* sink, size_t n_chunks, 
 // pre-activation (F1 = 2F for SwiGLU, gate | up; F for QuickGELU) and da (T, F) the gradient of the
 // activation's output, dh = act'(h) o da never reaches memory as f32: dyb[t,c] = bf16(dh[t,c] * tau[c]) and
 // db[c] += sum_t dh[t,c].  Same grid as scale_colsum_kernel over the F output features.
-template <int MODE>
+template <typename HT>
+__device__ __forceinline__ float2 ld_h2(const HT* p);
+template <>
+__device__ __forceinline__ float2 ld_h2<float>(const float* p) { return *reinterpret_cast<const float2*>(p); }
+template <>
+__device__ __forceinline__ float2 ld_h2<__nv_bfloat16>(const __nv_bfloat16* p)
+{
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
+
+// HT: type of the saved pre-activation (f32, or bf16 where the forward stored it so)
+template <int MODE, typename HT = float>
 __global__ void __launch_bounds__(128)
-act_bwd_scale_colsum_kernel(const float* __restrict__ h, const float* __restrict__ da, const float* __restrict__ tau, int T,
+act_bwd_scale_colsum_kernel(const HT* __restrict__ h, const float* __restrict__ da, const float* __restrict__ tau, int T,
                             int F, int chunk, __nv_bfloat16* __restrict__ out, float* __restrict__ part)
 {
     const int f = (blockIdx.x * 128 + threadIdx.x) * 2;
@@ -1066,8 +1091,8 @@ act_bwd_scale_colsum_kernel(const float* __restrict__ h, const float* __restrict
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
             const int tt = min(t + u, t1 - 1);
-            gv[u] = *reinterpret_cast<const float2*>(h + (size_t)tt * F1 + f);
-            uv[u] = MODE >= 2 ? *reinterpret_cast<const float2*>(h + (size_t)tt * F1 + F + f) : make_float2(0.f, 0.f);
+            gv[u] = ld_h2<HT>(h + (size_t)tt * F1 + f);
+            uv[u] = MODE >= 2 ? ld_h2<HT>(h + (size_t)tt * F1 + F + f) : make_float2(0.f, 0.f);
             go[u] = *reinterpret_cast<const float2*>(da + (size_t)tt * F + f);
         }
 #pragma unroll
@@ -1156,7 +1181,7 @@ nnb_status launch_scale_to_bf16(nnb_engine* e, const float* dy, const float* tau
 
 // mode 1 QuickGELU, 2 SwiGLU, 3 ReLU2GLU; F even
 nnb_status launch_act_bwd_scale_colsum(nnb_engine* e, int mode, const float* h, const float* da, const float* tau, size_t t,
-                                       size_t F, __nv_bfloat16* dyb, float* db, ColsumSink* sink)
+                                       size_t F, __nv_bfloat16* dyb, float* db, ColsumSink* sink, bool h_bf16)
 {
     NNB_REQUIRE(F % 2 == 0 && mode >= 1 && mode <= 3, "act_bwd_scale_colsum: bad arguments");
     const int chunk = 128;
@@ -1166,7 +1191,12 @@ nnb_status launch_act_bwd_scale_colsum(nnb_engine* e, int mode, const float* h, 
     float* part = nullptr;
     const nnb_status where = colsum_part(e, sink, grid.y, F1, db, &part);
     if (where < 0) return where;
-    if (mode == 2) act_bwd_scale_colsum_kernel<2><<<grid, 128, 0, e->stream>>>(h, da, tau, (int)t, (int)F, chunk, dyb, part);
+    if (h_bf16) {
+        const __nv_bfloat16* hb = reinterpret_cast<const __nv_bfloat16*>(h);
+        if (mode == 2) act_bwd_scale_colsum_kernel<2, __nv_bfloat16><<<grid, 128, 0, e->stream>>>(hb, da, tau, (int)t, (int)F, chunk, dyb, part);
+        else if (mode == 3) act_bwd_scale_colsum_kernel<3, __nv_bfloat16><<<grid, 128, 0, e->stream>>>(hb, da, tau, (int)t, (int)F, chunk, dyb, part);
+        else act_bwd_scale_colsum_kernel<1, __nv_bfloat16><<<grid, 128, 0, e->stream>>>(hb, da, tau, (int)t, (int)F, chunk, dyb, part);
+    } else if (mode == 2) act_bwd_scale_colsum_kernel<2><<<grid, 128, 0, e->stream>>>(h, da, tau, (int)t, (int)F, chunk, dyb, part);
     else if (mode == 3) act_bwd_scale_colsum_kernel<3><<<grid, 128, 0, e->stream>>>(h, da, tau, (int)t, (int)F, chunk, dyb, part);
     else act_bwd_scale_colsum_kernel<1><<<grid, 128, 0, e->stream>>>(h, da, tau, (int)t, (int)F, chunk, dyb, part);
     e->launches++;

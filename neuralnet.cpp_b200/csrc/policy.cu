@@ -156,17 +156,25 @@ nnb_status policy_ensure_wb(nnb_policy* p)
 }
 
 nnb_status policy_linear_fwd(nnb_policy* p, const LinW& l, size_t n_mats, const int8_t* q, const float* s,
-                             const int32_t* qsum, size_t T, const float* residual, float* y, size_t y_stride)
+                             const int32_t* qsum, size_t T, const float* residual, float* y, size_t y_stride, bool y_bf16)
 {
+    NNB_REQUIRE(!y_bf16 || policy_linear_can_bf16(p, T), "linear: a bf16 result needs the tensor-core forward");
     // from 64 tokens up the tcgen05 kernel wins (its tile width follows the shape; measured 1.7-1.9x over the
     // mma.sync kernel at 128 tokens); below that the persistent mma.sync kernels stream the 2-bit container,
     // a quarter of the int8 copy's bytes
     if (!p->cfg.exact && p->w8 && T >= 64)
         return launch_tc_forward(p->e, q, p->w8 + l.packed_off * 16, p->tau + l.tau_off, s, p->params + l.b_off, residual, T,
-                                 l.in, l.out, y, n_mats, y_stride);
+                                 l.in, l.out, y_bf16 ? nullptr : y, n_mats, y_stride,
+                                 y_bf16 ? reinterpret_cast<__nv_bfloat16*>(y) : nullptr);
     return launch_bitlinear_fwd_tm(p->e, p->packed + l.packed_off, n_mats > 1 ? l.out * (l.in / 16) : 0, p->tau + l.tau_off,
                                    p->params + l.b_off, residual, q, s, qsum, n_mats, T, l.in, l.out, y, y_stride, NNB_F32,
                                    nullptr);
+}
+
+bool policy_h1_bf16(const nnb_policy* p, size_t T, size_t F, size_t F1)
+{
+    static const bool on = [] { const char* ev = getenv("NNB_H1_BF16"); return !(ev && ev[0] == '0'); }();
+    return on && policy_linear_can_bf16(p, T) && F1 % 8 == 0 && F % 8 == 0;
 }
 
 // seeded = true: tau and the containers were just written from a model file and are authoritative (the first forward
@@ -400,10 +408,11 @@ static nnb_status decode_step(nnb_policy* p, const StepView& sv, bool with_head,
             NNB_TRY(so);
         }
         NNB_TRY(launch_row_quant(e, 0, exact, w.x, P + L.ln2_g, B, d, d, w.q8, w.s, w.qsum, nullptr));
-        NNB_TRY(policy_linear_fwd(p, L.fc1, 1, w.q8, w.s, w.qsum, B, nullptr, w.h1, 0));
+        const bool h1_b16 = policy_h1_bf16(p, B, F, F1);  // the buffer keeps its f32 size
+        NNB_TRY(policy_linear_fwd(p, L.fc1, 1, w.q8, w.s, w.qsum, B, nullptr, w.h1, 0, h1_b16));
         // SubLN: the activated hidden is normalised, then quantised for fc2, in the same launch
         NNB_TRY(launch_row_quant(e, act_quant_mode(c.act), exact, w.h1, c.sub_ln ? P + L.ffn_sub_g : nullptr, B, F, F1, w.q8, w.s,
-                                 w.qsum, nullptr, c.sub_ln != 0));
+                                 w.qsum, nullptr, c.sub_ln != 0, h1_b16));
         NNB_TRY(policy_linear_fwd(p, L.fc2, 1, w.q8, w.s, w.qsum, B, w.x, w.x, 0));
     }
     if (with_head) {

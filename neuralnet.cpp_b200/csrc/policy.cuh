@@ -101,5 +101,12 @@ nnb_status policy_ensure_wb(nnb_policy* p);
 nnb_status policy_tied_head_fwd(nnb_policy* p, const float* hn, __nv_bfloat16* hnb, size_t T, float* logits);
 // y = [residual +] linear(q) through the fastest kernel for this mode and token count
 nnb_status policy_linear_fwd(nnb_policy* p, const LinW& l, size_t n_mats, const int8_t* q, const float* s,
-                             const int32_t* qsum, size_t T, const float* residual, float* y, size_t y_stride);
+                             const int32_t* qsum, size_t T, const float* residual, float* y, size_t y_stride,
+                             bool y_bf16 = false);
+// y_bf16: the tensor-core forward rounds its result to bf16 and y points at bf16 elements (one matrix, no residual);
+// allowed where policy_linear_can_bf16 holds
+inline bool policy_linear_can_bf16(const nnb_policy* p, size_t T) { return !p->cfg.exact && p->w8 != nullptr && T >= 64; }
+// fast mode: fc1's output (T, F1) is kept as bf16; it is read once by the activation quantiser and once by the
+// activation's backward.  NNB_H1_BF16=0 keeps it f32, for A/B runs (read once per process).
+bool policy_h1_bf16(const nnb_policy* p, size_t T, size_t F, size_t F1);
 }  // namespace nnb

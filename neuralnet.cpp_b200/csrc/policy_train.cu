@@ -53,6 +53,7 @@ struct TrainWs {
     // fast mode: the LM head's GEMM computes log-prob / entropy in its epilogue and its backward operand is recomputed
     // from the same integer GEMM, so the (decisions x vocabulary) f32 logits do not exist
     bool fused_head = false;
+    bool h1_b16 = false;  // the saved fc1 outputs hold bf16 elements
     float *lse = nullptr, *head_scratch = nullptr;
     ColsumSink bias_sink;  // bias-gradient partial sums of a whole backward pass, finished by one launch
     // structure switches
@@ -108,6 +109,7 @@ static nnb_status ensure_train(nnb_policy* p, size_t n_seq, size_t S, size_t P, 
     // fast mode: attention runs on bf16 copies of q, k, v; those are what a layer keeps for its backward,
     // and the f32 projections become one buffer shared by all layers
     w->b16_attn = !c.exact && attn_b16_supported(d / H, d);
+    w->h1_b16 = policy_h1_bf16(p, T, F, F1);
     w->fused_head = with_head && !tie && !c.exact && p->w8 != nullptr && V % 8 == 0 && Td >= 64;
     // carve one arena: first pass measures, second assigns
     for (int pass = 0; pass < 2; ++pass) {
@@ -130,7 +132,7 @@ static nnb_status ensure_train(nnb_policy* p, size_t n_seq, size_t S, size_t P, 
             s.att = (float*)take(T * d * 4);
             s.lse = (float*)take(n_seq * H * S * 4);
             s.x_mid = (float*)take(T * d * 4);
-            s.h1 = (float*)take(T * F1 * 4);
+            s.h1 = (float*)take(T * F1 * (w->h1_b16 ? 2 : 4));
             s.q1 = (int8_t*)take(T * d);
             s.q2 = (int8_t*)take(T * d);
             s.q3 = (int8_t*)take(T * d);
@@ -292,10 +294,10 @@ static nnb_status forward(nnb_policy* p, const int32_t* tokens, size_t n_seq, si
                                  w->qsum, nullptr));
         NNB_TRY(lin_fwd(p, LW.o, 1, s.q2, s.s2, w->qsum, T, x_in, s.x_mid, 0));
         NNB_TRY(launch_row_quant(e, 0, exact, s.x_mid, PP + LW.ln2_g, T, d, d, s.q3, s.s3, w->qsum, nullptr));
-        NNB_TRY(lin_fwd(p, LW.fc1, 1, s.q3, s.s3, w->qsum, T, nullptr, s.h1, 0));
+        NNB_TRY(policy_linear_fwd(p, LW.fc1, 1, s.q3, s.s3, w->qsum, T, nullptr, s.h1, 0, w->h1_b16));
         // SubLN: the activated hidden is normalised, then quantised for fc2, in the same launch
         NNB_TRY(launch_row_quant(e, act_quant_mode(c.act), exact, s.h1, c.sub_ln ? PP + LW.ffn_sub_g : nullptr, T, F, F1, s.q4, s.s4,
-                                 w->qsum, nullptr, c.sub_ln != 0));
+                                 w->qsum, nullptr, c.sub_ln != 0, w->h1_b16));
         NNB_TRY(lin_fwd(p, LW.fc2, 1, s.q4, s.s4, w->qsum, T, s.x_mid, x_out, 0));
     }
     if (!w->with_head) return NNB_OK;
@@ -403,16 +405,18 @@ static nnb_status backward(nnb_policy* p, const int32_t* tokens, size_t n_seq, s
         if (c.sub_ln) {
             // SubLN: the activated hidden is recomputed from h1 (fc2's operands q4 / s4 are spent by now and serve as the
             // quantiser's scratch), the norm's backward turns d(normed) into d(activated)
-            NNB_TRY(launch_row_quant(e, act_quant_mode(c.act), exact, s.h1, nullptr, T, F, F1, s.q4, s.s4, w->qsum, w->act));
+            NNB_TRY(launch_row_quant(e, act_quant_mode(c.act), exact, s.h1, nullptr, T, F, F1, s.q4, s.s4, w->qsum, w->act,
+                                     false, w->h1_b16));
             NNB_TRY(launch_rmsnorm_bwd(e, w->act, PP + LW.ffn_sub_g, w->da, nullptr, T, F, w->dact, GG + LW.ffn_sub_g));
             da = w->dact;
         }
         if (tc_bwd_ok(p, LW.fc1.out, T) && F % 2 == 0) {
             // the activation's backward writes the GEMM operand directly (no f32 round trip of dh1)
             NNB_TRY(launch_act_bwd_scale_colsum(e, act_bwd_mode(c.act), s.h1, da, p->tau + LW.fc1.tau_off, T, F, w->dyb,
-                                                GG + LW.fc1.b_off, sink_of(w, T)));
+                                                GG + LW.fc1.b_off, sink_of(w, T), w->h1_b16));
             NNB_TRY(lin_bwd_gemms(p, LW.fc1, LW.fc1.out, s.q3, s.s3, T, w->dn, false));
         } else {
+            NNB_REQUIRE(!w->h1_b16, "backward: the bf16 fc1 output needs the tensor-core backward");
             NNB_TRY(launch_act_bwd(e, act_bwd_mode(c.act), s.h1, da, T, F, w->dh1));
             NNB_TRY(lin_bwd(p, LW.fc1, w->dh1, s.q3, s.s3, T, w->dn, false));
         }
