@@ -40,7 +40,7 @@ sys.path.insert(0, ROOT)
 WORKLOADS = {
     "grpo1b": dict(kind="grpo", model=dict(n_layer=24, d_model=2048, n_head=16, d_ff=5632, vocab=32000, ctx=640, act=1, pos=1),
                    groups=64, group_size=16, prompt_len=128, max_new=512, temperature=0.8, top_k=50, kl_coef=0.04,
-                   micro_batch=16, rollout_chunk=1024,
+                   micro_batch=32, rollout_chunk=1024,
                    text="GRPO step, ~1B ternary Llama-style policy (24 layers, d 2048, 16 heads, RoPE, SwiGLU 5632, vocab 32000), "
                         "64 prompts x group 16, prompt 128, 512 generated, top-k 50, T 0.8, clip 0.2, KL 0.04 vs frozen initial policy"),
     "tiny": dict(kind="grpo", model=dict(n_layer=4, d_model=256, n_head=4, d_ff=1024, vocab=10000, ctx=256, act=0, pos=0),
@@ -50,7 +50,7 @@ WORKLOADS = {
                       "prompt 32, 64 generated, T 1.0, clip 0.2, KL 0"),
     "ppo_gpt2s": dict(kind="ppo", model=dict(n_layer=12, d_model=768, n_head=12, d_ff=3072, vocab=32000, ctx=512, act=0, pos=0,
                                              value_head=True),
-                      n_seq=256, prompt_len=64, max_new=256, temperature=1.0, top_k=0, micro_batch=16, rollout_chunk=256,
+                      n_seq=256, prompt_len=64, max_new=256, temperature=1.0, top_k=0, micro_batch=64, rollout_chunk=256,
                       epochs=4, minibatches=4,
                       text="PPO step with GAE, GPT-2-small-shaped ternary policy with a value head (12 layers, d 768, 12 heads, MLP 3072, "
                            "vocab 32000), 256 sequences, prompt 64, 256 generated, gamma 0.99, lambda 0.95, clip 0.2, value coef 0.5, "
@@ -521,6 +521,9 @@ def run_ours(args):
     wl = WORKLOADS[args.workload]
     if args.groups and wl["kind"] == "grpo":
         wl = dict(wl, groups=args.groups, text=wl["text"] + f" [prompt groups overridden: {args.groups}]")
+    if args.micro_batch and "micro_batch" in wl:
+        # the sequences one forward/backward takes; gradients accumulate over a minibatch either way
+        wl = dict(wl, micro_batch=args.micro_batch, text=wl["text"] + f" [micro-batch overridden: {args.micro_batch}]")
     job = JOBS[wl["kind"]](torch, pkg, eng, wl, rank, world)
 
     def barrier():
@@ -851,6 +854,9 @@ def main():
     ap.add_argument("--groups", type=int, default=0,
                     help="GRPO workloads: prompt groups instead of the workload's own count (e.g. 8 = one GPU's share of "
                          "grpo1b at 8 GPUs); the line's config says so and is not the benchmark's")
+    ap.add_argument("--micro-batch", type=int, default=0,
+                    help="sequences per forward/backward instead of the workload's own micro-batch (a tuning knob: the "
+                         "step's result is the same accumulation)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

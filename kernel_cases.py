@@ -8,6 +8,8 @@ Used for Nsight Compute captures and quick timing; every case prints its CUDA-ev
   gemv [M [K N]]  2-bit packed weight stream, M (16) tokens, stack of 64 matrices (K 2048 x N 11264)
   attn_decode  decode attention of 512 sequences x 16 heads x 128 at position 400, fused int8 output
   train [n]    reference log-probs + one training micro-batch of n (16) sequences x 640 on the 1B policy
+  trainppo [n] one PPO micro-batch (clipped policy + value loss + entropy bonus) of n (64) sequences x 320 on the
+               GPT-2-small-shaped policy with a value head (12 layers, d 768, 12 heads, MLP 3072, vocab 32000)
   rollout [B P new]   batched rollout on the 1B policy (default 512 16 24)
   rollout3b [B P new [layers]] batched rollout on the 3B-shaped decode policy (26 layers, d 3200, 32 heads of 100;
                default 128 16 48); `layers` cuts the depth (same kernels, less memory: for profiler captures)
@@ -25,6 +27,7 @@ sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 from __graft_entry__ import load_package  # noqa: E402
 
 MODEL_1B = dict(n_layer=24, d_model=2048, n_head=16, d_ff=5632, vocab=32000, ctx=640, act=1, pos=1)
+MODEL_GPT2S = dict(n_layer=12, d_model=768, n_head=12, d_ff=3072, vocab=32000, ctx=512, act=0, pos=0, value_head=True)
 MODEL_3B = dict(n_layer=26, d_model=3200, n_head=32, d_ff=8640, vocab=32002, ctx=2048, act=1, pos=1)
 MODEL_2B4T = dict(n_layer=30, d_model=2560, n_head=20, n_head_kv=5, d_ff=6912, vocab=128256, ctx=2048, act=2, pos=1,
                   sub_ln=True, tie_embeddings=True)
@@ -123,6 +126,19 @@ def main(argv):
         _timed("reference log-probs", lambda: pol.logprobs(tokens, 128), reps=2)
         _timed("training micro-batch", lambda: pol.train_step(tokens, 128, mask, old_logp=lp, advantage=adv, ref_logp=lp,
                                                               kl_coef=0.04), reps=2)
+    elif case == "trainppo":
+        n = int(argv[2]) if len(argv) > 2 else 64
+        cfg, pol, g = _policy(pkg, eng, MODEL_GPT2S)
+        tokens = torch.randint(0, cfg.vocab, (n, 320), device=dev, dtype=torch.int32, generator=g)
+        mask = torch.ones((n, 256), device=dev)
+        adv = torch.randn((n, 256), device=dev, generator=g)
+        ret = torch.randn((n, 256), device=dev, generator=g)
+        lp, _, val = pol.logprobs(tokens, 64, want_value=True)
+        pol.zero_grad()
+        step = lambda: pol.train_step(tokens, 64, mask, old_logp=lp, advantage=adv, returns=ret, old_value=val,  # noqa: E731
+                                      entropy_coef=0.01, value_coef=0.5)
+        step()
+        _timed("PPO training micro-batch", step, reps=2)
     elif case == "rollout":
         B, P, new = (int(a) for a in argv[2:5]) if len(argv) > 4 else (512, 16, 24)
         cfg, pol, g = _policy(pkg, eng)

@@ -278,7 +278,7 @@ nnb_status launch_scatter_decisions(nnb_engine* e, const float* src, size_t n_se
 nnb_status launch_value_fwd(nnb_engine* e, const float* x, const float* w, const float* b, size_t n, size_t d,
                             float* value);
 nnb_status launch_value_bwd(nnb_engine* e, const float* x, const float* w, const float* dv, size_t n, size_t d,
-                            float* dx, float* dw, float* db);
+                            float* dx, float* dw, float* db, float* scratch, size_t scratch_floats);
 nnb_status launch_add(nnb_engine* e, float* dst, const float* src, size_t n);
 
 // ---- gemm_tc.cu (tcgen05 / TMEM / TMA GEMMs)

@@ -851,6 +851,26 @@ nnb_status launch_tc_nt(nnb_engine* e, const __nv_bfloat16* a, const __nv_bfloat
 }
 
 // dW: dyb (T,OUT) bf16, xs (T,K) bf16; dw (OUT,K) f32 +=
+// The contraction runs over the tokens, so the tile count is fixed by the weight matrix alone: a 768 x 768 matrix is 18
+// tiles of 128 x 256 on 148 SMs.  Narrower tiles fill the machine; their cost per column rises (the A operand's
+// shared-memory reads are shared by fewer columns), which the weights below stand for.
+static int choose_dw_bn(size_t out, size_t k, int sm_count)
+{
+    const int cand[3] = {256, 128, 64};
+    const size_t per_col[3] = {100, 118, 167};
+    int best = 256;
+    size_t best_cost = (size_t)-1;
+    for (int i = 0; i < 3; ++i) {
+        const size_t tiles = ceil_div(out, (size_t)tc::BM) * ceil_div(k, (size_t)cand[i]);
+        const size_t cost = ceil_div(tiles, (size_t)sm_count) * cand[i] * per_col[i];
+        if (cost < best_cost) {
+            best_cost = cost;
+            best = cand[i];
+        }
+    }
+    return best;
+}
+
 nnb_status launch_tc_dw(nnb_engine* e, const __nv_bfloat16* dyb, const __nv_bfloat16* xs, size_t t, size_t k, size_t out,
                         float* dw)
 {
@@ -859,7 +879,11 @@ nnb_status launch_tc_dw(nnb_engine* e, const __nv_bfloat16* dyb, const __nv_bflo
     NNB_TRY(make_map(&ta, dyb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, t, out, 64, 64));
     NNB_TRY(make_map(&tb, xs, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, t, k, 64, 64));
     Epi ep{dw, nullptr, nullptr, nullptr, nullptr, 1, (int)k, 0};
-    return launch<1, true, true, 1, 256>(e, ta, tb, ep, out, k, t);
+    switch (choose_dw_bn(out, k, e->sm_count)) {
+        case 64: return launch<1, true, true, 1, 64>(e, ta, tb, ep, out, k, t);
+        case 128: return launch<1, true, true, 1, 128>(e, ta, tb, ep, out, k, t);
+        default: return launch<1, true, true, 1, 256>(e, ta, tb, ep, out, k, t);
+    }
 }
 
 // reads (and clears) the device error flag of the tensor-core GEMMs; synchronises the stream

@@ -392,7 +392,8 @@ static nnb_status backward(nnb_policy* p, const int32_t* tokens, size_t n_seq, s
         NNB_TRY(lin_bwd(p, p->head, w->logits, w->qh, w->sh, Td, w->dhn, false));
     }
     if (c.value_head)
-        NNB_TRY(launch_value_bwd(e, w->hn, PP + p->value_w, w->dvalue, Td, d, w->dhn, GG + p->value_w, GG + p->value_b));
+        // w->dn (T, d) is free until the layers' backward: scratch for the partial sums
+        NNB_TRY(launch_value_bwd(e, w->hn, PP + p->value_w, w->dvalue, Td, d, w->dhn, GG + p->value_w, GG + p->value_b, w->dn, T * d));
     NNB_TRY(launch_rmsnorm_bwd(e, w->xd, PP + p->lnf_g, w->dhn, nullptr, Td, d, w->xd, GG + p->lnf_g));
     if (grouped) NNB_TRY(launch_scatter_decisions_map(e, w->xd, w->map, n_seq, d, w->g));
     else NNB_TRY(launch_scatter_decisions(e, w->xd, n_seq, S, P, G, d, w->g));

@@ -642,14 +642,18 @@ __global__ void value_fwd_kernel(const float* __restrict__ x, const float* __res
 }
 
 // dx[i,:] += dv[i]*w ; dw += sum_i dv[i]*x[i,:] ; db += sum_i dv[i]
-__global__ void value_bwd_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ dv,
-                                 size_t n, int d, float* __restrict__ dx, float* __restrict__ dw, float* __restrict__ db)
+// grid (feature blocks of 256, decision chunks): a CTA walks its chunk of decisions and leaves its partial sums of dw
+// (d floats) and db (one float) in part[chunk]; value_bwd_finish_kernel adds the chunks up in order, so the result does
+// not depend on which CTA ran first
+__global__ void __launch_bounds__(256)
+value_bwd_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ dv, size_t n, int d,
+                 size_t chunk, float* __restrict__ dx, float* __restrict__ part)
 {
-    // one CTA per feature chunk of 256; loops over decisions
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t i0 = (size_t)blockIdx.y * chunk, i1 = i0 + chunk < n ? i0 + chunk : n;
     float aw = 0.0f, ab = 0.0f;
     const float wc = c < d ? w[c] : 0.0f;
-    for (size_t i = 0; i < n; ++i) {
+    for (size_t i = i0; i < i1; ++i) {
         const float g = dv[i];
         if (c < d) {
             dx[i * d + c] += g * wc;
@@ -657,8 +661,20 @@ __global__ void value_bwd_kernel(const float* __restrict__ x, const float* __res
         }
         if (c == 0) ab += g;
     }
-    if (c < d) atomicAdd(dw + c, aw);
-    if (c == 0) atomicAdd(db, ab);
+    float* prow = part + (size_t)blockIdx.y * (d + 1);
+    if (c < d) prow[c] = aw;
+    if (c == 0) prow[d] = ab;
+}
+
+__global__ void __launch_bounds__(256)
+value_bwd_finish_kernel(const float* __restrict__ part, int n_chunks, int d, float* __restrict__ dw, float* __restrict__ db)
+{
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c > d) return;
+    float a = 0.0f;
+    for (int k = 0; k < n_chunks; ++k) a += part[(size_t)k * (d + 1) + c];
+    if (c < d) dw[c] += a;
+    else db[0] += a;
 }
 
 __global__ void add_kernel(float* __restrict__ dst, const float* __restrict__ src, size_t n)
@@ -886,12 +902,22 @@ nnb_status launch_value_fwd(nnb_engine* e, const float* x, const float* w, const
     return NNB_OK;
 }
 
+// scratch: at least (d + 1) floats; the more it holds (up to one row of d + 1 per 64 decisions), the more CTAs share
+// the decisions
 nnb_status launch_value_bwd(nnb_engine* e, const float* x, const float* w, const float* dv, size_t n, size_t d,
-                            float* dx, float* dw, float* db)
+                            float* dx, float* dw, float* db, float* scratch, size_t scratch_floats)
 {
-    value_bwd_kernel<<<(unsigned)ceil_div(d, 256), 256, 0, e->stream>>>(x, w, dv, n, (int)d, dx, dw, db);
+    NNB_REQUIRE(scratch && scratch_floats >= d + 1 && n > 0, "value_bwd: scratch of at least d + 1 floats");
+    size_t n_chunks = std::min<size_t>(std::min<size_t>(ceil_div(n, 64), scratch_floats / (d + 1)), 4096);
+    const size_t chunk = ceil_div(n, n_chunks);
+    n_chunks = ceil_div(n, chunk);
+    value_bwd_kernel<<<dim3((unsigned)ceil_div(d, 256), (unsigned)n_chunks), 256, 0, e->stream>>>(x, w, dv, n, (int)d, chunk, dx,
+                                                                                                    scratch);
     e->launches++;
     NNB_CHECK_LAUNCH("value_bwd_kernel");
+    value_bwd_finish_kernel<<<(unsigned)ceil_div(d + 1, 256), 256, 0, e->stream>>>(scratch, (int)n_chunks, (int)d, dw, db);
+    e->launches++;
+    NNB_CHECK_LAUNCH("value_bwd_finish_kernel");
     return NNB_OK;
 }
 

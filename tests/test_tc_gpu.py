@@ -71,8 +71,11 @@ def test_forward_tile_width_rejected(eng):
         eng.set_tc_forward_tile(100)
 
 
-@pytest.mark.parametrize("t,k,out", [(128, 256, 256), (64, 64, 64), (130, 192, 328), (300, 2048, 384), (1000, 320, 1000)])
+@pytest.mark.parametrize("t,k,out", [(128, 256, 256), (64, 64, 64), (130, 192, 328), (300, 2048, 384), (1000, 320, 1000),
+                                     (256, 768, 3072), (200, 704, 3072), (256, 2048, 2048)])
 def test_backward_tc(eng, orc, t, k, out):
+    """the weight-gradient GEMM picks its tile width from the matrix (64 columns for the small ones here, 128 for
+    3072 x 768 and the ragged 3072 x 704, 256 for 2048 x 2048)"""
     W, tau, X, _ = _case(orc, t, k, out, t + 3 * k + out)
     packed = orc.trit_pack(W, tau)
     trit = orc.trit_unpack(packed, k).astype(np.float64)
