@@ -67,6 +67,9 @@ struct nnb_engine {
     // counts kernel launches issued through this engine (reported by the benchmark)
     unsigned long long launches = 0;
     int* dev_flags = nullptr;  // small device block: [0] error flag raised by bounded device-side waits
+    // partial products of the weight-gradient GEMM when it splits the token axis (allocated at first use)
+    float* dw_part = nullptr;
+    size_t dw_part_floats = 0;
     // While set, launch_ex marks its launches for programmatic dependent launch: the next kernel may become
     // resident and run its prologue while this one drains.  Only kernels that call pdl_wait() before their
     // first global-memory access go through launch_ex.

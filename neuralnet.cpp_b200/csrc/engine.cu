@@ -111,6 +111,7 @@ void nnb_engine_destroy(nnb_engine* e)
     cudaStreamSynchronize(e->stream);
     if (e->scratch) cudaFree(e->scratch);
     if (e->dev_flags) cudaFree(e->dev_flags);
+    if (e->dw_part) cudaFree(e->dw_part);
     if (e->pinned) cudaFreeHost(e->pinned);
     if (e->own_stream) cudaStreamDestroy(e->own_stream);
     delete e;

@@ -155,6 +155,11 @@ struct Epi {
     float* db_part;
     // EPI 0: when set, the result is rounded to bf16 and stored here (same indexing) instead of `out`
     __nv_bfloat16* out_b;
+    // EPI 1: splits > 1 cuts the contraction into that many slices of k_tiles_per_split stages; slice i is a tile of its
+    // own and stores (never accumulates) its product at out + i * split_stride
+    int splits;
+    int k_tiles_per_split;
+    size_t split_stride;
 };
 
 // KIND 0: int8 (A, B K-major, 128 k per stage).  KIND 1: bf16 (64 k per stage), A/B K- or MN-major.
@@ -179,9 +184,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_launch();  // the next kernel of the stream may take the SM as soon as this CTA leaves it
     constexpr int KE = KIND == 0 ? 128 : 64;  // contraction elements per stage
-    const int ktiles = (KC + KE - 1) / KE;
+    const int ktiles_all = (KC + KE - 1) / KE;
+    const bool split = EPI == 1 && ep.splits > 1;
+    const int kt_per = split ? ep.k_tiles_per_split : ktiles_all;
     const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
-    const int n_tiles = tiles_m * tiles_n;
+    const int mn_tiles = tiles_m * tiles_n;
+    const int n_tiles = mn_tiles * (split ? ep.splits : 1);
     // with few row tiles, CTAs that run side by side take the row tiles of one column tile, so a tile of B
     // (the weights, in the forward) comes from DRAM once and from L2 for the others
     const bool m_fast = tiles_m <= 8;
@@ -215,8 +223,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             uint32_t it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-                const int tm = m_fast ? tile % tiles_m : tile / tiles_n, tn = m_fast ? tile / tiles_m : tile % tiles_n;
-                for (int kt = 0; kt < ktiles && ok; ++kt, ++it) {
+                const int sp = tile / mn_tiles, t2 = tile - sp * mn_tiles;
+                const int tm = m_fast ? t2 % tiles_m : t2 / tiles_n, tn = m_fast ? t2 / tiles_m : t2 % tiles_n;
+                const int kt0 = sp * kt_per, kt1 = min(ktiles_all, kt0 + kt_per);
+                for (int kt = kt0; kt < kt1 && ok; ++kt, ++it) {
                     const int st = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
                     if (it >= STAGES && !mbar_wait(&empty[st], ph ^ 1, abort_flag)) { ok = false; break; }
@@ -252,6 +262,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 if (tcount >= 2 && !mbar_wait(&acc_empty[acc], ((tcount >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 const uint32_t d_tmem = tmem_base + acc * BN;
+                const int sp = tile / mn_tiles;
+                const int ktiles = min(ktiles_all, (sp + 1) * kt_per) - sp * kt_per;
                 for (int kt = 0; kt < ktiles; ++kt, ++it) {
                     const int st = it % STAGES;
                     if (!mbar_wait(&full[st], (it / STAGES) & 1, abort_flag)) { ok = false; break; }
@@ -284,11 +296,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int lc = (lane & 7) * 4, lr = lane >> 3;
         const bool aligned = (((uintptr_t)ep.out | (uintptr_t)ep.tau | (uintptr_t)ep.bias | (uintptr_t)ep.residual) & 15) == 0 &&
                              ((uintptr_t)ep.out_b & 7) == 0 &&
-                             (ep.n_mat & 3) == 0 && (ep.mat_stride & 3) == 0;
+                             (ep.n_mat & 3) == 0 && (ep.mat_stride & 3) == 0 && (ep.split_stride & 3) == 0;
         uint32_t tcount = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++tcount) {
-            const int tm = m_fast ? tile % tiles_m : tile / tiles_n, tn = m_fast ? tile / tiles_m : tile % tiles_n;
+            const int sp = tile / mn_tiles, t2 = tile - sp * mn_tiles;
+            const int tm = m_fast ? t2 % tiles_m : t2 / tiles_n, tn = m_fast ? t2 / tiles_m : t2 % tiles_n;
+            float* const outp = split ? ep.out + (size_t)sp * ep.split_stride : ep.out;
             const int acc = tcount & 1;
             const int row0 = tm * BM + quarter * 32;
             const int row = row0 + lane;
@@ -440,7 +454,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             // what a chunk needs from global memory (tau, bias, and the residual or the values to accumulate
             // into) is fetched one chunk ahead, the first chunk's before the accumulator is even ready, so
             // that DRAM latency stays off the path between tcgen05.ld and the stores
-            const float* pre_src = EPI == 0 ? ep.residual : (ep.accumulate ? ep.out : nullptr);
+            const float* pre_src = EPI == 0 ? ep.residual : (ep.accumulate ? outp : nullptr);
             float4 pre[2][8], tau4[2], bias4[2];
             auto fetch = [&](int ci, int slot) {
                 const int col0 = tn * BN + chalf * (BN / 2) + ci * 32;
@@ -517,7 +531,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                                 w2.y = *reinterpret_cast<const uint32_t*>(&hi);
                                 *reinterpret_cast<uint2*>(ep.out_b + off) = w2;
                             } else {
-                                *reinterpret_cast<float4*>(ep.out + off) = o;
+                                *reinterpret_cast<float4*>(outp + off) = o;
                             }
                         }
                     }
@@ -535,10 +549,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                             if (ep.residual) x = __fadd_rn(ep.residual[off + j], x);
                         } else {
                             x = __uint_as_float(r[j]);
-                            if (ep.accumulate) x += ep.out[off + j];
+                            if (ep.accumulate) x += outp[off + j];
                         }
                         if (EPI == 0 && ep.out_b) ep.out_b[off + j] = __float2bfloat16_rn(x);
-                        else ep.out[off + j] = x;
+                        else outp[off + j] = x;
                     }
                 }
             }
@@ -614,7 +628,7 @@ static nnb_status launch(nnb_engine* e, const CUtensorMap& ta, const CUtensorMap
         cfg = true;
     }
     int* flag = e->dev_flags;
-    const size_t tiles = ceil_div(M, BM) * ceil_div(N, BN);
+    const size_t tiles = ceil_div(M, BM) * ceil_div(N, BN) * (size_t)(EPI == 1 && ep.splits > 1 ? ep.splits : 1);
     const unsigned grid = (unsigned)(tiles < (size_t)e->sm_count ? tiles : (size_t)e->sm_count);
     launch_ex(e, kern, dim3(grid), dim3(THREADS), (size_t)SMEM_BYTES, ta, tb, ep, (int)M, (int)N, (int)KC, flag);
     e->launches++;
@@ -852,24 +866,24 @@ nnb_status launch_tc_nt(nnb_engine* e, const __nv_bfloat16* a, const __nv_bfloat
 
 // dW: dyb (T,OUT) bf16, xs (T,K) bf16; dw (OUT,K) f32 +=
 // The contraction runs over the tokens, so the tile count is fixed by the weight matrix alone: a 768 x 768 matrix is 18
-// tiles of 128 x 256 on 148 SMs.  Narrower tiles fill the machine; their cost per column rises (the A operand's
-// shared-memory reads are shared by fewer columns), which the weights below stand for.
-static int choose_dw_bn(size_t out, size_t k, int sm_count)
+// tiles of 128 x 256 on 148 SMs, each walking all the tokens (narrower tiles fill the SMs but then every CTA streams
+// both operands for all the tokens through L2, which costs as much).  Small matrices therefore split the token axis:
+// slice i of every tile is a tile of its own and leaves its product in part[i]; dw_split_reduce_kernel adds the slices
+// to dw in order, so the sum does not depend on the schedule.
+__global__ void __launch_bounds__(256)
+dw_split_reduce_kernel(const float* __restrict__ part, int splits, size_t n4, float* __restrict__ dw)
 {
-    const int cand[3] = {256, 128, 64};
-    const size_t per_col[3] = {100, 118, 167};
-    int best = 256;
-    size_t best_cost = (size_t)-1;
-    for (int i = 0; i < 3; ++i) {
-        const size_t tiles = ceil_div(out, (size_t)tc::BM) * ceil_div(k, (size_t)cand[i]);
-        const size_t cost = ceil_div(tiles, (size_t)sm_count) * cand[i] * per_col[i];
-        if (cost < best_cost) {
-            best_cost = cost;
-            best = cand[i];
-        }
+    const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= n4) return;
+    float4 a = reinterpret_cast<const float4*>(dw)[i];
+    for (int s = 0; s < splits; ++s) {
+        const float4 v = reinterpret_cast<const float4*>(part)[(size_t)s * n4 + i];
+        a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
     }
-    return best;
+    reinterpret_cast<float4*>(dw)[i] = a;
 }
+
+constexpr size_t DW_PART_FLOATS = (size_t)148 * 128 * 256;  // one 128 x 256 slice per SM
 
 nnb_status launch_tc_dw(nnb_engine* e, const __nv_bfloat16* dyb, const __nv_bfloat16* xs, size_t t, size_t k, size_t out,
                         float* dw)
@@ -879,11 +893,33 @@ nnb_status launch_tc_dw(nnb_engine* e, const __nv_bfloat16* dyb, const __nv_bflo
     NNB_TRY(make_map(&ta, dyb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, t, out, 64, 64));
     NNB_TRY(make_map(&tb, xs, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, t, k, 64, 64));
     Epi ep{dw, nullptr, nullptr, nullptr, nullptr, 1, (int)k, 0};
-    switch (choose_dw_bn(out, k, e->sm_count)) {
-        case 64: return launch<1, true, true, 1, 64>(e, ta, tb, ep, out, k, t);
-        case 128: return launch<1, true, true, 1, 128>(e, ta, tb, ep, out, k, t);
-        default: return launch<1, true, true, 1, 256>(e, ta, tb, ep, out, k, t);
+    const size_t tiles = ceil_div(out, (size_t)BM) * ceil_div(k, (size_t)256), k_tiles = ceil_div(t, (size_t)64);
+    // split while the slices fit the SMs, each keeps at least 16 stages, and the partial products fit their buffer
+    size_t splits = std::min<size_t>(std::min<size_t>((size_t)e->sm_count / tiles, k_tiles / 16), DW_PART_FLOATS / (out * k));
+    if (tiles * 2 <= (size_t)e->sm_count && splits >= 2 && (out * k) % 4 == 0 && ((uintptr_t)dw & 15) == 0) {
+        if (!e->dw_part) {
+            cudaError_t er = cudaMalloc((void**)&e->dw_part, DW_PART_FLOATS * sizeof(float));
+            if (er != cudaSuccess) {
+                cudaGetLastError();
+                NNB_FAIL(NNB_ERR_OOM, "out of device memory for the weight-gradient partial products");
+            }
+            e->dw_part_floats = DW_PART_FLOATS;
+        }
+        const size_t per = ceil_div(k_tiles, splits);
+        splits = ceil_div(k_tiles, per);  // no empty slice
+        ep.out = e->dw_part;
+        ep.accumulate = 0;
+        ep.splits = (int)splits;
+        ep.k_tiles_per_split = (int)per;
+        ep.split_stride = out * k;
+        NNB_TRY((launch<1, true, true, 1, 256>(e, ta, tb, ep, out, k, t)));
+        const size_t n4 = out * k / 4;
+        dw_split_reduce_kernel<<<(unsigned)ceil_div(n4, 256), 256, 0, e->stream>>>(e->dw_part, (int)splits, n4, dw);
+        e->launches++;
+        NNB_CHECK_LAUNCH("dw_split_reduce_kernel");
+        return NNB_OK;
     }
+    return launch<1, true, true, 1, 256>(e, ta, tb, ep, out, k, t);
 }
 
 // reads (and clears) the device error flag of the tensor-core GEMMs; synchronises the stream

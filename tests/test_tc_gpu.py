@@ -72,10 +72,10 @@ def test_forward_tile_width_rejected(eng):
 
 
 @pytest.mark.parametrize("t,k,out", [(128, 256, 256), (64, 64, 64), (130, 192, 328), (300, 2048, 384), (1000, 320, 1000),
-                                     (256, 768, 3072), (200, 704, 3072), (256, 2048, 2048)])
+                                     (2100, 192, 328), (4096, 768, 768), (3000, 704, 1000), (256, 2048, 2048)])
 def test_backward_tc(eng, orc, t, k, out):
-    """the weight-gradient GEMM picks its tile width from the matrix (64 columns for the small ones here, 128 for
-    3072 x 768 and the ragged 3072 x 704, 256 for 2048 x 2048)"""
+    """from 2048 tokens up the weight-gradient GEMM of a small matrix splits the token axis (2100 tokens: two slices, the
+    second ragged; 4096 x 768 x 768: four slices of 18 tiles; 3000 x 704 x 1000: two slices with ragged tiles)"""
     W, tau, X, _ = _case(orc, t, k, out, t + 3 * k + out)
     packed = orc.trit_pack(W, tau)
     trit = orc.trit_unpack(packed, k).astype(np.float64)
