@@ -1026,7 +1026,8 @@ scale_colsum_kernel(const float* __restrict__ dy, const float* __restrict__ tau,
     *reinterpret_cast<float2*>(part + (size_t)blockIdx.y * O + o) = make_float2(sa, sb);
 }
 
-// the same with four adjacent columns per thread (16-byte loads, eight rows in flight): out, ld multiples of 4
+// the same with four adjacent columns per thread (16-byte loads, R rows in flight): out, ld multiples of 4
+template <int R>
 __global__ void __launch_bounds__(128)
 scale_colsum4_kernel(const float* __restrict__ dy, const float* __restrict__ tau, int T, int O, int chunk,
                      __nv_bfloat16* __restrict__ out, size_t ld, float* __restrict__ part)
@@ -1037,12 +1038,12 @@ scale_colsum4_kernel(const float* __restrict__ dy, const float* __restrict__ tau
     const float4 tv = *reinterpret_cast<const float4*>(tau + o);
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     int t = t0;
-    for (; t + 8 <= t1; t += 8) {
-        float4 v[8];
+    for (; t + R <= t1; t += R) {
+        float4 v[R];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) v[u] = *reinterpret_cast<const float4*>(dy + (size_t)(t + u) * O + o);
+        for (int u = 0; u < R; ++u) v[u] = *reinterpret_cast<const float4*>(dy + (size_t)(t + u) * O + o);
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
+        for (int u = 0; u < R; ++u) {
             acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w;
             const __nv_bfloat162 p0 = __floats2bfloat162_rn(v[u].x * tv.x, v[u].y * tv.y);
             const __nv_bfloat162 p1 = __floats2bfloat162_rn(v[u].z * tv.z, v[u].w * tv.w);
@@ -1283,7 +1284,12 @@ nnb_status launch_scale_colsum(nnb_engine* e, const float* dy, const float* tau,
     const bool vec4 = out % 4 == 0 && ld % 4 == 0 && (((uintptr_t)dy | (uintptr_t)tau | (uintptr_t)part) & 15) == 0 && ((uintptr_t)dyb & 7) == 0;
     if (vec4) {
         dim3 grid4((unsigned)ceil_div(out, 512), grid.y);
-        scale_colsum4_kernel<<<grid4, 128, 0, e->stream>>>(dy, tau, (int)t, (int)out, chunk, dyb, ld, part);
+        // rows a thread keeps in flight: 4 (NNB_COLSUM_ROWS=8 for A/B runs, read once per process).  Measured on the 1B
+        // training micro-batch: cold-cache 43 us per launch with 4 rows against 59 us with 8; inside the step, where dy
+        // is partly L2-resident, 99.4-99.8 against 101.5-102.8 ms per micro-batch (three runs each, alternating)
+        static const int rows = [] { const char* ev = getenv("NNB_COLSUM_ROWS"); return ev && ev[0] == '8' ? 8 : 4; }();
+        if (rows == 4) scale_colsum4_kernel<4><<<grid4, 128, 0, e->stream>>>(dy, tau, (int)t, (int)out, chunk, dyb, ld, part);
+        else scale_colsum4_kernel<8><<<grid4, 128, 0, e->stream>>>(dy, tau, (int)t, (int)out, chunk, dyb, ld, part);
     } else {
         scale_colsum_kernel<<<grid, 128, 0, e->stream>>>(dy, tau, (int)t, (int)out, chunk, dyb, ld, part);
     }
