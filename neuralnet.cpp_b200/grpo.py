@@ -18,7 +18,7 @@ from dataclasses import dataclass
 
 import torch
 
-from .pipeline import GptRolloutSource, RolloutSpec, TensorRecord
+from .pipeline import GptRolloutSource, RolloutSpec, TensorRecord, micro_batched
 from .policy import Policy
 
 # names of the ten floats nnb_policy_train_step reports (PpoReport / GrpoReport fields of the reference,
@@ -103,20 +103,25 @@ class GrpoTrainer(_DistMixin):
         N = tokens.shape[0]
         units = torch.tensor([float(N * c.max_new)], device=tokens.device)
         units_global = float(self._allreduce(units).item()) if self.world > 1 else float(N * c.max_new)
-        mb = c.micro_batch
-        # micro-batches made of whole groups let the engine compute a group's shared prompt once
-        gs = c.group_size if mb % c.group_size == 0 else 1
         ref_lp = record.get("ref_log_prob")
-        pol.zero_grad()
-        report = torch.zeros(10, device=tokens.device)
-        for a in range(0, N, mb):
-            sl = slice(a, a + mb)
-            report += pol.train_step(tokens[sl].contiguous(), c.prompt_len, mask[sl].contiguous(),
-                                     old_logp=record["old_log_prob"][sl].contiguous(),
-                                     advantage=record["advantage"][sl].contiguous(),
-                                     ref_logp=None if ref_lp is None else ref_lp[sl].contiguous(),
-                                     units=units_global, clip_eps=c.clip_eps, kl_coef=c.kl_coef,
-                                     entropy_coef=c.entropy_coef, group_size=gs)
+
+        def run(mb):
+            # micro-batches made of whole groups let the engine compute a group's shared prompt once
+            gs = c.group_size if mb % c.group_size == 0 else 1
+            pol.zero_grad()
+            report = torch.zeros(10, device=tokens.device)
+            for a in range(0, N, mb):
+                sl = slice(a, a + mb)
+                report += pol.train_step(tokens[sl].contiguous(), c.prompt_len, mask[sl].contiguous(),
+                                         old_logp=record["old_log_prob"][sl].contiguous(),
+                                         advantage=record["advantage"][sl].contiguous(),
+                                         ref_logp=None if ref_lp is None else ref_lp[sl].contiguous(),
+                                         units=units_global, clip_eps=c.clip_eps, kl_coef=c.kl_coef,
+                                         entropy_coef=c.entropy_coef, group_size=gs)
+            return report
+
+        # a workspace that does not fit halves the micro-batch (kept for the following steps)
+        report, self._micro_batch = micro_batched(N, getattr(self, "_micro_batch", c.micro_batch), c.group_size, run)
         report[7] = units_global  # every micro-batch reports the global count: it is not a sum
         ev("train")
         if self.world > 1:

@@ -150,6 +150,26 @@ class NullMetricSink:
         pass
 
 
+
+def micro_batched(n: int, micro_batch: int, group_size: int, run):
+    """Calls run(micro_batch), which walks n sequences in slices of micro_batch, and returns (its result, the micro-batch
+    used).  The engine sizes a forward/backward workspace at the first call of a shape and refuses one that does not fit
+    (status -4) before touching the device: run is then restarted from scratch with half the micro-batch (whole prompt
+    groups while that is possible).  Gradients accumulate over a minibatch either way, so the result is the same sum."""
+    from ._lib import NnbError
+
+    mb = max(1, min(micro_batch, n))
+    while True:
+        try:
+            return run(mb), mb
+        except NnbError as ex:
+            if getattr(ex, "status", 0) != -4 or mb <= 1:
+                raise
+            half = mb // 2
+            if group_size > 1 and half >= group_size:
+                half = half // group_size * group_size
+            mb = max(1, half)
+
 @dataclass
 class RLPipelineConfig:
     batch_size: int = 1
@@ -286,7 +306,15 @@ class GptRolloutSource(RolloutSource):
                   "old_log_prob": old_lp}
         reward = self.reward_fn(tokens).contiguous()
         fields["reward"] = reward
-        gs = c.group_size if c.eval_micro_batch % c.group_size == 0 else 1
+        def evaluate(policy, pick, **kw):
+            """teacher-forced pass over all N sequences in micro-batches; halves them if the workspace does not fit"""
+            def run(mb):
+                gs = c.group_size if mb % c.group_size == 0 else 1
+                return torch.cat([policy.logprobs(tokens[a:a + mb].contiguous(), P, group_size=gs, **kw)[pick]
+                                  for a in range(0, N, mb)])
+            out, self._eval_mb = micro_batched(N, getattr(self, "_eval_mb", c.eval_micro_batch), c.group_size, run)
+            return out
+
         if c.advantage == "group":
             adv_seq = eng.group_advantage(reward, [(g * c.group_size, c.group_size) for g in range(N // c.group_size)],
                                           eps=c.advantage_eps)
@@ -295,9 +323,7 @@ class GptRolloutSource(RolloutSource):
         else:
             if not pol.cfg.value_head:
                 raise PipelineError("GptRolloutSource: advantage='gae' needs a policy with a value head")
-            vals = [pol.logprobs(tokens[a:a + c.eval_micro_batch].contiguous(), P, want_value=True, group_size=gs)[2]
-                    for a in range(0, N, c.eval_micro_batch)]
-            old_value = torch.cat(vals)
+            old_value = evaluate(pol, 2, want_value=True)
             # GaeAdvantage works on (steps, batch) with row = time
             adv_t, ret_t = eng.gae(reward.t().contiguous(), old_value.t().contiguous(), mask=mask.t().contiguous(),
                                    gamma=c.gamma, lam=c.lam)
@@ -308,8 +334,6 @@ class GptRolloutSource(RolloutSource):
             fields["return"] = ret_t.t().contiguous()
             self._mark("advantage")
         if self.ref is not None:
-            parts = [self.ref.logprobs(tokens[a:a + c.eval_micro_batch].contiguous(), P, group_size=gs)[0]
-                     for a in range(0, N, c.eval_micro_batch)]
-            fields["ref_log_prob"] = torch.cat(parts)
+            fields["ref_log_prob"] = evaluate(self.ref, 0)
         self._mark("reference")
         return TensorRecord.create(fields)

@@ -20,7 +20,7 @@ from dataclasses import dataclass
 import torch
 
 from .grpo import _DistMixin
-from .pipeline import DeterministicRng, GptRolloutSource, RolloutSpec, TensorRecord, UniformBatchSampler
+from .pipeline import DeterministicRng, GptRolloutSource, RolloutSpec, TensorRecord, UniformBatchSampler, micro_batched
 from .policy import Policy
 
 
@@ -73,17 +73,23 @@ class PpoTrainer(_DistMixin):
         n = tokens.shape[0]
         units = mask.sum().reshape(1)
         units_global = float(self._allreduce(units).item())
-        pol.zero_grad()
-        report = torch.zeros(10, device=tokens.device)
-        for a in range(0, n, c.micro_batch):
-            sl = slice(a, a + c.micro_batch)
-            report += pol.train_step(tokens[sl].contiguous(), c.prompt_len, mask[sl].contiguous(),
-                                     old_logp=mb_rec["old_log_prob"][sl].contiguous(),
-                                     advantage=mb_rec["advantage"][sl].contiguous(),
-                                     returns=mb_rec["return"][sl].contiguous(),
-                                     old_value=mb_rec["old_value"][sl].contiguous(), units=units_global,
-                                     clip_eps=c.clip_eps, entropy_coef=c.entropy_coef, value_coef=c.value_coef,
-                                     value_clip_eps=c.value_clip_eps)
+
+        def run(mb):
+            pol.zero_grad()
+            report = torch.zeros(10, device=tokens.device)
+            for a in range(0, n, mb):
+                sl = slice(a, a + mb)
+                report += pol.train_step(tokens[sl].contiguous(), c.prompt_len, mask[sl].contiguous(),
+                                         old_logp=mb_rec["old_log_prob"][sl].contiguous(),
+                                         advantage=mb_rec["advantage"][sl].contiguous(),
+                                         returns=mb_rec["return"][sl].contiguous(),
+                                         old_value=mb_rec["old_value"][sl].contiguous(), units=units_global,
+                                         clip_eps=c.clip_eps, entropy_coef=c.entropy_coef, value_coef=c.value_coef,
+                                         value_clip_eps=c.value_clip_eps)
+            return report
+
+        # a workspace that does not fit halves the micro-batch (kept for the following minibatches)
+        report, self._micro_batch = micro_batched(n, getattr(self, "_micro_batch", c.micro_batch), 1, run)
         if self.world > 1:
             self._allreduce(pol.grads_view())
             self._allreduce(report)

@@ -79,6 +79,12 @@ class _StubEngine:
     def gae(self, rewards, values, mask=None, gamma=0.99, lam=0.95):
         return rewards - values, rewards.clone()
 
+    def group_advantage(self, rewards, spans, eps=1e-6):
+        out = torch.zeros_like(rewards)
+        for f, c in spans:
+            out[f:f + c] = rewards[f:f + c] - rewards[f:f + c].mean()
+        return out
+
 
 class _StubCfg:
     value_head = True
@@ -159,3 +165,64 @@ def test_two_rank_ppo_epochs_and_minibatches():
         assert seen == [0, 1, 2, 3]
     # gradients are summed over the ranks before each optimizer step: 2 + 2
     assert all(c[1] == 4.0 for c in c0 + c1 if c[0] == "opt")
+
+
+def test_micro_batch_halves_when_the_workspace_does_not_fit(pkg):
+    """The engine refuses a training workspace that does not fit (status -4) before it touches the device; the trainers
+    then restart the accumulation with half the micro-batch (whole prompt groups while possible) and keep the smaller
+    size.  Other errors pass through."""
+    from neuralnet_cpp_b200._lib import NnbError
+    from neuralnet_cpp_b200.pipeline import micro_batched
+
+    class Tight(_StubPolicy):
+        limit = 4
+
+        def train_step(self, tokens, prompt_len, mask, units=0.0, **kw):
+            if tokens.shape[0] > self.limit:
+                err = NnbError("nnb_status -4: training workspace does not fit")
+                err.status = -4
+                raise err
+            self.groups = kw.get("group_size")
+            return super().train_step(tokens, prompt_len, mask, units=units, **kw)
+
+        def logprobs(self, tokens, prompt_len, want_value=False, group_size=1):
+            if tokens.shape[0] > 8:
+                err = NnbError("nnb_status -4: workspace does not fit")
+                err.status = -4
+                raise err
+            self.calls.append(("eval", tokens.shape[0], group_size))
+            return super().logprobs(tokens, prompt_len, want_value=want_value, group_size=group_size)
+
+    pol, ref = Tight(0), Tight(0)
+    cfg = pkg.GrpoConfig(group_size=2, prompt_len=2, max_new=3, micro_batch=16, rollout_chunk=64, kl_coef=0.04)
+    tr = pkg.GrpoTrainer(pol, ref, cfg)
+    prompts = torch.zeros((6, 2), dtype=torch.int32)  # 6 groups of 2
+    out = tr.step(prompts, lambda t: torch.arange(t.shape[0]).float(), seed=1)
+    trains = [c for c in pol.calls if c[0] == "train"]
+    # 12 sequences: 16 -> 12 (all) refused, 6 refused, 2 (6 // 2 = 3, rounded down to whole groups) accepted
+    assert [c[1] for c in trains] == [2] * 6 and pol.groups == 2
+    assert float(pol.g[0]) == 12.0 and pol.stepped == 1 and float(out["report"][7]) == 36.0
+    # the frozen policy's log-probs: 12 at once refused, 6 accepted (whole groups)
+    assert [c for c in ref.calls if c[0] == "eval"] == [("eval", 6, 2), ("eval", 6, 2)]
+    # the smaller size is kept: the next step does not try 12 again
+    pol.calls.clear()
+    tr.step(prompts, lambda t: torch.arange(t.shape[0]).float(), seed=2)
+    assert [c[1] for c in pol.calls if c[0] == "train"] == [2] * 6
+
+    # other errors, and a refusal at one sequence, are the caller's
+    def boom(mb):
+        err = NnbError("nnb_status -2: bad argument")
+        err.status = -2
+        raise err
+
+    with pytest.raises(NnbError):
+        micro_batched(8, 4, 1, boom)
+
+    def never_fits(mb):
+        err = NnbError("nnb_status -4")
+        err.status = -4
+        raise err
+
+    with pytest.raises(NnbError):
+        micro_batched(8, 4, 1, never_fits)
+    assert micro_batched(8, 4, 1, lambda mb: mb * 10) == (40, 4)
