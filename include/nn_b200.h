@@ -452,7 +452,11 @@ enum {
     NNB_REPORT_COUNT = 10
 };
 /* forward + objective + GPTModel::backward (compute_layer_gpt.hpp:545-636): gradients are ADDED to the
- * policy's gradient buffer.  d_report[NNB_REPORT_COUNT] (may be NULL) as named above. */
+ * policy's gradient buffer.  d_report[NNB_REPORT_COUNT] (may be NULL) as named above.
+ * The activations kept for the backward live in one workspace sized at the first call of a shape (n_seq, seq_len,
+ * prompt_len, group).  A workspace that does not fit the free device memory is refused with NNB_ERR_OOM before any
+ * kernel runs and before the gradient buffer is touched: call again with fewer sequences (gradients accumulate over
+ * calls, so the split does not change the update). */
 nnb_status nnb_policy_train_step(nnb_policy* p, const int32_t* d_tokens, size_t n_seq, size_t seq_len,
                                  size_t prompt_len, const nnb_objective* obj, float* d_report);
 /* The same two calls for a batch whose sequences come in groups of `group` consecutive rows that share
