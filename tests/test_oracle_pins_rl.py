@@ -138,6 +138,35 @@ def test_adamw_single_step_hand_reference(rl):
     assert np.allclose(m2, 0.1 * g, rtol=1e-4) and np.allclose(v2, 0.001 * g * g, rtol=1e-4)
 
 
+# src/optimizer_test.cpp:167-235: one AdamW step on a 3 x 4 tensor (p = 0.5 + 0.03 i, g = -0.2 + 0.02 i, lr 0.05,
+# betas 0.9 / 0.999, eps 1e-8, weight decay 0.1) against the decay-first formula, relative 1e-5; with the two writes
+# swapped the result must differ by more than 1e-6 (the order is part of the contract)
+def test_adamw_decay_first_order_case(rl):
+    f = np.float32
+    i = np.arange(12, dtype=np.float32)
+    p0, g0 = (f(0.5) + i * f(0.03)).astype(np.float32), (f(-0.2) + i * f(0.02)).astype(np.float32)
+    lr, b1, b2, eps, wd = f(0.05), f(0.9), f(0.999), f(1e-8), f(0.1)
+
+    def reference(decay_first):
+        bc1, bc2 = f(1) - b1, f(1) - b2  # t = 1
+        m = (f(1) - b1) * g0
+        v = (f(1) - b2) * g0 * g0
+        p = p0.copy()
+        if decay_first:
+            p = p * (f(1) - lr * wd)
+        p = p - lr * (m / bc1) / (np.sqrt(v / bc2) + eps)
+        if not decay_first:
+            p = p * (f(1) - lr * wd)
+        return p.astype(np.float32)
+
+    got, _, _ = rl.adamw(p0, g0, np.zeros(12), np.zeros(12), lr=0.05, t=1, wd=0.1, beta1=0.9, beta2=0.999, eps=1e-8)
+    ref = reference(True)
+    rel = np.abs(got - ref) / np.maximum(np.abs(ref), 1e-6)
+    assert rel.max() < 1e-5
+    assert np.abs(ref - reference(False)).max() > 1e-6
+    assert np.abs(got - reference(False)).max() > 1e-6
+
+
 def test_clip_grad_norm(rl):
     g, norm = rl.clip_grad_norm([3.0, 4.0], 1.0)
     assert abs(norm - 5.0) < 1e-6 and near(g, [0.6, 0.8], 1e-6)

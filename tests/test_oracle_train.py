@@ -79,3 +79,33 @@ def test_objective_matches_c_oracle():
     assert np.abs(up_lp - (up_p + up_k)).max() < 1e-6 and np.abs(up_ent - up_e).max() < 1e-7
     assert abs(rep["policy_loss"] - m["loss"]) < 1e-5 and abs(rep["kl_loss"] - kl) < 1e-6 and abs(rep["entropy_loss"] - el) < 1e-6
     assert abs(rep["clip_fraction"] - m["clip_fraction"]) < 1e-6 and abs(rep["approx_kl"] - m["approx_kl"]) < 1e-6
+
+
+def test_grpo_preset_equals_its_parts_on_the_reference_case():
+    """src/rl_grpo_test.cpp:85-151: two groups of three samples, three classes, returns {1,2,3 | 10,10,10}, old log-probs
+    0, the preset's defaults (clip 0.2, entropy coefficient 0.01, no KL term: include/neuralnet.cpp/rl_policy.hpp:848-856).
+    Group advantages {-1/s, 0, 1/s, 0, 0, 0} with s = sqrt(2/3); the preset's loss and logit gradient equal
+    ClippedPolicyObjective + EntropyBonusObjective on those advantages."""
+    from oracle_binding import OracleRL
+
+    rl = OracleRL()
+    # the reference stores logits as (classes, samples); row-major list from the test
+    lg = np.array([1, 0, 0, 0, 0, 0, 0, 1, 0, 0, 0, 0, -1, 0, 1, 0, 0, 0], np.float32).reshape(3, 6).T.copy()
+    actions = np.array([0, 1, 2, 0, 1, 2], np.int32)
+    mask = np.ones(6)
+    s = np.sqrt(2.0 / 3.0)
+    adv = rl.group_advantage([1, 2, 3, 10, 10, 10], [(0, 3), (3, 3)], eps=1e-8)
+    assert np.abs(adv - np.array([-1 / s, 0, 1 / s, 0, 0, 0])).max() < 2e-5
+    logp, ent = rl.categorical_logp_entropy(lg, actions)
+    old = np.zeros(6)
+    rep, up_lp, up_ent, _ = ot.OracleTrainer.objective(logp, ent, mask, old, adv, None, clip_eps=0.2, kl_coef=0.0,
+                                                       entropy_coef=0.01)
+    up_p, m = rl.clipped_policy(logp, old, adv, mask, 0.2)
+    el, up_e = rl.entropy_bonus(ent, mask, 0.01)
+    total = rep["policy_loss"] + rep["kl_loss"] + rep["entropy_loss"] + rep["value_loss"]
+    assert abs(total - (m["loss"] + el)) < 1e-5 and rep["kl_loss"] == 0 and rep["value_loss"] == 0
+    grad = rl.categorical_backward(lg, actions, np.asarray(up_lp, np.float32), np.asarray(up_ent, np.float32))
+    want = rl.categorical_backward(lg, actions, up_p, None) + rl.categorical_backward(lg, actions, None, up_e)
+    assert np.abs(grad - want).max() < 1e-6
+    # the second group has zero variance: its advantages, and with them its policy gradient, vanish
+    assert np.abs(rl.categorical_backward(lg, actions, up_p, None)[3:]).max() == 0
