@@ -98,3 +98,53 @@ def test_two_rank_grpo_step_host_logic():
     assert torch.equal(g0, g1) and torch.all(g0 == 36)
     assert rep0[7] == 120 and rep1[7] == 120
     assert s0 == 1 and s1 == 1
+
+
+class TightStubPolicy(StubPolicy):
+    """refuses a training micro-batch of more than `limit` sequences the way the engine refuses a workspace that does
+    not fit: status -4, nothing accumulated"""
+    limit = 4
+
+    def train_step(self, tokens, prompt_len, mask, units=0.0, **kw):
+        if tokens.shape[0] > self.limit:
+            from neuralnet_cpp_b200._lib import NnbError
+
+            err = NnbError("nnb_status -4: training workspace does not fit")
+            err.status = -4
+            raise err
+        return super().train_step(tokens, prompt_len, mask, units=units, **kw)
+
+
+def _uneven_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    sys.path.insert(0, ROOT)
+    from __graft_entry__ import load_package
+
+    pkg = load_package()
+    cfg = pkg.GrpoConfig(group_size=4, prompt_len=3, max_new=5, micro_batch=12, rollout_chunk=16)
+    # only rank 1 runs short of memory: it falls back to 4-sequence micro-batches, rank 0 keeps 12
+    pol = TightStubPolicy(rank) if rank == 1 else StubPolicy(rank)
+    tr = pkg.GrpoTrainer(pol, None, cfg)
+    prompts = torch.arange(3 * 3).reshape(3, 3).to(torch.int32) + 100 * rank
+    out = tr.step(prompts, lambda t: (t[:, 3:].sum(1) % 2).float(), seed=1)
+    q.put((rank, pol.g.clone(), [c for c in pol.calls if c[0] == "train"], float(out["report"][7]), pol.stepped))
+    dist.destroy_process_group()
+
+
+def test_ranks_may_fall_back_to_different_micro_batches():
+    """the collectives of a step come after the micro-batch loop, so a rank that halves its micro-batch still meets the
+    others at the same all-reduces and the summed gradient is the same"""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 33500 + os.getpid() % 2000
+    procs = [ctx.Process(target=_uneven_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = sorted([q.get(timeout=120) for _ in procs], key=lambda r: r[0])
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    (_, g0, t0, u0, s0), (_, g1, t1, u1, s1) = res
+    assert [c[1] for c in t0] == [12] and [c[1] for c in t1] == [4, 4, 4]
+    assert torch.equal(g0, g1) and torch.all(g0 == 36) and u0 == 120 and u1 == 120 and s0 == 1 and s1 == 1
